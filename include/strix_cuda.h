@@ -1,0 +1,142 @@
+/*
+ * strix_cuda.h -- C ABI of the B200 (sm_100a) weight accelerator for strix.rs.
+ *
+ * One `strix_cuda` handle is one accelerator bound to one CUDA device. The
+ * entry points mirror, one to one, the methods of the reference trait
+ * `WeightAccel` (crates/strix-core/src/accel.rs:147-507) that lie on the
+ * quantized-matmul hot path; each declaration cites the trait method (and the
+ * ROCm implementation) it replaces. A Rust `impl WeightAccel` binds these with
+ * a plain `extern "C"` block.
+ *
+ * Return convention (the trait has no Result at this seam, accel.rs:144-146):
+ *    1  adopted / Some(..) / true
+ *    0  declined / None / false   -- the caller keeps the weight on the CPU
+ *   <0  device or argument error; text via strix_cuda_last_error()
+ * There is no CPU fallback inside the library.
+ *
+ * Buffers named `bytes`, `x`, `xs`, `h` are HOST memory borrowed for the call;
+ * outputs `y`, `logits` are HOST memory owned by the caller. Entry points whose
+ * name ends in `_dev` take DEVICE pointers and a cudaStream_t (as void*), do no
+ * host<->device copy and do not synchronise; they exist for measurement and for
+ * callers that keep activations resident.
+ *
+ * Threading: like the reference (decode.rs:559-562) a handle is not re-entrant;
+ * serialise calls on one handle.
+ */
+#ifndef STRIX_CUDA_H
+#define STRIX_CUDA_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#if defined(__GNUC__)
+#define STRIX_API __attribute__((visibility("default")))
+#else
+#define STRIX_API
+#endif
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef struct strix_cuda strix_cuda;
+
+/* Activation arithmetic of a GEMV. F32 = the reference's q4_gemv / q8_0_gemv /
+ * q6_gemv (kernels.rs:41-69, 646-668, 607-640). Q8DOT = the integer-dot
+ * variant: x is quantised per 32 to int8 (xquant8, kernels.rs:864-876) and the
+ * dot runs in int32 (q8i_gemv :894-912, q4_gemv_dp :259-287). */
+enum { STRIX_ACT_F32 = 0, STRIX_ACT_Q8DOT = 1 };
+
+/* Elementwise op fused in front of a device-resident GEMV's activation. */
+enum {
+    STRIX_PRE_NONE = 0,
+    STRIX_PRE_RMSNORM = 1, /* x = rmsnorm(a, w, eps)        (rmsnorm_xquant, kernels.rs:101-147) */
+    STRIX_PRE_SWIGLU = 2,  /* x = silu(a) * b               (silu_xquant,    kernels.rs:151-188) */
+    STRIX_PRE_GEGLU = 3    /* x = gelu_tanh(a) * b          (geglu_xquant,   kernels.rs:190-226) */
+};
+
+typedef struct strix_cuda_opts {
+    /* Row-sharding across a group of accelerators (one process per GPU).
+     * rank r of `world` adopts rows [shard_begin(r), shard_begin(r+1)) of every
+     * uploaded weight; world <= 1 means no sharding. No counterpart in the
+     * reference, which is single-device (hip.rs:149). */
+    int rank;
+    int world;
+    /* 1 = time every launch with CUDA events and keep per-kernel totals
+     * (the reference's STRIX_PROF, decode.rs:25-69). */
+    int profile;
+    int reserved[5];
+} strix_cuda_opts;
+
+/* RocmWeightAccel::new (decode.rs:565-829). `opts` may be NULL. */
+STRIX_API int strix_cuda_create(int device, const strix_cuda_opts *opts, strix_cuda **out);
+STRIX_API void strix_cuda_destroy(strix_cuda *h);
+/* Text of the last error on this handle ("" if none). Valid until the next call. */
+STRIX_API const char *strix_cuda_last_error(strix_cuda *h);
+/* Error text for a failed strix_cuda_create (no handle exists then). */
+STRIX_API const char *strix_cuda_create_error(void);
+
+/* WeightAccel::name (accel.rs:405), ::resident_count (accel.rs:402). */
+STRIX_API const char *strix_cuda_name(strix_cuda *h);
+STRIX_API size_t strix_cuda_resident_count(strix_cuda *h);
+
+/* WeightAccel::upload_q4_0 (accel.rs:150; decode.rs:2491-2521),
+ * ::upload_q8_0 (accel.rs:163; decode.rs:2683-2714),
+ * ::upload_q6_k (accel.rs:159; decode.rs:2629-2681).
+ * `bytes` = raw GGUF blocks, row-major [out_dim][in_dim/blk][blk_bytes], copied
+ * before return. Declines (0) when in_dim is not a multiple of the block size
+ * or len != out_dim * (in_dim/blk) * blk_bytes, as the reference does. */
+STRIX_API int strix_cuda_upload_q4_0(strix_cuda *h, const char *key, const uint8_t *bytes, size_t len,
+                           size_t in_dim, size_t out_dim);
+STRIX_API int strix_cuda_upload_q8_0(strix_cuda *h, const char *key, const uint8_t *bytes, size_t len,
+                           size_t in_dim, size_t out_dim);
+STRIX_API int strix_cuda_upload_q6_k(strix_cuda *h, const char *key, const uint8_t *bytes, size_t len,
+                           size_t in_dim, size_t out_dim);
+/* WeightAccel::upload_q4_1 (accel.rs:154): declined (returns 0), the trait's default. */
+STRIX_API int strix_cuda_upload_q4_1(strix_cuda *h, const char *key, const uint8_t *bytes, size_t len,
+                           size_t in_dim, size_t out_dim);
+/* WeightAccel::upload_f32 (accel.rs:413; decode.rs:3908-3912): norm weights. */
+STRIX_API int strix_cuda_upload_f32(strix_cuda *h, const char *key, const float *data, size_t n);
+
+/* Shape of an adopted weight: rows held by THIS accelerator (its shard) and the
+ * first global row of the shard. 0 if `key` is not resident. */
+STRIX_API int strix_cuda_weight_info(strix_cuda *h, const char *key, size_t *in_dim, size_t *out_dim_total,
+                           size_t *shard_row0, size_t *shard_rows, int *ggml_type);
+
+/* WeightAccel::gemv (accel.rs:391; decode.rs:3827-3898): y = W x on a resident
+ * weight; H2D x, one launch, sync, D2H y. 0 when `key` is not resident or
+ * k != in_dim (the reference returns None). y receives this accelerator's
+ * shard rows (all rows when unsharded); y_cap is y's capacity in floats.
+ * `act` selects STRIX_ACT_F32 or STRIX_ACT_Q8DOT. */
+STRIX_API int strix_cuda_gemv(strix_cuda *h, const char *key, const float *x, size_t k, float *y, size_t y_cap,
+                    int act);
+/* WeightAccel::gemv_batch (accel.rs:397-399; decode.rs:3227-3255): n GEMVs, one
+ * sync. status[i] receives 1/0 per item as gemv would return. */
+STRIX_API int strix_cuda_gemv_batch(strix_cuda *h, size_t n, const char *const *keys, const float *const *xs,
+                          const size_t *ks, float *const *ys, const size_t *y_caps, int act, int *status);
+
+/* Device-resident GEMV: d_y[shard_rows] = W * pre(d_a, d_b) on `stream`.
+ * `pre` is a STRIX_PRE_* op: NONE reads x = d_a; RMSNORM uses d_b as the norm
+ * weight and `eps`; SWIGLU/GEGLU combine gate d_a with up d_b. No copy, no sync.
+ * Up to 3 weights that share the activation run as one launch (the reference's
+ * q4_gemv_dp2 / _dp3, kernels.rs:228-255, 324-361): pass their keys and outputs. */
+STRIX_API int strix_cuda_gemv_dev(strix_cuda *h, int nmat, const char *const *keys, const float *d_a,
+                        const float *d_b, float eps, int pre, int act, float *const *d_ys, void *stream);
+
+/* Device status word written by kernels whose bounded waits ran out
+ * (0 = clean). Synchronises `stream`. */
+STRIX_API int strix_cuda_device_status(strix_cuda *h, void *stream, uint32_t *status);
+
+/* ---- test / measurement extras (not part of the trait) ---- */
+
+/* Dequantise a resident weight back to f32 [shard_rows][in_dim] on the host:
+ * must equal dequantize_into (ggml_quant.rs:139-183) bit for bit. */
+STRIX_API int strix_cuda_dequant_to_f32(strix_cuda *h, const char *key, float *out, size_t out_cap);
+/* The activation quantiser alone (xquant8_rows, kernels.rs:1000-1013):
+ * q[n] int8 and d[n/32] f32 from x[n], n a multiple of 32. */
+STRIX_API int strix_cuda_xquant8(strix_cuda *h, const float *x, size_t n, int8_t *q, float *d);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* STRIX_CUDA_H */

@@ -1,0 +1,165 @@
+"""ctypes binding of the CPU oracle (oracle/strix_oracle.c).
+
+Test infrastructure only: imported by tests/, by ``__graft_entry__.smoke()`` and
+by ``bench.py``'s CPU-baseline legs as the checker / the timed CPU baseline. The
+shipped backend never imports it.
+"""
+import ctypes as C
+import os
+import subprocess
+
+import numpy as np
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+_SO = os.path.join(_HERE, "libstrix_oracle.so")
+
+Q4_0, Q4_1, Q8_0, Q6_K = 2, 3, 8, 14
+BLOCK_ELEMS = {Q4_0: 32, Q4_1: 32, Q8_0: 32, Q6_K: 256}
+BLOCK_BYTES = {Q4_0: 18, Q4_1: 20, Q8_0: 34, Q6_K: 210}
+
+
+def build(force=False):
+    src = os.path.join(_HERE, "strix_oracle.c")
+    if force or not os.path.exists(_SO) or os.path.getmtime(_SO) < os.path.getmtime(src):
+        subprocess.check_call(["make", "-s", "-C", _HERE] + (["-B"] if force else []))
+    return _SO
+
+
+_lib = None
+
+
+def lib():
+    global _lib
+    if _lib is None:
+        build()
+        L = C.CDLL(_SO)
+        u8p, f32p, i8p, i32p = (C.POINTER(C.c_uint8), C.POINTER(C.c_float), C.POINTER(C.c_int8),
+                                C.POINTER(C.c_int32))
+        L.so_f16_to_f32.restype = C.c_float
+        L.so_f16_to_f32.argtypes = [C.c_uint16]
+        L.so_dequantize_into.restype = C.c_int
+        L.so_dequantize_into.argtypes = [C.c_int, u8p, C.c_size_t, f32p, C.c_size_t]
+        L.so_dot_f32.restype = C.c_float
+        L.so_dot_f32.argtypes = [f32p, f32p, C.c_size_t]
+        L.so_qmatmul.restype = C.c_int
+        L.so_qmatmul.argtypes = [f32p, f32p, u8p, C.c_int, C.c_size_t, C.c_size_t, C.c_int]
+        L.so_qmatmul_batch.restype = C.c_int
+        L.so_qmatmul_batch.argtypes = [f32p, f32p, C.c_size_t, u8p, C.c_int, C.c_size_t, C.c_size_t, C.c_int]
+        L.so_rmsnorm.restype = None
+        L.so_rmsnorm.argtypes = [f32p, f32p, f32p, C.c_size_t, C.c_float]
+        L.so_swiglu.restype = None
+        L.so_swiglu.argtypes = [f32p, f32p, C.c_size_t]
+        L.so_geglu.restype = None
+        L.so_geglu.argtypes = [f32p, f32p, f32p, C.c_size_t]
+        L.so_xquant8.restype = C.c_size_t
+        L.so_xquant8.argtypes = [f32p, C.c_size_t, i8p, f32p]
+        L.so_idot_gemm.restype = C.c_int
+        L.so_idot_gemm.argtypes = [f32p, u8p, C.c_int, i8p, f32p, C.c_size_t, C.c_size_t, C.c_size_t,
+                                   i32p, C.c_int]
+        _lib = L
+    return _lib
+
+
+def _p(a, ty):
+    return a.ctypes.data_as(C.POINTER(ty))
+
+
+def _u8(b):
+    a = np.frombuffer(b, dtype=np.uint8) if not isinstance(b, np.ndarray) else b
+    return np.ascontiguousarray(a, dtype=np.uint8)
+
+
+def _f32(a):
+    return np.ascontiguousarray(a, dtype=np.float32)
+
+
+def default_threads():
+    return os.cpu_count() or 1
+
+
+def f16_to_f32(h):
+    return float(lib().so_f16_to_f32(int(h) & 0xFFFF))
+
+
+def dequantize(ty, data, n):
+    """ggml_quant.rs dequantize(): raises ValueError on the reference's error cases."""
+    b = _u8(data)
+    out = np.zeros(n, dtype=np.float32)
+    rc = lib().so_dequantize_into(ty, _p(b, C.c_uint8), b.size, _p(out, C.c_float), n)
+    if rc != 0:
+        raise ValueError({-1: "element count not a multiple of the block size",
+                          -2: "too few bytes", -3: "unsupported type"}[rc])
+    return out
+
+
+def dot_f32(a, b):
+    a, b = _f32(a), _f32(b)
+    return float(lib().so_dot_f32(_p(a, C.c_float), _p(b, C.c_float), min(a.size, b.size)))
+
+
+def qmatmul(x, data, ty, in_dim, out_dim, threads=None):
+    x, b = _f32(x), _u8(data)
+    assert x.size == in_dim
+    out = np.empty(out_dim, dtype=np.float32)
+    rc = lib().so_qmatmul(_p(out, C.c_float), _p(x, C.c_float), _p(b, C.c_uint8), ty, in_dim, out_dim,
+                          threads or default_threads())
+    if rc != 0:
+        raise ValueError("bad shape")
+    return out
+
+
+def qmatmul_batch(xs, m, data, ty, in_dim, out_dim, threads=None):
+    xs, b = _f32(xs).reshape(-1), _u8(data)
+    assert xs.size == m * in_dim
+    out = np.empty((m, out_dim), dtype=np.float32)
+    rc = lib().so_qmatmul_batch(_p(out, C.c_float), _p(xs, C.c_float), m, _p(b, C.c_uint8), ty, in_dim,
+                                out_dim, threads or default_threads())
+    if rc != 0:
+        raise ValueError("bad shape")
+    return out
+
+
+def rmsnorm(x, w, eps):
+    x, w = _f32(x), _f32(w)
+    out = np.empty_like(x)
+    lib().so_rmsnorm(_p(out, C.c_float), _p(x, C.c_float), _p(w, C.c_float), x.size, eps)
+    return out
+
+
+def swiglu(gate, up):
+    g, u = _f32(gate).copy(), _f32(up)
+    lib().so_swiglu(_p(g, C.c_float), _p(u, C.c_float), g.size)
+    return g
+
+
+def geglu(gate, up):
+    g, u = _f32(gate), _f32(up)
+    out = np.empty_like(g)
+    lib().so_geglu(_p(out, C.c_float), _p(g, C.c_float), _p(u, C.c_float), g.size)
+    return out
+
+
+def xquant8(x):
+    """Returns (q int8[n], d f32[n/32], ties)."""
+    x = _f32(x).reshape(-1)
+    assert x.size % 32 == 0
+    q = np.empty(x.size, dtype=np.int8)
+    d = np.empty(x.size // 32, dtype=np.float32)
+    ties = lib().so_xquant8(_p(x, C.c_float), x.size, _p(q, C.c_int8), _p(d, C.c_float))
+    return q, d, int(ties)
+
+
+def idot_gemm(data, ty, xq, xd, m, in_dim, out_dim, want_isums=False, threads=None):
+    """Integer-dot GEMV (m=1) / W8A8 GEMM. Returns y[m][out] (and isums[m][out][in/32])."""
+    b = _u8(data)
+    xq = np.ascontiguousarray(xq, dtype=np.int8).reshape(-1)
+    xd = _f32(xd).reshape(-1)
+    assert xq.size == m * in_dim and xd.size == m * in_dim // 32
+    y = np.empty((m, out_dim), dtype=np.float32)
+    isums = np.empty((m, out_dim, in_dim // 32), dtype=np.int32) if want_isums else None
+    rc = lib().so_idot_gemm(_p(y, C.c_float), _p(b, C.c_uint8), ty, _p(xq, C.c_int8), _p(xd, C.c_float), m,
+                            in_dim, out_dim, _p(isums, C.c_int32) if want_isums else None,
+                            threads or default_threads())
+    if rc != 0:
+        raise ValueError("bad shape or type")
+    return (y, isums) if want_isums else y

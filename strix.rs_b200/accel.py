@@ -1,0 +1,226 @@
+"""Python mirror of the reference's ``WeightAccel`` trait over the C ABI.
+
+Method names, argument meaning and the None/False "declined" convention follow
+``crates/strix-core/src/accel.rs:147-507`` so that tests read like calls into the
+reference: ``upload_q4_0(key, bytes, in_dim, out_dim) -> bool``,
+``gemv(key, x) -> array | None``, ...  Every method goes through
+``libstrix_cuda.so``; nothing is computed in Python and there is no CPU fallback:
+if the library is missing, loading raises.
+"""
+import ctypes as C
+import os
+
+import numpy as np
+
+ACT_F32, ACT_Q8DOT = 0, 1
+PRE_NONE, PRE_RMSNORM, PRE_SWIGLU, PRE_GEGLU = 0, 1, 2, 3
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+
+
+class StrixCudaError(RuntimeError):
+    pass
+
+
+def library_path():
+    return os.path.join(_HERE, "lib", "libstrix_cuda.so")
+
+
+class _Opts(C.Structure):
+    _fields_ = [("rank", C.c_int), ("world", C.c_int), ("profile", C.c_int), ("reserved", C.c_int * 5)]
+
+
+_lib = None
+
+
+def load_library():
+    """Loads libstrix_cuda.so and declares every entry point of include/strix_cuda.h."""
+    global _lib
+    if _lib is not None:
+        return _lib
+    path = library_path()
+    if not os.path.exists(path):
+        raise StrixCudaError("%s is missing: run strix.rs_b200/build.py (there is no fallback path)" % path)
+    L = C.CDLL(path)
+    H = C.c_void_p
+    u8p, f32p, sz = C.POINTER(C.c_uint8), C.POINTER(C.c_float), C.c_size_t
+    szp = C.POINTER(C.c_size_t)
+
+    def sig(name, res, *args):
+        f = getattr(L, name)
+        f.restype, f.argtypes = res, list(args)
+
+    sig("strix_cuda_create", C.c_int, C.c_int, C.POINTER(_Opts), C.POINTER(H))
+    sig("strix_cuda_destroy", None, H)
+    sig("strix_cuda_last_error", C.c_char_p, H)
+    sig("strix_cuda_create_error", C.c_char_p)
+    sig("strix_cuda_name", C.c_char_p, H)
+    sig("strix_cuda_resident_count", sz, H)
+    for q in ("q4_0", "q8_0", "q6_k", "q4_1"):
+        sig("strix_cuda_upload_" + q, C.c_int, H, C.c_char_p, u8p, sz, sz, sz)
+    sig("strix_cuda_upload_f32", C.c_int, H, C.c_char_p, f32p, sz)
+    sig("strix_cuda_weight_info", C.c_int, H, C.c_char_p, szp, szp, szp, szp, C.POINTER(C.c_int))
+    sig("strix_cuda_gemv", C.c_int, H, C.c_char_p, f32p, sz, f32p, sz, C.c_int)
+    sig("strix_cuda_gemv_batch", C.c_int, H, sz, C.POINTER(C.c_char_p), C.POINTER(f32p), szp, C.POINTER(f32p), szp,
+        C.c_int, C.POINTER(C.c_int))
+    sig("strix_cuda_gemv_dev", C.c_int, H, C.c_int, C.POINTER(C.c_char_p), C.c_void_p, C.c_void_p, C.c_float,
+        C.c_int, C.c_int, C.POINTER(C.c_void_p), C.c_void_p)
+    sig("strix_cuda_device_status", C.c_int, H, C.c_void_p, C.POINTER(C.c_uint32))
+    sig("strix_cuda_dequant_to_f32", C.c_int, H, C.c_char_p, f32p, sz)
+    sig("strix_cuda_xquant8", C.c_int, H, f32p, sz, C.POINTER(C.c_int8), f32p)
+    _lib = L
+    return L
+
+
+def shard_begin(rows, world, r):
+    """First row of rank r's shard (contiguous shards, sizes differ by at most one)."""
+    if world <= 1:
+        return 0 if r <= 0 else rows
+    q, rem = divmod(rows, world)
+    return r * q + min(r, rem)
+
+
+def _u8(b):
+    a = b if isinstance(b, np.ndarray) else np.frombuffer(b, dtype=np.uint8)
+    return np.ascontiguousarray(a.reshape(-1), dtype=np.uint8)
+
+
+def _f32(a):
+    return np.ascontiguousarray(np.asarray(a, dtype=np.float32).reshape(-1))
+
+
+def _fp(a):
+    return a.ctypes.data_as(C.POINTER(C.c_float))
+
+
+class CudaWeightAccel:
+    """``impl WeightAccel`` for one CUDA device (the hot-path methods only)."""
+
+    def __init__(self, device=0, rank=0, world=1, profile=False):
+        self._L = load_library()
+        self._h = C.c_void_p()
+        o = _Opts(rank=rank, world=world, profile=int(profile))
+        rc = self._L.strix_cuda_create(device, C.byref(o), C.byref(self._h))
+        if rc != 1:
+            self._h = None
+            raise StrixCudaError(self._L.strix_cuda_create_error().decode())
+        self.device, self.rank, self.world = device, rank, world
+
+    # -- lifetime ---------------------------------------------------------
+    def close(self):
+        if getattr(self, "_h", None):
+            self._L.strix_cuda_destroy(self._h)
+            self._h = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+    def __enter__(self):
+        return self
+
+    def __exit__(self, *a):
+        self.close()
+
+    def _check(self, rc):
+        if rc < 0:
+            raise StrixCudaError(self._L.strix_cuda_last_error(self._h).decode())
+        return rc
+
+    # -- trait methods ----------------------------------------------------
+    def name(self):
+        return self._L.strix_cuda_name(self._h).decode()
+
+    def resident_count(self):
+        return int(self._L.strix_cuda_resident_count(self._h))
+
+    def _upload(self, fn, key, data, in_dim, out_dim):
+        b = _u8(data)
+        rc = fn(self._h, key.encode(), b.ctypes.data_as(C.POINTER(C.c_uint8)), b.size, in_dim, out_dim)
+        return self._check(rc) == 1
+
+    def upload_q4_0(self, key, data, in_dim, out_dim):
+        return self._upload(self._L.strix_cuda_upload_q4_0, key, data, in_dim, out_dim)
+
+    def upload_q4_1(self, key, data, in_dim, out_dim):
+        return self._upload(self._L.strix_cuda_upload_q4_1, key, data, in_dim, out_dim)
+
+    def upload_q8_0(self, key, data, in_dim, out_dim):
+        return self._upload(self._L.strix_cuda_upload_q8_0, key, data, in_dim, out_dim)
+
+    def upload_q6_k(self, key, data, in_dim, out_dim):
+        return self._upload(self._L.strix_cuda_upload_q6_k, key, data, in_dim, out_dim)
+
+    def upload_f32(self, key, data):
+        a = _f32(data)
+        self._check(self._L.strix_cuda_upload_f32(self._h, key.encode(), _fp(a), a.size))
+
+    def weight_info(self, key):
+        """None, or dict(in_dim, out_dim, row0, rows, ggml_type) for an adopted weight."""
+        v = [C.c_size_t() for _ in range(4)]
+        t = C.c_int()
+        rc = self._check(self._L.strix_cuda_weight_info(self._h, key.encode(), *[C.byref(x) for x in v], C.byref(t)))
+        if rc == 0:
+            return None
+        return dict(in_dim=v[0].value, out_dim=v[1].value, row0=v[2].value, rows=v[3].value, ggml_type=t.value)
+
+    def gemv(self, key, x, act=ACT_F32):
+        """y = W x, or None when `key` is not resident or len(x) != in_dim."""
+        info = self.weight_info(key)
+        if info is None:
+            return None
+        xa = _f32(x)
+        y = np.empty(info["rows"], dtype=np.float32)
+        rc = self._check(self._L.strix_cuda_gemv(self._h, key.encode(), _fp(xa), xa.size, _fp(y), y.size, act))
+        return y if rc == 1 else None
+
+    def gemv_batch(self, calls, act=ACT_F32):
+        """calls = [(key, x), ...] -> [array | None, ...] with one device sync."""
+        n = len(calls)
+        if n == 0:
+            return []
+        infos = [self.weight_info(k) for k, _ in calls]
+        xs = [_f32(x) for _, x in calls]
+        ys = [np.empty(i["rows"] if i else 0, dtype=np.float32) for i in infos]
+        keys = (C.c_char_p * n)(*[k.encode() for k, _ in calls])
+        xp = (C.POINTER(C.c_float) * n)(*[_fp(x) for x in xs])
+        yp = (C.POINTER(C.c_float) * n)(*[_fp(y) for y in ys])
+        ks = (C.c_size_t * n)(*[x.size for x in xs])
+        yc = (C.c_size_t * n)(*[y.size for y in ys])
+        st = (C.c_int * n)()
+        self._check(self._L.strix_cuda_gemv_batch(self._h, n, keys, xp, ks, yp, yc, act, st))
+        return [ys[i] if (infos[i] is not None and st[i] == 1) else None for i in range(n)]
+
+    # -- device-resident form (pointers are ints: torch ``tensor.data_ptr()``) ----
+    def gemv_dev(self, keys, d_a, d_ys, d_b=0, eps=0.0, pre=PRE_NONE, act=ACT_F32, stream=0):
+        n = len(keys)
+        kk = (C.c_char_p * n)(*[k.encode() for k in keys])
+        yy = (C.c_void_p * n)(*[int(p) for p in d_ys])
+        rc = self._check(self._L.strix_cuda_gemv_dev(self._h, n, kk, C.c_void_p(int(d_a)),
+                                                    C.c_void_p(int(d_b)) if d_b else None, float(eps), pre, act, yy,
+                                                    C.c_void_p(int(stream)) if stream else None))
+        return rc == 1
+
+    def device_status(self, stream=0):
+        s = C.c_uint32()
+        self._check(self._L.strix_cuda_device_status(self._h, C.c_void_p(int(stream)) if stream else None, C.byref(s)))
+        return s.value
+
+    # -- test / measurement extras ---------------------------------------
+    def dequant_to_f32(self, key):
+        info = self.weight_info(key)
+        if info is None:
+            return None
+        out = np.empty((info["rows"], info["in_dim"]), dtype=np.float32)
+        self._check(self._L.strix_cuda_dequant_to_f32(self._h, key.encode(), _fp(out), out.size))
+        return out
+
+    def xquant8(self, x):
+        xa = _f32(x)
+        q = np.empty(xa.size, dtype=np.int8)
+        d = np.empty(xa.size // 32, dtype=np.float32)
+        self._check(self._L.strix_cuda_xquant8(self._h, _fp(xa), xa.size, q.ctypes.data_as(C.POINTER(C.c_int8)),
+                                               _fp(d)))
+        return q, d

@@ -1,0 +1,440 @@
+// Host side of the accelerator: the handle, resident-weight bookkeeping, and the
+// extern "C" entry points declared in include/strix_cuda.h.
+//
+// Mirrors RocmWeightAccel (crates/strix-backend-rocm/src/decode.rs:445-557,
+// 2491-2714, 3227-3297, 3827-3912) for the quantized-matmul path only. There is
+// no CPU fallback: a call either runs on the GPU, declines (0) so that the caller
+// keeps the weight on its own CPU path, or fails (<0).
+#include <cuda_runtime.h>
+
+#include <algorithm>
+#include <cstdio>
+#include <cstring>
+#include <string>
+#include <unordered_map>
+#include <vector>
+
+#include "accel.h"
+
+using namespace strix;
+
+static thread_local std::string g_create_error;
+
+#define CU_TRY(h, expr)                                                                                  \
+    do {                                                                                                 \
+        cudaError_t _e = (expr);                                                                         \
+        if (_e != cudaSuccess) {                                                                         \
+            (h)->err = std::string(#expr) + ": " + cudaGetErrorString(_e);                               \
+            return -1;                                                                                   \
+        }                                                                                                \
+    } while (0)
+
+namespace strix {
+
+size_t shard_begin(size_t rows, int world, int r) {
+    if (world <= 1) return r <= 0 ? 0 : rows;
+    size_t q = rows / (size_t)world, rem = rows % (size_t)world;
+    return (size_t)r * q + std::min((size_t)r, rem);
+}
+
+int ensure_f32(strix_cuda *h, DevBuf &b, size_t n) {
+    if (b.cap >= n) return 1;
+    if (b.p) cudaFree(b.p);
+    b.p = nullptr;
+    b.cap = 0;
+    size_t want = std::max<size_t>(n, 4096);
+    CU_TRY(h, cudaMalloc(&b.p, want * sizeof(float)));
+    b.cap = want;
+    return 1;
+}
+
+int ensure_pinned(strix_cuda *h, PinBuf &b, size_t bytes) {
+    if (b.cap >= bytes) return 1;
+    if (b.p) cudaFreeHost(b.p);
+    b.p = nullptr;
+    b.cap = 0;
+    size_t want = std::max<size_t>(bytes, 1 << 16);
+    CU_TRY(h, cudaMallocHost(&b.p, want));
+    b.cap = want;
+    return 1;
+}
+
+const Resident *find_weight(strix_cuda *h, const char *key) {
+    auto it = h->weights.find(key);
+    return it == h->weights.end() ? nullptr : &it->second;
+}
+
+}  // namespace strix
+
+static int upload_quant(strix_cuda *h, int fmt, const char *key, const uint8_t *bytes, size_t len, size_t in_dim,
+                        size_t out_dim) {
+    if (!h || !key || !bytes) return -1;
+    h->err.clear();
+    const size_t be = gguf_block_elems(fmt), bb = gguf_block_bytes(fmt);
+    // the reference declines, it does not fail, on these (decode.rs:2492-2499, 2630-2636, 2684-2691)
+    if (in_dim == 0 || in_dim % be != 0) return 0;
+    const size_t nb = in_dim / be;
+    if (len != nb * out_dim * bb) return 0;
+    if (in_dim > 0x7fffffffu || out_dim > 0x7fffffffu) return 0;
+    CU_TRY(h, cudaSetDevice(h->device));
+
+    Resident r{};
+    r.fmt = fmt;
+    r.L = make_layout(fmt, (uint32_t)in_dim);
+    r.out_total = out_dim;
+    r.row0 = shard_begin(out_dim, h->world, h->rank);
+    r.rows = shard_begin(out_dim, h->world, h->rank + 1) - r.row0;
+    {
+        // the shared-memory pipeline must be able to hold two stages of one row
+        GemvArgs probe{};
+        probe.L = r.L;
+        probe.nmat = 1;
+        probe.mat[0].rows = (uint32_t)std::max<size_t>(r.rows, 1);
+        if (!gemv_plan(probe, h->num_sms, h->smem_optin)) return 0;
+    }
+    r.bytes = r.rows * (size_t)r.L.row_stride;
+    CU_TRY(h, cudaMalloc(&r.dev, std::max<size_t>(r.bytes, 16)));
+
+    // Raw GGUF bytes go up in row chunks; a kernel splits each chunk into planes.
+    const size_t raw_row = nb * bb;
+    const size_t chunk_rows = std::max<size_t>(1, (size_t)(128u << 20) / raw_row);
+    uint8_t *d_raw = nullptr;
+    cudaError_t e = cudaMalloc(&d_raw, std::min(chunk_rows, std::max<size_t>(r.rows, 1)) * raw_row);
+    if (e != cudaSuccess) {
+        cudaFree(r.dev);
+        h->err = std::string("upload staging: ") + cudaGetErrorString(e);
+        return -1;
+    }
+    for (size_t at = 0; at < r.rows && e == cudaSuccess; at += chunk_rows) {
+        const size_t n = std::min(chunk_rows, r.rows - at);
+        e = cudaMemcpyAsync(d_raw, bytes + (r.row0 + at) * raw_row, n * raw_row, cudaMemcpyHostToDevice, h->stream);
+        if (e == cudaSuccess)
+            e = launch_repack(fmt, d_raw, r.dev + at * (size_t)r.L.row_stride, r.L, (uint32_t)n, h->stream);
+        if (e == cudaSuccess) e = cudaStreamSynchronize(h->stream);  // `bytes` is borrowed; d_raw is reused
+    }
+    cudaFree(d_raw);
+    if (e != cudaSuccess) {
+        cudaFree(r.dev);
+        h->err = std::string("upload: ") + cudaGetErrorString(e);
+        return -1;
+    }
+    auto it = h->weights.find(key);
+    if (it != h->weights.end()) {
+        cudaFree(it->second.dev);
+        it->second = r;
+    } else {
+        h->weights.emplace(key, r);
+    }
+    return 1;
+}
+
+// One GEMV launch over up to 3 resident weights that share the activation.
+static int gemv_launch(strix_cuda *h, int nmat, const Resident *const *ws, const float *d_a, const float *d_b,
+                       float eps, int pre, int act, float *const *d_ys, cudaStream_t stream) {
+    if (nmat < 1 || nmat > GEMV_MAX_MATS) {
+        h->err = "gemv: between 1 and 3 weights per launch";
+        return -1;
+    }
+    if (act != STRIX_ACT_F32 && act != STRIX_ACT_Q8DOT) {
+        h->err = "gemv: unknown activation mode";
+        return -1;
+    }
+    GemvArgs a{};
+    a.nmat = nmat;
+    a.L = ws[0]->L;
+    for (int m = 0; m < nmat; m++) {
+        if (ws[m]->fmt != ws[0]->fmt || ws[m]->L.in_dim != ws[0]->L.in_dim) {
+            h->err = "gemv: fused weights must share format and in_dim";
+            return -1;
+        }
+        a.mat[m].w = ws[m]->dev;
+        a.mat[m].y = d_ys[m];
+        a.mat[m].rows = (uint32_t)ws[m]->rows;
+    }
+    a.a = d_a;
+    a.b = d_b;
+    a.eps = eps;
+    a.pre = pre;
+    a.act = act;
+    a.status = h->d_status;
+    if (!gemv_plan(a, h->num_sms, h->smem_optin)) {
+        h->err = "gemv: in_dim too large for the shared-memory pipeline";
+        return -1;
+    }
+    CU_TRY(h, launch_gemv(a, stream));
+    return 1;
+}
+
+extern "C" {
+
+int strix_cuda_create(int device, const strix_cuda_opts *opts, strix_cuda **out) {
+    if (!out) return -1;
+    *out = nullptr;
+    g_create_error.clear();
+    cudaError_t e = cudaSetDevice(device);
+    if (e != cudaSuccess) {
+        g_create_error = std::string("cudaSetDevice: ") + cudaGetErrorString(e);
+        return -1;
+    }
+    cudaDeviceProp p{};
+    e = cudaGetDeviceProperties(&p, device);
+    if (e != cudaSuccess) {
+        g_create_error = std::string("cudaGetDeviceProperties: ") + cudaGetErrorString(e);
+        return -1;
+    }
+    if (p.major != 10) {
+        // Kernels are built for sm_100a only; there is no other code path.
+        g_create_error = std::string("device ") + p.name + " is not sm_100 (Blackwell B200); no fallback exists";
+        return -1;
+    }
+    strix_cuda *h = new strix_cuda();
+    h->device = device;
+    h->rank = opts ? opts->rank : 0;
+    h->world = opts && opts->world > 1 ? opts->world : 1;
+    h->profile = opts ? opts->profile : 0;
+    if (h->rank < 0 || h->rank >= h->world) {
+        g_create_error = "rank outside [0, world)";
+        delete h;
+        return -1;
+    }
+    h->num_sms = p.multiProcessorCount;
+    h->smem_optin = p.sharedMemPerBlockOptin;
+    h->name = std::string("cuda:") + std::to_string(device) + " " + p.name + " (sm_" + std::to_string(p.major) +
+              std::to_string(p.minor) + "a)";
+    e = cudaStreamCreateWithFlags(&h->stream, cudaStreamNonBlocking);
+    if (e == cudaSuccess) e = cudaMalloc(&h->d_status, sizeof(uint32_t));
+    if (e == cudaSuccess) e = cudaMemset(h->d_status, 0, sizeof(uint32_t));
+    if (e == cudaSuccess) e = gemv_prepare_device(h->smem_optin);
+    if (e != cudaSuccess) {
+        g_create_error = std::string("create: ") + cudaGetErrorString(e);
+        if (h->d_status) cudaFree(h->d_status);
+        if (h->stream) cudaStreamDestroy(h->stream);
+        delete h;
+        return -1;
+    }
+    *out = h;
+    return 1;
+}
+
+void strix_cuda_destroy(strix_cuda *h) {
+    if (!h) return;
+    cudaSetDevice(h->device);
+    cudaStreamSynchronize(h->stream);
+    for (auto &kv : h->weights) cudaFree(kv.second.dev);
+    for (auto &kv : h->f32s) cudaFree(kv.second.p);
+    if (h->x.p) cudaFree(h->x.p);
+    if (h->y.p) cudaFree(h->y.p);
+    if (h->pin_in.p) cudaFreeHost(h->pin_in.p);
+    if (h->pin_out.p) cudaFreeHost(h->pin_out.p);
+    cudaFree(h->d_status);
+    cudaStreamDestroy(h->stream);
+    delete h;
+}
+
+const char *strix_cuda_last_error(strix_cuda *h) { return h ? h->err.c_str() : ""; }
+const char *strix_cuda_create_error(void) { return g_create_error.c_str(); }
+const char *strix_cuda_name(strix_cuda *h) { return h ? h->name.c_str() : ""; }
+size_t strix_cuda_resident_count(strix_cuda *h) { return h ? h->weights.size() : 0; }
+
+int strix_cuda_upload_q4_0(strix_cuda *h, const char *key, const uint8_t *bytes, size_t len, size_t in_dim,
+                           size_t out_dim) {
+    return upload_quant(h, FMT_Q4_0, key, bytes, len, in_dim, out_dim);
+}
+int strix_cuda_upload_q8_0(strix_cuda *h, const char *key, const uint8_t *bytes, size_t len, size_t in_dim,
+                           size_t out_dim) {
+    return upload_quant(h, FMT_Q8_0, key, bytes, len, in_dim, out_dim);
+}
+int strix_cuda_upload_q6_k(strix_cuda *h, const char *key, const uint8_t *bytes, size_t len, size_t in_dim,
+                           size_t out_dim) {
+    return upload_quant(h, FMT_Q6_K, key, bytes, len, in_dim, out_dim);
+}
+int strix_cuda_upload_q4_1(strix_cuda *, const char *, const uint8_t *, size_t, size_t, size_t) { return 0; }
+
+int strix_cuda_upload_f32(strix_cuda *h, const char *key, const float *data, size_t n) {
+    if (!h || !key || !data) return -1;
+    h->err.clear();
+    CU_TRY(h, cudaSetDevice(h->device));
+    DevBuf b{};
+    CU_TRY(h, cudaMalloc(&b.p, std::max<size_t>(n, 4) * sizeof(float)));
+    b.cap = n;
+    cudaError_t e = cudaMemcpy(b.p, data, n * sizeof(float), cudaMemcpyHostToDevice);
+    if (e != cudaSuccess) {
+        cudaFree(b.p);
+        h->err = std::string("upload_f32: ") + cudaGetErrorString(e);
+        return -1;
+    }
+    auto it = h->f32s.find(key);
+    if (it != h->f32s.end()) {
+        cudaFree(it->second.p);
+        it->second = b;
+    } else {
+        h->f32s.emplace(key, b);
+    }
+    return 1;
+}
+
+int strix_cuda_weight_info(strix_cuda *h, const char *key, size_t *in_dim, size_t *out_dim_total,
+                           size_t *shard_row0, size_t *shard_rows, int *ggml_type) {
+    if (!h || !key) return -1;
+    const Resident *r = find_weight(h, key);
+    if (!r) return 0;
+    if (in_dim) *in_dim = r->L.in_dim;
+    if (out_dim_total) *out_dim_total = r->out_total;
+    if (shard_row0) *shard_row0 = r->row0;
+    if (shard_rows) *shard_rows = r->rows;
+    if (ggml_type) *ggml_type = r->fmt == FMT_Q4_0 ? GGML_Q4_0 : r->fmt == FMT_Q8_0 ? GGML_Q8_0 : GGML_Q6_K;
+    return 1;
+}
+
+int strix_cuda_gemv_batch(strix_cuda *h, size_t n, const char *const *keys, const float *const *xs,
+                          const size_t *ks, float *const *ys, const size_t *y_caps, int act, int *status) {
+    if (!h || (n && (!keys || !xs || !ks || !ys || !y_caps))) return -1;
+    h->err.clear();
+    CU_TRY(h, cudaSetDevice(h->device));
+    // lay the n activations and n outputs out back to back in the staging buffers
+    std::vector<const Resident *> ws(n, nullptr);
+    std::vector<size_t> xoff(n, 0), yoff(n, 0);
+    size_t xtot = 0, ytot = 0;
+    int any = 0;
+    for (size_t i = 0; i < n; i++) {
+        const Resident *r = find_weight(h, keys[i]);
+        // the reference returns None for an unknown key or a length mismatch (decode.rs:3833-3836)
+        if (!r || ks[i] != r->L.in_dim || y_caps[i] < r->rows) {
+            if (status) status[i] = 0;
+            continue;
+        }
+        ws[i] = r;
+        xoff[i] = xtot;
+        yoff[i] = ytot;
+        xtot += (r->L.in_dim + 3) & ~(size_t)3;  // keep every x 16-byte aligned
+        ytot += r->rows;
+        if (status) status[i] = 1;
+        any = 1;
+    }
+    if (!any) return n ? 0 : 1;
+    if (ensure_f32(h, h->x, xtot) < 0 || ensure_f32(h, h->y, std::max<size_t>(ytot, 1)) < 0) return -1;
+    if (ensure_pinned(h, h->pin_in, xtot * 4) < 0 || ensure_pinned(h, h->pin_out, std::max<size_t>(ytot, 1) * 4) < 0)
+        return -1;
+    float *pin = static_cast<float *>(h->pin_in.p), *pout = static_cast<float *>(h->pin_out.p);
+    for (size_t i = 0; i < n; i++)
+        if (ws[i]) memcpy(pin + xoff[i], xs[i], ws[i]->L.in_dim * sizeof(float));
+    CU_TRY(h, cudaMemcpyAsync(h->x.p, pin, xtot * 4, cudaMemcpyHostToDevice, h->stream));
+    for (size_t i = 0; i < n; i++) {
+        if (!ws[i]) continue;
+        const Resident *w1[1] = {ws[i]};
+        float *y1[1] = {h->y.p + yoff[i]};
+        if (gemv_launch(h, 1, w1, h->x.p + xoff[i], nullptr, 0.f, STRIX_PRE_NONE, act, y1, h->stream) < 0) return -1;
+    }
+    if (ytot) CU_TRY(h, cudaMemcpyAsync(pout, h->y.p, ytot * 4, cudaMemcpyDeviceToHost, h->stream));
+    uint32_t st = 0;
+    CU_TRY(h, cudaMemcpyAsync(&h->status_host, h->d_status, 4, cudaMemcpyDeviceToHost, h->stream));
+    CU_TRY(h, cudaStreamSynchronize(h->stream));
+    st = h->status_host;
+    if (st != 0) {
+        h->err = "gemv: device status " + std::to_string(st) + " (a bounded wait ran out)";
+        cudaMemsetAsync(h->d_status, 0, 4, h->stream);
+        return -2;
+    }
+    for (size_t i = 0; i < n; i++)
+        if (ws[i]) memcpy(ys[i], pout + yoff[i], ws[i]->rows * sizeof(float));
+    return 1;
+}
+
+int strix_cuda_gemv(strix_cuda *h, const char *key, const float *x, size_t k, float *y, size_t y_cap, int act) {
+    if (!h || !key || !x || !y) return -1;
+    int status = 0;
+    const char *keys[1] = {key};
+    const float *xs[1] = {x};
+    float *ys[1] = {y};
+    int rc = strix_cuda_gemv_batch(h, 1, keys, xs, &k, ys, &y_cap, act, &status);
+    if (rc < 0) return rc;
+    return status;
+}
+
+int strix_cuda_gemv_dev(strix_cuda *h, int nmat, const char *const *keys, const float *d_a, const float *d_b,
+                        float eps, int pre, int act, float *const *d_ys, void *stream) {
+    if (!h || !keys || !d_a || !d_ys) return -1;
+    h->err.clear();
+    if (nmat < 1 || nmat > GEMV_MAX_MATS) {
+        h->err = "gemv_dev: between 1 and 3 weights per launch";
+        return -1;
+    }
+    if (pre != STRIX_PRE_NONE && !d_b) {
+        h->err = "gemv_dev: this prologue needs d_b";
+        return -1;
+    }
+    CU_TRY(h, cudaSetDevice(h->device));
+    const Resident *ws[GEMV_MAX_MATS];
+    for (int m = 0; m < nmat; m++) {
+        ws[m] = find_weight(h, keys[m]);
+        if (!ws[m]) return 0;
+    }
+    return gemv_launch(h, nmat, ws, d_a, d_b, eps, pre, act, d_ys, static_cast<cudaStream_t>(stream));
+}
+
+int strix_cuda_device_status(strix_cuda *h, void *stream, uint32_t *status) {
+    if (!h || !status) return -1;
+    h->err.clear();
+    CU_TRY(h, cudaSetDevice(h->device));
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    CU_TRY(h, cudaMemcpyAsync(&h->status_host, h->d_status, 4, cudaMemcpyDeviceToHost, s));
+    CU_TRY(h, cudaStreamSynchronize(s));
+    *status = h->status_host;
+    return 1;
+}
+
+int strix_cuda_dequant_to_f32(strix_cuda *h, const char *key, float *out, size_t out_cap) {
+    if (!h || !key || !out) return -1;
+    h->err.clear();
+    const Resident *r = find_weight(h, key);
+    if (!r) return 0;
+    const size_t n = r->rows * (size_t)r->L.in_dim;
+    if (out_cap < n) {
+        h->err = "dequant_to_f32: output too small";
+        return -1;
+    }
+    if (n == 0) return 1;
+    CU_TRY(h, cudaSetDevice(h->device));
+    float *d = nullptr;
+    CU_TRY(h, cudaMalloc(&d, n * sizeof(float)));
+    cudaError_t e = launch_dequant(r->dev, d, r->L, (uint32_t)r->rows, h->stream);
+    if (e == cudaSuccess) e = cudaMemcpyAsync(out, d, n * sizeof(float), cudaMemcpyDeviceToHost, h->stream);
+    if (e == cudaSuccess) e = cudaStreamSynchronize(h->stream);
+    cudaFree(d);
+    if (e != cudaSuccess) {
+        h->err = std::string("dequant_to_f32: ") + cudaGetErrorString(e);
+        return -1;
+    }
+    return 1;
+}
+
+int strix_cuda_xquant8(strix_cuda *h, const float *x, size_t n, int8_t *q, float *d) {
+    if (!h || !x || !q || !d) return -1;
+    h->err.clear();
+    if (n % 32 != 0 || n > 0x7fffffffu) {
+        h->err = "xquant8: n must be a multiple of 32";
+        return -1;
+    }
+    if (n == 0) return 1;
+    CU_TRY(h, cudaSetDevice(h->device));
+    float *dx = nullptr, *dd = nullptr;
+    int8_t *dq = nullptr;
+    cudaError_t e = cudaMalloc(&dx, n * 4);
+    if (e == cudaSuccess) e = cudaMalloc(&dd, n / 32 * 4);
+    if (e == cudaSuccess) e = cudaMalloc(&dq, n);
+    if (e == cudaSuccess) e = cudaMemcpyAsync(dx, x, n * 4, cudaMemcpyHostToDevice, h->stream);
+    if (e == cudaSuccess) e = launch_xquant8(dx, dq, dd, (uint32_t)n, h->stream);
+    if (e == cudaSuccess) e = cudaMemcpyAsync(q, dq, n, cudaMemcpyDeviceToHost, h->stream);
+    if (e == cudaSuccess) e = cudaMemcpyAsync(d, dd, n / 32 * 4, cudaMemcpyDeviceToHost, h->stream);
+    if (e == cudaSuccess) e = cudaStreamSynchronize(h->stream);
+    cudaFree(dx);
+    cudaFree(dd);
+    cudaFree(dq);
+    if (e != cudaSuccess) {
+        h->err = std::string("xquant8: ") + cudaGetErrorString(e);
+        return -1;
+    }
+    return 1;
+}
+
+}  // extern "C"

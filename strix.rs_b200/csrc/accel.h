@@ -1,0 +1,58 @@
+// Internal definition of the accelerator handle (shared by the .cu files that
+// implement groups of C-ABI entry points).
+#pragma once
+#include <cuda_runtime.h>
+
+#include <string>
+#include <unordered_map>
+
+#include "kernels.h"
+#include "strix_cuda.h"
+
+namespace strix {
+
+// One adopted weight: this accelerator's shard of rows in the row-planar layout.
+struct Resident {
+    int fmt;
+    RowLayout L;
+    size_t out_total;  // rows of the whole weight
+    size_t row0;       // first global row held here
+    size_t rows;       // rows held here
+    uint8_t *dev;
+    size_t bytes;
+};
+
+struct DevBuf {
+    float *p = nullptr;
+    size_t cap = 0;  // floats
+};
+struct PinBuf {
+    void *p = nullptr;
+    size_t cap = 0;  // bytes
+};
+
+}  // namespace strix
+
+struct strix_cuda {
+    int device = 0;
+    int rank = 0, world = 1, profile = 0;
+    int num_sms = 0;
+    size_t smem_optin = 0;
+    std::string name, err;
+    cudaStream_t stream = nullptr;
+    uint32_t *d_status = nullptr;
+    uint32_t status_host = 0;
+    std::unordered_map<std::string, strix::Resident> weights;
+    std::unordered_map<std::string, strix::DevBuf> f32s;
+    // staging for the host-pointer entry points (grown on demand, never shrunk; like the
+    // reference's persistent gemv_x / gemv_y, decode.rs:3827-3832)
+    strix::DevBuf x, y;
+    strix::PinBuf pin_in, pin_out;
+};
+
+namespace strix {
+size_t shard_begin(size_t rows, int world, int r);
+int ensure_f32(strix_cuda *h, DevBuf &b, size_t n);
+int ensure_pinned(strix_cuda *h, PinBuf &b, size_t bytes);
+const Resident *find_weight(strix_cuda *h, const char *key);
+}  // namespace strix

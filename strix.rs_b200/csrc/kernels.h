@@ -1,0 +1,58 @@
+// Host-callable launchers of the CUDA kernels (internal to the library).
+#pragma once
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "layout.h"
+
+namespace strix {
+
+cudaError_t launch_repack(int fmt, const uint8_t *d_raw, uint8_t *d_res, const RowLayout &L, uint32_t rows,
+                          cudaStream_t stream);
+cudaError_t launch_dequant(const uint8_t *d_res, float *d_out, const RowLayout &L, uint32_t rows,
+                           cudaStream_t stream);
+
+// ---- dequant-GEMV -------------------------------------------------------
+constexpr int GEMV_MAX_MATS = 3;
+constexpr int GEMV_MAX_STAGES = 8;
+constexpr int GEMV_MAX_WARPS = 20;  // 640 threads per CTA, one CTA per SM
+
+struct GemvMat {
+    const uint8_t *w;  // resident rows of this accelerator's shard
+    float *y;          // output, one float per resident row
+    uint32_t rows;
+    uint32_t tile0;  // index of this matrix's first tile in the launch-wide tile list
+};
+
+struct GemvArgs {
+    GemvMat mat[GEMV_MAX_MATS];
+    int nmat;
+    RowLayout L;
+    const float *a;  // activation (or gate) vector, in_dim floats
+    const float *b;  // norm weight (RMSNORM) or up vector (SWIGLU/GEGLU); unused for NONE
+    float eps;
+    int pre;  // STRIX_PRE_*
+    int act;  // STRIX_ACT_*
+    uint32_t rows_per_tile;
+    uint32_t n_tiles;
+    uint32_t stage_bytes;  // multiple of 128
+    uint32_t n_stages;
+    uint32_t wc;     // warps that split a row's K range between them
+    uint32_t slots;  // groups of wc warps, each working on different rows of a tile
+    uint32_t nch;    // 32-unit chunks of K owned by one warp (1..4)
+    uint32_t grid;
+    uint32_t smem_bytes;
+    uint32_t *status;
+};
+
+// Fills the launch geometry (rows_per_tile .. smem_bytes, tile0 of each matrix)
+// from L, mat[].rows and the device's SM count. Returns false when in_dim is
+// too large for the shared-memory pipeline.
+bool gemv_plan(GemvArgs &a, int num_sms, size_t smem_optin);
+cudaError_t gemv_prepare_device(size_t smem_optin);  // opt in to large dynamic shared memory, once per device
+cudaError_t launch_gemv(const GemvArgs &a, cudaStream_t stream);
+
+// The activation quantiser on its own: q[n] int8, d[n/32] f32 from x[n].
+cudaError_t launch_xquant8(const float *d_x, int8_t *d_q, float *d_d, uint32_t n, cudaStream_t stream);
+
+}  // namespace strix

@@ -1,0 +1,41 @@
+"""The C-ABI library loads without a GPU and exports every symbol the header declares."""
+import ctypes
+import os
+import re
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def declared_symbols():
+    names = []
+    for fn in sorted(os.listdir(os.path.join(ROOT, "include"))):
+        if fn.endswith(".h"):
+            txt = open(os.path.join(ROOT, "include", fn)).read()
+            names += re.findall(r"STRIX_API[^;(]*?\b(strix_cuda_\w+)\s*\(", txt)
+    return names
+
+
+def test_header_declares_the_trait_surface():
+    names = set(declared_symbols())
+    for must in ("strix_cuda_create", "strix_cuda_destroy", "strix_cuda_upload_q4_0", "strix_cuda_upload_q6_k",
+                 "strix_cuda_upload_q8_0", "strix_cuda_gemv", "strix_cuda_gemv_batch", "strix_cuda_resident_count",
+                 "strix_cuda_name", "strix_cuda_upload_f32"):
+        assert must in names
+
+
+def test_library_exports_every_declared_symbol(pkg):
+    lib = ctypes.CDLL(pkg.library_path())
+    missing = [n for n in declared_symbols() if not hasattr(lib, n)]
+    assert not missing, missing
+
+
+def test_create_fails_loudly_without_a_device(pkg):
+    import torch
+    if torch.cuda.is_available():
+        return  # covered by the gpu tests
+    try:
+        pkg.CudaWeightAccel(0)
+    except pkg.StrixCudaError as e:
+        assert str(e)  # a real message, not a silent fallback
+    else:
+        raise AssertionError("create succeeded without a CUDA device")

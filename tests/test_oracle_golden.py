@@ -1,0 +1,232 @@
+"""Pins the CPU oracle: the reference's own known-answer tests, the committed golden
+fixtures, and independent numpy restatements. CPU only."""
+import os
+
+import numpy as np
+import pytest
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+
+
+def f16b(v):
+    return np.array([v], dtype=np.float16).view(np.uint8)
+
+
+# ---- the reference's known-answer tests, crates/strix-models/src/ggml_quant.rs ----
+def test_ref_q8_0_scales_each_int(orc):
+    # ggml_quant.rs:443-453: d = 0.5, q[i] = i - 4
+    qs = (np.arange(32) - 4).astype(np.int8)
+    raw = np.concatenate([f16b(0.5), qs.view(np.uint8)])
+    y = orc.dequantize(orc.Q8_0, raw, 32)
+    np.testing.assert_array_equal(y, 0.5 * (np.arange(32, dtype=np.float32) - 4.0))
+
+
+def test_ref_q4_0_nibble_layout_and_bias(orc):
+    # ggml_quant.rs:456-469: d = 2; byte0 = 0x80, byte1 = 0xF1
+    qs = np.zeros(16, dtype=np.uint8)
+    qs[0], qs[1] = 0x80, 0xF1
+    y = orc.dequantize(orc.Q4_0, np.concatenate([f16b(2.0), qs]), 32)
+    assert y[0] == -16.0 and y[16] == 0.0 and y[1] == -14.0 and y[17] == 14.0
+
+
+def test_ref_q6_k_decodes_known_values(orc):
+    # ggml_quant.rs:497-514: ql[0] = 5, qh[0] = 1, scales 1, d = 1
+    blk = np.zeros(210, dtype=np.uint8)
+    blk[0], blk[128] = 0x05, 0x01
+    blk[192:208] = 1
+    blk[208:210] = f16b(1.0)
+    y = orc.dequantize(orc.Q6_K, blk, 256)
+    assert y[0] == -11.0 and y[1] == -32.0 and y[32] == -32.0 and y.size == 256
+
+
+def test_ref_rejects_bad_sizes(orc):
+    # ggml_quant.rs:562-565
+    with pytest.raises(ValueError):
+        orc.dequantize(orc.Q8_0, np.zeros(34, np.uint8), 16)
+    with pytest.raises(ValueError):
+        orc.dequantize(orc.Q4_0, np.zeros(4, np.uint8), 32)
+    # extra bytes are ignored (bytes.len() < need is the only length check, :151-157)
+    assert orc.dequantize(orc.Q4_0, np.zeros(40, np.uint8), 32).size == 32
+
+
+def test_block_geometry(orc):
+    # ggml_quant.rs:88-124
+    assert orc.BLOCK_BYTES == {orc.Q4_0: 18, orc.Q4_1: 20, orc.Q8_0: 34, orc.Q6_K: 210}
+    assert orc.BLOCK_ELEMS[orc.Q6_K] == 256 and orc.BLOCK_ELEMS[orc.Q4_0] == 32
+
+
+# ---- half 2.7.1 f16 -> f32, exhaustively against numpy's IEEE binary16 ----
+def test_f16_widening_exhaustive(orc):
+    bits = np.arange(65536, dtype=np.uint16)
+    want = bits.view(np.float16).astype(np.float32)
+    got = np.array([orc.f16_to_f32(int(b)) for b in bits], dtype=np.float32)
+    finite = ~np.isnan(want)
+    np.testing.assert_array_equal(got[finite].view(np.uint32), want[finite].view(np.uint32))
+    assert np.isnan(got[~finite]).all()
+
+
+# ---- committed golden fixtures (independent numpy restatement, tests/golden/make_golden.py) ----
+@pytest.mark.parametrize("name,ty,be", [("q4_0", 2, 32), ("q8_0", 8, 32), ("q6_k", 14, 256)])
+def test_golden_dequant(orc, name, ty, be):
+    g = np.load(os.path.join(HERE, "golden", "dequant_golden.npz"))
+    raw, want = g[name + "_raw"], g[name + "_f32"]
+    got = orc.dequantize(ty, raw, want.size)
+    np.testing.assert_array_equal(got.view(np.uint32), want.view(np.uint32))
+
+
+def test_q4_1_multiply_then_add(orc):
+    # ggml_quant.rs:264-275: y = d*q + m, two roundings
+    qs = np.arange(16, dtype=np.uint8) | ((15 - np.arange(16, dtype=np.uint8)) << 4)
+    raw = np.concatenate([f16b(0.1), f16b(-0.7), qs])
+    y = orc.dequantize(orc.Q4_1, raw, 32)
+    d, m = np.float32(np.float16(0.1)), np.float32(np.float16(-0.7))
+    lo = (d * np.arange(16, dtype=np.float32)).astype(np.float32) + m
+    hi = (d * (15 - np.arange(16)).astype(np.float32)).astype(np.float32) + m
+    np.testing.assert_array_equal(y, np.concatenate([lo, hi]).astype(np.float32))
+
+
+# ---- dot_f32: the 8-lane order of qwen3.rs:90-105 ----
+def _dot8(a, b):
+    a, b = a.astype(np.float32), b.astype(np.float32)
+    acc = np.zeros(8, dtype=np.float32)
+    n = a.size
+    for c in range(n // 8):
+        acc = (acc + a[8 * c:8 * c + 8] * b[8 * c:8 * c + 8]).astype(np.float32)
+    s = np.float32(np.float32(np.float32(acc[0] + acc[1]) + np.float32(acc[2] + acc[3])) +
+                   np.float32(np.float32(acc[4] + acc[5]) + np.float32(acc[6] + acc[7])))
+    for i in range(n // 8 * 8, n):
+        s = np.float32(s + np.float32(a[i] * b[i]))
+    return s
+
+
+@pytest.mark.parametrize("n", [0, 1, 7, 8, 9, 64, 259, 2560])
+def test_dot_f32_lane_order(orc, n):
+    g = np.random.default_rng(n)
+    a = (g.standard_normal(n) * 10 ** g.uniform(-3, 3, n)).astype(np.float32)
+    b = g.standard_normal(n).astype(np.float32)
+    assert np.float32(orc.dot_f32(a, b)).view(np.uint32) == _dot8(a, b).view(np.uint32)
+
+
+def test_qmatmul_is_row_dequant_then_dot(orc, synth):
+    in_dim, out_dim = 512, 37
+    for ty in (synth.Q4_0, synth.Q8_0, synth.Q6_K):
+        w = synth.quant(ty, 3, "w%d" % ty, out_dim, in_dim)
+        x = synth.normal(3, "x", in_dim)
+        y = orc.qmatmul(x, w, ty, in_dim, out_dim, threads=3)
+        bpr = in_dim // synth.BLOCK_ELEMS[ty] * synth.BLOCK_BYTES[ty]
+        for o in (0, 17, 36):
+            row = orc.dequantize(ty, w[o * bpr:(o + 1) * bpr], in_dim)
+            assert np.float32(y[o]).view(np.uint32) == _dot8(row, x).view(np.uint32)
+        # thread count must not change any bit (one thread owns a row)
+        np.testing.assert_array_equal(y, orc.qmatmul(x, w, ty, in_dim, out_dim, threads=1))
+
+
+def test_qmatmul_batch_matches_token_at_a_time(orc, synth):
+    # mellum.rs:244-271: "each row's value is bit-identical to the token-at-a-time path"
+    in_dim, out_dim, m = 256, 19, 5
+    w = synth.q8_0(4, "w", out_dim, in_dim)
+    xs = synth.normal(4, "xs", m, in_dim)
+    yb = orc.qmatmul_batch(xs, m, w, synth.Q8_0, in_dim, out_dim)
+    for t in range(m):
+        np.testing.assert_array_equal(yb[t], orc.qmatmul(xs[t], w, synth.Q8_0, in_dim, out_dim))
+
+
+# ---- norm / activations vs straight numpy in f32 ----
+def test_rmsnorm_swiglu_geglu(orc):
+    g = np.random.default_rng(5)
+    x = g.standard_normal(2560).astype(np.float32)
+    w = (1 + 0.02 * g.standard_normal(2560)).astype(np.float32)
+    ss = np.float32(0)
+    for v in x:
+        ss = np.float32(ss + np.float32(v * v))
+    scale = np.float32(1.0) / np.sqrt(np.float32(ss / np.float32(2560) + np.float32(1e-6)))
+    np.testing.assert_array_equal(orc.rmsnorm(x, w, 1e-6), ((x * scale).astype(np.float32) * w).astype(np.float32))
+    u = g.standard_normal(2560).astype(np.float32)
+    want = x.astype(np.float64) / (1 + np.exp(-x.astype(np.float64))) * u
+    np.testing.assert_allclose(orc.swiglu(x, u), want, rtol=2e-6, atol=1e-7)
+    xd = x.astype(np.float64)
+    wantg = 0.5 * xd * (1 + np.tanh(0.7978846 * (xd + 0.044715 * xd ** 3))) * u
+    np.testing.assert_allclose(orc.geglu(x, u), wantg, rtol=3e-6, atol=1e-7)
+
+
+# ---- activation quantiser (kernels.rs:864-876) ----
+def test_xquant8_rule(orc):
+    x = np.zeros(96, dtype=np.float32)
+    # block 0: amax 127 -> d = 1, inv = 1: ties go to even, clamp at +-127
+    x[0:8] = [127.0, 0.5, 1.5, 2.5, -0.5, -1.5, -2.5, 126.5]
+    # block 1: all zero -> d = 0, inv = 0, q = 0
+    # block 2: negative amax
+    x[64:68] = [-3.0, 1.0, 2.0, 3.0]
+    q, d, ties = orc.xquant8(x)
+    assert d[0] == 1.0 and list(q[0:8]) == [127, 0, 2, 2, 0, -2, -2, 126]
+    assert ties == 7
+    assert d[1] == 0.0 and not q[32:64].any()
+    assert d[2] == np.float32(3.0) / np.float32(127.0) and q[64] == -127 and q[67] == 127
+
+
+def test_xquant8_matches_numpy(orc, synth):
+    x = synth.normal(9, "x", 9728)
+    q, d, _ = orc.xquant8(x)
+    xb = x.reshape(-1, 32)
+    amax = np.abs(xb).max(axis=1)
+    dd = (amax / np.float32(127.0)).astype(np.float32)
+    inv = np.where(dd > 0, np.float32(1.0) / dd, np.float32(0)).astype(np.float32)
+    qq = np.clip(np.rint((xb * inv[:, None]).astype(np.float32)), -127, 127).astype(np.int8)
+    np.testing.assert_array_equal(d, dd)
+    np.testing.assert_array_equal(q, qq.reshape(-1))
+
+
+# ---- integer-dot GEMV / W8A8 GEMM ----
+def _np_isums_q8(w, xq, m, in_dim, out_dim):
+    blk = w.reshape(out_dim, in_dim // 32, 34)
+    wq = blk[:, :, 2:].view(np.int8).astype(np.int32)           # [n, nb, 32]
+    x = xq.reshape(m, in_dim // 32, 32).astype(np.int32)        # [m, nb, 32]
+    return np.einsum("nbi,mbi->mnb", wq, x).astype(np.int32)
+
+
+def test_idot_q8_isums_exact_and_scaled_sum(orc, synth):
+    in_dim, out_dim, m = 256, 23, 3
+    w = synth.q8_0(6, "w", out_dim, in_dim)
+    xs = synth.normal(6, "xs", m, in_dim)
+    xq, xd, _ = orc.xquant8(xs)
+    y, isums = orc.idot_gemm(w, synth.Q8_0, xq, xd, m, in_dim, out_dim, want_isums=True)
+    want_i = _np_isums_q8(w, xq, m, in_dim, out_dim)
+    np.testing.assert_array_equal(isums, want_i)
+    dw = w.reshape(out_dim, in_dim // 32, 34)[:, :, 0:2].copy().view(np.float16).astype(np.float32).reshape(out_dim, -1)
+    acc = np.zeros((m, out_dim), dtype=np.float32)
+    xdm = xd.reshape(m, -1)
+    for b in range(in_dim // 32):
+        sc = (dw[None, :, b] * xdm[:, None, b]).astype(np.float32)
+        acc = (acc + (sc * want_i[:, :, b].astype(np.float32)).astype(np.float32)).astype(np.float32)
+    np.testing.assert_array_equal(y, acc)
+
+
+def test_idot_q4_equals_signed_nibble_dot(orc, synth):
+    in_dim, out_dim = 128, 11
+    w = synth.q4_0(7, "w", out_dim, in_dim)
+    x = synth.normal(7, "x", in_dim)
+    xq, xd, _ = orc.xquant8(x)
+    _, isums = orc.idot_gemm(w, synth.Q4_0, xq, xd, 1, in_dim, out_dim, want_isums=True)
+    blk = w.reshape(out_dim, in_dim // 32, 18)[:, :, 2:]
+    codes = np.concatenate([blk & 0x0F, blk >> 4], axis=2).astype(np.int32) - 8   # element order j, j+16
+    want = np.einsum("nbi,bi->nb", codes, xq.reshape(-1, 32).astype(np.int32))
+    np.testing.assert_array_equal(isums[0], want)
+
+
+def test_idot_close_to_f32_path(orc, synth):
+    # integer-dot differs from the f32-activation result only by the activation's
+    # quantisation error (the reference accepts rel < 2e-2 for its dp4a variant)
+    in_dim, out_dim = 2560, 64
+    x = synth.normal(8, "x", in_dim)
+    xq, xd, _ = orc.xquant8(x)
+    for ty in (synth.Q4_0, synth.Q8_0, synth.Q6_K):
+        w = synth.quant(ty, 8, "w%d" % ty, out_dim, in_dim)
+        yi = orc.idot_gemm(w, ty, xq, xd, 1, in_dim, out_dim)[0]
+        yf = orc.qmatmul(x, w, ty, in_dim, out_dim)
+        rel = np.linalg.norm(yi - yf) / np.linalg.norm(yf)
+        assert rel < 2e-2, (ty, rel)
+        # and exactly equals a float64 evaluation of the same quantised operands within f32 rounding
+        deq = orc.dequantize(ty, w, in_dim * out_dim).reshape(out_dim, in_dim).astype(np.float64)
+        xdeq = (xq.astype(np.float64).reshape(-1, 32) * xd.astype(np.float64)[:, None]).reshape(-1)
+        ref = deq @ xdeq
+        assert np.linalg.norm(yi - ref) / np.linalg.norm(ref) < 1e-5
