@@ -1,0 +1,363 @@
+"""Benchmark of the quantized-matmul hot path on B200.
+
+``python bench.py --gpus N --steps K --warmup W`` prints ONE JSON line.
+
+Headline metric: dequant-GEMV HBM GB/s on the Q8_0 + Q6_K projection shapes of a
+Qwen3-4B-class model (2560->9728, 9728->2560, 2560->151936), batch 1, f32
+activations. One step = one pass over the six weights (six GEMV launches, 827.5 MB
+of GGUF blocks, far larger than L2, so every step streams from HBM). Inputs are
+seeded synthetic tensors (no model file, no dataset).
+
+  value     whole-job GB/s with weights, x and y resident in HBM (CUDA graph of one
+            step, replayed; CUDA events; max over ranks)
+  e2e       the same metric through the public host API (gemv_batch with host
+            buffers: H2D of every x and D2H of every y inside the timed region)
+  roofline  the largest launch (Q8_0 2560->151936) timed alone against the measured
+            HBM copy bandwidth
+  cpu_baseline  the CPU oracle (the reference's qmatmul restated in C) on a bounded
+            row sample, all host threads
+
+With N > 1 (torchrun) every weight is row-sharded over the ranks and each GEMV is
+followed by an NCCL all-gather of the output shards: strong scaling.
+
+``--impl reference`` times the reference's CPU path (the oracle port: the Rust
+reference cannot be built here) on a bounded sample of the same workload.
+"""
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+import __graft_entry__ as entry  # noqa: E402
+
+Q8_0, Q6_K, Q4_0 = 8, 14, 2
+SHAPES = [(2560, 9728), (9728, 2560), (2560, 151936)]          # (in_dim, out_dim)
+WORKLOAD = [(ty, k, n) for ty in (Q8_0, Q6_K) for (k, n) in SHAPES]
+BLOCK = {Q8_0: (32, 34), Q6_K: (256, 210), Q4_0: (32, 18)}
+TYNAME = {Q8_0: "q8_0", Q6_K: "q6_k", Q4_0: "q4_0"}
+GEN_ROWS = 8192   # synthetic rows generated per weight, tiled up to out_dim (keeps host set-up short)
+
+
+def algo_bytes(ty, k, n):
+    """Algorithmic bytes of one GEMV: GGUF blocks + f32 x + f32 y."""
+    be, bb = BLOCK[ty]
+    return n * (k // be) * bb + 4 * k + 4 * n
+
+
+def make_weight(synth, ty, k, n, seed, name, row0=0, rows=None):
+    """Rows [row0, row0+rows) of a seeded synthetic weight; big weights repeat a GEN_ROWS-row pattern."""
+    rows = n if rows is None else rows
+    be, bb = BLOCK[ty]
+    bpr = k // be * bb
+    base = synth.quant(ty, seed, name, min(n, GEN_ROWS), k).reshape(-1, bpr)
+    idx = (np.arange(row0, row0 + rows) % base.shape[0])
+    return np.ascontiguousarray(base[idx]).reshape(-1)
+
+
+class ClockSampler:
+    """Samples nvidia-smi clocks and throttle reasons while the timed region runs."""
+    Q = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+         "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index):
+        self.index, self.rows, self.p = index, [], None
+
+    def start(self):
+        try:
+            self.p = subprocess.Popen(["nvidia-smi", "-i", str(self.index), "--query-gpu=" + self.Q,
+                                       "--format=csv,noheader,nounits", "-lms", "100"],
+                                      stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.t = threading.Thread(target=self._read, daemon=True)
+            self.t.start()
+        except OSError:
+            self.p = None
+
+    def _read(self):
+        for line in self.p.stdout:
+            self.rows.append([c.strip() for c in line.split(",")])
+
+    def stop(self):
+        if not self.p:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        time.sleep(0.15)
+        self.p.terminate()
+        try:
+            self.p.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.p.kill()
+        sm, mx, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for r in self.rows:
+            if len(r) < 6:
+                continue
+            try:
+                sm.append(float(r[0]))
+                mx.append(float(r[1]))
+            except ValueError:
+                continue
+            for nm, v in zip(names, r[2:6]):
+                if v.lower().startswith("active"):
+                    reasons.add(nm)
+        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "reasons": sorted(reasons), "samples": len(sm)}
+
+
+def cpu_baseline(orc, synth, seconds=12.0):
+    """The oracle's qmatmul on a bounded sample: the first rows of each of the six weights,
+    sized from a calibration call so that the whole leg takes about `seconds`."""
+    threads = orc.default_threads()
+    x = {k: synth.normal(1, "cpu.x%d" % k, k) for k in (2560, 9728)}
+    # calibrate on 512 rows of the first weight
+    w = make_weight(synth, Q8_0, 2560, 9728, 1, "cpu.cal", 0, 512)
+    t0 = time.perf_counter()
+    orc.qmatmul(x[2560], w, Q8_0, 2560, 512, threads)
+    per_byte = (time.perf_counter() - t0) / w.size
+    budget_bytes = seconds / max(per_byte, 1e-12) / 2      # dequant cost varies by format; stay under budget
+    total_full = sum(algo_bytes(ty, k, n) for ty, k, n in WORKLOAD)
+    frac = min(1.0, budget_bytes / total_full)
+    done_bytes, secs, sample = 0, 0.0, []
+    for ty, k, n in WORKLOAD:
+        rows = max(64, int(n * frac))
+        rows = min(rows, n)
+        w = make_weight(synth, ty, k, n, 1, "cpu.%d.%d.%d" % (ty, k, n), 0, rows)
+        orc.qmatmul(x[k], w[: (k // BLOCK[ty][0]) * BLOCK[ty][1] * 8], ty, k, 8, threads)  # touch / warm
+        t0 = time.perf_counter()
+        orc.qmatmul(x[k], w, ty, k, rows, threads)
+        secs += time.perf_counter() - t0
+        done_bytes += algo_bytes(ty, k, rows)
+        sample.append("%s %d->%d rows %d" % (TYNAME[ty], k, n, rows))
+    return {"value": done_bytes / secs / 1e9, "unit": "GB/s", "cores": threads, "kind": "port",
+            "sample": "first rows of each weight: " + "; ".join(sample), "seconds": round(secs, 2)}
+
+
+def run_reference(args):
+    """--impl reference: the reference's CPU implementation of the path (oracle port), all host
+    threads, each step a bounded row sample of the same six GEMVs."""
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    orc = entry.load_oracle()
+    orc.build()
+    entry.load_package()
+    from strix_rs_b200 import synth
+    threads = orc.default_threads()
+    frac = 1.0 / 64.0
+    ws, xs = [], {k: synth.normal(1, "ref.x%d" % k, k) for k in (2560, 9728)}
+    nbytes = 0
+    for ty, k, n in WORKLOAD:
+        rows = max(64, int(n * frac))
+        ws.append((ty, k, rows, make_weight(synth, ty, k, n, 1, "ref.%d.%d.%d" % (ty, k, n), 0, rows)))
+        nbytes += algo_bytes(ty, k, rows)
+
+    def step():
+        for ty, k, rows, w in ws:
+            orc.qmatmul(xs[k], w, ty, k, rows, threads)
+
+    for _ in range(args.warmup):
+        step()
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        step()
+    dt = (time.perf_counter() - t0) / args.steps
+    val = nbytes / dt / 1e9
+    sample = "rows/64 of each of the six weights per step (%d bytes)" % nbytes
+    print(json.dumps({
+        "impl": "reference", "metric": "dequant_gemv_hbm_gbs", "value": val, "unit": "GB/s", "n_gpus": args.gpus,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": dt * 1e3, "higher_is_better": True,
+        "scaling": "strong" if args.gpus > 1 else "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": "configs[1]: Q8_0+Q6_K dequant-GEMV, batch 1, 2560->9728, 9728->2560, 2560->151936",
+                   "sample": sample},
+        "cpu_baseline": {"value": val, "unit": "GB/s", "cores": threads, "kind": "port", "sample": sample},
+        "e2e": {"value": val, "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }))
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=50)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 3)
+    if args.impl == "reference":
+        return run_reference(args)
+
+    import torch
+    import torch.distributed as dist
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: the backend has no CPU path")
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        dist.init_process_group("nccl", device_id=dev)
+
+    pkg = entry.load_package()
+    from strix_rs_b200 import synth
+    acc = pkg.CudaWeightAccel(local, rank=rank, world=world)
+
+    # ---- set-up: upload this rank's row shard of the six weights -------------------------
+    items = []
+    for ty, k, n in WORKLOAD:
+        key = "%s.%d.%d" % (TYNAME[ty], k, n)
+        r0, r1 = pkg.shard_begin(n, world, rank), pkg.shard_begin(n, world, rank + 1)
+        # the library slices its own shard out of the full tensor; hand it a buffer whose shard rows are real
+        be, bb = BLOCK[ty]
+        bpr = k // be * bb
+        full = np.zeros(n * bpr, dtype=np.uint8) if world > 1 else None
+        shard = make_weight(synth, ty, k, n, 1, key, r0, r1 - r0)
+        if world > 1:
+            full[r0 * bpr:r1 * bpr] = shard
+        up = {Q8_0: acc.upload_q8_0, Q6_K: acc.upload_q6_k}[ty]
+        assert up(key, full if world > 1 else shard, k, n), "upload declined: " + key
+        del full, shard
+        x_host = synth.normal(1, key + ".x", k)
+        x = torch.from_numpy(x_host).to(dev)
+        y_shard = torch.zeros(r1 - r0, device=dev)
+        y_full = torch.zeros(n, device=dev) if world > 1 else y_shard
+        items.append(dict(key=key, ty=ty, k=k, n=n, x=x, x_host=x_host, y=y_shard, y_full=y_full,
+                          bytes=algo_bytes(ty, k, n)))
+    step_bytes = sum(it["bytes"] for it in items)
+
+    stream = torch.cuda.Stream(device=dev)
+
+    def step_device():
+        s = torch.cuda.current_stream().cuda_stream
+        for it in items:
+            ok = acc.gemv_dev([it["key"]], it["x"].data_ptr(), [it["y"].data_ptr()], act=pkg.ACT_F32, stream=s)
+            assert ok
+            if world > 1:
+                dist.all_gather_into_tensor(it["y_full"], it["y"])
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    # ---- resident-input throughput: one step captured in a CUDA graph, replayed ----------
+    with torch.cuda.stream(stream):
+        for _ in range(2):
+            step_device()
+        torch.cuda.synchronize()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph, stream=stream):
+            step_device()
+        for _ in range(args.warmup):
+            graph.replay()
+        barrier()
+        sampler = ClockSampler(local)
+        if rank == 0:
+            sampler.start()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        barrier()
+        e0.record()
+        for _ in range(args.steps):
+            graph.replay()
+        e1.record()
+        barrier()
+        ms_total = e0.elapsed_time(e1)
+    if acc.device_status() != 0:
+        raise SystemExit("device status word is non-zero: a bounded wait ran out")
+    t = torch.tensor([ms_total], device=dev)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    ms_step = float(t.item()) / args.steps
+    value = step_bytes / (ms_step * 1e-3) / 1e9
+
+    # ---- end to end through the host API: host x in, host y out, one sync per step --------
+    calls = [(it["key"], it["x_host"]) for it in items]
+    for _ in range(3):
+        acc.gemv_batch(calls)
+    barrier()
+    t0 = time.perf_counter()
+    e2e_steps = max(3, min(args.steps, 20))
+    for _ in range(e2e_steps):
+        ys = acc.gemv_batch(calls)
+    dt = (time.perf_counter() - t0) / e2e_steps
+    tt = torch.tensor([dt], device=dev)
+    if world > 1:
+        dist.all_reduce(tt, op=dist.ReduceOp.MAX)
+    e2e_val = step_bytes / float(tt.item()) / 1e9
+    h2d = sum(4 * it["k"] for it in items)
+    d2h = sum(4 * int(y.size) for y in ys)
+    clocks = sampler.stop() if rank == 0 else None
+
+    # ---- roofline of the dominant launch (Q8_0 2560 -> 151936), timed alone ----------------
+    roof = None
+    detail = []
+    if rank == 0:
+        peaks = {}
+        try:
+            peaks = json.load(open(os.path.join(ROOT, "MEASURED_PEAKS.json")))
+        except OSError:
+            pass
+        peak = float(peaks.get("hbm_gbs", 6650.0))
+        peak_src = "measured" if "hbm_gbs" in peaks else "fallback"
+        with torch.cuda.stream(stream):
+            s = stream.cuda_stream
+            for it in items:
+                shard_frac = it["y"].numel() / it["n"]
+                reps = 20
+                g = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(g, stream=stream):
+                    for _ in range(reps):
+                        acc.gemv_dev([it["key"]], it["x"].data_ptr(), [it["y"].data_ptr()], act=pkg.ACT_F32, stream=s)
+                g.replay()
+                torch.cuda.synchronize()
+                a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                a.record()
+                g.replay()
+                b.record()
+                torch.cuda.synchronize()
+                us = a.elapsed_time(b) * 1e3 / reps
+                detail.append({"weight": it["key"], "us": round(us, 2),
+                               "gbs": round(it["bytes"] * shard_frac / us / 1e3, 1),
+                               "l2_resident": it["bytes"] * shard_frac < 126e6})
+        big = [d for d, it in zip(detail, items) if it["ty"] == Q8_0 and it["n"] == 151936][0]
+        roof = {"bound": "hbm", "achieved": big["gbs"], "peak": peak, "unit": "GB/s",
+                "frac": round(big["gbs"] / peak, 4), "traffic": None,
+                "kernel": "gemv_kernel<Q8_0,F32> on q8_0.2560.151936 (%s peak; traffic from ncu: see profiles/)" % peak_src,
+                "frac_of_8tbs": round(big["gbs"] / 8000.0, 4)}
+
+    cpu = None
+    if rank == 0 and world == 1 and not args.no_cpu_baseline:
+        orc = entry.load_oracle()
+        orc.build()
+        cpu = cpu_baseline(orc, synth)
+
+    if rank == 0:
+        out = {
+            "metric": "dequant_gemv_hbm_gbs", "value": round(value, 2), "unit": "GB/s", "n_gpus": world,
+            "steps": args.steps, "warmup": args.warmup, "ms_per_step": round(ms_step, 5), "higher_is_better": True,
+            "scaling": "strong" if world > 1 else "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+            "config": {"workload": "configs[1]: Q8_0+Q6_K dequant-GEMV, batch 1, 2560->9728, 9728->2560, 2560->151936",
+                       "bytes_per_step": step_bytes, "l2": "inputs larger than L2 (827.5 MB streamed per step)",
+                       "parallelism": "rows sharded over %d GPU(s)%s" % (world, ", NCCL all-gather per GEMV" if world > 1 else "")},
+            "e2e": {"value": round(e2e_val, 2), "unit": "GB/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
+            "gpu_launches": args.steps * len(items),
+            "clocks": clocks, "roofline": roof, "cpu_baseline": cpu, "per_weight": detail,
+            "frac_of_8tbs": round(value / 8000.0, 4),
+        }
+        print(json.dumps(out))
+    acc.close()
+    if world > 1:
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

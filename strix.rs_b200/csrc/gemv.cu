@@ -197,6 +197,26 @@ __device__ __forceinline__ float unit_dot(const uint8_t *__restrict__ rowp, cons
     }
 }
 
+// Sums GEMV_RB (= 4) per-lane values across the warp with 6 shuffles instead of 20: lanes trade the
+// halves they do not keep (xor 16, then xor 8), which leaves one row per lane, then a 3-step
+// butterfly over xor 4/2/1. On return lane 8k (k = 0..3) holds the full sum of row k.
+__device__ __forceinline__ float batch_reduce(const float (&v)[GEMV_RB], uint32_t lane) {
+    static_assert(GEMV_RB == 4, "batch_reduce is written for 4 rows");
+    const bool up16 = (lane & 16u) != 0u, up8 = (lane & 8u) != 0u;
+    // after this step lanes 0-15 hold rows 0,1 and lanes 16-31 hold rows 2,3
+    float k0 = up16 ? v[2] : v[0], s0 = up16 ? v[0] : v[2];
+    float k1 = up16 ? v[3] : v[1], s1 = up16 ? v[1] : v[3];
+    k0 += __shfl_xor_sync(0xffffffffu, s0, 16);
+    k1 += __shfl_xor_sync(0xffffffffu, s1, 16);
+    // lanes with bit 3 clear keep the even row of their pair, the others the odd one
+    float k = up8 ? k1 : k0, sx = up8 ? k0 : k1;
+    k += __shfl_xor_sync(0xffffffffu, sx, 8);
+    k += __shfl_xor_sync(0xffffffffu, k, 4);
+    k += __shfl_xor_sync(0xffffffffu, k, 2);
+    k += __shfl_xor_sync(0xffffffffu, k, 1);
+    return k;
+}
+
 struct TileRef {
     uint32_t mat, row0, rows;
     const uint8_t *src;
@@ -304,28 +324,30 @@ __global__ void __launch_bounds__(GEMV_MAX_WARPS * 32, 1) gemv_kernel(const __gr
         if (!ok) ctl[0] = 1;
         const TileRef t = tile_ref(A, bid + i * grid);
         float *pp = part + buf * (A.rows_per_tile * A.wc);
-        if (ok && slot < A.slots) {
-            const uint8_t *st = stages + (uint64_t)s * A.stage_bytes;
-            for (uint32_t r = slot; r < t.rows; r += 2u * A.slots) {
-                const uint32_t r2 = r + A.slots;
-                const bool two = r2 < t.rows;
-                const uint8_t *p0 = st + (uint64_t)r * L.row_stride;
-                const uint8_t *p1 = st + (uint64_t)(two ? r2 : r) * L.row_stride;
-                float acc0 = 0.f, acc1 = 0.f;
+        if (ok) {
+            const uint8_t *st = stages + s * A.stage_bytes;
+            // A slot works on GEMV_RB consecutive rows at a time: RB independent load/dot chains per
+            // lane, then one transposed warp reduction for the whole batch.
+            for (uint32_t r0 = slot * GEMV_RB; r0 < t.rows; r0 += A.slots * GEMV_RB) {
+                float acc[GEMV_RB];
+#pragma unroll
+                for (int j = 0; j < GEMV_RB; j++) acc[j] = 0.f;
 #pragma unroll
                 for (int c = 0; c < NCH; c++) {
                     const uint32_t u = (cw + (uint32_t)c * A.wc) * 32u + lane;
                     if (u < U) {
-                        acc0 += unit_dot<FMT, ACT>(p0, L, u, X[c]);
-                        acc1 += unit_dot<FMT, ACT>(p1, L, u, X[c]);
+#pragma unroll
+                        for (int j = 0; j < GEMV_RB; j++) {
+                            // rows past the tile's end re-read its last row; their sums are dropped below
+                            const uint32_t rr = min(r0 + (uint32_t)j, t.rows - 1u);
+                            acc[j] += unit_dot<FMT, ACT>(st + rr * L.row_stride, L, u, X[c]);
+                        }
                     }
                 }
-                acc0 = warp_sum(acc0);
-                acc1 = warp_sum(acc1);
-                if (lane == 0) {
-                    pp[r * A.wc + cw] = acc0;
-                    if (two) pp[r2 * A.wc + cw] = acc1;
-                }
+                const float tot = batch_reduce(acc, lane);
+                // lane 8k now holds the sum of row r0 + k
+                const uint32_t rr = r0 + (lane >> 3);
+                if ((lane & 7u) == 0u && rr < t.rows) pp[rr * A.wc + cw] = tot;
             }
         }
         __syncthreads();
@@ -366,22 +388,23 @@ bool gemv_plan(GemvArgs &a, int num_sms, size_t smem_optin) {
     const uint32_t stride = a.L.row_stride;
     const uint32_t budget = (uint32_t)smem_optin - 1024u;
 
-    uint32_t rt0 = 32768u / stride;
-    if (rt0 < 1) rt0 = 1;
-    if (rt0 > 64) rt0 = 64;
-    if (rt0 >= slots) rt0 = rt0 / slots * slots;
-    // Among tile heights down to half of rt0 pick the one with the least work on the busiest CTA.
-    uint32_t best_rt = rt0;
+    // A tile is a whole number of row batches for every slot: a multiple of slots * GEMV_RB rows,
+    // about 24-48 KB, capped at 160 rows. Among candidate heights pick the one with the least
+    // work on the busiest CTA (bytes streamed plus a fixed charge per tile).
+    const uint32_t quantum = slots * GEMV_RB;
+    uint32_t mmax = 40960u / (quantum * stride);
+    if (mmax < 1) mmax = 1;
+    while (mmax > 1 && mmax * quantum > 160) mmax--;
+    uint32_t best_rt = quantum;
     uint64_t best_cost = ~0ull;
-    const int step = rt0 >= slots ? (int)slots : 1;
-    for (int rt = (int)rt0; rt >= 1 && 2 * rt >= (int)rt0; rt -= step) {
+    for (uint32_t m = mmax; m >= 1 && 2 * m >= mmax; m--) {
+        const uint32_t rt = m * quantum;
         uint64_t tiles = 0;
-        for (int m = 0; m < a.nmat; m++) tiles += (a.mat[m].rows + (uint32_t)rt - 1) / (uint32_t)rt;
+        for (int k = 0; k < a.nmat; k++) tiles += (a.mat[k].rows + rt - 1) / rt;
         if (tiles == 0) tiles = 1;
-        uint64_t per_cta = (tiles + (uint64_t)num_sms - 1) / (uint64_t)num_sms;
-        // bytes streamed by the busiest CTA plus a fixed charge per tile (barrier + partial-sum pass)
-        uint64_t cost = per_cta * ((uint64_t)rt * stride + 2048u);
-        if (cost < best_cost) { best_cost = cost; best_rt = (uint32_t)rt; }
+        const uint64_t per_cta = (tiles + (uint64_t)num_sms - 1) / (uint64_t)num_sms;
+        const uint64_t cost = per_cta * ((uint64_t)rt * stride + 2048u);
+        if (cost < best_cost) { best_cost = cost; best_rt = rt; }
     }
     const uint32_t rt = best_rt;
     uint32_t tile = 0;

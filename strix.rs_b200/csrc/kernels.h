@@ -16,6 +16,7 @@ cudaError_t launch_dequant(const uint8_t *d_res, float *d_out, const RowLayout &
 constexpr int GEMV_MAX_MATS = 3;
 constexpr int GEMV_MAX_STAGES = 8;
 constexpr int GEMV_MAX_WARPS = 20;  // 640 threads per CTA, one CTA per SM
+constexpr int GEMV_RB = 4;          // rows a warp carries at once (independent chains, one batched reduction)
 
 struct GemvMat {
     const uint8_t *w;  // resident rows of this accelerator's shard
