@@ -47,16 +47,64 @@ __device__ __forceinline__ float gelu_tanh_f(float x) {
     return 0.5f * x * (1.0f + tanhf(C * (x + 0.044715f * x * x * x)));
 }
 
-// Per-lane activation state for one unit.
+// ---- shared-memory loads on 32-bit shared addresses (always LDS, 32-bit address arithmetic) ----
+__device__ __forceinline__ uint4 lds128(uint32_t a) {
+    uint4 v;
+    asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(a));
+    return v;
+}
+__device__ __forceinline__ uint2 lds64(uint32_t a) {
+    uint2 v;
+    asm volatile("ld.shared.v2.u32 {%0,%1}, [%2];" : "=r"(v.x), "=r"(v.y) : "r"(a));
+    return v;
+}
+__device__ __forceinline__ uint32_t lds32(uint32_t a) {
+    uint32_t v;
+    asm volatile("ld.shared.u32 %0, [%1];" : "=r"(v) : "r"(a));
+    return v;
+}
+__device__ __forceinline__ float lds_f16(uint32_t a) {
+    uint16_t v;
+    asm volatile("ld.shared.u16 %0, [%1];" : "=h"(v) : "r"(a));
+    return f16_bits_to_f32(v);
+}
+
+// Byte -> f32 without a conversion instruction: one PRMT drops byte i of `w` into the mantissa of
+// a constant, so the result is (2^k + byte) exactly.
+//   magic15: byte lands in bits 8..15 of 0x47000000 -> 32768 + byte   (any byte 0..255)
+//   magic7 : byte lands in bits 16..23 of 0x43000000 -> 128 + byte    (byte < 128 only)
+template <int I>
+__device__ __forceinline__ float magic15(uint32_t w) {
+    return __uint_as_float(__byte_perm(w, 0x47000000u, 0x7404u | (I << 4)));
+}
+template <int I>
+__device__ __forceinline__ float magic7(uint32_t w) {
+    return __uint_as_float(__byte_perm(w, 0x43000000u, 0x7044u | (I << 8)));
+}
+// sign-extended byte i of w (selector nibbles with bit 3 set replicate the byte's sign)
+// (the __byte_perm intrinsic keeps only 3 bits per selector nibble, so this goes through prmt.b32 itself)
+__device__ __forceinline__ int sext_byte(uint32_t w, uint32_t sel4) {
+    int d;
+    asm("prmt.b32 %0, %1, %2, %3;" : "=r"(d) : "r"(w), "r"(0u), "r"(sel4));
+    return d;
+}
+__host__ __device__ constexpr uint32_t sext_sel(uint32_t i) { return i | ((i | 8u) << 4) | ((i | 8u) << 8) | ((i | 8u) << 12); }
+
+// Per-lane activation state for one unit (16 x values), held in registers for the whole kernel.
 template <int FMT, int ACT>
 struct UnitX {
-    // f32 form
-    float v[ACT == STRIX_ACT_F32 ? 16 : 1];
-    float corr[ACT == STRIX_ACT_F32 ? (FMT == FMT_Q6_K ? 4 : 1) : 1];  // bias * sum(x): 8*sum16 (Q4_0), 32*sum4 (Q6_K)
+    // f32 form: the 16 values as 8 pairs (operands of the packed f32x2 FMA)
+    float2 v2[ACT == STRIX_ACT_F32 ? 8 : 1];
+    // bias correction folded into the accumulator's start value:
+    //   Q4_0: (128 + 8) * sum of the 16 x;  Q6_K: (128 + 32) * sum of each group of 4;  Q8_0: unused
+    float corr[ACT == STRIX_ACT_F32 ? (FMT == FMT_Q6_K ? 4 : 1) : 1];
     // int8 form
     uint32_t q[ACT == STRIX_ACT_Q8DOT ? 4 : 1];
     float d[ACT == STRIX_ACT_Q8DOT ? (FMT == FMT_Q6_K ? 4 : 1) : 1];
-    int qs[ACT == STRIX_ACT_Q8DOT ? (FMT == FMT_Q6_K ? 4 : 1) : 1];  // sum of the int8 values (bias correction)
+    int qs[ACT == STRIX_ACT_Q8DOT ? (FMT == FMT_Q6_K ? 4 : 1) : 1];  // bias * sum of the int8 values
+    // byte offsets of this unit's fields within a resident row
+    uint32_t off_w, off_s, off_hh, off_sc;
+    uint32_t sel_a, sel_b;  // Q6_K: sign-extending PRMT selectors of this unit's sub-scale bytes
 };
 
 __device__ __forceinline__ int quant1(float x, float inv) {
@@ -65,18 +113,33 @@ __device__ __forceinline__ int quant1(float x, float inv) {
 }
 
 template <int FMT, int ACT>
-__device__ __forceinline__ void make_unit_x(UnitX<FMT, ACT> &X, const float (&v)[16]) {
+__device__ __forceinline__ void make_unit_x(UnitX<FMT, ACT> &X, const float (&v)[16], uint32_t u, const RowLayout &L) {
+    if (FMT == FMT_Q8_0) {
+        X.off_w = u * 16u;
+        X.off_s = L.off_d + 2u * (u >> 1);
+    } else if (FMT == FMT_Q4_0) {
+        X.off_w = u * 8u;
+        X.off_s = L.off_d + 2u * (u >> 1);
+    } else {
+        const uint32_t sb = u >> 4, r = u & 15u, h = r >> 3, c4 = r & 7u;
+        X.off_w = sb * 128u + h * 64u + c4 * 4u;
+        X.off_hh = L.off_qh + sb * 64u + h * 32u + c4 * 4u;
+        X.off_sc = L.off_sc + sb * 16u + h * 8u;
+        X.off_s = L.off_d + 2u * sb;
+        X.sel_a = sext_sel(c4 >> 2);         // sub-scale byte (c4>>2)     of the word: groups 0 and 2
+        X.sel_b = sext_sel((c4 >> 2) + 2u);  // sub-scale byte (c4>>2) + 2 of the word: groups 1 and 3
+    }
     if (ACT == STRIX_ACT_F32) {
 #pragma unroll
-        for (int i = 0; i < 16; i++) X.v[i] = v[i];
+        for (int i = 0; i < 8; i++) X.v2[i] = make_float2(v[2 * i], v[2 * i + 1]);
         if (FMT == FMT_Q4_0) {
             float s = 0.f;
 #pragma unroll
             for (int i = 0; i < 16; i++) s += v[i];
-            X.corr[0] = 8.0f * s;
+            X.corr[0] = 136.0f * s;
         } else if (FMT == FMT_Q6_K) {
 #pragma unroll
-            for (int k = 0; k < 4; k++) X.corr[k] = 32.0f * ((v[4 * k] + v[4 * k + 1]) + (v[4 * k + 2] + v[4 * k + 3]));
+            for (int k = 0; k < 4; k++) X.corr[k] = 160.0f * ((v[4 * k] + v[4 * k + 1]) + (v[4 * k + 2] + v[4 * k + 3]));
         }
     } else {
         // per-32 quantiser (xquant8, kernels.rs:864-876): d = amax/127, inv = d>0 ? 1/d : 0,
@@ -99,7 +162,7 @@ __device__ __forceinline__ void make_unit_x(UnitX<FMT, ACT> &X, const float (&v)
                          ((uint32_t)(q3 & 0xff) << 24);
             }
             X.d[0] = d;
-            X.qs[0] = sum;
+            X.qs[0] = 8 * sum;
         } else {
 #pragma unroll
             for (int k = 0; k < 4; k++) {
@@ -115,82 +178,96 @@ __device__ __forceinline__ void make_unit_x(UnitX<FMT, ACT> &X, const float (&v)
                 X.q[k] = (uint32_t)(q0 & 0xff) | ((uint32_t)(q1 & 0xff) << 8) | ((uint32_t)(q2 & 0xff) << 16) |
                          ((uint32_t)(q3 & 0xff) << 24);
                 X.d[k] = d;
-                X.qs[k] = q0 + q1 + q2 + q3;
+                X.qs[k] = 32 * (q0 + q1 + q2 + q3);
             }
         }
     }
 }
 
-__device__ __forceinline__ float s8f(uint32_t w, int i) { return (float)(int)(int8_t)((w >> (8 * i)) & 0xffu); }
-__device__ __forceinline__ float u8f(uint32_t w, int i) { return (float)((w >> (8 * i)) & 0xffu); }
+// sum over 4 bytes of (2^k + byte_i) * x_i on two packed-f32x2 accumulators
+template <bool M7>
+__device__ __forceinline__ void fma4(uint32_t w, const float2 &xa, const float2 &xb, float2 &acc_a, float2 &acc_b) {
+    float2 p, q;
+    if (M7) {
+        p = make_float2(magic7<0>(w), magic7<1>(w));
+        q = make_float2(magic7<2>(w), magic7<3>(w));
+    } else {
+        p = make_float2(magic15<0>(w), magic15<1>(w));
+        q = make_float2(magic15<2>(w), magic15<3>(w));
+    }
+    acc_a = __ffma2_rn(p, xa, acc_a);
+    acc_b = __ffma2_rn(q, xb, acc_b);
+}
 
-// Contribution of unit u of one resident row (in shared memory) to that row's dot product.
+// Contribution of one unit of one resident row to that row's dot product.
+// `rb` = 32-bit shared address of the row's first byte.
 template <int FMT, int ACT>
-__device__ __forceinline__ float unit_dot(const uint8_t *__restrict__ rowp, const RowLayout &L, uint32_t u,
-                                          const UnitX<FMT, ACT> &X) {
+__device__ __forceinline__ float unit_dot(uint32_t rb, const UnitX<FMT, ACT> &X) {
     if (FMT == FMT_Q8_0) {
-        const uint4 w = *reinterpret_cast<const uint4 *>(rowp + u * 16u);
-        const float d = f16_bits_to_f32(*reinterpret_cast<const uint16_t *>(rowp + L.off_d + 2u * (u >> 1)));
-        const uint32_t ws[4] = {w.x, w.y, w.z, w.w};
+        const uint4 w = lds128(rb + X.off_w);
+        const float d = lds_f16(rb + X.off_s);
         if (ACT == STRIX_ACT_F32) {
-            float s = 0.f;
+            // q + 128 is an unsigned byte; (32768 + 128 + q) - 32896 = q exactly, then packed FMAs
+            const uint32_t ws[4] = {w.x ^ 0x80808080u, w.y ^ 0x80808080u, w.z ^ 0x80808080u, w.w ^ 0x80808080u};
+            const float2 bias = make_float2(-32896.0f, -32896.0f);
+            float2 acc_a = make_float2(0.f, 0.f), acc_b = make_float2(0.f, 0.f);
 #pragma unroll
-            for (int g = 0; g < 4; g++)
-#pragma unroll
-                for (int i = 0; i < 4; i++) s = fmaf(s8f(ws[g], i), X.v[4 * g + i], s);
-            return d * s;
+            for (int g = 0; g < 4; g++) {
+                float2 p = make_float2(magic15<0>(ws[g]), magic15<1>(ws[g]));
+                float2 q = make_float2(magic15<2>(ws[g]), magic15<3>(ws[g]));
+                p = __fadd2_rn(p, bias);
+                q = __fadd2_rn(q, bias);
+                acc_a = __ffma2_rn(p, X.v2[2 * g], acc_a);
+                acc_b = __ffma2_rn(q, X.v2[2 * g + 1], acc_b);
+            }
+            return d * ((acc_a.x + acc_a.y) + (acc_b.x + acc_b.y));
         } else {
-            int isum = 0;
-#pragma unroll
-            for (int g = 0; g < 4; g++) isum = dp4a_ss(ws[g], X.q[g], isum);
+            int isum = dp4a_ss(w.x, X.q[0], 0);
+            isum = dp4a_ss(w.y, X.q[1], isum);
+            isum = dp4a_ss(w.z, X.q[2], isum);
+            isum = dp4a_ss(w.w, X.q[3], isum);
             return (d * X.d[0]) * (float)isum;
         }
     } else if (FMT == FMT_Q4_0) {
-        const uint2 w = *reinterpret_cast<const uint2 *>(rowp + u * 8u);
-        const float d = f16_bits_to_f32(*reinterpret_cast<const uint16_t *>(rowp + L.off_d + 2u * (u >> 1)));
+        const uint2 w = lds64(rb + X.off_w);
+        const float d = lds_f16(rb + X.off_s);
         const uint32_t lo0 = w.x & 0x0F0F0F0Fu, lo1 = w.y & 0x0F0F0F0Fu;
         const uint32_t hi0 = (w.x >> 4) & 0x0F0F0F0Fu, hi1 = (w.y >> 4) & 0x0F0F0F0Fu;
-        const uint32_t ws[4] = {lo0, lo1, hi0, hi1};
         if (ACT == STRIX_ACT_F32) {
-            float s = 0.f;
-#pragma unroll
-            for (int g = 0; g < 4; g++)
-#pragma unroll
-                for (int i = 0; i < 4; i++) s = fmaf(u8f(ws[g], i), X.v[4 * g + i], s);
-            return d * (s - X.corr[0]);  // sum((q-8) x) = sum(q x) - 8 sum(x)
+            // sum((128 + nib) x) - 136 sum(x) = sum((nib - 8) x); the second term starts the accumulator
+            float2 acc_a = make_float2(-X.corr[0], 0.f), acc_b = make_float2(0.f, 0.f);
+            fma4<true>(lo0, X.v2[0], X.v2[1], acc_a, acc_b);
+            fma4<true>(lo1, X.v2[2], X.v2[3], acc_a, acc_b);
+            fma4<true>(hi0, X.v2[4], X.v2[5], acc_a, acc_b);
+            fma4<true>(hi1, X.v2[6], X.v2[7], acc_a, acc_b);
+            return d * ((acc_a.x + acc_a.y) + (acc_b.x + acc_b.y));
         } else {
-            int isum = 0;
-#pragma unroll
-            for (int g = 0; g < 4; g++) isum = dp4a_us(ws[g], X.q[g], isum);
-            isum -= 8 * X.qs[0];
+            int isum = dp4a_us(lo0, X.q[0], -X.qs[0]);  // raw nibbles, minus 8 * sum(xq)
+            isum = dp4a_us(lo1, X.q[1], isum);
+            isum = dp4a_us(hi0, X.q[2], isum);
+            isum = dp4a_us(hi1, X.q[3], isum);
             return (d * X.d[0]) * (float)isum;
         }
     } else {
-        const uint32_t sb = u >> 4, r = u & 15u, h = r >> 3, c4 = r & 7u;
-        const uint32_t a = *reinterpret_cast<const uint32_t *>(rowp + sb * 128u + h * 64u + c4 * 4u);
-        const uint32_t b = *reinterpret_cast<const uint32_t *>(rowp + sb * 128u + h * 64u + 32u + c4 * 4u);
-        const uint32_t hh = *reinterpret_cast<const uint32_t *>(rowp + L.off_qh + sb * 64u + h * 32u + c4 * 4u);
-        const float d = f16_bits_to_f32(*reinterpret_cast<const uint16_t *>(rowp + L.off_d + 2u * sb));
-        // the half's 8 sub-scales; this unit uses bytes (c4>>2) + {0,2,4,6}
-        const uint2 scw = *reinterpret_cast<const uint2 *>(rowp + L.off_sc + sb * 16u + h * 8u);
-        const uint32_t sel = c4 >> 2;
+        const uint32_t a = lds32(rb + X.off_w), b = lds32(rb + X.off_w + 32u), hh = lds32(rb + X.off_hh);
+        const uint2 scw = lds64(rb + X.off_sc);  // the half's 8 sub-scales
+        const float d = lds_f16(rb + X.off_s);
         const uint32_t qw[4] = {(a & 0x0F0F0F0Fu) | ((hh & 0x03030303u) << 4),
                                 (b & 0x0F0F0F0Fu) | ((hh & 0x0C0C0C0Cu) << 2),
                                 ((a >> 4) & 0x0F0F0F0Fu) | (hh & 0x30303030u),
                                 ((b >> 4) & 0x0F0F0F0Fu) | ((hh >> 2) & 0x30303030u)};
+        const float sc[4] = {(float)sext_byte(scw.x, X.sel_a), (float)sext_byte(scw.x, X.sel_b),
+                             (float)sext_byte(scw.y, X.sel_a), (float)sext_byte(scw.y, X.sel_b)};
         float t = 0.f;
 #pragma unroll
         for (int k = 0; k < 4; k++) {
-            const uint32_t word = (k < 2) ? scw.x : scw.y;
-            const float sc = (float)(int)(int8_t)((word >> (8u * (sel + 2u * (k & 1)))) & 0xffu);
             if (ACT == STRIX_ACT_F32) {
-                float s = 0.f;
-#pragma unroll
-                for (int i = 0; i < 4; i++) s = fmaf(u8f(qw[k], i), X.v[4 * k + i], s);
-                t = fmaf(sc, s - X.corr[k], t);
+                float2 acc_a = make_float2(-X.corr[k], 0.f), acc_b = make_float2(0.f, 0.f);
+                fma4<true>(qw[k], X.v2[2 * k], X.v2[2 * k + 1], acc_a, acc_b);
+                t = fmaf(sc[k], (acc_a.x + acc_a.y) + (acc_b.x + acc_b.y), t);
             } else {
-                int isum = dp4a_us(qw[k], X.q[k], 0) - 32 * X.qs[k];
-                t = fmaf(sc * X.d[k], (float)isum, t);
+                const int isum = dp4a_us(qw[k], X.q[k], -X.qs[k]);  // minus 32 * sum(xq)
+                t = fmaf(sc[k] * X.d[k], (float)isum, t);
             }
         }
         return d * t;
@@ -311,7 +388,7 @@ __global__ void __launch_bounds__(GEMV_MAX_WARPS * 32, 1) gemv_kernel(const __gr
             }
             v[4 * g] = a4.x; v[4 * g + 1] = a4.y; v[4 * g + 2] = a4.z; v[4 * g + 3] = a4.w;
         }
-        make_unit_x<FMT, ACT>(X[c], v);
+        make_unit_x<FMT, ACT>(X[c], v, u, L);
     }
 
     // ---- stream the tiles ----
@@ -325,23 +402,22 @@ __global__ void __launch_bounds__(GEMV_MAX_WARPS * 32, 1) gemv_kernel(const __gr
         const TileRef t = tile_ref(A, bid + i * grid);
         float *pp = part + buf * (A.rows_per_tile * A.wc);
         if (ok) {
-            const uint8_t *st = stages + s * A.stage_bytes;
+            const uint32_t st = smem_u32(stages) + s * A.stage_bytes;
             // A slot works on GEMV_RB consecutive rows at a time: RB independent load/dot chains per
-            // lane, then one transposed warp reduction for the whole batch.
+            // lane, then one transposed warp reduction for the whole batch. Rows past the tile's end
+            // read whatever the stage still holds from an earlier tile; their sums are dropped below.
             for (uint32_t r0 = slot * GEMV_RB; r0 < t.rows; r0 += A.slots * GEMV_RB) {
                 float acc[GEMV_RB];
 #pragma unroll
                 for (int j = 0; j < GEMV_RB; j++) acc[j] = 0.f;
+                const uint32_t rb0 = st + r0 * L.row_stride;
 #pragma unroll
                 for (int c = 0; c < NCH; c++) {
                     const uint32_t u = (cw + (uint32_t)c * A.wc) * 32u + lane;
                     if (u < U) {
 #pragma unroll
-                        for (int j = 0; j < GEMV_RB; j++) {
-                            // rows past the tile's end re-read its last row; their sums are dropped below
-                            const uint32_t rr = min(r0 + (uint32_t)j, t.rows - 1u);
-                            acc[j] += unit_dot<FMT, ACT>(st + rr * L.row_stride, L, u, X[c]);
-                        }
+                        for (int j = 0; j < GEMV_RB; j++)
+                            acc[j] += unit_dot<FMT, ACT>(rb0 + (uint32_t)j * L.row_stride, X[c]);
                     }
                 }
                 const float tot = batch_reduce(acc, lane);
