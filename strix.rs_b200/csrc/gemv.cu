@@ -7,21 +7,29 @@
 // 646-668, 607-640, 894-912, 228-361, 75-226).
 //
 // Design (HBM-bound streaming kernel, no tensor cores):
-//  * one persistent CTA per SM; the weight rows of a launch are cut into tiles
-//    of consecutive rows (one contiguous byte range each, see layout.h);
-//  * tiles stream HBM -> shared memory through a ring of up to 8 stages filled
-//    by 1-D bulk async copies (cp.async.bulk, no multicast) that complete on
-//    mbarriers, so the bytes in flight per SM do not depend on occupancy or on
-//    registers;
-//  * the activation vector never touches shared memory: K is cut into units of
-//    16 elements, a warp owns the same units for the whole kernel ("column
-//    stationary") and keeps their x values (f32, or int8 after the per-32
-//    quantiser) in registers; wc warps cover one row between them and `slots`
-//    such groups work on different rows of a tile;
-//  * a row's wc partial sums meet in shared memory and are added in a fixed
-//    order, so results are reproducible run to run;
+//  * one persistent CTA per SM; the weight rows of a launch are cut into tiles of
+//    consecutive rows (one contiguous byte range each, see layout.h);
+//  * a producer warp streams tiles HBM -> shared memory through a ring of stages
+//    with 1-D bulk async copies (cp.async.bulk, no multicast) that complete on
+//    "full" mbarriers; consumer warps hand a stage back through an "empty"
+//    mbarrier. Bytes in flight per SM do not depend on occupancy or registers;
+//  * the activation vector never touches shared memory: K is cut into units of 16
+//    elements, a consumer warp owns NCH runs of 32 units for the whole kernel
+//    ("column stationary") and keeps their x values (f32 pairs, or int8 after the
+//    per-32 quantiser) in registers; wc warps cover one row between them, and
+//    `slots` such groups work on different rows of a tile;
+//  * a warp carries RB (2 or 4) rows at once: NCH x RB independent load/dot chains
+//    per lane, then ONE transposed shuffle reduction for the batch;
+//  * when wc > 1 the wc partial sums of a row meet in shared memory behind a named
+//    barrier of just those warps and are added in a fixed order (reproducible);
+//  * byte -> f32 conversion avoids the conversion unit: a PRMT/LOP3 drops two codes
+//    into the mantissas of a packed f16 pair (1024 + code), a mixed-precision add
+//    (f16 + f32 -> f32) removes the bias exactly, and packed f32x2 FMAs accumulate;
 //  * every mbarrier wait is bounded; on expiry the kernel raises
-//    STATUS_WAIT_TIMEOUT in the accelerator's status word and leaves.
+//    STATUS_WAIT_TIMEOUT in the accelerator's status word and runs out its loops
+//    without waiting again.
+#include <cstdlib>
+
 #include "common.cuh"
 #include "kernels.h"
 #include "strix_cuda.h"
@@ -69,20 +77,25 @@ __device__ __forceinline__ float lds_f16(uint32_t a) {
     return f16_bits_to_f32(v);
 }
 
-// Byte -> f32 without a conversion instruction: one PRMT drops byte i of `w` into the mantissa of
-// a constant, so the result is (2^k + byte) exactly.
-//   magic15: byte lands in bits 8..15 of 0x47000000 -> 32768 + byte   (any byte 0..255)
-//   magic7 : byte lands in bits 16..23 of 0x43000000 -> 128 + byte    (byte < 128 only)
-template <int I>
-__device__ __forceinline__ float magic15(uint32_t w) {
-    return __uint_as_float(__byte_perm(w, 0x47000000u, 0x7404u | (I << 4)));
+// (f16 pair) + bias -> (f32 pair), one mixed-precision add per half. With the halves holding
+// 1024 + code (or 64 + code) and bias = -(1024 + offset) the result is (code - offset) exactly.
+__device__ __forceinline__ float2 unbias_pair(uint32_t h2, float bias) {
+    float2 r;
+    asm("{\n\t.reg .b16 lo, hi;\n\t"
+        "mov.b32 {lo, hi}, %2;\n\t"
+        "add.rn.f32.f16 %0, lo, %3;\n\t"
+        "add.rn.f32.f16 %1, hi, %3;\n\t}"
+        : "=f"(r.x), "=f"(r.y)
+        : "r"(h2), "f"(bias));
+    return r;
 }
+// bytes (I, I+1) of w -> packed f16 pair (1024 + b_I, 1024 + b_I+1)
 template <int I>
-__device__ __forceinline__ float magic7(uint32_t w) {
-    return __uint_as_float(__byte_perm(w, 0x43000000u, 0x7044u | (I << 8)));
+__device__ __forceinline__ uint32_t bytes_to_h2(uint32_t w) {
+    return __byte_perm(w, 0x64646464u, I == 0 ? 0x4140u : 0x4342u);
 }
-// sign-extended byte i of w (selector nibbles with bit 3 set replicate the byte's sign)
-// (the __byte_perm intrinsic keeps only 3 bits per selector nibble, so this goes through prmt.b32 itself)
+// sign-extended byte of w; sel4 from sext_sel(). (__byte_perm keeps only 3 bits per selector
+// nibble, so the sign-replicating form goes through prmt.b32 itself.)
 __device__ __forceinline__ int sext_byte(uint32_t w, uint32_t sel4) {
     int d;
     asm("prmt.b32 %0, %1, %2, %3;" : "=r"(d) : "r"(w), "r"(0u), "r"(sel4));
@@ -90,56 +103,57 @@ __device__ __forceinline__ int sext_byte(uint32_t w, uint32_t sel4) {
 }
 __host__ __device__ constexpr uint32_t sext_sel(uint32_t i) { return i | ((i | 8u) << 4) | ((i | 8u) << 8) | ((i | 8u) << 12); }
 
-// Per-lane activation state for one unit (16 x values), held in registers for the whole kernel.
-template <int FMT, int ACT>
-struct UnitX {
-    // f32 form: the 16 values as 8 pairs (operands of the packed f32x2 FMA)
-    float2 v2[ACT == STRIX_ACT_F32 ? 8 : 1];
-    // bias correction folded into the accumulator's start value:
-    //   Q4_0: (128 + 8) * sum of the 16 x;  Q6_K: (128 + 32) * sum of each group of 4;  Q8_0: unused
-    float corr[ACT == STRIX_ACT_F32 ? (FMT == FMT_Q6_K ? 4 : 1) : 1];
-    // int8 form
-    uint32_t q[ACT == STRIX_ACT_Q8DOT ? 4 : 1];
-    float d[ACT == STRIX_ACT_Q8DOT ? (FMT == FMT_Q6_K ? 4 : 1) : 1];
-    int qs[ACT == STRIX_ACT_Q8DOT ? (FMT == FMT_Q6_K ? 4 : 1) : 1];  // bias * sum of the int8 values
-    // byte offsets of this unit's fields within a resident row
+// Per-lane activation state: NCH units (unit c = first_unit + 32 c), in registers for the whole kernel.
+template <int FMT, int ACT, int NCH>
+struct LaneX {
+    static constexpr int ND = (FMT == FMT_Q6_K) ? 4 : 1;
+    // f32 form: the 16 values of a unit as 8 pairs, ordered to match the packed f16 pairs the
+    // decoder produces (see pair_index)
+    float2 v2[ACT == STRIX_ACT_F32 ? NCH : 1][8];
+    // int8 form: 16 codes as 4 words, per-32 scale(s), bias * sum of the codes
+    uint32_t q[ACT == STRIX_ACT_Q8DOT ? NCH : 1][4];
+    float d[ACT == STRIX_ACT_Q8DOT ? NCH : 1][ND];
+    int qs[ACT == STRIX_ACT_Q8DOT ? NCH : 1][ND];
+    // byte offsets (within a resident row) of unit 0's fields; unit c adds a compile-time step
     uint32_t off_w, off_s, off_hh, off_sc;
-    uint32_t sel_a, sel_b;  // Q6_K: sign-extending PRMT selectors of this unit's sub-scale bytes
+    uint32_t sel_a, sel_b;  // Q6_K: sign-extending PRMT selectors of this lane's sub-scale bytes
+    uint32_t valid;         // bit c set: unit c lies inside the row
 };
+
+// Which two of a unit's 16 x values (order of unit_elem: v[4g + i]) go into pair p.
+//   Q8_0 / Q6_K: natural order, pair p = (v[2p], v[2p+1]).
+//   Q4_0: the nibble decoder yields, per code word wd (bytes 4wd..4wd+3), the pairs
+//         (b0.lo, b2.lo), (b1.lo, b3.lo), (b0.hi, b2.hi), (b1.hi, b3.hi); low nibbles are
+//         v[0..7], high nibbles v[8..15].
+template <int FMT>
+__device__ __forceinline__ void pair_index(int p, int &i0, int &i1) {
+    if (FMT == FMT_Q4_0) {
+        const int wd = p >> 2, k = p & 3;  // k: 0 lo(0,2)  1 lo(1,3)  2 hi(0,2)  3 hi(1,3)
+        const int base = 4 * wd + (k & 1) + ((k & 2) ? 8 : 0);
+        i0 = base;
+        i1 = base + 2;
+    } else {
+        i0 = 2 * p;
+        i1 = 2 * p + 1;
+    }
+}
 
 __device__ __forceinline__ int quant1(float x, float inv) {
     int q = (int)rintf(x * inv);
     return max(-127, min(127, q));
 }
+__device__ __forceinline__ uint32_t pack4(int a, int b, int c, int d) {
+    return (uint32_t)(a & 0xff) | ((uint32_t)(b & 0xff) << 8) | ((uint32_t)(c & 0xff) << 16) | ((uint32_t)(d & 0xff) << 24);
+}
 
-template <int FMT, int ACT>
-__device__ __forceinline__ void make_unit_x(UnitX<FMT, ACT> &X, const float (&v)[16], uint32_t u, const RowLayout &L) {
-    if (FMT == FMT_Q8_0) {
-        X.off_w = u * 16u;
-        X.off_s = L.off_d + 2u * (u >> 1);
-    } else if (FMT == FMT_Q4_0) {
-        X.off_w = u * 8u;
-        X.off_s = L.off_d + 2u * (u >> 1);
-    } else {
-        const uint32_t sb = u >> 4, r = u & 15u, h = r >> 3, c4 = r & 7u;
-        X.off_w = sb * 128u + h * 64u + c4 * 4u;
-        X.off_hh = L.off_qh + sb * 64u + h * 32u + c4 * 4u;
-        X.off_sc = L.off_sc + sb * 16u + h * 8u;
-        X.off_s = L.off_d + 2u * sb;
-        X.sel_a = sext_sel(c4 >> 2);         // sub-scale byte (c4>>2)     of the word: groups 0 and 2
-        X.sel_b = sext_sel((c4 >> 2) + 2u);  // sub-scale byte (c4>>2) + 2 of the word: groups 1 and 3
-    }
+template <int FMT, int ACT, int NCH>
+__device__ __forceinline__ void set_unit_x(LaneX<FMT, ACT, NCH> &X, int c, const float (&v)[16]) {
     if (ACT == STRIX_ACT_F32) {
 #pragma unroll
-        for (int i = 0; i < 8; i++) X.v2[i] = make_float2(v[2 * i], v[2 * i + 1]);
-        if (FMT == FMT_Q4_0) {
-            float s = 0.f;
-#pragma unroll
-            for (int i = 0; i < 16; i++) s += v[i];
-            X.corr[0] = 136.0f * s;
-        } else if (FMT == FMT_Q6_K) {
-#pragma unroll
-            for (int k = 0; k < 4; k++) X.corr[k] = 160.0f * ((v[4 * k] + v[4 * k + 1]) + (v[4 * k + 2] + v[4 * k + 3]));
+        for (int p = 0; p < 8; p++) {
+            int i0, i1;
+            pair_index<FMT>(p, i0, i1);
+            X.v2[c][p] = make_float2(v[i0], v[i1]);
         }
     } else {
         // per-32 quantiser (xquant8, kernels.rs:864-876): d = amax/127, inv = d>0 ? 1/d : 0,
@@ -150,19 +164,18 @@ __device__ __forceinline__ void make_unit_x(UnitX<FMT, ACT> &X, const float (&v)
 #pragma unroll
             for (int i = 0; i < 16; i++) amax = fmaxf(amax, fabsf(v[i]));
             amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
-            float d = amax / 127.0f;
-            float inv = d > 0.f ? 1.0f / d : 0.f;
+            const float d = amax / 127.0f;
+            const float inv = d > 0.f ? 1.0f / d : 0.f;
             int sum = 0;
 #pragma unroll
             for (int g = 0; g < 4; g++) {
-                int q0 = quant1(v[4 * g], inv), q1 = quant1(v[4 * g + 1], inv);
-                int q2 = quant1(v[4 * g + 2], inv), q3 = quant1(v[4 * g + 3], inv);
+                const int q0 = quant1(v[4 * g], inv), q1 = quant1(v[4 * g + 1], inv);
+                const int q2 = quant1(v[4 * g + 2], inv), q3 = quant1(v[4 * g + 3], inv);
                 sum += q0 + q1 + q2 + q3;
-                X.q[g] = (uint32_t)(q0 & 0xff) | ((uint32_t)(q1 & 0xff) << 8) | ((uint32_t)(q2 & 0xff) << 16) |
-                         ((uint32_t)(q3 & 0xff) << 24);
+                X.q[c][g] = pack4(q0, q1, q2, q3);
             }
-            X.d[0] = d;
-            X.qs[0] = 8 * sum;
+            X.d[c][0] = d;
+            X.qs[c][0] = (FMT == FMT_Q4_0 ? 8 : 128) * sum;  // resident codes carry this offset
         } else {
 #pragma unroll
             for (int k = 0; k < 4; k++) {
@@ -171,123 +184,135 @@ __device__ __forceinline__ void make_unit_x(UnitX<FMT, ACT> &X, const float (&v)
                 amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
                 amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 2));
                 amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 4));
-                float d = amax / 127.0f;
-                float inv = d > 0.f ? 1.0f / d : 0.f;
-                int q0 = quant1(v[4 * k], inv), q1 = quant1(v[4 * k + 1], inv);
-                int q2 = quant1(v[4 * k + 2], inv), q3 = quant1(v[4 * k + 3], inv);
-                X.q[k] = (uint32_t)(q0 & 0xff) | ((uint32_t)(q1 & 0xff) << 8) | ((uint32_t)(q2 & 0xff) << 16) |
-                         ((uint32_t)(q3 & 0xff) << 24);
-                X.d[k] = d;
-                X.qs[k] = 32 * (q0 + q1 + q2 + q3);
+                const float d = amax / 127.0f;
+                const float inv = d > 0.f ? 1.0f / d : 0.f;
+                const int q0 = quant1(v[4 * k], inv), q1 = quant1(v[4 * k + 1], inv);
+                const int q2 = quant1(v[4 * k + 2], inv), q3 = quant1(v[4 * k + 3], inv);
+                X.q[c][k] = pack4(q0, q1, q2, q3);
+                X.d[c][k] = d;
+                X.qs[c][k] = 32 * (q0 + q1 + q2 + q3);
             }
         }
     }
 }
 
-// sum over 4 bytes of (2^k + byte_i) * x_i on two packed-f32x2 accumulators
-template <bool M7>
-__device__ __forceinline__ void fma4(uint32_t w, const float2 &xa, const float2 &xb, float2 &acc_a, float2 &acc_b) {
-    float2 p, q;
-    if (M7) {
-        p = make_float2(magic7<0>(w), magic7<1>(w));
-        q = make_float2(magic7<2>(w), magic7<3>(w));
-    } else {
-        p = make_float2(magic15<0>(w), magic15<1>(w));
-        q = make_float2(magic15<2>(w), magic15<3>(w));
-    }
-    acc_a = __ffma2_rn(p, xa, acc_a);
-    acc_b = __ffma2_rn(q, xb, acc_b);
-}
+// Byte step between unit c and unit c+1 of a lane (32 units further along the row).
+template <int FMT> struct Step;
+template <> struct Step<FMT_Q8_0> { static constexpr uint32_t w = 512, s = 32, hh = 0, sc = 0; };
+template <> struct Step<FMT_Q4_0> { static constexpr uint32_t w = 256, s = 32, hh = 0, sc = 0; };
+template <> struct Step<FMT_Q6_K> { static constexpr uint32_t w = 256, s = 4, hh = 128, sc = 32; };
 
-// Contribution of one unit of one resident row to that row's dot product.
+// Contribution of unit c of one resident row to that row's dot product.
 // `rb` = 32-bit shared address of the row's first byte.
-template <int FMT, int ACT>
-__device__ __forceinline__ float unit_dot(uint32_t rb, const UnitX<FMT, ACT> &X) {
+template <int FMT, int ACT, int NCH>
+__device__ __forceinline__ float unit_dot(uint32_t rb, const LaneX<FMT, ACT, NCH> &X, int c) {
+    const uint32_t cu = (uint32_t)c;
     if (FMT == FMT_Q8_0) {
-        const uint4 w = lds128(rb + X.off_w);
-        const float d = lds_f16(rb + X.off_s);
+        // resident codes are q + 128 (unsigned bytes)
+        const uint4 w = lds128(rb + X.off_w + cu * Step<FMT>::w);
+        const float d = lds_f16(rb + X.off_s + cu * Step<FMT>::s);
         if (ACT == STRIX_ACT_F32) {
-            // q + 128 is an unsigned byte; (32768 + 128 + q) - 32896 = q exactly, then packed FMAs
-            const uint32_t ws[4] = {w.x ^ 0x80808080u, w.y ^ 0x80808080u, w.z ^ 0x80808080u, w.w ^ 0x80808080u};
-            const float2 bias = make_float2(-32896.0f, -32896.0f);
+            const uint32_t ws[4] = {w.x, w.y, w.z, w.w};
             float2 acc_a = make_float2(0.f, 0.f), acc_b = make_float2(0.f, 0.f);
 #pragma unroll
             for (int g = 0; g < 4; g++) {
-                float2 p = make_float2(magic15<0>(ws[g]), magic15<1>(ws[g]));
-                float2 q = make_float2(magic15<2>(ws[g]), magic15<3>(ws[g]));
-                p = __fadd2_rn(p, bias);
-                q = __fadd2_rn(q, bias);
-                acc_a = __ffma2_rn(p, X.v2[2 * g], acc_a);
-                acc_b = __ffma2_rn(q, X.v2[2 * g + 1], acc_b);
+                acc_a = __ffma2_rn(unbias_pair(bytes_to_h2<0>(ws[g]), -1152.0f), X.v2[c][2 * g], acc_a);
+                acc_b = __ffma2_rn(unbias_pair(bytes_to_h2<2>(ws[g]), -1152.0f), X.v2[c][2 * g + 1], acc_b);
             }
-            return d * ((acc_a.x + acc_a.y) + (acc_b.x + acc_b.y));
+            acc_a = __fadd2_rn(acc_a, acc_b);
+            return d * (acc_a.x + acc_a.y);
         } else {
-            int isum = dp4a_ss(w.x, X.q[0], 0);
-            isum = dp4a_ss(w.y, X.q[1], isum);
-            isum = dp4a_ss(w.z, X.q[2], isum);
-            isum = dp4a_ss(w.w, X.q[3], isum);
-            return (d * X.d[0]) * (float)isum;
+            int isum = dp4a_us(w.x, X.q[c][0], -X.qs[c][0]);  // sum((q+128) xq) - 128 sum(xq)
+            isum = dp4a_us(w.y, X.q[c][1], isum);
+            isum = dp4a_us(w.z, X.q[c][2], isum);
+            isum = dp4a_us(w.w, X.q[c][3], isum);
+            return (d * X.d[c][0]) * (float)isum;
         }
     } else if (FMT == FMT_Q4_0) {
-        const uint2 w = lds64(rb + X.off_w);
-        const float d = lds_f16(rb + X.off_s);
-        const uint32_t lo0 = w.x & 0x0F0F0F0Fu, lo1 = w.y & 0x0F0F0F0Fu;
-        const uint32_t hi0 = (w.x >> 4) & 0x0F0F0F0Fu, hi1 = (w.y >> 4) & 0x0F0F0F0Fu;
+        const uint2 w = lds64(rb + X.off_w + cu * Step<FMT>::w);
+        const float d = lds_f16(rb + X.off_s + cu * Step<FMT>::s);
         if (ACT == STRIX_ACT_F32) {
-            // sum((128 + nib) x) - 136 sum(x) = sum((nib - 8) x); the second term starts the accumulator
-            float2 acc_a = make_float2(-X.corr[0], 0.f), acc_b = make_float2(0.f, 0.f);
-            fma4<true>(lo0, X.v2[0], X.v2[1], acc_a, acc_b);
-            fma4<true>(lo1, X.v2[2], X.v2[3], acc_a, acc_b);
-            fma4<true>(hi0, X.v2[4], X.v2[5], acc_a, acc_b);
-            fma4<true>(hi1, X.v2[6], X.v2[7], acc_a, acc_b);
-            return d * ((acc_a.x + acc_a.y) + (acc_b.x + acc_b.y));
+            float2 acc_a = make_float2(0.f, 0.f), acc_b = make_float2(0.f, 0.f);
+            const uint32_t wd[2] = {w.x, w.y};
+#pragma unroll
+            for (int k = 0; k < 2; k++) {
+                const uint32_t w0 = wd[k], w8 = wd[k] >> 8;
+                // nibble in bits 0..3 of a half: 0x6400 | n = 1024 + n;  in bits 4..7: 0x5400 | (n << 4) = 64 + n
+                const uint32_t lo02 = (w0 & 0x000F000Fu) | 0x64006400u, lo13 = (w8 & 0x000F000Fu) | 0x64006400u;
+                const uint32_t hi02 = (w0 & 0x00F000F0u) | 0x54005400u, hi13 = (w8 & 0x00F000F0u) | 0x54005400u;
+                acc_a = __ffma2_rn(unbias_pair(lo02, -1032.0f), X.v2[c][4 * k + 0], acc_a);
+                acc_b = __ffma2_rn(unbias_pair(lo13, -1032.0f), X.v2[c][4 * k + 1], acc_b);
+                acc_a = __ffma2_rn(unbias_pair(hi02, -72.0f), X.v2[c][4 * k + 2], acc_a);
+                acc_b = __ffma2_rn(unbias_pair(hi13, -72.0f), X.v2[c][4 * k + 3], acc_b);
+            }
+            acc_a = __fadd2_rn(acc_a, acc_b);
+            return d * (acc_a.x + acc_a.y);
         } else {
-            int isum = dp4a_us(lo0, X.q[0], -X.qs[0]);  // raw nibbles, minus 8 * sum(xq)
-            isum = dp4a_us(lo1, X.q[1], isum);
-            isum = dp4a_us(hi0, X.q[2], isum);
-            isum = dp4a_us(hi1, X.q[3], isum);
-            return (d * X.d[0]) * (float)isum;
+            const uint32_t lo0 = w.x & 0x0F0F0F0Fu, lo1 = w.y & 0x0F0F0F0Fu;
+            const uint32_t hi0 = (w.x >> 4) & 0x0F0F0F0Fu, hi1 = (w.y >> 4) & 0x0F0F0F0Fu;
+            int isum = dp4a_us(lo0, X.q[c][0], -X.qs[c][0]);  // raw nibbles, minus 8 * sum(xq)
+            isum = dp4a_us(lo1, X.q[c][1], isum);
+            isum = dp4a_us(hi0, X.q[c][2], isum);
+            isum = dp4a_us(hi1, X.q[c][3], isum);
+            return (d * X.d[c][0]) * (float)isum;
         }
     } else {
-        const uint32_t a = lds32(rb + X.off_w), b = lds32(rb + X.off_w + 32u), hh = lds32(rb + X.off_hh);
-        const uint2 scw = lds64(rb + X.off_sc);  // the half's 8 sub-scales
-        const float d = lds_f16(rb + X.off_s);
+        const uint32_t ow = rb + X.off_w + cu * Step<FMT>::w;
+        const uint32_t a = lds32(ow), b = lds32(ow + 32u), hh = lds32(rb + X.off_hh + cu * Step<FMT>::hh);
+        const uint2 scw = lds64(rb + X.off_sc + cu * Step<FMT>::sc);  // the half's 8 sub-scales
+        const float d = lds_f16(rb + X.off_s + cu * Step<FMT>::s);
         const uint32_t qw[4] = {(a & 0x0F0F0F0Fu) | ((hh & 0x03030303u) << 4),
                                 (b & 0x0F0F0F0Fu) | ((hh & 0x0C0C0C0Cu) << 2),
                                 ((a >> 4) & 0x0F0F0F0Fu) | (hh & 0x30303030u),
                                 ((b >> 4) & 0x0F0F0F0Fu) | ((hh >> 2) & 0x30303030u)};
         const float sc[4] = {(float)sext_byte(scw.x, X.sel_a), (float)sext_byte(scw.x, X.sel_b),
                              (float)sext_byte(scw.y, X.sel_a), (float)sext_byte(scw.y, X.sel_b)};
-        float t = 0.f;
+        if (ACT == STRIX_ACT_F32) {
+            float2 t2 = make_float2(0.f, 0.f);
 #pragma unroll
-        for (int k = 0; k < 4; k++) {
-            if (ACT == STRIX_ACT_F32) {
-                float2 acc_a = make_float2(-X.corr[k], 0.f), acc_b = make_float2(0.f, 0.f);
-                fma4<true>(qw[k], X.v2[2 * k], X.v2[2 * k + 1], acc_a, acc_b);
-                t = fmaf(sc[k], (acc_a.x + acc_a.y) + (acc_b.x + acc_b.y), t);
-            } else {
-                const int isum = dp4a_us(qw[k], X.q[k], -X.qs[k]);  // minus 32 * sum(xq)
-                t = fmaf(sc[k] * X.d[k], (float)isum, t);
+            for (int k = 0; k < 4; k++) {
+                float2 acc = __ffma2_rn(unbias_pair(bytes_to_h2<0>(qw[k]), -1056.0f), X.v2[c][2 * k], make_float2(0.f, 0.f));
+                acc = __ffma2_rn(unbias_pair(bytes_to_h2<2>(qw[k]), -1056.0f), X.v2[c][2 * k + 1], acc);
+                t2 = __ffma2_rn(make_float2(sc[k], sc[k]), acc, t2);
             }
+            return d * (t2.x + t2.y);
+        } else {
+            float t = 0.f;
+#pragma unroll
+            for (int k = 0; k < 4; k++) {
+                const int isum = dp4a_us(qw[k], X.q[c][k], -X.qs[c][k]);  // minus 32 * sum(xq)
+                t = fmaf(sc[k] * X.d[c][k], (float)isum, t);
+            }
+            return d * t;
         }
-        return d * t;
     }
 }
 
-// Sums GEMV_RB (= 4) per-lane values across the warp with 6 shuffles instead of 20: lanes trade the
-// halves they do not keep (xor 16, then xor 8), which leaves one row per lane, then a 3-step
-// butterfly over xor 4/2/1. On return lane 8k (k = 0..3) holds the full sum of row k.
-__device__ __forceinline__ float batch_reduce(const float (&v)[GEMV_RB], uint32_t lane) {
-    static_assert(GEMV_RB == 4, "batch_reduce is written for 4 rows");
-    const bool up16 = (lane & 16u) != 0u, up8 = (lane & 8u) != 0u;
-    // after this step lanes 0-15 hold rows 0,1 and lanes 16-31 hold rows 2,3
-    float k0 = up16 ? v[2] : v[0], s0 = up16 ? v[0] : v[2];
-    float k1 = up16 ? v[3] : v[1], s1 = up16 ? v[1] : v[3];
-    k0 += __shfl_xor_sync(0xffffffffu, s0, 16);
-    k1 += __shfl_xor_sync(0xffffffffu, s1, 16);
-    // lanes with bit 3 clear keep the even row of their pair, the others the odd one
-    float k = up8 ? k1 : k0, sx = up8 ? k0 : k1;
-    k += __shfl_xor_sync(0xffffffffu, sx, 8);
+// Sums RB per-lane values across the warp with fewer shuffles than RB separate butterflies: lanes
+// trade the halves they do not keep (xor 16, then xor 8 for RB = 4), which leaves one row per lane,
+// then a plain butterfly over the remaining lane bits. On return lane (32/RB) k holds the sum of row k.
+template <int RB>
+__device__ __forceinline__ float batch_reduce(const float (&v)[RB], uint32_t lane) {
+    static_assert(RB == 2 || RB == 4, "batch_reduce is written for 2 or 4 rows");
+    const bool up16 = (lane & 16u) != 0u;
+    float k;
+    if (RB == 4) {
+        const bool up8 = (lane & 8u) != 0u;
+        // after this step lanes 0-15 hold rows 0,1 and lanes 16-31 hold rows 2,3
+        float k0 = up16 ? v[2] : v[0], s0 = up16 ? v[0] : v[2];
+        float k1 = up16 ? v[RB - 1] : v[1], s1 = up16 ? v[1] : v[RB - 1];
+        k0 += __shfl_xor_sync(0xffffffffu, s0, 16);
+        k1 += __shfl_xor_sync(0xffffffffu, s1, 16);
+        // lanes with bit 3 clear keep the even row of their pair, the others the odd one
+        k = up8 ? k1 : k0;
+        const float sx = up8 ? k0 : k1;
+        k += __shfl_xor_sync(0xffffffffu, sx, 8);
+    } else {
+        k = up16 ? v[1] : v[0];
+        const float sx = up16 ? v[0] : v[1];
+        k += __shfl_xor_sync(0xffffffffu, sx, 16);
+        k += __shfl_xor_sync(0xffffffffu, k, 8);
+    }
     k += __shfl_xor_sync(0xffffffffu, k, 4);
     k += __shfl_xor_sync(0xffffffffu, k, 2);
     k += __shfl_xor_sync(0xffffffffu, k, 1);
@@ -311,29 +336,43 @@ __device__ __forceinline__ TileRef tile_ref(const GemvArgs &A, uint32_t t) {
     return r;
 }
 
-template <int FMT, int ACT, int NCH>
-__global__ void __launch_bounds__(GEMV_MAX_WARPS * 32, 1) gemv_kernel(const __grid_constant__ GemvArgs A) {
+// Shared-memory map of gemv_kernel (offsets in bytes):
+//   0    full[8]   mbarriers: a stage's bulk copy has landed        (producer arms, copy completes)
+//   64   empty[8]  mbarriers: every consumer warp is done with it   (one arrival per consumer warp)
+//   128  ctl[0]    abort flag (a bounded wait ran out)
+//   256  red[32]   block reduction scratch (RMSNORM prologue)
+//   512  part      per slot: 2 x RB x wc partial sums
+//   ...  stages    n_stages x stage_bytes, 128-byte aligned
+constexpr uint32_t SMEM_PART_OFF = 512;
+
+template <int FMT, int ACT, int NCH, int RB>
+__global__ void __launch_bounds__((gemv_warps(ACT) + 1) * 32, 1) gemv_kernel(const __grid_constant__ GemvArgs A) {
     extern __shared__ __align__(128) uint8_t smem[];
-    uint64_t *full = reinterpret_cast<uint64_t *>(smem);        // GEMV_MAX_STAGES barriers
-    uint32_t *ctl = reinterpret_cast<uint32_t *>(smem + 64);    // [0] = abort flag
-    float *red = reinterpret_cast<float *>(smem + 128);         // 32 floats: block reduction
-    float *part = reinterpret_cast<float *>(smem + 256);        // 2 x rows_per_tile x wc partial sums
-    uint8_t *stages = smem + 256 + ((2u * A.rows_per_tile * A.wc * 4u + 127u) & ~127u);
+    uint64_t *full = reinterpret_cast<uint64_t *>(smem);
+    uint64_t *empty = reinterpret_cast<uint64_t *>(smem + 64);
+    volatile uint32_t *ctl = reinterpret_cast<volatile uint32_t *>(smem + 128);
+    float *red = reinterpret_cast<float *>(smem + 256);
+    float *part = reinterpret_cast<float *>(smem + SMEM_PART_OFF);
+    uint8_t *stages = smem + A.stage_off;
 
     const uint32_t tid = threadIdx.x, lane = tid & 31u, warp = tid >> 5;
+    const uint32_t n_cons = A.wc * A.slots;  // consumer warps; warp n_cons is the producer
     const uint32_t S = A.n_stages, grid = gridDim.x, bid = blockIdx.x;
     const uint32_t my_n = (A.n_tiles > bid) ? (A.n_tiles - bid + grid - 1) / grid : 0;
     const RowLayout L = A.L;
     const uint32_t U = L.in_dim / 16u;
 
     if (tid == 0) {
-        for (uint32_t s = 0; s < S; s++) mbar_init(&full[s], 1);
+        for (uint32_t s = 0; s < S; s++) {
+            mbar_init(&full[s], 1);
+            mbar_init(&empty[s], n_cons);
+        }
         ctl[0] = 0;
         mbar_fence_init();
     }
     __syncthreads();
-    // Start the first S tile copies before the activation prologue so that they overlap it.
-    if (tid == 0) {
+    // The first S tile copies start before the activation prologue and overlap it.
+    if (warp == n_cons && lane == 0) {
         const uint32_t n0 = min(S, my_n);
         for (uint32_t i = 0; i < n0; i++) {
             TileRef t = tile_ref(A, bid + i * grid);
@@ -343,7 +382,6 @@ __global__ void __launch_bounds__(GEMV_MAX_WARPS * 32, 1) gemv_kernel(const __gr
         }
     }
 
-    // ---- activation prologue: this lane's x values, kept in registers for the whole kernel ----
     float scale = 1.0f;
     if (A.pre == STRIX_PRE_RMSNORM) {
         // rmsnorm (crates/strix-backend-cpu/src/qwen3.rs:107-114): x * (1/sqrt(mean(x^2)+eps)) * w
@@ -359,127 +397,191 @@ __global__ void __launch_bounds__(GEMV_MAX_WARPS * 32, 1) gemv_kernel(const __gr
         for (uint32_t w = 0; w < (blockDim.x >> 5); w++) tot += red[w];
         scale = 1.0f / sqrtf(tot / (float)L.in_dim + A.eps);
     }
-    const uint32_t cw = warp % A.wc, slot = warp / A.wc;
-    UnitX<FMT, ACT> X[NCH];
-#pragma unroll
-    for (int c = 0; c < NCH; c++) {
-        const uint32_t u = (cw + (uint32_t)c * A.wc) * 32u + lane;
-        const bool valid = u < U;
-        float v[16];
-#pragma unroll
-        for (uint32_t g = 0; g < 4; g++) {
-            float4 a4 = make_float4(0.f, 0.f, 0.f, 0.f);
-            if (valid) {
-                const uint32_t e = unit_elem<FMT>(u, g);
-                a4 = __ldg(reinterpret_cast<const float4 *>(A.a + e));
-                if (A.pre != STRIX_PRE_NONE) {
-                    const float4 b4 = __ldg(reinterpret_cast<const float4 *>(A.b + e));
-                    if (A.pre == STRIX_PRE_RMSNORM) {
-                        a4.x = (a4.x * scale) * b4.x; a4.y = (a4.y * scale) * b4.y;
-                        a4.z = (a4.z * scale) * b4.z; a4.w = (a4.w * scale) * b4.w;
-                    } else if (A.pre == STRIX_PRE_SWIGLU) {
-                        a4.x = silu_f(a4.x) * b4.x; a4.y = silu_f(a4.y) * b4.y;
-                        a4.z = silu_f(a4.z) * b4.z; a4.w = silu_f(a4.w) * b4.w;
-                    } else {
-                        a4.x = gelu_tanh_f(a4.x) * b4.x; a4.y = gelu_tanh_f(a4.y) * b4.y;
-                        a4.z = gelu_tanh_f(a4.z) * b4.z; a4.w = gelu_tanh_f(a4.w) * b4.w;
-                    }
-                }
+
+    if (warp == n_cons) {
+        // ---- producer: refill a stage as soon as every consumer warp has released it ----
+        if (lane == 0) {
+            for (uint32_t i = S; i < my_n; i++) {
+                const uint32_t s = i % S;
+                if (!ctl[0] && !mbar_wait_bounded(&empty[s], ((i / S) - 1u) & 1u, A.status)) ctl[0] = 1;
+                TileRef t = tile_ref(A, bid + i * grid);
+                const uint32_t bytes = t.rows * L.row_stride;
+                mbar_arrive_expect_tx(&full[s], bytes);
+                bulk_g2s(stages + (uint64_t)s * A.stage_bytes, t.src, bytes, &full[s]);
             }
-            v[4 * g] = a4.x; v[4 * g + 1] = a4.y; v[4 * g + 2] = a4.z; v[4 * g + 3] = a4.w;
+            if (ctl[0]) {
+                // after an abort consumers stop waiting: let the copies still in flight land (bounded)
+                // before the CTA's shared memory is released
+                for (uint32_t i = (my_n > S ? my_n - S : 0); i < my_n; i++)
+                    mbar_wait_bounded(&full[i % S], (i / S) & 1u, nullptr);
+            }
         }
-        make_unit_x<FMT, ACT>(X[c], v, u, L);
+        return;
     }
 
-    // ---- stream the tiles ----
-    uint32_t buf = 0;
-    bool aborted = false;
-    uint32_t i = 0;
-    for (; i < my_n; i++) {
-        const uint32_t s = i % S, ph = (i / S) & 1u;
-        const bool ok = mbar_wait_bounded(&full[s], ph, A.status);
-        if (!ok) ctl[0] = 1;
-        const TileRef t = tile_ref(A, bid + i * grid);
-        float *pp = part + buf * (A.rows_per_tile * A.wc);
-        if (ok) {
-            const uint32_t st = smem_u32(stages) + s * A.stage_bytes;
-            // A slot works on GEMV_RB consecutive rows at a time: RB independent load/dot chains per
-            // lane, then one transposed warp reduction for the whole batch. Rows past the tile's end
-            // read whatever the stage still holds from an earlier tile; their sums are dropped below.
-            for (uint32_t r0 = slot * GEMV_RB; r0 < t.rows; r0 += A.slots * GEMV_RB) {
-                float acc[GEMV_RB];
+    // ---- consumers: this lane's x values, kept in registers for the whole kernel ----
+    const uint32_t cw = warp % A.wc, slot = warp / A.wc;
+    LaneX<FMT, ACT, NCH> X;
+    {
+        const uint32_t u0 = cw * (uint32_t)NCH * 32u + lane;  // warp cw owns runs cw*NCH .. cw*NCH+NCH-1
+        X.off_hh = X.off_sc = X.sel_a = X.sel_b = 0;
+        if (FMT == FMT_Q8_0) {
+            X.off_w = u0 * 16u;
+            X.off_s = L.off_d + 2u * (u0 >> 1);
+        } else if (FMT == FMT_Q4_0) {
+            X.off_w = u0 * 8u;
+            X.off_s = L.off_d + 2u * (u0 >> 1);
+        } else {
+            const uint32_t sb = u0 >> 4, r = u0 & 15u, h = r >> 3, c4 = r & 7u;
+            X.off_w = sb * 128u + h * 64u + c4 * 4u;
+            X.off_hh = L.off_qh + sb * 64u + h * 32u + c4 * 4u;
+            X.off_sc = L.off_sc + sb * 16u + h * 8u;
+            X.off_s = L.off_d + 2u * sb;
+            X.sel_a = sext_sel(c4 >> 2);         // sub-scale byte (c4>>2)     of a word: groups 0 and 2
+            X.sel_b = sext_sel((c4 >> 2) + 2u);  // sub-scale byte (c4>>2) + 2 of a word: groups 1 and 3
+        }
+        X.valid = 0;
 #pragma unroll
-                for (int j = 0; j < GEMV_RB; j++) acc[j] = 0.f;
-                const uint32_t rb0 = st + r0 * L.row_stride;
+        for (int c = 0; c < NCH; c++) {
+            const uint32_t u = u0 + 32u * (uint32_t)c;
+            const bool valid = u < U;
+            if (valid) X.valid |= 1u << c;
+            float v[16];
 #pragma unroll
-                for (int c = 0; c < NCH; c++) {
-                    const uint32_t u = (cw + (uint32_t)c * A.wc) * 32u + lane;
-                    if (u < U) {
-#pragma unroll
-                        for (int j = 0; j < GEMV_RB; j++)
-                            acc[j] += unit_dot<FMT, ACT>(rb0 + (uint32_t)j * L.row_stride, X[c]);
+            for (uint32_t g = 0; g < 4; g++) {
+                float4 a4 = make_float4(0.f, 0.f, 0.f, 0.f);
+                if (valid) {
+                    const uint32_t e = unit_elem<FMT>(u, g);
+                    a4 = __ldg(reinterpret_cast<const float4 *>(A.a + e));
+                    if (A.pre != STRIX_PRE_NONE) {
+                        const float4 b4 = __ldg(reinterpret_cast<const float4 *>(A.b + e));
+                        if (A.pre == STRIX_PRE_RMSNORM) {
+                            a4.x = (a4.x * scale) * b4.x; a4.y = (a4.y * scale) * b4.y;
+                            a4.z = (a4.z * scale) * b4.z; a4.w = (a4.w * scale) * b4.w;
+                        } else if (A.pre == STRIX_PRE_SWIGLU) {
+                            a4.x = silu_f(a4.x) * b4.x; a4.y = silu_f(a4.y) * b4.y;
+                            a4.z = silu_f(a4.z) * b4.z; a4.w = silu_f(a4.w) * b4.w;
+                        } else {
+                            a4.x = gelu_tanh_f(a4.x) * b4.x; a4.y = gelu_tanh_f(a4.y) * b4.y;
+                            a4.z = gelu_tanh_f(a4.z) * b4.z; a4.w = gelu_tanh_f(a4.w) * b4.w;
+                        }
                     }
                 }
-                const float tot = batch_reduce(acc, lane);
-                // lane 8k now holds the sum of row r0 + k
-                const uint32_t rr = r0 + (lane >> 3);
-                if ((lane & 7u) == 0u && rr < t.rows) pp[rr * A.wc + cw] = tot;
+                v[4 * g] = a4.x; v[4 * g + 1] = a4.y; v[4 * g + 2] = a4.z; v[4 * g + 3] = a4.w;
+            }
+            set_unit_x<FMT, ACT, NCH>(X, c, v);
+        }
+    }
+
+    // ---- stream the tiles. The wc warps of a slot meet on a named barrier per row batch; slots
+    //      run independently of one another, and nothing in the loop is CTA-wide. ----
+    float *pp = part + slot * (2u * RB * A.wc);
+    const uint32_t bar_id = 1u + slot, bar_n = A.wc * 32u;
+    uint32_t buf = 0;
+    const uint32_t st0 = smem_u32(stages);
+    const bool skip = (A.debug & 1u) != 0u;
+    constexpr uint32_t LPR = 32u / RB;  // after batch_reduce lane LPR*k holds row k
+    const uint32_t bpt = A.rows_per_tile / RB;  // batches per (full) tile
+    for (uint32_t i = 0; i < my_n; i++) {
+        const uint32_t s = i % S;
+        // once any wait has run out, nobody waits again: the loop runs to its end on whatever is in
+        // shared memory (barrier participation stays consistent) and the status word reports it
+        if (!ctl[0] && !mbar_wait_bounded(&full[s], (i / S) & 1u, A.status)) ctl[0] = 1;
+        const TileRef t = tile_ref(A, bid + i * grid);
+        const uint32_t st = st0 + s * A.stage_bytes;
+        float *y = A.mat[t.mat].y + t.row0;
+        // Row batches go round-robin over the slots, counted across this CTA's tiles, so that small
+        // tiles (fewer batches than slots) still keep every slot busy. Rows past the tile's end read
+        // whatever the stage still holds; their sums are dropped.
+        const uint32_t first = (slot + A.slots - (i * bpt) % A.slots) % A.slots;  // this slot's first batch in the tile
+        for (uint32_t r0 = first * RB; r0 < t.rows && !skip; r0 += A.slots * RB) {
+            float acc[RB];
+#pragma unroll
+            for (int j = 0; j < RB; j++) acc[j] = 0.f;
+            const uint32_t rb0 = st + r0 * L.row_stride;
+#pragma unroll
+            for (int c = 0; c < NCH; c++) {
+                if (X.valid & (1u << c)) {
+#pragma unroll
+                    for (int j = 0; j < RB; j++)
+                        acc[j] += unit_dot<FMT, ACT, NCH>(rb0 + (uint32_t)j * L.row_stride, X, c);
+                }
+            }
+            const float tot = batch_reduce<RB>(acc, lane);
+            if (A.wc == 1) {
+                const uint32_t rr = r0 + lane / LPR;
+                if ((lane & (LPR - 1u)) == 0u && rr < t.rows) y[rr] = tot;
+            } else {
+                float *pb = pp + buf * (RB * A.wc);
+                if ((lane & (LPR - 1u)) == 0u) pb[(lane / LPR) * A.wc + cw] = tot;
+                __syncwarp();
+                asm volatile("bar.sync %0, %1;" ::"r"(bar_id), "r"(bar_n) : "memory");
+                if (cw == 0 && lane < RB && r0 + lane < t.rows) {
+                    // fixed summation order over the wc column owners: reproducible run to run
+                    float sum = 0.f;
+                    for (uint32_t k = 0; k < A.wc; k++) sum += pb[lane * A.wc + k];
+                    y[r0 + lane] = sum;
+                }
+                buf ^= 1u;  // the next batch writes the other buffer while warp cw==0 still reads this one
             }
         }
-        __syncthreads();
-        if (ctl[0]) { aborted = true; break; }
-        if (tid == 0 && i + S < my_n) {
-            // the stage is drained (barrier above): refill it with the tile S steps ahead
-            fence_proxy_async_smem();
-            TileRef n = tile_ref(A, bid + (i + S) * grid);
-            const uint32_t bytes = n.rows * L.row_stride;
-            mbar_arrive_expect_tx(&full[s], bytes);
-            bulk_g2s(stages + (uint64_t)s * A.stage_bytes, n.src, bytes, &full[s]);
-        }
-        if (tid < t.rows) {
-            float sum = 0.f;
-            for (uint32_t c = 0; c < A.wc; c++) sum += pp[tid * A.wc + c];
-            A.mat[t.mat].y[t.row0 + tid] = sum;
-        }
-        buf ^= 1u;
-    }
-    if (aborted && tid == 0) {
-        // Copies already issued for later tiles are still in flight: give them a bounded
-        // chance to land before the CTA's shared memory is released.
-        for (uint32_t j = i + 1; j < min(my_n, i + S); j++) mbar_wait_bounded(&full[j % S], (j / S) & 1u, nullptr);
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&empty[s]);  // this warp's reads of the stage are complete
     }
 }
 
 // ------------------------------------------------------------------ host side
 static inline uint32_t align128u(uint32_t v) { return (v + 127u) & ~127u; }
 
+// Largest NCH (runs of 32 units per consumer warp) a kernel variant is built for: bounded by the
+// registers the x values need (16 per run as f32; as int8 6 per run, 12 for Q6_K).
+static inline uint32_t max_nch(int fmt, int act) { return (act == STRIX_ACT_F32 || fmt == FMT_Q6_K) ? 5u : 8u; }
+
 bool gemv_plan(GemvArgs &a, int num_sms, size_t smem_optin) {
     const uint32_t K = a.L.in_dim;
     if (K == 0 || K % 32 != 0) return false;
     const uint32_t U = K / 16, C = (U + 31) / 32;
-    const uint32_t nch = (C + GEMV_MAX_WARPS - 1) / GEMV_MAX_WARPS;
-    if (nch > 4) return false;
-    const uint32_t wc = (C + nch - 1) / nch;
-    const uint32_t slots = GEMV_MAX_WARPS / wc > 0 ? GEMV_MAX_WARPS / wc : 1;
+    // wc warps x nch runs cover the C runs of a row; prefer the split that wastes the fewest
+    // warp-slots (runs past C, and consumer warps left over when wc does not divide the pool)
+    const uint32_t cap = max_nch(a.L.fmt, a.act);
+    uint32_t wc = 0, nch = 0;
+    double best = 1e30;
+    const uint32_t pool = (uint32_t)gemv_warps(a.act);
+    for (uint32_t w = (C + cap - 1) / cap; w <= pool && w <= C; w++) {
+        const uint32_t n = (C + w - 1) / w;
+        if (n > cap) continue;
+        const uint32_t sl = pool / w;
+        const double waste = ((double)(w * n) / C) * ((double)pool / (w * sl)) + 0.02 * w;
+        if (waste < best) { best = waste; wc = w; nch = n; }
+    }
+    if (wc == 0) return false;  // in_dim beyond what the consumer warps can hold in registers
+    const uint32_t slots = pool / wc;
     const uint32_t stride = a.L.row_stride;
     const uint32_t budget = (uint32_t)smem_optin - 1024u;
 
-    // A tile is a whole number of row batches for every slot: a multiple of slots * GEMV_RB rows,
-    // about 24-48 KB, capped at 160 rows. Among candidate heights pick the one with the least
-    // work on the busiest CTA (bytes streamed plus a fixed charge per tile).
-    const uint32_t quantum = slots * GEMV_RB;
-    uint32_t mmax = 40960u / (quantum * stride);
-    if (mmax < 1) mmax = 1;
-    while (mmax > 1 && mmax * quantum > 160) mmax--;
-    uint32_t best_rt = quantum;
+    // Tile height: any multiple of rb up to ~72 KB.
+    // Large tiles amortise the per-tile bookkeeping and two to four stages of them keep HBM busy;
+    // few rows per SM want small tiles so that the busiest CTA does not carry a whole extra tile.
+    // Cost of a candidate = tiles on the busiest CTA x (bytes streamed + a fixed charge per tile).
+    // (Measured: shrinking the tiles of a small launch does not help; its time is set by the
+    // serial work per warp, not by the arrival of the first tile.)
+    uint32_t target = 73728u;
+    if (const char *e = getenv("STRIX_GEMV_TILE_BYTES")) target = (uint32_t)atoi(e);  // tuning knob
+    // A warp carries rb rows at once: four give more independent work per lane and fewer
+    // reductions per row; two when four rows of a long row would overshoot the tile size.
+    const uint32_t rb = (4u * stride <= target) ? 4u : 2u;
+    a.rb = rb;
+    uint32_t jmax = target / (rb * stride);
+    if (jmax < 1) jmax = 1;
+    uint32_t best_rt = rb;
     uint64_t best_cost = ~0ull;
-    for (uint32_t m = mmax; m >= 1 && 2 * m >= mmax; m--) {
-        const uint32_t rt = m * quantum;
+    for (uint32_t j = jmax; j >= 1; j--) {
+        const uint32_t rt = j * rb;
         uint64_t tiles = 0;
         for (int k = 0; k < a.nmat; k++) tiles += (a.mat[k].rows + rt - 1) / rt;
         if (tiles == 0) tiles = 1;
         const uint64_t per_cta = (tiles + (uint64_t)num_sms - 1) / (uint64_t)num_sms;
-        const uint64_t cost = per_cta * ((uint64_t)rt * stride + 2048u);
+        const uint64_t cost = per_cta * ((uint64_t)rt * stride + 4096u);
         if (cost < best_cost) { best_cost = cost; best_rt = rt; }
     }
     const uint32_t rt = best_rt;
@@ -493,11 +595,18 @@ bool gemv_plan(GemvArgs &a, int num_sms, size_t smem_optin) {
     a.wc = wc;
     a.slots = slots;
     a.nch = nch;
-    const uint32_t stage_off = 256u + align128u(2u * rt * wc * 4u);
+    const uint32_t stage_off = SMEM_PART_OFF + align128u(slots * 2u * rb * wc * 4u);
+    a.stage_off = stage_off;
     a.stage_bytes = align128u(rt * stride);
     if (budget < stage_off + 2u * a.stage_bytes) return false;
     uint32_t S = (budget - stage_off) / a.stage_bytes;
-    if (S > GEMV_MAX_STAGES) S = GEMV_MAX_STAGES;
+    if (S > (a.stage_bytes > 32768u ? 4u : (uint32_t)GEMV_MAX_STAGES)) S = a.stage_bytes > 32768u ? 4u : (uint32_t)GEMV_MAX_STAGES;
+    if (const char *e = getenv("STRIX_GEMV_STAGES")) {  // tuning knob
+        const uint32_t v = (uint32_t)atoi(e);
+        if (v >= 2 && v <= (uint32_t)GEMV_MAX_STAGES && stage_off + v * a.stage_bytes <= budget) S = v;
+    }
+    a.debug = 0;
+    if (const char *e = getenv("STRIX_GEMV_DEBUG")) a.debug = (uint32_t)atoi(e);  // 1 = stream only, no arithmetic
     a.n_stages = S;
     a.smem_bytes = stage_off + S * a.stage_bytes;
     a.grid = a.n_tiles < (uint32_t)num_sms ? a.n_tiles : (uint32_t)num_sms;
@@ -506,52 +615,72 @@ bool gemv_plan(GemvArgs &a, int num_sms, size_t smem_optin) {
 
 template <int FMT, int ACT, int NCH>
 static cudaError_t launch_t(const GemvArgs &a, cudaStream_t stream) {
-    const uint32_t threads = a.wc * a.slots * 32u;
-    gemv_kernel<FMT, ACT, NCH><<<a.grid, threads, a.smem_bytes, stream>>>(a);
+    const uint32_t threads = (a.wc * a.slots + 1u) * 32u;  // consumer warps + one producer warp
+    if (a.rb == 4)
+        gemv_kernel<FMT, ACT, NCH, 4><<<a.grid, threads, a.smem_bytes, stream>>>(a);
+    else
+        gemv_kernel<FMT, ACT, NCH, 2><<<a.grid, threads, a.smem_bytes, stream>>>(a);
     return cudaGetLastError();
 }
 
-template <int FMT, int ACT>
-static cudaError_t launch_nch(const GemvArgs &a, cudaStream_t stream) {
-    switch (a.nch) {
-        case 1: return launch_t<FMT, ACT, 1>(a, stream);
-        case 2: return launch_t<FMT, ACT, 2>(a, stream);
-        case 3: return launch_t<FMT, ACT, 3>(a, stream);
-        default: return launch_t<FMT, ACT, 4>(a, stream);
-    }
-}
-
 template <int FMT>
-static cudaError_t launch_act(const GemvArgs &a, cudaStream_t stream) {
-    return a.act == STRIX_ACT_Q8DOT ? launch_nch<FMT, STRIX_ACT_Q8DOT>(a, stream)
-                                    : launch_nch<FMT, STRIX_ACT_F32>(a, stream);
+static cudaError_t launch_fmt(const GemvArgs &a, cudaStream_t stream) {
+    if (a.act == STRIX_ACT_F32) {
+        switch (a.nch) {
+            case 1: return launch_t<FMT, STRIX_ACT_F32, 1>(a, stream);
+            case 2: return launch_t<FMT, STRIX_ACT_F32, 2>(a, stream);
+            case 3: return launch_t<FMT, STRIX_ACT_F32, 3>(a, stream);
+            case 4: return launch_t<FMT, STRIX_ACT_F32, 4>(a, stream);
+            default: return launch_t<FMT, STRIX_ACT_F32, 5>(a, stream);
+        }
+    }
+    switch (a.nch) {
+        case 1: return launch_t<FMT, STRIX_ACT_Q8DOT, 1>(a, stream);
+        case 2: return launch_t<FMT, STRIX_ACT_Q8DOT, 2>(a, stream);
+        case 3: return launch_t<FMT, STRIX_ACT_Q8DOT, 3>(a, stream);
+        case 4: return launch_t<FMT, STRIX_ACT_Q8DOT, 4>(a, stream);
+        case 5: return launch_t<FMT, STRIX_ACT_Q8DOT, 5>(a, stream);
+        default: break;
+    }
+    if constexpr (FMT != FMT_Q6_K) {
+        switch (a.nch) {
+            case 6: return launch_t<FMT, STRIX_ACT_Q8DOT, 6>(a, stream);
+            case 7: return launch_t<FMT, STRIX_ACT_Q8DOT, 7>(a, stream);
+            default: return launch_t<FMT, STRIX_ACT_Q8DOT, 8>(a, stream);
+        }
+    }
+    return cudaErrorInvalidValue;
 }
 
 cudaError_t launch_gemv(const GemvArgs &a, cudaStream_t stream) {
     if (a.n_tiles == 0) return cudaSuccess;
     switch (a.L.fmt) {
-        case FMT_Q4_0: return launch_act<FMT_Q4_0>(a, stream);
-        case FMT_Q8_0: return launch_act<FMT_Q8_0>(a, stream);
-        default: return launch_act<FMT_Q6_K>(a, stream);
+        case FMT_Q4_0: return launch_fmt<FMT_Q4_0>(a, stream);
+        case FMT_Q8_0: return launch_fmt<FMT_Q8_0>(a, stream);
+        default: return launch_fmt<FMT_Q6_K>(a, stream);
     }
 }
 
 template <int FMT, int ACT, int NCH>
 static cudaError_t optin_one(size_t bytes) {
-    return cudaFuncSetAttribute(gemv_kernel<FMT, ACT, NCH>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes);
-}
-template <int FMT, int ACT>
-static cudaError_t optin_nch(size_t b) {
-    cudaError_t e;
-    if ((e = optin_one<FMT, ACT, 1>(b)) != cudaSuccess) return e;
-    if ((e = optin_one<FMT, ACT, 2>(b)) != cudaSuccess) return e;
-    if ((e = optin_one<FMT, ACT, 3>(b)) != cudaSuccess) return e;
-    return optin_one<FMT, ACT, 4>(b);
+    cudaError_t e = cudaFuncSetAttribute(gemv_kernel<FMT, ACT, NCH, 4>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes);
+    if (e != cudaSuccess) return e;
+    return cudaFuncSetAttribute(gemv_kernel<FMT, ACT, NCH, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes);
 }
 template <int FMT>
 static cudaError_t optin_fmt(size_t b) {
-    cudaError_t e = optin_nch<FMT, STRIX_ACT_F32>(b);
-    return e != cudaSuccess ? e : optin_nch<FMT, STRIX_ACT_Q8DOT>(b);
+    cudaError_t e;
+#define STRIX_OPTIN(ACT, N) \
+    if ((e = optin_one<FMT, ACT, N>(b)) != cudaSuccess) return e;
+    STRIX_OPTIN(STRIX_ACT_F32, 1) STRIX_OPTIN(STRIX_ACT_F32, 2) STRIX_OPTIN(STRIX_ACT_F32, 3)
+    STRIX_OPTIN(STRIX_ACT_F32, 4) STRIX_OPTIN(STRIX_ACT_F32, 5)
+    STRIX_OPTIN(STRIX_ACT_Q8DOT, 1) STRIX_OPTIN(STRIX_ACT_Q8DOT, 2) STRIX_OPTIN(STRIX_ACT_Q8DOT, 3)
+    STRIX_OPTIN(STRIX_ACT_Q8DOT, 4) STRIX_OPTIN(STRIX_ACT_Q8DOT, 5)
+    if constexpr (FMT != FMT_Q6_K) {
+        STRIX_OPTIN(STRIX_ACT_Q8DOT, 6) STRIX_OPTIN(STRIX_ACT_Q8DOT, 7) STRIX_OPTIN(STRIX_ACT_Q8DOT, 8)
+    }
+#undef STRIX_OPTIN
+    return cudaSuccess;
 }
 
 cudaError_t gemv_prepare_device(size_t smem_optin) {

@@ -15,8 +15,9 @@ cudaError_t launch_dequant(const uint8_t *d_res, float *d_out, const RowLayout &
 // ---- dequant-GEMV -------------------------------------------------------
 constexpr int GEMV_MAX_MATS = 3;
 constexpr int GEMV_MAX_STAGES = 8;
-constexpr int GEMV_MAX_WARPS = 20;  // 640 threads per CTA, one CTA per SM
-constexpr int GEMV_RB = 4;          // rows a warp carries at once (independent chains, one batched reduction)
+// Consumer warps per CTA (plus one producer warp), one CTA per SM. The f32-activation kernels keep
+// up to 80 x values per lane in registers, so they run fewer, fatter warps.
+constexpr int gemv_warps(int act) { return act == 0 /* STRIX_ACT_F32 */ ? 12 : 16; }
 
 struct GemvMat {
     const uint8_t *w;  // resident rows of this accelerator's shard
@@ -37,12 +38,15 @@ struct GemvArgs {
     uint32_t rows_per_tile;
     uint32_t n_tiles;
     uint32_t stage_bytes;  // multiple of 128
+    uint32_t stage_off;    // byte offset of the first stage in dynamic shared memory
     uint32_t n_stages;
     uint32_t wc;     // warps that split a row's K range between them
     uint32_t slots;  // groups of wc warps, each working on different rows of a tile
-    uint32_t nch;    // 32-unit chunks of K owned by one warp (1..4)
+    uint32_t nch;    // runs of 32 units of K owned by one consumer warp
+    uint32_t rb;     // rows a warp carries at once (2 or 4): independent chains, one batched reduction
     uint32_t grid;
     uint32_t smem_bytes;
+    uint32_t debug;  // measurement only: bit 0 = stream the tiles but skip the arithmetic
     uint32_t *status;
 };
 

@@ -10,7 +10,8 @@
 //   Q8_0 row: [ qs : nb x 32 B ][ d : nb x f16 ]                      pad to 16
 //   Q6_K row: [ ql : nb x 128 B ][ qh : nb x 64 B ][ sc : nb x 16 B ][ d : nb x f16 ]  pad to 16
 //
-// Bytes inside a plane keep their GGUF order. No scale is widened or folded, so
+// Bytes inside a plane keep their GGUF order; Q8_0 codes are stored as q + 128 (the byte with
+// its top bit flipped). No scale is widened or folded, so
 // a resident row is the GGUF row's size rounded up to 16 (Q4_0: exact when nb is
 // a multiple of 8), and dequantisation reproduces the reference bit for bit.
 #pragma once

@@ -30,6 +30,9 @@ __global__ void repack_q4q8_kernel(const uint8_t *__restrict__ raw, uint8_t *__r
     for (uint32_t i = 0; i < QB / 4; i++) {
         const uint8_t *p = src + 2 + 4 * i;
         w[i] = (uint32_t)p[0] | ((uint32_t)p[1] << 8) | ((uint32_t)p[2] << 16) | ((uint32_t)p[3] << 24);
+        // Q8_0 codes are kept as q + 128 (unsigned bytes): the GEMV turns a byte into a float by
+        // dropping it into a mantissa, which wants an unsigned value
+        if (FMT == FMT_Q8_0) w[i] ^= 0x80808080u;
     }
     uint4 *dst = reinterpret_cast<uint4 *>(rowp + (uint64_t)b * QB);
 #pragma unroll
@@ -108,8 +111,8 @@ __global__ void dequant_kernel(const uint8_t *__restrict__ res, float *__restric
     if (L.fmt == FMT_Q8_0) {
         uint32_t b = u >> 1;
         float d = f16_bits_to_f32(*reinterpret_cast<const uint16_t *>(rowp + L.off_d + 2 * b));
-        const int8_t *q = reinterpret_cast<const int8_t *>(rowp + (uint64_t)u * 16);
-        for (int i = 0; i < 16; i++) o[i] = __fmul_rn(d, (float)q[i]);
+        const uint8_t *q = rowp + (uint64_t)u * 16;  // resident codes are q + 128
+        for (int i = 0; i < 16; i++) o[i] = __fmul_rn(d, (float)((int)q[i] - 128));
     } else if (L.fmt == FMT_Q4_0) {
         // elements 16u .. 16u+15 of block b: low nibbles (u even) or high nibbles (u odd) of bytes 0..15
         uint32_t b = u >> 1, hi = u & 1;
