@@ -123,6 +123,18 @@ STRIX_API int strix_cuda_gemv_batch(strix_cuda *h, size_t n, const char *const *
 STRIX_API int strix_cuda_gemv_dev(strix_cuda *h, int nmat, const char *const *keys, const float *d_a,
                         const float *d_b, float eps, int pre, int act, float *const *d_ys, void *stream);
 
+/* WeightAccel::prefill_q8_gemm (accel.rs:213; decode.rs:3257-3297): y[m][rows] = W8A8 GEMM of m
+ * token rows xs[m][in_dim] with a resident Q8_0 weight: per-32 int8 activations (xquant8_rows,
+ * kernels.rs:1000-1013), int32 block sums on tcgen05, f32 combine with both block scales
+ * (q8w_gemm32, kernels.rs:1373-1443); split-K over long in_dim (the reference's q4_gemm_w_sk,
+ * kernels.rs:539-601, with a fixed-order reduction instead of atomics). 0 when `key` is not a
+ * resident Q8_0 weight. Unlike the reference (m <= 256, out_dim <= 8192) any m is accepted. */
+STRIX_API int strix_cuda_prefill_q8_gemm(strix_cuda *h, const char *key, const float *xs, size_t m, float *y,
+                               size_t y_cap);
+/* The same on device pointers: d_y[m][rows] from d_xs[m][in_dim] on `stream`; no copy, no sync. */
+STRIX_API int strix_cuda_prefill_q8_gemm_dev(strix_cuda *h, const char *key, const float *d_xs, size_t m, float *d_y,
+                                   void *stream);
+
 /* Device status word written by kernels whose bounded waits ran out
  * (0 = clean). Synchronises `stream`. */
 STRIX_API int strix_cuda_device_status(strix_cuda *h, void *stream, uint32_t *status);
@@ -135,6 +147,11 @@ STRIX_API int strix_cuda_dequant_to_f32(strix_cuda *h, const char *key, float *o
 /* The activation quantiser alone (xquant8_rows, kernels.rs:1000-1013):
  * q[n] int8 and d[n/32] f32 from x[n], n a multiple of 32. */
 STRIX_API int strix_cuda_xquant8(strix_cuda *h, const float *x, size_t n, int8_t *q, float *d);
+
+/* int32 block sums isum[m][rows][in_dim/32] of a resident Q8_0 weight with the int8 codes of
+ * xs[m][in_dim] (the bit-exact tier of the GEMM; computed without tensor cores). */
+STRIX_API int strix_cuda_debug_block_isums(strix_cuda *h, const char *key, const float *xs, size_t m, int32_t *out,
+                                 size_t out_cap);
 
 #ifdef __cplusplus
 }

@@ -65,6 +65,9 @@ def load_library():
         C.c_int, C.POINTER(C.c_int))
     sig("strix_cuda_gemv_dev", C.c_int, H, C.c_int, C.POINTER(C.c_char_p), C.c_void_p, C.c_void_p, C.c_float,
         C.c_int, C.c_int, C.POINTER(C.c_void_p), C.c_void_p)
+    sig("strix_cuda_prefill_q8_gemm", C.c_int, H, C.c_char_p, f32p, sz, f32p, sz)
+    sig("strix_cuda_prefill_q8_gemm_dev", C.c_int, H, C.c_char_p, C.c_void_p, sz, C.c_void_p, C.c_void_p)
+    sig("strix_cuda_debug_block_isums", C.c_int, H, C.c_char_p, f32p, sz, C.POINTER(C.c_int32), sz)
     sig("strix_cuda_device_status", C.c_int, H, C.c_void_p, C.POINTER(C.c_uint32))
     sig("strix_cuda_dequant_to_f32", C.c_int, H, C.c_char_p, f32p, sz)
     sig("strix_cuda_xquant8", C.c_int, H, f32p, sz, C.POINTER(C.c_int8), f32p)
@@ -192,6 +195,33 @@ class CudaWeightAccel:
         st = (C.c_int * n)()
         self._check(self._L.strix_cuda_gemv_batch(self._h, n, keys, xp, ks, yp, yc, act, st))
         return [ys[i] if (infos[i] is not None and st[i] == 1) else None for i in range(n)]
+
+    def prefill_q8_gemm(self, key, xs, m):
+        """y[m][out] = W8A8 GEMM on a resident Q8_0 weight, or None (unknown key / not Q8_0 / bad length)."""
+        info = self.weight_info(key)
+        xa = _f32(xs)
+        if info is None or xa.size != m * info["in_dim"]:
+            return None
+        y = np.empty((m, info["rows"]), dtype=np.float32)
+        rc = self._check(self._L.strix_cuda_prefill_q8_gemm(self._h, key.encode(), _fp(xa), m, _fp(y), y.size))
+        return y if rc == 1 else None
+
+    def prefill_q8_gemm_dev(self, key, d_xs, m, d_y, stream=0):
+        rc = self._check(self._L.strix_cuda_prefill_q8_gemm_dev(self._h, key.encode(), C.c_void_p(int(d_xs)), m,
+                                                               C.c_void_p(int(d_y)),
+                                                               C.c_void_p(int(stream)) if stream else None))
+        return rc == 1
+
+    def debug_block_isums(self, key, xs, m):
+        """int32 [m][rows][in_dim/32] block sums of the GEMM (bit-exact tier)."""
+        info = self.weight_info(key)
+        xa = _f32(xs)
+        if info is None or xa.size != m * info["in_dim"]:
+            return None
+        out = np.empty((m, info["rows"], info["in_dim"] // 32), dtype=np.int32)
+        rc = self._check(self._L.strix_cuda_debug_block_isums(self._h, key.encode(), _fp(xa), m,
+                                                             out.ctypes.data_as(C.POINTER(C.c_int32)), out.size))
+        return out if rc == 1 else None
 
     # -- device-resident form (pointers are ints: torch ``tensor.data_ptr()``) ----
     def gemv_dev(self, keys, d_a, d_ys, d_b=0, eps=0.0, pre=PRE_NONE, act=ACT_F32, stream=0):

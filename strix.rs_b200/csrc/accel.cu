@@ -63,6 +63,10 @@ const Resident *find_weight(strix_cuda *h, const char *key) {
     auto it = h->weights.find(key);
     return it == h->weights.end() ? nullptr : &it->second;
 }
+Resident *find_weight_mut(strix_cuda *h, const char *key) {
+    auto it = h->weights.find(key);
+    return it == h->weights.end() ? nullptr : &it->second;
+}
 
 }  // namespace strix
 
@@ -121,6 +125,7 @@ static int upload_quant(strix_cuda *h, int fmt, const char *key, const uint8_t *
     auto it = h->weights.find(key);
     if (it != h->weights.end()) {
         cudaFree(it->second.dev);
+        if (it->second.scalesT) cudaFree(it->second.scalesT);
         it->second = r;
     } else {
         h->weights.emplace(key, r);
@@ -205,6 +210,7 @@ int strix_cuda_create(int device, const strix_cuda_opts *opts, strix_cuda **out)
     if (e == cudaSuccess) e = cudaMalloc(&h->d_status, sizeof(uint32_t));
     if (e == cudaSuccess) e = cudaMemset(h->d_status, 0, sizeof(uint32_t));
     if (e == cudaSuccess) e = gemv_prepare_device(h->smem_optin);
+    if (e == cudaSuccess) e = gemm_prepare_device();
     if (e != cudaSuccess) {
         g_create_error = std::string("create: ") + cudaGetErrorString(e);
         if (h->d_status) cudaFree(h->d_status);
@@ -220,7 +226,14 @@ void strix_cuda_destroy(strix_cuda *h) {
     if (!h) return;
     cudaSetDevice(h->device);
     cudaStreamSynchronize(h->stream);
-    for (auto &kv : h->weights) cudaFree(kv.second.dev);
+    for (auto &kv : h->weights) {
+        cudaFree(kv.second.dev);
+        if (kv.second.scalesT) cudaFree(kv.second.scalesT);
+    }
+    for (float *p : {h->gm_x.p, h->gm_y.p, h->gm_part.p, h->gm_xd.p})
+        if (p) cudaFree(p);
+    if (h->gm_xq) cudaFree(h->gm_xq);
+    if (h->gm_xs) cudaFree(h->gm_xs);
     for (auto &kv : h->f32s) cudaFree(kv.second.p);
     if (h->x.p) cudaFree(h->x.p);
     if (h->y.p) cudaFree(h->y.p);

@@ -20,6 +20,7 @@ struct Resident {
     size_t rows;       // rows held here
     uint8_t *dev;
     size_t bytes;
+    float *scalesT;  // Q8_0 only, built on the first GEMM: f32 scales transposed to [nb][ld] (see gemm_w8a8.cu)
 };
 
 struct DevBuf {
@@ -48,6 +49,13 @@ struct strix_cuda {
     // reference's persistent gemv_x / gemv_y, decode.rs:3827-3832)
     strix::DevBuf x, y;
     strix::PinBuf pin_in, pin_out;
+    // scratch of the prefill GEMM (grown on demand): f32 activations, their int8 codes, block scales,
+    // block code sums, f32 output, split-K partials
+    strix::DevBuf gm_x, gm_y, gm_part, gm_xd;
+    int8_t *gm_xq = nullptr;
+    size_t gm_xq_cap = 0;
+    int32_t *gm_xs = nullptr;
+    size_t gm_xs_cap = 0;
 };
 
 namespace strix {
@@ -55,4 +63,5 @@ size_t shard_begin(size_t rows, int world, int r);
 int ensure_f32(strix_cuda *h, DevBuf &b, size_t n);
 int ensure_pinned(strix_cuda *h, PinBuf &b, size_t bytes);
 const Resident *find_weight(strix_cuda *h, const char *key);
+Resident *find_weight_mut(strix_cuda *h, const char *key);
 }  // namespace strix

@@ -1,0 +1,466 @@
+// W8A8 prefill GEMM for sm_100a: Q8_0 weights x per-32 int8 activations on tcgen05
+// int8 MMA with TMEM accumulators fed by TMA.
+//
+//   Y[m][n] = sum_kb  d_w[n,kb] * d_x[m,kb] * (float) isum[m,n,kb],
+//   isum[m,n,kb] = sum_{i<32} W[n,kb,i] * X[m,kb,i]          (int32, exact)
+//
+// Replaces the reference's xquant8_rows + q8w_gemm32 / q8w_gemm
+// (crates/strix-backend-rocm/src/kernels.rs:1000-1013, 1308-1443; dispatch
+// decode.rs:1742-1766, entry decode.rs:3257-3297) and the split-K form of its
+// prefill GEMM (kernels.rs:539-601).
+//
+// Both operands carry a scale per 32 elements of K, so the int32 sum of one
+// K-block cannot be carried into the next: every tcgen05.mma (K = 32 for int8)
+// writes a FRESH accumulator, and CUDA cores fold it into f32 with the two
+// scales. The kernel is organised around that drain:
+//   * CTA tile 128 tokens x 128 weight rows; warp 0 issues TMA loads (activations
+//     and weights as 128-byte-swizzled K-major tiles, the K-block's weight scales
+//     as an f32 row), warp 1 issues one MMA per K-block into one of four
+//     128-column TMEM buffers and commits it to an mbarrier;
+//   * eight epilogue warps (TMEM lane group = warp % 4, column half = warp / 4)
+//     read a finished buffer with tcgen05.ld, hand it back, and run
+//     acc[n] += d_w[n] * (d_x[m] * isum) as packed f32x2 FMAs, 64 columns per thread;
+//   * weight codes are resident as q + 128 (unsigned bytes): the MMA runs
+//     u8 x s8 and the epilogue removes 128 * sum(x codes) per (token, K-block);
+//   * split-K (grid.z) writes f32 partials that a second kernel adds in a fixed
+//     order: reproducible, unlike the reference's atomicAdd;
+//   * every wait is bounded; after a timeout nothing waits again, the status word
+//     is raised, and the CTA still frees its TMEM before it returns.
+#include <cuda.h>
+
+#include "common.cuh"
+#include "kernels.h"
+
+namespace strix {
+
+constexpr uint32_t GM_BM = 128, GM_BN = 128;      // CTA tile: tokens x weight rows
+constexpr uint32_t GM_KB_STAGE = 4;               // K-blocks (of 32) per shared-memory stage = one 128-byte atom
+constexpr uint32_t GM_STAGES = 5;
+constexpr uint32_t GM_TBUF = 4;                   // TMEM accumulator buffers of GM_BN columns
+constexpr uint32_t GM_A_BYTES = GM_BM * 128, GM_B_BYTES = GM_BN * 128, GM_S_BYTES = GM_KB_STAGE * GM_BN * 4;
+constexpr uint32_t GM_STAGE_BYTES = GM_A_BYTES + GM_B_BYTES + GM_S_BYTES;  // 34816
+constexpr uint32_t GM_EPI_WARPS = 8, GM_THREADS = (4 + GM_EPI_WARPS) * 32;
+constexpr uint32_t GM_SMEM = 1024 /* barriers */ + GM_STAGES * GM_STAGE_BYTES + 1024 /* alignment slack */;
+
+__device__ __forceinline__ void tma_load_2d(void *dst, const CUtensorMap *map, int x, int y, uint64_t *bar) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];" ::"r"(
+            smem_u32(dst)),
+        "l"(map), "r"(x), "r"(y), "r"(smem_u32(bar))
+        : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_commit(uint64_t *bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar))
+                 : "memory");
+}
+// D[tmem] = A[smem desc] * B[smem desc], int8 inputs, int32 result, no accumulation into D.
+__device__ __forceinline__ void tc_mma_i8(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::i8 [%0], %1, %2, %3, {%5, %5, %5, %5}, p;\n\t}"
+        ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(0u), "r"(0u)
+        : "memory");
+}
+__device__ __forceinline__ void tc_ld32(uint32_t taddr, uint32_t (&r)[32]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+        "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+          "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
+          "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
+          "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+        : "r"(taddr)
+        : "memory");
+}
+__device__ __forceinline__ void tc_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+
+// Shared-memory matrix descriptor of a K-major tile stored as rows of 128 bytes with the
+// 128-byte swizzle (what TMA writes with CU_TENSOR_MAP_SWIZZLE_128B): start address >> 4,
+// leading byte offset 1 (ignored for swizzled K-major), stride byte offset = 8 rows x 128 B = 1024
+// (>> 4 = 64), descriptor version 1 (Blackwell), layout type 2 (SWIZZLE_128B). The tile base must
+// be 1024-byte aligned. Stepping 32 bytes along K inside the atom adds 2 to the start field.
+__device__ __forceinline__ uint64_t smem_desc_sw128(uint32_t saddr) {
+    uint64_t d = 0;
+    d |= (uint64_t)((saddr >> 4) & 0x3FFFu);
+    d |= (uint64_t)1u << 16;
+    d |= (uint64_t)64u << 32;
+    d |= (uint64_t)1u << 46;
+    d |= (uint64_t)2u << 61;
+    return d;
+}
+// Instruction descriptor (kind::i8): D = s32 (bits 4-5 = 2), A = signed int8 (bits 7-9 = 1),
+// B = unsigned int8 (bits 10-12 = 0), both K-major (bits 15, 16 = 0), N >> 3 in bits 17-22,
+// M >> 4 in bits 24-28.
+constexpr uint32_t GM_IDESC = (2u << 4) | (1u << 7) | (0u << 10) | ((GM_BN >> 3) << 17) | ((GM_BM >> 4) << 24);
+
+struct GemmArgs {
+    const float *xd;    // [M][nb] activation scales
+    const int32_t *xs;  // [M][nb] sum of the activation codes per block
+    float *y;           // [splits][M][ldy] (splits > 1: partials) or [M][ldy]
+    uint32_t M, N, nb, ldy;
+    uint32_t kb_per_split;  // K-blocks per grid.z slice, a multiple of GM_KB_STAGE
+    uint32_t *status;
+};
+
+__global__ void __launch_bounds__(GM_THREADS, 1)
+gemm_w8a8_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_w,
+                 const __grid_constant__ CUtensorMap map_s, const __grid_constant__ GemmArgs A) {
+    extern __shared__ uint8_t smem_raw[];
+    // barriers in the first KB, stages from the next 1024-byte boundary (the swizzle atom wants it)
+    const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+    uint8_t *smem = smem_raw + (base - smem_u32(smem_raw));
+    uint64_t *full = reinterpret_cast<uint64_t *>(smem);             // [GM_STAGES] TMA landed
+    uint64_t *empty = full + GM_STAGES;                              // [GM_STAGES] MMA + epilogue done with the stage
+    uint64_t *tfull = empty + GM_STAGES;                             // [GM_TBUF] MMA result ready in TMEM
+    uint64_t *tempty = tfull + GM_TBUF;                              // [GM_TBUF] epilogue has read the buffer
+    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(tempty + GM_TBUF);
+    volatile uint32_t *ctl = tmem_slot + 1;
+    uint8_t *stages = smem + 1024;
+
+    const uint32_t tid = threadIdx.x, warp = tid >> 5, lane = tid & 31u;
+    const uint32_t n0 = blockIdx.x * GM_BN, m0 = blockIdx.y * GM_BM;
+    const uint32_t kb0 = blockIdx.z * A.kb_per_split;
+    const uint32_t kb1 = min(A.nb, kb0 + A.kb_per_split);
+    const uint32_t n_stage_iters = (kb1 - kb0 + GM_KB_STAGE - 1) / GM_KB_STAGE;
+
+    if (tid == 0) {
+        for (uint32_t s = 0; s < GM_STAGES; s++) {
+            mbar_init(&full[s], 1);
+            mbar_init(&empty[s], 1 + GM_EPI_WARPS);
+        }
+        for (uint32_t b = 0; b < GM_TBUF; b++) {
+            mbar_init(&tfull[b], 1);
+            mbar_init(&tempty[b], GM_EPI_WARPS);
+        }
+        *ctl = 0;
+        mbar_fence_init();
+    }
+    if (warp == 1) {
+        // 512 columns = four accumulator buffers; this CTA is alone on its SM
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)),
+                     "r"(GM_TBUF * GM_BN)
+                     : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+
+    if (warp == 0) {
+        // ---------------- TMA producer ----------------
+        if (lane == 0) {
+            for (uint32_t it = 0; it < n_stage_iters; it++) {
+                const uint32_t s = it % GM_STAGES;
+                if (it >= GM_STAGES && !*ctl && !mbar_wait_bounded(&empty[s], ((it / GM_STAGES) - 1u) & 1u, A.status))
+                    *ctl = 1;
+                uint8_t *st = stages + s * GM_STAGE_BYTES;
+                const uint32_t kb = kb0 + it * GM_KB_STAGE;
+                mbar_arrive_expect_tx(&full[s], GM_STAGE_BYTES);
+                tma_load_2d(st, &map_x, (int)(kb * 32u), (int)m0, &full[s]);
+                tma_load_2d(st + GM_A_BYTES, &map_w, (int)(kb * 32u), (int)n0, &full[s]);
+                tma_load_2d(st + GM_A_BYTES + GM_B_BYTES, &map_s, (int)n0, (int)kb, &full[s]);
+            }
+        }
+    } else if (warp == 1) {
+        // ---------------- MMA issuer ----------------
+        if (lane == 0) {
+            uint32_t g = 0;  // K-block counter of this CTA
+            for (uint32_t it = 0; it < n_stage_iters; it++) {
+                const uint32_t s = it % GM_STAGES;
+                if (!*ctl && !mbar_wait_bounded(&full[s], (it / GM_STAGES) & 1u, A.status)) *ctl = 1;
+                tc_fence_after();
+                const uint32_t sa = smem_u32(stages + s * GM_STAGE_BYTES);
+                const uint64_t adesc = smem_desc_sw128(sa), bdesc = smem_desc_sw128(sa + GM_A_BYTES);
+                const uint32_t nkb = min(GM_KB_STAGE, kb1 - (kb0 + it * GM_KB_STAGE));
+                for (uint32_t j = 0; j < nkb; j++, g++) {
+                    const uint32_t buf = g % GM_TBUF, use = g / GM_TBUF;
+                    if (use > 0 && !*ctl && !mbar_wait_bounded(&tempty[buf], (use - 1u) & 1u, A.status)) *ctl = 1;
+                    tc_fence_after();
+                    tc_mma_i8(tmem_base + buf * GM_BN, adesc + 2u * j, bdesc + 2u * j, GM_IDESC);
+                    tc_commit(&tfull[buf]);  // arrives when this MMA (and all before it) has completed
+                }
+                tc_commit(&empty[s]);  // the stage's operand tiles are no longer being read
+            }
+        }
+    } else if (warp >= 4) {
+        // ---------------- epilogue: drain TMEM, apply the block scales ----------------
+        const uint32_t lg = warp & 3u, ch = (warp - 4u) >> 2;  // TMEM lane group, column half
+        const uint32_t m = m0 + lg * 32u + lane;               // this thread's token
+        const bool m_ok = m < A.M;
+        const uint32_t taddr0 = tmem_base + ((lg * 32u) << 16) + ch * 64u;
+        float2 acc[32];
+#pragma unroll
+        for (int i = 0; i < 32; i++) acc[i] = make_float2(0.f, 0.f);
+        uint32_t g = 0;
+        for (uint32_t it = 0; it < n_stage_iters; it++) {
+            const uint32_t s = it % GM_STAGES;
+            const uint32_t kb = kb0 + it * GM_KB_STAGE;
+            const uint32_t nkb = min(GM_KB_STAGE, kb1 - kb);
+            // this token's scales and code sums for the stage's K-blocks
+            float dx[GM_KB_STAGE];
+            int xs[GM_KB_STAGE];
+#pragma unroll
+            for (uint32_t j = 0; j < GM_KB_STAGE; j++) {
+                const bool ok = m_ok && j < nkb;
+                dx[j] = ok ? __ldg(A.xd + (uint64_t)m * A.nb + kb + j) : 0.f;
+                xs[j] = ok ? __ldg(A.xs + (uint64_t)m * A.nb + kb + j) : 0;
+            }
+            if (!*ctl && !mbar_wait_bounded(&full[s], (it / GM_STAGES) & 1u, A.status)) *ctl = 1;
+            const float *sw = reinterpret_cast<const float *>(stages + s * GM_STAGE_BYTES + GM_A_BYTES + GM_B_BYTES) +
+                              ch * 64u;
+#pragma unroll 1
+            for (uint32_t j = 0; j < nkb; j++, g++) {
+                const uint32_t buf = g % GM_TBUF, use = g / GM_TBUF;
+                if (!*ctl && !mbar_wait_bounded(&tfull[buf], use & 1u, A.status)) *ctl = 1;
+                tc_fence_after();
+                uint32_t r0[32], r1[32];
+                tc_ld32(taddr0 + buf * GM_BN, r0);
+                tc_ld32(taddr0 + buf * GM_BN + 32u, r1);
+                tc_wait_ld();
+                tc_fence_before();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(&tempty[buf]);  // the MMA warp may overwrite the buffer
+                // u = d_x * (isum' - 128 * xs) = d_x * isum' + c1;   acc[n] += d_w[n] * u
+                const float c0 = dx[j], c1 = -c0 * (128.0f * (float)xs[j]);
+                const float2 c0v = make_float2(c0, c0), c1v = make_float2(c1, c1);
+                const float4 *swj = reinterpret_cast<const float4 *>(sw + j * GM_BN);
+#pragma unroll
+                for (int q = 0; q < 8; q++) {
+                    const float4 w4 = swj[q];
+                    float2 u0 = __ffma2_rn(c0v, make_float2((float)(int)r0[4 * q], (float)(int)r0[4 * q + 1]), c1v);
+                    float2 u1 = __ffma2_rn(c0v, make_float2((float)(int)r0[4 * q + 2], (float)(int)r0[4 * q + 3]), c1v);
+                    acc[2 * q] = __ffma2_rn(make_float2(w4.x, w4.y), u0, acc[2 * q]);
+                    acc[2 * q + 1] = __ffma2_rn(make_float2(w4.z, w4.w), u1, acc[2 * q + 1]);
+                }
+#pragma unroll
+                for (int q = 0; q < 8; q++) {
+                    const float4 w4 = swj[8 + q];
+                    float2 u0 = __ffma2_rn(c0v, make_float2((float)(int)r1[4 * q], (float)(int)r1[4 * q + 1]), c1v);
+                    float2 u1 = __ffma2_rn(c0v, make_float2((float)(int)r1[4 * q + 2], (float)(int)r1[4 * q + 3]), c1v);
+                    acc[16 + 2 * q] = __ffma2_rn(make_float2(w4.x, w4.y), u0, acc[16 + 2 * q]);
+                    acc[16 + 2 * q + 1] = __ffma2_rn(make_float2(w4.z, w4.w), u1, acc[16 + 2 * q + 1]);
+                }
+            }
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&empty[s]);  // done with the stage's scale rows
+        }
+        // write this thread's 64 outputs (one token, 64 consecutive weight rows)
+        if (m_ok) {
+            float *yrow = A.y + ((uint64_t)blockIdx.z * A.M + m) * A.ldy + n0 + ch * 64u;
+            const uint32_t nleft = (A.N > n0 + ch * 64u) ? A.N - (n0 + ch * 64u) : 0u;
+            if (nleft >= 64u && (A.ldy & 3u) == 0u) {
+#pragma unroll
+                for (int i = 0; i < 16; i++)
+                    reinterpret_cast<float4 *>(yrow)[i] = make_float4(acc[2 * i].x, acc[2 * i].y, acc[2 * i + 1].x, acc[2 * i + 1].y);
+            } else {
+#pragma unroll
+                for (int i = 0; i < 32; i++) {
+                    if (2u * i < nleft) yrow[2 * i] = acc[i].x;
+                    if (2u * i + 1u < nleft) yrow[2 * i + 1] = acc[i].y;
+                }
+            }
+        }
+    }
+    // ---------------- teardown: every warp arrives; TMEM goes back before the CTA ends ----------------
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        tc_fence_after();
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(GM_TBUF * GM_BN)
+                     : "memory");
+    }
+}
+
+// y[m][n] = sum over splits of part[z][m][n], in z order.
+__global__ void splitk_reduce_kernel(const float *__restrict__ part, float *__restrict__ y, uint32_t M, uint32_t N,
+                                     uint32_t ldp, uint32_t splits) {
+    const uint64_t i = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= (uint64_t)M * N) return;
+    const uint32_t m = (uint32_t)(i / N), n = (uint32_t)(i % N);
+    float s = 0.f;
+    for (uint32_t z = 0; z < splits; z++) s += part[((uint64_t)z * M + m) * ldp + n];
+    y[(uint64_t)m * N + n] = s;
+}
+
+// Activation quantiser for the GEMM (xquant8_rows, kernels.rs:1000-1013) that also emits the
+// per-block sum of the codes. One warp per 32-element block.
+__global__ void xquant8_sum_kernel(const float *__restrict__ x, int8_t *__restrict__ q, float *__restrict__ d,
+                                   int32_t *__restrict__ xs, uint32_t nblk) {
+    const uint32_t blk = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31u;
+    if (blk >= nblk) return;
+    const float v = x[(uint64_t)blk * 32u + lane];
+    float amax = fabsf(v);
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
+    const float sc = amax / 127.0f;
+    const float inv = sc > 0.f ? 1.0f / sc : 0.f;
+    int qi = (int)rintf(v * inv);
+    qi = max(-127, min(127, qi));
+    q[(uint64_t)blk * 32u + lane] = (int8_t)qi;
+    int sum = qi;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
+    if (lane == 0) {
+        d[blk] = sc;
+        xs[blk] = sum;
+    }
+}
+
+// f32 copy of a Q8_0 weight's scales, transposed to [nb][lds] so that one K-block's scales for
+// 128 consecutive rows are one contiguous run (what the GEMM's TMA box fetches).
+__global__ void scales_transpose_kernel(const uint8_t *__restrict__ res, float *__restrict__ out, RowLayout L,
+                                        uint32_t rows, uint32_t lds) {
+    const uint64_t i = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= (uint64_t)L.nb * lds) return;
+    const uint32_t kb = (uint32_t)(i / lds), n = (uint32_t)(i % lds);
+    float v = 0.f;
+    if (n < rows) v = f16_bits_to_f32(*reinterpret_cast<const uint16_t *>(res + (uint64_t)n * L.row_stride + L.off_d + 2u * kb));
+    out[i] = v;
+}
+
+// int32 block sums isum[m][n][kb] of a Q8_0 weight with int8 activations, one thread each:
+// the bit-exact tier of the GEMM contract, computed the plain way (no tensor cores).
+__global__ void block_isums_kernel(const uint8_t *__restrict__ res, const int8_t *__restrict__ xq, int32_t *__restrict__ out,
+                                   RowLayout L, uint32_t M, uint32_t rows) {
+    const uint64_t i = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= (uint64_t)M * rows * L.nb) return;
+    const uint32_t kb = (uint32_t)(i % L.nb);
+    const uint32_t n = (uint32_t)((i / L.nb) % rows), m = (uint32_t)(i / ((uint64_t)L.nb * rows));
+    const uint8_t *w = res + (uint64_t)n * L.row_stride + (uint64_t)kb * 32u;
+    const int8_t *x = xq + (uint64_t)m * L.in_dim + (uint64_t)kb * 32u;
+    int s = 0;
+    for (int k = 0; k < 32; k++) s += ((int)w[k] - 128) * (int)x[k];
+    out[i] = s;
+}
+
+// ------------------------------------------------------------------ host side
+typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *,
+                                  const cuuint64_t *, const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn encode_fn() {
+    static EncodeTiledFn fn = nullptr;
+    if (!fn) {
+        void *p = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+            q == cudaDriverEntryPointSuccess)
+            fn = reinterpret_cast<EncodeTiledFn>(p);
+    }
+    return fn;
+}
+
+static bool make_map_2d(CUtensorMap *map, CUtensorMapDataType dt, void *base, uint64_t dim0, uint64_t dim1,
+                        uint64_t stride1_bytes, uint32_t box0, uint32_t box1, CUtensorMapSwizzle sw) {
+    EncodeTiledFn fn = encode_fn();
+    if (!fn) return false;
+    cuuint64_t dims[2] = {dim0, dim1};
+    cuuint64_t strides[1] = {stride1_bytes};
+    cuuint32_t box[2] = {box0, box1};
+    cuuint32_t estr[2] = {1, 1};
+    return fn(map, dt, 2, base, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, sw,
+              CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+uint32_t gemm_scales_ld(uint32_t rows) { return (rows + 3u) & ~3u; }
+
+cudaError_t launch_scales_transpose(const uint8_t *d_res, float *d_out, const RowLayout &L, uint32_t rows,
+                                    cudaStream_t stream) {
+    const uint32_t lds = gemm_scales_ld(rows);
+    const uint64_t total = (uint64_t)L.nb * lds;
+    if (total == 0) return cudaSuccess;
+    scales_transpose_kernel<<<(unsigned)((total + 255) / 256), 256, 0, stream>>>(d_res, d_out, L, rows, lds);
+    return cudaGetLastError();
+}
+
+cudaError_t launch_xquant8_sum(const float *d_x, int8_t *d_q, float *d_d, int32_t *d_xs, uint64_t n, cudaStream_t stream) {
+    const uint64_t nblk = n / 32;
+    if (nblk == 0) return cudaSuccess;
+    const uint32_t T = 256, per = T / 32;
+    xquant8_sum_kernel<<<(unsigned)((nblk + per - 1) / per), T, 0, stream>>>(d_x, d_q, d_d, d_xs, (uint32_t)nblk);
+    return cudaGetLastError();
+}
+
+cudaError_t launch_block_isums(const uint8_t *d_res, const int8_t *d_xq, int32_t *d_out, const RowLayout &L, uint32_t M,
+                               uint32_t rows, cudaStream_t stream) {
+    const uint64_t total = (uint64_t)M * rows * L.nb;
+    if (total == 0) return cudaSuccess;
+    block_isums_kernel<<<(unsigned)((total + 255) / 256), 256, 0, stream>>>(d_res, d_xq, d_out, L, M, rows);
+    return cudaGetLastError();
+}
+
+cudaError_t gemm_prepare_device() {
+    return cudaFuncSetAttribute(gemm_w8a8_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)GM_SMEM);
+}
+
+uint32_t gemm_pick_splits(uint32_t M, uint32_t rows, uint32_t nb, int num_sms) {
+    // Split K when the output tiles alone leave most SMs idle (ffn_down: few rows, long K).
+    const uint32_t tiles = ((M + GM_BM - 1) / GM_BM) * ((rows + GM_BN - 1) / GM_BN);
+    const uint32_t stages = (nb + GM_KB_STAGE - 1) / GM_KB_STAGE;
+    uint32_t splits = 1;
+    while (tiles * splits * 2 <= (uint32_t)num_sms && splits * 2 <= stages && splits < 8) splits *= 2;
+    // one more slice if that fills a wave better
+    if (tiles * splits < (uint32_t)num_sms && tiles * (splits + 1) <= (uint32_t)num_sms && splits + 1 <= stages) {
+        const uint32_t s1 = (uint32_t)num_sms / tiles;
+        if (s1 > splits && s1 <= 8 && s1 <= stages) splits = s1;
+    }
+    return splits;
+}
+
+size_t gemm_workspace_floats(uint32_t M, uint32_t rows, uint32_t splits) {
+    return splits > 1 ? (size_t)splits * M * gemm_scales_ld(rows) : 0;
+}
+
+// d_y[M][rows] = W8A8 GEMM. d_part: workspace of gemm_workspace_floats() floats when splits > 1.
+cudaError_t launch_gemm_w8a8(const uint8_t *d_res, const RowLayout &L, uint32_t rows, const float *d_scalesT,
+                             const int8_t *d_xq, const float *d_xd, const int32_t *d_xs, uint32_t M, float *d_y,
+                             float *d_part, uint32_t splits, uint32_t *d_status, cudaStream_t stream) {
+    if (M == 0 || rows == 0) return cudaSuccess;
+    CUtensorMap mx, mw, ms;
+    const uint32_t lds = gemm_scales_ld(rows);
+    // activations: [M][K] int8, K innermost; weights: [rows][row_stride] bytes, first K bytes of a row
+    // are its codes; scales: [nb][lds] f32. Coordinates past a dimension read as zero.
+    if (!make_map_2d(&mx, CU_TENSOR_MAP_DATA_TYPE_UINT8, const_cast<int8_t *>(d_xq), L.in_dim, M, L.in_dim, 128, GM_BM,
+                     CU_TENSOR_MAP_SWIZZLE_128B) ||
+        !make_map_2d(&mw, CU_TENSOR_MAP_DATA_TYPE_UINT8, const_cast<uint8_t *>(d_res), L.in_dim, rows, L.row_stride, 128,
+                     GM_BN, CU_TENSOR_MAP_SWIZZLE_128B) ||
+        !make_map_2d(&ms, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, const_cast<float *>(d_scalesT), lds, L.nb, (uint64_t)lds * 4,
+                     GM_BN, GM_KB_STAGE, CU_TENSOR_MAP_SWIZZLE_NONE))
+        return cudaErrorInvalidValue;
+    GemmArgs a{};
+    a.xd = d_xd;
+    a.xs = d_xs;
+    a.M = M;
+    a.N = rows;
+    a.nb = L.nb;
+    a.status = d_status;
+    const uint32_t stages = (L.nb + GM_KB_STAGE - 1) / GM_KB_STAGE;
+    if (splits < 1) splits = 1;
+    if (splits > stages) splits = stages;
+    a.kb_per_split = ((stages + splits - 1) / splits) * GM_KB_STAGE;
+    splits = (L.nb + a.kb_per_split - 1) / a.kb_per_split;
+    if (splits > 1) {
+        a.y = d_part;
+        a.ldy = lds;
+    } else {
+        a.y = d_y;
+        a.ldy = rows;
+    }
+    dim3 grid((rows + GM_BN - 1) / GM_BN, (M + GM_BM - 1) / GM_BM, splits);
+    gemm_w8a8_kernel<<<grid, GM_THREADS, GM_SMEM, stream>>>(mx, mw, ms, a);
+    cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess) return e;
+    if (splits > 1) {
+        const uint64_t total = (uint64_t)M * rows;
+        splitk_reduce_kernel<<<(unsigned)((total + 255) / 256), 256, 0, stream>>>(d_part, d_y, M, rows, lds, splits);
+        e = cudaGetLastError();
+    }
+    return e;
+}
+
+}  // namespace strix

@@ -57,6 +57,20 @@ bool gemv_plan(GemvArgs &a, int num_sms, size_t smem_optin);
 cudaError_t gemv_prepare_device(size_t smem_optin);  // opt in to large dynamic shared memory, once per device
 cudaError_t launch_gemv(const GemvArgs &a, cudaStream_t stream);
 
+// ---- W8A8 prefill GEMM (tcgen05 int8 MMA) ----------------------------------
+cudaError_t gemm_prepare_device();
+uint32_t gemm_scales_ld(uint32_t rows);  // leading dimension (floats) of the transposed f32 scale plane
+cudaError_t launch_scales_transpose(const uint8_t *d_res, float *d_out, const RowLayout &L, uint32_t rows,
+                                    cudaStream_t stream);
+cudaError_t launch_xquant8_sum(const float *d_x, int8_t *d_q, float *d_d, int32_t *d_xs, uint64_t n, cudaStream_t stream);
+cudaError_t launch_block_isums(const uint8_t *d_res, const int8_t *d_xq, int32_t *d_out, const RowLayout &L, uint32_t M,
+                               uint32_t rows, cudaStream_t stream);
+uint32_t gemm_pick_splits(uint32_t M, uint32_t rows, uint32_t nb, int num_sms);
+size_t gemm_workspace_floats(uint32_t M, uint32_t rows, uint32_t splits);
+cudaError_t launch_gemm_w8a8(const uint8_t *d_res, const RowLayout &L, uint32_t rows, const float *d_scalesT,
+                             const int8_t *d_xq, const float *d_xd, const int32_t *d_xs, uint32_t M, float *d_y,
+                             float *d_part, uint32_t splits, uint32_t *d_status, cudaStream_t stream);
+
 // The activation quantiser on its own: q[n] int8, d[n/32] f32 from x[n].
 cudaError_t launch_xquant8(const float *d_x, int8_t *d_q, float *d_d, uint32_t n, cudaStream_t stream);
 
