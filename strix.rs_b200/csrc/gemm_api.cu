@@ -48,12 +48,13 @@ static int gemm_device(strix_cuda *h, Resident *r, const float *d_xs, size_t m, 
     const size_t K = r->L.in_dim, nb = r->L.nb;
     if (ensure_scales(h, r, stream) < 0) return -1;
     if (ensure_raw(h, h->gm_xq, h->gm_xq_cap, m * K) < 0) return -1;
-    if (ensure_raw(h, h->gm_xs, h->gm_xs_cap, m * nb) < 0) return -1;
-    if (ensure_f32(h, h->gm_xd, m * nb) < 0) return -1;
+    const size_t ldx = gemm_x_ld((uint32_t)nb);
+    if (ensure_raw(h, h->gm_xs, h->gm_xs_cap, m * ldx) < 0) return -1;
+    if (ensure_f32(h, h->gm_xd, m * ldx) < 0) return -1;
     const uint32_t splits = gemm_pick_splits((uint32_t)m, (uint32_t)r->rows, (uint32_t)nb, h->num_sms);
     const size_t wsf = gemm_workspace_floats((uint32_t)m, (uint32_t)r->rows, splits);
     if (wsf && ensure_f32(h, h->gm_part, wsf) < 0) return -1;
-    CU_TRY(h, launch_xquant8_sum(d_xs, h->gm_xq, h->gm_xd.p, h->gm_xs, (uint64_t)m * K, stream));
+    CU_TRY(h, launch_xquant8_sum(d_xs, h->gm_xq, h->gm_xd.p, h->gm_xs, (uint32_t)m, (uint32_t)nb, stream));
     CU_TRY(h, launch_gemm_w8a8(r->dev, r->L, (uint32_t)r->rows, r->scalesT, h->gm_xq, h->gm_xd.p, h->gm_xs, (uint32_t)m,
                               d_y, h->gm_part.p, splits, h->d_status, stream));
     return 1;
@@ -112,12 +113,13 @@ int strix_cuda_debug_block_isums(strix_cuda *h, const char *key, const float *xs
     if (total == 0) return 1;
     CU_TRY(h, cudaSetDevice(h->device));
     if (ensure_f32(h, h->gm_x, m * K) < 0 || ensure_raw(h, h->gm_xq, h->gm_xq_cap, m * K) < 0 ||
-        ensure_raw(h, h->gm_xs, h->gm_xs_cap, m * nb) < 0 || ensure_f32(h, h->gm_xd, m * nb) < 0)
+        ensure_raw(h, h->gm_xs, h->gm_xs_cap, m * gemm_x_ld((uint32_t)nb)) < 0 ||
+        ensure_f32(h, h->gm_xd, m * gemm_x_ld((uint32_t)nb)) < 0)
         return -1;
     int32_t *d_out = nullptr;
     CU_TRY(h, cudaMalloc(&d_out, total * sizeof(int32_t)));
     cudaError_t e = cudaMemcpyAsync(h->gm_x.p, xs, m * K * sizeof(float), cudaMemcpyHostToDevice, h->stream);
-    if (e == cudaSuccess) e = launch_xquant8_sum(h->gm_x.p, h->gm_xq, h->gm_xd.p, h->gm_xs, (uint64_t)m * K, h->stream);
+    if (e == cudaSuccess) e = launch_xquant8_sum(h->gm_x.p, h->gm_xq, h->gm_xd.p, h->gm_xs, (uint32_t)m, (uint32_t)nb, h->stream);
     if (e == cudaSuccess) e = launch_block_isums(r->dev, h->gm_xq, d_out, r->L, (uint32_t)m, (uint32_t)r->rows, h->stream);
     if (e == cudaSuccess) e = cudaMemcpyAsync(out, d_out, total * sizeof(int32_t), cudaMemcpyDeviceToHost, h->stream);
     if (e == cudaSuccess) e = cudaStreamSynchronize(h->stream);

@@ -17,11 +17,15 @@
 //     and weights as 128-byte-swizzled K-major tiles, the K-block's weight scales
 //     as an f32 row), warp 1 issues one MMA per K-block into one of four
 //     128-column TMEM buffers and commits it to an mbarrier;
-//   * eight epilogue warps (TMEM lane group = warp % 4, column half = warp / 4)
-//     read a finished buffer with tcgen05.ld, hand it back, and run
-//     acc[n] += d_w[n] * (d_x[m] * isum) as packed f32x2 FMAs, 64 columns per thread;
-//   * weight codes are resident as q + 128 (unsigned bytes): the MMA runs
-//     u8 x s8 and the epilogue removes 128 * sum(x codes) per (token, K-block);
+//   * sixteen epilogue warps (TMEM lane group = warp % 4, column quarter = index / 4)
+//     read a finished buffer with tcgen05.ld, re-arm it, hand it back, and run
+//     acc[n] += d_w[n] * (d_x[m] * isum) as packed f32x2 ops, 32 columns per thread;
+//   * int32 -> f32 costs no conversion instruction: a buffer is pre-loaded (tcgen05.st) with
+//     the bit pattern of 1.5 * 2^23 and the MMA ACCUMULATES into it, so what comes back is
+//     the float 12582912 + isum; one packed subtract recovers isum exactly;
+//   * weight codes are resident as q + 128 (unsigned bytes): the MMA runs u8 x s8, and the
+//     128 * sum(x codes) that this adds per (token, K-block) rides on the same subtract
+//     (12582912 + 128 * sum is an exact f32);
 //   * split-K (grid.z) writes f32 partials that a second kernel adds in a fixed
 //     order: reproducible, unlike the reference's atomicAdd;
 //   * every wait is bounded; after a timeout nothing waits again, the status word
@@ -38,8 +42,12 @@ constexpr uint32_t GM_KB_STAGE = 4;               // K-blocks (of 32) per shared
 constexpr uint32_t GM_STAGES = 5;
 constexpr uint32_t GM_TBUF = 4;                   // TMEM accumulator buffers of GM_BN columns
 constexpr uint32_t GM_A_BYTES = GM_BM * 128, GM_B_BYTES = GM_BN * 128, GM_S_BYTES = GM_KB_STAGE * GM_BN * 4;
-constexpr uint32_t GM_STAGE_BYTES = GM_A_BYTES + GM_B_BYTES + GM_S_BYTES;  // 34816
-constexpr uint32_t GM_EPI_WARPS = 8, GM_THREADS = (4 + GM_EPI_WARPS) * 32;
+constexpr uint32_t GM_XD_BYTES = GM_BM * GM_KB_STAGE * 4;  // per token: 4 activation scales / 4 code sums
+constexpr uint32_t GM_OFF_S = GM_A_BYTES + GM_B_BYTES, GM_OFF_XD = GM_OFF_S + GM_S_BYTES, GM_OFF_XS = GM_OFF_XD + GM_XD_BYTES;
+constexpr uint32_t GM_STAGE_BYTES = GM_OFF_XS + GM_XD_BYTES;  // 38912 = 38 KB
+constexpr uint32_t GM_EPI_WARPS = 16, GM_EPI_WARP0 = 2, GM_THREADS = (GM_EPI_WARP0 + GM_EPI_WARPS) * 32;
+constexpr uint32_t GM_MAGIC = 0x4B400000u;  // bits of 12582912.0f = 1.5 * 2^23: ulp 1, room for |isum| < 2^22
+static_assert(GM_KB_STAGE == GM_TBUF, "a TMEM buffer is reused by the same K-block slot of the next stage");
 constexpr uint32_t GM_SMEM = 1024 /* barriers */ + GM_STAGES * GM_STAGE_BYTES + 1024 /* alignment slack */;
 
 __device__ __forceinline__ void tma_load_2d(void *dst, const CUtensorMap *map, int x, int y, uint64_t *bar) {
@@ -55,13 +63,13 @@ __device__ __forceinline__ void tc_commit(uint64_t *bar) {
     asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar))
                  : "memory");
 }
-// D[tmem] = A[smem desc] * B[smem desc], int8 inputs, int32 result, no accumulation into D.
+// D[tmem] += A[smem desc] * B[smem desc], int8 inputs, int32 accumulation.
 __device__ __forceinline__ void tc_mma_i8(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc) {
     asm volatile(
         "{\n\t.reg .pred p;\n\t"
         "setp.ne.b32 p, %4, 0;\n\t"
         "tcgen05.mma.cta_group::1.kind::i8 [%0], %1, %2, %3, {%5, %5, %5, %5}, p;\n\t}"
-        ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(0u), "r"(0u)
+        ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(1u), "r"(0u)
         : "memory");
 }
 __device__ __forceinline__ void tc_ld32(uint32_t taddr, uint32_t (&r)[32]) {
@@ -77,6 +85,20 @@ __device__ __forceinline__ void tc_ld32(uint32_t taddr, uint32_t (&r)[32]) {
         : "memory");
 }
 __device__ __forceinline__ void tc_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+// 8 columns of this thread's TMEM lane <- c[0..7] (kept in registers for the whole kernel)
+__device__ __forceinline__ void tc_st8(uint32_t taddr, const uint32_t (&c)[8]) {
+    asm volatile("tcgen05.st.sync.aligned.32x32b.x8.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};" ::"r"(taddr),
+                 "r"(c[0]), "r"(c[1]), "r"(c[2]), "r"(c[3]), "r"(c[4]), "r"(c[5]), "r"(c[6]), "r"(c[7])
+                 : "memory");
+}
+// 32 columns of this thread's TMEM lane <- the magic constant
+__device__ __forceinline__ void tc_rearm32(uint32_t taddr, const uint32_t (&c)[8]) {
+    tc_st8(taddr, c);
+    tc_st8(taddr + 8u, c);
+    tc_st8(taddr + 16u, c);
+    tc_st8(taddr + 24u, c);
+}
+__device__ __forceinline__ void tc_wait_st() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
 
 // Shared-memory matrix descriptor of a K-major tile stored as rows of 128 bytes with the
 // 128-byte swizzle (what TMA writes with CU_TENSOR_MAP_SWIZZLE_128B): start address >> 4,
@@ -98,17 +120,16 @@ __device__ __forceinline__ uint64_t smem_desc_sw128(uint32_t saddr) {
 constexpr uint32_t GM_IDESC = (2u << 4) | (1u << 7) | (0u << 10) | ((GM_BN >> 3) << 17) | ((GM_BM >> 4) << 24);
 
 struct GemmArgs {
-    const float *xd;    // [M][nb] activation scales
-    const int32_t *xs;  // [M][nb] sum of the activation codes per block
     float *y;           // [splits][M][ldy] (splits > 1: partials) or [M][ldy]
-    uint32_t M, N, nb, ldy;
+    uint32_t M, N, nb, ldy, ldx;  // ldx: leading dimension of xs / xd (nb rounded up to 4: TMA strides are multiples of 16 B)
     uint32_t kb_per_split;  // K-blocks per grid.z slice, a multiple of GM_KB_STAGE
     uint32_t *status;
 };
 
 __global__ void __launch_bounds__(GM_THREADS, 1)
 gemm_w8a8_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_w,
-                 const __grid_constant__ CUtensorMap map_s, const __grid_constant__ GemmArgs A) {
+                 const __grid_constant__ CUtensorMap map_s, const __grid_constant__ CUtensorMap map_xd,
+                 const __grid_constant__ CUtensorMap map_xs, const __grid_constant__ GemmArgs A) {
     extern __shared__ uint8_t smem_raw[];
     // barriers in the first KB, stages from the next 1024-byte boundary (the swizzle atom wants it)
     const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
@@ -163,7 +184,9 @@ gemm_w8a8_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
                 mbar_arrive_expect_tx(&full[s], GM_STAGE_BYTES);
                 tma_load_2d(st, &map_x, (int)(kb * 32u), (int)m0, &full[s]);
                 tma_load_2d(st + GM_A_BYTES, &map_w, (int)(kb * 32u), (int)n0, &full[s]);
-                tma_load_2d(st + GM_A_BYTES + GM_B_BYTES, &map_s, (int)n0, (int)kb, &full[s]);
+                tma_load_2d(st + GM_OFF_S, &map_s, (int)n0, (int)kb, &full[s]);
+                tma_load_2d(st + GM_OFF_XD, &map_xd, (int)kb, (int)m0, &full[s]);
+                tma_load_2d(st + GM_OFF_XS, &map_xs, (int)kb, (int)m0, &full[s]);
             }
         }
     } else if (warp == 1) {
@@ -179,7 +202,8 @@ gemm_w8a8_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
                 const uint32_t nkb = min(GM_KB_STAGE, kb1 - (kb0 + it * GM_KB_STAGE));
                 for (uint32_t j = 0; j < nkb; j++, g++) {
                     const uint32_t buf = g % GM_TBUF, use = g / GM_TBUF;
-                    if (use > 0 && !*ctl && !mbar_wait_bounded(&tempty[buf], (use - 1u) & 1u, A.status)) *ctl = 1;
+                    // the epilogue warps pre-load every buffer (first use included) before it may be accumulated into
+                    if (!*ctl && !mbar_wait_bounded(&tempty[buf], use & 1u, A.status)) *ctl = 1;
                     tc_fence_after();
                     tc_mma_i8(tmem_base + buf * GM_BN, adesc + 2u * j, bdesc + 2u * j, GM_IDESC);
                     tc_commit(&tfull[buf]);  // arrives when this MMA (and all before it) has completed
@@ -187,79 +211,81 @@ gemm_w8a8_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
                 tc_commit(&empty[s]);  // the stage's operand tiles are no longer being read
             }
         }
-    } else if (warp >= 4) {
+    } else {
         // ---------------- epilogue: drain TMEM, apply the block scales ----------------
-        const uint32_t lg = warp & 3u, ch = (warp - 4u) >> 2;  // TMEM lane group, column half
-        const uint32_t m = m0 + lg * 32u + lane;               // this thread's token
+        const uint32_t lg = warp & 3u, cq = (warp - GM_EPI_WARP0) >> 2;  // TMEM lane group (fixed by warp % 4), column quarter
+        const uint32_t m = m0 + lg * 32u + lane;                         // this thread's token
         const bool m_ok = m < A.M;
-        const uint32_t taddr0 = tmem_base + ((lg * 32u) << 16) + ch * 64u;
-        float2 acc[32];
+        const uint32_t taddr0 = tmem_base + ((lg * 32u) << 16) + cq * 32u;
+        const uint32_t trow = lg * 32u + lane;  // this thread's row in the tile
+        uint32_t magic[8];
 #pragma unroll
-        for (int i = 0; i < 32; i++) acc[i] = make_float2(0.f, 0.f);
-        uint32_t g = 0;
+        for (int i = 0; i < 8; i++) magic[i] = GM_MAGIC;
+        // arm the four buffers
+#pragma unroll
+        for (uint32_t j = 0; j < GM_TBUF; j++) tc_rearm32(taddr0 + j * GM_BN, magic);
+        tc_wait_st();
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0)
+            for (uint32_t j = 0; j < GM_TBUF; j++) mbar_arrive(&tempty[j]);
+        float2 acc[16];
+#pragma unroll
+        for (int i = 0; i < 16; i++) acc[i] = make_float2(0.f, 0.f);
         for (uint32_t it = 0; it < n_stage_iters; it++) {
             const uint32_t s = it % GM_STAGES;
             const uint32_t kb = kb0 + it * GM_KB_STAGE;
-            const uint32_t nkb = min(GM_KB_STAGE, kb1 - kb);
-            // this token's scales and code sums for the stage's K-blocks
-            float dx[GM_KB_STAGE];
-            int xs[GM_KB_STAGE];
-#pragma unroll
-            for (uint32_t j = 0; j < GM_KB_STAGE; j++) {
-                const bool ok = m_ok && j < nkb;
-                dx[j] = ok ? __ldg(A.xd + (uint64_t)m * A.nb + kb + j) : 0.f;
-                xs[j] = ok ? __ldg(A.xs + (uint64_t)m * A.nb + kb + j) : 0;
-            }
             if (!*ctl && !mbar_wait_bounded(&full[s], (it / GM_STAGES) & 1u, A.status)) *ctl = 1;
-            const float *sw = reinterpret_cast<const float *>(stages + s * GM_STAGE_BYTES + GM_A_BYTES + GM_B_BYTES) +
-                              ch * 64u;
+            const uint8_t *stg = stages + s * GM_STAGE_BYTES;
+            const float *sw = reinterpret_cast<const float *>(stg + GM_OFF_S) + cq * 32u;
+            const float *sxd = reinterpret_cast<const float *>(stg + GM_OFF_XD) + trow * GM_KB_STAGE;
+            const int32_t *sxs = reinterpret_cast<const int32_t *>(stg + GM_OFF_XS) + trow * GM_KB_STAGE;
 #pragma unroll 1
-            for (uint32_t j = 0; j < nkb; j++, g++) {
-                const uint32_t buf = g % GM_TBUF, use = g / GM_TBUF;
-                if (!*ctl && !mbar_wait_bounded(&tfull[buf], use & 1u, A.status)) *ctl = 1;
-                tc_fence_after();
-                uint32_t r0[32], r1[32];
-                tc_ld32(taddr0 + buf * GM_BN, r0);
-                tc_ld32(taddr0 + buf * GM_BN + 32u, r1);
-                tc_wait_ld();
-                tc_fence_before();
-                __syncwarp();
-                if (lane == 0) mbar_arrive(&tempty[buf]);  // the MMA warp may overwrite the buffer
-                // u = d_x * (isum' - 128 * xs) = d_x * isum' + c1;   acc[n] += d_w[n] * u
-                const float c0 = dx[j], c1 = -c0 * (128.0f * (float)xs[j]);
-                const float2 c0v = make_float2(c0, c0), c1v = make_float2(c1, c1);
-                const float4 *swj = reinterpret_cast<const float4 *>(sw + j * GM_BN);
+            for (uint32_t j = 0; j < GM_KB_STAGE; j++) {
+                if (kb + j < kb1) {  // uniform across the CTA
+                    // this token's scale and code sum for the K-block (rows past M were zero-filled by TMA)
+                    const float dxj = sxd[j];
+                    const float unm = -(12582912.0f + 128.0f * (float)sxs[j]);  // exact: an integer below 2^24
+                    if (!*ctl && !mbar_wait_bounded(&tfull[j], it & 1u, A.status)) *ctl = 1;
+                    tc_fence_after();
+                    uint32_t r[32];
+                    tc_ld32(taddr0 + j * GM_BN, r);
+                    tc_wait_ld();
+                    tc_rearm32(taddr0 + j * GM_BN, magic);  // completes while the arithmetic below runs
+                    const float2 unmagic = make_float2(unm, unm);
+                    // r holds the floats 12582912 + isum + 128 * xs;  acc[n] += d_w[n] * (d_x * isum)
+                    const float2 c0v = make_float2(dxj, dxj);
+                    const float4 *swj = reinterpret_cast<const float4 *>(sw + j * GM_BN);
 #pragma unroll
-                for (int q = 0; q < 8; q++) {
-                    const float4 w4 = swj[q];
-                    float2 u0 = __ffma2_rn(c0v, make_float2((float)(int)r0[4 * q], (float)(int)r0[4 * q + 1]), c1v);
-                    float2 u1 = __ffma2_rn(c0v, make_float2((float)(int)r0[4 * q + 2], (float)(int)r0[4 * q + 3]), c1v);
-                    acc[2 * q] = __ffma2_rn(make_float2(w4.x, w4.y), u0, acc[2 * q]);
-                    acc[2 * q + 1] = __ffma2_rn(make_float2(w4.z, w4.w), u1, acc[2 * q + 1]);
-                }
-#pragma unroll
-                for (int q = 0; q < 8; q++) {
-                    const float4 w4 = swj[8 + q];
-                    float2 u0 = __ffma2_rn(c0v, make_float2((float)(int)r1[4 * q], (float)(int)r1[4 * q + 1]), c1v);
-                    float2 u1 = __ffma2_rn(c0v, make_float2((float)(int)r1[4 * q + 2], (float)(int)r1[4 * q + 3]), c1v);
-                    acc[16 + 2 * q] = __ffma2_rn(make_float2(w4.x, w4.y), u0, acc[16 + 2 * q]);
-                    acc[16 + 2 * q + 1] = __ffma2_rn(make_float2(w4.z, w4.w), u1, acc[16 + 2 * q + 1]);
+                    for (int q = 0; q < 8; q++) {
+                        const float4 w4 = swj[q];
+                        float2 g0 = __fadd2_rn(make_float2(__uint_as_float(r[4 * q]), __uint_as_float(r[4 * q + 1])), unmagic);
+                        float2 g1 = __fadd2_rn(make_float2(__uint_as_float(r[4 * q + 2]), __uint_as_float(r[4 * q + 3])), unmagic);
+                        g0 = __fmul2_rn(c0v, g0);
+                        g1 = __fmul2_rn(c0v, g1);
+                        acc[2 * q] = __ffma2_rn(make_float2(w4.x, w4.y), g0, acc[2 * q]);
+                        acc[2 * q + 1] = __ffma2_rn(make_float2(w4.z, w4.w), g1, acc[2 * q + 1]);
+                    }
+                    tc_wait_st();
+                    tc_fence_before();
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(&tempty[j]);  // the MMA warp may accumulate into the buffer again
                 }
             }
             __syncwarp();
             if (lane == 0) mbar_arrive(&empty[s]);  // done with the stage's scale rows
         }
-        // write this thread's 64 outputs (one token, 64 consecutive weight rows)
+        // write this thread's 32 outputs (one token, 32 consecutive weight rows)
         if (m_ok) {
-            float *yrow = A.y + ((uint64_t)blockIdx.z * A.M + m) * A.ldy + n0 + ch * 64u;
-            const uint32_t nleft = (A.N > n0 + ch * 64u) ? A.N - (n0 + ch * 64u) : 0u;
-            if (nleft >= 64u && (A.ldy & 3u) == 0u) {
+            float *yrow = A.y + ((uint64_t)blockIdx.z * A.M + m) * A.ldy + n0 + cq * 32u;
+            const uint32_t nleft = (A.N > n0 + cq * 32u) ? A.N - (n0 + cq * 32u) : 0u;
+            if (nleft >= 32u && (A.ldy & 3u) == 0u) {
 #pragma unroll
-                for (int i = 0; i < 16; i++)
+                for (int i = 0; i < 8; i++)
                     reinterpret_cast<float4 *>(yrow)[i] = make_float4(acc[2 * i].x, acc[2 * i].y, acc[2 * i + 1].x, acc[2 * i + 1].y);
             } else {
 #pragma unroll
-                for (int i = 0; i < 32; i++) {
+                for (int i = 0; i < 16; i++) {
                     if (2u * i < nleft) yrow[2 * i] = acc[i].x;
                     if (2u * i + 1u < nleft) yrow[2 * i + 1] = acc[i].y;
                 }
@@ -290,9 +316,10 @@ __global__ void splitk_reduce_kernel(const float *__restrict__ part, float *__re
 // Activation quantiser for the GEMM (xquant8_rows, kernels.rs:1000-1013) that also emits the
 // per-block sum of the codes. One warp per 32-element block.
 __global__ void xquant8_sum_kernel(const float *__restrict__ x, int8_t *__restrict__ q, float *__restrict__ d,
-                                   int32_t *__restrict__ xs, uint32_t nblk) {
+                                   int32_t *__restrict__ xs, uint32_t nblk, uint32_t nb, uint32_t ldx) {
     const uint32_t blk = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31u;
     if (blk >= nblk) return;
+    const uint32_t o = (blk / nb) * ldx + blk % nb;  // [row][ldx] with ldx >= nb
     const float v = x[(uint64_t)blk * 32u + lane];
     float amax = fabsf(v);
 #pragma unroll
@@ -306,8 +333,8 @@ __global__ void xquant8_sum_kernel(const float *__restrict__ x, int8_t *__restri
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
     if (lane == 0) {
-        d[blk] = sc;
-        xs[blk] = sum;
+        d[o] = sc;
+        xs[o] = sum;
     }
 }
 
@@ -378,11 +405,16 @@ cudaError_t launch_scales_transpose(const uint8_t *d_res, float *d_out, const Ro
     return cudaGetLastError();
 }
 
-cudaError_t launch_xquant8_sum(const float *d_x, int8_t *d_q, float *d_d, int32_t *d_xs, uint64_t n, cudaStream_t stream) {
-    const uint64_t nblk = n / 32;
+uint32_t gemm_x_ld(uint32_t nb) { return (nb + 3u) & ~3u; }
+
+// x[m][nb*32] -> q[m][nb*32] int8, d[m][ldx] f32, xs[m][ldx] int32 with ldx = gemm_x_ld(nb)
+cudaError_t launch_xquant8_sum(const float *d_x, int8_t *d_q, float *d_d, int32_t *d_xs, uint32_t m, uint32_t nb,
+                               cudaStream_t stream) {
+    const uint64_t nblk = (uint64_t)m * nb;
     if (nblk == 0) return cudaSuccess;
     const uint32_t T = 256, per = T / 32;
-    xquant8_sum_kernel<<<(unsigned)((nblk + per - 1) / per), T, 0, stream>>>(d_x, d_q, d_d, d_xs, (uint32_t)nblk);
+    xquant8_sum_kernel<<<(unsigned)((nblk + per - 1) / per), T, 0, stream>>>(d_x, d_q, d_d, d_xs, (uint32_t)nblk, nb,
+                                                                               gemm_x_ld(nb));
     return cudaGetLastError();
 }
 
@@ -421,8 +453,8 @@ cudaError_t launch_gemm_w8a8(const uint8_t *d_res, const RowLayout &L, uint32_t 
                              const int8_t *d_xq, const float *d_xd, const int32_t *d_xs, uint32_t M, float *d_y,
                              float *d_part, uint32_t splits, uint32_t *d_status, cudaStream_t stream) {
     if (M == 0 || rows == 0) return cudaSuccess;
-    CUtensorMap mx, mw, ms;
-    const uint32_t lds = gemm_scales_ld(rows);
+    CUtensorMap mx, mw, ms, mxd, mxs;
+    const uint32_t lds = gemm_scales_ld(rows), ldx = gemm_x_ld(L.nb);
     // activations: [M][K] int8, K innermost; weights: [rows][row_stride] bytes, first K bytes of a row
     // are its codes; scales: [nb][lds] f32. Coordinates past a dimension read as zero.
     if (!make_map_2d(&mx, CU_TENSOR_MAP_DATA_TYPE_UINT8, const_cast<int8_t *>(d_xq), L.in_dim, M, L.in_dim, 128, GM_BM,
@@ -430,14 +462,17 @@ cudaError_t launch_gemm_w8a8(const uint8_t *d_res, const RowLayout &L, uint32_t 
         !make_map_2d(&mw, CU_TENSOR_MAP_DATA_TYPE_UINT8, const_cast<uint8_t *>(d_res), L.in_dim, rows, L.row_stride, 128,
                      GM_BN, CU_TENSOR_MAP_SWIZZLE_128B) ||
         !make_map_2d(&ms, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, const_cast<float *>(d_scalesT), lds, L.nb, (uint64_t)lds * 4,
-                     GM_BN, GM_KB_STAGE, CU_TENSOR_MAP_SWIZZLE_NONE))
+                     GM_BN, GM_KB_STAGE, CU_TENSOR_MAP_SWIZZLE_NONE) ||
+        !make_map_2d(&mxd, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, const_cast<float *>(d_xd), L.nb, M, (uint64_t)ldx * 4,
+                     GM_KB_STAGE, GM_BM, CU_TENSOR_MAP_SWIZZLE_NONE) ||
+        !make_map_2d(&mxs, CU_TENSOR_MAP_DATA_TYPE_INT32, const_cast<int32_t *>(d_xs), L.nb, M, (uint64_t)ldx * 4,
+                     GM_KB_STAGE, GM_BM, CU_TENSOR_MAP_SWIZZLE_NONE))
         return cudaErrorInvalidValue;
     GemmArgs a{};
-    a.xd = d_xd;
-    a.xs = d_xs;
     a.M = M;
     a.N = rows;
     a.nb = L.nb;
+    a.ldx = ldx;
     a.status = d_status;
     const uint32_t stages = (L.nb + GM_KB_STAGE - 1) / GM_KB_STAGE;
     if (splits < 1) splits = 1;
@@ -452,7 +487,7 @@ cudaError_t launch_gemm_w8a8(const uint8_t *d_res, const RowLayout &L, uint32_t 
         a.ldy = rows;
     }
     dim3 grid((rows + GM_BN - 1) / GM_BN, (M + GM_BM - 1) / GM_BM, splits);
-    gemm_w8a8_kernel<<<grid, GM_THREADS, GM_SMEM, stream>>>(mx, mw, ms, a);
+    gemm_w8a8_kernel<<<grid, GM_THREADS, GM_SMEM, stream>>>(mx, mw, ms, mxd, mxs, a);
     cudaError_t e = cudaGetLastError();
     if (e != cudaSuccess) return e;
     if (splits > 1) {

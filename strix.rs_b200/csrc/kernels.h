@@ -62,7 +62,9 @@ cudaError_t gemm_prepare_device();
 uint32_t gemm_scales_ld(uint32_t rows);  // leading dimension (floats) of the transposed f32 scale plane
 cudaError_t launch_scales_transpose(const uint8_t *d_res, float *d_out, const RowLayout &L, uint32_t rows,
                                     cudaStream_t stream);
-cudaError_t launch_xquant8_sum(const float *d_x, int8_t *d_q, float *d_d, int32_t *d_xs, uint64_t n, cudaStream_t stream);
+uint32_t gemm_x_ld(uint32_t nb);  // leading dimension of the per-token scale / code-sum arrays
+cudaError_t launch_xquant8_sum(const float *d_x, int8_t *d_q, float *d_d, int32_t *d_xs, uint32_t m, uint32_t nb,
+                               cudaStream_t stream);
 cudaError_t launch_block_isums(const uint8_t *d_res, const int8_t *d_xq, int32_t *d_out, const RowLayout &L, uint32_t M,
                                uint32_t rows, cudaStream_t stream);
 uint32_t gemm_pick_splits(uint32_t M, uint32_t rows, uint32_t nb, int num_sms);
