@@ -135,6 +135,19 @@ STRIX_API int strix_cuda_prefill_q8_gemm(strix_cuda *h, const char *key, const f
 STRIX_API int strix_cuda_prefill_q8_gemm_dev(strix_cuda *h, const char *key, const float *d_xs, size_t m, float *d_y,
                                    void *stream);
 
+/* No counterpart in the reference. The W8A8 GEMM for callers that must not allocate device memory
+ * (a server whose arena owns the whole device; a latency-critical path that cannot risk the
+ * device-wide synchronisation of cudaMalloc/cudaFree): same kernels and result as
+ * strix_cuda_prefill_q8_gemm_dev, but ALL scratch comes from one fixed device array built into the
+ * library (strix_cuda_noalloc_scratch_bytes() = 32 MiB per GPU, held until process exit). Calls no
+ * cudaMalloc/cudaFree. A shape whose scratch exceeds the array returns <0 with the sizes in the
+ * error text. The first call on a device looks the array's address up: make it outside any stream
+ * capture. Every call shares the array (it keeps the last call's contents; nothing needs
+ * zeroing), so calls whose kernels overlap on the GPU race: serialise them. */
+STRIX_API int strix_cuda_prefill_q8_gemm_noalloc(strix_cuda *h, const char *key, const float *d_xs, size_t m,
+                                       float *d_y, void *stream);
+STRIX_API size_t strix_cuda_noalloc_scratch_bytes(void);
+
 /* Device status word written by kernels whose bounded waits ran out
  * (0 = clean). Synchronises `stream`. */
 STRIX_API int strix_cuda_device_status(strix_cuda *h, void *stream, uint32_t *status);

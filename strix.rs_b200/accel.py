@@ -67,6 +67,8 @@ def load_library():
         C.c_int, C.c_int, C.POINTER(C.c_void_p), C.c_void_p)
     sig("strix_cuda_prefill_q8_gemm", C.c_int, H, C.c_char_p, f32p, sz, f32p, sz)
     sig("strix_cuda_prefill_q8_gemm_dev", C.c_int, H, C.c_char_p, C.c_void_p, sz, C.c_void_p, C.c_void_p)
+    sig("strix_cuda_prefill_q8_gemm_noalloc", C.c_int, H, C.c_char_p, C.c_void_p, sz, C.c_void_p, C.c_void_p)
+    sig("strix_cuda_noalloc_scratch_bytes", sz)
     sig("strix_cuda_debug_block_isums", C.c_int, H, C.c_char_p, f32p, sz, C.POINTER(C.c_int32), sz)
     sig("strix_cuda_device_status", C.c_int, H, C.c_void_p, C.POINTER(C.c_uint32))
     sig("strix_cuda_dequant_to_f32", C.c_int, H, C.c_char_p, f32p, sz)
@@ -211,6 +213,17 @@ class CudaWeightAccel:
                                                                C.c_void_p(int(d_y)),
                                                                C.c_void_p(int(stream)) if stream else None))
         return rc == 1
+
+    def prefill_q8_gemm_noalloc(self, key, d_xs, m, d_y, stream=0):
+        """The GEMM with all scratch in the library's fixed device array: for callers that cannot
+        allocate device memory. Raises StrixCudaError when the shape needs more than the array holds."""
+        rc = self._check(self._L.strix_cuda_prefill_q8_gemm_noalloc(self._h, key.encode(), C.c_void_p(int(d_xs)), m,
+                                                                   C.c_void_p(int(d_y)),
+                                                                   C.c_void_p(int(stream)) if stream else None))
+        return rc == 1
+
+    def noalloc_scratch_bytes(self):
+        return int(self._L.strix_cuda_noalloc_scratch_bytes())
 
     def debug_block_isums(self, key, xs, m):
         """int32 [m][rows][in_dim/32] block sums of the GEMM (bit-exact tier)."""
