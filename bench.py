@@ -334,6 +334,55 @@ def main():
                 "kernel": "gemv_kernel<Q8_0,F32> on q8_0.2560.151936 (%s peak; traffic from ncu: see profiles/)" % peak_src,
                 "frac_of_8tbs": round(big["gbs"] / 8000.0, 4)}
 
+    # ---- extras on rank 0 at N=1: the integer-dot GEMV variant and the W8A8 GEMM (configs[2]) ----
+    extras = None
+    if rank == 0 and world == 1:
+        extras = {"q8dot_gemv": [], "w8a8_gemm": []}
+        with torch.cuda.stream(stream):
+            s = stream.cuda_stream
+            g = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g, stream=stream):
+                for it in items:
+                    acc.gemv_dev([it["key"]], it["x"].data_ptr(), [it["y"].data_ptr()], act=pkg.ACT_Q8DOT, stream=s)
+            for _ in range(3):
+                g.replay()
+            torch.cuda.synchronize()
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            reps = 10
+            a.record()
+            for _ in range(reps):
+                g.replay()
+            b.record()
+            torch.cuda.synchronize()
+            ms = a.elapsed_time(b) / reps
+            extras["q8dot_gemv"] = {"ms_per_step": round(ms, 5), "gbs": round(step_bytes / ms / 1e6, 1),
+                                    "note": "same six weights, activation quantised per 32 to int8 inside the kernel"}
+            for (k, n) in ((2560, 9728), (2560, 4096), (9728, 2560)):
+                key = "gemm.%d.%d" % (k, n)
+                assert acc.upload_q8_0(key, make_weight(synth, Q8_0, k, n, 2, key), k, n)
+                for m in (512, 2048):
+                    xg = torch.randn(m, k, device=dev)
+                    yg = torch.empty(m, n, device=dev)
+                    for _ in range(2):
+                        acc.prefill_q8_gemm_dev(key, xg.data_ptr(), m, yg.data_ptr(), stream=s)
+                    torch.cuda.synchronize()
+                    gg = torch.cuda.CUDAGraph()
+                    with torch.cuda.graph(gg, stream=stream):
+                        for _ in range(10):
+                            acc.prefill_q8_gemm_dev(key, xg.data_ptr(), m, yg.data_ptr(), stream=s)
+                    gg.replay()
+                    torch.cuda.synchronize()
+                    a.record()
+                    gg.replay()
+                    b.record()
+                    torch.cuda.synchronize()
+                    us = a.elapsed_time(b) * 1e3 / 10
+                    extras["w8a8_gemm"].append({"M": m, "K": k, "N": n, "us": round(us, 1),
+                                                "tops": round(2.0 * m * n * k / us / 1e6, 1)})
+                    del xg, yg
+        if acc.device_status() != 0:
+            raise SystemExit("device status word is non-zero after the extras")
+
     cpu = None
     if rank == 0 and world == 1 and not args.no_cpu_baseline:
         orc = entry.load_oracle()
@@ -350,7 +399,7 @@ def main():
                        "parallelism": "rows sharded over %d GPU(s)%s" % (world, ", NCCL all-gather per GEMV" if world > 1 else "")},
             "e2e": {"value": round(e2e_val, 2), "unit": "GB/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
             "gpu_launches": args.steps * len(items),
-            "clocks": clocks, "roofline": roof, "cpu_baseline": cpu, "per_weight": detail,
+            "clocks": clocks, "roofline": roof, "cpu_baseline": cpu, "per_weight": detail, "extras": extras,
             "frac_of_8tbs": round(value / 8000.0, 4),
         }
         print(json.dumps(out))
