@@ -148,6 +148,39 @@ STRIX_API int strix_cuda_prefill_q8_gemm_noalloc(strix_cuda *h, const char *key,
                                        float *d_y, void *stream);
 STRIX_API size_t strix_cuda_noalloc_scratch_bytes(void);
 
+/* Plain-data mirror of GpuLayerCfg / GpuDecodeConfig (crates/strix-core/src/accel.rs:19-72). */
+typedef struct strix_gpu_layer_cfg {
+    uint32_t head_dim, n_kv;
+    int k_eq_v;
+    float rope_theta;
+    int is_local;
+    float output_scale;
+    int no_rope, rope_norm;
+} strix_gpu_layer_cfg;
+typedef struct strix_gpu_decode_config {
+    uint32_t hidden, n_heads, ffn, vocab, n_layers;
+    float eps, final_softcap;
+    int attn_rsqrt, norm_v, qk_norm, post_norm, act_gelu, gpu_prefill;
+    uint32_t n_swa, max_seq;
+    const strix_gpu_layer_cfg *layers; /* n_layers entries; may be NULL (unused by the projection chain) */
+    /* Not in the reference struct: */
+    int attn_standin_q; /* must be 1: attention is outside this library's path; Wo is fed with q */
+    int act;            /* STRIX_ACT_F32 or STRIX_ACT_Q8DOT for every projection */
+} strix_gpu_decode_config;
+
+/* WeightAccel::configure_decode (accel.rs:417; decode.rs:4528-4622). Call after every weight
+ * (blk.N.attn_q/attn_k/attn_v/attn_output/ffn_gate/ffn_up/ffn_down.weight, output.weight or
+ * token_embd.weight) and norm (blk.N.attn_norm/ffn_norm.weight, output_norm.weight via upload_f32)
+ * is uploaded. 0 = declined (a weight missing, post-norm / softcap / real attention requested, or a
+ * sharded handle): the model keeps its per-weight gemv path. Any later upload drops the configuration. */
+STRIX_API int strix_cuda_configure_decode(strix_cuda *h, const strix_gpu_decode_config *cfg);
+/* WeightAccel::decode_step (accel.rs:433; decode.rs:5047-5531), projection chain only: logits[vocab]
+ * from the embedded hidden state hvec[hidden]; four GEMV launches per layer replayed from a CUDA
+ * graph. `pos` is accepted for signature parity (no KV cache on this path). 0 = not configured. */
+STRIX_API int strix_cuda_decode_step(strix_cuda *h, const float *hvec, size_t pos, float *logits, size_t logits_cap);
+/* The same chain on device pointers (d_h is updated in place), enqueued on `stream`; no copy, no sync. */
+STRIX_API int strix_cuda_decode_chain_dev(strix_cuda *h, float *d_h, float *d_logits, void *stream);
+
 /* Device status word written by kernels whose bounded waits ran out
  * (0 = clean). Synchronises `stream`. */
 STRIX_API int strix_cuda_device_status(strix_cuda *h, void *stream, uint32_t *status);

@@ -30,6 +30,19 @@ class _Opts(C.Structure):
     _fields_ = [("rank", C.c_int), ("world", C.c_int), ("profile", C.c_int), ("reserved", C.c_int * 5)]
 
 
+class _LayerCfg(C.Structure):
+    _fields_ = [("head_dim", C.c_uint32), ("n_kv", C.c_uint32), ("k_eq_v", C.c_int), ("rope_theta", C.c_float),
+                ("is_local", C.c_int), ("output_scale", C.c_float), ("no_rope", C.c_int), ("rope_norm", C.c_int)]
+
+
+class _DecodeCfg(C.Structure):
+    _fields_ = [("hidden", C.c_uint32), ("n_heads", C.c_uint32), ("ffn", C.c_uint32), ("vocab", C.c_uint32),
+                ("n_layers", C.c_uint32), ("eps", C.c_float), ("final_softcap", C.c_float), ("attn_rsqrt", C.c_int),
+                ("norm_v", C.c_int), ("qk_norm", C.c_int), ("post_norm", C.c_int), ("act_gelu", C.c_int),
+                ("gpu_prefill", C.c_int), ("n_swa", C.c_uint32), ("max_seq", C.c_uint32),
+                ("layers", C.POINTER(_LayerCfg)), ("attn_standin_q", C.c_int), ("act", C.c_int)]
+
+
 _lib = None
 
 
@@ -70,6 +83,9 @@ def load_library():
     sig("strix_cuda_prefill_q8_gemm_noalloc", C.c_int, H, C.c_char_p, C.c_void_p, sz, C.c_void_p, C.c_void_p)
     sig("strix_cuda_noalloc_scratch_bytes", sz)
     sig("strix_cuda_debug_block_isums", C.c_int, H, C.c_char_p, f32p, sz, C.POINTER(C.c_int32), sz)
+    sig("strix_cuda_configure_decode", C.c_int, H, C.POINTER(_DecodeCfg))
+    sig("strix_cuda_decode_step", C.c_int, H, f32p, sz, f32p, sz)
+    sig("strix_cuda_decode_chain_dev", C.c_int, H, C.c_void_p, C.c_void_p, C.c_void_p)
     sig("strix_cuda_device_status", C.c_int, H, C.c_void_p, C.POINTER(C.c_uint32))
     sig("strix_cuda_dequant_to_f32", C.c_int, H, C.c_char_p, f32p, sz)
     sig("strix_cuda_xquant8", C.c_int, H, f32p, sz, C.POINTER(C.c_int8), f32p)
@@ -235,6 +251,31 @@ class CudaWeightAccel:
         rc = self._check(self._L.strix_cuda_debug_block_isums(self._h, key.encode(), _fp(xa), m,
                                                              out.ctypes.data_as(C.POINTER(C.c_int32)), out.size))
         return out if rc == 1 else None
+
+    def configure_decode(self, hidden, n_heads, ffn, vocab, n_layers, eps=1e-6, act_gelu=False, act=ACT_Q8DOT,
+                         attn_standin_q=True, post_norm=False, final_softcap=0.0):
+        """GpuDecodeConfig -> bool (accel.rs:417). Only the projection chain is on this path:
+        attn_standin_q must stay True or the configuration is declined."""
+        c = _DecodeCfg(hidden=hidden, n_heads=n_heads, ffn=ffn, vocab=vocab, n_layers=n_layers, eps=eps,
+                       final_softcap=final_softcap, post_norm=int(post_norm), act_gelu=int(act_gelu),
+                       attn_standin_q=int(attn_standin_q), act=act)
+        rc = self._check(self._L.strix_cuda_configure_decode(self._h, C.byref(c)))
+        self._vocab = vocab if rc == 1 else None
+        return rc == 1
+
+    def decode_step(self, h, pos=0):
+        """logits[vocab] or None (accel.rs:433)."""
+        if not getattr(self, "_vocab", None):
+            return None
+        ha = _f32(h)
+        out = np.empty(self._vocab, dtype=np.float32)
+        rc = self._check(self._L.strix_cuda_decode_step(self._h, _fp(ha), pos, _fp(out), out.size))
+        return out if rc == 1 else None
+
+    def decode_chain_dev(self, d_h, d_logits, stream=0):
+        rc = self._check(self._L.strix_cuda_decode_chain_dev(self._h, C.c_void_p(int(d_h)), C.c_void_p(int(d_logits)),
+                                                            C.c_void_p(int(stream)) if stream else None))
+        return rc == 1
 
     # -- device-resident form (pointers are ints: torch ``tensor.data_ptr()``) ----
     def gemv_dev(self, keys, d_a, d_ys, d_b=0, eps=0.0, pre=PRE_NONE, act=ACT_F32, stream=0):

@@ -122,6 +122,7 @@ static int upload_quant(strix_cuda *h, int fmt, const char *key, const uint8_t *
         h->err = std::string("upload: ") + cudaGetErrorString(e);
         return -1;
     }
+    decode_release(h);  // a configured chain may hold the pointer this upload replaces
     auto it = h->weights.find(key);
     if (it != h->weights.end()) {
         cudaFree(it->second.dev);
@@ -134,8 +135,9 @@ static int upload_quant(strix_cuda *h, int fmt, const char *key, const uint8_t *
 }
 
 // One GEMV launch over up to 3 resident weights that share the activation.
-static int gemv_launch(strix_cuda *h, int nmat, const Resident *const *ws, const float *d_a, const float *d_b,
-                       float eps, int pre, int act, float *const *d_ys, cudaStream_t stream) {
+namespace strix {
+int gemv_launch(strix_cuda *h, int nmat, const Resident *const *ws, const float *d_a, const float *d_b, float eps,
+                int pre, int act, float *const *d_ys, const float *const *d_res, cudaStream_t stream) {
     if (nmat < 1 || nmat > GEMV_MAX_MATS) {
         h->err = "gemv: between 1 and 3 weights per launch";
         return -1;
@@ -154,6 +156,7 @@ static int gemv_launch(strix_cuda *h, int nmat, const Resident *const *ws, const
         }
         a.mat[m].w = ws[m]->dev;
         a.mat[m].y = d_ys[m];
+        a.mat[m].res = d_res ? d_res[m] : nullptr;
         a.mat[m].rows = (uint32_t)ws[m]->rows;
     }
     a.a = d_a;
@@ -169,6 +172,7 @@ static int gemv_launch(strix_cuda *h, int nmat, const Resident *const *ws, const
     CU_TRY(h, launch_gemv(a, stream));
     return 1;
 }
+}  // namespace strix
 
 extern "C" {
 
@@ -226,6 +230,7 @@ void strix_cuda_destroy(strix_cuda *h) {
     if (!h) return;
     cudaSetDevice(h->device);
     cudaStreamSynchronize(h->stream);
+    decode_release(h);
     for (auto &kv : h->weights) {
         cudaFree(kv.second.dev);
         if (kv.second.scalesT) cudaFree(kv.second.scalesT);
@@ -276,6 +281,7 @@ int strix_cuda_upload_f32(strix_cuda *h, const char *key, const float *data, siz
         h->err = std::string("upload_f32: ") + cudaGetErrorString(e);
         return -1;
     }
+    decode_release(h);
     auto it = h->f32s.find(key);
     if (it != h->f32s.end()) {
         cudaFree(it->second.p);
@@ -336,7 +342,7 @@ int strix_cuda_gemv_batch(strix_cuda *h, size_t n, const char *const *keys, cons
         if (!ws[i]) continue;
         const Resident *w1[1] = {ws[i]};
         float *y1[1] = {h->y.p + yoff[i]};
-        if (gemv_launch(h, 1, w1, h->x.p + xoff[i], nullptr, 0.f, STRIX_PRE_NONE, act, y1, h->stream) < 0) return -1;
+        if (gemv_launch(h, 1, w1, h->x.p + xoff[i], nullptr, 0.f, STRIX_PRE_NONE, act, y1, nullptr, h->stream) < 0) return -1;
     }
     if (ytot) CU_TRY(h, cudaMemcpyAsync(pout, h->y.p, ytot * 4, cudaMemcpyDeviceToHost, h->stream));
     uint32_t st = 0;
@@ -382,7 +388,7 @@ int strix_cuda_gemv_dev(strix_cuda *h, int nmat, const char *const *keys, const 
         ws[m] = find_weight(h, keys[m]);
         if (!ws[m]) return 0;
     }
-    return gemv_launch(h, nmat, ws, d_a, d_b, eps, pre, act, d_ys, static_cast<cudaStream_t>(stream));
+    return gemv_launch(h, nmat, ws, d_a, d_b, eps, pre, act, d_ys, nullptr, static_cast<cudaStream_t>(stream));
 }
 
 int strix_cuda_device_status(strix_cuda *h, void *stream, uint32_t *status) {

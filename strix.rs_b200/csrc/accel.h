@@ -34,6 +34,8 @@ struct PinBuf {
 
 }  // namespace strix
 
+struct strix_decode_state;  // decode.cu
+
 struct strix_cuda {
     int device = 0;
     int rank = 0, world = 1, profile = 0;
@@ -52,6 +54,7 @@ struct strix_cuda {
     // scratch of the prefill GEMM (grown on demand): f32 activations, their int8 codes, block scales,
     // block code sums, f32 output, split-K partials
     strix::DevBuf gm_x, gm_y, gm_part, gm_xd;
+    strix_decode_state *decode = nullptr;  // configured projection chain (decode.cu), or null
     int8_t *gm_xq = nullptr;
     size_t gm_xq_cap = 0;
     int32_t *gm_xs = nullptr;
@@ -64,4 +67,9 @@ int ensure_f32(strix_cuda *h, DevBuf &b, size_t n);
 int ensure_pinned(strix_cuda *h, PinBuf &b, size_t bytes);
 const Resident *find_weight(strix_cuda *h, const char *key);
 Resident *find_weight_mut(strix_cuda *h, const char *key);
+// One GEMV launch over up to 3 resident weights that share the activation; d_res (may be null)
+// gives per-weight residual vectors added to the outputs.
+void decode_release(strix_cuda *h);  // drops a configured decode chain (its graph holds weight pointers)
+int gemv_launch(strix_cuda *h, int nmat, const Resident *const *ws, const float *d_a, const float *d_b, float eps,
+                int pre, int act, float *const *d_ys, const float *const *d_res, cudaStream_t stream);
 }  // namespace strix

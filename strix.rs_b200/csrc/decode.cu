@@ -1,0 +1,249 @@
+// Resident decode step: the per-token projection chain, four GEMV launches per layer.
+//
+// Mirrors the projection part of RocmWeightAccel::configure_decode / decode_step
+// (crates/strix-backend-rocm/src/decode.rs:4528-4622, 5047-5531) and the CPU forward it
+// must agree with (crates/strix-backend-cpu/src/qwen3.rs:818-899):
+//
+//   per layer:  n = rmsnorm(h, attn_norm);  q,k,v = Wq n, Wk n, Wv n      (one launch, norm fused)
+//               a = attention(q, k, v)                                     -- NOT on this path
+//               h += Wo a                                                  (one launch, residual fused)
+//               n = rmsnorm(h, ffn_norm);  g,u = Wg n, Wu n                (one launch, norm fused)
+//               h += Wd (act(g) * u)                                       (one launch, SwiGLU/GeGLU + residual fused)
+//   logits = Whead rmsnorm(h, output_norm)                                 (one launch, norm fused)
+//
+// The reference needs 12 launches per layer for the same work (decode.rs:5239-5477); here the
+// norm, the activation quantiser, the gate activation and the residual add live inside the GEMV.
+// Attention (QK-norm, RoPE, KV cache, SDPA) is outside this library's path: a configuration is
+// accepted only with `attn_standin_q = 1`, which feeds Wo with q itself (n_heads * head_dim
+// values) so that the whole projection chain can be run and measured; anything else is declined
+// and the model keeps its per-weight gemv path.
+//
+// The step is captured into a CUDA graph on the first call and replayed afterwards
+// (one H2D of h, one graph launch, one D2H of the logits, one sync per token).
+#include <algorithm>
+#include <cstring>
+#include <string>
+#include <vector>
+
+#include "accel.h"
+
+using namespace strix;
+
+#define CU_TRY(h, expr)                                                    \
+    do {                                                                   \
+        cudaError_t _e = (expr);                                           \
+        if (_e != cudaSuccess) {                                           \
+            (h)->err = std::string(#expr) + ": " + cudaGetErrorString(_e); \
+            return -1;                                                     \
+        }                                                                  \
+    } while (0)
+
+struct strix_decode_state {
+    strix_gpu_decode_config cfg{};
+    struct Layer {
+        const Resident *q, *k, *v, *o, *gate, *up, *down;
+        const float *attn_norm, *ffn_norm;
+    };
+    std::vector<Layer> layers;
+    const Resident *head = nullptr;
+    const float *out_norm = nullptr;
+    // activations (device)
+    float *h = nullptr, *q = nullptr, *k = nullptr, *v = nullptr, *gate = nullptr, *up = nullptr, *logits = nullptr;
+    void *pin_h = nullptr, *pin_logits = nullptr;
+    cudaGraphExec_t exec = nullptr;
+};
+
+static void decode_free(strix_decode_state *d) {
+    if (!d) return;
+    for (float *p : {d->h, d->q, d->k, d->v, d->gate, d->up, d->logits})
+        if (p) cudaFree(p);
+    if (d->pin_h) cudaFreeHost(d->pin_h);
+    if (d->pin_logits) cudaFreeHost(d->pin_logits);
+    if (d->exec) cudaGraphExecDestroy(d->exec);
+    delete d;
+}
+
+namespace strix {
+void decode_release(strix_cuda *h) {
+    decode_free(h->decode);
+    h->decode = nullptr;
+}
+}  // namespace strix
+
+static const float *f32_of(strix_cuda *h, const std::string &key, size_t n) {
+    auto it = h->f32s.find(key);
+    if (it == h->f32s.end() || it->second.cap < n) return nullptr;
+    return it->second.p;
+}
+
+// Enqueue the whole chain on `s`. Returns 1, or <0 with h->err set.
+static int enqueue_chain(strix_cuda *h, strix_decode_state *d, cudaStream_t s) {
+    const float eps = d->cfg.eps;
+    const int act = d->cfg.act;
+    const int gate_pre = d->cfg.act_gelu ? STRIX_PRE_GEGLU : STRIX_PRE_SWIGLU;
+    for (auto &L : d->layers) {
+        {
+            const Resident *w[3] = {L.q, L.k, L.v};
+            float *y[3] = {d->q, d->k, d->v};
+            if (gemv_launch(h, 3, w, d->h, L.attn_norm, eps, STRIX_PRE_RMSNORM, act, y, nullptr, s) < 0) return -1;
+        }
+        {   // attention stand-in: Wo is fed with q; h += Wo q
+            const Resident *w[1] = {L.o};
+            float *y[1] = {d->h};
+            const float *r[1] = {d->h};
+            if (gemv_launch(h, 1, w, d->q, nullptr, 0.f, STRIX_PRE_NONE, act, y, r, s) < 0) return -1;
+        }
+        {
+            const Resident *w[2] = {L.gate, L.up};
+            float *y[2] = {d->gate, d->up};
+            if (gemv_launch(h, 2, w, d->h, L.ffn_norm, eps, STRIX_PRE_RMSNORM, act, y, nullptr, s) < 0) return -1;
+        }
+        {
+            const Resident *w[1] = {L.down};
+            float *y[1] = {d->h};
+            const float *r[1] = {d->h};
+            if (gemv_launch(h, 1, w, d->gate, d->up, 0.f, gate_pre, act, y, r, s) < 0) return -1;
+        }
+    }
+    const Resident *w[1] = {d->head};
+    float *y[1] = {d->logits};
+    return gemv_launch(h, 1, w, d->h, d->out_norm, eps, STRIX_PRE_RMSNORM, act, y, nullptr, s);
+}
+
+extern "C" {
+
+int strix_cuda_configure_decode(strix_cuda *h, const strix_gpu_decode_config *cfg) {
+    if (!h || !cfg) return -1;
+    h->err.clear();
+    decode_release(h);
+    // Only the projection chain is on this library's path; a model that expects attention here is declined.
+    if (!cfg->attn_standin_q || cfg->post_norm || cfg->final_softcap != 0.f) return 0;
+    if (h->world > 1) return 0;  // a sharded handle holds row shards only; the chain needs whole vectors
+    if (cfg->act != STRIX_ACT_F32 && cfg->act != STRIX_ACT_Q8DOT) return 0;
+    CU_TRY(h, cudaSetDevice(h->device));
+    auto *d = new strix_decode_state();
+    d->cfg = *cfg;
+    d->cfg.layers = nullptr;
+    const size_t hidden = cfg->hidden, ffn = cfg->ffn;
+    size_t qdim = 0, kvdim = 0;
+    auto need = [&](const std::string &key, size_t in_dim, size_t out_dim) -> const Resident * {
+        const Resident *r = find_weight(h, key.c_str());
+        if (!r || r->L.in_dim != in_dim || (out_dim && r->out_total != out_dim)) return nullptr;
+        return r;
+    };
+    bool ok = true;
+    for (uint32_t il = 0; il < cfg->n_layers && ok; il++) {
+        const std::string b = "blk." + std::to_string(il) + ".";
+        strix_decode_state::Layer L{};
+        L.q = need(b + "attn_q.weight", hidden, 0);
+        L.k = need(b + "attn_k.weight", hidden, 0);
+        L.v = need(b + "attn_v.weight", hidden, 0);
+        ok = L.q && L.k && L.v && L.k->out_total == L.v->out_total && L.q->fmt == L.k->fmt && L.q->fmt == L.v->fmt;
+        if (!ok) break;
+        if (il == 0) {
+            qdim = L.q->out_total;
+            kvdim = L.k->out_total;
+        }
+        ok = L.q->out_total == qdim && L.k->out_total == kvdim;
+        L.o = need(b + "attn_output.weight", qdim, hidden);
+        L.gate = need(b + "ffn_gate.weight", hidden, ffn);
+        L.up = need(b + "ffn_up.weight", hidden, ffn);
+        L.down = need(b + "ffn_down.weight", ffn, hidden);
+        L.attn_norm = f32_of(h, b + "attn_norm.weight", hidden);
+        L.ffn_norm = f32_of(h, b + "ffn_norm.weight", hidden);
+        ok = ok && L.o && L.gate && L.up && L.down && L.attn_norm && L.ffn_norm && L.gate->fmt == L.up->fmt;
+        d->layers.push_back(L);
+    }
+    if (ok) {
+        d->head = need("output.weight", hidden, cfg->vocab);
+        if (!d->head) d->head = need("token_embd.weight", hidden, cfg->vocab);  // tied embedding (qwen3.rs:891-895)
+        d->out_norm = f32_of(h, "output_norm.weight", hidden);
+        ok = d->head && d->out_norm;
+    }
+    if (!ok) {  // a weight the chain needs was not adopted: decline, the model keeps per-weight gemv
+        decode_free(d);
+        return 0;
+    }
+    cudaError_t e = cudaSuccess;
+    auto alloc = [&](float **p, size_t n) {
+        if (e == cudaSuccess) e = cudaMalloc(p, std::max<size_t>(n, 4) * sizeof(float));
+    };
+    alloc(&d->h, hidden);
+    alloc(&d->q, qdim);
+    alloc(&d->k, kvdim);
+    alloc(&d->v, kvdim);
+    alloc(&d->gate, ffn);
+    alloc(&d->up, ffn);
+    alloc(&d->logits, cfg->vocab);
+    if (e == cudaSuccess) e = cudaMallocHost(&d->pin_h, hidden * sizeof(float));
+    if (e == cudaSuccess) e = cudaMallocHost(&d->pin_logits, (size_t)cfg->vocab * sizeof(float));
+    if (e != cudaSuccess) {
+        h->err = std::string("configure_decode: ") + cudaGetErrorString(e);
+        decode_free(d);
+        return -1;
+    }
+    h->decode = d;
+    return 1;
+}
+
+// Device-resident form: runs the chain on d_h[hidden] (updated in place) into d_logits[vocab] on `stream`.
+int strix_cuda_decode_chain_dev(strix_cuda *h, float *d_h, float *d_logits, void *stream) {
+    if (!h || !d_h || !d_logits) return -1;
+    h->err.clear();
+    strix_decode_state *d = h->decode;
+    if (!d) return 0;
+    CU_TRY(h, cudaSetDevice(h->device));
+    float *save_h = d->h, *save_l = d->logits;
+    d->h = d_h;
+    d->logits = d_logits;
+    int rc = enqueue_chain(h, d, static_cast<cudaStream_t>(stream));
+    d->h = save_h;
+    d->logits = save_l;
+    return rc;
+}
+
+int strix_cuda_decode_step(strix_cuda *h, const float *hvec, size_t pos, float *logits, size_t logits_cap) {
+    (void)pos;  // no KV cache on this path: the attention stand-in does not depend on the position
+    if (!h || !hvec || !logits) return -1;
+    h->err.clear();
+    strix_decode_state *d = h->decode;
+    if (!d) return 0;  // not configured: None, the model falls back to per-weight gemv
+    if (logits_cap < d->cfg.vocab) {
+        h->err = "decode_step: logits buffer too small";
+        return -1;
+    }
+    CU_TRY(h, cudaSetDevice(h->device));
+    if (!d->exec) {
+        cudaGraph_t g = nullptr;
+        CU_TRY(h, cudaStreamBeginCapture(h->stream, cudaStreamCaptureModeThreadLocal));
+        int rc = enqueue_chain(h, d, h->stream);
+        cudaError_t e = cudaStreamEndCapture(h->stream, &g);
+        if (rc < 0 || e != cudaSuccess) {
+            if (g) cudaGraphDestroy(g);
+            if (rc >= 0) h->err = std::string("decode_step: graph capture: ") + cudaGetErrorString(e);
+            return -1;
+        }
+        e = cudaGraphInstantiate(&d->exec, g, 0);
+        cudaGraphDestroy(g);
+        if (e != cudaSuccess) {
+            d->exec = nullptr;
+            h->err = std::string("decode_step: graph instantiate: ") + cudaGetErrorString(e);
+            return -1;
+        }
+    }
+    memcpy(d->pin_h, hvec, d->cfg.hidden * sizeof(float));
+    CU_TRY(h, cudaMemcpyAsync(d->h, d->pin_h, d->cfg.hidden * sizeof(float), cudaMemcpyHostToDevice, h->stream));
+    CU_TRY(h, cudaGraphLaunch(d->exec, h->stream));
+    CU_TRY(h, cudaMemcpyAsync(d->pin_logits, d->logits, (size_t)d->cfg.vocab * sizeof(float), cudaMemcpyDeviceToHost, h->stream));
+    CU_TRY(h, cudaMemcpyAsync(&h->status_host, h->d_status, 4, cudaMemcpyDeviceToHost, h->stream));
+    CU_TRY(h, cudaStreamSynchronize(h->stream));
+    if (h->status_host != 0) {
+        h->err = "decode_step: device status " + std::to_string(h->status_host) + " (a bounded wait ran out)";
+        cudaMemsetAsync(h->d_status, 0, 4, h->stream);
+        return -2;
+    }
+    memcpy(logits, d->pin_logits, (size_t)d->cfg.vocab * sizeof(float));
+    return 1;
+}
+
+}  // extern "C"

@@ -490,6 +490,7 @@ __global__ void __launch_bounds__((gemv_warps(ACT) + 1) * 32, 1) gemv_kernel(con
         const TileRef t = tile_ref(A, bid + i * grid);
         const uint32_t st = st0 + s * A.stage_bytes;
         float *y = A.mat[t.mat].y + t.row0;
+        const float *res = A.mat[t.mat].res ? A.mat[t.mat].res + t.row0 : nullptr;
         // Row batches go round-robin over the slots, counted across this CTA's tiles, so that small
         // tiles (fewer batches than slots) still keep every slot busy. Rows past the tile's end read
         // whatever the stage still holds; their sums are dropped.
@@ -510,7 +511,7 @@ __global__ void __launch_bounds__((gemv_warps(ACT) + 1) * 32, 1) gemv_kernel(con
             const float tot = batch_reduce<RB>(acc, lane);
             if (A.wc == 1) {
                 const uint32_t rr = r0 + lane / LPR;
-                if ((lane & (LPR - 1u)) == 0u && rr < t.rows) y[rr] = tot;
+                if ((lane & (LPR - 1u)) == 0u && rr < t.rows) y[rr] = res ? tot + res[rr] : tot;
             } else {
                 float *pb = pp + buf * (RB * A.wc);
                 if ((lane & (LPR - 1u)) == 0u) pb[(lane / LPR) * A.wc + cw] = tot;
@@ -520,7 +521,7 @@ __global__ void __launch_bounds__((gemv_warps(ACT) + 1) * 32, 1) gemv_kernel(con
                     // fixed summation order over the wc column owners: reproducible run to run
                     float sum = 0.f;
                     for (uint32_t k = 0; k < A.wc; k++) sum += pb[lane * A.wc + k];
-                    y[r0 + lane] = sum;
+                    y[r0 + lane] = res ? sum + res[r0 + lane] : sum;
                 }
                 buf ^= 1u;  // the next batch writes the other buffer while warp cw==0 still reads this one
             }

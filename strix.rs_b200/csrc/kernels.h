@@ -22,6 +22,7 @@ constexpr int gemv_warps(int act) { return act == 0 /* STRIX_ACT_F32 */ ? 12 : 1
 struct GemvMat {
     const uint8_t *w;  // resident rows of this accelerator's shard
     float *y;          // output, one float per resident row
+    const float *res;  // optional residual added to the output (y = W x + res); may alias y
     uint32_t rows;
     uint32_t tile0;  // index of this matrix's first tile in the launch-wide tile list
 };
