@@ -138,6 +138,70 @@ def cpu_baseline(orc, synth, seconds=12.0):
             "sample": "first rows of each weight: " + "; ".join(sample), "seconds": round(secs, 2)}
 
 
+def decode_chain_extra(pkg, synth, torch, device, stream):
+    """configs[3]: Qwen3-4B-shaped projection chain (36 layers, hidden 2560, q 4096, kv 1024, ffn 9728,
+    Q4_0 projections, Q6_K lm_head 2560->151936), batch 1; attention replaced by the q stand-in."""
+    hidden, qdim, kvdim, ffn, vocab, n_layers = 2560, 4096, 1024, 9728, 151936, 36
+    acc = pkg.CudaWeightAccel(device)
+    out = {}
+    try:
+        shapes = {"attn_q": (qdim, hidden), "attn_k": (kvdim, hidden), "attn_v": (kvdim, hidden),
+                  "attn_output": (hidden, qdim), "ffn_gate": (ffn, hidden), "ffn_up": (ffn, hidden),
+                  "ffn_down": (hidden, ffn)}
+        base = {nm: make_weight(synth, Q4_0, k, n, 3, "dc." + nm) for nm, (n, k) in shapes.items()}
+        nbytes = 0
+        for il in range(n_layers):
+            for nm, (n, k) in shapes.items():
+                # the same seeded bytes under every layer's name: the chain streams 36 distinct resident copies
+                assert acc.upload_q4_0("blk.%d.%s.weight" % (il, nm), base[nm], k, n)
+                nbytes += n * (k // 32) * 18
+            for nn in ("attn_norm", "ffn_norm"):
+                acc.upload_f32("blk.%d.%s.weight" % (il, nn), synth.norm_weight(3, "dc.%d.%s" % (il, nn), hidden))
+        assert acc.upload_q6_k("output.weight", make_weight(synth, Q6_K, hidden, vocab, 3, "dc.head"), hidden, vocab)
+        nbytes += vocab * (hidden // 256) * 210
+        acc.upload_f32("output_norm.weight", synth.norm_weight(3, "dc.out_norm", hidden))
+        h0 = synth.normal(3, "dc.h0", hidden)
+        dev = torch.device("cuda", device)
+        for act, name in ((pkg.ACT_Q8DOT, "q8dot"), (pkg.ACT_F32, "f32")):
+            assert acc.configure_decode(hidden, 32, ffn, vocab, n_layers, eps=1e-6, act=act)
+            for _ in range(3):
+                logits = acc.decode_step(h0, 0)
+            t0 = time.perf_counter()
+            reps = 20
+            for i in range(reps):
+                logits = acc.decode_step(h0, i)
+            e2e_ms = (time.perf_counter() - t0) / reps * 1e3
+            assert np.isfinite(logits).all()
+            d_h = torch.from_numpy(h0).to(dev)
+            d_h0 = d_h.clone()
+            d_l = torch.empty(vocab, device=dev)
+            with torch.cuda.stream(stream):
+                s = stream.cuda_stream
+                acc.decode_chain_dev(d_h.data_ptr(), d_l.data_ptr(), stream=s)
+                torch.cuda.synchronize()
+                g = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(g, stream=stream):
+                    d_h.copy_(d_h0)
+                    acc.decode_chain_dev(d_h.data_ptr(), d_l.data_ptr(), stream=s)
+                for _ in range(3):
+                    g.replay()
+                torch.cuda.synchronize()
+                a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                a.record()
+                for _ in range(reps):
+                    g.replay()
+                b.record()
+                torch.cuda.synchronize()
+                dev_ms = a.elapsed_time(b) / reps
+            out[name] = {"ms_per_token": round(dev_ms, 4), "ms_per_token_e2e": round(e2e_ms, 4),
+                         "gbs": round(nbytes / dev_ms / 1e6, 1), "launches_per_token": 4 * n_layers + 1}
+        out["bytes_per_token"] = nbytes
+        out["note"] = "projection chain only; attention replaced by feeding Wo with q (no KV cache)"
+    finally:
+        acc.close()
+    return out
+
+
 def run_reference(args):
     """--impl reference: the reference's CPU implementation of the path (oracle port), all host
     threads, each step a bounded row sample of the same six GEMVs."""
@@ -380,6 +444,7 @@ def main():
                     extras["w8a8_gemm"].append({"M": m, "K": k, "N": n, "us": round(us, 1),
                                                 "tops": round(2.0 * m * n * k / us / 1e6, 1)})
                     del xg, yg
+        extras["decode_chain"] = decode_chain_extra(pkg, synth, torch, local, stream)
         if acc.device_status() != 0:
             raise SystemExit("device status word is non-zero after the extras")
 

@@ -148,51 +148,45 @@ __device__ __forceinline__ uint32_t pack4(int a, int b, int c, int d) {
 
 template <int FMT, int ACT, int NCH>
 __device__ __forceinline__ void set_unit_x(LaneX<FMT, ACT, NCH> &X, int c, const float (&v)[16]) {
-    if (ACT == STRIX_ACT_F32) {
 #pragma unroll
-        for (int p = 0; p < 8; p++) {
-            int i0, i1;
-            pair_index<FMT>(p, i0, i1);
-            X.v2[c][p] = make_float2(v[i0], v[i1]);
-        }
+    for (int p = 0; p < 8; p++) {
+        int i0, i1;
+        pair_index<FMT>(p, i0, i1);
+        X.v2[c][p] = make_float2(v[i0], v[i1]);
+    }
+}
+
+__device__ __forceinline__ int sum4(uint32_t w) { return dp4a_ss(w, 0x01010101u, 0); }
+
+// Integer-dot form: copy unit u's 16 int8 codes (as 4 words in the decoder's order), the block
+// scale(s) and bias * sum(codes) from the CTA's quantised activation in shared memory.
+template <int FMT, int ACT, int NCH>
+__device__ __forceinline__ void load_unit_q(LaneX<FMT, ACT, NCH> &X, int c, uint32_t u, bool valid, const int8_t *xq,
+                                            const float *sd) {
+    if (FMT == FMT_Q8_0) {
+        const uint4 w = *reinterpret_cast<const uint4 *>(xq + 16u * u);
+        X.q[c][0] = w.x; X.q[c][1] = w.y; X.q[c][2] = w.z; X.q[c][3] = w.w;
+        X.d[c][0] = sd[u >> 1];
+        X.qs[c][0] = 128 * (sum4(w.x) + sum4(w.y) + sum4(w.z) + sum4(w.w));  // resident codes are q + 128
+    } else if (FMT == FMT_Q4_0) {
+        const uint32_t e = 32u * (u >> 1) + 8u * (u & 1u);
+        const uint2 lo = *reinterpret_cast<const uint2 *>(xq + e), hi = *reinterpret_cast<const uint2 *>(xq + e + 16u);
+        X.q[c][0] = lo.x; X.q[c][1] = lo.y; X.q[c][2] = hi.x; X.q[c][3] = hi.y;
+        X.d[c][0] = sd[u >> 1];
+        X.qs[c][0] = 8 * (sum4(lo.x) + sum4(lo.y) + sum4(hi.x) + sum4(hi.y));  // nibbles carry +8
     } else {
-        // per-32 quantiser (xquant8, kernels.rs:864-876): d = amax/127, inv = d>0 ? 1/d : 0,
-        // q = clamp(rintf(x*inv)). The 32 elements of a block sit in 2 lanes (Q4_0, Q8_0)
-        // or in the 8 lanes that share (sb, half) (Q6_K).
-        if (FMT != FMT_Q6_K) {
-            float amax = 0.f;
 #pragma unroll
-            for (int i = 0; i < 16; i++) amax = fmaxf(amax, fabsf(v[i]));
-            amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
-            const float d = amax / 127.0f;
-            const float inv = d > 0.f ? 1.0f / d : 0.f;
-            int sum = 0;
-#pragma unroll
-            for (int g = 0; g < 4; g++) {
-                const int q0 = quant1(v[4 * g], inv), q1 = quant1(v[4 * g + 1], inv);
-                const int q2 = quant1(v[4 * g + 2], inv), q3 = quant1(v[4 * g + 3], inv);
-                sum += q0 + q1 + q2 + q3;
-                X.q[c][g] = pack4(q0, q1, q2, q3);
-            }
-            X.d[c][0] = d;
-            X.qs[c][0] = (FMT == FMT_Q4_0 ? 8 : 128) * sum;  // resident codes carry this offset
-        } else {
-#pragma unroll
-            for (int k = 0; k < 4; k++) {
-                float amax = fmaxf(fmaxf(fabsf(v[4 * k]), fabsf(v[4 * k + 1])),
-                                   fmaxf(fabsf(v[4 * k + 2]), fabsf(v[4 * k + 3])));
-                amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
-                amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 2));
-                amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 4));
-                const float d = amax / 127.0f;
-                const float inv = d > 0.f ? 1.0f / d : 0.f;
-                const int q0 = quant1(v[4 * k], inv), q1 = quant1(v[4 * k + 1], inv);
-                const int q2 = quant1(v[4 * k + 2], inv), q3 = quant1(v[4 * k + 3], inv);
-                X.q[c][k] = pack4(q0, q1, q2, q3);
-                X.d[c][k] = d;
-                X.qs[c][k] = 32 * (q0 + q1 + q2 + q3);
-            }
+        for (uint32_t k = 0; k < 4; k++) {
+            const uint32_t e = unit_elem<FMT>(u, k);
+            const uint32_t w = *reinterpret_cast<const uint32_t *>(xq + e);
+            X.q[c][k] = w;
+            X.d[c][k] = sd[e >> 5];
+            X.qs[c][k] = 32 * sum4(w);  // 6-bit codes carry +32
         }
+    }
+    if (!valid) {
+#pragma unroll
+        for (int k = 0; k < 4; k++) X.q[c][k] = 0;
     }
 }
 
@@ -342,6 +336,7 @@ __device__ __forceinline__ TileRef tile_ref(const GemvArgs &A, uint32_t t) {
 //   128  ctl[0]    abort flag (a bounded wait ran out)
 //   256  red[32]   block reduction scratch (RMSNORM prologue)
 //   512  part      per slot: 2 x RB x wc partial sums
+//   ...  x         the activation: K f32 [+ K int8 codes + K/32 f32 block scales]
 //   ...  stages    n_stages x stage_bytes, 128-byte aligned
 constexpr uint32_t SMEM_PART_OFF = 512;
 
@@ -355,6 +350,7 @@ __global__ void __launch_bounds__((gemv_warps(ACT) + 1) * 32, 1) gemv_kernel(con
     float *part = reinterpret_cast<float *>(smem + SMEM_PART_OFF);
     uint8_t *stages = smem + A.stage_off;
 
+    if (A.debug & 2u) return;  // measurement only: cost of an empty launch of this shape
     const uint32_t tid = threadIdx.x, lane = tid & 31u, warp = tid >> 5;
     const uint32_t n_cons = A.wc * A.slots;  // consumer warps; warp n_cons is the producer
     const uint32_t S = A.n_stages, grid = gridDim.x, bid = blockIdx.x;
@@ -382,22 +378,6 @@ __global__ void __launch_bounds__((gemv_warps(ACT) + 1) * 32, 1) gemv_kernel(con
         }
     }
 
-    float scale = 1.0f;
-    if (A.pre == STRIX_PRE_RMSNORM) {
-        // rmsnorm (crates/strix-backend-cpu/src/qwen3.rs:107-114): x * (1/sqrt(mean(x^2)+eps)) * w
-        float ss = 0.f;
-        for (uint32_t i = tid; i < L.in_dim; i += blockDim.x) {
-            float t = __ldg(A.a + i);
-            ss = fmaf(t, t, ss);
-        }
-        ss = warp_sum(ss);
-        if (lane == 0) red[warp] = ss;
-        __syncthreads();
-        float tot = 0.f;
-        for (uint32_t w = 0; w < (blockDim.x >> 5); w++) tot += red[w];
-        scale = 1.0f / sqrtf(tot / (float)L.in_dim + A.eps);
-    }
-
     if (warp == n_cons) {
         // ---- producer: refill a stage as soon as every consumer warp has released it ----
         if (lane == 0) {
@@ -419,8 +399,70 @@ __global__ void __launch_bounds__((gemv_warps(ACT) + 1) * 32, 1) gemv_kernel(con
         return;
     }
 
-    // ---- consumers: this lane's x values, kept in registers for the whole kernel ----
+    // ---- consumers: activation prologue ----
+    // The activation (after the optional RMSNorm / SwiGLU / GeGLU) is produced ONCE per CTA,
+    // cooperatively, into shared memory; for the integer-dot form it is then quantised per 32
+    // elements, one warp per block. Each lane finally copies the values of the units it owns into
+    // registers, where they stay for the whole kernel. (Having every warp rebuild all of x on its
+    // own cost 5-14 us per launch; this costs about one global-load latency.)
     const uint32_t cw = warp % A.wc, slot = warp / A.wc;
+    const uint32_t ct = n_cons * 32u;  // consumer threads = tid < ct
+    float *xs = reinterpret_cast<float *>(smem + A.x_off);                 // [K] f32
+    int8_t *xq = reinterpret_cast<int8_t *>(smem + A.x_off + L.in_dim * 4u);  // [K] int8 codes (Q8DOT)
+    float *sd = reinterpret_cast<float *>(smem + A.x_off + L.in_dim * 5u);    // [K/32] block scales (Q8DOT)
+#define STRIX_CONS_BAR() asm volatile("bar.sync 15, %0;" ::"r"(ct) : "memory")
+    {
+        float scale = 1.0f;
+        if (A.pre == STRIX_PRE_RMSNORM) {
+            // rmsnorm (crates/strix-backend-cpu/src/qwen3.rs:107-114): x * (1/sqrt(mean(x^2)+eps)) * w
+            float ss = 0.f;
+            for (uint32_t e4 = tid; e4 < L.in_dim / 4u; e4 += ct) {
+                const float4 t = __ldg(reinterpret_cast<const float4 *>(A.a) + e4);
+                ss = fmaf(t.x, t.x, ss); ss = fmaf(t.y, t.y, ss); ss = fmaf(t.z, t.z, ss); ss = fmaf(t.w, t.w, ss);
+            }
+            ss = warp_sum(ss);
+            if (lane == 0) red[warp] = ss;
+            STRIX_CONS_BAR();
+            float tot = 0.f;
+            for (uint32_t w = 0; w < n_cons; w++) tot += red[w];
+            scale = 1.0f / sqrtf(tot / (float)L.in_dim + A.eps);
+        }
+        for (uint32_t e4 = tid; e4 < L.in_dim / 4u; e4 += ct) {
+            float4 a4 = __ldg(reinterpret_cast<const float4 *>(A.a) + e4);
+            if (A.pre != STRIX_PRE_NONE) {
+                const float4 b4 = __ldg(reinterpret_cast<const float4 *>(A.b) + e4);
+                if (A.pre == STRIX_PRE_RMSNORM) {
+                    a4.x = (a4.x * scale) * b4.x; a4.y = (a4.y * scale) * b4.y;
+                    a4.z = (a4.z * scale) * b4.z; a4.w = (a4.w * scale) * b4.w;
+                } else if (A.pre == STRIX_PRE_SWIGLU) {
+                    a4.x = silu_f(a4.x) * b4.x; a4.y = silu_f(a4.y) * b4.y;
+                    a4.z = silu_f(a4.z) * b4.z; a4.w = silu_f(a4.w) * b4.w;
+                } else {
+                    a4.x = gelu_tanh_f(a4.x) * b4.x; a4.y = gelu_tanh_f(a4.y) * b4.y;
+                    a4.z = gelu_tanh_f(a4.z) * b4.z; a4.w = gelu_tanh_f(a4.w) * b4.w;
+                }
+            }
+            reinterpret_cast<float4 *>(xs)[e4] = a4;
+        }
+        STRIX_CONS_BAR();
+        if (ACT == STRIX_ACT_Q8DOT) {
+            // per-32 quantiser (xquant8, kernels.rs:864-876): d = amax/127, inv = d>0 ? 1/d : 0,
+            // q = clamp(rintf(x*inv)); one warp per block, one lane per element
+            for (uint32_t blk = warp; blk < L.in_dim / 32u; blk += n_cons) {
+                const float v = xs[blk * 32u + lane];
+                float amax = fabsf(v);
+#pragma unroll
+                for (int o = 16; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
+                const float d = amax / 127.0f;
+                const float inv = d > 0.f ? 1.0f / d : 0.f;
+                xq[blk * 32u + lane] = (int8_t)quant1(v, inv);
+                if (lane == 0) sd[blk] = d;
+            }
+            STRIX_CONS_BAR();
+        }
+    }
+#undef STRIX_CONS_BAR
+    // this lane's units: offsets into a resident row, and the x values, in registers from here on
     LaneX<FMT, ACT, NCH> X;
     {
         const uint32_t u0 = cw * (uint32_t)NCH * 32u + lane;  // warp cw owns runs cw*NCH .. cw*NCH+NCH-1
@@ -446,35 +488,27 @@ __global__ void __launch_bounds__((gemv_warps(ACT) + 1) * 32, 1) gemv_kernel(con
             const uint32_t u = u0 + 32u * (uint32_t)c;
             const bool valid = u < U;
             if (valid) X.valid |= 1u << c;
-            float v[16];
+            if (ACT == STRIX_ACT_F32) {
+                float v[16];
 #pragma unroll
-            for (uint32_t g = 0; g < 4; g++) {
-                float4 a4 = make_float4(0.f, 0.f, 0.f, 0.f);
-                if (valid) {
-                    const uint32_t e = unit_elem<FMT>(u, g);
-                    a4 = __ldg(reinterpret_cast<const float4 *>(A.a + e));
-                    if (A.pre != STRIX_PRE_NONE) {
-                        const float4 b4 = __ldg(reinterpret_cast<const float4 *>(A.b + e));
-                        if (A.pre == STRIX_PRE_RMSNORM) {
-                            a4.x = (a4.x * scale) * b4.x; a4.y = (a4.y * scale) * b4.y;
-                            a4.z = (a4.z * scale) * b4.z; a4.w = (a4.w * scale) * b4.w;
-                        } else if (A.pre == STRIX_PRE_SWIGLU) {
-                            a4.x = silu_f(a4.x) * b4.x; a4.y = silu_f(a4.y) * b4.y;
-                            a4.z = silu_f(a4.z) * b4.z; a4.w = silu_f(a4.w) * b4.w;
-                        } else {
-                            a4.x = gelu_tanh_f(a4.x) * b4.x; a4.y = gelu_tanh_f(a4.y) * b4.y;
-                            a4.z = gelu_tanh_f(a4.z) * b4.z; a4.w = gelu_tanh_f(a4.w) * b4.w;
-                        }
-                    }
+                for (uint32_t g = 0; g < 4; g++) {
+                    const float4 a4 = valid ? *reinterpret_cast<const float4 *>(xs + unit_elem<FMT>(u, g))
+                                            : make_float4(0.f, 0.f, 0.f, 0.f);
+                    v[4 * g] = a4.x; v[4 * g + 1] = a4.y; v[4 * g + 2] = a4.z; v[4 * g + 3] = a4.w;
                 }
-                v[4 * g] = a4.x; v[4 * g + 1] = a4.y; v[4 * g + 2] = a4.z; v[4 * g + 3] = a4.w;
+                set_unit_x<FMT, ACT, NCH>(X, c, v);
+            } else {
+                load_unit_q<FMT, ACT, NCH>(X, c, valid ? u : 0u, valid, xq, sd);
             }
-            set_unit_x<FMT, ACT, NCH>(X, c, v);
         }
     }
 
     // ---- stream the tiles. The wc warps of a slot meet on a named barrier per row batch; slots
     //      run independently of one another, and nothing in the loop is CTA-wide. ----
+    if (A.debug & 4u) {  // measurement only: stop after the activation prologue (keeps X alive through a dummy store)
+        if (X.valid == 0xffffffffu) A.mat[0].y[0] = (float)X.off_w;
+        return;
+    }
     float *pp = part + slot * (2u * RB * A.wc);
     const uint32_t bar_id = 1u + slot, bar_n = A.wc * 32u;
     uint32_t buf = 0;
@@ -596,7 +630,9 @@ bool gemv_plan(GemvArgs &a, int num_sms, size_t smem_optin) {
     a.wc = wc;
     a.slots = slots;
     a.nch = nch;
-    const uint32_t stage_off = SMEM_PART_OFF + align128u(slots * 2u * rb * wc * 4u);
+    a.x_off = SMEM_PART_OFF + align128u(slots * 2u * rb * wc * 4u);
+    // the CTA's activation: K f32 values; for the integer-dot form also K int8 codes and K/32 scales
+    const uint32_t stage_off = a.x_off + align128u(K * 4u + (a.act == STRIX_ACT_Q8DOT ? K + K / 8u : 0u));
     a.stage_off = stage_off;
     a.stage_bytes = align128u(rt * stride);
     if (budget < stage_off + 2u * a.stage_bytes) return false;

@@ -40,6 +40,7 @@ struct GemvArgs {
     uint32_t n_tiles;
     uint32_t stage_bytes;  // multiple of 128
     uint32_t stage_off;    // byte offset of the first stage in dynamic shared memory
+    uint32_t x_off;        // byte offset of the CTA's activation vector in dynamic shared memory
     uint32_t n_stages;
     uint32_t wc;     // warps that split a row's K range between them
     uint32_t slots;  // groups of wc warps, each working on different rows of a tile
