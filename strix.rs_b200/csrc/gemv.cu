@@ -49,10 +49,14 @@ __device__ __forceinline__ uint32_t unit_elem(uint32_t u, uint32_t g) {
     return 256u * sb + 128u * (r >> 3) + 32u * g + 4u * (r & 7u);
 }
 
-__device__ __forceinline__ float silu_f(float g) { return g / (1.0f + expf(-g)); }
+// SwiGLU / GeGLU gates with the fast exponential (as the reference's device kernels do:
+// silu_quant uses __expf, kernels.rs:879-892); relative error ~1e-6, far inside the 1e-3 contract.
+__device__ __forceinline__ float silu_f(float g) { return __fdividef(g, 1.0f + __expf(-g)); }
 __device__ __forceinline__ float gelu_tanh_f(float x) {
     const float C = 0.7978846f;
-    return 0.5f * x * (1.0f + tanhf(C * (x + 0.044715f * x * x * x)));
+    const float t = C * (x + 0.044715f * x * x * x);
+    const float th = 1.0f - __fdividef(2.0f, 1.0f + __expf(2.0f * t));  // tanh(t)
+    return 0.5f * x * (1.0f + th);
 }
 
 // ---- shared-memory loads on 32-bit shared addresses (always LDS, 32-bit address arithmetic) ----
@@ -447,16 +451,22 @@ __global__ void __launch_bounds__((gemv_warps(ACT) + 1) * 32, 1) gemv_kernel(con
         STRIX_CONS_BAR();
         if (ACT == STRIX_ACT_Q8DOT) {
             // per-32 quantiser (xquant8, kernels.rs:864-876): d = amax/127, inv = d>0 ? 1/d : 0,
-            // q = clamp(rintf(x*inv)); one warp per block, one lane per element
-            for (uint32_t blk = warp; blk < L.in_dim / 32u; blk += n_cons) {
-                const float v = xs[blk * 32u + lane];
-                float amax = fabsf(v);
-#pragma unroll
-                for (int o = 16; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
+            // q = clamp(rintf(x*inv)); eight lanes per block (four elements each), four blocks per warp pass
+            const uint32_t sub = lane >> 3, l8 = lane & 7u;
+            for (uint32_t blk = warp * 4u + sub; blk < L.in_dim / 32u; blk += n_cons * 4u) {
+                const float4 v = *reinterpret_cast<const float4 *>(xs + blk * 32u + l8 * 4u);
+                float amax = fmaxf(fmaxf(fabsf(v.x), fabsf(v.y)), fmaxf(fabsf(v.z), fabsf(v.w)));
+                // (the loop bound is uniform within each group of eight lanes; all 32 lanes run the same
+                // number of passes only when the block count is a multiple of 4, hence the masks)
+                const uint32_t mask = 0xffu << (sub * 8u);
+                amax = fmaxf(amax, __shfl_xor_sync(mask, amax, 1));
+                amax = fmaxf(amax, __shfl_xor_sync(mask, amax, 2));
+                amax = fmaxf(amax, __shfl_xor_sync(mask, amax, 4));
                 const float d = amax / 127.0f;
                 const float inv = d > 0.f ? 1.0f / d : 0.f;
-                xq[blk * 32u + lane] = (int8_t)quant1(v, inv);
-                if (lane == 0) sd[blk] = d;
+                *reinterpret_cast<uint32_t *>(xq + blk * 32u + l8 * 4u) =
+                    pack4(quant1(v.x, inv), quant1(v.y, inv), quant1(v.z, inv), quant1(v.w, inv));
+                if (l8 == 0) sd[blk] = d;
             }
             STRIX_CONS_BAR();
         }
