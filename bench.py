@@ -267,9 +267,14 @@ def main():
         raise SystemExit("bench.py needs a CUDA device: the backend has no CPU path")
     torch.cuda.set_device(local)
     dev = torch.device("cuda", local)
+    cpu_group = None
     if world > 1:
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        # plain peer-to-peer NCCL: the gathers here are a few KB to 600 KB, and a rank that leaves while
+        # its memory is bound to an NVLink multicast object can fault its peers
+        os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
         dist.init_process_group("nccl", device_id=dev)
+        cpu_group = dist.new_group(backend="gloo")  # host-side rendezvous for the end of the run
 
     pkg = entry.load_package()
     from strix_rs_b200 import synth
@@ -468,9 +473,17 @@ def main():
             "frac_of_8tbs": round(value / 8000.0, 4),
         }
         print(json.dumps(out))
-    acc.close()
+    sys.stdout.flush()
     if world > 1:
-        dist.destroy_process_group()
+        # Leave together and without NCCL teardown: destroying the process group after CUDA graphs that
+        # captured collectives have run was seen to block for ever on this stack. All GPU work is done
+        # (synchronised above); the ranks meet on the host, then exit.
+        del graph
+        torch.cuda.synchronize()
+        dist.barrier(group=cpu_group)
+        sys.stderr.flush()
+        os._exit(0)
+    acc.close()
 
 
 if __name__ == "__main__":
