@@ -181,6 +181,15 @@ STRIX_API int strix_cuda_decode_step(strix_cuda *h, const float *hvec, size_t po
 /* The same chain on device pointers (d_h is updated in place), enqueued on `stream`; no copy, no sync. */
 STRIX_API int strix_cuda_decode_chain_dev(strix_cuda *h, float *d_h, float *d_logits, void *stream);
 
+/* Batched GEMV for speculative verify (the reference runs its verify rows through the 128-token
+ * prefill GEMM, decode.rs:5548-5553, 6366-6410): ys[b][rows] = W xs[b][in_dim] for b activation rows
+ * with ONE pass over the weights per chunk of up to 8 rows. Host buffers, one sync. */
+STRIX_API int strix_cuda_gemv_rows(strix_cuda *h, const char *key, const float *xs, size_t b, float *y, size_t y_cap,
+                         int act);
+/* The same on device pointers, up to 3 weights that share the activations per launch; no copy, no sync. */
+STRIX_API int strix_cuda_gemv_rows_dev(strix_cuda *h, int nmat, const char *const *keys, const float *d_xs, size_t b,
+                             int act, float *const *d_ys, void *stream);
+
 /* Device status word written by kernels whose bounded waits ran out
  * (0 = clean). Synchronises `stream`. */
 STRIX_API int strix_cuda_device_status(strix_cuda *h, void *stream, uint32_t *status);

@@ -86,6 +86,9 @@ def load_library():
     sig("strix_cuda_configure_decode", C.c_int, H, C.POINTER(_DecodeCfg))
     sig("strix_cuda_decode_step", C.c_int, H, f32p, sz, f32p, sz)
     sig("strix_cuda_decode_chain_dev", C.c_int, H, C.c_void_p, C.c_void_p, C.c_void_p)
+    sig("strix_cuda_gemv_rows", C.c_int, H, C.c_char_p, f32p, sz, f32p, sz, C.c_int)
+    sig("strix_cuda_gemv_rows_dev", C.c_int, H, C.c_int, C.POINTER(C.c_char_p), C.c_void_p, sz, C.c_int,
+        C.POINTER(C.c_void_p), C.c_void_p)
     sig("strix_cuda_device_status", C.c_int, H, C.c_void_p, C.POINTER(C.c_uint32))
     sig("strix_cuda_dequant_to_f32", C.c_int, H, C.c_char_p, f32p, sz)
     sig("strix_cuda_xquant8", C.c_int, H, f32p, sz, C.POINTER(C.c_int8), f32p)
@@ -213,6 +216,24 @@ class CudaWeightAccel:
         st = (C.c_int * n)()
         self._check(self._L.strix_cuda_gemv_batch(self._h, n, keys, xp, ks, yp, yc, act, st))
         return [ys[i] if (infos[i] is not None and st[i] == 1) else None for i in range(n)]
+
+    def gemv_rows(self, key, xs, b, act=ACT_F32):
+        """ys[b][rows] = W xs[b][in_dim]: b activation rows, one pass over the weights. None if not resident."""
+        info = self.weight_info(key)
+        xa = _f32(xs)
+        if info is None or xa.size != b * info["in_dim"]:
+            return None
+        y = np.empty((b, info["rows"]), dtype=np.float32)
+        rc = self._check(self._L.strix_cuda_gemv_rows(self._h, key.encode(), _fp(xa), b, _fp(y), y.size, act))
+        return y if rc == 1 else None
+
+    def gemv_rows_dev(self, keys, d_xs, b, d_ys, act=ACT_F32, stream=0):
+        n = len(keys)
+        kk = (C.c_char_p * n)(*[k.encode() for k in keys])
+        yy = (C.c_void_p * n)(*[int(p) for p in d_ys])
+        rc = self._check(self._L.strix_cuda_gemv_rows_dev(self._h, n, kk, C.c_void_p(int(d_xs)), b, act, yy,
+                                                         C.c_void_p(int(stream)) if stream else None))
+        return rc == 1
 
     def prefill_q8_gemm(self, key, xs, m):
         """y[m][out] = W8A8 GEMM on a resident Q8_0 weight, or None (unknown key / not Q8_0 / bad length)."""

@@ -138,6 +138,15 @@ static int upload_quant(strix_cuda *h, int fmt, const char *key, const uint8_t *
 namespace strix {
 int gemv_launch(strix_cuda *h, int nmat, const Resident *const *ws, const float *d_a, const float *d_b, float eps,
                 int pre, int act, float *const *d_ys, const float *const *d_res, cudaStream_t stream) {
+    return gemv_launch_rows(h, nmat, ws, d_a, d_b, eps, pre, act, d_ys, d_res, 1, 0, 0, stream);
+}
+
+// b activation rows (a_stride / b_stride floats apart; outputs rows-of-the-weight floats apart) share
+// one pass over the weights. Rows are taken in chunks when their activations do not fit in shared
+// memory next to at least two pipeline stages.
+int gemv_launch_rows(strix_cuda *h, int nmat, const Resident *const *ws, const float *d_a, const float *d_b, float eps,
+                     int pre, int act, float *const *d_ys, const float *const *d_res, uint32_t b, uint32_t a_stride,
+                     uint32_t b_stride, cudaStream_t stream) {
     if (nmat < 1 || nmat > GEMV_MAX_MATS) {
         h->err = "gemv: between 1 and 3 weights per launch";
         return -1;
@@ -159,17 +168,35 @@ int gemv_launch(strix_cuda *h, int nmat, const Resident *const *ws, const float 
         a.mat[m].res = d_res ? d_res[m] : nullptr;
         a.mat[m].rows = (uint32_t)ws[m]->rows;
     }
-    a.a = d_a;
-    a.b = d_b;
     a.eps = eps;
     a.pre = pre;
     a.act = act;
     a.status = h->d_status;
-    if (!gemv_plan(a, h->num_sms, h->smem_optin)) {
-        h->err = "gemv: in_dim too large for the shared-memory pipeline";
-        return -1;
+    a.a_stride = a_stride;
+    a.b_stride = b_stride;
+    for (int m = 0; m < nmat; m++) a.mat[m].ystride = (uint32_t)ws[m]->rows;
+    uint32_t done = 0;
+    while (done < b) {
+        uint32_t chunk = std::min<uint32_t>(b - done, 8u);
+        GemvArgs c = a;
+        for (;; chunk = (chunk + 1) / 2) {
+            c = a;
+            c.nbatch = chunk;
+            if (gemv_plan(c, h->num_sms, h->smem_optin)) break;
+            if (chunk == 1) {
+                h->err = "gemv: in_dim too large for the shared-memory pipeline";
+                return -1;
+            }
+        }
+        c.a = d_a + (size_t)done * a_stride;
+        c.b = d_b ? d_b + (size_t)done * b_stride : nullptr;
+        for (int m = 0; m < nmat; m++) {
+            c.mat[m].y = d_ys[m] + (size_t)done * c.mat[m].ystride;
+            c.mat[m].res = (d_res && d_res[m]) ? d_res[m] + (size_t)done * c.mat[m].ystride : nullptr;
+        }
+        CU_TRY(h, launch_gemv(c, stream));
+        done += chunk;
     }
-    CU_TRY(h, launch_gemv(a, stream));
     return 1;
 }
 }  // namespace strix
@@ -389,6 +416,55 @@ int strix_cuda_gemv_dev(strix_cuda *h, int nmat, const char *const *keys, const 
         if (!ws[m]) return 0;
     }
     return gemv_launch(h, nmat, ws, d_a, d_b, eps, pre, act, d_ys, nullptr, static_cast<cudaStream_t>(stream));
+}
+
+int strix_cuda_gemv_rows_dev(strix_cuda *h, int nmat, const char *const *keys, const float *d_xs, size_t b, int act,
+                             float *const *d_ys, void *stream) {
+    if (!h || !keys || !d_xs || !d_ys) return -1;
+    h->err.clear();
+    if (nmat < 1 || nmat > GEMV_MAX_MATS) {
+        h->err = "gemv_rows_dev: between 1 and 3 weights per launch";
+        return -1;
+    }
+    if (b == 0) return 1;
+    CU_TRY(h, cudaSetDevice(h->device));
+    const Resident *ws[GEMV_MAX_MATS];
+    for (int m = 0; m < nmat; m++) {
+        ws[m] = find_weight(h, keys[m]);
+        if (!ws[m]) return 0;
+    }
+    return gemv_launch_rows(h, nmat, ws, d_xs, nullptr, 0.f, STRIX_PRE_NONE, act, d_ys, nullptr, (uint32_t)b,
+                            ws[0]->L.in_dim, 0, static_cast<cudaStream_t>(stream));
+}
+
+int strix_cuda_gemv_rows(strix_cuda *h, const char *key, const float *xs, size_t b, float *y, size_t y_cap, int act) {
+    if (!h || !key || !xs || !y) return -1;
+    h->err.clear();
+    const Resident *r = find_weight(h, key);
+    if (!r) return 0;
+    if (b == 0) return 1;
+    if (y_cap < b * r->rows) {
+        h->err = "gemv_rows: output too small";
+        return -1;
+    }
+    CU_TRY(h, cudaSetDevice(h->device));
+    const size_t K = r->L.in_dim;
+    if (ensure_f32(h, h->x, b * K) < 0 || ensure_f32(h, h->y, std::max<size_t>(b * r->rows, 1)) < 0) return -1;
+    CU_TRY(h, cudaMemcpyAsync(h->x.p, xs, b * K * sizeof(float), cudaMemcpyHostToDevice, h->stream));
+    const Resident *w1[1] = {r};
+    float *y1[1] = {h->y.p};
+    if (gemv_launch_rows(h, 1, w1, h->x.p, nullptr, 0.f, STRIX_PRE_NONE, act, y1, nullptr, (uint32_t)b, (uint32_t)K, 0,
+                         h->stream) < 0)
+        return -1;
+    if (r->rows) CU_TRY(h, cudaMemcpyAsync(y, h->y.p, b * r->rows * sizeof(float), cudaMemcpyDeviceToHost, h->stream));
+    CU_TRY(h, cudaMemcpyAsync(&h->status_host, h->d_status, 4, cudaMemcpyDeviceToHost, h->stream));
+    CU_TRY(h, cudaStreamSynchronize(h->stream));
+    if (h->status_host != 0) {
+        h->err = "gemv_rows: device status " + std::to_string(h->status_host) + " (a bounded wait ran out)";
+        cudaMemsetAsync(h->d_status, 0, 4, h->stream);
+        return -2;
+    }
+    return 1;
 }
 
 int strix_cuda_device_status(strix_cuda *h, void *stream, uint32_t *status) {

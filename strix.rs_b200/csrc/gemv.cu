@@ -340,7 +340,7 @@ __device__ __forceinline__ TileRef tile_ref(const GemvArgs &A, uint32_t t) {
 //   128  ctl[0]    abort flag (a bounded wait ran out)
 //   256  red[32]   block reduction scratch (RMSNORM prologue)
 //   512  part      per slot: 2 x RB x wc partial sums
-//   ...  x         the activation: K f32 [+ K int8 codes + K/32 f32 block scales]
+//   ...  x         the activations: B x K f32, or K f32 staging + B x (K int8 codes + K/32 f32 block scales)
 //   ...  stages    n_stages x stage_bytes, 128-byte aligned
 constexpr uint32_t SMEM_PART_OFF = 512;
 
@@ -411,17 +411,25 @@ __global__ void __launch_bounds__((gemv_warps(ACT) + 1) * 32, 1) gemv_kernel(con
     // own cost 5-14 us per launch; this costs about one global-load latency.)
     const uint32_t cw = warp % A.wc, slot = warp / A.wc;
     const uint32_t ct = n_cons * 32u;  // consumer threads = tid < ct
-    float *xs = reinterpret_cast<float *>(smem + A.x_off);                 // [K] f32
-    int8_t *xq = reinterpret_cast<int8_t *>(smem + A.x_off + L.in_dim * 4u);  // [K] int8 codes (Q8DOT)
-    float *sd = reinterpret_cast<float *>(smem + A.x_off + L.in_dim * 5u);    // [K/32] block scales (Q8DOT)
+    // f32 form: xs[B][K].  integer-dot form: xs[K] (staging, reused per activation row), then
+    // xq[B][K] int8 codes and sd[B][K/32] block scales.   B = A.nbatch activation rows share the weights.
+    const uint32_t B = A.nbatch, K = L.in_dim;
+    float *xs0 = reinterpret_cast<float *>(smem + A.x_off);
+    int8_t *xq0 = reinterpret_cast<int8_t *>(smem + A.x_off + K * 4u);
+    float *sd0 = reinterpret_cast<float *>(smem + A.x_off + K * 4u + B * K);
 #define STRIX_CONS_BAR() asm volatile("bar.sync 15, %0;" ::"r"(ct) : "memory")
-    {
+    for (uint32_t bi = 0; bi < B; bi++) {
+        const float *Aa = A.a + (size_t)bi * A.a_stride;
+        const float *Ab = A.b ? A.b + (size_t)bi * A.b_stride : nullptr;
+        float *xs = (ACT == STRIX_ACT_F32) ? xs0 + bi * K : xs0;
+        int8_t *xq = xq0 + bi * K;
+        float *sd = sd0 + bi * (K / 32u);
         float scale = 1.0f;
         if (A.pre == STRIX_PRE_RMSNORM) {
             // rmsnorm (crates/strix-backend-cpu/src/qwen3.rs:107-114): x * (1/sqrt(mean(x^2)+eps)) * w
             float ss = 0.f;
             for (uint32_t e4 = tid; e4 < L.in_dim / 4u; e4 += ct) {
-                const float4 t = __ldg(reinterpret_cast<const float4 *>(A.a) + e4);
+                const float4 t = __ldg(reinterpret_cast<const float4 *>(Aa) + e4);
                 ss = fmaf(t.x, t.x, ss); ss = fmaf(t.y, t.y, ss); ss = fmaf(t.z, t.z, ss); ss = fmaf(t.w, t.w, ss);
             }
             ss = warp_sum(ss);
@@ -430,11 +438,12 @@ __global__ void __launch_bounds__((gemv_warps(ACT) + 1) * 32, 1) gemv_kernel(con
             float tot = 0.f;
             for (uint32_t w = 0; w < n_cons; w++) tot += red[w];
             scale = 1.0f / sqrtf(tot / (float)L.in_dim + A.eps);
+            if (B > 1) STRIX_CONS_BAR();  // red[] is rewritten for the next activation row
         }
         for (uint32_t e4 = tid; e4 < L.in_dim / 4u; e4 += ct) {
-            float4 a4 = __ldg(reinterpret_cast<const float4 *>(A.a) + e4);
+            float4 a4 = __ldg(reinterpret_cast<const float4 *>(Aa) + e4);
             if (A.pre != STRIX_PRE_NONE) {
-                const float4 b4 = __ldg(reinterpret_cast<const float4 *>(A.b) + e4);
+                const float4 b4 = __ldg(reinterpret_cast<const float4 *>(Ab) + e4);
                 if (A.pre == STRIX_PRE_RMSNORM) {
                     a4.x = (a4.x * scale) * b4.x; a4.y = (a4.y * scale) * b4.y;
                     a4.z = (a4.z * scale) * b4.z; a4.w = (a4.w * scale) * b4.w;
@@ -474,31 +483,35 @@ __global__ void __launch_bounds__((gemv_warps(ACT) + 1) * 32, 1) gemv_kernel(con
 #undef STRIX_CONS_BAR
     // this lane's units: offsets into a resident row, and the x values, in registers from here on
     LaneX<FMT, ACT, NCH> X;
-    {
-        const uint32_t u0 = cw * (uint32_t)NCH * 32u + lane;  // warp cw owns runs cw*NCH .. cw*NCH+NCH-1
-        X.off_hh = X.off_sc = X.sel_a = X.sel_b = 0;
-        if (FMT == FMT_Q8_0) {
-            X.off_w = u0 * 16u;
-            X.off_s = L.off_d + 2u * (u0 >> 1);
-        } else if (FMT == FMT_Q4_0) {
-            X.off_w = u0 * 8u;
-            X.off_s = L.off_d + 2u * (u0 >> 1);
-        } else {
-            const uint32_t sb = u0 >> 4, r = u0 & 15u, h = r >> 3, c4 = r & 7u;
-            X.off_w = sb * 128u + h * 64u + c4 * 4u;
-            X.off_hh = L.off_qh + sb * 64u + h * 32u + c4 * 4u;
-            X.off_sc = L.off_sc + sb * 16u + h * 8u;
-            X.off_s = L.off_d + 2u * sb;
-            X.sel_a = sext_sel(c4 >> 2);         // sub-scale byte (c4>>2)     of a word: groups 0 and 2
-            X.sel_b = sext_sel((c4 >> 2) + 2u);  // sub-scale byte (c4>>2) + 2 of a word: groups 1 and 3
-        }
-        X.valid = 0;
+    const uint32_t u0 = cw * (uint32_t)NCH * 32u + lane;  // warp cw owns runs cw*NCH .. cw*NCH+NCH-1
+    X.off_hh = X.off_sc = X.sel_a = X.sel_b = 0;
+    if (FMT == FMT_Q8_0) {
+        X.off_w = u0 * 16u;
+        X.off_s = L.off_d + 2u * (u0 >> 1);
+    } else if (FMT == FMT_Q4_0) {
+        X.off_w = u0 * 8u;
+        X.off_s = L.off_d + 2u * (u0 >> 1);
+    } else {
+        const uint32_t sb = u0 >> 4, r = u0 & 15u, h = r >> 3, c4 = r & 7u;
+        X.off_w = sb * 128u + h * 64u + c4 * 4u;
+        X.off_hh = L.off_qh + sb * 64u + h * 32u + c4 * 4u;
+        X.off_sc = L.off_sc + sb * 16u + h * 8u;
+        X.off_s = L.off_d + 2u * sb;
+        X.sel_a = sext_sel(c4 >> 2);         // sub-scale byte (c4>>2)     of a word: groups 0 and 2
+        X.sel_b = sext_sel((c4 >> 2) + 2u);  // sub-scale byte (c4>>2) + 2 of a word: groups 1 and 3
+    }
+    X.valid = 0;
+#pragma unroll
+    for (int c = 0; c < NCH; c++)
+        if (u0 + 32u * (uint32_t)c < U) X.valid |= 1u << c;
+    // copies activation row bi's values for this lane's units from shared memory into X
+    auto load_x = [&](uint32_t bi) {
 #pragma unroll
         for (int c = 0; c < NCH; c++) {
             const uint32_t u = u0 + 32u * (uint32_t)c;
             const bool valid = u < U;
-            if (valid) X.valid |= 1u << c;
             if (ACT == STRIX_ACT_F32) {
+                const float *xs = xs0 + bi * K;
                 float v[16];
 #pragma unroll
                 for (uint32_t g = 0; g < 4; g++) {
@@ -508,10 +521,11 @@ __global__ void __launch_bounds__((gemv_warps(ACT) + 1) * 32, 1) gemv_kernel(con
                 }
                 set_unit_x<FMT, ACT, NCH>(X, c, v);
             } else {
-                load_unit_q<FMT, ACT, NCH>(X, c, valid ? u : 0u, valid, xq, sd);
+                load_unit_q<FMT, ACT, NCH>(X, c, valid ? u : 0u, valid, xq0 + bi * K, sd0 + bi * (K / 32u));
             }
         }
-    }
+    };
+    load_x(0);
 
     // ---- stream the tiles. The wc warps of a slot meet on a named barrier per row batch; slots
     //      run independently of one another, and nothing in the loop is CTA-wide. ----
@@ -533,8 +547,10 @@ __global__ void __launch_bounds__((gemv_warps(ACT) + 1) * 32, 1) gemv_kernel(con
         if (!ctl[0] && !mbar_wait_bounded(&full[s], (i / S) & 1u, A.status)) ctl[0] = 1;
         const TileRef t = tile_ref(A, bid + i * grid);
         const uint32_t st = st0 + s * A.stage_bytes;
-        float *y = A.mat[t.mat].y + t.row0;
-        const float *res = A.mat[t.mat].res ? A.mat[t.mat].res + t.row0 : nullptr;
+        for (uint32_t bi = 0; bi < B; bi++) {
+        if (B > 1) load_x(bi);  // weights stay in shared memory; only this lane's x values change
+        float *y = A.mat[t.mat].y + (size_t)bi * A.mat[t.mat].ystride + t.row0;
+        const float *res = A.mat[t.mat].res ? A.mat[t.mat].res + (size_t)bi * A.mat[t.mat].ystride + t.row0 : nullptr;
         // Row batches go round-robin over the slots, counted across this CTA's tiles, so that small
         // tiles (fewer batches than slots) still keep every slot busy. Rows past the tile's end read
         // whatever the stage still holds; their sums are dropped.
@@ -570,6 +586,7 @@ __global__ void __launch_bounds__((gemv_warps(ACT) + 1) * 32, 1) gemv_kernel(con
                 buf ^= 1u;  // the next batch writes the other buffer while warp cw==0 still reads this one
             }
         }
+        }  // activation rows
         __syncwarp();
         if (lane == 0) mbar_arrive(&empty[s]);  // this warp's reads of the stage are complete
     }
@@ -642,7 +659,10 @@ bool gemv_plan(GemvArgs &a, int num_sms, size_t smem_optin) {
     a.nch = nch;
     a.x_off = SMEM_PART_OFF + align128u(slots * 2u * rb * wc * 4u);
     // the CTA's activation: K f32 values; for the integer-dot form also K int8 codes and K/32 scales
-    const uint32_t stage_off = a.x_off + align128u(K * 4u + (a.act == STRIX_ACT_Q8DOT ? K + K / 8u : 0u));
+    const uint32_t nbt = a.nbatch ? a.nbatch : 1u;
+    a.nbatch = nbt;
+    const uint32_t stage_off =
+        a.x_off + align128u(a.act == STRIX_ACT_Q8DOT ? K * 4u + nbt * (K + K / 8u) : nbt * K * 4u);
     a.stage_off = stage_off;
     a.stage_bytes = align128u(rt * stride);
     if (budget < stage_off + 2u * a.stage_bytes) return false;

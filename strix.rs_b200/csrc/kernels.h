@@ -24,6 +24,7 @@ struct GemvMat {
     float *y;          // output, one float per resident row
     const float *res;  // optional residual added to the output (y = W x + res); may alias y
     uint32_t rows;
+    uint32_t ystride;  // floats between the outputs (and residuals) of consecutive activation rows
     uint32_t tile0;  // index of this matrix's first tile in the launch-wide tile list
 };
 
@@ -33,6 +34,8 @@ struct GemvArgs {
     RowLayout L;
     const float *a;  // activation (or gate) vector, in_dim floats
     const float *b;  // norm weight (RMSNORM) or up vector (SWIGLU/GEGLU); unused for NONE
+    uint32_t nbatch;             // activation rows that share the weights (1 = plain GEMV)
+    uint32_t a_stride, b_stride;  // floats between consecutive activation rows of a / b (0 = shared)
     float eps;
     int pre;  // STRIX_PRE_*
     int act;  // STRIX_ACT_*

@@ -227,3 +227,25 @@ def test_gemv_dev_prologues_and_fused_weights(accel, orc, synth, pkg):
             assert rel_l2(y.cpu().numpy(), orc.qmatmul(n_cpu, w_, synth.Q4_0, hidden, n_)) <= tol
         assert rel_l2(yd.cpu().numpy(), orc.qmatmul(orc.swiglu(gate, up), wd, synth.Q4_0, ffn, hidden)) <= tol
         assert rel_l2(yg.cpu().numpy(), orc.qmatmul(orc.geglu(gate, up), wd, synth.Q4_0, ffn, hidden)) <= tol
+
+
+# ------------------------------------------------------------------ batched rows (speculative verify)
+@pytest.mark.parametrize("ty,out_dim,in_dim", [(2, 257, 3840), (2, 100, 15360), (8, 64, 2560), (14, 33, 3840), (2, 9, 64)])
+@pytest.mark.parametrize("b", [1, 2, 4, 8])
+def test_gemv_rows_matches_oracle(accel, orc, synth, pkg, ty, out_dim, in_dim, b):
+    w = synth.quant(ty, 33, "rows", out_dim, in_dim)
+    xs = synth.normal(33, "rows.x", b, in_dim)
+    key = "rows.%d.%d.%d" % (ty, out_dim, in_dim)
+    assert uploader(accel, synth, ty)(key, w, in_dim, out_dim)
+    want = orc.qmatmul_batch(xs, b, w, ty, in_dim, out_dim)
+    got = accel.gemv_rows(key, xs, b)
+    assert got.shape == (b, out_dim)
+    assert rel_l2(got, want) <= REL_L2_TOL
+    for t in range(b):      # each activation row on its own, so that a swapped row cannot hide
+        assert rel_l2(got[t], want[t]) <= REL_L2_TOL
+    xq, xd, _ = orc.xquant8(xs)
+    want_i = orc.idot_gemm(w, ty, xq, xd, b, in_dim, out_dim)
+    got_i = accel.gemv_rows(key, xs, b, act=pkg.ACT_Q8DOT)
+    for t in range(b):
+        assert rel_l2(got_i[t], want_i[t]) <= REL_L2_TOL
+    assert accel.device_status() == 0
