@@ -202,6 +202,65 @@ def decode_chain_extra(pkg, synth, torch, device, stream):
     return out
 
 
+def verify_rows_extra(pkg, synth, torch, device, stream):
+    """configs[4]: speculative-verify batched GEMV at Gemma-3-12B-class shapes (48 layers, hidden 3840,
+    q 4096, kv 2048, ffn 15360, Q4_0), b in {1,2,4,8} activation rows; 6.05 GB of weights per step."""
+    hidden, qdim, kvdim, ffn, n_layers = 3840, 4096, 2048, 15360, 48
+    acc = pkg.CudaWeightAccel(device)
+    out = {"per_b": []}
+    try:
+        shapes = {"q": (qdim, hidden), "k": (kvdim, hidden), "v": (kvdim, hidden), "o": (hidden, qdim),
+                  "gate": (ffn, hidden), "up": (ffn, hidden), "down": (hidden, ffn)}
+        base = {nm: make_weight(synth, Q4_0, k, n, 4, "vr." + nm) for nm, (n, k) in shapes.items()}
+        nbytes = 0
+        for il in range(n_layers):
+            for nm, (n, k) in shapes.items():
+                assert acc.upload_q4_0("L%d.%s" % (il, nm), base[nm], k, n)
+                nbytes += n * (k // 32) * 18
+        dev = torch.device("cuda", device)
+        for b in (1, 2, 4, 8):
+            xh = torch.randn(b, hidden, device=dev)
+            xq_ = torch.randn(b, qdim, device=dev)
+            xf = torch.randn(b, ffn, device=dev)
+            yq, yk, yv = (torch.empty(b, n, device=dev) for n in (qdim, kvdim, kvdim))
+            yo, yd = torch.empty(b, hidden, device=dev), torch.empty(b, hidden, device=dev)
+            yg, yu = torch.empty(b, ffn, device=dev), torch.empty(b, ffn, device=dev)
+
+            def step(s):
+                for il in range(n_layers):
+                    p = "L%d." % il
+                    acc.gemv_rows_dev([p + "q", p + "k", p + "v"], xh.data_ptr(), b,
+                                      [yq.data_ptr(), yk.data_ptr(), yv.data_ptr()], act=pkg.ACT_Q8DOT, stream=s)
+                    acc.gemv_rows_dev([p + "o"], xq_.data_ptr(), b, [yo.data_ptr()], act=pkg.ACT_Q8DOT, stream=s)
+                    acc.gemv_rows_dev([p + "gate", p + "up"], xh.data_ptr(), b, [yg.data_ptr(), yu.data_ptr()],
+                                      act=pkg.ACT_Q8DOT, stream=s)
+                    acc.gemv_rows_dev([p + "down"], xf.data_ptr(), b, [yd.data_ptr()], act=pkg.ACT_Q8DOT, stream=s)
+
+            with torch.cuda.stream(stream):
+                s = stream.cuda_stream
+                step(s)
+                torch.cuda.synchronize()
+                g = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(g, stream=stream):
+                    step(s)
+                g.replay()
+                torch.cuda.synchronize()
+                a, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                reps = 5
+                a.record()
+                for _ in range(reps):
+                    g.replay()
+                e.record()
+                torch.cuda.synchronize()
+                ms = a.elapsed_time(e) / reps
+            out["per_b"].append({"b": b, "ms_per_step": round(ms, 4), "gbs": round(nbytes / ms / 1e6, 1)})
+        out["bytes_per_step"] = nbytes
+        out["note"] = "int8-dot activations; projections only (4 launches per layer), weights streamed once per step"
+    finally:
+        acc.close()
+    return out
+
+
 def run_reference(args):
     """--impl reference: the reference's CPU implementation of the path (oracle port), all host
     threads, each step a bounded row sample of the same six GEMVs."""
@@ -450,6 +509,7 @@ def main():
                                                 "tops": round(2.0 * m * n * k / us / 1e6, 1)})
                     del xg, yg
         extras["decode_chain"] = decode_chain_extra(pkg, synth, torch, local, stream)
+        extras["verify_rows"] = verify_rows_extra(pkg, synth, torch, local, stream)
         if acc.device_status() != 0:
             raise SystemExit("device status word is non-zero after the extras")
 

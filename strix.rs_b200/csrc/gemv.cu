@@ -344,7 +344,9 @@ __device__ __forceinline__ TileRef tile_ref(const GemvArgs &A, uint32_t t) {
 //   ...  stages    n_stages x stage_bytes, 128-byte aligned
 constexpr uint32_t SMEM_PART_OFF = 512;
 
-template <int FMT, int ACT, int NCH, int RB>
+// MB = true: A.nbatch activation rows share one pass over the weights (speculative verify);
+// MB = false compiles the batch loops away and keeps the x registers loop-invariant.
+template <int FMT, int ACT, int NCH, int RB, bool MB>
 __global__ void __launch_bounds__((gemv_warps(ACT) + 1) * 32, 1) gemv_kernel(const __grid_constant__ GemvArgs A) {
     extern __shared__ __align__(128) uint8_t smem[];
     uint64_t *full = reinterpret_cast<uint64_t *>(smem);
@@ -413,7 +415,7 @@ __global__ void __launch_bounds__((gemv_warps(ACT) + 1) * 32, 1) gemv_kernel(con
     const uint32_t ct = n_cons * 32u;  // consumer threads = tid < ct
     // f32 form: xs[B][K].  integer-dot form: xs[K] (staging, reused per activation row), then
     // xq[B][K] int8 codes and sd[B][K/32] block scales.   B = A.nbatch activation rows share the weights.
-    const uint32_t B = A.nbatch, K = L.in_dim;
+    const uint32_t B = MB ? A.nbatch : 1u, K = L.in_dim;
     float *xs0 = reinterpret_cast<float *>(smem + A.x_off);
     int8_t *xq0 = reinterpret_cast<int8_t *>(smem + A.x_off + K * 4u);
     float *sd0 = reinterpret_cast<float *>(smem + A.x_off + K * 4u + B * K);
@@ -683,10 +685,16 @@ bool gemv_plan(GemvArgs &a, int num_sms, size_t smem_optin) {
 template <int FMT, int ACT, int NCH>
 static cudaError_t launch_t(const GemvArgs &a, cudaStream_t stream) {
     const uint32_t threads = (a.wc * a.slots + 1u) * 32u;  // consumer warps + one producer warp
-    if (a.rb == 4)
-        gemv_kernel<FMT, ACT, NCH, 4><<<a.grid, threads, a.smem_bytes, stream>>>(a);
-    else
-        gemv_kernel<FMT, ACT, NCH, 2><<<a.grid, threads, a.smem_bytes, stream>>>(a);
+    if (a.nbatch > 1) {
+        if (a.rb == 4)
+            gemv_kernel<FMT, ACT, NCH, 4, true><<<a.grid, threads, a.smem_bytes, stream>>>(a);
+        else
+            gemv_kernel<FMT, ACT, NCH, 2, true><<<a.grid, threads, a.smem_bytes, stream>>>(a);
+    } else if (a.rb == 4) {
+        gemv_kernel<FMT, ACT, NCH, 4, false><<<a.grid, threads, a.smem_bytes, stream>>>(a);
+    } else {
+        gemv_kernel<FMT, ACT, NCH, 2, false><<<a.grid, threads, a.smem_bytes, stream>>>(a);
+    }
     return cudaGetLastError();
 }
 
@@ -730,9 +738,14 @@ cudaError_t launch_gemv(const GemvArgs &a, cudaStream_t stream) {
 
 template <int FMT, int ACT, int NCH>
 static cudaError_t optin_one(size_t bytes) {
-    cudaError_t e = cudaFuncSetAttribute(gemv_kernel<FMT, ACT, NCH, 4>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes);
-    if (e != cudaSuccess) return e;
-    return cudaFuncSetAttribute(gemv_kernel<FMT, ACT, NCH, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes);
+    cudaError_t e = cudaSuccess;
+#define STRIX_ATTR(RB_, MB_)                                                                                      \
+    if (e == cudaSuccess)                                                                                         \
+        e = cudaFuncSetAttribute(gemv_kernel<FMT, ACT, NCH, RB_, MB_>, cudaFuncAttributeMaxDynamicSharedMemorySize, \
+                                 (int)bytes);
+    STRIX_ATTR(4, false) STRIX_ATTR(2, false) STRIX_ATTR(4, true) STRIX_ATTR(2, true)
+#undef STRIX_ATTR
+    return e;
 }
 template <int FMT>
 static cudaError_t optin_fmt(size_t b) {
