@@ -456,11 +456,20 @@ def main():
                 detail.append({"weight": it["key"], "us": round(us, 2),
                                "gbs": round(it["bytes"] * shard_frac / us / 1e3, 1),
                                "l2_resident": it["bytes"] * shard_frac < 126e6})
-        big = [d for d, it in zip(detail, items) if it["ty"] == Q8_0 and it["n"] == 151936][0]
-        roof = {"bound": "hbm", "achieved": big["gbs"], "peak": peak, "unit": "GB/s",
-                "frac": round(big["gbs"] / peak, 4), "traffic": None,
-                "kernel": "gemv_kernel<Q8_0,F32> on q8_0.2560.151936 (%s peak; traffic from ncu: see profiles/)" % peak_src,
-                "frac_of_8tbs": round(big["gbs"] / 8000.0, 4)}
+        # the kernel with the largest share of the timed step is the Q6_K f32 instantiation (58 % in the
+        # ncu launch list, profiles/); its roofline is taken on its largest launch. DRAM traffic per
+        # launch from the ncu capture of a 65536-row case, scaled by rows (traffic grows with rows).
+        dom = [d for d, it in zip(detail, items) if it["ty"] == Q6_K and it["n"] == 151936][0]
+        sec = [d for d, it in zip(detail, items) if it["ty"] == Q8_0 and it["n"] == 151936][0]
+        roof = {"bound": "hbm", "achieved": dom["gbs"], "peak": peak, "unit": "GB/s",
+                "frac": round(dom["gbs"] / peak, 4),
+                "traffic": int(142.88e6 * 151936 / 65536) if world == 1 else None,
+                "kernel": "gemv_kernel<Q6_K,F32> on q6_k.2560.151936, 319,683,584 algorithmic bytes per launch "
+                          "(of %s peak)" % peak_src,
+                "frac_of_8tbs": round(dom["gbs"] / 8000.0, 4),
+                "second_kernel": {"kernel": "gemv_kernel<Q8_0,F32> on q8_0.2560.151936, 413,883,904 bytes",
+                                  "achieved": sec["gbs"], "frac": round(sec["gbs"] / peak, 4),
+                                  "traffic": int(182.34e6 * 151936 / 65536) if world == 1 else None}}
 
     # ---- extras on rank 0 at N=1: the integer-dot GEMV variant and the W8A8 GEMM (configs[2]) ----
     extras = None
