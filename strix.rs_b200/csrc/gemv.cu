@@ -162,35 +162,27 @@ __device__ __forceinline__ void set_unit_x(LaneX<FMT, ACT, NCH> &X, int c, const
 
 __device__ __forceinline__ int sum4(uint32_t w) { return dp4a_ss(w, 0x01010101u, 0); }
 
-// Integer-dot form: copy unit u's 16 int8 codes (as 4 words in the decoder's order), the block
-// scale(s) and bias * sum(codes) from the CTA's quantised activation in shared memory.
+// Integer-dot form: read unit u's 16 int8 codes (4 words in the decoder's order: the CTA's
+// quantised activation is stored unit-major, so this is one 16-byte load), the block scale(s),
+// and bias * sum(codes).
 template <int FMT, int ACT, int NCH>
-__device__ __forceinline__ void load_unit_q(LaneX<FMT, ACT, NCH> &X, int c, uint32_t u, bool valid, const int8_t *xq,
+__device__ __forceinline__ void load_unit_q(LaneX<FMT, ACT, NCH> &X, int c, uint32_t u, const uint4 *xq4,
                                             const float *sd) {
+    const uint4 w = xq4[u];
+    X.q[c][0] = w.x; X.q[c][1] = w.y; X.q[c][2] = w.z; X.q[c][3] = w.w;
     if (FMT == FMT_Q8_0) {
-        const uint4 w = *reinterpret_cast<const uint4 *>(xq + 16u * u);
-        X.q[c][0] = w.x; X.q[c][1] = w.y; X.q[c][2] = w.z; X.q[c][3] = w.w;
         X.d[c][0] = sd[u >> 1];
         X.qs[c][0] = 128 * (sum4(w.x) + sum4(w.y) + sum4(w.z) + sum4(w.w));  // resident codes are q + 128
     } else if (FMT == FMT_Q4_0) {
-        const uint32_t e = 32u * (u >> 1) + 8u * (u & 1u);
-        const uint2 lo = *reinterpret_cast<const uint2 *>(xq + e), hi = *reinterpret_cast<const uint2 *>(xq + e + 16u);
-        X.q[c][0] = lo.x; X.q[c][1] = lo.y; X.q[c][2] = hi.x; X.q[c][3] = hi.y;
         X.d[c][0] = sd[u >> 1];
-        X.qs[c][0] = 8 * (sum4(lo.x) + sum4(lo.y) + sum4(hi.x) + sum4(hi.y));  // nibbles carry +8
+        X.qs[c][0] = 8 * (sum4(w.x) + sum4(w.y) + sum4(w.z) + sum4(w.w));  // nibbles carry +8
     } else {
+        const uint32_t blk0 = unit_elem<FMT>(u, 0) >> 5;  // group k of the unit lies in block blk0 + k
 #pragma unroll
         for (uint32_t k = 0; k < 4; k++) {
-            const uint32_t e = unit_elem<FMT>(u, k);
-            const uint32_t w = *reinterpret_cast<const uint32_t *>(xq + e);
-            X.q[c][k] = w;
-            X.d[c][k] = sd[e >> 5];
-            X.qs[c][k] = 32 * sum4(w);  // 6-bit codes carry +32
+            X.d[c][k] = sd[blk0 + k];
+            X.qs[c][k] = 32 * sum4(X.q[c][k]);  // 6-bit codes carry +32
         }
-    }
-    if (!valid) {
-#pragma unroll
-        for (int k = 0; k < 4; k++) X.q[c][k] = 0;
     }
 }
 
@@ -291,14 +283,17 @@ __device__ __forceinline__ float unit_dot(uint32_t rb, const LaneX<FMT, ACT, NCH
 // then a plain butterfly over the remaining lane bits. On return lane (32/RB) k holds the sum of row k.
 template <int RB>
 __device__ __forceinline__ float batch_reduce(const float (&v)[RB], uint32_t lane) {
-    static_assert(RB == 2 || RB == 4, "batch_reduce is written for 2 or 4 rows");
+    static_assert(RB == 1 || RB == 2 || RB == 4, "batch_reduce is written for 1, 2 or 4 rows");
     const bool up16 = (lane & 16u) != 0u;
     float k;
-    if (RB == 4) {
+    if constexpr (RB == 1) {
+        k = v[0] + __shfl_xor_sync(0xffffffffu, v[0], 16);
+        k += __shfl_xor_sync(0xffffffffu, k, 8);
+    } else if constexpr (RB == 4) {
         const bool up8 = (lane & 8u) != 0u;
         // after this step lanes 0-15 hold rows 0,1 and lanes 16-31 hold rows 2,3
         float k0 = up16 ? v[2] : v[0], s0 = up16 ? v[0] : v[2];
-        float k1 = up16 ? v[RB - 1] : v[1], s1 = up16 ? v[1] : v[RB - 1];
+        float k1 = up16 ? v[3] : v[1], s1 = up16 ? v[1] : v[3];
         k0 += __shfl_xor_sync(0xffffffffu, s0, 16);
         k1 += __shfl_xor_sync(0xffffffffu, s1, 16);
         // lanes with bit 3 clear keep the even row of their pair, the others the odd one
@@ -306,8 +301,8 @@ __device__ __forceinline__ float batch_reduce(const float (&v)[RB], uint32_t lan
         const float sx = up8 ? k0 : k1;
         k += __shfl_xor_sync(0xffffffffu, sx, 8);
     } else {
-        k = up16 ? v[1] : v[0];
-        const float sx = up16 ? v[0] : v[1];
+        k = up16 ? v[RB - 1] : v[0];
+        const float sx = up16 ? v[0] : v[RB - 1];
         k += __shfl_xor_sync(0xffffffffu, sx, 16);
         k += __shfl_xor_sync(0xffffffffu, k, 8);
     }
@@ -339,30 +334,44 @@ __device__ __forceinline__ TileRef tile_ref(const GemvArgs &A, uint32_t t) {
 //   64   empty[8]  mbarriers: every consumer warp is done with it   (one arrival per consumer warp)
 //   128  ctl[0]    abort flag (a bounded wait ran out)
 //   256  red[32]   block reduction scratch (RMSNORM prologue)
-//   512  part      per slot: 2 x RB x wc partial sums
-//   ...  x         the activations: B x K f32, or K f32 staging + B x (K int8 codes + K/32 f32 block scales)
+//   512  x         the activations: B x K f32, or K f32 staging + B x (K int8 codes + K/32 f32 block scales)
 //   ...  stages    n_stages x stage_bytes, 128-byte aligned
-constexpr uint32_t SMEM_PART_OFF = 512;
+constexpr uint32_t SMEM_X_OFF = 512;
 
-// MB = true: A.nbatch activation rows share one pass over the weights (speculative verify);
-// MB = false compiles the batch loops away and keeps the x registers loop-invariant.
-template <int FMT, int ACT, int NCH, int RB, bool MB>
-__global__ void __launch_bounds__((gemv_warps(ACT) + 1) * 32, 1) gemv_kernel(const __grid_constant__ GemvArgs A) {
+// Inverse of unit_elem for groups of four elements: natural float4 index e4 -> (unit, group).
+template <int FMT>
+__device__ __forceinline__ void elem4_to_unit(uint32_t e4, uint32_t &u, uint32_t &g) {
+    if (FMT == FMT_Q8_0) {
+        u = e4 >> 2;
+        g = e4 & 3u;
+    } else if (FMT == FMT_Q4_0) {
+        const uint32_t e = e4 * 4u, w = e & 31u;
+        u = 2u * (e >> 5) + ((w & 15u) >> 3);
+        g = 2u * (w >> 4) + ((w & 7u) >> 2);
+    } else {
+        const uint32_t e = e4 * 4u;
+        u = 16u * (e >> 8) + 8u * ((e >> 7) & 1u) + ((e & 31u) >> 2);
+        g = (e >> 5) & 3u;
+    }
+}
+
+template <int FMT, int ACT, int RB>
+__global__ void __launch_bounds__((GEMV_WARPS + 1) * 32, 1) gemv_kernel(const __grid_constant__ GemvArgs A) {
     extern __shared__ __align__(128) uint8_t smem[];
+    if (A.debug & 2u) return;  // measurement only: cost of an empty launch of this shape
     uint64_t *full = reinterpret_cast<uint64_t *>(smem);
     uint64_t *empty = reinterpret_cast<uint64_t *>(smem + 64);
     volatile uint32_t *ctl = reinterpret_cast<volatile uint32_t *>(smem + 128);
     float *red = reinterpret_cast<float *>(smem + 256);
-    float *part = reinterpret_cast<float *>(smem + SMEM_PART_OFF);
     uint8_t *stages = smem + A.stage_off;
 
-    if (A.debug & 2u) return;  // measurement only: cost of an empty launch of this shape
     const uint32_t tid = threadIdx.x, lane = tid & 31u, warp = tid >> 5;
-    const uint32_t n_cons = A.wc * A.slots;  // consumer warps; warp n_cons is the producer
+    const uint32_t n_cons = A.slots;  // consumer warps; warp n_cons is the producer
     const uint32_t S = A.n_stages, grid = gridDim.x, bid = blockIdx.x;
     const uint32_t my_n = (A.n_tiles > bid) ? (A.n_tiles - bid + grid - 1) / grid : 0;
     const RowLayout L = A.L;
-    const uint32_t U = L.in_dim / 16u;
+    const uint32_t U = L.in_dim / 16u, K = L.in_dim, B = A.nbatch;
+    const uint32_t C = (U + 31u) / 32u;  // runs of 32 units along a row
 
     if (tid == 0) {
         for (uint32_t s = 0; s < S; s++) {
@@ -373,23 +382,13 @@ __global__ void __launch_bounds__((gemv_warps(ACT) + 1) * 32, 1) gemv_kernel(con
         mbar_fence_init();
     }
     __syncthreads();
-    // The first S tile copies start before the activation prologue and overlap it.
-    if (warp == n_cons && lane == 0) {
-        const uint32_t n0 = min(S, my_n);
-        for (uint32_t i = 0; i < n0; i++) {
-            TileRef t = tile_ref(A, bid + i * grid);
-            const uint32_t bytes = t.rows * L.row_stride;
-            mbar_arrive_expect_tx(&full[i], bytes);
-            bulk_g2s(stages + (uint64_t)i * A.stage_bytes, t.src, bytes, &full[i]);
-        }
-    }
-
     if (warp == n_cons) {
-        // ---- producer: refill a stage as soon as every consumer warp has released it ----
+        // ---- producer: start the first S tile copies at once (they overlap the activation prologue),
+        //      then refill a stage as soon as every consumer warp has released it ----
         if (lane == 0) {
-            for (uint32_t i = S; i < my_n; i++) {
+            for (uint32_t i = 0; i < my_n; i++) {
                 const uint32_t s = i % S;
-                if (!ctl[0] && !mbar_wait_bounded(&empty[s], ((i / S) - 1u) & 1u, A.status)) ctl[0] = 1;
+                if (i >= S && !ctl[0] && !mbar_wait_bounded(&empty[s], ((i / S) - 1u) & 1u, A.status)) ctl[0] = 1;
                 TileRef t = tile_ref(A, bid + i * grid);
                 const uint32_t bytes = t.rows * L.row_stride;
                 mbar_arrive_expect_tx(&full[s], bytes);
@@ -407,15 +406,14 @@ __global__ void __launch_bounds__((gemv_warps(ACT) + 1) * 32, 1) gemv_kernel(con
 
     // ---- consumers: activation prologue ----
     // The activation (after the optional RMSNorm / SwiGLU / GeGLU) is produced ONCE per CTA,
-    // cooperatively, into shared memory; for the integer-dot form it is then quantised per 32
-    // elements, one warp per block. Each lane finally copies the values of the units it owns into
-    // registers, where they stay for the whole kernel. (Having every warp rebuild all of x on its
-    // own cost 5-14 us per launch; this costs about one global-load latency.)
-    const uint32_t cw = warp % A.wc, slot = warp / A.wc;
+    // cooperatively, into shared memory, and stays there: a lane re-reads the 16 values of a unit
+    // for every batch of rows (one conflict-free 16-byte load per group of four; the f32 form is
+    // stored unit-major for that). Keeping x out of the register file is what lets 24 consumer
+    // warps run per SM; the extra shared-memory reads are shared by the RB rows of a batch.
+    //   f32 form:          xs4[b][g][U]   float4 = group g of unit u of activation row b
+    //   integer-dot form:  xs[K] f32 staging (natural order, reused per activation row),
+    //                      xq[b][U][16] int8 codes (unit-major), sd[b][K/32] block scales
     const uint32_t ct = n_cons * 32u;  // consumer threads = tid < ct
-    // f32 form: xs[B][K].  integer-dot form: xs[K] (staging, reused per activation row), then
-    // xq[B][K] int8 codes and sd[B][K/32] block scales.   B = A.nbatch activation rows share the weights.
-    const uint32_t B = MB ? A.nbatch : 1u, K = L.in_dim;
     float *xs0 = reinterpret_cast<float *>(smem + A.x_off);
     int8_t *xq0 = reinterpret_cast<int8_t *>(smem + A.x_off + K * 4u);
     float *sd0 = reinterpret_cast<float *>(smem + A.x_off + K * 4u + B * K);
@@ -424,13 +422,11 @@ __global__ void __launch_bounds__((gemv_warps(ACT) + 1) * 32, 1) gemv_kernel(con
         const float *Aa = A.a + (size_t)bi * A.a_stride;
         const float *Ab = A.b ? A.b + (size_t)bi * A.b_stride : nullptr;
         float *xs = (ACT == STRIX_ACT_F32) ? xs0 + bi * K : xs0;
-        int8_t *xq = xq0 + bi * K;
-        float *sd = sd0 + bi * (K / 32u);
         float scale = 1.0f;
         if (A.pre == STRIX_PRE_RMSNORM) {
             // rmsnorm (crates/strix-backend-cpu/src/qwen3.rs:107-114): x * (1/sqrt(mean(x^2)+eps)) * w
             float ss = 0.f;
-            for (uint32_t e4 = tid; e4 < L.in_dim / 4u; e4 += ct) {
+            for (uint32_t e4 = tid; e4 < K / 4u; e4 += ct) {
                 const float4 t = __ldg(reinterpret_cast<const float4 *>(Aa) + e4);
                 ss = fmaf(t.x, t.x, ss); ss = fmaf(t.y, t.y, ss); ss = fmaf(t.z, t.z, ss); ss = fmaf(t.w, t.w, ss);
             }
@@ -439,10 +435,10 @@ __global__ void __launch_bounds__((gemv_warps(ACT) + 1) * 32, 1) gemv_kernel(con
             STRIX_CONS_BAR();
             float tot = 0.f;
             for (uint32_t w = 0; w < n_cons; w++) tot += red[w];
-            scale = 1.0f / sqrtf(tot / (float)L.in_dim + A.eps);
+            scale = 1.0f / sqrtf(tot / (float)K + A.eps);
             if (B > 1) STRIX_CONS_BAR();  // red[] is rewritten for the next activation row
         }
-        for (uint32_t e4 = tid; e4 < L.in_dim / 4u; e4 += ct) {
+        for (uint32_t e4 = tid; e4 < K / 4u; e4 += ct) {
             float4 a4 = __ldg(reinterpret_cast<const float4 *>(Aa) + e4);
             if (A.pre != STRIX_PRE_NONE) {
                 const float4 b4 = __ldg(reinterpret_cast<const float4 *>(Ab) + e4);
@@ -457,25 +453,34 @@ __global__ void __launch_bounds__((gemv_warps(ACT) + 1) * 32, 1) gemv_kernel(con
                     a4.z = gelu_tanh_f(a4.z) * b4.z; a4.w = gelu_tanh_f(a4.w) * b4.w;
                 }
             }
-            reinterpret_cast<float4 *>(xs)[e4] = a4;
+            if (ACT == STRIX_ACT_F32) {
+                uint32_t u, g;
+                elem4_to_unit<FMT>(e4, u, g);
+                reinterpret_cast<float4 *>(xs)[g * U + u] = a4;
+            } else {
+                reinterpret_cast<float4 *>(xs)[e4] = a4;
+            }
         }
         STRIX_CONS_BAR();
         if (ACT == STRIX_ACT_Q8DOT) {
             // per-32 quantiser (xquant8, kernels.rs:864-876): d = amax/127, inv = d>0 ? 1/d : 0,
             // q = clamp(rintf(x*inv)); eight lanes per block (four elements each), four blocks per warp pass
+            int8_t *xq = xq0 + bi * K;
+            float *sd = sd0 + bi * (K / 32u);
             const uint32_t sub = lane >> 3, l8 = lane & 7u;
-            for (uint32_t blk = warp * 4u + sub; blk < L.in_dim / 32u; blk += n_cons * 4u) {
+            for (uint32_t blk = warp * 4u + sub; blk < K / 32u; blk += n_cons * 4u) {
                 const float4 v = *reinterpret_cast<const float4 *>(xs + blk * 32u + l8 * 4u);
                 float amax = fmaxf(fmaxf(fabsf(v.x), fabsf(v.y)), fmaxf(fabsf(v.z), fabsf(v.w)));
-                // (the loop bound is uniform within each group of eight lanes; all 32 lanes run the same
-                // number of passes only when the block count is a multiple of 4, hence the masks)
+                // (the trip count is uniform within each group of eight lanes only, hence the masks)
                 const uint32_t mask = 0xffu << (sub * 8u);
                 amax = fmaxf(amax, __shfl_xor_sync(mask, amax, 1));
                 amax = fmaxf(amax, __shfl_xor_sync(mask, amax, 2));
                 amax = fmaxf(amax, __shfl_xor_sync(mask, amax, 4));
                 const float d = amax / 127.0f;
                 const float inv = d > 0.f ? 1.0f / d : 0.f;
-                *reinterpret_cast<uint32_t *>(xq + blk * 32u + l8 * 4u) =
+                uint32_t qu, qg;
+                elem4_to_unit<FMT>(blk * 8u + l8, qu, qg);
+                reinterpret_cast<uint32_t *>(xq)[qu * 4u + qg] =
                     pack4(quant1(v.x, inv), quant1(v.y, inv), quant1(v.z, inv), quant1(v.w, inv));
                 if (l8 == 0) sd[blk] = d;
             }
@@ -483,61 +488,31 @@ __global__ void __launch_bounds__((gemv_warps(ACT) + 1) * 32, 1) gemv_kernel(con
         }
     }
 #undef STRIX_CONS_BAR
-    // this lane's units: offsets into a resident row, and the x values, in registers from here on
-    LaneX<FMT, ACT, NCH> X;
-    const uint32_t u0 = cw * (uint32_t)NCH * 32u + lane;  // warp cw owns runs cw*NCH .. cw*NCH+NCH-1
+    if (A.debug & 4u) return;  // measurement only: stop after the activation prologue
+
+    // byte offsets (within a resident row) of the fields of this lane's unit in run 0
+    LaneX<FMT, ACT, 1> X;
+    uint32_t b_w, b_s, b_hh = 0, b_sc = 0;
     X.off_hh = X.off_sc = X.sel_a = X.sel_b = 0;
+    X.valid = 1;
     if (FMT == FMT_Q8_0) {
-        X.off_w = u0 * 16u;
-        X.off_s = L.off_d + 2u * (u0 >> 1);
+        b_w = lane * 16u;
+        b_s = L.off_d + 2u * (lane >> 1);
     } else if (FMT == FMT_Q4_0) {
-        X.off_w = u0 * 8u;
-        X.off_s = L.off_d + 2u * (u0 >> 1);
+        b_w = lane * 8u;
+        b_s = L.off_d + 2u * (lane >> 1);
     } else {
-        const uint32_t sb = u0 >> 4, r = u0 & 15u, h = r >> 3, c4 = r & 7u;
-        X.off_w = sb * 128u + h * 64u + c4 * 4u;
-        X.off_hh = L.off_qh + sb * 64u + h * 32u + c4 * 4u;
-        X.off_sc = L.off_sc + sb * 16u + h * 8u;
-        X.off_s = L.off_d + 2u * sb;
+        const uint32_t sb = lane >> 4, r = lane & 15u, h = r >> 3, c4 = r & 7u;
+        b_w = sb * 128u + h * 64u + c4 * 4u;
+        b_hh = L.off_qh + sb * 64u + h * 32u + c4 * 4u;
+        b_sc = L.off_sc + sb * 16u + h * 8u;
+        b_s = L.off_d + 2u * sb;
         X.sel_a = sext_sel(c4 >> 2);         // sub-scale byte (c4>>2)     of a word: groups 0 and 2
         X.sel_b = sext_sel((c4 >> 2) + 2u);  // sub-scale byte (c4>>2) + 2 of a word: groups 1 and 3
     }
-    X.valid = 0;
-#pragma unroll
-    for (int c = 0; c < NCH; c++)
-        if (u0 + 32u * (uint32_t)c < U) X.valid |= 1u << c;
-    // copies activation row bi's values for this lane's units from shared memory into X
-    auto load_x = [&](uint32_t bi) {
-#pragma unroll
-        for (int c = 0; c < NCH; c++) {
-            const uint32_t u = u0 + 32u * (uint32_t)c;
-            const bool valid = u < U;
-            if (ACT == STRIX_ACT_F32) {
-                const float *xs = xs0 + bi * K;
-                float v[16];
-#pragma unroll
-                for (uint32_t g = 0; g < 4; g++) {
-                    const float4 a4 = valid ? *reinterpret_cast<const float4 *>(xs + unit_elem<FMT>(u, g))
-                                            : make_float4(0.f, 0.f, 0.f, 0.f);
-                    v[4 * g] = a4.x; v[4 * g + 1] = a4.y; v[4 * g + 2] = a4.z; v[4 * g + 3] = a4.w;
-                }
-                set_unit_x<FMT, ACT, NCH>(X, c, v);
-            } else {
-                load_unit_q<FMT, ACT, NCH>(X, c, valid ? u : 0u, valid, xq0 + bi * K, sd0 + bi * (K / 32u));
-            }
-        }
-    };
-    load_x(0);
 
-    // ---- stream the tiles. The wc warps of a slot meet on a named barrier per row batch; slots
-    //      run independently of one another, and nothing in the loop is CTA-wide. ----
-    if (A.debug & 4u) {  // measurement only: stop after the activation prologue (keeps X alive through a dummy store)
-        if (X.valid == 0xffffffffu) A.mat[0].y[0] = (float)X.off_w;
-        return;
-    }
-    float *pp = part + slot * (2u * RB * A.wc);
-    const uint32_t bar_id = 1u + slot, bar_n = A.wc * 32u;
-    uint32_t buf = 0;
+    // ---- stream the tiles: every consumer warp takes whole rows, RB at a time, round-robin ----
+    const uint32_t slot = warp;
     const uint32_t st0 = smem_u32(stages);
     const bool skip = (A.debug & 1u) != 0u;
     constexpr uint32_t LPR = 32u / RB;  // after batch_reduce lane LPR*k holds row k
@@ -545,50 +520,50 @@ __global__ void __launch_bounds__((gemv_warps(ACT) + 1) * 32, 1) gemv_kernel(con
     for (uint32_t i = 0; i < my_n; i++) {
         const uint32_t s = i % S;
         // once any wait has run out, nobody waits again: the loop runs to its end on whatever is in
-        // shared memory (barrier participation stays consistent) and the status word reports it
+        // shared memory and the status word reports it
         if (!ctl[0] && !mbar_wait_bounded(&full[s], (i / S) & 1u, A.status)) ctl[0] = 1;
         const TileRef t = tile_ref(A, bid + i * grid);
         const uint32_t st = st0 + s * A.stage_bytes;
+        // Row batches go round-robin over the warps, counted across this CTA's tiles, so that small
+        // tiles still keep every warp busy. Rows past the tile's end read whatever the stage still
+        // holds; their sums are dropped.
+        const uint32_t first = (slot + n_cons - (i * bpt) % n_cons) % n_cons;  // this warp's first batch in the tile
         for (uint32_t bi = 0; bi < B; bi++) {
-        if (B > 1) load_x(bi);  // weights stay in shared memory; only this lane's x values change
-        float *y = A.mat[t.mat].y + (size_t)bi * A.mat[t.mat].ystride + t.row0;
-        const float *res = A.mat[t.mat].res ? A.mat[t.mat].res + (size_t)bi * A.mat[t.mat].ystride + t.row0 : nullptr;
-        // Row batches go round-robin over the slots, counted across this CTA's tiles, so that small
-        // tiles (fewer batches than slots) still keep every slot busy. Rows past the tile's end read
-        // whatever the stage still holds; their sums are dropped.
-        const uint32_t first = (slot + A.slots - (i * bpt) % A.slots) % A.slots;  // this slot's first batch in the tile
-        for (uint32_t r0 = first * RB; r0 < t.rows && !skip; r0 += A.slots * RB) {
-            float acc[RB];
+            float *y = A.mat[t.mat].y + (size_t)bi * A.mat[t.mat].ystride + t.row0;
+            const float *res = A.mat[t.mat].res ? A.mat[t.mat].res + (size_t)bi * A.mat[t.mat].ystride + t.row0 : nullptr;
+            const float4 *xs4 = reinterpret_cast<const float4 *>(xs0 + bi * K);
+            const uint4 *xq4 = reinterpret_cast<const uint4 *>(xq0 + bi * K);
+            const float *sd = sd0 + bi * (K / 32u);
+            for (uint32_t r0 = first * RB; r0 < t.rows && !skip; r0 += n_cons * RB) {
+                float acc[RB];
 #pragma unroll
-            for (int j = 0; j < RB; j++) acc[j] = 0.f;
-            const uint32_t rb0 = st + r0 * L.row_stride;
+                for (int j = 0; j < RB; j++) acc[j] = 0.f;
+                const uint32_t rb0 = st + r0 * L.row_stride;
+                X.off_w = b_w; X.off_s = b_s; X.off_hh = b_hh; X.off_sc = b_sc;
+                for (uint32_t c = 0, u = lane; c < C; c++, u += 32u) {
+                    if (u < U) {
+                        if (ACT == STRIX_ACT_F32) {
+                            float v[16];
 #pragma unroll
-            for (int c = 0; c < NCH; c++) {
-                if (X.valid & (1u << c)) {
+                            for (uint32_t g = 0; g < 4; g++) {
+                                const float4 a4 = xs4[g * U + u];
+                                v[4 * g] = a4.x; v[4 * g + 1] = a4.y; v[4 * g + 2] = a4.z; v[4 * g + 3] = a4.w;
+                            }
+                            set_unit_x<FMT, ACT, 1>(X, 0, v);
+                        } else {
+                            load_unit_q<FMT, ACT, 1>(X, 0, u, xq4, sd);
+                        }
 #pragma unroll
-                    for (int j = 0; j < RB; j++)
-                        acc[j] += unit_dot<FMT, ACT, NCH>(rb0 + (uint32_t)j * L.row_stride, X, c);
+                        for (int j = 0; j < RB; j++)
+                            acc[j] += unit_dot<FMT, ACT, 1>(rb0 + (uint32_t)j * L.row_stride, X, 0);
+                    }
+                    X.off_w += Step<FMT>::w; X.off_s += Step<FMT>::s; X.off_hh += Step<FMT>::hh; X.off_sc += Step<FMT>::sc;
                 }
-            }
-            const float tot = batch_reduce<RB>(acc, lane);
-            if (A.wc == 1) {
+                const float tot = batch_reduce<RB>(acc, lane);
                 const uint32_t rr = r0 + lane / LPR;
                 if ((lane & (LPR - 1u)) == 0u && rr < t.rows) y[rr] = res ? tot + res[rr] : tot;
-            } else {
-                float *pb = pp + buf * (RB * A.wc);
-                if ((lane & (LPR - 1u)) == 0u) pb[(lane / LPR) * A.wc + cw] = tot;
-                __syncwarp();
-                asm volatile("bar.sync %0, %1;" ::"r"(bar_id), "r"(bar_n) : "memory");
-                if (cw == 0 && lane < RB && r0 + lane < t.rows) {
-                    // fixed summation order over the wc column owners: reproducible run to run
-                    float sum = 0.f;
-                    for (uint32_t k = 0; k < A.wc; k++) sum += pb[lane * A.wc + k];
-                    y[r0 + lane] = res ? sum + res[r0 + lane] : sum;
-                }
-                buf ^= 1u;  // the next batch writes the other buffer while warp cw==0 still reads this one
             }
         }
-        }  // activation rows
         __syncwarp();
         if (lane == 0) mbar_arrive(&empty[s]);  // this warp's reads of the stage are complete
     }
@@ -597,29 +572,10 @@ __global__ void __launch_bounds__((gemv_warps(ACT) + 1) * 32, 1) gemv_kernel(con
 // ------------------------------------------------------------------ host side
 static inline uint32_t align128u(uint32_t v) { return (v + 127u) & ~127u; }
 
-// Largest NCH (runs of 32 units per consumer warp) a kernel variant is built for: bounded by the
-// registers the x values need (16 per run as f32; as int8 6 per run, 12 for Q6_K).
-static inline uint32_t max_nch(int fmt, int act) { return (act == STRIX_ACT_F32 || fmt == FMT_Q6_K) ? 5u : 8u; }
-
 bool gemv_plan(GemvArgs &a, int num_sms, size_t smem_optin) {
     const uint32_t K = a.L.in_dim;
     if (K == 0 || K % 32 != 0) return false;
-    const uint32_t U = K / 16, C = (U + 31) / 32;
-    // wc warps x nch runs cover the C runs of a row; prefer the split that wastes the fewest
-    // warp-slots (runs past C, and consumer warps left over when wc does not divide the pool)
-    const uint32_t cap = max_nch(a.L.fmt, a.act);
-    uint32_t wc = 0, nch = 0;
-    double best = 1e30;
-    const uint32_t pool = (uint32_t)gemv_warps(a.act);
-    for (uint32_t w = (C + cap - 1) / cap; w <= pool && w <= C; w++) {
-        const uint32_t n = (C + w - 1) / w;
-        if (n > cap) continue;
-        const uint32_t sl = pool / w;
-        const double waste = ((double)(w * n) / C) * ((double)pool / (w * sl)) + 0.02 * w;
-        if (waste < best) { best = waste; wc = w; nch = n; }
-    }
-    if (wc == 0) return false;  // in_dim beyond what the consumer warps can hold in registers
-    const uint32_t slots = pool / wc;
+    const uint32_t pool = (uint32_t)GEMV_WARPS;
     const uint32_t stride = a.L.row_stride;
     const uint32_t budget = (uint32_t)smem_optin - 1024u;
 
@@ -631,9 +587,18 @@ bool gemv_plan(GemvArgs &a, int num_sms, size_t smem_optin) {
     // serial work per warp, not by the arrival of the first tile.)
     uint32_t target = 73728u;
     if (const char *e = getenv("STRIX_GEMV_TILE_BYTES")) target = (uint32_t)atoi(e);  // tuning knob
-    // A warp carries rb rows at once: four give more independent work per lane and fewer
-    // reductions per row; two when four rows of a long row would overshoot the tile size.
-    const uint32_t rb = (4u * stride <= target) ? 4u : 2u;
+    // A warp carries rb rows at once: four give more independent work per lane, fewer reductions
+    // per row and fewer re-reads of x from shared memory; fewer when there are not enough rows per
+    // SM to give every warp such a batch, or when rb long rows would overshoot the tile size.
+    uint64_t total_rows = 0;
+    for (int k = 0; k < a.nmat; k++) total_rows += a.mat[k].rows;
+    const uint64_t rows_per_sm = (total_rows + (uint64_t)num_sms - 1) / (uint64_t)num_sms;
+    uint32_t rb = 4u;
+    while (rb > 1u && (rb * stride > target || rows_per_sm < (uint64_t)pool * rb)) rb >>= 1;
+    if (const char *e = getenv("STRIX_GEMV_RB")) {  // tuning knob
+        const uint32_t v = (uint32_t)atoi(e);
+        if ((v == 1 || v == 2 || v == 4) && v * stride <= target) rb = v;
+    }
     a.rb = rb;
     uint32_t jmax = target / (rb * stride);
     if (jmax < 1) jmax = 1;
@@ -656,10 +621,10 @@ bool gemv_plan(GemvArgs &a, int num_sms, size_t smem_optin) {
     }
     a.n_tiles = tile;
     a.rows_per_tile = rt;
-    a.wc = wc;
-    a.slots = slots;
-    a.nch = nch;
-    a.x_off = SMEM_PART_OFF + align128u(slots * 2u * rb * wc * 4u);
+    a.wc = 1;
+    a.slots = pool;
+    a.nch = 0;
+    a.x_off = SMEM_X_OFF;
     // the CTA's activation: K f32 values; for the integer-dot form also K int8 codes and K/32 scales
     const uint32_t nbt = a.nbatch ? a.nbatch : 1u;
     a.nbatch = nbt;
@@ -682,49 +647,22 @@ bool gemv_plan(GemvArgs &a, int num_sms, size_t smem_optin) {
     return true;
 }
 
-template <int FMT, int ACT, int NCH>
+template <int FMT, int ACT>
 static cudaError_t launch_t(const GemvArgs &a, cudaStream_t stream) {
-    const uint32_t threads = (a.wc * a.slots + 1u) * 32u;  // consumer warps + one producer warp
-    if (a.nbatch > 1) {
-        if (a.rb == 4)
-            gemv_kernel<FMT, ACT, NCH, 4, true><<<a.grid, threads, a.smem_bytes, stream>>>(a);
-        else
-            gemv_kernel<FMT, ACT, NCH, 2, true><<<a.grid, threads, a.smem_bytes, stream>>>(a);
-    } else if (a.rb == 4) {
-        gemv_kernel<FMT, ACT, NCH, 4, false><<<a.grid, threads, a.smem_bytes, stream>>>(a);
-    } else {
-        gemv_kernel<FMT, ACT, NCH, 2, false><<<a.grid, threads, a.smem_bytes, stream>>>(a);
-    }
+    const uint32_t threads = (a.slots + 1u) * 32u;  // consumer warps + one producer warp
+    if (a.rb == 4)
+        gemv_kernel<FMT, ACT, 4><<<a.grid, threads, a.smem_bytes, stream>>>(a);
+    else if (a.rb == 2)
+        gemv_kernel<FMT, ACT, 2><<<a.grid, threads, a.smem_bytes, stream>>>(a);
+    else
+        gemv_kernel<FMT, ACT, 1><<<a.grid, threads, a.smem_bytes, stream>>>(a);
     return cudaGetLastError();
 }
 
 template <int FMT>
 static cudaError_t launch_fmt(const GemvArgs &a, cudaStream_t stream) {
-    if (a.act == STRIX_ACT_F32) {
-        switch (a.nch) {
-            case 1: return launch_t<FMT, STRIX_ACT_F32, 1>(a, stream);
-            case 2: return launch_t<FMT, STRIX_ACT_F32, 2>(a, stream);
-            case 3: return launch_t<FMT, STRIX_ACT_F32, 3>(a, stream);
-            case 4: return launch_t<FMT, STRIX_ACT_F32, 4>(a, stream);
-            default: return launch_t<FMT, STRIX_ACT_F32, 5>(a, stream);
-        }
-    }
-    switch (a.nch) {
-        case 1: return launch_t<FMT, STRIX_ACT_Q8DOT, 1>(a, stream);
-        case 2: return launch_t<FMT, STRIX_ACT_Q8DOT, 2>(a, stream);
-        case 3: return launch_t<FMT, STRIX_ACT_Q8DOT, 3>(a, stream);
-        case 4: return launch_t<FMT, STRIX_ACT_Q8DOT, 4>(a, stream);
-        case 5: return launch_t<FMT, STRIX_ACT_Q8DOT, 5>(a, stream);
-        default: break;
-    }
-    if constexpr (FMT != FMT_Q6_K) {
-        switch (a.nch) {
-            case 6: return launch_t<FMT, STRIX_ACT_Q8DOT, 6>(a, stream);
-            case 7: return launch_t<FMT, STRIX_ACT_Q8DOT, 7>(a, stream);
-            default: return launch_t<FMT, STRIX_ACT_Q8DOT, 8>(a, stream);
-        }
-    }
-    return cudaErrorInvalidValue;
+    if (a.act == STRIX_ACT_F32) return launch_t<FMT, STRIX_ACT_F32>(a, stream);
+    return launch_t<FMT, STRIX_ACT_Q8DOT>(a, stream);
 }
 
 cudaError_t launch_gemv(const GemvArgs &a, cudaStream_t stream) {
@@ -736,31 +674,17 @@ cudaError_t launch_gemv(const GemvArgs &a, cudaStream_t stream) {
     }
 }
 
-template <int FMT, int ACT, int NCH>
-static cudaError_t optin_one(size_t bytes) {
-    cudaError_t e = cudaSuccess;
-#define STRIX_ATTR(RB_, MB_)                                                                                      \
-    if (e == cudaSuccess)                                                                                         \
-        e = cudaFuncSetAttribute(gemv_kernel<FMT, ACT, NCH, RB_, MB_>, cudaFuncAttributeMaxDynamicSharedMemorySize, \
-                                 (int)bytes);
-    STRIX_ATTR(4, false) STRIX_ATTR(2, false) STRIX_ATTR(4, true) STRIX_ATTR(2, true)
-#undef STRIX_ATTR
-    return e;
-}
 template <int FMT>
 static cudaError_t optin_fmt(size_t b) {
-    cudaError_t e;
-#define STRIX_OPTIN(ACT, N) \
-    if ((e = optin_one<FMT, ACT, N>(b)) != cudaSuccess) return e;
-    STRIX_OPTIN(STRIX_ACT_F32, 1) STRIX_OPTIN(STRIX_ACT_F32, 2) STRIX_OPTIN(STRIX_ACT_F32, 3)
-    STRIX_OPTIN(STRIX_ACT_F32, 4) STRIX_OPTIN(STRIX_ACT_F32, 5)
-    STRIX_OPTIN(STRIX_ACT_Q8DOT, 1) STRIX_OPTIN(STRIX_ACT_Q8DOT, 2) STRIX_OPTIN(STRIX_ACT_Q8DOT, 3)
-    STRIX_OPTIN(STRIX_ACT_Q8DOT, 4) STRIX_OPTIN(STRIX_ACT_Q8DOT, 5)
-    if constexpr (FMT != FMT_Q6_K) {
-        STRIX_OPTIN(STRIX_ACT_Q8DOT, 6) STRIX_OPTIN(STRIX_ACT_Q8DOT, 7) STRIX_OPTIN(STRIX_ACT_Q8DOT, 8)
-    }
-#undef STRIX_OPTIN
-    return cudaSuccess;
+    cudaError_t e = cudaSuccess;
+#define STRIX_ATTR(ACT_, RB_)                                                                               \
+    if (e == cudaSuccess)                                                                                   \
+        e = cudaFuncSetAttribute(gemv_kernel<FMT, ACT_, RB_>, cudaFuncAttributeMaxDynamicSharedMemorySize, \
+                                 (int)b);
+    STRIX_ATTR(STRIX_ACT_F32, 1) STRIX_ATTR(STRIX_ACT_F32, 2) STRIX_ATTR(STRIX_ACT_F32, 4)
+    STRIX_ATTR(STRIX_ACT_Q8DOT, 1) STRIX_ATTR(STRIX_ACT_Q8DOT, 2) STRIX_ATTR(STRIX_ACT_Q8DOT, 4)
+#undef STRIX_ATTR
+    return e;
 }
 
 cudaError_t gemv_prepare_device(size_t smem_optin) {

@@ -15,9 +15,10 @@ cudaError_t launch_dequant(const uint8_t *d_res, float *d_out, const RowLayout &
 // ---- dequant-GEMV -------------------------------------------------------
 constexpr int GEMV_MAX_MATS = 3;
 constexpr int GEMV_MAX_STAGES = 8;
-// Consumer warps per CTA (plus one producer warp), one CTA per SM. The f32-activation kernels keep
-// up to 80 x values per lane in registers, so they run fewer, fatter warps.
-constexpr int gemv_warps(int act) { return act == 0 /* STRIX_ACT_F32 */ ? 12 : 16; }
+// Consumer warps per CTA (plus one producer warp), one CTA per SM: six per scheduler, which the
+// register file allows because the activation stays in shared memory (80 registers per thread).
+constexpr int GEMV_WARPS = 24;
+constexpr int gemv_warps(int /*act*/) { return GEMV_WARPS; }
 
 struct GemvMat {
     const uint8_t *w;  // resident rows of this accelerator's shard
