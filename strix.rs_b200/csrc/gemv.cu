@@ -330,13 +330,16 @@ __device__ __forceinline__ TileRef tile_ref(const GemvArgs &A, uint32_t t) {
 }
 
 // Shared-memory map of gemv_kernel (offsets in bytes):
-//   0    full[8]   mbarriers: a stage's bulk copy has landed        (producer arms, copy completes)
-//   64   empty[8]  mbarriers: every consumer warp is done with it   (one arrival per consumer warp)
-//   128  ctl[0]    abort flag (a bounded wait ran out)
-//   256  red[32]   block reduction scratch (RMSNORM prologue)
-//   512  x         the activations: B x K f32, or K f32 staging + B x (K int8 codes + K/32 f32 block scales)
-//   ...  stages    n_stages x stage_bytes, 128-byte aligned
-constexpr uint32_t SMEM_X_OFF = 512;
+//   0     full[64]   mbarriers: a stage's bulk copy has landed            (producer arms, copy completes)
+//   512   empty[64]  mbarriers: the stage's consumer warps are done with it (one arrival per warp of the slot)
+//   1024  ctl[0]     abort flag (a bounded wait ran out)
+//   1088  red[32]    block reduction scratch (RMSNORM prologue)
+//   1280  part       per slot: 2 x wc x 4 partial sums (rows split along K over wc warps)
+//   2304  seq[64]    batch index last issued into each stage
+//   2560  x          the activations: B x K f32, or K f32 staging + B x (K int8 codes + K/32 f32 block scales)
+//   ...   stages     n_stages x stage_bytes, 128-byte aligned; one stage = one batch of RB rows
+constexpr uint32_t SMEM_EMPTY_OFF = 512, SMEM_CTL_OFF = 1024, SMEM_RED_OFF = 1088, SMEM_PART_OFF = 1280;
+constexpr uint32_t SMEM_SEQ_OFF = 2304, SMEM_X_OFF = 2560;
 
 // Inverse of unit_elem for groups of four elements: natural float4 index e4 -> (unit, group).
 template <int FMT>
@@ -360,13 +363,16 @@ __global__ void __launch_bounds__((GEMV_WARPS + 1) * 32, 1) gemv_kernel(const __
     extern __shared__ __align__(128) uint8_t smem[];
     if (A.debug & 2u) return;  // measurement only: cost of an empty launch of this shape
     uint64_t *full = reinterpret_cast<uint64_t *>(smem);
-    uint64_t *empty = reinterpret_cast<uint64_t *>(smem + 64);
-    volatile uint32_t *ctl = reinterpret_cast<volatile uint32_t *>(smem + 128);
-    float *red = reinterpret_cast<float *>(smem + 256);
+    uint64_t *empty = reinterpret_cast<uint64_t *>(smem + SMEM_EMPTY_OFF);
+    volatile uint32_t *ctl = reinterpret_cast<volatile uint32_t *>(smem + SMEM_CTL_OFF);
+    float *red = reinterpret_cast<float *>(smem + SMEM_RED_OFF);
+    float *part = reinterpret_cast<float *>(smem + SMEM_PART_OFF);
+    volatile uint32_t *seq = reinterpret_cast<volatile uint32_t *>(smem + SMEM_SEQ_OFF);
     uint8_t *stages = smem + A.stage_off;
 
     const uint32_t tid = threadIdx.x, lane = tid & 31u, warp = tid >> 5;
-    const uint32_t n_cons = A.slots;  // consumer warps; warp n_cons is the producer
+    const uint32_t wc = A.wc, n_slots = A.slots;
+    const uint32_t n_cons = n_slots * wc;  // consumer warps; warp n_cons is the producer
     const uint32_t S = A.n_stages, grid = gridDim.x, bid = blockIdx.x;
     const uint32_t my_n = (A.n_tiles > bid) ? (A.n_tiles - bid + grid - 1) / grid : 0;
     const RowLayout L = A.L;
@@ -376,30 +382,60 @@ __global__ void __launch_bounds__((GEMV_WARPS + 1) * 32, 1) gemv_kernel(const __
     if (tid == 0) {
         for (uint32_t s = 0; s < S; s++) {
             mbar_init(&full[s], 1);
-            mbar_init(&empty[s], n_cons);
+            mbar_init(&empty[s], wc);
         }
         ctl[0] = 0;
         mbar_fence_init();
     }
     __syncthreads();
     if (warp == n_cons) {
-        // ---- producer: start the first S tile copies at once (they overlap the activation prologue),
-        //      then refill a stage as soon as every consumer warp has released it ----
-        if (lane == 0) {
-            for (uint32_t i = 0; i < my_n; i++) {
-                const uint32_t s = i % S;
-                if (i >= S && !ctl[0] && !mbar_wait_bounded(&empty[s], ((i / S) - 1u) & 1u, A.status)) ctl[0] = 1;
+        // ---- producer: one bulk copy per batch of RB rows, into a ring of S stages. The first S copies
+        //      start at once (they overlap the activation prologue); after that a stage is refilled as
+        //      soon as the warps of the slot that consumed it have released it ----
+        // The 32 lanes share the work: issuing one copy costs a few hundred cycles of dependent
+        // instructions, which a single lane cannot hide at one copy per 5 KB. Each pass the lanes look
+        // at the next 32 batches (lane l at batch base + l), poll their stages once, and the leading
+        // run of free ones is issued. Issue stays strictly in batch order: a lane that polls stage s for
+        // lap n can then rely on lap n - 1 having been issued, so the parity it tests cannot be
+        // mistaken for the phase two laps back.
+        const uint32_t win = S < 32u ? S : 32u;
+        uint32_t base = 0, idle = 0;
+        while (base < my_n && !ctl[0]) {  // after an abort nothing more is issued
+            const uint32_t i = base + lane;
+            bool ready = false;
+            uint32_t s = 0;
+            if (lane < win && i < my_n) {
+                const uint32_t lap = i / S;
+                s = i - lap * S;
+                ready = lap == 0 || mbar_try_wait(&empty[s], (lap - 1u) & 1u);
+            }
+            const uint32_t m = __ballot_sync(0xffffffffu, ready);
+            const uint32_t n = (m == 0xffffffffu) ? 32u : (uint32_t)__ffs((int)~m) - 1u;  // leading run of ready lanes
+            if (lane < n) {
                 TileRef t = tile_ref(A, bid + i * grid);
                 const uint32_t bytes = t.rows * L.row_stride;
+                seq[s] = i;  // consumers check it: tells this lap's completion from an older one's
                 mbar_arrive_expect_tx(&full[s], bytes);
                 bulk_g2s(stages + (uint64_t)s * A.stage_bytes, t.src, bytes, &full[s]);
             }
-            if (ctl[0]) {
-                // after an abort consumers stop waiting: let the copies still in flight land (bounded)
-                // before the CTA's shared memory is released
-                for (uint32_t i = (my_n > S ? my_n - S : 0); i < my_n; i++)
-                    mbar_wait_bounded(&full[i % S], (i / S) & 1u, nullptr);
+            base += n;
+            // bounded like every other wait: 2^22 passes without progress
+            if (n) {
+                idle = 0;
+            } else if (++idle >= (1u << 22)) {
+                if (lane == 0) {
+                    if (A.status) atomicOr(A.status, STATUS_WAIT_TIMEOUT);
+                    ctl[0] = 1;
+                }
+                idle = 0;
             }
+            __syncwarp();
+        }
+        if (lane == 0 && ctl[0]) {
+            // after an abort consumers stop waiting: let the copies still in flight land (bounded)
+            // before the CTA's shared memory is released
+            for (uint32_t k = (base > S ? base - S : 0); k < base; k++)
+                mbar_wait_bounded(&full[k % S], (k / S) & 1u, nullptr);
         }
         return;
     }
@@ -511,61 +547,86 @@ __global__ void __launch_bounds__((GEMV_WARPS + 1) * 32, 1) gemv_kernel(const __
         X.sel_b = sext_sel((c4 >> 2) + 2u);  // sub-scale byte (c4>>2) + 2 of a word: groups 1 and 3
     }
 
-    // ---- stream the tiles: every consumer warp takes whole rows, RB at a time, round-robin ----
-    const uint32_t slot = warp;
+    // ---- stream the batches: slot k (wc warps) takes batches k, k + n_slots, ... of this CTA; the
+    //      wc warps of a slot split the runs of a row between them (warp w: runs w, w + wc, ...) ----
+    const uint32_t slot = warp / wc, w = warp - slot * wc;
     const uint32_t st0 = smem_u32(stages);
     const bool skip = (A.debug & 1u) != 0u;
     constexpr uint32_t LPR = 32u / RB;  // after batch_reduce lane LPR*k holds row k
-    const uint32_t bpt = A.rows_per_tile / RB;  // batches per (full) tile
-    for (uint32_t i = 0; i < my_n; i++) {
-        const uint32_t s = i % S;
+    b_w += w * Step<FMT>::w; b_s += w * Step<FMT>::s; b_hh += w * Step<FMT>::hh; b_sc += w * Step<FMT>::sc;
+    const uint32_t d_w = wc * Step<FMT>::w, d_s = wc * Step<FMT>::s, d_hh = wc * Step<FMT>::hh, d_sc = wc * Step<FMT>::sc;
+    float *my_part = part + slot * (2u * wc * 4u);
+    uint32_t par = 0;
+    uint32_t s = slot % S, ph = (slot / S) & 1u;
+    for (uint32_t i = slot; i < my_n; i += n_slots) {
         // once any wait has run out, nobody waits again: the loop runs to its end on whatever is in
         // shared memory and the status word reports it
-        if (!ctl[0] && !mbar_wait_bounded(&full[s], (i / S) & 1u, A.status)) ctl[0] = 1;
+        // (a stage is used by different slots on different laps, so a slot does not see every phase of
+        // full[s] go by; the batch index the producer left in seq[s] tells this lap's completion from
+        // that of the lap before last, which has the same parity)
+        if (!ctl[0]) {
+            bool got = false;
+            for (uint32_t it = 0; it < (1u << 22) && !got; ++it) got = mbar_try_wait(&full[s], ph) && seq[s] == i;
+            if (!got) {
+                if (A.status) atomicOr(A.status, STATUS_WAIT_TIMEOUT);
+                ctl[0] = 1;
+            }
+        }
         const TileRef t = tile_ref(A, bid + i * grid);
-        const uint32_t st = st0 + s * A.stage_bytes;
-        // Row batches go round-robin over the warps, counted across this CTA's tiles, so that small
-        // tiles still keep every warp busy. Rows past the tile's end read whatever the stage still
-        // holds; their sums are dropped.
-        const uint32_t first = (slot + n_cons - (i * bpt) % n_cons) % n_cons;  // this warp's first batch in the tile
-        for (uint32_t bi = 0; bi < B; bi++) {
+        const uint32_t rb0 = st0 + s * A.stage_bytes;
+        // Rows past the matrix's end read whatever the stage still holds; their sums are dropped.
+        for (uint32_t bi = 0; bi < B && !skip; bi++) {
             float *y = A.mat[t.mat].y + (size_t)bi * A.mat[t.mat].ystride + t.row0;
             const float *res = A.mat[t.mat].res ? A.mat[t.mat].res + (size_t)bi * A.mat[t.mat].ystride + t.row0 : nullptr;
             const float4 *xs4 = reinterpret_cast<const float4 *>(xs0 + bi * K);
             const uint4 *xq4 = reinterpret_cast<const uint4 *>(xq0 + bi * K);
             const float *sd = sd0 + bi * (K / 32u);
-            for (uint32_t r0 = first * RB; r0 < t.rows && !skip; r0 += n_cons * RB) {
-                float acc[RB];
+            float acc[RB];
 #pragma unroll
-                for (int j = 0; j < RB; j++) acc[j] = 0.f;
-                const uint32_t rb0 = st + r0 * L.row_stride;
-                X.off_w = b_w; X.off_s = b_s; X.off_hh = b_hh; X.off_sc = b_sc;
-                for (uint32_t c = 0, u = lane; c < C; c++, u += 32u) {
-                    if (u < U) {
-                        if (ACT == STRIX_ACT_F32) {
-                            float v[16];
+            for (int j = 0; j < RB; j++) acc[j] = 0.f;
+            X.off_w = b_w; X.off_s = b_s; X.off_hh = b_hh; X.off_sc = b_sc;
+            for (uint32_t u = w * 32u + lane; u < C * 32u; u += wc * 32u) {
+                if (u < U) {
+                    if (ACT == STRIX_ACT_F32) {
+                        float v[16];
 #pragma unroll
-                            for (uint32_t g = 0; g < 4; g++) {
-                                const float4 a4 = xs4[g * U + u];
-                                v[4 * g] = a4.x; v[4 * g + 1] = a4.y; v[4 * g + 2] = a4.z; v[4 * g + 3] = a4.w;
-                            }
-                            set_unit_x<FMT, ACT, 1>(X, 0, v);
-                        } else {
-                            load_unit_q<FMT, ACT, 1>(X, 0, u, xq4, sd);
+                        for (uint32_t g = 0; g < 4; g++) {
+                            const float4 a4 = xs4[g * U + u];
+                            v[4 * g] = a4.x; v[4 * g + 1] = a4.y; v[4 * g + 2] = a4.z; v[4 * g + 3] = a4.w;
                         }
-#pragma unroll
-                        for (int j = 0; j < RB; j++)
-                            acc[j] += unit_dot<FMT, ACT, 1>(rb0 + (uint32_t)j * L.row_stride, X, 0);
+                        set_unit_x<FMT, ACT, 1>(X, 0, v);
+                    } else {
+                        load_unit_q<FMT, ACT, 1>(X, 0, u, xq4, sd);
                     }
-                    X.off_w += Step<FMT>::w; X.off_s += Step<FMT>::s; X.off_hh += Step<FMT>::hh; X.off_sc += Step<FMT>::sc;
+#pragma unroll
+                    for (int j = 0; j < RB; j++)
+                        acc[j] += unit_dot<FMT, ACT, 1>(rb0 + (uint32_t)j * L.row_stride, X, 0);
                 }
-                const float tot = batch_reduce<RB>(acc, lane);
-                const uint32_t rr = r0 + lane / LPR;
-                if ((lane & (LPR - 1u)) == 0u && rr < t.rows) y[rr] = res ? tot + res[rr] : tot;
+                X.off_w += d_w; X.off_s += d_s; X.off_hh += d_hh; X.off_sc += d_sc;
+            }
+            const float tot = batch_reduce<RB>(acc, lane);
+            const uint32_t rr = lane / LPR;
+            const bool leader = (lane & (LPR - 1u)) == 0u;
+            if (wc == 1) {
+                if (leader && rr < t.rows) y[rr] = res ? tot + res[rr] : tot;
+            } else {
+                // partial sums of the slot's warps meet in shared memory (double-buffered, so one
+                // barrier per batch is enough); warp 0 of the slot adds them in warp order
+                float *pp = my_part + par * (wc * 4u);
+                if (leader) pp[w * 4u + rr] = tot;
+                asm volatile("bar.sync %0, %1;" ::"r"(1u + slot), "r"(wc * 32u) : "memory");
+                if (w == 0 && lane < RB && lane < t.rows) {
+                    float sum = pp[lane];
+                    for (uint32_t k = 1; k < wc; k++) sum += pp[k * 4u + lane];
+                    y[lane] = res ? sum + res[lane] : sum;
+                }
+                par ^= 1u;
             }
         }
         __syncwarp();
         if (lane == 0) mbar_arrive(&empty[s]);  // this warp's reads of the stage are complete
+        s += n_slots;
+        while (s >= S) { s -= S; ph ^= 1u; }
     }
 }
 
@@ -576,68 +637,77 @@ bool gemv_plan(GemvArgs &a, int num_sms, size_t smem_optin) {
     const uint32_t K = a.L.in_dim;
     if (K == 0 || K % 32 != 0) return false;
     const uint32_t pool = (uint32_t)GEMV_WARPS;
+    const uint32_t U = K / 16, C = (U + 31) / 32;
     const uint32_t stride = a.L.row_stride;
     const uint32_t budget = (uint32_t)smem_optin - 1024u;
+    const uint32_t nbt = a.nbatch ? a.nbatch : 1u;
+    a.nbatch = nbt;
+    // the CTA's activation: K f32 values; for the integer-dot form also K int8 codes and K/32 scales
+    a.x_off = SMEM_X_OFF;
+    const uint32_t stage_off =
+        a.x_off + align128u(a.act == STRIX_ACT_Q8DOT ? K * 4u + nbt * (K + K / 8u) : nbt * K * 4u);
+    if (stage_off + 2u * align128u(stride) > budget) return false;  // in_dim beyond what one SM can hold
+    const uint32_t avail = budget - stage_off;
 
-    // Tile height: any multiple of rb up to ~72 KB.
-    // Large tiles amortise the per-tile bookkeeping and two to four stages of them keep HBM busy;
-    // few rows per SM want small tiles so that the busiest CTA does not carry a whole extra tile.
-    // Cost of a candidate = tiles on the busiest CTA x (bytes streamed + a fixed charge per tile).
-    // (Measured: shrinking the tiles of a small launch does not help; its time is set by the
-    // serial work per warp, not by the arrival of the first tile.)
-    uint32_t target = 73728u;
-    if (const char *e = getenv("STRIX_GEMV_TILE_BYTES")) target = (uint32_t)atoi(e);  // tuning knob
-    // A warp carries rb rows at once: four give more independent work per lane, fewer reductions
-    // per row and fewer re-reads of x from shared memory; fewer when there are not enough rows per
-    // SM to give every warp such a batch, or when rb long rows would overshoot the tile size.
+    // Geometry: a slot of wc warps works on one batch of rb rows (= one stage of the ring) at a time,
+    // the 24 / wc slots on different batches. What must fit in shared memory is one stage per slot
+    // plus the copies in flight (about 64 KB per SM keeps HBM busy). More rows per batch re-use each
+    // x value read from shared memory and share one reduction; more warps per row shorten the serial
+    // work of a small launch and shrink the footprint of long rows. Every feasible (rb, wc) is
+    // costed in "unit-dots on the busiest warp" and the cheapest wins.
     uint64_t total_rows = 0;
     for (int k = 0; k < a.nmat; k++) total_rows += a.mat[k].rows;
-    const uint64_t rows_per_sm = (total_rows + (uint64_t)num_sms - 1) / (uint64_t)num_sms;
-    uint32_t rb = 4u;
-    while (rb > 1u && (rb * stride > target || rows_per_sm < (uint64_t)pool * rb)) rb >>= 1;
-    if (const char *e = getenv("STRIX_GEMV_RB")) {  // tuning knob
-        const uint32_t v = (uint32_t)atoi(e);
-        if ((v == 1 || v == 2 || v == 4) && v * stride <= target) rb = v;
+    uint32_t best_rb = 0, best_wc = 0, best_S = 0;
+    double best_cost = 1e300;
+    static const uint32_t wcs[] = {1, 2, 3, 4, 6, 8, 12};
+    uint32_t force_rb = 0, force_wc = 0;
+    if (const char *e = getenv("STRIX_GEMV_RB")) force_rb = (uint32_t)atoi(e);  // tuning knobs
+    if (const char *e = getenv("STRIX_GEMV_WC")) force_wc = (uint32_t)atoi(e);
+    for (uint32_t flight = 65536u; flight >= 8192u && best_rb == 0; flight >>= 1) {
+        for (uint32_t rb = 4; rb >= 1; rb >>= 1) {
+            if (force_rb && rb != force_rb) continue;
+            const uint32_t sb = align128u(rb * stride);
+            uint32_t S = avail / sb;
+            if (S > (uint32_t)GEMV_MAX_STAGES) S = (uint32_t)GEMV_MAX_STAGES;
+            if (S < 2) continue;
+            uint64_t batches = 0;
+            for (int k = 0; k < a.nmat; k++) batches += (a.mat[k].rows + rb - 1) / rb;
+            if (batches == 0) batches = 1;
+            const uint64_t ctas = batches < (uint64_t)num_sms ? batches : (uint64_t)num_sms;
+            const uint64_t per_cta = (batches + ctas - 1) / ctas;
+            for (uint32_t wc : wcs) {
+                if (force_wc && wc != force_wc) continue;
+                if (wc > C) break;
+                const uint32_t slots = pool / wc;
+                uint64_t need = slots + (flight + sb - 1) / sb;
+                if (need > per_cta) need = per_cta;  // a short launch never has more in the ring
+                if (S < need) continue;
+                const uint64_t rounds = (per_cta + slots - 1) / slots;
+                const uint32_t passes = (C + wc - 1) / wc;
+                const double cost = (double)rounds * nbt * (passes * (rb + 0.5) + 2.5 + (wc > 1 ? 2.0 : 0.0));
+                if (cost < best_cost) { best_cost = cost; best_rb = rb; best_wc = wc; best_S = S; }
+            }
+        }
     }
+    if (best_rb == 0) return false;
+    const uint32_t rb = best_rb;
     a.rb = rb;
-    uint32_t jmax = target / (rb * stride);
-    if (jmax < 1) jmax = 1;
-    uint32_t best_rt = rb;
-    uint64_t best_cost = ~0ull;
-    for (uint32_t j = jmax; j >= 1; j--) {
-        const uint32_t rt = j * rb;
-        uint64_t tiles = 0;
-        for (int k = 0; k < a.nmat; k++) tiles += (a.mat[k].rows + rt - 1) / rt;
-        if (tiles == 0) tiles = 1;
-        const uint64_t per_cta = (tiles + (uint64_t)num_sms - 1) / (uint64_t)num_sms;
-        const uint64_t cost = per_cta * ((uint64_t)rt * stride + 4096u);
-        if (cost < best_cost) { best_cost = cost; best_rt = rt; }
-    }
-    const uint32_t rt = best_rt;
+    a.wc = best_wc;
+    a.slots = pool / best_wc;
+    a.nch = 0;
     uint32_t tile = 0;
     for (int m = 0; m < a.nmat; m++) {
         a.mat[m].tile0 = tile;
-        tile += (a.mat[m].rows + rt - 1) / rt;
+        tile += (a.mat[m].rows + rb - 1) / rb;
     }
     a.n_tiles = tile;
-    a.rows_per_tile = rt;
-    a.wc = 1;
-    a.slots = pool;
-    a.nch = 0;
-    a.x_off = SMEM_X_OFF;
-    // the CTA's activation: K f32 values; for the integer-dot form also K int8 codes and K/32 scales
-    const uint32_t nbt = a.nbatch ? a.nbatch : 1u;
-    a.nbatch = nbt;
-    const uint32_t stage_off =
-        a.x_off + align128u(a.act == STRIX_ACT_Q8DOT ? K * 4u + nbt * (K + K / 8u) : nbt * K * 4u);
+    a.rows_per_tile = rb;
     a.stage_off = stage_off;
-    a.stage_bytes = align128u(rt * stride);
-    if (budget < stage_off + 2u * a.stage_bytes) return false;
-    uint32_t S = (budget - stage_off) / a.stage_bytes;
-    if (S > (a.stage_bytes > 32768u ? 4u : (uint32_t)GEMV_MAX_STAGES)) S = a.stage_bytes > 32768u ? 4u : (uint32_t)GEMV_MAX_STAGES;
+    a.stage_bytes = align128u(rb * stride);
+    uint32_t S = best_S;
     if (const char *e = getenv("STRIX_GEMV_STAGES")) {  // tuning knob
         const uint32_t v = (uint32_t)atoi(e);
-        if (v >= 2 && v <= (uint32_t)GEMV_MAX_STAGES && stage_off + v * a.stage_bytes <= budget) S = v;
+        if (v >= 2 && v <= (uint32_t)GEMV_MAX_STAGES && v * a.stage_bytes <= avail) S = v;
     }
     a.debug = 0;
     if (const char *e = getenv("STRIX_GEMV_DEBUG")) a.debug = (uint32_t)atoi(e);  // 1 = stream only, no arithmetic
@@ -649,7 +719,7 @@ bool gemv_plan(GemvArgs &a, int num_sms, size_t smem_optin) {
 
 template <int FMT, int ACT>
 static cudaError_t launch_t(const GemvArgs &a, cudaStream_t stream) {
-    const uint32_t threads = (a.slots + 1u) * 32u;  // consumer warps + one producer warp
+    const uint32_t threads = (a.slots * a.wc + 1u) * 32u;  // consumer warps + one producer warp
     if (a.rb == 4)
         gemv_kernel<FMT, ACT, 4><<<a.grid, threads, a.smem_bytes, stream>>>(a);
     else if (a.rb == 2)

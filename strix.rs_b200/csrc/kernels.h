@@ -14,7 +14,7 @@ cudaError_t launch_dequant(const uint8_t *d_res, float *d_out, const RowLayout &
 
 // ---- dequant-GEMV -------------------------------------------------------
 constexpr int GEMV_MAX_MATS = 3;
-constexpr int GEMV_MAX_STAGES = 8;
+constexpr int GEMV_MAX_STAGES = 64;
 // Consumer warps per CTA (plus one producer warp), one CTA per SM: six per scheduler, which the
 // register file allows because the activation stays in shared memory (80 registers per thread).
 constexpr int GEMV_WARPS = 24;
