@@ -96,16 +96,25 @@ static int upload_quant(strix_cuda *h, int fmt, const char *key, const uint8_t *
         probe.mat[0].rows = (uint32_t)std::max<size_t>(r.rows, 1);
         if (!gemv_plan(probe, h->num_sms, h->smem_optin)) return 0;
     }
-    r.bytes = r.rows * (size_t)r.L.row_stride;
+    r.bytes = (size_t)resident_bytes(r.L, r.rows);
     CU_TRY(h, cudaMalloc(&r.dev, std::max<size_t>(r.bytes, 16)));
+    if (fmt == FMT_Q8_0) {
+        const cudaError_t eg = cudaMalloc(&r.gemm_codes, std::max<size_t>(r.rows * in_dim, 16));
+        if (eg != cudaSuccess) {
+            cudaFree(r.dev);
+            h->err = std::string("upload (GEMM copy): ") + cudaGetErrorString(eg);
+            return -1;
+        }
+    }
 
-    // Raw GGUF bytes go up in row chunks; a kernel splits each chunk into planes.
+    // Raw GGUF bytes go up in chunks of whole row groups; a kernel regroups each chunk into tiles.
     const size_t raw_row = nb * bb;
-    const size_t chunk_rows = std::max<size_t>(1, (size_t)(128u << 20) / raw_row);
+    const size_t chunk_rows = std::max<size_t>(1, (size_t)(128u << 20) / raw_row / TILE_ROWS) * TILE_ROWS;
     uint8_t *d_raw = nullptr;
     cudaError_t e = cudaMalloc(&d_raw, std::min(chunk_rows, std::max<size_t>(r.rows, 1)) * raw_row);
     if (e != cudaSuccess) {
         cudaFree(r.dev);
+        if (r.gemm_codes) cudaFree(r.gemm_codes);
         h->err = std::string("upload staging: ") + cudaGetErrorString(e);
         return -1;
     }
@@ -113,12 +122,13 @@ static int upload_quant(strix_cuda *h, int fmt, const char *key, const uint8_t *
         const size_t n = std::min(chunk_rows, r.rows - at);
         e = cudaMemcpyAsync(d_raw, bytes + (r.row0 + at) * raw_row, n * raw_row, cudaMemcpyHostToDevice, h->stream);
         if (e == cudaSuccess)
-            e = launch_repack(fmt, d_raw, r.dev + at * (size_t)r.L.row_stride, r.L, (uint32_t)n, h->stream);
+            e = launch_repack(fmt, d_raw, r.dev, r.gemm_codes, r.L, (uint32_t)at, (uint32_t)n, h->stream);
         if (e == cudaSuccess) e = cudaStreamSynchronize(h->stream);  // `bytes` is borrowed; d_raw is reused
     }
     cudaFree(d_raw);
     if (e != cudaSuccess) {
         cudaFree(r.dev);
+        if (r.gemm_codes) cudaFree(r.gemm_codes);
         h->err = std::string("upload: ") + cudaGetErrorString(e);
         return -1;
     }
@@ -126,6 +136,7 @@ static int upload_quant(strix_cuda *h, int fmt, const char *key, const uint8_t *
     auto it = h->weights.find(key);
     if (it != h->weights.end()) {
         cudaFree(it->second.dev);
+        if (it->second.gemm_codes) cudaFree(it->second.gemm_codes);
         if (it->second.scalesT) cudaFree(it->second.scalesT);
         it->second = r;
     } else {
@@ -260,6 +271,7 @@ void strix_cuda_destroy(strix_cuda *h) {
     decode_release(h);
     for (auto &kv : h->weights) {
         cudaFree(kv.second.dev);
+        if (kv.second.gemm_codes) cudaFree(kv.second.gemm_codes);
         if (kv.second.scalesT) cudaFree(kv.second.scalesT);
     }
     for (float *p : {h->gm_x.p, h->gm_y.p, h->gm_part.p, h->gm_xd.p})

@@ -11,7 +11,7 @@
 
 namespace strix {
 
-// One adopted weight: this accelerator's shard of rows in the row-planar layout.
+// One adopted weight: this accelerator's shard of rows in the tile-major layout.
 struct Resident {
     int fmt;
     RowLayout L;
@@ -20,6 +20,8 @@ struct Resident {
     size_t rows;       // rows held here
     uint8_t *dev;
     size_t bytes;
+    uint8_t *gemm_codes;  // Q8_0 only: the codes once more, row-major [rows][in_dim] as q + 128 (the prefill GEMM's
+                          // TMA boxes want K-major rows; the GEMV's tile-major order does not give them)
     float *scalesT;  // Q8_0 only, built on the first GEMM: f32 scales transposed to [nb][ld] (see gemm_w8a8.cu)
 };
 

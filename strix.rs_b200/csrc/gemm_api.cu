@@ -55,7 +55,7 @@ static int gemm_device(strix_cuda *h, Resident *r, const float *d_xs, size_t m, 
     const size_t wsf = gemm_workspace_floats((uint32_t)m, (uint32_t)r->rows, splits);
     if (wsf && ensure_f32(h, h->gm_part, wsf) < 0) return -1;
     CU_TRY(h, launch_xquant8_sum(d_xs, h->gm_xq, h->gm_xd.p, h->gm_xs, (uint32_t)m, (uint32_t)nb, stream));
-    CU_TRY(h, launch_gemm_w8a8(r->dev, r->L, (uint32_t)r->rows, r->scalesT, h->gm_xq, h->gm_xd.p, h->gm_xs, (uint32_t)m,
+    CU_TRY(h, launch_gemm_w8a8(r->gemm_codes, r->L, (uint32_t)r->rows, r->scalesT, h->gm_xq, h->gm_xd.p, h->gm_xs, (uint32_t)m,
                               d_y, h->gm_part.p, splits, h->d_status, stream));
     return 1;
 }
@@ -120,7 +120,7 @@ int strix_cuda_debug_block_isums(strix_cuda *h, const char *key, const float *xs
     CU_TRY(h, cudaMalloc(&d_out, total * sizeof(int32_t)));
     cudaError_t e = cudaMemcpyAsync(h->gm_x.p, xs, m * K * sizeof(float), cudaMemcpyHostToDevice, h->stream);
     if (e == cudaSuccess) e = launch_xquant8_sum(h->gm_x.p, h->gm_xq, h->gm_xd.p, h->gm_xs, (uint32_t)m, (uint32_t)nb, h->stream);
-    if (e == cudaSuccess) e = launch_block_isums(r->dev, h->gm_xq, d_out, r->L, (uint32_t)m, (uint32_t)r->rows, h->stream);
+    if (e == cudaSuccess) e = launch_block_isums(r->gemm_codes, h->gm_xq, d_out, r->L, (uint32_t)m, (uint32_t)r->rows, h->stream);
     if (e == cudaSuccess) e = cudaMemcpyAsync(out, d_out, total * sizeof(int32_t), cudaMemcpyDeviceToHost, h->stream);
     if (e == cudaSuccess) e = cudaStreamSynchronize(h->stream);
     cudaFree(d_out);

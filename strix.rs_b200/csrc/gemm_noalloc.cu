@@ -101,7 +101,7 @@ int strix_cuda_prefill_q8_gemm_noalloc(strix_cuda *h, const char *key, const flo
     e = launch_scales_transpose(r->dev, sc, r->L, (uint32_t)r->rows, st);
     if (e == cudaSuccess) e = launch_xquant8_sum(d_xs, xq, xd, xs, (uint32_t)m, (uint32_t)nb, st);
     if (e == cudaSuccess)
-        e = launch_gemm_w8a8(r->dev, r->L, (uint32_t)r->rows, sc, xq, xd, xs, (uint32_t)m, d_y, pt, splits, h->d_status, st);
+        e = launch_gemm_w8a8(r->gemm_codes, r->L, (uint32_t)r->rows, sc, xq, xd, xs, (uint32_t)m, d_y, pt, splits, h->d_status, st);
     if (e != cudaSuccess) {
         h->err = std::string("prefill_q8_gemm_noalloc: ") + cudaGetErrorString(e);
         return -1;

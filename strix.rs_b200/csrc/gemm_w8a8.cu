@@ -346,19 +346,20 @@ __global__ void scales_transpose_kernel(const uint8_t *__restrict__ res, float *
     if (i >= (uint64_t)L.nb * lds) return;
     const uint32_t kb = (uint32_t)(i / lds), n = (uint32_t)(i % lds);
     float v = 0.f;
-    if (n < rows) v = f16_bits_to_f32(*reinterpret_cast<const uint16_t *>(res + (uint64_t)n * L.row_stride + L.off_d + 2u * kb));
+    if (n < rows) v = f16_bits_to_f32(resident_scale_bits(res, L, n, kb));
     out[i] = v;
 }
 
 // int32 block sums isum[m][n][kb] of a Q8_0 weight with int8 activations, one thread each:
 // the bit-exact tier of the GEMM contract, computed the plain way (no tensor cores).
-__global__ void block_isums_kernel(const uint8_t *__restrict__ res, const int8_t *__restrict__ xq, int32_t *__restrict__ out,
+// `codes`: the weight's codes row-major [rows][in_dim], stored as q + 128.
+__global__ void block_isums_kernel(const uint8_t *__restrict__ codes, const int8_t *__restrict__ xq, int32_t *__restrict__ out,
                                    RowLayout L, uint32_t M, uint32_t rows) {
     const uint64_t i = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x;
     if (i >= (uint64_t)M * rows * L.nb) return;
     const uint32_t kb = (uint32_t)(i % L.nb);
     const uint32_t n = (uint32_t)((i / L.nb) % rows), m = (uint32_t)(i / ((uint64_t)L.nb * rows));
-    const uint8_t *w = res + (uint64_t)n * L.row_stride + (uint64_t)kb * 32u;
+    const uint8_t *w = codes + (uint64_t)n * L.in_dim + (uint64_t)kb * 32u;
     const int8_t *x = xq + (uint64_t)m * L.in_dim + (uint64_t)kb * 32u;
     int s = 0;
     for (int k = 0; k < 32; k++) s += ((int)w[k] - 128) * (int)x[k];
@@ -455,11 +456,11 @@ cudaError_t launch_gemm_w8a8(const uint8_t *d_res, const RowLayout &L, uint32_t 
     if (M == 0 || rows == 0) return cudaSuccess;
     CUtensorMap mx, mw, ms, mxd, mxs;
     const uint32_t lds = gemm_scales_ld(rows), ldx = gemm_x_ld(L.nb);
-    // activations: [M][K] int8, K innermost; weights: [rows][row_stride] bytes, first K bytes of a row
+    // activations: [M][K] int8, K innermost; weights: [rows][K] bytes (codes as q + 128), K innermost
     // are its codes; scales: [nb][lds] f32. Coordinates past a dimension read as zero.
     if (!make_map_2d(&mx, CU_TENSOR_MAP_DATA_TYPE_UINT8, const_cast<int8_t *>(d_xq), L.in_dim, M, L.in_dim, 128, GM_BM,
                      CU_TENSOR_MAP_SWIZZLE_128B) ||
-        !make_map_2d(&mw, CU_TENSOR_MAP_DATA_TYPE_UINT8, const_cast<uint8_t *>(d_res), L.in_dim, rows, L.row_stride, 128,
+        !make_map_2d(&mw, CU_TENSOR_MAP_DATA_TYPE_UINT8, const_cast<uint8_t *>(d_res), L.in_dim, rows, L.in_dim, 128,
                      GM_BN, CU_TENSOR_MAP_SWIZZLE_128B) ||
         !make_map_2d(&ms, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, const_cast<float *>(d_scalesT), lds, L.nb, (uint64_t)lds * 4,
                      GM_BN, GM_KB_STAGE, CU_TENSOR_MAP_SWIZZLE_NONE) ||

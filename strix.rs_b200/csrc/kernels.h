@@ -7,16 +7,17 @@
 
 namespace strix {
 
-cudaError_t launch_repack(int fmt, const uint8_t *d_raw, uint8_t *d_res, const RowLayout &L, uint32_t rows,
-                          cudaStream_t stream);
+// Regroups raw GGUF rows [row0, row0 + n) of a shard (row0 a multiple of 16) into the resident shard;
+// for Q8_0, d_gemm_codes (may be null) also receives the codes row-major for the prefill GEMM.
+cudaError_t launch_repack(int fmt, const uint8_t *d_raw, uint8_t *d_res, uint8_t *d_gemm_codes, const RowLayout &L,
+                          uint32_t row0, uint32_t n, cudaStream_t stream);
 cudaError_t launch_dequant(const uint8_t *d_res, float *d_out, const RowLayout &L, uint32_t rows,
                            cudaStream_t stream);
 
 // ---- dequant-GEMV -------------------------------------------------------
 constexpr int GEMV_MAX_MATS = 3;
-constexpr int GEMV_MAX_STAGES = 64;
-// Consumer warps per CTA (plus one producer warp), one CTA per SM: six per scheduler, which the
-// register file allows because the activation stays in shared memory (80 registers per thread).
+constexpr int GEMV_MAX_STAGES = 96;
+// Consumer warps per CTA (plus one producer warp), one CTA per SM: six per scheduler.
 constexpr int GEMV_WARPS = 24;
 constexpr int gemv_warps(int /*act*/) { return GEMV_WARPS; }
 
@@ -30,7 +31,7 @@ struct GemvMat {
 };
 
 struct GemvArgs {
-    GemvMat mat[GEMV_MAX_MATS];
+    GemvMat mat[GEMV_MAX_MATS];  // tile0 = index of the matrix's first row group in the launch-wide list
     int nmat;
     RowLayout L;
     const float *a;  // activation (or gate) vector, in_dim floats
@@ -40,16 +41,17 @@ struct GemvArgs {
     float eps;
     int pre;  // STRIX_PRE_*
     int act;  // STRIX_ACT_*
-    uint32_t rows_per_tile;
-    uint32_t n_tiles;
-    uint32_t stage_bytes;  // multiple of 128
-    uint32_t stage_off;    // byte offset of the first stage in dynamic shared memory
-    uint32_t x_off;        // byte offset of the CTA's activation vector in dynamic shared memory
-    uint32_t n_stages;
-    uint32_t wc;     // warps that split a row's K range between them
-    uint32_t slots;  // groups of wc warps, each working on different rows of a tile
-    uint32_t nch;    // runs of 32 units of K owned by one consumer warp
-    uint32_t rb;     // rows a warp carries at once (2 or 4): independent chains, one batched reduction
+    uint32_t rows_per_tile;  // rows of a row group (16)
+    uint32_t n_tiles;        // row groups of the launch, over all its matrices
+    uint32_t stage_bytes;    // multiple of 128
+    uint32_t stage_off;      // byte offset of the first stage in dynamic shared memory
+    uint32_t x_off;          // byte offset of the activation operands in dynamic shared memory
+    uint32_t n_stages;       // stages in each slot's ring
+    uint32_t wc;             // warps that share a row group (they split its tiles along K)
+    uint32_t slots;          // groups of wc warps, each working on a different row group
+    uint32_t chunk_tiles;    // GGUF blocks of K per stage
+    uint32_t n_chunks;       // stages per row group
+    uint32_t multi;          // integer form with more than one activation row (Q4_0 / Q8_0)
     uint32_t grid;
     uint32_t smem_bytes;
     uint32_t debug;  // measurement only: bit 0 = stream the tiles but skip the arithmetic
@@ -67,7 +69,7 @@ cudaError_t launch_gemv(const GemvArgs &a, cudaStream_t stream);
 cudaError_t gemm_prepare_device();
 uint32_t gemm_scales_ld(uint32_t rows);  // leading dimension (floats) of the transposed f32 scale plane
 cudaError_t launch_scales_transpose(const uint8_t *d_res, float *d_out, const RowLayout &L, uint32_t rows,
-                                    cudaStream_t stream);
+                                    cudaStream_t stream);  // d_res: the resident (tile-major) weight
 uint32_t gemm_x_ld(uint32_t nb);  // leading dimension of the per-token scale / code-sum arrays
 cudaError_t launch_xquant8_sum(const float *d_x, int8_t *d_q, float *d_d, int32_t *d_xs, uint32_t m, uint32_t nb,
                                cudaStream_t stream);
