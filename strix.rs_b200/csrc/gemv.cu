@@ -111,13 +111,14 @@ __device__ __forceinline__ GroupRef group_ref(const GemvArgs &A, uint32_t t) {
 //   0     full[96]   mbarriers: a stage's bulk copy has landed             (producer arms, copy completes)
 //   768   empty[96]  mbarriers: the stage's consumer warps are done with it (one arrival per warp of the slot)
 //   1536  ctl[0]     abort flag (a bounded wait ran out)
-//   1600  red[32]    block reduction scratch (prologue)
-//   1728  inv_s[8]   f32 form: 1 / (power-of-two scale applied to activation row j before the f16 split)
-//   1792  part       24 warps x 32 lanes x NV partial sums (rows split along K over the warps of a slot)
+//   1600  red[64]    block reduction scratch (prologue): 32 sums of squares, 32 maxima
+//   1856  oscale[8]  factor applied to the outputs of activation row j: the RMSNorm scale (which is
+//                    linear, so it is applied after the product) / the power-of-two scale of the f16 split
+//   1920  part       24 warps x 32 lanes x NV partial sums (rows split along K over the warps of a slot)
 //   ...   x          the B operands, block sums and scales of the activations (see the prologue)
 //   ...   stages     slots x n_stages x stage_bytes, 128-byte aligned; a stage = a run of tiles of one row group
-constexpr uint32_t SMEM_EMPTY_OFF = 768, SMEM_CTL_OFF = 1536, SMEM_RED_OFF = 1600, SMEM_INVS_OFF = 1728;
-constexpr uint32_t SMEM_PART_OFF = 1792;
+constexpr uint32_t SMEM_EMPTY_OFF = 768, SMEM_CTL_OFF = 1536, SMEM_RED_OFF = 1600, SMEM_OSCALE_OFF = 1856;
+constexpr uint32_t SMEM_PART_OFF = 1920;
 
 // Values each lane carries per row group: rows g and g + 8 of one activation row (NV = 2), or of two
 // (integer form with more than one activation row: C columns 2t and 2t + 1 are rows 2t, 2t + 1).
@@ -352,14 +353,16 @@ __device__ __forceinline__ void tile_mac(uint32_t ta, uint32_t da, uint32_t xb_a
     }
 }
 
-// The activation after the optional pre-op, four consecutive elements (e4 = float4 index).
-__device__ __forceinline__ float4 load_post(const float *Aa, const float *Ab, int pre, float scale, uint32_t e4) {
+// The activation after the optional pre-op, four consecutive elements (e4 = float4 index). RMSNorm is
+// applied WITHOUT its scalar 1/rms (the caller multiplies the outputs by it); `ss` collects the
+// squares of the raw values for it.
+__device__ __forceinline__ float4 load_pre(const float *Aa, const float *Ab, int pre, uint32_t e4, float &ss) {
     float4 a4 = __ldg(reinterpret_cast<const float4 *>(Aa) + e4);
     if (pre != STRIX_PRE_NONE) {
         const float4 b4 = __ldg(reinterpret_cast<const float4 *>(Ab) + e4);
         if (pre == STRIX_PRE_RMSNORM) {
-            a4.x = (a4.x * scale) * b4.x; a4.y = (a4.y * scale) * b4.y;
-            a4.z = (a4.z * scale) * b4.z; a4.w = (a4.w * scale) * b4.w;
+            ss = fmaf(a4.x, a4.x, ss); ss = fmaf(a4.y, a4.y, ss); ss = fmaf(a4.z, a4.z, ss); ss = fmaf(a4.w, a4.w, ss);
+            a4.x *= b4.x; a4.y *= b4.y; a4.z *= b4.z; a4.w *= b4.w;
         } else if (pre == STRIX_PRE_SWIGLU) {
             a4.x = silu_f(a4.x) * b4.x; a4.y = silu_f(a4.y) * b4.y;
             a4.z = silu_f(a4.z) * b4.z; a4.w = silu_f(a4.w) * b4.w;
@@ -381,13 +384,16 @@ __device__ __forceinline__ void split_h(float x, float s, __half &hi, __half &lo
 template <int FMT, int ACT, bool MULTI>
 __global__ void __launch_bounds__((GEMV_WARPS + 1) * 32, 1) gemv_kernel(const __grid_constant__ GemvArgs A) {
     extern __shared__ __align__(128) uint8_t smem[];
+    // Programmatic dependent launch: the next kernel of the stream may start on an SM as soon as this
+    // kernel's CTA there has gone; it prefetches its weights and only then waits for this grid (below).
+    asm volatile("griddepcontrol.launch_dependents;");
     if (A.debug & 2u) return;  // measurement only: cost of an empty launch of this shape
     constexpr int NV = lane_values(ACT, MULTI);
     uint64_t *full = reinterpret_cast<uint64_t *>(smem);
     uint64_t *empty = reinterpret_cast<uint64_t *>(smem + SMEM_EMPTY_OFF);
     volatile uint32_t *ctl = reinterpret_cast<volatile uint32_t *>(smem + SMEM_CTL_OFF);
     float *red = reinterpret_cast<float *>(smem + SMEM_RED_OFF);
-    float *inv_s = reinterpret_cast<float *>(smem + SMEM_INVS_OFF);
+    float *oscale = reinterpret_cast<float *>(smem + SMEM_OSCALE_OFF);
     float *part = reinterpret_cast<float *>(smem + SMEM_PART_OFF);
     uint8_t *stages = smem + A.stage_off;
 
@@ -400,12 +406,10 @@ __global__ void __launch_bounds__((GEMV_WARPS + 1) * 32, 1) gemv_kernel(const __
     const uint32_t K = L.in_dim, B = A.nbatch, NB32 = K / 32u;
     const uint32_t CT = A.chunk_tiles, NC = A.n_chunks;  // GGUF blocks per stage, stages per row group
 
-    if (tid == 0) {
-        for (uint32_t s = 0; s < n_slots * Sk; s++) {
-            mbar_init(&full[s], 1);
-            mbar_init(&empty[s], wc);
-        }
-        ctl[0] = 0;
+    if (tid < n_slots * Sk) {
+        mbar_init(&full[tid], 1);
+        mbar_init(&empty[tid], wc);
+        if (tid == 0) ctl[0] = 0;
         mbar_fence_init();
     }
     __syncthreads();
@@ -475,125 +479,151 @@ __global__ void __launch_bounds__((GEMV_WARPS + 1) * 32, 1) gemv_kernel(const __
     // ---- consumers: activation prologue ----
     // The activation (after the optional RMSNorm / SwiGLU / GeGLU) is turned ONCE per CTA,
     // cooperatively, into the B operands of the tensor-core instructions, in shared memory (see
-    // x_layout). It is recomputed from global memory (L2) in each pass rather than staged.
+    // x_layout). It sits on the critical path of a small launch (the weights of such a launch are all
+    // in flight before it ends), so it is one trip to global memory: thread tid owns the float4s
+    // tid, tid + ct, ... of the row (eight consecutive threads = one 32-element block) and keeps
+    // them in registers across the one block-wide reduction. RMSNorm's scalar 1/rms is not applied
+    // here at all: the product is linear in it, so it multiplies the outputs (oscale).
     const uint32_t ct = n_cons * 32u;  // consumer threads = tid < ct
     const XLayout XL = x_layout(FMT, ACT, K, B, A.x_off);
+    // Everything above (and the producer's first copies) touches only this launch's weights. The
+    // activation and the outputs belong to the stream's order: wait for the preceding grid here.
+    asm volatile("griddepcontrol.wait;" ::: "memory");
 #define STRIX_CONS_BAR() asm volatile("bar.sync 15, %0;" ::"r"(ct) : "memory")
-    if (XL.end > XL.rec) {
-        // records of columns that carry no activation row stay zero (what they produce is never stored)
-        uint32_t *z = reinterpret_cast<uint32_t *>(smem + XL.rec);
-        for (uint32_t i = tid; i < (XL.end - XL.rec) / 4u; i += ct) z[i] = 0u;
-        STRIX_CONS_BAR();
-    }
-    for (uint32_t bi = 0; bi < B; bi++) {
-        const float *Aa = A.a + (size_t)bi * A.a_stride;
-        const float *Ab = A.b ? A.b + (size_t)bi * A.b_stride : nullptr;
-        float scale = 1.0f;
-        if (A.pre == STRIX_PRE_RMSNORM) {
-            // rmsnorm (crates/strix-backend-cpu/src/qwen3.rs:107-114): x * (1/sqrt(mean(x^2)+eps)) * w
-            float ss = 0.f;
-            for (uint32_t e4 = tid; e4 < K / 4u; e4 += ct) {
-                const float4 v = __ldg(reinterpret_cast<const float4 *>(Aa) + e4);
-                ss = fmaf(v.x, v.x, ss); ss = fmaf(v.y, v.y, ss); ss = fmaf(v.z, v.z, ss); ss = fmaf(v.w, v.w, ss);
-            }
-            ss = warp_sum(ss);
-            if (lane == 0) red[warp] = ss;
-            STRIX_CONS_BAR();
-            float tot = 0.f;
-            for (uint32_t w = 0; w < n_cons; w++) tot += red[w];
-            scale = 1.0f / sqrtf(tot / (float)K + A.eps);
-            STRIX_CONS_BAR();  // red[] is reused below and for the next activation row
+    {
+        constexpr uint32_t NI = 6;  // float4s a thread keeps in registers; longer rows re-load the rest
+        const uint32_t K4 = K / 4u, l8 = lane & 7u;
+        const bool need_max = ACT == STRIX_ACT_F32;
+        const bool need_red = need_max || A.pre == STRIX_PRE_RMSNORM;
+        if (XL.end > XL.rec && B > 1) {
+            // records of columns that carry no activation row stay zero (what they produce is never stored)
+            uint32_t *z = reinterpret_cast<uint32_t *>(smem + XL.rec);
+            for (uint32_t i = tid; i < (XL.end - XL.rec) / 4u; i += ct) z[i] = 0u;
         }
-        if (ACT == STRIX_ACT_F32) {
-            // largest magnitude -> power-of-two scale that puts it in [2^13, 2^14): keeps hi inside the
-            // f16 range, and lo (the 11 bits below hi) out of the subnormals except for values
-            // 2^-27 of the largest, whose contribution is below f32 resolution anyway
-            float amax = 0.f;
-            for (uint32_t e4 = tid; e4 < K / 4u; e4 += ct) {
-                const float4 v = load_post(Aa, Ab, A.pre, scale, e4);
-                amax = fmaxf(fmaxf(amax, fmaxf(fabsf(v.x), fabsf(v.y))), fmaxf(fabsf(v.z), fabsf(v.w)));
-            }
+        for (uint32_t bi = 0; bi < B; bi++) {
+            const float *Aa = A.a + (size_t)bi * A.a_stride;
+            const float *Ab = A.b ? A.b + (size_t)bi * A.b_stride : nullptr;
+            // phase A: load, apply the pre-op (without the RMSNorm scalar), partial sum of squares / maximum
+            float4 v[NI];
+            float ss = 0.f, amax = 0.f;
 #pragma unroll
-            for (int o = 16; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
-            if (lane == 0) red[warp] = amax;
-            STRIX_CONS_BAR();
-            float am = 0.f;
-            for (uint32_t w = 0; w < n_cons; w++) am = fmaxf(am, red[w]);
-            STRIX_CONS_BAR();  // red[] is written again for the next activation row
-            // s = 2^(13 - floor(log2(am))), from the exponent field; 1 for zero, denormal or non-finite input
-            const int ex = (int)((__float_as_uint(am) >> 23) & 0xffu);
-            float s = 1.0f, is = 1.0f;
-            if (ex > 0 && ex < 255) {
-                int se = 127 + 13 - (ex - 127);  // biased exponent of s
-                se = max(1, min(254, se));
-                s = __uint_as_float((uint32_t)se << 23);
-                is = 1.0f / s;  // exact: a power of two
+            for (uint32_t i = 0; i < NI; i++) {
+                const uint32_t e4 = tid + i * ct;
+                v[i] = make_float4(0.f, 0.f, 0.f, 0.f);
+                if (e4 < K4) v[i] = load_pre(Aa, Ab, A.pre, e4, ss);
+                amax = fmaxf(fmaxf(amax, fmaxf(fabsf(v[i].x), fabsf(v[i].y))), fmaxf(fabsf(v[i].z), fabsf(v[i].w)));
             }
-            if (tid == 0) inv_s[bi] = is;
-            uint4 *xb4 = reinterpret_cast<uint4 *>(smem + XL.xb);
-            // item = (block, t): the eight x values k = 4t..4t+3 and 16+4t..16+4t+3 of the block
-            for (uint32_t it = tid; it < NB32 * 4u; it += ct) {
-                const uint32_t blk = it >> 2, t = it & 3u;
-                const float4 v0 = load_post(Aa, Ab, A.pre, scale, blk * 8u + t);
-                const float4 v1 = load_post(Aa, Ab, A.pre, scale, blk * 8u + 4u + t);
-                __half h[8], l[8];
-                split_h(v0.x, s, h[0], l[0]); split_h(v0.y, s, h[1], l[1]); split_h(v0.z, s, h[2], l[2]); split_h(v0.w, s, h[3], l[3]);
-                split_h(v1.x, s, h[4], l[4]); split_h(v1.y, s, h[5], l[5]); split_h(v1.z, s, h[6], l[6]); split_h(v1.w, s, h[7], l[7]);
-                // B registers: {b0, b1} of the first MMA (k 4t..4t+3), then of the second (k 16+4t..).
-                // Q8_0 / Q6_K pair the codes (k0,k1), (k2,k3); the Q4_0 nibble decoder (k0,k2), (k1,k3).
-                uint4 uh, ul;
-                if (FMT == FMT_Q4_0) {
-                    uh = make_uint4(pack_h2(h[0], h[2]), pack_h2(h[1], h[3]), pack_h2(h[4], h[6]), pack_h2(h[5], h[7]));
-                    ul = make_uint4(pack_h2(l[0], l[2]), pack_h2(l[1], l[3]), pack_h2(l[4], l[6]), pack_h2(l[5], l[7]));
-                } else {
-                    uh = make_uint4(pack_h2(h[0], h[1]), pack_h2(h[2], h[3]), pack_h2(h[4], h[5]), pack_h2(h[6], h[7]));
-                    ul = make_uint4(pack_h2(l[0], l[1]), pack_h2(l[2], l[3]), pack_h2(l[4], l[5]), pack_h2(l[6], l[7]));
+            for (uint32_t e4 = tid + NI * ct; e4 < K4; e4 += ct) {
+                const float4 t4 = load_pre(Aa, Ab, A.pre, e4, ss);
+                amax = fmaxf(fmaxf(amax, fmaxf(fabsf(t4.x), fabsf(t4.y))), fmaxf(fabsf(t4.z), fabsf(t4.w)));
+            }
+            float s = 1.0f;  // f32 form: power-of-two scale before the f16 split
+            if (need_red) {
+                ss = warp_sum(ss);
+#pragma unroll
+                for (int o = 16; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
+                if (lane == 0) {
+                    red[warp] = ss;
+                    red[32 + warp] = amax;
                 }
-                xb4[blk * 8u * B + (2u * bi) * 4u + t] = uh;
-                xb4[blk * 8u * B + (2u * bi + 1u) * 4u + t] = ul;
+                STRIX_CONS_BAR();
+                float tot = 0.f, am = 0.f;
+                for (uint32_t w2 = 0; w2 < n_cons; w2++) {
+                    tot += red[w2];
+                    am = fmaxf(am, red[32 + w2]);
+                }
+                // rmsnorm (crates/strix-backend-cpu/src/qwen3.rs:107-114): x * (1/sqrt(mean(x^2)+eps)) * w
+                float os = A.pre == STRIX_PRE_RMSNORM ? 1.0f / sqrtf(tot / (float)K + A.eps) : 1.0f;
+                if (need_max) {
+                    // largest magnitude -> power-of-two scale that puts it in [2^13, 2^14): keeps hi inside the
+                    // f16 range, and lo (the 11 bits below hi) out of the subnormals except for values
+                    // 2^-27 of the largest, whose contribution is below f32 resolution anyway.
+                    // s = 2^(13 - floor(log2(am))), from the exponent field; 1 for zero, denormal or non-finite input
+                    const int ex = (int)((__float_as_uint(am) >> 23) & 0xffu);
+                    if (ex > 0 && ex < 255) {
+                        const int se = max(1, min(254, 127 + 13 - (ex - 127)));  // biased exponent of s
+                        s = __uint_as_float((uint32_t)se << 23);
+                        os *= __uint_as_float((uint32_t)(254 - se) << 23);  // times 1/s, exact
+                    }
+                }
+                if (tid == 0) oscale[bi] = os;
+                if (B > 1) STRIX_CONS_BAR();  // red[] is written again for the next activation row
+            } else if (tid == 0) {
+                oscale[bi] = 1.0f;
             }
-        } else {
-            // per-32 quantiser (xquant8, kernels.rs:864-876): d = amax/127, inv = d>0 ? 1/d : 0,
-            // q = clamp(rintf(x*inv)); eight lanes per block (four elements each), four blocks per warp pass
-            uint32_t *xbw = reinterpret_cast<uint32_t *>(smem + XL.xb);
-            const uint32_t l8 = lane & 7u;
-            const uint32_t nblk = (NB32 + 3u) & ~3u;
-            constexpr int BIAS = FMT == FMT_Q8_0 ? 128 : FMT == FMT_Q4_0 ? 8 : 32;
-            for (uint32_t blk = warp * 4u + (lane >> 3); blk < nblk; blk += n_cons * 4u) {
-                float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
-                if (blk < NB32) v = load_post(Aa, Ab, A.pre, scale, blk * 8u + l8);
-                float amax = fmaxf(fmaxf(fabsf(v.x), fabsf(v.y)), fmaxf(fabsf(v.z), fabsf(v.w)));
-                amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
-                amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 2));
-                amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 4));
-                const float d = amax / 127.0f;
-                const float inv = d > 0.f ? 1.0f / d : 0.f;
-                const uint32_t wq = pack4(quant1(v.x, inv), quant1(v.y, inv), quant1(v.z, inv), quant1(v.w, inv));
-                int cs = sum4(wq);
-                cs += __shfl_xor_sync(0xffffffffu, cs, 1);
-                cs += __shfl_xor_sync(0xffffffffu, cs, 2);
-                const int half_sum = cs;  // over this lane's 16-weight half of the block
-                cs += __shfl_xor_sync(0xffffffffu, cs, 4);
-                if (blk < NB32) {
-                    // lane l8 holds codes 4 l8 .. 4 l8 + 3 of the block = word (l8 >> 2) of B-register pair t = l8 & 3
-                    const uint32_t t = l8 & 3u, hf = l8 >> 2;
-                    float *rec = reinterpret_cast<float *>(smem + XL.rec);
-                    if (FMT == FMT_Q6_K) {
-                        // column 2 bi + hf sees only its own 16 weights: the other word stays zero
-                        xbw[(blk * 8u * B + (2u * bi + hf) * 4u + t) * 2u + hf] = wq;
-                        xbw[(blk * 8u * B + (2u * bi + hf) * 4u + t) * 2u + (hf ^ 1u)] = 0u;
-                        if (l8 == 0) rec[blk * 16u + bi * 4u] = d;
-                        if (t == 0) rec[blk * 16u + bi * 4u + 1u + hf] = -(float)BIAS * d * (float)half_sum;
+            // phase B: build the operands
+            for (uint32_t i = 0;; i++) {
+                const uint32_t e4 = tid + i * ct;
+                if ((tid - lane) + i * ct >= K4) break;  // the whole warp is past the row's end (the loop body shuffles)
+                const bool live = e4 < K4;
+                float4 t4 = make_float4(0.f, 0.f, 0.f, 0.f);
+                if (i < NI) {
+                    // (static indexing keeps v[] in registers)
+#pragma unroll
+                    for (uint32_t k = 0; k < NI; k++)
+                        if (k == i) t4 = v[k];
+                } else if (live) {
+                    float dummy = 0.f;
+                    t4 = load_pre(Aa, Ab, A.pre, e4, dummy);
+                }
+                const uint32_t blk = e4 >> 3, t = l8 & 3u, hf = l8 >> 2;
+                if (ACT == STRIX_ACT_F32) {
+                    // this thread's four values are one MMA's worth of k for column pair (hi, lo) of row bi:
+                    // words {b0, b1} of the first (hf = 0) or second (hf = 1) MMA of the block.
+                    // Q8_0 / Q6_K pair the codes (k0,k1), (k2,k3); the Q4_0 nibble decoder (k0,k2), (k1,k3).
+                    __half h[4], l[4];
+                    split_h(t4.x, s, h[0], l[0]); split_h(t4.y, s, h[1], l[1]);
+                    split_h(t4.z, s, h[2], l[2]); split_h(t4.w, s, h[3], l[3]);
+                    uint2 uh, ul;
+                    if (FMT == FMT_Q4_0) {
+                        uh = make_uint2(pack_h2(h[0], h[2]), pack_h2(h[1], h[3]));
+                        ul = make_uint2(pack_h2(l[0], l[2]), pack_h2(l[1], l[3]));
                     } else {
-                        xbw[(blk * 4u * B + bi * 4u + t) * 2u + hf] = wq;
-                        if (l8 == 0) {
-                            const float kf = -(float)BIAS * d * (float)cs;
-                            if (B > 1) {
-                                rec[blk * 16u + (bi >> 1) * 4u + (bi & 1u)] = d;
-                                rec[blk * 16u + (bi >> 1) * 4u + 2u + (bi & 1u)] = kf;
-                            } else {
-                                rec[blk * 2u] = d;
-                                rec[blk * 2u + 1u] = kf;
+                        uh = make_uint2(pack_h2(h[0], h[1]), pack_h2(h[2], h[3]));
+                        ul = make_uint2(pack_h2(l[0], l[1]), pack_h2(l[2], l[3]));
+                    }
+                    if (live) {
+                        uint2 *xb2 = reinterpret_cast<uint2 *>(smem + XL.xb);
+                        xb2[(blk * 8u * B + (2u * bi) * 4u + t) * 2u + hf] = uh;
+                        xb2[(blk * 8u * B + (2u * bi + 1u) * 4u + t) * 2u + hf] = ul;
+                    }
+                } else {
+                    // per-32 quantiser (xquant8, kernels.rs:864-876): d = amax/127, inv = d>0 ? 1/d : 0,
+                    // q = clamp(rintf(x*inv)); eight lanes per block, four elements each
+                    uint32_t *xbw = reinterpret_cast<uint32_t *>(smem + XL.xb);
+                    float *rec = reinterpret_cast<float *>(smem + XL.rec);
+                    constexpr int BIAS = FMT == FMT_Q8_0 ? 128 : FMT == FMT_Q4_0 ? 8 : 32;
+                    float bm = fmaxf(fmaxf(fabsf(t4.x), fabsf(t4.y)), fmaxf(fabsf(t4.z), fabsf(t4.w)));
+                    bm = fmaxf(bm, __shfl_xor_sync(0xffffffffu, bm, 1));
+                    bm = fmaxf(bm, __shfl_xor_sync(0xffffffffu, bm, 2));
+                    bm = fmaxf(bm, __shfl_xor_sync(0xffffffffu, bm, 4));
+                    const float d = bm / 127.0f;
+                    const float inv = d > 0.f ? 1.0f / d : 0.f;
+                    const uint32_t wq = pack4(quant1(t4.x, inv), quant1(t4.y, inv), quant1(t4.z, inv), quant1(t4.w, inv));
+                    int cs = sum4(wq);
+                    cs += __shfl_xor_sync(0xffffffffu, cs, 1);
+                    cs += __shfl_xor_sync(0xffffffffu, cs, 2);
+                    const int half_sum = cs;  // over this lane's 16-weight half of the block
+                    cs += __shfl_xor_sync(0xffffffffu, cs, 4);
+                    if (live) {
+                        // lane l8 holds codes 4 l8 .. 4 l8 + 3 of the block = word hf of B-register pair t
+                        if (FMT == FMT_Q6_K) {
+                            // column 2 bi + hf sees only its own 16 weights: the other word stays zero
+                            xbw[(blk * 8u * B + (2u * bi + hf) * 4u + t) * 2u + hf] = wq;
+                            xbw[(blk * 8u * B + (2u * bi + hf) * 4u + t) * 2u + (hf ^ 1u)] = 0u;
+                            if (l8 == 0) rec[blk * 16u + bi * 4u] = d;
+                            if (t == 0) rec[blk * 16u + bi * 4u + 1u + hf] = -(float)BIAS * d * (float)half_sum;
+                        } else {
+                            xbw[(blk * 4u * B + bi * 4u + t) * 2u + hf] = wq;
+                            if (l8 == 0) {
+                                const float kf = -(float)BIAS * d * (float)cs;
+                                if (B > 1) {
+                                    rec[blk * 16u + (bi >> 1) * 4u + (bi & 1u)] = d;
+                                    rec[blk * 16u + (bi >> 1) * 4u + 2u + (bi & 1u)] = kf;
+                                } else {
+                                    rec[blk * 2u] = d;
+                                    rec[blk * 2u + 1u] = kf;
+                                }
                             }
                         }
                     }
@@ -672,7 +702,7 @@ __global__ void __launch_bounds__((GEMV_WARPS + 1) * 32, 1) gemv_kernel(const __
             const uint32_t j = NV == 2 ? t : 2u * t + (uint32_t)(v & 1);
             if (j < B && row < gr.rows) {
                 float val = acc[v];
-                if (ACT == STRIX_ACT_F32) val *= inv_s[j];
+                val *= oscale[j];
                 const size_t o = (size_t)j * A.mat[gr.mat].ystride + gr.row0 + row;
                 const float *res = A.mat[gr.mat].res;
                 A.mat[gr.mat].y[o] = res ? val + res[o] : val;
@@ -766,6 +796,8 @@ bool gemv_plan(GemvArgs &a, int num_sms, size_t smem_optin) {
     a.n_tiles = tile;
     a.rows_per_tile = TILE_ROWS;
     a.multi = multi ? 1u : 0u;
+    a.pdl = 1;
+    if (const char *e = getenv("STRIX_GEMV_PDL")) a.pdl = (uint32_t)atoi(e);  // 0 = plain stream order
     a.debug = 0;
     if (const char *e = getenv("STRIX_GEMV_DEBUG")) a.debug = (uint32_t)atoi(e);  // 1 = stream only, no arithmetic
     a.smem_bytes = stage_off + a.slots * a.n_stages * a.stage_bytes;
@@ -776,8 +808,19 @@ bool gemv_plan(GemvArgs &a, int num_sms, size_t smem_optin) {
 template <int FMT, int ACT, bool MULTI>
 static cudaError_t launch_t(const GemvArgs &a, cudaStream_t stream) {
     const uint32_t threads = (a.slots * a.wc + 1u) * 32u;  // consumer warps + one producer warp
-    gemv_kernel<FMT, ACT, MULTI><<<a.grid, threads, a.smem_bytes, stream>>>(a);
-    return cudaGetLastError();
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(a.grid);
+    cfg.blockDim = dim3(threads);
+    cfg.dynamicSmemBytes = a.smem_bytes;
+    cfg.stream = stream;
+    // programmatic stream serialization: this launch may begin (weight prefetch) while the previous
+    // kernel of the stream drains; the kernel itself waits before it touches activations or outputs
+    cudaLaunchAttribute at[1];
+    at[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    at[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = at;
+    cfg.numAttrs = a.pdl ? 1u : 0u;
+    return cudaLaunchKernelEx(&cfg, gemv_kernel<FMT, ACT, MULTI>, a);
 }
 
 template <int FMT>

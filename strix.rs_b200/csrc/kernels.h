@@ -52,6 +52,7 @@ struct GemvArgs {
     uint32_t chunk_tiles;    // GGUF blocks of K per stage
     uint32_t n_chunks;       // stages per row group
     uint32_t multi;          // integer form with more than one activation row (Q4_0 / Q8_0)
+    uint32_t pdl;            // launch with programmatic stream serialization
     uint32_t grid;
     uint32_t smem_bytes;
     uint32_t debug;  // measurement only: bit 0 = stream the tiles but skip the arithmetic
