@@ -155,9 +155,9 @@ int gemv_launch(strix_cuda *h, int nmat, const Resident *const *ws, const float 
 // b activation rows (a_stride / b_stride floats apart; outputs rows-of-the-weight floats apart) share
 // one pass over the weights. Rows are taken in chunks when their activations do not fit in shared
 // memory next to at least two pipeline stages.
-int gemv_launch_rows(strix_cuda *h, int nmat, const Resident *const *ws, const float *d_a, const float *d_b, float eps,
-                     int pre, int act, float *const *d_ys, const float *const *d_res, uint32_t b, uint32_t a_stride,
-                     uint32_t b_stride, cudaStream_t stream) {
+// The launch arguments of one step (everything but the geometry, which a plan fills in).
+int gemv_fill_args(strix_cuda *h, int nmat, const Resident *const *ws, const float *d_a, const float *d_b, float eps,
+                   int pre, int act, float *const *d_ys, const float *const *d_res, GemvArgs *out) {
     if (nmat < 1 || nmat > GEMV_MAX_MATS) {
         h->err = "gemv: between 1 and 3 weights per launch";
         return -1;
@@ -178,14 +178,25 @@ int gemv_launch_rows(strix_cuda *h, int nmat, const Resident *const *ws, const f
         a.mat[m].y = d_ys[m];
         a.mat[m].res = d_res ? d_res[m] : nullptr;
         a.mat[m].rows = (uint32_t)ws[m]->rows;
+        a.mat[m].ystride = (uint32_t)ws[m]->rows;
     }
+    a.a = d_a;
+    a.b = d_b;
     a.eps = eps;
     a.pre = pre;
     a.act = act;
     a.status = h->d_status;
+    *out = a;
+    return 1;
+}
+
+int gemv_launch_rows(strix_cuda *h, int nmat, const Resident *const *ws, const float *d_a, const float *d_b, float eps,
+                     int pre, int act, float *const *d_ys, const float *const *d_res, uint32_t b, uint32_t a_stride,
+                     uint32_t b_stride, cudaStream_t stream) {
+    GemvArgs a{};
+    if (gemv_fill_args(h, nmat, ws, d_a, d_b, eps, pre, act, d_ys, d_res, &a) < 0) return -1;
     a.a_stride = a_stride;
     a.b_stride = b_stride;
-    for (int m = 0; m < nmat; m++) a.mat[m].ystride = (uint32_t)ws[m]->rows;
     uint32_t done = 0;
     while (done < b) {
         uint32_t chunk = std::min<uint32_t>(b - done, 8u);

@@ -74,6 +74,8 @@ Resident *find_weight_mut(strix_cuda *h, const char *key);
 int gemv_launch_rows(strix_cuda *h, int nmat, const Resident *const *ws, const float *d_a, const float *d_b, float eps,
                      int pre, int act, float *const *d_ys, const float *const *d_res, uint32_t b, uint32_t a_stride,
                      uint32_t b_stride, cudaStream_t stream);
+int gemv_fill_args(strix_cuda *h, int nmat, const Resident *const *ws, const float *d_a, const float *d_b, float eps,
+                   int pre, int act, float *const *d_ys, const float *const *d_res, GemvArgs *out);
 void decode_release(strix_cuda *h);  // drops a configured decode chain (its graph holds weight pointers)
 int gemv_launch(strix_cuda *h, int nmat, const Resident *const *ws, const float *d_a, const float *d_b, float eps,
                 int pre, int act, float *const *d_ys, const float *const *d_res, cudaStream_t stream);

@@ -18,9 +18,16 @@
 // values) so that the whole projection chain can be run and measured; anything else is declined
 // and the model keeps its per-weight gemv path.
 //
+// On one GPU the whole chain runs as ONE cooperative kernel (gemv_chain_kernel): the steps above
+// become a list the kernel walks, with a grid-wide barrier between steps, while its producer warps
+// keep prefetching the next steps' weights. The list holds device pointers, so it is built (and
+// uploaded) once per (hidden-state, logits) buffer pair, outside any stream capture; a pair first
+// seen inside a capture takes the launch-per-step path.
+//
 // The step is captured into a CUDA graph on the first call and replayed afterwards
 // (one H2D of h, one graph launch, one D2H of the logits, one sync per token).
 #include <algorithm>
+#include <cstdio>
 #include <cstring>
 #include <string>
 #include <vector>
@@ -51,6 +58,19 @@ struct strix_decode_state {
     float *h = nullptr, *q = nullptr, *k = nullptr, *v = nullptr, *gate = nullptr, *up = nullptr, *logits = nullptr;
     void *pin_h = nullptr, *pin_logits = nullptr;
     cudaGraphExec_t exec = nullptr;
+    // chain-kernel programs, one per (h, logits) buffer pair
+    struct Program {
+        const float *h;
+        const float *logits;
+        GemvArgs *d_steps;
+        uint32_t n_steps, smem_bytes;
+    };
+    std::vector<Program> programs;
+    uint32_t *d_gbar = nullptr;
+    unsigned long long *d_trace = nullptr;  // measurement only (STRIX_CHAIN_TRACE): per-step clocks of CTA 0
+    std::string trace_path;
+    uint32_t trace_n = 0;
+    bool chain_ok = true;  // false once a plan has failed: every call takes the launch-per-step path
 };
 
 static void decode_free(strix_decode_state *d) {
@@ -60,6 +80,19 @@ static void decode_free(strix_decode_state *d) {
     if (d->pin_h) cudaFreeHost(d->pin_h);
     if (d->pin_logits) cudaFreeHost(d->pin_logits);
     if (d->exec) cudaGraphExecDestroy(d->exec);
+    for (auto &p : d->programs) cudaFree(p.d_steps);
+    if (d->d_gbar) cudaFree(d->d_gbar);
+    if (d->d_trace) {
+        std::vector<unsigned long long> t(3 * d->trace_n);
+        if (cudaMemcpy(t.data(), d->d_trace, t.size() * sizeof(unsigned long long), cudaMemcpyDeviceToHost) == cudaSuccess) {
+            if (FILE *f = fopen(d->trace_path.c_str(), "w")) {
+                for (uint32_t i = 0; i < d->trace_n; i++)
+                    fprintf(f, "%u %llu %llu %llu\n", i, t[3 * i], t[3 * i + 1], t[3 * i + 2]);
+                fclose(f);
+            }
+        }
+        cudaFree(d->d_trace);
+    }
     delete d;
 }
 
@@ -76,38 +109,109 @@ static const float *f32_of(strix_cuda *h, const std::string &key, size_t n) {
     return it->second.p;
 }
 
-// Enqueue the whole chain on `s`. Returns 1, or <0 with h->err set.
-static int enqueue_chain(strix_cuda *h, strix_decode_state *d, cudaStream_t s) {
+// The chain as a list of steps, handed one at a time to `emit` (launch it, or collect it).
+template <typename Emit>
+static int walk_chain(strix_decode_state *d, Emit emit) {
     const float eps = d->cfg.eps;
-    const int act = d->cfg.act;
     const int gate_pre = d->cfg.act_gelu ? STRIX_PRE_GEGLU : STRIX_PRE_SWIGLU;
     for (auto &L : d->layers) {
         {
             const Resident *w[3] = {L.q, L.k, L.v};
             float *y[3] = {d->q, d->k, d->v};
-            if (gemv_launch(h, 3, w, d->h, L.attn_norm, eps, STRIX_PRE_RMSNORM, act, y, nullptr, s) < 0) return -1;
+            if (emit(3, w, d->h, L.attn_norm, eps, STRIX_PRE_RMSNORM, y, nullptr) < 0) return -1;
         }
         {   // attention stand-in: Wo is fed with q; h += Wo q
             const Resident *w[1] = {L.o};
             float *y[1] = {d->h};
             const float *r[1] = {d->h};
-            if (gemv_launch(h, 1, w, d->q, nullptr, 0.f, STRIX_PRE_NONE, act, y, r, s) < 0) return -1;
+            if (emit(1, w, d->q, nullptr, 0.f, STRIX_PRE_NONE, y, r) < 0) return -1;
         }
         {
             const Resident *w[2] = {L.gate, L.up};
             float *y[2] = {d->gate, d->up};
-            if (gemv_launch(h, 2, w, d->h, L.ffn_norm, eps, STRIX_PRE_RMSNORM, act, y, nullptr, s) < 0) return -1;
+            if (emit(2, w, d->h, L.ffn_norm, eps, STRIX_PRE_RMSNORM, y, nullptr) < 0) return -1;
         }
         {
             const Resident *w[1] = {L.down};
             float *y[1] = {d->h};
             const float *r[1] = {d->h};
-            if (gemv_launch(h, 1, w, d->gate, d->up, 0.f, gate_pre, act, y, r, s) < 0) return -1;
+            if (emit(1, w, d->gate, d->up, 0.f, gate_pre, y, r) < 0) return -1;
         }
     }
     const Resident *w[1] = {d->head};
     float *y[1] = {d->logits};
-    return gemv_launch(h, 1, w, d->h, d->out_norm, eps, STRIX_PRE_RMSNORM, act, y, nullptr, s);
+    return emit(1, w, d->h, d->out_norm, eps, STRIX_PRE_RMSNORM, y, nullptr);
+}
+
+// The chain-kernel program for the current d->h / d->logits, built on first use. Null when the
+// chain kernel cannot be used (plan failed, switched off, or a new buffer pair inside a stream capture).
+static const strix_decode_state::Program *chain_program(strix_cuda *h, strix_decode_state *d, cudaStream_t s) {
+    if (!d->chain_ok) return nullptr;
+    for (auto &p : d->programs)
+        if (p.h == d->h && p.logits == d->logits) return &p;
+    cudaStreamCaptureStatus cs = cudaStreamCaptureStatusNone;
+    if (cudaStreamIsCapturing(s, &cs) != cudaSuccess || cs != cudaStreamCaptureStatusNone) return nullptr;
+    {
+        // (measured slower than a launch per step so far: off unless asked for)
+        const char *e = getenv("STRIX_DECODE_CHAIN");
+        if (!e || atoi(e) == 0) {
+            d->chain_ok = false;
+            return nullptr;
+        }
+    }
+    std::vector<GemvArgs> steps;
+    const int act = d->cfg.act;
+    int rc = walk_chain(d, [&](int nmat, const Resident *const *w, const float *a, const float *b, float eps, int pre,
+                               float *const *y, const float *const *r) {
+        GemvArgs g{};
+        if (gemv_fill_args(h, nmat, w, a, b, eps, pre, act, y, r, &g) < 0) return -1;
+        steps.push_back(g);
+        return 1;
+    });
+    uint32_t smem = 0;
+    if (rc < 0 || !gemv_chain_plan(steps.data(), (uint32_t)steps.size(), h->num_sms, h->smem_optin, &smem)) {
+        d->chain_ok = false;
+        h->err.clear();
+        return nullptr;
+    }
+    strix_decode_state::Program p{};
+    p.h = d->h;
+    p.logits = d->logits;
+    p.n_steps = (uint32_t)steps.size();
+    p.smem_bytes = smem;
+    if (!d->d_gbar && cudaMalloc(&d->d_gbar, sizeof(uint32_t)) != cudaSuccess) {
+        d->chain_ok = false;
+        return nullptr;
+    }
+    if (const char *e = getenv("STRIX_CHAIN_TRACE")) {
+        // measurement only: the file named by the variable receives the clocks when the state is freed
+        if (!d->d_trace && cudaMalloc(&d->d_trace, 3 * steps.size() * sizeof(unsigned long long)) == cudaSuccess) {
+            cudaMemset(d->d_trace, 0, 3 * steps.size() * sizeof(unsigned long long));
+            d->trace_path = e;
+            d->trace_n = (uint32_t)steps.size();
+        }
+    }
+    if (cudaMalloc(&p.d_steps, steps.size() * sizeof(GemvArgs)) != cudaSuccess ||
+        cudaMemcpy(p.d_steps, steps.data(), steps.size() * sizeof(GemvArgs), cudaMemcpyHostToDevice) != cudaSuccess) {
+        if (p.d_steps) cudaFree(p.d_steps);
+        d->chain_ok = false;
+        return nullptr;
+    }
+    d->programs.push_back(p);
+    return &d->programs.back();
+}
+
+// Enqueue the whole chain on `s`. Returns 1, or <0 with h->err set.
+static int enqueue_chain(strix_cuda *h, strix_decode_state *d, cudaStream_t s) {
+    if (const strix_decode_state::Program *p = chain_program(h, d, s)) {
+        CU_TRY(h, launch_gemv_chain(p->d_steps, p->n_steps, d->cfg.act, d->d_gbar, h->num_sms, p->smem_bytes, d->d_trace, s));
+        return 1;
+    }
+    const int act = d->cfg.act;
+    return walk_chain(d, [&](int nmat, const Resident *const *w, const float *a, const float *b, float eps, int pre,
+                             float *const *y, const float *const *r) {
+        return gemv_launch(h, nmat, w, a, b, eps, pre, act, y, r, s);
+    });
 }
 
 extern "C" {
@@ -215,6 +319,7 @@ int strix_cuda_decode_step(strix_cuda *h, const float *hvec, size_t pos, float *
     CU_TRY(h, cudaSetDevice(h->device));
     if (!d->exec) {
         cudaGraph_t g = nullptr;
+        (void)chain_program(h, d, h->stream);  // built (and uploaded) before the capture starts
         CU_TRY(h, cudaStreamBeginCapture(h->stream, cudaStreamCaptureModeThreadLocal));
         int rc = enqueue_chain(h, d, h->stream);
         cudaError_t e = cudaStreamEndCapture(h->stream, &g);

@@ -357,9 +357,9 @@ __device__ __forceinline__ void tile_mac(uint32_t ta, uint32_t da, uint32_t xb_a
 // applied WITHOUT its scalar 1/rms (the caller multiplies the outputs by it); `ss` collects the
 // squares of the raw values for it.
 __device__ __forceinline__ float4 load_pre(const float *Aa, const float *Ab, int pre, uint32_t e4, float &ss) {
-    float4 a4 = __ldg(reinterpret_cast<const float4 *>(Aa) + e4);
+    float4 a4 = __ldcg(reinterpret_cast<const float4 *>(Aa) + e4);
     if (pre != STRIX_PRE_NONE) {
-        const float4 b4 = __ldg(reinterpret_cast<const float4 *>(Ab) + e4);
+        const float4 b4 = __ldcg(reinterpret_cast<const float4 *>(Ab) + e4);
         if (pre == STRIX_PRE_RMSNORM) {
             ss = fmaf(a4.x, a4.x, ss); ss = fmaf(a4.y, a4.y, ss); ss = fmaf(a4.z, a4.z, ss); ss = fmaf(a4.w, a4.w, ss);
             a4.x *= b4.x; a4.y *= b4.y; a4.z *= b4.z; a4.w *= b4.w;
@@ -381,115 +381,128 @@ __device__ __forceinline__ void split_h(float x, float s, __half &hi, __half &lo
     lo = __float2half_rn(v - __half2float(hi));
 }
 
+// Per-thread view of the CTA: geometry that is the same for every step a CTA runs, and the ring
+// positions that carry over from one step to the next.
+struct Cta {
+    uint8_t *smem;
+    uint32_t tid, lane, warp, grid, bid;
+    uint32_t wc, n_slots, n_cons, Sk, stage_bytes, stage_off;
+    uint32_t *status;
+    // producer: stage hand-overs every slot has seen so far; consumer: position in the slot's ring and
+    // the parity of the phase to wait for
+    uint32_t tq_base, sl, ph;
+};
+__device__ __forceinline__ uint64_t *cta_full(const Cta &C) { return reinterpret_cast<uint64_t *>(C.smem); }
+__device__ __forceinline__ uint64_t *cta_empty(const Cta &C) { return reinterpret_cast<uint64_t *>(C.smem + SMEM_EMPTY_OFF); }
+__device__ __forceinline__ volatile uint32_t *cta_ctl(const Cta &C) {
+    return reinterpret_cast<volatile uint32_t *>(C.smem + SMEM_CTL_OFF);
+}
+// row groups of one step are dealt round-robin to the CTAs, starting at a CTA that moves with the
+// step (so that the CTAs that get one group more are not always the same ones)
+__device__ __forceinline__ uint32_t cta_rank(const Cta &C, const GemvArgs &A) {
+    const uint32_t r = C.bid + A.rot;
+    return r >= C.grid ? r - C.grid : r;
+}
+__device__ __forceinline__ uint32_t cta_groups(const Cta &C, const GemvArgs &A) {
+    const uint32_t r = cta_rank(C, A);
+    return A.n_tiles > r ? (A.n_tiles - r + C.grid - 1) / C.grid : 0;
+}
+
+// ---- producer (one warp): one bulk copy per stage (a run of CT tiles of one row group). Slot k owns
+//      stages k Sk .. k Sk + Sk - 1 and takes the CTA's row groups k, k + slots, ...; copies are issued in
+//      the order (round of row groups, chunk, slot), so every slot's ring fills at the same pace. A
+//      slot without a row group in the last round still gets its (empty) hand-overs, so that all rings
+//      stay in step. The 32 lanes share the work: each pass they look at the next 32 entries, poll
+//      their stages once, and the leading run of free ones is issued - strictly in order, so a lane
+//      that polls a stage for lap n can rely on lap n - 1 having been issued. ----
+__device__ __forceinline__ void producer_step(const GemvArgs &A, Cta &C) {
+    uint64_t *full = cta_full(C), *empty = cta_empty(C);
+    volatile uint32_t *ctl = cta_ctl(C);
+    uint8_t *stages = C.smem + C.stage_off;
+    const uint32_t n_slots = C.n_slots, Sk = C.Sk, lane = C.lane;
+    const uint32_t my_n = cta_groups(C, A), rank = cta_rank(C, A);
+    const uint32_t CT = A.chunk_tiles, NC = A.n_chunks;
+    const uint32_t rounds = (my_n + n_slots - 1) / n_slots;
+    uint32_t total = rounds * NC * n_slots;
+    // (measurement mode "stop after the prologue": only the copies that need no consumer are issued)
+    if ((A.debug & 4u) && total > n_slots * Sk) total = n_slots * Sk;
+    const uint32_t win = n_slots * Sk < 32u ? n_slots * Sk : 32u;
+    uint32_t base = 0, idle = 0;
+    while (base < total && !ctl[0]) {  // after an abort nothing more is issued
+        const uint32_t q = base + lane;
+        bool ready = false, live = false;
+        uint32_t s = 0, n = 0, c = 0;
+        if (lane < win && q < total) {
+            const uint32_t tq = q / n_slots, k = q - tq * n_slots;  // tq: this step's hand-over number in slot k
+            const uint32_t r = tq / NC;
+            c = tq - r * NC;
+            n = r * n_slots + k;
+            live = n < my_n;
+            const uint32_t gq = C.tq_base + tq, lap = gq / Sk;
+            s = k * Sk + (gq - lap * Sk);
+            ready = lap == 0 || mbar_try_wait(&empty[s], (lap - 1u) & 1u);
+        }
+        const uint32_t m = __ballot_sync(0xffffffffu, ready);
+        const uint32_t nrun = (m == 0xffffffffu) ? 32u : (uint32_t)__ffs((int)~m) - 1u;  // leading run of ready lanes
+        if (lane < nrun && q < total) {
+            if (live) {
+                const GroupRef gr = group_ref(A, rank + n * C.grid);
+                const uint32_t nbk = min(CT, A.L.nb - c * CT);
+                const uint32_t bytes = nbk * A.L.tile_bytes;
+                mbar_arrive_expect_tx(&full[s], bytes);
+                bulk_g2s(stages + (uint64_t)s * C.stage_bytes, gr.src + (uint64_t)c * CT * A.L.tile_bytes, bytes, &full[s]);
+            } else {
+                mbar_arrive(&full[s]);  // an empty hand-over: the phase completes at once
+            }
+        }
+        base += nrun;
+        // bounded like every other wait: 2^22 passes without progress
+        if (nrun) {
+            idle = 0;
+        } else if (++idle >= (1u << 22)) {
+            if (lane == 0) {
+                if (C.status) atomicOr(C.status, STATUS_WAIT_TIMEOUT);
+                ctl[0] = 1;
+            }
+            idle = 0;
+        }
+        __syncwarp();
+    }
+    if (ctl[0]) {
+        // after an abort consumers stop waiting: let the copies still in flight land (bounded) before
+        // the CTA's shared memory is released. Lane k looks after slot k's last Sk hand-overs.
+        if (lane < n_slots && base > lane) {
+            const uint32_t tq_last = C.tq_base + (base - 1u - lane) / n_slots;
+            for (uint32_t gq = (tq_last + 1u > Sk ? tq_last + 1u - Sk : 0u); gq <= tq_last; gq++) {
+                uint64_t *bar = &full[lane * Sk + gq % Sk];
+                for (uint32_t it = 0; it < (1u << 16); ++it)
+                    if (mbar_try_wait(bar, (gq / Sk) & 1u)) break;
+            }
+        }
+    } else {
+        C.tq_base += rounds * NC;
+    }
+}
+
+// ---- consumers: activation prologue ----
+// The activation (after the optional RMSNorm / SwiGLU / GeGLU) is turned ONCE per CTA,
+// cooperatively, into the B operands of the tensor-core instructions, in shared memory (see
+// x_layout). It sits on the critical path of a small launch (the weights of such a launch are all
+// in flight before it ends), so it is one trip to global memory: thread tid owns the float4s
+// tid, tid + ct, ... of the row (eight consecutive threads = one 32-element block) and keeps
+// them in registers across the one block-wide reduction. RMSNorm's scalar 1/rms is not applied
+// here at all: the product is linear in it, so it multiplies the outputs (oscale).
+// (Activations are read past L1: inside a chain kernel another CTA wrote them a moment ago.)
+#define STRIX_CONS_BAR() asm volatile("bar.sync 15, %0;" ::"r"(ct) : "memory")
 template <int FMT, int ACT, bool MULTI>
-__global__ void __launch_bounds__((GEMV_WARPS + 1) * 32, 1) gemv_kernel(const __grid_constant__ GemvArgs A) {
-    extern __shared__ __align__(128) uint8_t smem[];
-    // Programmatic dependent launch: the next kernel of the stream may start on an SM as soon as this
-    // kernel's CTA there has gone; it prefetches its weights and only then waits for this grid (below).
-    asm volatile("griddepcontrol.launch_dependents;");
-    if (A.debug & 2u) return;  // measurement only: cost of an empty launch of this shape
-    constexpr int NV = lane_values(ACT, MULTI);
-    uint64_t *full = reinterpret_cast<uint64_t *>(smem);
-    uint64_t *empty = reinterpret_cast<uint64_t *>(smem + SMEM_EMPTY_OFF);
-    volatile uint32_t *ctl = reinterpret_cast<volatile uint32_t *>(smem + SMEM_CTL_OFF);
+__device__ __forceinline__ void consumer_prologue(const GemvArgs &A, const Cta &C) {
+    uint8_t *smem = C.smem;
     float *red = reinterpret_cast<float *>(smem + SMEM_RED_OFF);
     float *oscale = reinterpret_cast<float *>(smem + SMEM_OSCALE_OFF);
-    float *part = reinterpret_cast<float *>(smem + SMEM_PART_OFF);
-    uint8_t *stages = smem + A.stage_off;
-
-    const uint32_t tid = threadIdx.x, lane = tid & 31u, warp = tid >> 5;
-    const uint32_t wc = A.wc, n_slots = A.slots;
-    const uint32_t n_cons = n_slots * wc;  // consumer warps; warp n_cons is the producer
-    const uint32_t Sk = A.n_stages, grid = gridDim.x, bid = blockIdx.x;  // Sk: stages per slot
-    const uint32_t my_n = (A.n_tiles > bid) ? (A.n_tiles - bid + grid - 1) / grid : 0;  // row groups of this CTA
-    const RowLayout L = A.L;
-    const uint32_t K = L.in_dim, B = A.nbatch, NB32 = K / 32u;
-    const uint32_t CT = A.chunk_tiles, NC = A.n_chunks;  // GGUF blocks per stage, stages per row group
-
-    if (tid < n_slots * Sk) {
-        mbar_init(&full[tid], 1);
-        mbar_init(&empty[tid], wc);
-        if (tid == 0) ctl[0] = 0;
-        mbar_fence_init();
-    }
-    __syncthreads();
-    if (warp == n_cons) {
-        // ---- producer: one bulk copy per stage (a run of CT tiles of one row group). Slot k owns stages
-        //      k Sk .. k Sk + Sk - 1 and takes the CTA's row groups k, k + slots, ...; copies are issued
-        //      in the order (round of row groups, chunk, slot), so every slot's ring fills at the same
-        //      pace. The 32 lanes share the work: each pass they look at the next 32 entries, poll
-        //      their stages once, and the leading run of free ones is issued - strictly in order, so
-        //      a lane that polls a stage for lap n can rely on lap n - 1 having been issued. ----
-        const uint32_t rounds = (my_n + n_slots - 1) / n_slots;
-        uint32_t total = rounds * NC * n_slots;
-        // (measurement mode "stop after the prologue": only the copies that need no consumer are issued)
-        if ((A.debug & 4u) && total > n_slots * Sk) total = n_slots * Sk;
-        const uint32_t win = n_slots * Sk < 32u ? n_slots * Sk : 32u;
-        uint32_t base = 0, idle = 0;
-        while (base < total && !ctl[0]) {  // after an abort nothing more is issued
-            const uint32_t q = base + lane;
-            bool ready = false, live = false;
-            uint32_t s = 0, n = 0, c = 0;
-            if (lane < win && q < total) {
-                const uint32_t tq = q / n_slots, k = q - tq * n_slots;  // tq: chunk counter of slot k
-                const uint32_t r = tq / NC;
-                c = tq - r * NC;
-                n = r * n_slots + k;
-                live = n < my_n;
-                const uint32_t lap = tq / Sk;
-                s = k * Sk + (tq - lap * Sk);
-                ready = !live || lap == 0 || mbar_try_wait(&empty[s], (lap - 1u) & 1u);
-            }
-            const uint32_t m = __ballot_sync(0xffffffffu, ready);
-            const uint32_t nrun = (m == 0xffffffffu) ? 32u : (uint32_t)__ffs((int)~m) - 1u;  // leading run of ready lanes
-            if (lane < nrun && live) {
-                const GroupRef gr = group_ref(A, bid + n * grid);
-                const uint32_t nbk = min(CT, L.nb - c * CT);
-                const uint32_t bytes = nbk * L.tile_bytes;
-                mbar_arrive_expect_tx(&full[s], bytes);
-                bulk_g2s(stages + (uint64_t)s * A.stage_bytes, gr.src + (uint64_t)c * CT * L.tile_bytes, bytes, &full[s]);
-            }
-            base += nrun;
-            // bounded like every other wait: 2^22 passes without progress
-            if (nrun) {
-                idle = 0;
-            } else if (++idle >= (1u << 22)) {
-                if (lane == 0) {
-                    if (A.status) atomicOr(A.status, STATUS_WAIT_TIMEOUT);
-                    ctl[0] = 1;
-                }
-                idle = 0;
-            }
-            __syncwarp();
-        }
-        if (ctl[0] && lane < n_slots && base > lane) {
-            // after an abort consumers stop waiting: let the copies still in flight land (bounded)
-            // before the CTA's shared memory is released. Lane k looks after slot k's last Sk copies.
-            const uint32_t tq_last = (base - 1u - lane) / n_slots;
-            for (uint32_t tq = (tq_last + 1u > Sk ? tq_last + 1u - Sk : 0u); tq <= tq_last; tq++) {
-                if ((tq / NC) * n_slots + lane >= my_n) continue;  // an entry past the last row group: nothing was copied
-                uint64_t *bar = &full[lane * Sk + tq % Sk];
-                for (uint32_t it = 0; it < (1u << 16); ++it)
-                    if (mbar_try_wait(bar, (tq / Sk) & 1u)) break;
-            }
-        }
-        return;
-    }
-
-    // ---- consumers: activation prologue ----
-    // The activation (after the optional RMSNorm / SwiGLU / GeGLU) is turned ONCE per CTA,
-    // cooperatively, into the B operands of the tensor-core instructions, in shared memory (see
-    // x_layout). It sits on the critical path of a small launch (the weights of such a launch are all
-    // in flight before it ends), so it is one trip to global memory: thread tid owns the float4s
-    // tid, tid + ct, ... of the row (eight consecutive threads = one 32-element block) and keeps
-    // them in registers across the one block-wide reduction. RMSNorm's scalar 1/rms is not applied
-    // here at all: the product is linear in it, so it multiplies the outputs (oscale).
+    const uint32_t tid = C.tid, lane = C.lane, warp = C.warp, n_cons = C.n_cons;
+    const uint32_t K = A.L.in_dim, B = A.nbatch;
     const uint32_t ct = n_cons * 32u;  // consumer threads = tid < ct
     const XLayout XL = x_layout(FMT, ACT, K, B, A.x_off);
-    // Everything above (and the producer's first copies) touches only this launch's weights. The
-    // activation and the outputs belong to the stream's order: wait for the preceding grid here.
-    asm volatile("griddepcontrol.wait;" ::: "memory");
-#define STRIX_CONS_BAR() asm volatile("bar.sync 15, %0;" ::"r"(ct) : "memory")
     {
         constexpr uint32_t NI = 6;  // float4s a thread keeps in registers; longer rows re-load the rest
         const uint32_t K4 = K / 4u, l8 = lane & 7u;
@@ -632,13 +645,26 @@ __global__ void __launch_bounds__((GEMV_WARPS + 1) * 32, 1) gemv_kernel(const __
         }
     }
     STRIX_CONS_BAR();
-#undef STRIX_CONS_BAR
-    if (A.debug & 4u) return;  // measurement only: stop after the activation prologue
+}
 
-    // ---- stream the row groups: slot k takes the CTA's groups k, k + slots, ...; within a stage the
-    //      wc warps of the slot take tiles w, w + wc, ... ----
+// ---- consumers: stream the row groups. Slot k takes the CTA's groups k, k + slots, ...; within a
+//      stage the wc warps of the slot take tiles w, w + wc, ... ----
+template <int FMT, int ACT, bool MULTI>
+__device__ __forceinline__ void consumer_groups(const GemvArgs &A, Cta &C) {
+    constexpr int NV = lane_values(ACT, MULTI);
+    uint8_t *smem = C.smem;
+    uint64_t *full = cta_full(C), *empty = cta_empty(C);
+    volatile uint32_t *ctl = cta_ctl(C);
+    const float *oscale = reinterpret_cast<const float *>(smem + SMEM_OSCALE_OFF);
+    float *part = reinterpret_cast<float *>(smem + SMEM_PART_OFF);
+    const uint32_t lane = C.lane, warp = C.warp, wc = C.wc, n_slots = C.n_slots, Sk = C.Sk;
+    const RowLayout L = A.L;
+    const uint32_t B = A.nbatch, CT = A.chunk_tiles, NC = A.n_chunks;
+    const uint32_t my_n = cta_groups(C, A), rank = cta_rank(C, A);
+    const uint32_t rounds = (my_n + n_slots - 1) / n_slots;
+    const XLayout XL = x_layout(FMT, ACT, L.in_dim, B, A.x_off);
     const uint32_t slot = warp / wc, w = warp - slot * wc;
-    const uint32_t st0 = smem_u32(stages) + slot * Sk * A.stage_bytes;
+    const uint32_t st0 = smem_u32(smem + C.stage_off) + slot * Sk * C.stage_bytes;
     const bool skip = (A.debug & 1u) != 0u;
     const uint32_t g = lane >> 2, t = lane & 3u;
     // this lane's B-operand and record addresses for block 0 (see x_layout). Lanes whose MMA column
@@ -649,19 +675,19 @@ __global__ void __launch_bounds__((GEMV_WARPS + 1) * 32, 1) gemv_kernel(const __
     const uint32_t xr_l = xs0 + XL.rec + ((FMT == FMT_Q6_K || MULTI) ? 16u * t : 0u);
     const TileConsts TC = tile_consts<FMT, ACT>();
     float *my_part = part + (size_t)(warp * 32u + lane) * NV;
-    uint32_t sl = 0, ph = 0;  // position in the slot's ring, parity of the phase to wait for
-    for (uint32_t n = slot; n < my_n; n += n_slots) {
-        const GroupRef gr = group_ref(A, bid + n * grid);
+    for (uint32_t r = 0; r < rounds; r++) {
+        const uint32_t n = r * n_slots + slot;
+        const bool live = n < my_n;  // in the last round a slot may have no row group: its hand-overs are empty
         float acc[NV];
 #pragma unroll
         for (int v = 0; v < NV; v++) acc[v] = 0.f;
         for (uint32_t c = 0; c < NC; c++) {
             // once any wait has run out, nobody waits again: the loop runs to its end on whatever is in
             // shared memory and the status word reports it
-            if (!ctl[0] && !mbar_wait_bounded(&full[slot * Sk + sl], ph, A.status)) ctl[0] = 1;
-            const uint32_t base = st0 + sl * A.stage_bytes;
+            if (!ctl[0] && !mbar_wait_bounded(&full[slot * Sk + C.sl], C.ph, C.status)) ctl[0] = 1;
+            const uint32_t base = st0 + C.sl * C.stage_bytes;
             const uint32_t nbk = min(CT, L.nb - c * CT);
-            if (!skip) {
+            if (live && !skip) {
                 // tiles w, w + wc, ... of the stage; block index of tile i = first block of the stage + i
                 // (addresses by multiply-add: that pipe has room, the logic pipe does not)
                 constexpr uint32_t SUB = FMT == FMT_Q6_K ? 8u : 1u;
@@ -679,9 +705,11 @@ __global__ void __launch_bounds__((GEMV_WARPS + 1) * 32, 1) gemv_kernel(const __
                 }
             }
             __syncwarp();
-            if (lane == 0) mbar_arrive(&empty[slot * Sk + sl]);  // this warp's reads of the stage are complete
-            if (++sl == Sk) { sl = 0; ph ^= 1u; }
+            if (lane == 0) mbar_arrive(&empty[slot * Sk + C.sl]);  // this warp's reads of the stage are complete
+            if (++C.sl == Sk) { C.sl = 0; C.ph ^= 1u; }
         }
+        if (!live) continue;
+        const GroupRef gr = group_ref(A, rank + n * C.grid);
         // ---- the row group is complete: add up the slot's partial sums (warp order) and store ----
         if (wc > 1) {
             // (first barrier: warp 0 has finished reading the previous group's partial sums)
@@ -705,11 +733,133 @@ __global__ void __launch_bounds__((GEMV_WARPS + 1) * 32, 1) gemv_kernel(const __
                 val *= oscale[j];
                 const size_t o = (size_t)j * A.mat[gr.mat].ystride + gr.row0 + row;
                 const float *res = A.mat[gr.mat].res;
-                A.mat[gr.mat].y[o] = res ? val + res[o] : val;
+                A.mat[gr.mat].y[o] = res ? val + __ldcg(res + o) : val;
             }
         }
     }
 }
+
+__device__ __forceinline__ Cta cta_init(uint8_t *smem, uint32_t wc, uint32_t n_slots, uint32_t Sk, uint32_t stage_bytes,
+                                        uint32_t stage_off, uint32_t *status) {
+    Cta C;
+    C.smem = smem;
+    C.tid = threadIdx.x;
+    C.lane = C.tid & 31u;
+    C.warp = C.tid >> 5;
+    C.grid = gridDim.x;
+    C.bid = blockIdx.x;
+    C.wc = wc;
+    C.n_slots = n_slots;
+    C.n_cons = n_slots * wc;  // consumer warps; warp n_cons is the producer
+    C.Sk = Sk;
+    C.stage_bytes = stage_bytes;
+    C.stage_off = stage_off;
+    C.status = status;
+    C.tq_base = C.sl = C.ph = 0;
+    if (C.tid < n_slots * Sk) {
+        mbar_init(&cta_full(C)[C.tid], 1);
+        mbar_init(&cta_empty(C)[C.tid], wc);
+        if (C.tid == 0) cta_ctl(C)[0] = 0;
+        mbar_fence_init();
+    }
+    __syncthreads();
+    return C;
+}
+
+// One launch = one step: up to three weights that share an activation.
+template <int FMT, int ACT, bool MULTI>
+__global__ void __launch_bounds__((GEMV_WARPS + 1) * 32, 1) gemv_kernel(const __grid_constant__ GemvArgs A) {
+    extern __shared__ __align__(128) uint8_t smem[];
+    // Programmatic dependent launch: the next kernel of the stream may start on an SM as soon as this
+    // kernel's CTA there has gone; it prefetches its weights and only then waits for this grid (below).
+    asm volatile("griddepcontrol.launch_dependents;");
+    if (A.debug & 2u) return;  // measurement only: cost of an empty launch of this shape
+    Cta C = cta_init(smem, A.wc, A.slots, A.n_stages, A.stage_bytes, A.stage_off, A.status);
+    if (C.warp == C.n_cons) {
+        producer_step(A, C);
+        return;
+    }
+    // Everything above (and the producer's copies) touches only this launch's weights. The activation
+    // and the outputs belong to the stream's order: wait for the preceding grid here.
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    consumer_prologue<FMT, ACT, MULTI>(A, C);
+    if (A.debug & 4u) return;  // measurement only: stop after the activation prologue
+    consumer_groups<FMT, ACT, MULTI>(A, C);
+}
+
+// A whole chain of steps in ONE cooperative launch (one CTA per SM, all resident): the decode
+// projection chain. Every step needs the outputs of the one before it, so between steps the CTAs
+// meet at a grid-wide barrier (a counter in global memory; the wait is bounded like every other).
+// What the single launches cannot do happens here: the producer warp does not wait at that barrier -
+// it goes on filling the rings with the NEXT steps' weights (they depend on nothing) while the
+// consumers finish this step and exchange activations, so HBM never idles between projections.
+template <int ACT>
+__global__ void __launch_bounds__((GEMV_WARPS + 1) * 32, 1)
+gemv_chain_kernel(const GemvArgs *__restrict__ steps, uint32_t n_steps, uint32_t *gbar, unsigned long long *trace) {
+    extern __shared__ __align__(128) uint8_t smem[];
+    const GemvArgs &A0 = steps[0];
+    Cta C = cta_init(smem, A0.wc, A0.slots, A0.n_stages, A0.stage_bytes, A0.stage_off, A0.status);
+    volatile uint32_t *ctl = cta_ctl(C);
+    if (C.warp == C.n_cons) {
+        for (uint32_t s = 0; s < n_steps && !ctl[0]; s++) producer_step(steps[s], C);
+        return;
+    }
+    const uint32_t ct = C.n_cons * 32u;
+    for (uint32_t s = 0; s < n_steps; s++) {
+        const GemvArgs &A = steps[s];
+        if (s > 0) {
+            // grid barrier: every CTA has stored the outputs of step s - 1
+            STRIX_CONS_BAR();
+            if (C.tid == 0) {
+                __threadfence();
+                atomicAdd(gbar, 1u);
+                const uint32_t want = s * C.grid;
+                bool ok = ctl[0] != 0;
+                for (uint32_t it = 0; it < (1u << 22) && !ok; ++it) {
+                    uint32_t seen;
+                    asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(seen) : "l"(gbar) : "memory");
+                    ok = seen >= want;
+                    // another CTA gave up: do not sit out the full bound
+                    if (!ok && (it & 1023u) == 1023u && C.status && (*(volatile uint32_t *)C.status & STATUS_WAIT_TIMEOUT)) break;
+                }
+                if (!ok) {
+                    if (C.status) atomicOr(C.status, STATUS_WAIT_TIMEOUT);
+                    ctl[0] = 1;
+                }
+            }
+            STRIX_CONS_BAR();
+        }
+        // (measurement only: with a trace buffer, CTA 0 notes the time after the barrier, after the
+        // prologue and after its row groups)
+#define STRIX_TRACE(slot_)                                                                  \
+    if (trace && C.bid == 0 && C.tid == 0) {                                                \
+        unsigned long long t_;                                                              \
+        asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t_));                              \
+        trace[3u * s + (slot_)] = t_;                                                       \
+    }
+        STRIX_TRACE(0)
+        switch (A.L.fmt) {
+            case FMT_Q4_0:
+                consumer_prologue<FMT_Q4_0, ACT, false>(A, C);
+                STRIX_TRACE(1)
+                consumer_groups<FMT_Q4_0, ACT, false>(A, C);
+                break;
+            case FMT_Q8_0:
+                consumer_prologue<FMT_Q8_0, ACT, false>(A, C);
+                STRIX_TRACE(1)
+                consumer_groups<FMT_Q8_0, ACT, false>(A, C);
+                break;
+            default:
+                consumer_prologue<FMT_Q6_K, ACT, false>(A, C);
+                STRIX_TRACE(1)
+                consumer_groups<FMT_Q6_K, ACT, false>(A, C);
+                break;
+        }
+        STRIX_TRACE(2)
+#undef STRIX_TRACE
+    }
+}
+#undef STRIX_CONS_BAR
 
 // ------------------------------------------------------------------ host side
 static inline uint32_t align128u(uint32_t v) { return (v + 127u) & ~127u; }
@@ -841,6 +991,79 @@ cudaError_t launch_gemv(const GemvArgs &a, cudaStream_t stream) {
     }
 }
 
+// Geometry for a chain of steps run by one cooperative launch: the rings (warps per row group, slots,
+// stages per slot, stage size) and the activation region are the same for every step, because the
+// rings carry over from step to step; only the run of tiles per stage follows each step's tile size.
+bool gemv_chain_plan(GemvArgs *steps, uint32_t n, int num_sms, size_t smem_optin, uint32_t *smem_bytes) {
+    if (n == 0) return false;
+    const uint32_t pool = (uint32_t)GEMV_WARPS;
+    const uint32_t budget = (uint32_t)smem_optin - 1024u;
+    uint32_t wc = 8;
+    if (const char *e = getenv("STRIX_CHAIN_WC")) wc = (uint32_t)atoi(e);  // tuning knob
+    if (wc < 2 || pool % wc != 0 || pool / wc > 12) return false;
+    const uint32_t slots = pool / wc;
+    uint32_t sk = 4;
+    if (const char *e = getenv("STRIX_CHAIN_STAGES")) sk = (uint32_t)atoi(e);
+    if (sk < 2 || slots * sk > (uint32_t)GEMV_MAX_STAGES) return false;
+    const uint32_t x_off = align128u(SMEM_PART_OFF + pool * 32u * 2u * 4u);
+    uint32_t x_end = x_off;
+    for (uint32_t i = 0; i < n; i++) {
+        GemvArgs &a = steps[i];
+        if (a.act != steps[0].act || a.L.in_dim == 0 || a.L.in_dim % 32 != 0) return false;
+        a.nbatch = 1;
+        const XLayout XL = x_layout(a.L.fmt, a.act, a.L.in_dim, 1, x_off);
+        if (XL.end > x_end) x_end = XL.end;
+    }
+    const uint32_t stage_off = align128u(x_end);
+    if (stage_off >= budget) return false;
+    uint32_t sb = ((budget - stage_off) / (slots * sk)) & ~127u;
+    if (sb > 16384u) sb = 16384u;
+    for (uint32_t i = 0; i < n; i++) {
+        GemvArgs &a = steps[i];
+        const uint32_t sub = a.L.fmt == FMT_Q6_K ? 8u : 1u;
+        const uint32_t quantum = (wc + sub - 1) / sub;
+        uint32_t ct = (sb / a.L.tile_bytes) / quantum * quantum;
+        if (ct == 0) return false;  // a stage cannot hold one tile per warp of the slot
+        if (ct > a.L.nb) ct = a.L.nb;
+        a.wc = wc;
+        a.slots = slots;
+        a.n_stages = sk;
+        a.stage_bytes = sb;
+        a.stage_off = stage_off;
+        a.x_off = x_off;
+        a.chunk_tiles = ct;
+        a.n_chunks = (a.L.nb + ct - 1) / ct;
+        uint32_t tile = 0;
+        for (int m = 0; m < a.nmat; m++) {
+            a.mat[m].tile0 = tile;
+            tile += (a.mat[m].rows + TILE_ROWS - 1) / TILE_ROWS;
+        }
+        a.n_tiles = tile;
+        a.rows_per_tile = TILE_ROWS;
+        a.multi = 0;
+        a.pdl = 0;
+        a.debug = 0;
+        if (const char *e = getenv("STRIX_GEMV_DEBUG")) a.debug = (uint32_t)atoi(e) & 1u;  // 1 = no arithmetic
+        a.rot = (i * 37u) % (uint32_t)num_sms;
+        a.grid = (uint32_t)num_sms;
+        a.smem_bytes = stage_off + slots * sk * sb;
+    }
+    *smem_bytes = steps[0].smem_bytes;
+    return true;
+}
+
+cudaError_t launch_gemv_chain(const GemvArgs *d_steps, uint32_t n_steps, int act, uint32_t *d_gbar, int num_sms,
+                              uint32_t smem_bytes, unsigned long long *d_trace, cudaStream_t stream) {
+    cudaError_t e = cudaMemsetAsync(d_gbar, 0, sizeof(uint32_t), stream);
+    if (e != cudaSuccess) return e;
+    void *args[4] = {(void *)&d_steps, (void *)&n_steps, (void *)&d_gbar, (void *)&d_trace};
+    const dim3 grid((unsigned)num_sms), block((GEMV_WARPS + 1) * 32);
+    // cooperative: the CTAs wait on one another between steps, so all of them must be resident
+    if (act == STRIX_ACT_F32)
+        return cudaLaunchCooperativeKernel((const void *)gemv_chain_kernel<STRIX_ACT_F32>, grid, block, args, smem_bytes, stream);
+    return cudaLaunchCooperativeKernel((const void *)gemv_chain_kernel<STRIX_ACT_Q8DOT>, grid, block, args, smem_bytes, stream);
+}
+
 template <int FMT>
 static cudaError_t optin_fmt(size_t b) {
     cudaError_t e = cudaSuccess;
@@ -858,7 +1081,12 @@ cudaError_t gemv_prepare_device(size_t smem_optin) {
     cudaError_t e;
     if ((e = optin_fmt<FMT_Q4_0>(smem_optin)) != cudaSuccess) return e;
     if ((e = optin_fmt<FMT_Q8_0>(smem_optin)) != cudaSuccess) return e;
-    return optin_fmt<FMT_Q6_K>(smem_optin);
+    if ((e = optin_fmt<FMT_Q6_K>(smem_optin)) != cudaSuccess) return e;
+    if ((e = cudaFuncSetAttribute(gemv_chain_kernel<STRIX_ACT_F32>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                  (int)smem_optin)) != cudaSuccess)
+        return e;
+    return cudaFuncSetAttribute(gemv_chain_kernel<STRIX_ACT_Q8DOT>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                (int)smem_optin);
 }
 
 // ---- the activation quantiser on its own (xquant8_rows, kernels.rs:1000-1013) ----

@@ -53,6 +53,7 @@ struct GemvArgs {
     uint32_t n_chunks;       // stages per row group
     uint32_t multi;          // integer form with more than one activation row (Q4_0 / Q8_0)
     uint32_t pdl;            // launch with programmatic stream serialization
+    uint32_t rot;            // chain kernel: CTA that takes the step's first row group
     uint32_t grid;
     uint32_t smem_bytes;
     uint32_t debug;  // measurement only: bit 0 = stream the tiles but skip the arithmetic
@@ -65,6 +66,13 @@ struct GemvArgs {
 bool gemv_plan(GemvArgs &a, int num_sms, size_t smem_optin);
 cudaError_t gemv_prepare_device(size_t smem_optin);  // opt in to large dynamic shared memory, once per device
 cudaError_t launch_gemv(const GemvArgs &a, cudaStream_t stream);
+// A chain of steps (each the outputs of the one before it as activation) in one cooperative launch:
+// plan fills the shared geometry of steps[0..n) on the host; the launch takes the same array on the device.
+bool gemv_chain_plan(GemvArgs *steps, uint32_t n, int num_sms, size_t smem_optin, uint32_t *smem_bytes);
+// d_trace: null, or 3 * n_steps device words that receive CTA 0's clock after each step's barrier,
+// prologue and row groups (measurement only).
+cudaError_t launch_gemv_chain(const GemvArgs *d_steps, uint32_t n_steps, int act, uint32_t *d_gbar, int num_sms,
+                              uint32_t smem_bytes, unsigned long long *d_trace, cudaStream_t stream);
 
 // ---- W8A8 prefill GEMM (tcgen05 int8 MMA) ----------------------------------
 cudaError_t gemm_prepare_device();
