@@ -62,9 +62,12 @@ def oracle_chain(orc, W, h0, n_layers, eps, int8, gelu=False):
     return mm("output.weight", orc.rmsnorm(h, W["output_norm.weight"], eps))
 
 
+@pytest.mark.parametrize("chain_kernel", ["0", "1"])
 @pytest.mark.parametrize("int8", [False, True])
-def test_decode_step_matches_oracle_chain(pkg, orc, synth, int8):
+def test_decode_step_matches_oracle_chain(pkg, orc, synth, int8, chain_kernel, monkeypatch):
+    """chain_kernel = "1": the whole chain as one cooperative kernel; "0": one launch per step."""
     hidden, qdim, kvdim, ffn, vocab, n_layers, eps = 512, 768, 256, 1536, 3000, 3, 1e-6
+    monkeypatch.setenv("STRIX_DECODE_CHAIN", chain_kernel)
     acc = pkg.CudaWeightAccel(0)
     try:
         W = build_model(acc, synth, hidden, qdim, kvdim, ffn, vocab, n_layers)
