@@ -238,7 +238,9 @@ __device__ __forceinline__ TileConsts tile_consts() {
 //   ta: shared address of the tile (Q6_K: of the 416-byte sub-tile); da: Q6_K only, shared address of
 //   the super-block's scale pairs; xb_a / xr_a: this lane's B-operand and record addresses for the
 //   block. acc: see lane_values().
-template <int FMT, int ACT, bool MULTI>
+//   Q6D = false (Q6_K only): the super-block scale is left out (the caller applies it once per
+//   super-block to what this adds into acc).
+template <int FMT, int ACT, bool MULTI, bool Q6D = true>
 __device__ __forceinline__ void tile_mac(uint32_t ta, uint32_t da, uint32_t xb_a, uint32_t xr_a, const TileConsts &C,
                                          uint32_t lane, float (&acc)[lane_values(ACT, MULTI)]) {
     const uint32_t g = lane >> 2;
@@ -266,16 +268,19 @@ __device__ __forceinline__ void tile_mac(uint32_t ta, uint32_t da, uint32_t xb_a
         W1 = ((lo.x >> 4) & M4) | ((H << 2) & M30);
         W2 = (lo.y & M4) | (H & M30);
         W3 = ((lo.y >> 4) & M4) | ((H >> 2) & M30);
-        d = h2_to_f2(lds32(da + 4u * g));
+        d = Q6D ? h2_to_f2(lds32(da + 4u * g)) : make_float2(1.f, 1.f);
     }
     // Q6_K: (d * sub-scale) for the two 16-weight halves of rows g and g + 8
     float s_lo0 = 0.f, s_lo1 = 0.f, s_hi0 = 0.f, s_hi1 = 0.f;
     if (FMT == FMT_Q6_K) {
         const uint32_t sc = lds32(ta + 384u + 4u * g);  // {row g: first, last 16; row g + 8: first, last 16}, each + 128
-        s_lo0 = d.x * biased_byte_to_float<0>(sc);
-        s_lo1 = d.x * biased_byte_to_float<1>(sc);
-        s_hi0 = d.y * biased_byte_to_float<2>(sc);
-        s_hi1 = d.y * biased_byte_to_float<3>(sc);
+        s_lo0 = biased_byte_to_float<0>(sc);
+        s_lo1 = biased_byte_to_float<1>(sc);
+        s_hi0 = biased_byte_to_float<2>(sc);
+        s_hi1 = biased_byte_to_float<3>(sc);
+        if (Q6D) {
+            s_lo0 *= d.x; s_lo1 *= d.x; s_hi0 *= d.y; s_hi1 *= d.y;
+        }
     }
 
     if (ACT == STRIX_ACT_F32) {
@@ -674,6 +679,8 @@ __device__ __forceinline__ void consumer_groups(const GemvArgs &A, Cta &C) {
     const uint32_t xb_l = xs0 + XL.xb + lane_eff * (ACT == STRIX_ACT_F32 ? 16u : 8u);
     const uint32_t xr_l = xs0 + XL.rec + ((FMT == FMT_Q6_K || MULTI) ? 16u * t : 0u);
     const TileConsts TC = tile_consts<FMT, ACT>();
+    const uint32_t xb_step = wc * XL.xb_stride, xr_step = wc * XL.rec_stride, ta_step = wc * L.tile_bytes;
+    const uint32_t q6_step = wc * Q6_SUB;
     float *my_part = part + (size_t)(warp * 32u + lane) * NV;
     for (uint32_t r = 0; r < rounds; r++) {
         const uint32_t n = r * n_slots + slot;
@@ -689,19 +696,56 @@ __device__ __forceinline__ void consumer_groups(const GemvArgs &A, Cta &C) {
             const uint32_t nbk = min(CT, L.nb - c * CT);
             if (live && !skip) {
                 // tiles w, w + wc, ... of the stage; block index of tile i = first block of the stage + i
-                // (addresses by multiply-add: that pipe has room, the logic pipe does not)
                 constexpr uint32_t SUB = FMT == FMT_Q6_K ? 8u : 1u;
-                const uint32_t blk0 = c * CT * SUB;
-                if (FMT == FMT_Q6_K) {
-                    for (uint32_t i = w; i < nbk * 8u; i += wc) {
+                const uint32_t blk0 = c * CT * SUB + w;
+                uint32_t xb_a = mad_u32(blk0, XL.xb_stride, xb_l), xr_a = mad_u32(blk0, XL.rec_stride, xr_l);
+                if (FMT == FMT_Q6_K && (wc == 1 || wc == 2 || wc == 4 || wc == 8)) {
+                    // a warp's sub-tiles of one super-block share the super-block scale: it is applied
+                    // once to their sum
+                    uint32_t tb = base;
+                    for (uint32_t sb = 0; sb < nbk; sb++, tb += Q6_TILE) {
+                        const float2 d = h2_to_f2(lds32(tb + 8u * Q6_SUB + 4u * g));
+                        float part_sb[NV];
+#pragma unroll
+                        for (int v = 0; v < NV; v++) part_sb[v] = 0.f;
+                        uint32_t ta = tb + w * Q6_SUB;
+                        // two sub-tiles per pass: two independent chains for the scheduler to interleave
+                        float part_2[NV];
+#pragma unroll
+                        for (int v = 0; v < NV; v++) part_2[v] = 0.f;
+                        for (uint32_t st = w; st < 8u; st += 2u * wc, ta += 2u * q6_step) {
+                            tile_mac<FMT, ACT, MULTI, false>(ta, 0u, xb_a, xr_a, TC, lane, part_sb);
+                            xb_a += xb_step;
+                            xr_a += xr_step;
+                            if (st + wc < 8u) {
+                                tile_mac<FMT, ACT, MULTI, false>(ta + q6_step, 0u, xb_a, xr_a, TC, lane, part_2);
+                                xb_a += xb_step;
+                                xr_a += xr_step;
+                            }
+                        }
+                        part_sb[0] += part_2[0];
+                        part_sb[1] += part_2[1];
+                        acc[0] = fmaf(d.x, part_sb[0], acc[0]);
+                        acc[1] = fmaf(d.y, part_sb[1], acc[1]);
+                    }
+                } else if (FMT == FMT_Q6_K) {
+                    for (uint32_t i = w; i < nbk * 8u; i += wc, xb_a += xb_step, xr_a += xr_step) {
                         const uint32_t tb = mad_u32(i >> 3, Q6_TILE, base);
-                        tile_mac<FMT, ACT, MULTI>(mad_u32(i & 7u, Q6_SUB, tb), tb + 8u * Q6_SUB, mad_u32(blk0 + i, XL.xb_stride, xb_l),
-                                                  mad_u32(blk0 + i, XL.rec_stride, xr_l), TC, lane, acc);
+                        tile_mac<FMT, ACT, MULTI>(mad_u32(i & 7u, Q6_SUB, tb), tb + 8u * Q6_SUB, xb_a, xr_a, TC, lane, acc);
                     }
                 } else {
-                    for (uint32_t i = w; i < nbk; i += wc)
-                        tile_mac<FMT, ACT, MULTI>(mad_u32(i, L.tile_bytes, base), 0u, mad_u32(blk0 + i, XL.xb_stride, xb_l),
-                                                  mad_u32(blk0 + i, XL.rec_stride, xr_l), TC, lane, acc);
+                    // two tiles per pass: two independent chains for the scheduler to interleave
+                    uint32_t ta = base + w * L.tile_bytes, i = w;
+                    float acc2[NV];
+#pragma unroll
+                    for (int v = 0; v < NV; v++) acc2[v] = 0.f;
+                    for (; i + wc < nbk; i += 2u * wc, ta += 2u * ta_step, xb_a += 2u * xb_step, xr_a += 2u * xr_step) {
+                        tile_mac<FMT, ACT, MULTI>(ta, 0u, xb_a, xr_a, TC, lane, acc);
+                        tile_mac<FMT, ACT, MULTI>(ta + ta_step, 0u, xb_a + xb_step, xr_a + xr_step, TC, lane, acc2);
+                    }
+                    if (i < nbk) tile_mac<FMT, ACT, MULTI>(ta, 0u, xb_a, xr_a, TC, lane, acc);
+#pragma unroll
+                    for (int v = 0; v < NV; v++) acc[v] += acc2[v];
                 }
             }
             __syncwarp();
