@@ -662,7 +662,9 @@ __device__ __forceinline__ void consumer_groups(const GemvArgs &A, Cta &C) {
     volatile uint32_t *ctl = cta_ctl(C);
     const float *oscale = reinterpret_cast<const float *>(smem + SMEM_OSCALE_OFF);
     float *part = reinterpret_cast<float *>(smem + SMEM_PART_OFF);
-    const uint32_t lane = C.lane, warp = C.warp, wc = C.wc, n_slots = C.n_slots, Sk = C.Sk;
+    // (the warp index through a shuffle: the compiler then knows it is the same in every lane and keeps
+    // the loop control that depends on it off the per-lane logic pipe)
+    const uint32_t lane = C.lane, warp = __shfl_sync(0xffffffffu, C.warp, 0), wc = C.wc, n_slots = C.n_slots, Sk = C.Sk;
     const RowLayout L = A.L;
     const uint32_t B = A.nbatch, CT = A.chunk_tiles, NC = A.n_chunks;
     const uint32_t my_n = cta_groups(C, A), rank = cta_rank(C, A);
