@@ -471,13 +471,13 @@ def main():
         sec = [d for d, it in zip(detail, items) if it["ty"] == Q8_0 and it["n"] == 151936][0]
         roof = {"bound": "hbm", "achieved": dom["gbs"], "peak": peak, "unit": "GB/s",
                 "frac": round(dom["gbs"] / peak, 4),
-                "traffic": int(142.88e6 * 151936 / 65536) if world == 1 else None,
+                "traffic": int(142.07e6 * 151936 / 65536) if world == 1 else None,
                 "kernel": "gemv_kernel<Q6_K,F32> on q6_k.2560.151936, 319,683,584 algorithmic bytes per launch "
                           "(of %s peak)" % peak_src,
                 "frac_of_8tbs": round(dom["gbs"] / 8000.0, 4),
                 "second_kernel": {"kernel": "gemv_kernel<Q8_0,F32> on q8_0.2560.151936, 413,883,904 bytes",
                                   "achieved": sec["gbs"], "frac": round(sec["gbs"] / peak, 4),
-                                  "traffic": int(182.34e6 * 151936 / 65536) if world == 1 else None}}
+                                  "traffic": int(184.21e6 * 151936 / 65536) if world == 1 else None}}
 
     # ---- extras on rank 0 at N=1: the integer-dot GEMV variant and the W8A8 GEMM (configs[2]) ----
     extras = None
