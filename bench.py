@@ -205,6 +205,114 @@ def decode_chain_extra(pkg, synth, torch, device, stream):
     return out
 
 
+def decode_chain_sharded_extra(pkg, synth, torch, dist, local, stream, rank, world):
+    """configs[3] on `world` GPUs: every projection row-sharded, an NCCL all-gather after each sharded
+    projection or group (q|k|v and gate|up gathered in one coalesced call each). Every rank runs this."""
+    hidden, qdim, kvdim, ffn, vocab, n_layers = 2560, 4096, 1024, 9728, 151936, 36
+    dev = torch.device("cuda", local)
+    acc = pkg.CudaWeightAccel(local, rank=rank, world=world)
+    out = {}
+    try:
+        shapes = {"attn_q": (qdim, hidden), "attn_k": (kvdim, hidden), "attn_v": (kvdim, hidden),
+                  "attn_output": (hidden, qdim), "ffn_gate": (ffn, hidden), "ffn_up": (ffn, hidden),
+                  "ffn_down": (hidden, ffn)}
+        base = {nm: make_weight(synth, Q4_0, k, n, 3, "dc." + nm) for nm, (n, k) in shapes.items()}
+        nbytes = 0
+        norms = []
+        for il in range(n_layers):
+            for nm, (n, k) in shapes.items():
+                assert acc.upload_q4_0("blk.%d.%s.weight" % (il, nm), base[nm], k, n)   # the library keeps its row shard
+                nbytes += n * (k // 32) * 18
+            norms.append([torch.from_numpy(synth.norm_weight(3, "dc.%d.%s" % (il, nn), hidden)).to(dev)
+                          for nn in ("attn_norm", "ffn_norm")])
+        assert acc.upload_q6_k("output.weight", make_weight(synth, Q6_K, hidden, vocab, 3, "dc.head"), hidden, vocab)
+        nbytes += vocab * (hidden // 256) * 210
+        out_norm = torch.from_numpy(synth.norm_weight(3, "dc.out_norm", hidden)).to(dev)
+        h0 = torch.from_numpy(synth.normal(3, "dc.h0", hidden)).to(dev)
+
+        def full(n):
+            return torch.zeros(n, device=dev)
+
+        def shard(n):
+            assert n % world == 0
+            return torch.zeros(n // world, device=dev)
+
+        h_full, q_full, k_full, v_full = full(hidden), full(qdim), full(kvdim), full(kvdim)
+        g_full, u_full, lg_full = full(ffn), full(ffn), full(vocab)
+        q_sh, k_sh, v_sh, h_sh, g_sh, u_sh, lg_sh = (shard(n) for n in (qdim, kvdim, kvdim, hidden, ffn, ffn, vocab))
+        h_res = h_full[rank * (hidden // world):(rank + 1) * (hidden // world)]   # this rank's rows of the residual
+        state = {"coalesce": True}
+
+        def gather(pairs):
+            if len(pairs) > 1 and state["coalesce"]:
+                try:
+                    with dist._coalescing_manager(device=dev):
+                        for f, s_ in pairs:
+                            dist.all_gather_into_tensor(f, s_)
+                    return
+                except Exception:
+                    state["coalesce"] = False
+            for f, s_ in pairs:
+                dist.all_gather_into_tensor(f, s_)
+
+        def chain(act):
+            s = torch.cuda.current_stream().cuda_stream
+            p = lambda t: t.data_ptr()  # noqa: E731
+            for il in range(n_layers):
+                b = "blk.%d." % il
+                an, fn = norms[il]
+                assert acc.gemv_dev([b + "attn_q.weight", b + "attn_k.weight", b + "attn_v.weight"], p(h_full),
+                                    [p(q_sh), p(k_sh), p(v_sh)], d_b=p(an), eps=1e-6, pre=pkg.PRE_RMSNORM, act=act, stream=s)
+                gather([(q_full, q_sh), (k_full, k_sh), (v_full, v_sh)])
+                assert acc.gemv_dev([b + "attn_output.weight"], p(q_full), [p(h_sh)], act=act, stream=s, d_res=[p(h_res)])
+                gather([(h_full, h_sh)])
+                assert acc.gemv_dev([b + "ffn_gate.weight", b + "ffn_up.weight"], p(h_full), [p(g_sh), p(u_sh)],
+                                    d_b=p(fn), eps=1e-6, pre=pkg.PRE_RMSNORM, act=act, stream=s)
+                gather([(g_full, g_sh), (u_full, u_sh)])
+                assert acc.gemv_dev([b + "ffn_down.weight"], p(g_full), [p(h_sh)], d_b=p(u_full), pre=pkg.PRE_SWIGLU,
+                                    act=act, stream=s, d_res=[p(h_res)])
+                gather([(h_full, h_sh)])
+            assert acc.gemv_dev(["output.weight"], p(h_full), [p(lg_sh)], d_b=p(out_norm), eps=1e-6,
+                                pre=pkg.PRE_RMSNORM, act=act, stream=s)
+            gather([(lg_full, lg_sh)])
+
+        for act, name in ((pkg.ACT_Q8DOT, "q8dot"),):
+            with torch.cuda.stream(stream):
+                h_full.copy_(h0)
+                chain(act)
+                torch.cuda.synchronize()
+                g = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(g, stream=stream):
+                    h_full.copy_(h0)
+                    chain(act)
+                for _ in range(3):
+                    g.replay()
+                torch.cuda.synchronize()
+                dist.barrier()
+                torch.cuda.synchronize()
+                a, b2 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                reps = 20
+                a.record()
+                for _ in range(reps):
+                    g.replay()
+                b2.record()
+                torch.cuda.synchronize()
+                t = torch.tensor([a.elapsed_time(b2) / reps], device=dev)
+                dist.all_reduce(t, op=dist.ReduceOp.MAX)
+                ms = float(t.item())
+            assert bool(torch.isfinite(lg_full).all()) and acc.device_status(stream.cuda_stream) == 0
+            out[name] = {"ms_per_token": round(ms, 4), "gbs_aggregate": round(nbytes / ms / 1e6, 1),
+                         "gbs_per_gpu": round(nbytes / ms / 1e6 / world, 1),
+                         "launches_per_token": 4 * n_layers + 1, "collectives_per_token": 4 * n_layers + 1}
+        out["n_gpus"] = world
+        out["bytes_per_token"] = nbytes
+        out["note"] = ("row-sharded projections, NCCL all-gather after each projection or fused group "
+                       "(coalesced: %s); attention replaced by feeding Wo with q" % state["coalesce"])
+    finally:
+        acc.close()
+    return out
+
+
 def verify_rows_extra(pkg, synth, torch, device, stream):
     """configs[4]: speculative-verify batched GEMV at Gemma-3-12B-class shapes (48 layers, hidden 3840,
     q 4096, kv 2048, ffn 15360, Q4_0), b in {1,2,4,8} activation rows; 6.05 GB of weights per step."""
@@ -359,11 +467,20 @@ def main():
         del full, shard
         x_host = synth.normal(1, key + ".x", k)
         x = torch.from_numpy(x_host).to(dev)
-        y_shard = torch.zeros(r1 - r0, device=dev)
-        y_full = torch.zeros(n, device=dev) if world > 1 else y_shard
-        items.append(dict(key=key, ty=ty, k=k, n=n, x=x, x_host=x_host, y=y_shard, y_full=y_full,
+        items.append(dict(key=key, ty=ty, k=k, n=n, x=x, x_host=x_host, rows=r1 - r0,
                           bytes=algo_bytes(ty, k, n)))
     step_bytes = sum(it["bytes"] for it in items)
+    # The six outputs of a rank sit in ONE buffer (slots of ceil(n / world) floats), so that the step's
+    # exchange is one all-gather: the six GEMVs of configs[1] do not depend on each other. (In the
+    # decode chain every projection feeds the next one and is gathered on its own.)
+    off = 0
+    for it in items:
+        it["off"] = off
+        off += -(-it["n"] // world)
+    y_mine = torch.zeros(off, device=dev)
+    y_all = torch.zeros(world * off, device=dev) if world > 1 else y_mine
+    for it in items:
+        it["y"] = y_mine[it["off"]:it["off"] + it["rows"]]
 
     stream = torch.cuda.Stream(device=dev)
 
@@ -372,8 +489,8 @@ def main():
         for it in items:
             ok = acc.gemv_dev([it["key"]], it["x"].data_ptr(), [it["y"].data_ptr()], act=pkg.ACT_F32, stream=s)
             assert ok
-            if world > 1:
-                dist.all_gather_into_tensor(it["y_full"], it["y"])
+        if world > 1:
+            dist.all_gather_into_tensor(y_all, y_mine)
 
     def barrier():
         if world > 1:
@@ -530,6 +647,12 @@ def main():
         if acc.device_status() != 0:
             raise SystemExit("device status word is non-zero after the extras")
 
+    if world > 1:
+        # configs[3] on all ranks: the row-sharded decode chain with an all-gather per projection
+        sharded = decode_chain_sharded_extra(pkg, synth, torch, dist, local, stream, rank, world)
+        if rank == 0:
+            extras = {"decode_chain_sharded": sharded}
+
     cpu = None
     if rank == 0 and world == 1 and not args.no_cpu_baseline:
         orc = entry.load_oracle()
@@ -543,7 +666,8 @@ def main():
             "scaling": "strong" if world > 1 else "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
             "config": {"workload": "configs[1]: Q8_0+Q6_K dequant-GEMV, batch 1, 2560->9728, 9728->2560, 2560->151936",
                        "bytes_per_step": step_bytes, "l2": "inputs larger than L2 (827.5 MB streamed per step)",
-                       "parallelism": "rows sharded over %d GPU(s)%s" % (world, ", NCCL all-gather per GEMV" if world > 1 else "")},
+                       "parallelism": "rows sharded over %d GPU(s)%s" % (
+                           world, ", one NCCL all-gather of the six output shards per step" if world > 1 else "")},
             "e2e": {"value": round(e2e_val, 2), "unit": "GB/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
             "gpu_launches": args.steps * len(items),
             "clocks": clocks, "roofline": roof, "cpu_baseline": cpu, "per_weight": detail, "extras": extras,

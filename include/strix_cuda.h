@@ -122,6 +122,13 @@ STRIX_API int strix_cuda_gemv_batch(strix_cuda *h, size_t n, const char *const *
  * q4_gemv_dp2 / _dp3, kernels.rs:228-255, 324-361): pass their keys and outputs. */
 STRIX_API int strix_cuda_gemv_dev(strix_cuda *h, int nmat, const char *const *keys, const float *d_a,
                         const float *d_b, float eps, int pre, int act, float *const *d_ys, void *stream);
+/* The same with a fused residual add: d_ys[m][r] = (W_m x)[r] + d_res[m][r] (d_res[m] may be null; it
+ * may equal d_ys[m]). This is the reference's q4_gemv_w_add / accumulate-into-h form of the o and down
+ * projections (decode.rs:5390-5400, 5470-5477). With row shards, d_res[m] points at this shard's
+ * rows of the residual vector. */
+STRIX_API int strix_cuda_gemv_res_dev(strix_cuda *h, int nmat, const char *const *keys, const float *d_a,
+                            const float *d_b, float eps, int pre, int act, float *const *d_ys,
+                            const float *const *d_res, void *stream);
 
 /* WeightAccel::prefill_q8_gemm (accel.rs:213; decode.rs:3257-3297): y[m][rows] = W8A8 GEMM of m
  * token rows xs[m][in_dim] with a resident Q8_0 weight: per-32 int8 activations (xquant8_rows,

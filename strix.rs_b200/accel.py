@@ -78,6 +78,8 @@ def load_library():
         C.c_int, C.POINTER(C.c_int))
     sig("strix_cuda_gemv_dev", C.c_int, H, C.c_int, C.POINTER(C.c_char_p), C.c_void_p, C.c_void_p, C.c_float,
         C.c_int, C.c_int, C.POINTER(C.c_void_p), C.c_void_p)
+    sig("strix_cuda_gemv_res_dev", C.c_int, H, C.c_int, C.POINTER(C.c_char_p), C.c_void_p, C.c_void_p, C.c_float,
+        C.c_int, C.c_int, C.POINTER(C.c_void_p), C.POINTER(C.c_void_p), C.c_void_p)
     sig("strix_cuda_prefill_q8_gemm", C.c_int, H, C.c_char_p, f32p, sz, f32p, sz)
     sig("strix_cuda_prefill_q8_gemm_dev", C.c_int, H, C.c_char_p, C.c_void_p, sz, C.c_void_p, C.c_void_p)
     sig("strix_cuda_prefill_q8_gemm_noalloc", C.c_int, H, C.c_char_p, C.c_void_p, sz, C.c_void_p, C.c_void_p)
@@ -299,10 +301,17 @@ class CudaWeightAccel:
         return rc == 1
 
     # -- device-resident form (pointers are ints: torch ``tensor.data_ptr()``) ----
-    def gemv_dev(self, keys, d_a, d_ys, d_b=0, eps=0.0, pre=PRE_NONE, act=ACT_F32, stream=0):
+    def gemv_dev(self, keys, d_a, d_ys, d_b=0, eps=0.0, pre=PRE_NONE, act=ACT_F32, stream=0, d_res=None):
+        """d_res: per-weight device pointers (0 = none) of residual vectors added to the outputs."""
         n = len(keys)
         kk = (C.c_char_p * n)(*[k.encode() for k in keys])
         yy = (C.c_void_p * n)(*[int(p) for p in d_ys])
+        if d_res is not None:
+            rr = (C.c_void_p * n)(*[int(p) if p else None for p in d_res])
+            rc = self._check(self._L.strix_cuda_gemv_res_dev(self._h, n, kk, C.c_void_p(int(d_a)),
+                                                            C.c_void_p(int(d_b)) if d_b else None, float(eps), pre, act,
+                                                            yy, rr, C.c_void_p(int(stream)) if stream else None))
+            return rc == 1
         rc = self._check(self._L.strix_cuda_gemv_dev(self._h, n, kk, C.c_void_p(int(d_a)),
                                                     C.c_void_p(int(d_b)) if d_b else None, float(eps), pre, act, yy,
                                                     C.c_void_p(int(stream)) if stream else None))

@@ -441,6 +441,27 @@ int strix_cuda_gemv_dev(strix_cuda *h, int nmat, const char *const *keys, const 
     return gemv_launch(h, nmat, ws, d_a, d_b, eps, pre, act, d_ys, nullptr, static_cast<cudaStream_t>(stream));
 }
 
+int strix_cuda_gemv_res_dev(strix_cuda *h, int nmat, const char *const *keys, const float *d_a, const float *d_b,
+                            float eps, int pre, int act, float *const *d_ys, const float *const *d_res, void *stream) {
+    if (!h || !keys || !d_a || !d_ys || !d_res) return -1;
+    h->err.clear();
+    if (nmat < 1 || nmat > GEMV_MAX_MATS) {
+        h->err = "gemv_res_dev: between 1 and 3 weights per launch";
+        return -1;
+    }
+    if (pre != STRIX_PRE_NONE && !d_b) {
+        h->err = "gemv_res_dev: this prologue needs d_b";
+        return -1;
+    }
+    CU_TRY(h, cudaSetDevice(h->device));
+    const Resident *ws[GEMV_MAX_MATS];
+    for (int m = 0; m < nmat; m++) {
+        ws[m] = find_weight(h, keys[m]);
+        if (!ws[m]) return 0;
+    }
+    return gemv_launch(h, nmat, ws, d_a, d_b, eps, pre, act, d_ys, d_res, static_cast<cudaStream_t>(stream));
+}
+
 int strix_cuda_gemv_rows_dev(strix_cuda *h, int nmat, const char *const *keys, const float *d_xs, size_t b, int act,
                              float *const *d_ys, void *stream) {
     if (!h || !keys || !d_xs || !d_ys) return -1;

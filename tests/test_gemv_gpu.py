@@ -227,6 +227,12 @@ def test_gemv_dev_prologues_and_fused_weights(accel, orc, synth, pkg):
             assert rel_l2(y.cpu().numpy(), orc.qmatmul(n_cpu, w_, synth.Q4_0, hidden, n_)) <= tol
         assert rel_l2(yd.cpu().numpy(), orc.qmatmul(orc.swiglu(gate, up), wd, synth.Q4_0, ffn, hidden)) <= tol
         assert rel_l2(yg.cpu().numpy(), orc.qmatmul(orc.geglu(gate, up), wd, synth.Q4_0, ffn, hidden)) <= tol
+        # fused residual: h + W_down swiglu(gate, up), accumulated in place (the o / down projections of the chain)
+        acc_h = d_h.clone()
+        assert accel.gemv_dev(["f.down"], d_g.data_ptr(), [acc_h.data_ptr()], d_b=d_u.data_ptr(), pre=pkg.PRE_SWIGLU,
+                              act=act, stream=s, d_res=[acc_h.data_ptr()])
+        want = h + orc.qmatmul(orc.swiglu(gate, up), wd, synth.Q4_0, ffn, hidden)
+        assert rel_l2(acc_h.cpu().numpy(), want) <= tol
 
 
 # ------------------------------------------------------------------ batched rows (speculative verify)
