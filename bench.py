@@ -276,7 +276,96 @@ def decode_chain_sharded_extra(pkg, synth, torch, dist, local, stream, rank, wor
                                 pre=pkg.PRE_RMSNORM, act=act, stream=s)
             gather([(lg_full, lg_sh)])
 
-        for act, name in ((pkg.ACT_Q8DOT, "q8dot"),):
+        # ---- fused form: the GEMV stores its rows into every rank's full vectors (peer-mapped memory), a
+        #      flag barrier follows instead of a collective ----
+        fused = {"ok": False, "why": ""}
+        try:
+            opened = {}
+
+            def share(t):
+                """device pointers of every rank's copy of tensor t: the owner exports the CUDA IPC handle of
+                the allocation (through torch, which knows its base) and the offset of t in it; the library
+                opens each handle once, with this rank's device current"""
+                meta = t.untyped_storage()._share_cuda_()
+                handle = bytes(meta[1])
+                if len(handle) == 66 and handle[1:2] == b"c":
+                    handle = handle[2:]      # torch prefixes a version byte and a type byte ('c' = cudaMalloc)
+                if len(handle) != 64:
+                    raise RuntimeError("torch exported a %d-byte handle: not a plain cudaMalloc allocation" % len(handle))
+                mine = (handle, int(meta[3]) + t.storage_offset() * t.element_size())
+                metas = [None] * world
+                dist.all_gather_object(metas, mine)
+                ptrs_ = []
+                for r, (handle, offset) in enumerate(metas):
+                    if r == rank:
+                        ptrs_.append(t.data_ptr())
+                        continue
+                    if (r, handle) not in opened:
+                        opened[(r, handle)] = acc.ipc_open(handle)
+                    ptrs_.append(opened[(r, handle)] + offset)
+                return ptrs_
+
+            flags = torch.zeros(8, dtype=torch.int32, device=dev)
+            epoch = torch.zeros(1, dtype=torch.int32, device=dev)
+            ptrs = {nm: share(t) for nm, t in (("h", h_full), ("q", q_full), ("k", k_full), ("v", v_full),
+                                               ("g", g_full), ("u", u_full), ("lg", lg_full), ("flags", flags))}
+            # check every mapping with a copy-engine read before any kernel stores through it: each rank
+            # leaves a mark in the last word of each of its buffers and reads its peers' marks
+            marks = {}
+            for i, (nm, t) in enumerate((("h", h_full), ("q", q_full), ("k", k_full), ("v", v_full), ("g", g_full),
+                                         ("u", u_full), ("lg", lg_full), ("flags", flags))):
+                marks[nm] = (t, 0x5EED0000 + 256 * i)
+                t.view(torch.int32)[-1] = marks[nm][1] + rank
+            torch.cuda.synchronize()
+            dist.barrier()
+            for nm, (t, mark) in marks.items():
+                for r in range(world):
+                    got = acc.peek_u32(ptrs[nm][r] + 4 * (t.numel() - 1))
+                    if got != mark + r:
+                        raise RuntimeError("peer mapping of %s on rank %d reads %#x, expected %#x" % (nm, r, got, mark + r))
+            dist.barrier()
+            for nm, (t, mark) in marks.items():
+                t.view(torch.int32)[-1] = 0
+            torch.cuda.synchronize()
+            dist.barrier()
+            fused["ok"] = True
+        except Exception as ex:   # the NCCL form above stands on its own
+            fused["why"] = "%s: %s" % (type(ex).__name__, ex)
+
+        def chain_fused(act):
+            s = torch.cuda.current_stream().cuda_stream
+            p = lambda t: t.data_ptr()  # noqa: E731
+
+            def bar():
+                acc.peer_barrier_dev(p(epoch), p(flags), ptrs["flags"], stream=s)
+
+            for il in range(n_layers):
+                b = "blk.%d." % il
+                an, fn = norms[il]
+                assert acc.gemv_peers_dev([b + "attn_q.weight", b + "attn_k.weight", b + "attn_v.weight"], p(h_full),
+                                          [ptrs["q"], ptrs["k"], ptrs["v"]], d_b=p(an), eps=1e-6, pre=pkg.PRE_RMSNORM,
+                                          act=act, stream=s)
+                bar()
+                assert acc.gemv_peers_dev([b + "attn_output.weight"], p(q_full), [ptrs["h"]], act=act, stream=s,
+                                          d_res=[p(h_res)])
+                bar()
+                assert acc.gemv_peers_dev([b + "ffn_gate.weight", b + "ffn_up.weight"], p(h_full), [ptrs["g"], ptrs["u"]],
+                                          d_b=p(fn), eps=1e-6, pre=pkg.PRE_RMSNORM, act=act, stream=s)
+                bar()
+                assert acc.gemv_peers_dev([b + "ffn_down.weight"], p(g_full), [ptrs["h"]], d_b=p(u_full),
+                                          pre=pkg.PRE_SWIGLU, act=act, stream=s, d_res=[p(h_res)])
+                bar()
+            assert acc.gemv_peers_dev(["output.weight"], p(h_full), [ptrs["lg"]], d_b=p(out_norm), eps=1e-6,
+                                      pre=pkg.PRE_RMSNORM, act=act, stream=s)
+            bar()
+
+        variants = [("nccl", chain)] + ([("fused", chain_fused)] if fused["ok"] else [])
+        logits_ref = None
+        for vname, chain in variants:
+          for act, name in ((pkg.ACT_Q8DOT, "q8dot"),):
+            if rank == 0:
+                sys.stderr.write("decode_chain_sharded: %s %s\n" % (vname, name))
+                sys.stderr.flush()
             with torch.cuda.stream(stream):
                 h_full.copy_(h0)
                 chain(act)
@@ -301,13 +390,20 @@ def decode_chain_sharded_extra(pkg, synth, torch, dist, local, stream, rank, wor
                 dist.all_reduce(t, op=dist.ReduceOp.MAX)
                 ms = float(t.item())
             assert bool(torch.isfinite(lg_full).all()) and acc.device_status(stream.cuda_stream) == 0
-            out[name] = {"ms_per_token": round(ms, 4), "gbs_aggregate": round(nbytes / ms / 1e6, 1),
-                         "gbs_per_gpu": round(nbytes / ms / 1e6 / world, 1),
-                         "launches_per_token": 4 * n_layers + 1, "collectives_per_token": 4 * n_layers + 1}
+            if logits_ref is None:
+                logits_ref = lg_full.clone()
+            else:   # same shards, same kernels: the two exchange forms must agree bit for bit
+                assert bool((lg_full == logits_ref).all()), "fused and NCCL chains disagree"
+            out[vname + "_" + name] = {"ms_per_token": round(ms, 4), "gbs_aggregate": round(nbytes / ms / 1e6, 1),
+                                       "gbs_per_gpu": round(nbytes / ms / 1e6 / world, 1),
+                                       "launches_per_token": (4 * n_layers + 1) * (2 if vname == "fused" else 1),
+                                       "collectives_per_token": 4 * n_layers + 1 if vname == "nccl" else 0}
         out["n_gpus"] = world
         out["bytes_per_token"] = nbytes
-        out["note"] = ("row-sharded projections, NCCL all-gather after each projection or fused group "
-                       "(coalesced: %s); attention replaced by feeding Wo with q" % state["coalesce"])
+        out["note"] = ("row-sharded projections; nccl: all-gather after each projection or fused group (coalesced: %s); "
+                       "fused: the GEMV stores its rows into every rank's vectors over peer memory, then a flag barrier "
+                       "(%s); attention replaced by feeding Wo with q"
+                       % (state["coalesce"], "ran" if fused["ok"] else "not run: " + fused["why"]))
     finally:
         acc.close()
     return out

@@ -130,6 +130,33 @@ STRIX_API int strix_cuda_gemv_res_dev(strix_cuda *h, int nmat, const char *const
                             const float *d_b, float eps, int pre, int act, float *const *d_ys,
                             const float *const *d_res, void *stream);
 
+/* Row-sharded multi-GPU form of the device GEMV (no counterpart in the reference, which is
+ * single-GPU): instead of a local output shard, every output row r of weight m is stored into
+ * peer_ys[m * n_peers + p][row0_m + r] for p < n_peers - the FULL output vectors of all accelerators
+ * of the group (peer-mapped device memory, this accelerator's own copy among them), so that no
+ * all-gather follows. d_res (may be null, entries may be null) are this shard's rows of residual
+ * vectors. The stores are plain peer stores; they are complete when the kernel is, and
+ * strix_cuda_peer_barrier_dev after it on every rank's stream makes them safe to read. */
+STRIX_API int strix_cuda_gemv_peers_dev(strix_cuda *h, int nmat, const char *const *keys, const float *d_a,
+                              const float *d_b, float eps, int pre, int act, const float *const *d_res,
+                              int n_peers, float *const *peer_ys, void *stream);
+/* Lets kernels of this accelerator's device store into memory of `peer_device` (as mapped into this
+ * process, e.g. through CUDA IPC). 1 = enabled (or already so), 0 = the devices cannot reach each other. */
+STRIX_API int strix_cuda_enable_peer_access(strix_cuda *h, int peer_device);
+/* Maps memory that another process exported with cudaIpcGetMemHandle (64 bytes) for the kernels of this
+ * accelerator's device; *out is the base of the exported allocation. Open a given handle once. */
+STRIX_API int strix_cuda_ipc_open(strix_cuda *h, const void *handle, size_t handle_len, void **out);
+STRIX_API int strix_cuda_ipc_close(strix_cuda *h, void *p);
+/* One 32-bit word of device (or peer-mapped) memory, by a copy engine transfer: lets a caller check a
+ * mapping it was handed before any kernel stores through it. */
+STRIX_API int strix_cuda_peek_u32(strix_cuda *h, const void *d_ptr, uint32_t *out);
+/* Cross-GPU barrier for the form above: one launch per rank (opts.rank / opts.world of the handle), one
+ * rank per GPU. d_epoch: one zero-initialised word of this rank; d_local_flags: `world` zero-initialised
+ * words of this rank; peer_flags[i]: rank i's flag array as mapped into this process. The wait is
+ * bounded; on expiry the handle's status word gets the time-out bit and the kernel returns. */
+STRIX_API int strix_cuda_peer_barrier_dev(strix_cuda *h, uint32_t *d_epoch, uint32_t *d_local_flags,
+                                uint32_t *const *peer_flags, void *stream);
+
 /* WeightAccel::prefill_q8_gemm (accel.rs:213; decode.rs:3257-3297): y[m][rows] = W8A8 GEMM of m
  * token rows xs[m][in_dim] with a resident Q8_0 weight: per-32 int8 activations (xquant8_rows,
  * kernels.rs:1000-1013), int32 block sums on tcgen05, f32 combine with both block scales

@@ -80,6 +80,13 @@ def load_library():
         C.c_int, C.c_int, C.POINTER(C.c_void_p), C.c_void_p)
     sig("strix_cuda_gemv_res_dev", C.c_int, H, C.c_int, C.POINTER(C.c_char_p), C.c_void_p, C.c_void_p, C.c_float,
         C.c_int, C.c_int, C.POINTER(C.c_void_p), C.POINTER(C.c_void_p), C.c_void_p)
+    sig("strix_cuda_gemv_peers_dev", C.c_int, H, C.c_int, C.POINTER(C.c_char_p), C.c_void_p, C.c_void_p, C.c_float,
+        C.c_int, C.c_int, C.POINTER(C.c_void_p), C.c_int, C.POINTER(C.c_void_p), C.c_void_p)
+    sig("strix_cuda_enable_peer_access", C.c_int, H, C.c_int)
+    sig("strix_cuda_ipc_open", C.c_int, H, C.c_char_p, sz, C.POINTER(C.c_void_p))
+    sig("strix_cuda_ipc_close", C.c_int, H, C.c_void_p)
+    sig("strix_cuda_peek_u32", C.c_int, H, C.c_void_p, C.POINTER(C.c_uint32))
+    sig("strix_cuda_peer_barrier_dev", C.c_int, H, C.c_void_p, C.c_void_p, C.POINTER(C.c_void_p), C.c_void_p)
     sig("strix_cuda_prefill_q8_gemm", C.c_int, H, C.c_char_p, f32p, sz, f32p, sz)
     sig("strix_cuda_prefill_q8_gemm_dev", C.c_int, H, C.c_char_p, C.c_void_p, sz, C.c_void_p, C.c_void_p)
     sig("strix_cuda_prefill_q8_gemm_noalloc", C.c_int, H, C.c_char_p, C.c_void_p, sz, C.c_void_p, C.c_void_p)
@@ -316,6 +323,40 @@ class CudaWeightAccel:
                                                     C.c_void_p(int(d_b)) if d_b else None, float(eps), pre, act, yy,
                                                     C.c_void_p(int(stream)) if stream else None))
         return rc == 1
+
+    def gemv_peers_dev(self, keys, d_a, peer_ys, d_b=0, eps=0.0, pre=PRE_NONE, act=ACT_F32, stream=0, d_res=None):
+        """Row-sharded form: peer_ys[m] = the device pointers of weight m's FULL output vector on every
+        accelerator of the group (own copy included); rows land at row0 + r in each of them."""
+        n, npeer = len(keys), len(peer_ys[0])
+        kk = (C.c_char_p * n)(*[k.encode() for k in keys])
+        pp = (C.c_void_p * (n * npeer))(*[int(p) for ys in peer_ys for p in ys])
+        rr = (C.c_void_p * n)(*[int(p) if p else None for p in d_res]) if d_res is not None else None
+        rc = self._check(self._L.strix_cuda_gemv_peers_dev(self._h, n, kk, C.c_void_p(int(d_a)),
+                                                          C.c_void_p(int(d_b)) if d_b else None, float(eps), pre, act,
+                                                          rr, npeer, pp, C.c_void_p(int(stream)) if stream else None))
+        return rc == 1
+
+    def enable_peer_access(self, peer_device):
+        return self._check(self._L.strix_cuda_enable_peer_access(self._h, int(peer_device))) == 1
+
+    def ipc_open(self, handle):
+        """Base address (int) of memory another process exported (64-byte CUDA IPC handle), mapped for this device."""
+        out = C.c_void_p()
+        self._check(self._L.strix_cuda_ipc_open(self._h, bytes(handle), len(handle), C.byref(out)))
+        return int(out.value)
+
+    def peek_u32(self, d_ptr):
+        out = C.c_uint32()
+        self._check(self._L.strix_cuda_peek_u32(self._h, C.c_void_p(int(d_ptr)), C.byref(out)))
+        return out.value
+
+    def ipc_close(self, base):
+        self._check(self._L.strix_cuda_ipc_close(self._h, C.c_void_p(int(base))))
+
+    def peer_barrier_dev(self, d_epoch, d_local_flags, peer_flags, stream=0):
+        pf = (C.c_void_p * len(peer_flags))(*[int(p) for p in peer_flags])
+        self._check(self._L.strix_cuda_peer_barrier_dev(self._h, C.c_void_p(int(d_epoch)), C.c_void_p(int(d_local_flags)),
+                                                        pf, C.c_void_p(int(stream)) if stream else None))
 
     def device_status(self, stream=0):
         s = C.c_uint32()

@@ -462,6 +462,103 @@ int strix_cuda_gemv_res_dev(strix_cuda *h, int nmat, const char *const *keys, co
     return gemv_launch(h, nmat, ws, d_a, d_b, eps, pre, act, d_ys, d_res, static_cast<cudaStream_t>(stream));
 }
 
+int strix_cuda_gemv_peers_dev(strix_cuda *h, int nmat, const char *const *keys, const float *d_a, const float *d_b,
+                              float eps, int pre, int act, const float *const *d_res, int n_peers,
+                              float *const *peer_ys, void *stream) {
+    if (!h || !keys || !d_a || !peer_ys) return -1;
+    h->err.clear();
+    if (nmat < 1 || nmat > GEMV_MAX_MATS || n_peers < 1 || n_peers > GEMV_MAX_PEERS) {
+        h->err = "gemv_peers_dev: between 1 and 3 weights, 1 and 8 peers per launch";
+        return -1;
+    }
+    if (pre != STRIX_PRE_NONE && !d_b) {
+        h->err = "gemv_peers_dev: this prologue needs d_b";
+        return -1;
+    }
+    CU_TRY(h, cudaSetDevice(h->device));
+    const Resident *ws[GEMV_MAX_MATS];
+    float *no_y[GEMV_MAX_MATS] = {nullptr, nullptr, nullptr};
+    for (int m = 0; m < nmat; m++) {
+        ws[m] = find_weight(h, keys[m]);
+        if (!ws[m]) return 0;
+    }
+    GemvArgs a{};
+    if (gemv_fill_args(h, nmat, ws, d_a, d_b, eps, pre, act, no_y, d_res, &a) < 0) return -1;
+    for (int m = 0; m < nmat; m++) {
+        a.mat[m].n_peer = (uint32_t)n_peers;
+        a.mat[m].row_base = (uint32_t)ws[m]->row0;
+        for (int p = 0; p < n_peers; p++) a.mat[m].peer_y[p] = peer_ys[m * n_peers + p];
+    }
+    a.nbatch = 1;
+    if (!gemv_plan(a, h->num_sms, h->smem_optin)) {
+        h->err = "gemv_peers_dev: in_dim too large for the shared-memory pipeline";
+        return -1;
+    }
+    CU_TRY(h, launch_gemv(a, static_cast<cudaStream_t>(stream)));
+    return 1;
+}
+
+int strix_cuda_enable_peer_access(strix_cuda *h, int peer_device) {
+    if (!h) return -1;
+    h->err.clear();
+    if (peer_device == h->device) return 1;
+    CU_TRY(h, cudaSetDevice(h->device));
+    int can = 0;
+    CU_TRY(h, cudaDeviceCanAccessPeer(&can, h->device, peer_device));
+    if (!can) return 0;
+    const cudaError_t e = cudaDeviceEnablePeerAccess(peer_device, 0);
+    if (e == cudaErrorPeerAccessAlreadyEnabled) {
+        cudaGetLastError();  // not an error: clear it
+        return 1;
+    }
+    CU_TRY(h, e);
+    return 1;
+}
+
+int strix_cuda_ipc_open(strix_cuda *h, const void *handle, size_t handle_len, void **out) {
+    if (!h || !handle || !out) return -1;
+    h->err.clear();
+    if (handle_len != sizeof(cudaIpcMemHandle_t)) {
+        h->err = "ipc_open: a CUDA IPC memory handle is " + std::to_string(sizeof(cudaIpcMemHandle_t)) + " bytes";
+        return -1;
+    }
+    // opened with THIS accelerator's device current: that is the device whose kernels will store into the
+    // memory, and the flag lets the runtime set up peer access to the device that owns it
+    CU_TRY(h, cudaSetDevice(h->device));
+    cudaIpcMemHandle_t hd;
+    memcpy(&hd, handle, sizeof(hd));
+    void *p = nullptr;
+    CU_TRY(h, cudaIpcOpenMemHandle(&p, hd, cudaIpcMemLazyEnablePeerAccess));
+    *out = p;
+    return 1;
+}
+
+int strix_cuda_peek_u32(strix_cuda *h, const void *d_ptr, uint32_t *out) {
+    if (!h || !d_ptr || !out) return -1;
+    h->err.clear();
+    CU_TRY(h, cudaSetDevice(h->device));
+    CU_TRY(h, cudaMemcpy(out, d_ptr, sizeof(uint32_t), cudaMemcpyDeviceToHost));
+    return 1;
+}
+
+int strix_cuda_ipc_close(strix_cuda *h, void *p) {
+    if (!h || !p) return -1;
+    h->err.clear();
+    CU_TRY(h, cudaSetDevice(h->device));
+    CU_TRY(h, cudaIpcCloseMemHandle(p));
+    return 1;
+}
+
+int strix_cuda_peer_barrier_dev(strix_cuda *h, uint32_t *d_epoch, uint32_t *d_local_flags, uint32_t *const *peer_flags,
+                                void *stream) {
+    if (!h || !d_epoch || !d_local_flags || !peer_flags) return -1;
+    h->err.clear();
+    CU_TRY(h, cudaSetDevice(h->device));
+    CU_TRY(h, launch_peer_barrier(d_epoch, d_local_flags, peer_flags, h->rank, h->world, h->d_status,
+                                  static_cast<cudaStream_t>(stream)));
+    return 1;
+}
+
 int strix_cuda_gemv_rows_dev(strix_cuda *h, int nmat, const char *const *keys, const float *d_xs, size_t b, int act,
                              float *const *d_ys, void *stream) {
     if (!h || !keys || !d_xs || !d_ys) return -1;

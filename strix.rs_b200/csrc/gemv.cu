@@ -778,8 +778,13 @@ __device__ __forceinline__ void consumer_groups(const GemvArgs &A, Cta &C) {
                 float val = acc[v];
                 val *= oscale[j];
                 const size_t o = (size_t)j * A.mat[gr.mat].ystride + gr.row0 + row;
-                const float *res = A.mat[gr.mat].res;
-                A.mat[gr.mat].y[o] = res ? val + __ldcg(res + o) : val;
+                const GemvMat &M = A.mat[gr.mat];
+                if (M.res) val += __ldcg(M.res + o);
+                if (M.y) M.y[o] = val;
+                // row-sharded form: the row also goes straight into every accelerator's full vector
+                // (plain stores over NVLink peer memory; what makes them visible is the end of this
+                // kernel, which the barrier that follows it on the stream waits for)
+                for (uint32_t p = 0; p < M.n_peer; p++) M.peer_y[p][(size_t)M.row_base + o] = val;
             }
         }
     }
@@ -1133,6 +1138,39 @@ cudaError_t gemv_prepare_device(size_t smem_optin) {
         return e;
     return cudaFuncSetAttribute(gemv_chain_kernel<STRIX_ACT_Q8DOT>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                 (int)smem_optin);
+}
+
+// ---- cross-GPU barrier (one rank per GPU; never run two ranks of it on one GPU) ----
+struct PeerFlags {
+    uint32_t *p[GEMV_MAX_PEERS];
+};
+__global__ void peer_barrier_kernel(uint32_t *epoch, volatile uint32_t *local_flags, PeerFlags peers, int rank, int world,
+                                    uint32_t *status) {
+    __shared__ uint32_t seq;
+    if (threadIdx.x == 0) seq = ++(*epoch);
+    __syncthreads();
+    const uint32_t want = seq;
+    if ((int)threadIdx.x < world) {
+        // the kernels before this one on the stream have completed: their stores to peer memory are done
+        __threadfence_system();
+        asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(peers.p[threadIdx.x] + rank), "r"(want) : "memory");
+        bool ok = false;
+        for (uint32_t it = 0; it < (1u << 24) && !ok; ++it) {
+            uint32_t seen;
+            asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(seen) : "l"(local_flags + threadIdx.x) : "memory");
+            ok = (int32_t)(seen - want) >= 0;
+        }
+        if (!ok && status) atomicOr(status, STATUS_WAIT_TIMEOUT);  // bounded: report and go on
+    }
+}
+
+cudaError_t launch_peer_barrier(uint32_t *d_epoch, uint32_t *d_local_flags, uint32_t *const *peer_flags, int rank,
+                                int world, uint32_t *d_status, cudaStream_t stream) {
+    if (world < 1 || world > GEMV_MAX_PEERS) return cudaErrorInvalidValue;
+    PeerFlags pf{};
+    for (int i = 0; i < world; i++) pf.p[i] = peer_flags[i];
+    peer_barrier_kernel<<<1, 32, 0, stream>>>(d_epoch, d_local_flags, pf, rank, world, d_status);
+    return cudaGetLastError();
 }
 
 // ---- the activation quantiser on its own (xquant8_rows, kernels.rs:1000-1013) ----

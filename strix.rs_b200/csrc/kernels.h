@@ -16,6 +16,7 @@ cudaError_t launch_dequant(const uint8_t *d_res, float *d_out, const RowLayout &
 
 // ---- dequant-GEMV -------------------------------------------------------
 constexpr int GEMV_MAX_MATS = 3;
+constexpr int GEMV_MAX_PEERS = 8;
 constexpr int GEMV_MAX_STAGES = 96;
 // Consumer warps per CTA (plus one producer warp), one CTA per SM: six per scheduler.
 constexpr int GEMV_WARPS = 24;
@@ -28,6 +29,11 @@ struct GemvMat {
     uint32_t rows;
     uint32_t ystride;  // floats between the outputs (and residuals) of consecutive activation rows
     uint32_t tile0;  // index of this matrix's first tile in the launch-wide tile list
+    // Row-sharded multi-GPU form: every output is also stored into the FULL output vector of each of
+    // n_peer accelerators (peer-mapped device memory, this GPU's own copy included), at row_base + row.
+    float *peer_y[GEMV_MAX_PEERS];
+    uint32_t n_peer;
+    uint32_t row_base;
 };
 
 struct GemvArgs {
@@ -89,6 +95,12 @@ size_t gemm_workspace_floats(uint32_t M, uint32_t rows, uint32_t splits);
 cudaError_t launch_gemm_w8a8(const uint8_t *d_res, const RowLayout &L, uint32_t rows, const float *d_scalesT,
                              const int8_t *d_xq, const float *d_xd, const int32_t *d_xs, uint32_t M, float *d_y,
                              float *d_part, uint32_t splits, uint32_t *d_status, cudaStream_t stream);
+
+// Cross-GPU barrier on flag words in peer-mapped memory (one launch per rank, one rank per GPU):
+// bumps *d_epoch, stores the new value into flag word `rank` of every rank's flag array and waits
+// (bounded) until all `world` words of this rank's own array have reached it.
+cudaError_t launch_peer_barrier(uint32_t *d_epoch, uint32_t *d_local_flags, uint32_t *const *peer_flags, int rank,
+                                int world, uint32_t *d_status, cudaStream_t stream);
 
 // The activation quantiser on its own: q[n] int8, d[n/32] f32 from x[n].
 cudaError_t launch_xquant8(const float *d_x, int8_t *d_q, float *d_d, uint32_t n, cudaStream_t stream);

@@ -189,6 +189,52 @@ def test_sharded_accelerators_cover_all_rows(pkg, orc, synth):
     assert got.size == out_dim and rel_l2(got, want) <= REL_L2_TOL
 
 
+def test_peer_store_form_fills_full_vectors_on_every_peer(pkg, orc, synth):
+    """The multi-GPU epilogue on one GPU: the "peers" are two full-length buffers of this device. Each rank
+    handle (run one after the other: nothing here waits on another rank) stores its row shard at its row
+    offset into both; after all ranks both buffers hold the whole product. The residual is the shard's rows."""
+    import torch
+    dev = torch.device("cuda:0")
+    in_dim, out_dim, world = 512, 208, 2
+    w = synth.q4_0(51, "peer", out_dim, in_dim)
+    x = synth.normal(51, "peer.x", in_dim)
+    res = synth.normal(51, "peer.res", out_dim)
+    want = orc.qmatmul(x, w, synth.Q4_0, in_dim, out_dim) + res
+    d_x, d_res = torch.from_numpy(x).to(dev), torch.from_numpy(res).to(dev)
+    full = [torch.full((out_dim,), float("nan"), device=dev) for _ in range(2)]
+    s = torch.cuda.current_stream().cuda_stream
+    for r in range(world):
+        a = pkg.CudaWeightAccel(0, rank=r, world=world)
+        try:
+            assert a.upload_q4_0("peer", w, in_dim, out_dim)
+            row0 = a.weight_info("peer")["row0"]
+            assert a.gemv_peers_dev(["peer"], d_x.data_ptr(), [[f.data_ptr() for f in full]], stream=s,
+                                    d_res=[d_res.data_ptr() + 4 * row0])
+            torch.cuda.synchronize()
+            assert a.device_status(s) == 0
+        finally:
+            a.close()
+    for f in full:
+        assert rel_l2(f.cpu().numpy(), want) <= REL_L2_TOL
+
+
+def test_peer_barrier_single_rank(pkg):
+    """world = 1: the barrier bumps its epoch and finds its own flag; no other rank is involved."""
+    import torch
+    dev = torch.device("cuda:0")
+    a = pkg.CudaWeightAccel(0)
+    try:
+        epoch = torch.zeros(1, dtype=torch.int32, device=dev)
+        flags = torch.zeros(8, dtype=torch.int32, device=dev)
+        s = torch.cuda.current_stream().cuda_stream
+        for _ in range(3):
+            a.peer_barrier_dev(epoch.data_ptr(), flags.data_ptr(), [flags.data_ptr()], stream=s)
+        torch.cuda.synchronize()
+        assert int(epoch.item()) == 3 and int(flags[0].item()) == 3 and a.device_status(s) == 0
+    finally:
+        a.close()
+
+
 # ------------------------------------------------------------------ device-resident form + fused prologues
 def test_gemv_dev_prologues_and_fused_weights(accel, orc, synth, pkg):
     import torch
