@@ -359,7 +359,31 @@ def decode_chain_sharded_extra(pkg, synth, torch, dist, local, stream, rank, wor
                                       pre=pkg.PRE_RMSNORM, act=act, stream=s)
             bar()
 
-        variants = [("nccl", chain)] + ([("fused", chain_fused)] if fused["ok"] else [])
+        def chain_fused_sync(act):
+            """as chain_fused, but the exchange lives inside the GEMV kernels: no barrier launch between steps"""
+            s = torch.cuda.current_stream().cuda_stream
+            p = lambda t: t.data_ptr()  # noqa: E731
+            sy = fused["sync"]
+            for il in range(n_layers):
+                b = "blk.%d." % il
+                an, fn = norms[il]
+                assert acc.gemv_peers_dev([b + "attn_q.weight", b + "attn_k.weight", b + "attn_v.weight"], p(h_full),
+                                          [ptrs["q"], ptrs["k"], ptrs["v"]], d_b=p(an), eps=1e-6, pre=pkg.PRE_RMSNORM,
+                                          act=act, stream=s, sync=sy)
+                assert acc.gemv_peers_dev([b + "attn_output.weight"], p(q_full), [ptrs["h"]], act=act, stream=s,
+                                          d_res=[p(h_res)], sync=sy)
+                assert acc.gemv_peers_dev([b + "ffn_gate.weight", b + "ffn_up.weight"], p(h_full), [ptrs["g"], ptrs["u"]],
+                                          d_b=p(fn), eps=1e-6, pre=pkg.PRE_RMSNORM, act=act, stream=s, sync=sy)
+                assert acc.gemv_peers_dev([b + "ffn_down.weight"], p(g_full), [ptrs["h"]], d_b=p(u_full),
+                                          pre=pkg.PRE_SWIGLU, act=act, stream=s, d_res=[p(h_res)], sync=sy)
+            assert acc.gemv_peers_dev(["output.weight"], p(h_full), [ptrs["lg"]], d_b=p(out_norm), eps=1e-6,
+                                      pre=pkg.PRE_RMSNORM, act=act, stream=s, sync=sy)
+            acc.peer_barrier_dev(p(epoch), p(flags), ptrs["flags"], stream=s)   # before anyone reads the logits
+
+        if fused["ok"]:
+            done = torch.zeros(1, dtype=torch.int32, device=dev)
+            fused["sync"] = acc.make_peer_sync(epoch.data_ptr(), done.data_ptr(), flags.data_ptr(), ptrs["flags"])
+        variants = [("nccl", chain)] + ([("fused", chain_fused), ("fused_sync", chain_fused_sync)] if fused["ok"] else [])
         logits_ref = None
         for vname, chain in variants:
           for act, name in ((pkg.ACT_Q8DOT, "q8dot"),):
@@ -396,13 +420,14 @@ def decode_chain_sharded_extra(pkg, synth, torch, dist, local, stream, rank, wor
                 assert bool((lg_full == logits_ref).all()), "fused and NCCL chains disagree"
             out[vname + "_" + name] = {"ms_per_token": round(ms, 4), "gbs_aggregate": round(nbytes / ms / 1e6, 1),
                                        "gbs_per_gpu": round(nbytes / ms / 1e6 / world, 1),
-                                       "launches_per_token": (4 * n_layers + 1) * (2 if vname == "fused" else 1),
+                                       "launches_per_token": (4 * n_layers + 1) * (2 if vname == "fused" else 1) + (vname == "fused_sync"),
                                        "collectives_per_token": 4 * n_layers + 1 if vname == "nccl" else 0}
         out["n_gpus"] = world
         out["bytes_per_token"] = nbytes
         out["note"] = ("row-sharded projections; nccl: all-gather after each projection or fused group (coalesced: %s); "
                        "fused: the GEMV stores its rows into every rank's vectors over peer memory, then a flag barrier "
-                       "(%s); attention replaced by feeding Wo with q"
+                       "kernel; fused_sync: the flag wait / release sits inside the GEMV kernels (%s); attention replaced "
+                       "by feeding Wo with q"
                        % (state["coalesce"], "ran" if fused["ok"] else "not run: " + fused["why"]))
     finally:
         acc.close()

@@ -136,10 +136,21 @@ STRIX_API int strix_cuda_gemv_res_dev(strix_cuda *h, int nmat, const char *const
  * of the group (peer-mapped device memory, this accelerator's own copy among them), so that no
  * all-gather follows. d_res (may be null, entries may be null) are this shard's rows of residual
  * vectors. The stores are plain peer stores; they are complete when the kernel is, and
- * strix_cuda_peer_barrier_dev after it on every rank's stream makes them safe to read. */
+ * strix_cuda_peer_barrier_dev after it on every rank's stream makes them safe to read.
+ * With `sync` (may be null) the exchange is folded into the kernel: before it reads the activations it
+ * waits (bounded) until every rank's word in d_local_flags has reached *d_epoch, and when its last CTA
+ * has stored its rows it bumps *d_epoch and releases it into word `rank` of every rank's flag array -
+ * so a chain of such launches needs no barrier launch between them (one strix_cuda_peer_barrier_dev at
+ * the end of the chain, before the host reads results). */
+typedef struct strix_peer_sync {
+    uint32_t *d_epoch;            /* one word of this rank, shared with strix_cuda_peer_barrier_dev; starts at 0 */
+    uint32_t *d_done;             /* one word of this rank, starts at 0 */
+    uint32_t *d_local_flags;      /* `world` words of this rank, start at 0 */
+    uint32_t *const *peer_flags;  /* [world]: rank i's flag array as mapped into this process */
+} strix_peer_sync;
 STRIX_API int strix_cuda_gemv_peers_dev(strix_cuda *h, int nmat, const char *const *keys, const float *d_a,
                               const float *d_b, float eps, int pre, int act, const float *const *d_res,
-                              int n_peers, float *const *peer_ys, void *stream);
+                              int n_peers, float *const *peer_ys, const strix_peer_sync *sync, void *stream);
 /* Lets kernels of this accelerator's device store into memory of `peer_device` (as mapped into this
  * process, e.g. through CUDA IPC). 1 = enabled (or already so), 0 = the devices cannot reach each other. */
 STRIX_API int strix_cuda_enable_peer_access(strix_cuda *h, int peer_device);

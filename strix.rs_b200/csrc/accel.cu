@@ -464,7 +464,7 @@ int strix_cuda_gemv_res_dev(strix_cuda *h, int nmat, const char *const *keys, co
 
 int strix_cuda_gemv_peers_dev(strix_cuda *h, int nmat, const char *const *keys, const float *d_a, const float *d_b,
                               float eps, int pre, int act, const float *const *d_res, int n_peers,
-                              float *const *peer_ys, void *stream) {
+                              float *const *peer_ys, const strix_peer_sync *sync, void *stream) {
     if (!h || !keys || !d_a || !peer_ys) return -1;
     h->err.clear();
     if (nmat < 1 || nmat > GEMV_MAX_MATS || n_peers < 1 || n_peers > GEMV_MAX_PEERS) {
@@ -490,6 +490,22 @@ int strix_cuda_gemv_peers_dev(strix_cuda *h, int nmat, const char *const *keys, 
         for (int p = 0; p < n_peers; p++) a.mat[m].peer_y[p] = peer_ys[m * n_peers + p];
     }
     a.nbatch = 1;
+    if (sync) {
+        if (!sync->d_epoch || !sync->d_done || !sync->d_local_flags || !sync->peer_flags) {
+            h->err = "gemv_peers_dev: incomplete sync block";
+            return -1;
+        }
+        a.sync_epoch = sync->d_epoch;
+        a.sync_done = sync->d_done;
+        a.sync_local = sync->d_local_flags;
+        a.sync_world = (uint32_t)h->world;
+        a.sync_rank = (uint32_t)h->rank;
+        if (h->world > GEMV_MAX_PEERS) {
+            h->err = "gemv_peers_dev: at most 8 ranks";
+            return -1;
+        }
+        for (int p = 0; p < h->world; p++) a.sync_peer[p] = sync->peer_flags[p];
+    }
     if (!gemv_plan(a, h->num_sms, h->smem_optin)) {
         h->err = "gemv_peers_dev: in_dim too large for the shared-memory pipeline";
         return -1;

@@ -60,6 +60,13 @@ struct GemvArgs {
     uint32_t multi;          // integer form with more than one activation row (Q4_0 / Q8_0)
     uint32_t pdl;            // launch with programmatic stream serialization
     uint32_t rot;            // chain kernel: CTA that takes the step's first row group
+    // Row-sharded multi-GPU form with the exchange folded in (null sync_epoch = off): the consumers wait
+    // (bounded) until every rank's flag word in sync_local has reached *sync_epoch before they read the
+    // activations, and the last CTA to finish bumps *sync_epoch and releases it into word sync_rank of every
+    // rank's flag array. sync_done counts finished CTAs.
+    uint32_t *sync_epoch, *sync_done, *sync_local;
+    uint32_t *sync_peer[GEMV_MAX_PEERS];
+    uint32_t sync_world, sync_rank;
     uint32_t grid;
     uint32_t smem_bytes;
     uint32_t debug;  // measurement only: bit 0 = stream the tiles but skip the arithmetic

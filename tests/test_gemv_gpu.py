@@ -218,6 +218,35 @@ def test_peer_store_form_fills_full_vectors_on_every_peer(pkg, orc, synth):
         assert rel_l2(f.cpu().numpy(), want) <= REL_L2_TOL
 
 
+def test_peer_store_form_with_folded_exchange_single_rank(pkg, orc, synth):
+    """world = 1: the kernel waits on its own flag (already there), stores, and its last CTA releases the
+    next epoch; a second launch finds that epoch. No other rank is involved, so nothing can wait for ever."""
+    import torch
+    dev = torch.device("cuda:0")
+    in_dim, out_dim = 1024, 333
+    w = synth.q8_0(52, "sync", out_dim, in_dim)
+    x = synth.normal(52, "sync.x", in_dim)
+    want = orc.qmatmul(x, w, synth.Q8_0, in_dim, out_dim)
+    a = pkg.CudaWeightAccel(0)
+    try:
+        assert a.upload_q8_0("sync", w, in_dim, out_dim)
+        d_x = torch.from_numpy(x).to(dev)
+        y = torch.full((out_dim,), float("nan"), device=dev)
+        epoch, done = torch.zeros(1, dtype=torch.int32, device=dev), torch.zeros(1, dtype=torch.int32, device=dev)
+        flags = torch.zeros(8, dtype=torch.int32, device=dev)
+        sync = a.make_peer_sync(epoch.data_ptr(), done.data_ptr(), flags.data_ptr(), [flags.data_ptr()])
+        s = torch.cuda.current_stream().cuda_stream
+        for _ in range(2):
+            assert a.gemv_peers_dev(["sync"], d_x.data_ptr(), [[y.data_ptr()]], stream=s, sync=sync)
+        a.peer_barrier_dev(epoch.data_ptr(), flags.data_ptr(), [flags.data_ptr()], stream=s)
+        torch.cuda.synchronize()
+        assert a.device_status(s) == 0
+        assert int(epoch.item()) == 3 and int(flags[0].item()) == 3 and int(done.item()) == 0
+        assert rel_l2(y.cpu().numpy(), want) <= REL_L2_TOL
+    finally:
+        a.close()
+
+
 def test_peer_barrier_single_rank(pkg):
     """world = 1: the barrier bumps its epoch and finds its own flag; no other rank is involved."""
     import torch
