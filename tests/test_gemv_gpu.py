@@ -94,6 +94,9 @@ GEMV_CASES = [
     (2, 1, 32), (2, 7, 64), (2, 9, 96), (2, 257, 2560), (2, 4096, 4096), (2, 2560, 9728), (2, 100, 16384),
     (8, 1, 32), (8, 8, 64), (8, 9, 3840), (8, 9728, 2560), (8, 2560, 9728), (8, 64, 16384),
     (14, 1, 256), (14, 7, 512), (14, 17, 3840), (14, 9728, 2560), (14, 2560, 9728), (14, 40, 16384),
+    # rows longer than the activation prologue keeps in registers (6 float4 x 768 threads = 18432 values):
+    # the rest of the row is re-read; and the widest FFN of the reference's model zoo (27648)
+    (2, 33, 20480), (8, 20, 27648), (14, 18, 20480),
 ]
 
 
