@@ -280,6 +280,8 @@ void strix_cuda_destroy(strix_cuda *h) {
     cudaSetDevice(h->device);
     cudaStreamSynchronize(h->stream);
     decode_release(h);
+    if (h->copy_stream) cudaStreamDestroy(h->copy_stream);
+    for (cudaEvent_t e : h->batch_events) cudaEventDestroy(e);
     for (auto &kv : h->weights) {
         cudaFree(kv.second.dev);
         if (kv.second.gemm_codes) cudaFree(kv.second.gemm_codes);
@@ -388,24 +390,40 @@ int strix_cuda_gemv_batch(strix_cuda *h, size_t n, const char *const *keys, cons
     for (size_t i = 0; i < n; i++)
         if (ws[i]) memcpy(pin + xoff[i], xs[i], ws[i]->L.in_dim * sizeof(float));
     CU_TRY(h, cudaMemcpyAsync(h->x.p, pin, xtot * 4, cudaMemcpyHostToDevice, h->stream));
+    // Outputs leave on a second stream, each as soon as its kernel is done, so that the copies (and the
+    // host's own copy out of the pinned buffer) overlap the kernels still to run.
+    if (!h->copy_stream) CU_TRY(h, cudaStreamCreateWithFlags(&h->copy_stream, cudaStreamNonBlocking));
+    while (h->batch_events.size() < 2 * n) {
+        cudaEvent_t e = nullptr;
+        CU_TRY(h, cudaEventCreateWithFlags(&e, cudaEventDisableTiming));
+        h->batch_events.push_back(e);
+    }
     for (size_t i = 0; i < n; i++) {
         if (!ws[i]) continue;
         const Resident *w1[1] = {ws[i]};
         float *y1[1] = {h->y.p + yoff[i]};
         if (gemv_launch(h, 1, w1, h->x.p + xoff[i], nullptr, 0.f, STRIX_PRE_NONE, act, y1, nullptr, h->stream) < 0) return -1;
+        cudaEvent_t done = h->batch_events[2 * i], copied = h->batch_events[2 * i + 1];
+        CU_TRY(h, cudaEventRecord(done, h->stream));
+        CU_TRY(h, cudaStreamWaitEvent(h->copy_stream, done, 0));
+        if (ws[i]->rows)
+            CU_TRY(h, cudaMemcpyAsync(pout + yoff[i], h->y.p + yoff[i], ws[i]->rows * 4, cudaMemcpyDeviceToHost, h->copy_stream));
+        CU_TRY(h, cudaEventRecord(copied, h->copy_stream));
     }
-    if (ytot) CU_TRY(h, cudaMemcpyAsync(pout, h->y.p, ytot * 4, cudaMemcpyDeviceToHost, h->stream));
-    uint32_t st = 0;
     CU_TRY(h, cudaMemcpyAsync(&h->status_host, h->d_status, 4, cudaMemcpyDeviceToHost, h->stream));
+    // hand each output to the caller as its copy lands
+    for (size_t i = 0; i < n; i++) {
+        if (!ws[i]) continue;
+        CU_TRY(h, cudaEventSynchronize(h->batch_events[2 * i + 1]));
+        memcpy(ys[i], pout + yoff[i], ws[i]->rows * sizeof(float));
+    }
     CU_TRY(h, cudaStreamSynchronize(h->stream));
-    st = h->status_host;
+    const uint32_t st = h->status_host;
     if (st != 0) {
         h->err = "gemv: device status " + std::to_string(st) + " (a bounded wait ran out)";
         cudaMemsetAsync(h->d_status, 0, 4, h->stream);
         return -2;
     }
-    for (size_t i = 0; i < n; i++)
-        if (ws[i]) memcpy(ys[i], pout + yoff[i], ws[i]->rows * sizeof(float));
     return 1;
 }
 

@@ -5,6 +5,7 @@
 
 #include <string>
 #include <unordered_map>
+#include <vector>
 
 #include "kernels.h"
 #include "strix_cuda.h"
@@ -45,6 +46,8 @@ struct strix_cuda {
     size_t smem_optin = 0;
     std::string name, err;
     cudaStream_t stream = nullptr;
+    cudaStream_t copy_stream = nullptr;        // gemv_batch: outputs leave here while later kernels run
+    std::vector<cudaEvent_t> batch_events;     // gemv_batch: (kernel done, copy done) per call slot
     uint32_t *d_status = nullptr;
     uint32_t status_host = 0;
     std::unordered_map<std::string, strix::Resident> weights;

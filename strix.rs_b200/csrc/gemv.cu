@@ -111,7 +111,7 @@ __device__ __forceinline__ GroupRef group_ref(const GemvArgs &A, uint32_t t) {
 //   0     full[96]   mbarriers: a stage's bulk copy has landed             (producer arms, copy completes)
 //   768   empty[96]  mbarriers: the stage's consumer warps are done with it (one arrival per warp of the slot)
 //   1536  ctl[0]     abort flag (a bounded wait ran out)
-//   1600  red[64]    block reduction scratch (prologue): 32 sums of squares, 32 maxima
+//   1600  (64 words spare)
 //   1856  oscale[8]  factor applied to the outputs of activation row j: the RMSNorm scale (which is
 //                    linear, so it is applied after the product) / the power-of-two scale of the f16 split
 //   1920  part       24 warps x 32 lanes x NV partial sums (rows split along K over the warps of a slot)
@@ -502,7 +502,6 @@ __device__ __forceinline__ void producer_step(const GemvArgs &A, Cta &C) {
 template <int FMT, int ACT, bool MULTI>
 __device__ __forceinline__ void consumer_prologue(const GemvArgs &A, const Cta &C) {
     uint8_t *smem = C.smem;
-    float *red = reinterpret_cast<float *>(smem + SMEM_RED_OFF);
     float *oscale = reinterpret_cast<float *>(smem + SMEM_OSCALE_OFF);
     const uint32_t tid = C.tid, lane = C.lane, warp = C.warp, n_cons = C.n_cons;
     const uint32_t K = A.L.in_dim, B = A.nbatch;
@@ -517,8 +516,21 @@ __device__ __forceinline__ void consumer_prologue(const GemvArgs &A, const Cta &
             // records of columns that carry no activation row stay zero (what they produce is never stored)
             uint32_t *z = reinterpret_cast<uint32_t *>(smem + XL.rec);
             for (uint32_t i = tid; i < (XL.end - XL.rec) / 4u; i += ct) z[i] = 0u;
+            STRIX_CONS_BAR();
         }
-        for (uint32_t bi = 0; bi < B; bi++) {
+        // With several activation rows the warps split into one group per row and the rows are
+        // prepared side by side (their trips to global memory overlap); a group meets at a named
+        // barrier of its own. gt / gct: this thread's index in its group / threads per group.
+        // (Long rows stay with all warps, one row after the other: a group of three warps would have to
+        // re-read most of a 15360-long row, which measured slower than taking turns.)
+        const bool grouped = B > 1 && K <= 8192u;
+        const uint32_t wpg = grouped ? n_cons / B : n_cons;  // warps per group
+        const uint32_t n_groups = grouped ? B : 1u;
+        const uint32_t grp = warp / wpg, gw = warp - grp * wpg;
+        const uint32_t gt = gw * 32u + lane, gct = wpg * 32u;
+        float *scr = reinterpret_cast<float *>(smem + SMEM_PART_OFF);  // [row][2][32]: the partial-sum area is idle here
+#define STRIX_ROW_BAR() asm volatile("bar.sync %0, %1;" ::"r"(grouped ? 1u + grp : 15u), "r"(gct) : "memory")
+        for (uint32_t bi = grp; bi < B && grp < n_groups; bi += n_groups) {
             const float *Aa = A.a + (size_t)bi * A.a_stride;
             const float *Ab = A.b ? A.b + (size_t)bi * A.b_stride : nullptr;
             // phase A: load, apply the pre-op (without the RMSNorm scalar), partial sum of squares / maximum
@@ -526,12 +538,12 @@ __device__ __forceinline__ void consumer_prologue(const GemvArgs &A, const Cta &
             float ss = 0.f, amax = 0.f;
 #pragma unroll
             for (uint32_t i = 0; i < NI; i++) {
-                const uint32_t e4 = tid + i * ct;
+                const uint32_t e4 = gt + i * gct;
                 v[i] = make_float4(0.f, 0.f, 0.f, 0.f);
                 if (e4 < K4) v[i] = load_pre(Aa, Ab, A.pre, e4, ss);
                 amax = fmaxf(fmaxf(amax, fmaxf(fabsf(v[i].x), fabsf(v[i].y))), fmaxf(fabsf(v[i].z), fabsf(v[i].w)));
             }
-            for (uint32_t e4 = tid + NI * ct; e4 < K4; e4 += ct) {
+            for (uint32_t e4 = gt + NI * gct; e4 < K4; e4 += gct) {
                 const float4 t4 = load_pre(Aa, Ab, A.pre, e4, ss);
                 amax = fmaxf(fmaxf(amax, fmaxf(fabsf(t4.x), fabsf(t4.y))), fmaxf(fabsf(t4.z), fabsf(t4.w)));
             }
@@ -541,14 +553,14 @@ __device__ __forceinline__ void consumer_prologue(const GemvArgs &A, const Cta &
 #pragma unroll
                 for (int o = 16; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
                 if (lane == 0) {
-                    red[warp] = ss;
-                    red[32 + warp] = amax;
+                    scr[bi * 64u + gw] = ss;
+                    scr[bi * 64u + 32u + gw] = amax;
                 }
-                STRIX_CONS_BAR();
+                STRIX_ROW_BAR();
                 float tot = 0.f, am = 0.f;
-                for (uint32_t w2 = 0; w2 < n_cons; w2++) {
-                    tot += red[w2];
-                    am = fmaxf(am, red[32 + w2]);
+                for (uint32_t w2 = 0; w2 < wpg; w2++) {
+                    tot += scr[bi * 64u + w2];
+                    am = fmaxf(am, scr[bi * 64u + 32u + w2]);
                 }
                 // rmsnorm (crates/strix-backend-cpu/src/qwen3.rs:107-114): x * (1/sqrt(mean(x^2)+eps)) * w
                 float os = A.pre == STRIX_PRE_RMSNORM ? 1.0f / sqrtf(tot / (float)K + A.eps) : 1.0f;
@@ -564,15 +576,14 @@ __device__ __forceinline__ void consumer_prologue(const GemvArgs &A, const Cta &
                         os *= __uint_as_float((uint32_t)(254 - se) << 23);  // times 1/s, exact
                     }
                 }
-                if (tid == 0) oscale[bi] = os;
-                if (B > 1) STRIX_CONS_BAR();  // red[] is written again for the next activation row
-            } else if (tid == 0) {
+                if (gt == 0) oscale[bi] = os;
+            } else if (gt == 0) {
                 oscale[bi] = 1.0f;
             }
             // phase B: build the operands
             for (uint32_t i = 0;; i++) {
-                const uint32_t e4 = tid + i * ct;
-                if ((tid - lane) + i * ct >= K4) break;  // the whole warp is past the row's end (the loop body shuffles)
+                const uint32_t e4 = gt + i * gct;
+                if ((gt - lane) + i * gct >= K4) break;  // the whole warp is past the row's end (the loop body shuffles)
                 const bool live = e4 < K4;
                 float4 t4 = make_float4(0.f, 0.f, 0.f, 0.f);
                 if (i < NI) {
@@ -649,6 +660,7 @@ __device__ __forceinline__ void consumer_prologue(const GemvArgs &A, const Cta &
             }
         }
     }
+#undef STRIX_ROW_BAR
     STRIX_CONS_BAR();
 }
 
