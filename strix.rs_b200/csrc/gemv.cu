@@ -361,14 +361,15 @@ __device__ __forceinline__ void tile_mac(uint32_t ta, uint32_t da, uint32_t xb_a
 // The activation after the optional pre-op, four consecutive elements (e4 = float4 index). RMSNorm is
 // applied WITHOUT its scalar 1/rms (the caller multiplies the outputs by it); `ss` collects the
 // squares of the raw values for it.
-__device__ __forceinline__ float4 load_pre(const float *Aa, const float *Ab, int pre, uint32_t e4, float &ss) {
+template <int PRE>
+__device__ __forceinline__ float4 load_pre(const float *Aa, const float *Ab, uint32_t e4, float &ss) {
     float4 a4 = __ldcg(reinterpret_cast<const float4 *>(Aa) + e4);
-    if (pre != STRIX_PRE_NONE) {
+    if (PRE != STRIX_PRE_NONE) {
         const float4 b4 = __ldcg(reinterpret_cast<const float4 *>(Ab) + e4);
-        if (pre == STRIX_PRE_RMSNORM) {
+        if (PRE == STRIX_PRE_RMSNORM) {
             ss = fmaf(a4.x, a4.x, ss); ss = fmaf(a4.y, a4.y, ss); ss = fmaf(a4.z, a4.z, ss); ss = fmaf(a4.w, a4.w, ss);
             a4.x *= b4.x; a4.y *= b4.y; a4.z *= b4.z; a4.w *= b4.w;
-        } else if (pre == STRIX_PRE_SWIGLU) {
+        } else if (PRE == STRIX_PRE_SWIGLU) {
             a4.x = silu_f(a4.x) * b4.x; a4.y = silu_f(a4.y) * b4.y;
             a4.z = silu_f(a4.z) * b4.z; a4.w = silu_f(a4.w) * b4.w;
         } else {
@@ -499,7 +500,9 @@ __device__ __forceinline__ void producer_step(const GemvArgs &A, Cta &C) {
 // here at all: the product is linear in it, so it multiplies the outputs (oscale).
 // (Activations are read past L1: inside a chain kernel another CTA wrote them a moment ago.)
 #define STRIX_CONS_BAR() asm volatile("bar.sync 15, %0;" ::"r"(ct) : "memory")
-template <int FMT, int ACT, bool MULTI>
+// (The pre-op is a template parameter: with all four inlined at every unrolled load the prologue
+// alone was most of the kernel's code, and a small launch spent its time fetching instructions.)
+template <int FMT, int ACT, bool MULTI, int PRE>
 __device__ __forceinline__ void consumer_prologue(const GemvArgs &A, const Cta &C) {
     uint8_t *smem = C.smem;
     float *oscale = reinterpret_cast<float *>(smem + SMEM_OSCALE_OFF);
@@ -511,7 +514,7 @@ __device__ __forceinline__ void consumer_prologue(const GemvArgs &A, const Cta &
         constexpr uint32_t NI = 6;  // float4s a thread keeps in registers; longer rows re-load the rest
         const uint32_t K4 = K / 4u, l8 = lane & 7u;
         const bool need_max = ACT == STRIX_ACT_F32;
-        const bool need_red = need_max || A.pre == STRIX_PRE_RMSNORM;
+        const bool need_red = need_max || PRE == STRIX_PRE_RMSNORM;
         if (XL.end > XL.rec && B > 1) {
             // records of columns that carry no activation row stay zero (what they produce is never stored)
             uint32_t *z = reinterpret_cast<uint32_t *>(smem + XL.rec);
@@ -540,11 +543,11 @@ __device__ __forceinline__ void consumer_prologue(const GemvArgs &A, const Cta &
             for (uint32_t i = 0; i < NI; i++) {
                 const uint32_t e4 = gt + i * gct;
                 v[i] = make_float4(0.f, 0.f, 0.f, 0.f);
-                if (e4 < K4) v[i] = load_pre(Aa, Ab, A.pre, e4, ss);
+                if (e4 < K4) v[i] = load_pre<PRE>(Aa, Ab, e4, ss);
                 amax = fmaxf(fmaxf(amax, fmaxf(fabsf(v[i].x), fabsf(v[i].y))), fmaxf(fabsf(v[i].z), fabsf(v[i].w)));
             }
             for (uint32_t e4 = gt + NI * gct; e4 < K4; e4 += gct) {
-                const float4 t4 = load_pre(Aa, Ab, A.pre, e4, ss);
+                const float4 t4 = load_pre<PRE>(Aa, Ab, e4, ss);
                 amax = fmaxf(fmaxf(amax, fmaxf(fabsf(t4.x), fabsf(t4.y))), fmaxf(fabsf(t4.z), fabsf(t4.w)));
             }
             float s = 1.0f;  // f32 form: power-of-two scale before the f16 split
@@ -563,7 +566,7 @@ __device__ __forceinline__ void consumer_prologue(const GemvArgs &A, const Cta &
                     am = fmaxf(am, scr[bi * 64u + 32u + w2]);
                 }
                 // rmsnorm (crates/strix-backend-cpu/src/qwen3.rs:107-114): x * (1/sqrt(mean(x^2)+eps)) * w
-                float os = A.pre == STRIX_PRE_RMSNORM ? 1.0f / sqrtf(tot / (float)K + A.eps) : 1.0f;
+                float os = PRE == STRIX_PRE_RMSNORM ? 1.0f / sqrtf(tot / (float)K + A.eps) : 1.0f;
                 if (need_max) {
                     // largest magnitude -> power-of-two scale that puts it in [2^13, 2^14): keeps hi inside the
                     // f16 range, and lo (the 11 bits below hi) out of the subnormals except for values
@@ -593,7 +596,7 @@ __device__ __forceinline__ void consumer_prologue(const GemvArgs &A, const Cta &
                         if (k == i) t4 = v[k];
                 } else if (live) {
                     float dummy = 0.f;
-                    t4 = load_pre(Aa, Ab, A.pre, e4, dummy);
+                    t4 = load_pre<PRE>(Aa, Ab, e4, dummy);
                 }
                 const uint32_t blk = e4 >> 3, t = l8 & 3u, hf = l8 >> 2;
                 if (ACT == STRIX_ACT_F32) {
@@ -830,7 +833,7 @@ __device__ __forceinline__ Cta cta_init(uint8_t *smem, uint32_t wc, uint32_t n_s
 }
 
 // One launch = one step: up to three weights that share an activation.
-template <int FMT, int ACT, bool MULTI>
+template <int FMT, int ACT, bool MULTI, int PRE>
 __global__ void __launch_bounds__((GEMV_WARPS + 1) * 32, 1) gemv_kernel(const __grid_constant__ GemvArgs A) {
     extern __shared__ __align__(128) uint8_t smem[];
     // Programmatic dependent launch: the next kernel of the stream may start on an SM as soon as this
@@ -863,7 +866,7 @@ __global__ void __launch_bounds__((GEMV_WARPS + 1) * 32, 1) gemv_kernel(const __
         }
         asm volatile("bar.sync 15, %0;" ::"r"(C.n_cons * 32u) : "memory");
     }
-    consumer_prologue<FMT, ACT, MULTI>(A, C);
+    consumer_prologue<FMT, ACT, MULTI, PRE>(A, C);
     if (A.debug & 4u) return;  // measurement only: stop after the activation prologue
     consumer_groups<FMT, ACT, MULTI>(A, C);
     if (A.sync_epoch) {
@@ -881,6 +884,16 @@ __global__ void __launch_bounds__((GEMV_WARPS + 1) * 32, 1) gemv_kernel(const __
                     asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(A.sync_peer[p] + A.sync_rank), "r"(e) : "memory");
             }
         }
+    }
+}
+
+template <int FMT, int ACT>
+__device__ __forceinline__ void chain_prologue(const GemvArgs &A, const Cta &C) {
+    switch (A.pre) {
+        case STRIX_PRE_NONE: consumer_prologue<FMT, ACT, false, STRIX_PRE_NONE>(A, C); break;
+        case STRIX_PRE_RMSNORM: consumer_prologue<FMT, ACT, false, STRIX_PRE_RMSNORM>(A, C); break;
+        case STRIX_PRE_SWIGLU: consumer_prologue<FMT, ACT, false, STRIX_PRE_SWIGLU>(A, C); break;
+        default: consumer_prologue<FMT, ACT, false, STRIX_PRE_GEGLU>(A, C); break;
     }
 }
 
@@ -937,17 +950,17 @@ gemv_chain_kernel(const GemvArgs *__restrict__ steps, uint32_t n_steps, uint32_t
         STRIX_TRACE(0)
         switch (A.L.fmt) {
             case FMT_Q4_0:
-                consumer_prologue<FMT_Q4_0, ACT, false>(A, C);
+                chain_prologue<FMT_Q4_0, ACT>(A, C);
                 STRIX_TRACE(1)
                 consumer_groups<FMT_Q4_0, ACT, false>(A, C);
                 break;
             case FMT_Q8_0:
-                consumer_prologue<FMT_Q8_0, ACT, false>(A, C);
+                chain_prologue<FMT_Q8_0, ACT>(A, C);
                 STRIX_TRACE(1)
                 consumer_groups<FMT_Q8_0, ACT, false>(A, C);
                 break;
             default:
-                consumer_prologue<FMT_Q6_K, ACT, false>(A, C);
+                chain_prologue<FMT_Q6_K, ACT>(A, C);
                 STRIX_TRACE(1)
                 consumer_groups<FMT_Q6_K, ACT, false>(A, C);
                 break;
@@ -1067,7 +1080,13 @@ static cudaError_t launch_t(const GemvArgs &a, cudaStream_t stream) {
     at[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = at;
     cfg.numAttrs = a.pdl ? 1u : 0u;
-    return cudaLaunchKernelEx(&cfg, gemv_kernel<FMT, ACT, MULTI>, a);
+    switch (a.pre) {
+        case STRIX_PRE_NONE: return cudaLaunchKernelEx(&cfg, gemv_kernel<FMT, ACT, MULTI, STRIX_PRE_NONE>, a);
+        case STRIX_PRE_RMSNORM: return cudaLaunchKernelEx(&cfg, gemv_kernel<FMT, ACT, MULTI, STRIX_PRE_RMSNORM>, a);
+        case STRIX_PRE_SWIGLU: return cudaLaunchKernelEx(&cfg, gemv_kernel<FMT, ACT, MULTI, STRIX_PRE_SWIGLU>, a);
+        case STRIX_PRE_GEGLU: return cudaLaunchKernelEx(&cfg, gemv_kernel<FMT, ACT, MULTI, STRIX_PRE_GEGLU>, a);
+        default: return cudaErrorInvalidValue;
+    }
 }
 
 template <int FMT>
@@ -1164,13 +1183,17 @@ cudaError_t launch_gemv_chain(const GemvArgs *d_steps, uint32_t n_steps, int act
 template <int FMT>
 static cudaError_t optin_fmt(size_t b) {
     cudaError_t e = cudaSuccess;
-#define STRIX_ATTR(ACT_, MULTI_)                                                                                 \
-    if (e == cudaSuccess)                                                                                        \
-        e = cudaFuncSetAttribute(gemv_kernel<FMT, ACT_, MULTI_>, cudaFuncAttributeMaxDynamicSharedMemorySize, \
+#define STRIX_ATTR1(ACT_, MULTI_, PRE_)                                                                                \
+    if (e == cudaSuccess)                                                                                              \
+        e = cudaFuncSetAttribute(gemv_kernel<FMT, ACT_, MULTI_, PRE_>, cudaFuncAttributeMaxDynamicSharedMemorySize, \
                                  (int)b);
+#define STRIX_ATTR(ACT_, MULTI_)                                                                 \
+    STRIX_ATTR1(ACT_, MULTI_, STRIX_PRE_NONE) STRIX_ATTR1(ACT_, MULTI_, STRIX_PRE_RMSNORM)      \
+    STRIX_ATTR1(ACT_, MULTI_, STRIX_PRE_SWIGLU) STRIX_ATTR1(ACT_, MULTI_, STRIX_PRE_GEGLU)
     STRIX_ATTR(STRIX_ACT_F32, false) STRIX_ATTR(STRIX_ACT_Q8DOT, false)
     if constexpr (FMT != FMT_Q6_K) { STRIX_ATTR(STRIX_ACT_Q8DOT, true) }
 #undef STRIX_ATTR
+#undef STRIX_ATTR1
     return e;
 }
 
