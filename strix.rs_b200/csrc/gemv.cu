@@ -730,14 +730,22 @@ __device__ __forceinline__ void consumer_groups(const GemvArgs &A, Cta &C) {
                         float part_2[NV];
 #pragma unroll
                         for (int v = 0; v < NV; v++) part_2[v] = 0.f;
-                        for (uint32_t st = w; st < 8u; st += 2u * wc, ta += 2u * q6_step) {
+                        if (wc == 4u) {
+                            // (the large-launch geometry: exactly two sub-tiles per warp and super-block, no loop)
                             tile_mac<FMT, ACT, MULTI, false>(ta, 0u, xb_a, xr_a, TC, lane, part_sb);
-                            xb_a += xb_step;
-                            xr_a += xr_step;
-                            if (st + wc < 8u) {
-                                tile_mac<FMT, ACT, MULTI, false>(ta + q6_step, 0u, xb_a, xr_a, TC, lane, part_2);
+                            tile_mac<FMT, ACT, MULTI, false>(ta + 4u * Q6_SUB, 0u, xb_a + xb_step, xr_a + xr_step, TC, lane, part_2);
+                            xb_a += 2u * xb_step;
+                            xr_a += 2u * xr_step;
+                        } else {
+                            for (uint32_t st = w; st < 8u; st += 2u * wc, ta += 2u * q6_step) {
+                                tile_mac<FMT, ACT, MULTI, false>(ta, 0u, xb_a, xr_a, TC, lane, part_sb);
                                 xb_a += xb_step;
                                 xr_a += xr_step;
+                                if (st + wc < 8u) {
+                                    tile_mac<FMT, ACT, MULTI, false>(ta + q6_step, 0u, xb_a, xr_a, TC, lane, part_2);
+                                    xb_a += xb_step;
+                                    xr_a += xr_step;
+                                }
                             }
                         }
                         part_sb[0] += part_2[0];
