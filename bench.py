@@ -702,7 +702,7 @@ def main():
                 us = statistics.median(evs[r][i][0].elapsed_time(evs[r][i][1]) for r in range(rounds)) * 1e3
                 detail.append({"weight": it["key"], "us": round(us, 2),
                                "gbs": round(it["bytes"] * shard_frac / us / 1e3, 1)})
-        # the kernel with the largest share of the timed step is the Q6_K f32 instantiation (ncu launch
+        # the kernel with the largest share of the timed step is the Q6_K f32-activation instantiation (ncu launch
         # list, profiles/); its roofline is taken on its largest launch. DRAM traffic per launch from
         # the ncu capture of a 65536-row case, scaled by rows (traffic grows with rows).
         dom = [d for d, it in zip(detail, items) if it["ty"] == Q6_K and it["n"] == 151936][0]
@@ -710,7 +710,7 @@ def main():
         roof = {"bound": "hbm", "achieved": dom["gbs"], "peak": peak, "unit": "GB/s",
                 "frac": round(dom["gbs"] / peak, 4),
                 "traffic": int(142.07e6 * 151936 / 65536) if world == 1 else None,
-                "kernel": "gemv_kernel<Q6_K,F32> on q6_k.2560.151936, 319,683,584 algorithmic bytes per launch "
+                "kernel": "gemv_kernel<Q6_K, f32 row as int8 digits> on q6_k.2560.151936, 319,683,584 algorithmic bytes per launch "
                           "(of %s peak)" % peak_src,
                 "frac_of_8tbs": round(dom["gbs"] / 8000.0, 4),
                 "second_kernel": {"kernel": "gemv_kernel<Q8_0,F32> on q8_0.2560.151936, 413,883,904 bytes",

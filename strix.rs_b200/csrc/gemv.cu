@@ -124,6 +124,15 @@ constexpr uint32_t SMEM_PART_OFF = 1920;
 // (integer form with more than one activation row: C columns 2t and 2t + 1 are rows 2t, 2t + 1).
 __host__ __device__ constexpr int lane_values(int act, bool multi) { return (act == STRIX_ACT_Q8DOT && multi) ? 4 : 2; }
 
+// Kernel-internal third activation form (Q6_K, one f32 activation row): the row is carried as THREE
+// int8 digit rows, x = d * (q1 + q2 / 254 + q3 / 254^2) per 32-weight block (d = amax / 127, what is
+// left over is below 2^-24 of the block's largest value), and runs through the integer form as if
+// they were three activation rows; the epilogue adds the three partial results. The weight codes
+// then feed the u8 x s8 MMA as they are stored: no conversion to f16, which was a third of the f32
+// form's instructions for this format.
+constexpr int ACT_F32_DIGITS = 2;
+constexpr uint32_t N_DIGITS = 3;
+
 // Where the activation operands live in shared memory (all offsets from x_off, computed the same
 // way by gemv_plan).
 //   f32 form:      xB  uint4 [K/32][8 b]  lane 4c + t of block blk: B registers of column c (= 2j + hl:
@@ -137,6 +146,7 @@ __host__ __device__ constexpr int lane_values(int act, bool multi) { return (act
 //                      Q4_0 / Q8_0, one row:   [K/32]    { d_x, kf }
 //                      Q4_0 / Q8_0, 2..8 rows: [K/32][4] { d_x(2t), d_x(2t+1), kf(2t), kf(2t+1) }
 //                      Q6_K:                   [K/32][4] { d_x(t), kf(t, first 16), kf(t, last 16), 0 }
+//   digit form:    the integer form's Q6_K layout with three rows (the digits of the one f32 row)
 struct XLayout {
     uint32_t xb, rec, end;
     uint32_t xb_stride, rec_stride;  // bytes per 32-weight block
@@ -146,6 +156,7 @@ __host__ __device__ inline XLayout x_layout(int fmt, int act, uint32_t K, uint32
     XLayout X;
     const uint32_t nb32 = K / 32u;
     X.xb = x_off;
+    if (act == ACT_F32_DIGITS) b = N_DIGITS;
     if (act == STRIX_ACT_F32) {
         X.cols = 2u * b;
         X.xb_stride = X.cols * 4u * 16u;
@@ -515,7 +526,7 @@ __device__ __forceinline__ void consumer_prologue(const GemvArgs &A, const Cta &
         const uint32_t K4 = K / 4u, l8 = lane & 7u;
         const bool need_max = ACT == STRIX_ACT_F32;
         const bool need_red = need_max || PRE == STRIX_PRE_RMSNORM;
-        if (XL.end > XL.rec && B > 1) {
+        if (XL.end > XL.rec && (B > 1 || ACT == ACT_F32_DIGITS)) {
             // records of columns that carry no activation row stay zero (what they produce is never stored)
             uint32_t *z = reinterpret_cast<uint32_t *>(smem + XL.rec);
             for (uint32_t i = tid; i < (XL.end - XL.rec) / 4u; i += ct) z[i] = 0u;
@@ -618,6 +629,37 @@ __device__ __forceinline__ void consumer_prologue(const GemvArgs &A, const Cta &
                         uint2 *xb2 = reinterpret_cast<uint2 *>(smem + XL.xb);
                         xb2[(blk * 8u * B + (2u * bi) * 4u + t) * 2u + hf] = uh;
                         xb2[(blk * 8u * B + (2u * bi + 1u) * 4u + t) * 2u + hf] = ul;
+                    }
+                } else if (ACT == ACT_F32_DIGITS) {
+                    // three int8 digits per value, base 254: q1 = rint(x / d), r = x / d - q1 (|r| <= 1/2),
+                    // q2 = rint(254 r), q3 = rint(254 (254 r - q2)); digit j is activation row j of the
+                    // integer form's Q6_K layout, with block scale d / 254^j
+                    uint32_t *xbw = reinterpret_cast<uint32_t *>(smem + XL.xb);
+                    float *rec = reinterpret_cast<float *>(smem + XL.rec);
+                    float bm = fmaxf(fmaxf(fabsf(t4.x), fabsf(t4.y)), fmaxf(fabsf(t4.z), fabsf(t4.w)));
+                    bm = fmaxf(bm, __shfl_xor_sync(0xffffffffu, bm, 1));
+                    bm = fmaxf(bm, __shfl_xor_sync(0xffffffffu, bm, 2));
+                    bm = fmaxf(bm, __shfl_xor_sync(0xffffffffu, bm, 4));
+                    const float d = bm / 127.0f;
+                    float mul = d > 0.f ? 1.0f / d : 0.f, dj = d;
+                    float r0 = t4.x, r1 = t4.y, r2 = t4.z, r3 = t4.w;
+#pragma unroll
+                    for (uint32_t j = 0; j < N_DIGITS; j++) {
+                        const int q0 = quant1(r0, mul), q1 = quant1(r1, mul), q2 = quant1(r2, mul), q3 = quant1(r3, mul);
+                        r0 = fmaf(r0, mul, -(float)q0); r1 = fmaf(r1, mul, -(float)q1);
+                        r2 = fmaf(r2, mul, -(float)q2); r3 = fmaf(r3, mul, -(float)q3);
+                        const uint32_t wq = pack4(q0, q1, q2, q3);
+                        int cs = sum4(wq);
+                        cs += __shfl_xor_sync(0xffffffffu, cs, 1);
+                        cs += __shfl_xor_sync(0xffffffffu, cs, 2);  // over this lane's 16-weight half of the block
+                        if (live) {
+                            xbw[(blk * 8u * N_DIGITS + (2u * j + hf) * 4u + t) * 2u + hf] = wq;
+                            xbw[(blk * 8u * N_DIGITS + (2u * j + hf) * 4u + t) * 2u + (hf ^ 1u)] = 0u;
+                            if (l8 == 0) rec[blk * 16u + j * 4u] = dj;
+                            if (t == 0) rec[blk * 16u + j * 4u + 1u + hf] = -32.0f * dj * (float)cs;
+                        }
+                        mul = 254.0f;
+                        dj *= (1.0f / 254.0f);
                     }
                 } else {
                     // per-32 quantiser (xquant8, kernels.rs:864-876): d = amax/127, inv = d>0 ? 1/d : 0,
@@ -790,6 +832,16 @@ __device__ __forceinline__ void consumer_groups(const GemvArgs &A, Cta &C) {
             for (uint32_t k = 1; k < wc; k++) {
 #pragma unroll
                 for (int v = 0; v < NV; v++) acc[v] += my_part[(size_t)k * 32u * NV + v];
+            }
+        }
+        if (ACT == ACT_F32_DIGITS) {
+            // lane t of a quad holds digit t's share of rows g and g + 8: their sum is the output (lane 0 stores it)
+#pragma unroll
+            for (int v = 0; v < NV; v++) {
+                float a = t < N_DIGITS ? acc[v] : 0.f;
+                a += __shfl_xor_sync(0xffffffffu, a, 1);
+                a += __shfl_xor_sync(0xffffffffu, a, 2);
+                acc[v] = a;
             }
         }
         // lane (g, t): NV = 2 -> rows g, g + 8 of activation row t; NV = 4 -> rows g, g + 8 of rows 2t, 2t + 1
@@ -996,7 +1048,19 @@ bool gemv_plan(GemvArgs &a, int num_sms, size_t smem_optin) {
     const bool multi = a.act == STRIX_ACT_Q8DOT && a.L.fmt != FMT_Q6_K && nbt > 1;
     const uint32_t nv = (uint32_t)lane_values(a.act, multi);
     a.x_off = align128u(SMEM_PART_OFF + pool * 32u * nv * 4u);
-    const XLayout XL = x_layout(a.L.fmt, a.act, K, nbt, a.x_off);
+    // Q6_K with one f32 row: the digit form (its operands take 8 bytes of shared memory per weight
+    // column, so long rows, which would starve the rings, keep the f16 form)
+    uint32_t digit_rule = 1;
+    if (const char *e = getenv("STRIX_GEMV_DIGITS")) digit_rule = (uint32_t)atoi(e);  // 0 = never, 2 = whenever it fits
+    a.digits = (a.L.fmt == FMT_Q6_K && a.act == STRIX_ACT_F32 && nbt == 1 && digit_rule != 0 &&
+                (K <= 8192u || digit_rule == 2))
+                   ? 1u
+                   : 0u;
+    XLayout XL = x_layout(a.L.fmt, a.digits ? ACT_F32_DIGITS : a.act, K, nbt, a.x_off);
+    if (a.digits && align128u(XL.end) + 2u * align128u(a.L.tile_bytes) > budget) {
+        a.digits = 0;
+        XL = x_layout(a.L.fmt, a.act, K, nbt, a.x_off);
+    }
     const uint32_t stage_off = align128u(XL.end);
     if (stage_off + 2u * align128u(a.L.tile_bytes) > budget) return false;  // in_dim beyond what one SM can hold
     const uint32_t avail = budget - stage_off;
@@ -1099,6 +1163,9 @@ static cudaError_t launch_t(const GemvArgs &a, cudaStream_t stream) {
 
 template <int FMT>
 static cudaError_t launch_fmt(const GemvArgs &a, cudaStream_t stream) {
+    if constexpr (FMT == FMT_Q6_K) {
+        if (a.digits) return launch_t<FMT, ACT_F32_DIGITS, false>(a, stream);
+    }
     if (a.act == STRIX_ACT_F32) return launch_t<FMT, STRIX_ACT_F32, false>(a, stream);
     if constexpr (FMT != FMT_Q6_K) {
         if (a.multi) return launch_t<FMT, STRIX_ACT_Q8DOT, true>(a, stream);
@@ -1165,6 +1232,7 @@ bool gemv_chain_plan(GemvArgs *steps, uint32_t n, int num_sms, size_t smem_optin
         a.n_tiles = tile;
         a.rows_per_tile = TILE_ROWS;
         a.multi = 0;
+        a.digits = 0;
         a.pdl = 0;
         a.debug = 0;
         if (const char *e = getenv("STRIX_GEMV_DEBUG")) a.debug = (uint32_t)atoi(e) & 1u;  // 1 = no arithmetic
@@ -1200,6 +1268,7 @@ static cudaError_t optin_fmt(size_t b) {
     STRIX_ATTR1(ACT_, MULTI_, STRIX_PRE_SWIGLU) STRIX_ATTR1(ACT_, MULTI_, STRIX_PRE_GEGLU)
     STRIX_ATTR(STRIX_ACT_F32, false) STRIX_ATTR(STRIX_ACT_Q8DOT, false)
     if constexpr (FMT != FMT_Q6_K) { STRIX_ATTR(STRIX_ACT_Q8DOT, true) }
+    if constexpr (FMT == FMT_Q6_K) { STRIX_ATTR(ACT_F32_DIGITS, false) }
 #undef STRIX_ATTR
 #undef STRIX_ATTR1
     return e;

@@ -58,6 +58,7 @@ struct GemvArgs {
     uint32_t chunk_tiles;    // GGUF blocks of K per stage
     uint32_t n_chunks;       // stages per row group
     uint32_t multi;          // integer form with more than one activation row (Q4_0 / Q8_0)
+    uint32_t digits;         // f32 activations carried as three int8 digits per value (Q6_K, one activation row)
     uint32_t pdl;            // launch with programmatic stream serialization
     uint32_t rot;            // chain kernel: CTA that takes the step's first row group
     // Row-sharded multi-GPU form with the exchange folded in (null sync_epoch = off): the consumers wait

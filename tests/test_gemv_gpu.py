@@ -126,6 +126,27 @@ def test_gemv_f32_and_q8dot_match_oracle(accel, orc, synth, pkg, ty, out_dim, in
     assert accel.device_status() == 0
 
 
+@pytest.mark.parametrize("rule", ["0", "2"])
+@pytest.mark.parametrize("out_dim,in_dim", [(300, 256), (1030, 2560), (64, 9728)])
+def test_q6k_f32_forms_agree(accel, orc, synth, monkeypatch, rule, out_dim, in_dim):
+    """Q6_K with one f32 row runs either on f16 tensor-core tiles (activation split hi + lo) or on int8
+    tiles (activation as three base-254 digits). STRIX_GEMV_DIGITS picks: 0 = never the digit form,
+    2 = whenever it fits. Both must sit at f32 rounding level from the f64 product of the dequantised
+    weight, far inside the contract's tolerance."""
+    monkeypatch.setenv("STRIX_GEMV_DIGITS", rule)
+    w = synth.quant(14, 41, "dg", out_dim, in_dim)
+    assert accel.upload_q6_k("dg", w, in_dim, out_dim)
+    W = accel.dequant_to_f32("dg").reshape(out_dim, in_dim).astype(np.float64)
+    for seed, scale in ((1, 1.0), (2, 1e-4), (3, 3e3)):
+        x = (synth.normal(seed, "dg.x", in_dim) * scale).astype(np.float32)
+        x[::7] = 0.0                      # zeros inside blocks
+        x[32:64] = 0.0                    # an all-zero block
+        got = accel.gemv("dg", x)
+        assert rel_l2(got, W @ x.astype(np.float64)) <= 2e-6
+        assert rel_l2(got, orc.qmatmul(x, w, 14, in_dim, out_dim)) <= REL_L2_TOL
+    assert accel.device_status() == 0
+
+
 def test_lm_head_shapes(accel, orc, synth):
     # the 2560 -> 151936 lm_head of the benchmark, Q8_0 and Q6_K; every row must be written
     # (the reference once left half the rows unwritten through a grid-size slip, README.md:125-128)
