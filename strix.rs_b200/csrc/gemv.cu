@@ -145,7 +145,8 @@ constexpr uint32_t N_DIGITS = 3;
 //                  the stored weight codes carry):
 //                      Q4_0 / Q8_0, one row:   [K/32]    { d_x, kf }
 //                      Q4_0 / Q8_0, 2..8 rows: [K/32][4] { d_x(2t), d_x(2t+1), kf(2t), kf(2t+1) }
-//                      Q6_K:                   [K/32][4] { d_x(t), kf(t, first 16), kf(t, last 16), 0 }
+//                      Q6_K:                   [K/32][4] { d_x(t), -32 * sum(codes of row t, first 16) as an int,
+//                                                          the same for the last 16, 0 }
 //   digit form:    the integer form's Q6_K layout with three rows (the digits of the one f32 row)
 struct XLayout {
     uint32_t xb, rec, end;
@@ -183,6 +184,14 @@ __device__ __forceinline__ float2 h2_to_f2(uint32_t w) {
 template <int I>
 __device__ __forceinline__ float biased_byte_to_float(uint32_t w) {
     return __uint_as_float(__byte_perm(w, 0x4B000000u, 0x7540u | I)) - 8388736.0f;
+}
+// byte I of w as a sign-extended int: one byte permute (a selector nibble with its top bit set copies
+// the sign of the byte it names)
+template <int I>
+__device__ __forceinline__ int sext_byte(uint32_t w) {
+    int d;
+    asm("prmt.b32 %0, %1, %1, %2;" : "=r"(d) : "r"(w), "n"(0x8880 + 0x1111 * I));
+    return d;
 }
 // (a & b) | c in one instruction, all three from registers
 __device__ __forceinline__ uint32_t and_or(uint32_t a, uint32_t b, uint32_t c) {
@@ -281,18 +290,10 @@ __device__ __forceinline__ void tile_mac(uint32_t ta, uint32_t da, uint32_t xb_a
         W3 = ((lo.y >> 4) & M4) | ((H >> 2) & M30);
         d = Q6D ? h2_to_f2(lds32(da + 4u * g)) : make_float2(1.f, 1.f);
     }
-    // Q6_K: (d * sub-scale) for the two 16-weight halves of rows g and g + 8
-    float s_lo0 = 0.f, s_lo1 = 0.f, s_hi0 = 0.f, s_hi1 = 0.f;
-    if (FMT == FMT_Q6_K) {
-        const uint32_t sc = lds32(ta + 384u + 4u * g);  // {row g: first, last 16; row g + 8: first, last 16}, each + 128
-        s_lo0 = biased_byte_to_float<0>(sc);
-        s_lo1 = biased_byte_to_float<1>(sc);
-        s_hi0 = biased_byte_to_float<2>(sc);
-        s_hi1 = biased_byte_to_float<3>(sc);
-        if (Q6D) {
-            s_lo0 *= d.x; s_lo1 *= d.x; s_hi0 *= d.y; s_hi1 *= d.y;
-        }
-    }
+    // Q6_K: the int8 sub-scales of the two 16-weight halves of rows g and g + 8, stored + 128:
+    // {row g: first, last 16; row g + 8: first, last 16}
+    uint32_t sc = 0u;
+    if (FMT == FMT_Q6_K) sc = lds32(ta + 384u + 4u * g);
 
     if (ACT == STRIX_ACT_F32) {
         const uint4 xb = lds128(xb_a);
@@ -317,6 +318,12 @@ __device__ __forceinline__ void tile_mac(uint32_t ta, uint32_t da, uint32_t xb_a
             acc[0] = fmaf(d.x, c0[0] + c0[1], acc[0]);
             acc[1] = fmaf(d.y, c0[2] + c0[3], acc[1]);
         } else {
+            // (d * sub-scale) per half and row
+            float s_lo0 = biased_byte_to_float<0>(sc), s_lo1 = biased_byte_to_float<1>(sc);
+            float s_hi0 = biased_byte_to_float<2>(sc), s_hi1 = biased_byte_to_float<3>(sc);
+            if (Q6D) {
+                s_lo0 *= d.x; s_lo1 *= d.x; s_hi0 *= d.y; s_hi1 *= d.y;
+            }
             float c1[4];
             mma_f16_z(c0, hsub2_bits(bytes_to_h2<0>(W0), C.bias_a), hsub2_bits(bytes_to_h2<0>(W1), C.bias_a),
                       hsub2_bits(bytes_to_h2<2>(W0), C.bias_a), hsub2_bits(bytes_to_h2<2>(W1), C.bias_a), xb.x, xb.y);
@@ -337,21 +344,28 @@ __device__ __forceinline__ void tile_mac(uint32_t ta, uint32_t da, uint32_t xb_a
         }
         const uint2 xq = lds64(xb_a);
         int c[4];
+        if (FMT == FMT_Q6_K) {
+            // columns (2j, 2j + 1) = activation row j against the first / last 16 weights of the tile.
+            // All in integers up to the block scale: the record's -32 * sum(x codes) of each half goes in
+            // as the accumulator (it removes the +32 the stored weight codes carry), and the two halves
+            // meet their int8 sub-scales in integer multiply-adds (|result| < 2^26):
+            // y += (d_w * d_x) * (sc_first * (isum_first - 32 sum_first) + sc_last * (isum_last - 32 sum_last))
+            const uint4 r = lds128(xr_a);
+            const int cin[4] = {(int)r.y, (int)r.z, (int)r.y, (int)r.z};
+            mma_u8s8_c(c, W0, W1, W2, W3, xq.x, xq.y, cin);
+            const uint32_t ss = sc ^ 0x80808080u;  // signed bytes; the selectors below sign-extend one byte each
+            const int s0 = sext_byte<0>(ss), s1 = sext_byte<1>(ss), s2 = sext_byte<2>(ss), s3 = sext_byte<3>(ss);
+            const float dx = __uint_as_float(r.x);
+            acc[0] = fmaf(Q6D ? dx * d.x : dx, (float)(s0 * c[0] + s1 * c[1]), acc[0]);
+            acc[1] = fmaf(Q6D ? dx * d.y : dx, (float)(s2 * c[2] + s3 * c[3]), acc[1]);
+            return;
+        }
         mma_u8s8_c(c, W0, W1, W2, W3, xq.x, xq.y, C.magic);
         // the integer sums arrive inside the mantissa of 1.5 * 2^23: one subtraction makes them floats.
         // y += d_w * (d_x * (float)isum + kf)  =  (d_w * d_x) * (float)(isum - bias * sum(codes)), the block
         // term of q8i_gemv / q4_gemv_dp (kernels.rs:894-912, 259-287)
         const float f0 = __int_as_float(c[0]) - 12582912.0f, f2 = __int_as_float(c[2]) - 12582912.0f;
-        if (FMT == FMT_Q6_K) {
-            // columns (2j, 2j + 1) = activation row j against the first / last 16 weights of the tile
-            const uint4 r = lds128(xr_a);
-            const float f1 = __int_as_float(c[1]) - 12582912.0f, f3 = __int_as_float(c[3]) - 12582912.0f;
-            const float dx = __uint_as_float(r.x), k0 = __uint_as_float(r.y), k1 = __uint_as_float(r.z);
-            acc[0] = fmaf(s_lo0, fmaf(dx, f0, k0), acc[0]);
-            acc[0] = fmaf(s_lo1, fmaf(dx, f1, k1), acc[0]);
-            acc[1] = fmaf(s_hi0, fmaf(dx, f2, k0), acc[1]);
-            acc[1] = fmaf(s_hi1, fmaf(dx, f3, k1), acc[1]);
-        } else if constexpr (MULTI) {
+        if constexpr (MULTI) {
             const uint4 r = lds128(xr_a);
             const float f1 = __int_as_float(c[1]) - 12582912.0f, f3 = __int_as_float(c[3]) - 12582912.0f;
             const float dx0 = __uint_as_float(r.x), dx1 = __uint_as_float(r.y);
@@ -656,7 +670,7 @@ __device__ __forceinline__ void consumer_prologue(const GemvArgs &A, const Cta &
                             xbw[(blk * 8u * N_DIGITS + (2u * j + hf) * 4u + t) * 2u + hf] = wq;
                             xbw[(blk * 8u * N_DIGITS + (2u * j + hf) * 4u + t) * 2u + (hf ^ 1u)] = 0u;
                             if (l8 == 0) rec[blk * 16u + j * 4u] = dj;
-                            if (t == 0) rec[blk * 16u + j * 4u + 1u + hf] = -32.0f * dj * (float)cs;
+                            if (t == 0) rec[blk * 16u + j * 4u + 1u + hf] = __int_as_float(-32 * cs);
                         }
                         mul = 254.0f;
                         dj *= (1.0f / 254.0f);
@@ -686,7 +700,7 @@ __device__ __forceinline__ void consumer_prologue(const GemvArgs &A, const Cta &
                             xbw[(blk * 8u * B + (2u * bi + hf) * 4u + t) * 2u + hf] = wq;
                             xbw[(blk * 8u * B + (2u * bi + hf) * 4u + t) * 2u + (hf ^ 1u)] = 0u;
                             if (l8 == 0) rec[blk * 16u + bi * 4u] = d;
-                            if (t == 0) rec[blk * 16u + bi * 4u + 1u + hf] = -(float)BIAS * d * (float)half_sum;
+                            if (t == 0) rec[blk * 16u + bi * 4u + 1u + hf] = __int_as_float(-BIAS * half_sum);
                         } else {
                             xbw[(blk * 4u * B + bi * 4u + t) * 2u + hf] = wq;
                             if (l8 == 0) {
@@ -734,7 +748,10 @@ __device__ __forceinline__ void consumer_groups(const GemvArgs &A, Cta &C) {
     // this lane's B-operand and record addresses for block 0 (see x_layout). Lanes whose MMA column
     // carries no activation row re-read a column that does: what they produce is never stored.
     const uint32_t xs0 = smem_u32(smem);
-    const uint32_t lane_eff = lane % (XL.cols * 4u);
+    // (a duplicate stays inside its own half of the warp, whose 16 lanes then touch one 128-byte run: a
+    // duplicate of the other half's address would land on the same banks as this half's own lanes)
+    const uint32_t n_op = XL.cols * 4u;
+    const uint32_t lane_eff = (n_op > 16u && lane >= 16u) ? 16u + (lane - 16u) % (n_op - 16u) : lane % n_op;
     const uint32_t xb_l = xs0 + XL.xb + lane_eff * (ACT == STRIX_ACT_F32 ? 16u : 8u);
     const uint32_t xr_l = xs0 + XL.rec + ((FMT == FMT_Q6_K || MULTI) ? 16u * t : 0u);
     const TileConsts TC = tile_consts<FMT, ACT>();
