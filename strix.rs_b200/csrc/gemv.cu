@@ -1099,6 +1099,10 @@ bool gemv_plan(GemvArgs &a, int num_sms, size_t smem_optin) {
     if (const char *e = getenv("STRIX_GEMV_WC")) force_wc = (uint32_t)atoi(e);  // tuning knobs
     if (const char *e = getenv("STRIX_GEMV_CT")) force_ct = (uint32_t)atoi(e);
     if (const char *e = getenv("STRIX_GEMV_STAGES")) force_sk = (uint32_t)atoi(e);
+    // Q6_K launches with at least two row groups for every warp of the grid: one warp per group (a warp
+    // then owns whole super-blocks and nothing is exchanged between warps) measured 66.0 us against 70.1
+    // for four warps per group on 151936 x 2560 inside the benchmark step; Q8_0 loses by it (84 against 68).
+    const bool q6k_many = a.L.fmt == FMT_Q6_K && groups >= (uint64_t)num_sms * pool * 2u && !force_wc;
     uint32_t best_wc = 0, best_ct = 0, best_sk = 0;
     double best_cost = 1e300;
     for (uint32_t wc : wcs) {
@@ -1128,6 +1132,7 @@ bool gemv_plan(GemvArgs &a, int num_sms, size_t smem_optin) {
         const double cost = (double)rounds * (tiles + 0.5 * chunks + (wc > 1 ? 4.0 : 1.5)) * (sk >= 3u ? 1.0 : 1.3) *
                             (1.0 + 1500.0 / sb);
         if (cost < best_cost) { best_cost = cost; best_wc = wc; best_ct = ct; best_sk = sk; }
+        if (q6k_many && wc == 1u) break;  // feasible: taken
     }
     if (best_wc == 0) return false;
     a.wc = best_wc;
