@@ -175,6 +175,13 @@ def decode_chain_extra(pkg, synth, torch, device, stream):
                 logits = acc.decode_step(h0, i)
             e2e_ms = (time.perf_counter() - t0) / reps * 1e3
             assert np.isfinite(logits).all()
+            # greedy form: the argmax on the device, 4 bytes back instead of the logits
+            tok = acc.decode_step_argmax(h0, 0)
+            assert tok == int(np.argmax(logits))
+            t0 = time.perf_counter()
+            for i in range(reps):
+                tok = acc.decode_step_argmax(h0, i)
+            e2e_argmax_ms = (time.perf_counter() - t0) / reps * 1e3
             d_h = torch.from_numpy(h0).to(dev)
             d_h0 = d_h.clone()
             d_l = torch.empty(vocab, device=dev)
@@ -197,6 +204,7 @@ def decode_chain_extra(pkg, synth, torch, device, stream):
                 torch.cuda.synchronize()
                 dev_ms = a.elapsed_time(b) / reps
             out[name] = {"ms_per_token": round(dev_ms, 4), "ms_per_token_e2e": round(e2e_ms, 4),
+                         "ms_per_token_e2e_argmax": round(e2e_argmax_ms, 4),
                          "gbs": round(nbytes / dev_ms / 1e6, 1), "launches_per_token": 4 * n_layers + 1}
         out["bytes_per_token"] = nbytes
         out["note"] = "projection chain only; attention replaced by feeding Wo with q (no KV cache)"

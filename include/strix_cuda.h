@@ -223,6 +223,23 @@ STRIX_API int strix_cuda_configure_decode(strix_cuda *h, const strix_gpu_decode_
  * from the embedded hidden state hvec[hidden]; four GEMV launches per layer replayed from a CUDA
  * graph. `pos` is accepted for signature parity (no KV cache on this path). 0 = not configured. */
 STRIX_API int strix_cuda_decode_step(strix_cuda *h, const float *hvec, size_t pos, float *logits, size_t logits_cap);
+/* WeightAccel::decode_step_argmax (accel.rs:437-442; decode.rs:5497-5515, 5533-5538): the same step,
+ * then the argmax over the logits on the device; only the winning token id crosses back (4 bytes
+ * instead of vocab * 4). Ties resolve to the lowest index, NaN never wins, as in the reference's
+ * argmax_f32 (kernels.rs:2088-2110). 0 = not configured, or a row-sharded handle. */
+STRIX_API int strix_cuda_decode_step_argmax(strix_cuda *h, const float *hvec, size_t pos, uint32_t *id);
+/* WeightAccel::lm_head_argmax_rows (accel.rs:216-219; decode.rs:3631-3689): ids[t] = argmax over the
+ * rows of W xs[t], t < m, with one pass over the weights per chunk of activation rows and the argmax
+ * on the device. xs_len must be m * in_dim and m <= 16, else 0 (None), as in the reference; unlike
+ * the reference any resident format is accepted (`act` picks the f32 or the integer-dot GEMV).
+ * ids are row indices of the whole weight; a row-sharded handle returns the winner among ITS rows, and
+ * vals (may be null) receives the winning values so that the caller can fold the shards. */
+STRIX_API int strix_cuda_lm_head_argmax_rows(strix_cuda *h, const char *key, const float *xs, size_t xs_len, size_t m,
+                                             int act, uint32_t *ids, float *vals);
+/* argmax per row of a device matrix d_x[rows][stride] (n entries per row, rows <= 16) on `stream`;
+ * d_ids[rows] / d_vals[rows] (either may be null) are device pointers. No sync. */
+STRIX_API int strix_cuda_argmax_dev(strix_cuda *h, const float *d_x, size_t n, size_t stride, size_t rows,
+                                    uint32_t *d_ids, float *d_vals, void *stream);
 /* The same chain on device pointers (d_h is updated in place), enqueued on `stream`; no copy, no sync. */
 STRIX_API int strix_cuda_decode_chain_dev(strix_cuda *h, float *d_h, float *d_logits, void *stream);
 

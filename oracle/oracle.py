@@ -163,3 +163,16 @@ def idot_gemm(data, ty, xq, xd, m, in_dim, out_dim, want_isums=False, threads=No
     if rc != 0:
         raise ValueError("bad shape or type")
     return (y, isums) if want_isums else y
+
+
+def argmax_f32(x):
+    """Greedy argmax with the reference kernel's semantics (crates/strix-backend-rocm/src/kernels.rs:2088-2110):
+    the running best starts at (-3.0e38, index 0) and is replaced only by a GREATER value, so NaN never
+    wins and a row with nothing above -3.0e38 gives 0; ties resolve to the lowest index. Pure numpy."""
+    x = _f32(x).reshape(-1)
+    with np.errstate(invalid="ignore"):
+        ok = x > np.float32(-3.0e38)          # False for NaN
+    if not ok.any():
+        return 0
+    masked = np.where(ok, x, -np.inf)
+    return int(np.argmax(masked))             # numpy returns the first (lowest) index of the maximum

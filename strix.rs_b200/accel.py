@@ -101,6 +101,9 @@ def load_library():
     sig("strix_cuda_configure_decode", C.c_int, H, C.POINTER(_DecodeCfg))
     sig("strix_cuda_decode_step", C.c_int, H, f32p, sz, f32p, sz)
     sig("strix_cuda_decode_chain_dev", C.c_int, H, C.c_void_p, C.c_void_p, C.c_void_p)
+    sig("strix_cuda_decode_step_argmax", C.c_int, H, f32p, sz, C.POINTER(C.c_uint32))
+    sig("strix_cuda_lm_head_argmax_rows", C.c_int, H, C.c_char_p, f32p, sz, sz, C.c_int, C.POINTER(C.c_uint32), f32p)
+    sig("strix_cuda_argmax_dev", C.c_int, H, C.c_void_p, sz, sz, sz, C.c_void_p, C.c_void_p, C.c_void_p)
     sig("strix_cuda_gemv_rows", C.c_int, H, C.c_char_p, f32p, sz, f32p, sz, C.c_int)
     sig("strix_cuda_gemv_rows_dev", C.c_int, H, C.c_int, C.POINTER(C.c_char_p), C.c_void_p, sz, C.c_int,
         C.POINTER(C.c_void_p), C.c_void_p)
@@ -307,6 +310,32 @@ class CudaWeightAccel:
         out = np.empty(self._vocab, dtype=np.float32)
         rc = self._check(self._L.strix_cuda_decode_step(self._h, _fp(ha), pos, _fp(out), out.size))
         return out if rc == 1 else None
+
+    def decode_step_argmax(self, h, pos=0):
+        """Greedy token id of one decode step, argmax on the device, or None (accel.rs:437-442)."""
+        if not getattr(self, "_vocab", None):
+            return None
+        ha = _f32(h)
+        out = C.c_uint32(0)
+        rc = self._check(self._L.strix_cuda_decode_step_argmax(self._h, _fp(ha), pos, C.byref(out)))
+        return int(out.value) if rc == 1 else None
+
+    def lm_head_argmax_rows(self, key, xs, m, act=ACT_F32, with_values=False):
+        """ids[m] = argmax over the rows of W xs[t], or None (unknown key, bad length, m > 16) (accel.rs:216-219)."""
+        xa = _f32(xs)
+        ids = np.zeros(max(m, 1), dtype=np.uint32)
+        vals = np.zeros(max(m, 1), dtype=np.float32)
+        rc = self._check(self._L.strix_cuda_lm_head_argmax_rows(
+            self._h, key.encode(), _fp(xa), xa.size, m, act, ids.ctypes.data_as(C.POINTER(C.c_uint32)), _fp(vals)))
+        if rc != 1:
+            return None
+        return (ids[:m], vals[:m]) if with_values else ids[:m]
+
+    def argmax_dev(self, d_x, n, stride, rows, d_ids=0, d_vals=0, stream=0):
+        rc = self._check(self._L.strix_cuda_argmax_dev(
+            self._h, C.c_void_p(int(d_x)), n, stride, rows, C.c_void_p(int(d_ids)) if d_ids else None,
+            C.c_void_p(int(d_vals)) if d_vals else None, C.c_void_p(int(stream)) if stream else None))
+        return rc == 1
 
     def decode_chain_dev(self, d_h, d_logits, stream=0):
         rc = self._check(self._L.strix_cuda_decode_chain_dev(self._h, C.c_void_p(int(d_h)), C.c_void_p(int(d_logits)),

@@ -290,6 +290,8 @@ void strix_cuda_destroy(strix_cuda *h) {
     for (float *p : {h->gm_x.p, h->gm_y.p, h->gm_part.p, h->gm_xd.p})
         if (p) cudaFree(p);
     if (h->gm_xq) cudaFree(h->gm_xq);
+    if (h->am_part) cudaFree(h->am_part);  // one allocation: winners, tickets, ids, values
+    if (h->am_pin) cudaFreeHost(h->am_pin);
     if (h->gm_xs) cudaFree(h->gm_xs);
     for (auto &kv : h->f32s) cudaFree(kv.second.p);
     if (h->x.p) cudaFree(h->x.p);

@@ -60,6 +60,11 @@ struct strix_cuda {
     // block code sums, f32 output, split-K partials
     strix::DevBuf gm_x, gm_y, gm_part, gm_xd;
     strix_decode_state *decode = nullptr;  // configured projection chain (decode.cu), or null
+    // argmax scratch (argmax.cu), allocated on first use: per-block winners, per-row tickets, results
+    void *am_part = nullptr;
+    uint32_t *am_ticket = nullptr, *am_idx = nullptr;
+    float *am_val = nullptr;
+    uint32_t *am_pin = nullptr;  // pinned: ids (16) then the status word
     int8_t *gm_xq = nullptr;
     size_t gm_xq_cap = 0;
     int32_t *gm_xs = nullptr;
@@ -71,6 +76,8 @@ size_t shard_begin(size_t rows, int world, int r);
 int ensure_f32(strix_cuda *h, DevBuf &b, size_t n);
 int ensure_pinned(strix_cuda *h, PinBuf &b, size_t bytes);
 const Resident *find_weight(strix_cuda *h, const char *key);
+// argmax per row of d_x[rows][stride] (n entries each, rows <= 16) into h->am_idx (and h->am_val) on `stream`
+int argmax_rows_enqueue(strix_cuda *h, const float *d_x, size_t n, size_t stride, size_t rows, cudaStream_t stream);
 Resident *find_weight_mut(strix_cuda *h, const char *key);
 // One GEMV launch over up to 3 resident weights that share the activation; d_res (may be null)
 // gives per-weight residual vectors added to the outputs.

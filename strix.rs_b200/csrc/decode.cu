@@ -306,16 +306,9 @@ int strix_cuda_decode_chain_dev(strix_cuda *h, float *d_h, float *d_logits, void
     return rc;
 }
 
-int strix_cuda_decode_step(strix_cuda *h, const float *hvec, size_t pos, float *logits, size_t logits_cap) {
-    (void)pos;  // no KV cache on this path: the attention stand-in does not depend on the position
-    if (!h || !hvec || !logits) return -1;
-    h->err.clear();
-    strix_decode_state *d = h->decode;
-    if (!d) return 0;  // not configured: None, the model falls back to per-weight gemv
-    if (logits_cap < d->cfg.vocab) {
-        h->err = "decode_step: logits buffer too small";
-        return -1;
-    }
+// H2D of the hidden state and one replay of the captured chain on the handle's stream (captured on
+// the first call); the logits are then in d->logits.
+static int decode_enqueue_step(strix_cuda *h, strix_decode_state *d, const float *hvec) {
     CU_TRY(h, cudaSetDevice(h->device));
     if (!d->exec) {
         cudaGraph_t g = nullptr;
@@ -339,15 +332,54 @@ int strix_cuda_decode_step(strix_cuda *h, const float *hvec, size_t pos, float *
     memcpy(d->pin_h, hvec, d->cfg.hidden * sizeof(float));
     CU_TRY(h, cudaMemcpyAsync(d->h, d->pin_h, d->cfg.hidden * sizeof(float), cudaMemcpyHostToDevice, h->stream));
     CU_TRY(h, cudaGraphLaunch(d->exec, h->stream));
-    CU_TRY(h, cudaMemcpyAsync(d->pin_logits, d->logits, (size_t)d->cfg.vocab * sizeof(float), cudaMemcpyDeviceToHost, h->stream));
+    return 1;
+}
+
+static int decode_finish(strix_cuda *h, const char *who) {
     CU_TRY(h, cudaMemcpyAsync(&h->status_host, h->d_status, 4, cudaMemcpyDeviceToHost, h->stream));
     CU_TRY(h, cudaStreamSynchronize(h->stream));
     if (h->status_host != 0) {
-        h->err = "decode_step: device status " + std::to_string(h->status_host) + " (a bounded wait ran out)";
+        h->err = std::string(who) + ": device status " + std::to_string(h->status_host) + " (a bounded wait ran out)";
         cudaMemsetAsync(h->d_status, 0, 4, h->stream);
         return -2;
     }
+    return 1;
+}
+
+int strix_cuda_decode_step(strix_cuda *h, const float *hvec, size_t pos, float *logits, size_t logits_cap) {
+    (void)pos;  // no KV cache on this path: the attention stand-in does not depend on the position
+    if (!h || !hvec || !logits) return -1;
+    h->err.clear();
+    strix_decode_state *d = h->decode;
+    if (!d) return 0;  // not configured: None, the model falls back to per-weight gemv
+    if (logits_cap < d->cfg.vocab) {
+        h->err = "decode_step: logits buffer too small";
+        return -1;
+    }
+    int rc = decode_enqueue_step(h, d, hvec);
+    if (rc < 0) return rc;
+    CU_TRY(h, cudaMemcpyAsync(d->pin_logits, d->logits, (size_t)d->cfg.vocab * sizeof(float), cudaMemcpyDeviceToHost, h->stream));
+    if ((rc = decode_finish(h, "decode_step")) < 0) return rc;
     memcpy(logits, d->pin_logits, (size_t)d->cfg.vocab * sizeof(float));
+    return 1;
+}
+
+// Greedy decode of one token: the chain, then the argmax on the device; 4 bytes come back instead of
+// the vocabulary-wide logits (decode.rs:5497-5515, 5533-5538). Ties resolve to the lowest index.
+// A row-sharded accelerator (world > 1) holds only its own logits and declines (0): the caller folds
+// the shards' winners itself.
+int strix_cuda_decode_step_argmax(strix_cuda *h, const float *hvec, size_t pos, uint32_t *id) {
+    (void)pos;
+    if (!h || !hvec || !id) return -1;
+    h->err.clear();
+    strix_decode_state *d = h->decode;
+    if (!d || h->world > 1) return 0;
+    int rc = decode_enqueue_step(h, d, hvec);
+    if (rc < 0) return rc;
+    if (argmax_rows_enqueue(h, d->logits, d->cfg.vocab, d->cfg.vocab, 1, h->stream) < 0) return -1;
+    CU_TRY(h, cudaMemcpyAsync(h->am_pin, h->am_idx, 4, cudaMemcpyDeviceToHost, h->stream));
+    if ((rc = decode_finish(h, "decode_step_argmax")) < 0) return rc;
+    *id = h->am_pin[0];
     return 1;
 }
 

@@ -230,3 +230,23 @@ def test_idot_close_to_f32_path(orc, synth):
         xdeq = (xq.astype(np.float64).reshape(-1, 32) * xd.astype(np.float64)[:, None]).reshape(-1)
         ref = deq @ xdeq
         assert np.linalg.norm(yi - ref) / np.linalg.norm(ref) < 1e-5
+
+
+def test_argmax_follows_the_reference_kernel(orc):
+    # kernels.rs:2088-2110: start at (-3.0e38, 0), replace on GREATER only, lowest index on ties.
+    # A scalar replay of that loop (one thread, ascending) is the known answer.
+    def replay(x):
+        bv, bi = np.float32(-3.0e38), 0
+        for i, v in enumerate(x):
+            if v > bv:
+                bv, bi = v, i
+        return bi
+
+    rng = np.random.default_rng(5)
+    cases = [np.array([1.0, 3.0, 3.0, 2.0], np.float32), np.array([np.nan, 2.0, np.nan, 2.0], np.float32),
+             np.full(7, -np.inf, np.float32), np.array([-3.0e38, -3.0e38], np.float32),
+             np.array([np.nan], np.float32), np.array([np.inf, np.inf, 1.0], np.float32)]
+    cases += [rng.integers(-3, 4, 50).astype(np.float32) for _ in range(20)]
+    for x in cases:
+        with np.errstate(invalid="ignore"):
+            assert orc.argmax_f32(x) == replay(x), x
