@@ -62,6 +62,7 @@ def test_model_file_to_decode_step(pkg, orc, synth, tmp_path):
         assert acc.decode_step_argmax(h0, 0) == orc.argmax_f32(got)
         # bit-exact weight tier through the file: dequantised resident bytes == oracle dequant of the file's bytes
         w, ty, k, n = W["output.weight"]
-        np.testing.assert_array_equal(acc.dequant_to_f32("output.weight"), orc.dequantize(ty, w, n * k))
+        np.testing.assert_array_equal(acc.dequant_to_f32("output.weight").reshape(-1).view(np.uint32),
+                                      orc.dequantize(ty, w, n * k).reshape(-1).view(np.uint32))
     finally:
         acc.close()
