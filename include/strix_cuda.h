@@ -92,7 +92,8 @@ STRIX_API int strix_cuda_upload_q8_0(strix_cuda *h, const char *key, const uint8
                            size_t in_dim, size_t out_dim);
 STRIX_API int strix_cuda_upload_q6_k(strix_cuda *h, const char *key, const uint8_t *bytes, size_t len,
                            size_t in_dim, size_t out_dim);
-/* WeightAccel::upload_q4_1 (accel.rs:154): declined (returns 0), the trait's default. */
+/* WeightAccel::upload_q4_1 (accel.rs:154; decode.rs:2588-2627): 20-byte blocks [d f16][m f16][16 code bytes],
+ * value = d * code + m; llama.cpp keeps early-layer ffn_down in this format. Same guards as upload_q4_0. */
 STRIX_API int strix_cuda_upload_q4_1(strix_cuda *h, const char *key, const uint8_t *bytes, size_t len,
                            size_t in_dim, size_t out_dim);
 /* WeightAccel::upload_f32 (accel.rs:413; decode.rs:3908-3912): norm weights. */

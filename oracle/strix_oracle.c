@@ -371,6 +371,28 @@ static void idot_row(size_t o, void *c, float *scratch) {
                 float term = sc * (float)s;
                 acc = acc + term;
             }
+        } else if (k->ty == SO_Q4_1) {
+            /* q4_1_gemv_dp (kernels.rs:289-320): value = d * code + m, codes 0..15 not centred; per block
+             * acc += xd[b] * (dw * (float)isum + mw * (float)xsum[b]) */
+            size_t nb = k->in_dim / 32;
+            const float *xd = k->xd + t * nb;
+            for (size_t b = 0; b < nb; b++) {
+                const uint8_t *blk = row + b * 20;
+                const int8_t *a = xq + b * 32;
+                int32_t s = 0, xs = 0;
+                for (int j = 0; j < 16; j++) {
+                    s += (int32_t)(blk[4 + j] & 0x0F) * (int32_t)a[j];
+                    s += (int32_t)(blk[4 + j] >> 4) * (int32_t)a[j + 16];
+                }
+                for (int i = 0; i < 32; i++) xs += a[i];
+                if (k->isums) k->isums[(t * k->out_dim + o) * nb + b] = s;
+                float dw = so_f16_to_f32(rd16(blk)), mw = so_f16_to_f32(rd16(blk + 2));
+                float inner = dw * (float)s;
+                float mterm = mw * (float)xs;
+                inner = inner + mterm;
+                float term = xd[b] * inner;
+                acc = acc + term;
+            }
         } else { /* SO_Q6_K: no reference kernel; per 16-element sub-scale group */
             size_t nsb = k->in_dim / 256;
             const float *xd = k->xd + t * (k->in_dim / 32);
@@ -410,7 +432,7 @@ static void idot_row(size_t o, void *c, float *scratch) {
  * Integer-dot GEMV / W8A8 GEMM over m quantised activation rows:
  *   y[t][o] = sum_kb (d_w[o,kb] * d_x[t,kb]) * (float)isum[t,o,kb], summed in
  * f32 in block order. Q8_0 restates q8i_gemv (kernels.rs:894-912) and
- * q8w_gemm32 (:1417-1428); Q4_0 restates q4_gemv_dp (:259-287). Q6_K has no
+ * q8w_gemm32 (:1417-1428); Q4_0 restates q4_gemv_dp (:259-287), Q4_1 q4_1_gemv_dp (:289-320). Q6_K has no
  * integer-dot kernel in the reference: it is defined here per 16-element
  * sub-scale group with weight (d*sc)*d_x. The contract fixes the int32 block
  * sums exactly and y within rel-L2 1e-3; the reference's own lane/shuffle
@@ -420,7 +442,7 @@ static void idot_row(size_t o, void *c, float *scratch) {
 int so_idot_gemm(float *y, const uint8_t *bytes, int ty, const int8_t *xq, const float *xd,
                  size_t m, size_t in_dim, size_t out_dim, int32_t *isums, int nthreads) {
     int be = so_block_elems(ty);
-    if (be == 0 || ty == SO_Q4_1 || in_dim % (size_t)be != 0) return -1;
+    if (be == 0 || in_dim % (size_t)be != 0) return -1;
     id_ctx c = {y, bytes, xq, xd, ty, in_dim, out_dim, m,
                 (in_dim / (size_t)be) * (size_t)so_block_bytes(ty), isums};
     par_rows(out_dim, nthreads, 0, idot_row, &c);

@@ -320,7 +320,9 @@ int strix_cuda_upload_q6_k(strix_cuda *h, const char *key, const uint8_t *bytes,
                            size_t out_dim) {
     return upload_quant(h, FMT_Q6_K, key, bytes, len, in_dim, out_dim);
 }
-int strix_cuda_upload_q4_1(strix_cuda *, const char *, const uint8_t *, size_t, size_t, size_t) { return 0; }
+int strix_cuda_upload_q4_1(strix_cuda *h, const char *key, const uint8_t *bytes, size_t len, size_t in_dim, size_t out_dim) {
+    return upload_quant(h, FMT_Q4_1, key, bytes, len, in_dim, out_dim);
+}
 
 int strix_cuda_upload_f32(strix_cuda *h, const char *key, const float *data, size_t n) {
     if (!h || !key || !data) return -1;
@@ -355,7 +357,8 @@ int strix_cuda_weight_info(strix_cuda *h, const char *key, size_t *in_dim, size_
     if (out_dim_total) *out_dim_total = r->out_total;
     if (shard_row0) *shard_row0 = r->row0;
     if (shard_rows) *shard_rows = r->rows;
-    if (ggml_type) *ggml_type = r->fmt == FMT_Q4_0 ? GGML_Q4_0 : r->fmt == FMT_Q8_0 ? GGML_Q8_0 : GGML_Q6_K;
+    if (ggml_type)
+        *ggml_type = r->fmt == FMT_Q4_0 ? GGML_Q4_0 : r->fmt == FMT_Q4_1 ? GGML_Q4_1 : r->fmt == FMT_Q8_0 ? GGML_Q8_0 : GGML_Q6_K;
     return 1;
 }
 

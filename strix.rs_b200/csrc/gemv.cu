@@ -137,6 +137,7 @@ constexpr uint32_t N_DIGITS = 3;
 // way by gemv_plan).
 //   f32 form:      xB  uint4 [K/32][8 b]  lane 4c + t of block blk: B registers of column c (= 2j + hl:
 //                                         hi / lo half of activation row j) for the block's two MMAs
+//                  rec (Q4_1 only) [K/32][4] f32: the block's sum of row j's activations, scaled like xB
 //   integer form:  xB  uint2 [K/32][4 b]  lane 4j + t: int8 codes k 4t..4t+3 and 16+4t..16+4t+3 of row j
 //                  (Q6_K: [K/32][8 b], column 2j + h = row j against the first / last 16 weights only:
 //                   the other word is zero)
@@ -161,7 +162,7 @@ __host__ __device__ inline XLayout x_layout(int fmt, int act, uint32_t K, uint32
     if (act == STRIX_ACT_F32) {
         X.cols = 2u * b;
         X.xb_stride = X.cols * 4u * 16u;
-        X.rec_stride = 0u;
+        X.rec_stride = fmt == FMT_Q4_1 ? 16u : 0u;  // Q4_1: the block's sum of (scaled) activations, per row
     } else {
         X.cols = fmt == FMT_Q6_K ? 2u * b : b;
         X.xb_stride = X.cols * 4u * 8u;
@@ -246,9 +247,10 @@ __device__ __forceinline__ TileConsts tile_consts() {
     C.m00f0 = reg_const(0x00F000F0u);
     C.k6400 = reg_const(0x64006400u);
     C.k5400 = reg_const(0x54005400u);
-    // f16 pairs: 1024 + 8 and 64 + 8 (Q4_0), 1024 + 128 (Q8_0), 1024 + 32 (Q6_K)
-    C.bias_a = reg_const(FMT == FMT_Q4_0 ? 0x64086408u : FMT == FMT_Q8_0 ? 0x64806480u : 0x64206420u);
-    C.bias_b = reg_const(0x54805480u);
+    // f16 pairs: 1024 + 8 and 64 + 8 (Q4_0), 1024 and 64 (Q4_1: codes are not centred), 1024 + 128 (Q8_0),
+    // 1024 + 32 (Q6_K)
+    C.bias_a = reg_const(FMT == FMT_Q4_0 ? 0x64086408u : FMT == FMT_Q4_1 ? 0x64006400u : FMT == FMT_Q8_0 ? 0x64806480u : 0x64206420u);
+    C.bias_b = reg_const(FMT == FMT_Q4_1 ? 0x54005400u : 0x54805480u);
 #pragma unroll
     for (int i = 0; i < 4; i++) C.magic[i] = (int)reg_const(0x4B400000u);
     return C;
@@ -268,19 +270,20 @@ __device__ __forceinline__ void tile_mac(uint32_t ta, uint32_t da, uint32_t xb_a
     // ---- the 16 codes of this lane: A operand words (bytes) W0 (row g, k 4t..), W1 (row g+8, k 4t..),
     //      W2 (row g, k 16+4t..), W3 (row g+8, k 16+4t..); block scales of rows g and g + 8 ----
     uint32_t W0, W1, W2, W3;
-    float2 d;
+    float2 d, mn = make_float2(0.f, 0.f);
     if (FMT == FMT_Q8_0) {
         W0 = lds32(ta + 4u * lane);
         W2 = lds32(ta + 128u + 4u * lane);
         W1 = lds32(ta + 256u + 4u * lane);
         W3 = lds32(ta + 384u + 4u * lane);
         d = h2_to_f2(lds32(ta + 512u + 4u * g));
-    } else if (FMT == FMT_Q4_0) {
+    } else if (FMT == FMT_Q4_0 || FMT == FMT_Q4_1) {
         const uint2 n = lds64(ta + 8u * lane);
         W0 = n.x;  // nibbles: kept packed for the f32 form, split below for the integer form
         W2 = n.y;
         W1 = W3 = 0;
         d = h2_to_f2(lds32(ta + 256u + 4u * g));
+        if (FMT == FMT_Q4_1) mn = h2_to_f2(lds32(ta + 288u + 4u * g));  // the block minimums of rows g and g + 8
     } else {
         const uint2 lo = lds64(ta + 8u * lane);
         const uint32_t H = lds32(ta + 256u + 4u * lane);
@@ -298,7 +301,7 @@ __device__ __forceinline__ void tile_mac(uint32_t ta, uint32_t da, uint32_t xb_a
     if (ACT == STRIX_ACT_F32) {
         const uint4 xb = lds128(xb_a);
         float c0[4];
-        if (FMT == FMT_Q4_0) {
+        if (FMT == FMT_Q4_0 || FMT == FMT_Q4_1) {
             // nibble in bits 0..3 of a half-word: 0x6400 | n = 1024 + n; in bits 4..7: 0x5400 | (n << 4) = 64 + n;
             // minus 1024 + 8 / 64 + 8 gives the signed weight, exactly. Even nibbles are row g, odd ones row g + 8.
             const uint32_t w8 = W0 >> 8, v8 = W2 >> 8;
@@ -308,6 +311,13 @@ __device__ __forceinline__ void tile_mac(uint32_t ta, uint32_t da, uint32_t xb_a
             mma_f16(c0, hsub2_bits(and_or(W2, C.m000f, C.k6400), C.bias_a), hsub2_bits(and_or(W2, C.m00f0, C.k5400), C.bias_b),
                     hsub2_bits(and_or(v8, C.m000f, C.k6400), C.bias_a), hsub2_bits(and_or(v8, C.m00f0, C.k5400), C.bias_b),
                     xb.z, xb.w);
+            if (FMT == FMT_Q4_1) {
+                // value = d * code + m: the minimum meets the block's sum of activations (scaled like the
+                // operands; the record holds it per activation row), q4_1_gemv_dp's term (kernels.rs:289-320)
+                const float xs = __uint_as_float(lds32(xr_a));
+                acc[0] = fmaf(mn.x, xs, acc[0]);
+                acc[1] = fmaf(mn.y, xs, acc[1]);
+            }
             acc[0] = fmaf(d.x, c0[0] + c0[1], acc[0]);
             acc[1] = fmaf(d.y, c0[2] + c0[3], acc[1]);
         } else if (FMT == FMT_Q8_0) {
@@ -335,7 +345,7 @@ __device__ __forceinline__ void tile_mac(uint32_t ta, uint32_t da, uint32_t xb_a
             acc[1] = fmaf(s_hi1, c1[2] + c1[3], acc[1]);
         }
     } else {
-        if (FMT == FMT_Q4_0) {
+        if (FMT == FMT_Q4_0 || FMT == FMT_Q4_1) {
             const uint32_t n0 = W0, n1 = W2;
             W0 = n0 & M4;
             W1 = (n0 >> 4) & M4;
@@ -370,15 +380,28 @@ __device__ __forceinline__ void tile_mac(uint32_t ta, uint32_t da, uint32_t xb_a
             const float f1 = __int_as_float(c[1]) - 12582912.0f, f3 = __int_as_float(c[3]) - 12582912.0f;
             const float dx0 = __uint_as_float(r.x), dx1 = __uint_as_float(r.y);
             const float k0 = __uint_as_float(r.z), k1 = __uint_as_float(r.w);
-            acc[0] = fmaf(d.x, fmaf(dx0, f0, k0), acc[0]);
-            acc[1] = fmaf(d.x, fmaf(dx1, f1, k1), acc[1]);
-            acc[2] = fmaf(d.y, fmaf(dx0, f2, k0), acc[2]);
-            acc[3] = fmaf(d.y, fmaf(dx1, f3, k1), acc[3]);
+            if (FMT == FMT_Q4_1) {
+                // Q4_1: the record's k is d_x * sum(x codes); y += d_w * d_x * isum + m_w * k (kernels.rs:316)
+                acc[0] = fmaf(d.x, dx0 * f0, fmaf(mn.x, k0, acc[0]));
+                acc[1] = fmaf(d.x, dx1 * f1, fmaf(mn.x, k1, acc[1]));
+                acc[2] = fmaf(d.y, dx0 * f2, fmaf(mn.y, k0, acc[2]));
+                acc[3] = fmaf(d.y, dx1 * f3, fmaf(mn.y, k1, acc[3]));
+            } else {
+                acc[0] = fmaf(d.x, fmaf(dx0, f0, k0), acc[0]);
+                acc[1] = fmaf(d.x, fmaf(dx1, f1, k1), acc[1]);
+                acc[2] = fmaf(d.y, fmaf(dx0, f2, k0), acc[2]);
+                acc[3] = fmaf(d.y, fmaf(dx1, f3, k1), acc[3]);
+            }
         } else {
             const uint2 r = lds64(xr_a);
             const float dx = __uint_as_float(r.x), k0 = __uint_as_float(r.y);
-            acc[0] = fmaf(d.x, fmaf(dx, f0, k0), acc[0]);
-            acc[1] = fmaf(d.y, fmaf(dx, f2, k0), acc[1]);
+            if (FMT == FMT_Q4_1) {
+                acc[0] = fmaf(d.x, dx * f0, fmaf(mn.x, k0, acc[0]));
+                acc[1] = fmaf(d.y, dx * f2, fmaf(mn.y, k0, acc[1]));
+            } else {
+                acc[0] = fmaf(d.x, fmaf(dx, f0, k0), acc[0]);
+                acc[1] = fmaf(d.y, fmaf(dx, f2, k0), acc[1]);
+            }
         }
     }
 }
@@ -632,7 +655,7 @@ __device__ __forceinline__ void consumer_prologue(const GemvArgs &A, const Cta &
                     split_h(t4.x, s, h[0], l[0]); split_h(t4.y, s, h[1], l[1]);
                     split_h(t4.z, s, h[2], l[2]); split_h(t4.w, s, h[3], l[3]);
                     uint2 uh, ul;
-                    if (FMT == FMT_Q4_0) {
+                    if (FMT == FMT_Q4_0 || FMT == FMT_Q4_1) {
                         uh = make_uint2(pack_h2(h[0], h[2]), pack_h2(h[1], h[3]));
                         ul = make_uint2(pack_h2(l[0], l[2]), pack_h2(l[1], l[3]));
                     } else {
@@ -643,6 +666,13 @@ __device__ __forceinline__ void consumer_prologue(const GemvArgs &A, const Cta &
                         uint2 *xb2 = reinterpret_cast<uint2 *>(smem + XL.xb);
                         xb2[(blk * 8u * B + (2u * bi) * 4u + t) * 2u + hf] = uh;
                         xb2[(blk * 8u * B + (2u * bi + 1u) * 4u + t) * 2u + hf] = ul;
+                    }
+                    if (FMT == FMT_Q4_1) {
+                        float bs = ((t4.x + t4.y) + (t4.z + t4.w)) * s;  // s is a power of two: exact
+                        bs += __shfl_xor_sync(0xffffffffu, bs, 1);
+                        bs += __shfl_xor_sync(0xffffffffu, bs, 2);
+                        bs += __shfl_xor_sync(0xffffffffu, bs, 4);
+                        if (live && l8 == 0) reinterpret_cast<float *>(smem + XL.rec)[blk * 4u + bi] = bs;
                     }
                 } else if (ACT == ACT_F32_DIGITS) {
                     // three int8 digits per value, base 254: q1 = rint(x / d), r = x / d - q1 (|r| <= 1/2),
@@ -680,7 +710,8 @@ __device__ __forceinline__ void consumer_prologue(const GemvArgs &A, const Cta &
                     // q = clamp(rintf(x*inv)); eight lanes per block, four elements each
                     uint32_t *xbw = reinterpret_cast<uint32_t *>(smem + XL.xb);
                     float *rec = reinterpret_cast<float *>(smem + XL.rec);
-                    constexpr int BIAS = FMT == FMT_Q8_0 ? 128 : FMT == FMT_Q4_0 ? 8 : 32;
+                    // (Q4_1 is not centred: its record keeps +d_x * sum(codes) for the minimum's term)
+                    constexpr int BIAS = FMT == FMT_Q8_0 ? 128 : FMT == FMT_Q4_0 ? 8 : FMT == FMT_Q4_1 ? -1 : 32;
                     float bm = fmaxf(fmaxf(fabsf(t4.x), fabsf(t4.y)), fmaxf(fabsf(t4.z), fabsf(t4.w)));
                     bm = fmaxf(bm, __shfl_xor_sync(0xffffffffu, bm, 1));
                     bm = fmaxf(bm, __shfl_xor_sync(0xffffffffu, bm, 2));
@@ -753,7 +784,7 @@ __device__ __forceinline__ void consumer_groups(const GemvArgs &A, Cta &C) {
     const uint32_t n_op = XL.cols * 4u;
     const uint32_t lane_eff = (n_op > 16u && lane >= 16u) ? 16u + (lane - 16u) % (n_op - 16u) : lane % n_op;
     const uint32_t xb_l = xs0 + XL.xb + lane_eff * (ACT == STRIX_ACT_F32 ? 16u : 8u);
-    const uint32_t xr_l = xs0 + XL.rec + ((FMT == FMT_Q6_K || MULTI) ? 16u * t : 0u);
+    const uint32_t xr_l = xs0 + XL.rec + ((FMT == FMT_Q6_K || MULTI) ? 16u * t : (FMT == FMT_Q4_1 && ACT == STRIX_ACT_F32) ? 4u * t : 0u);
     const TileConsts TC = tile_consts<FMT, ACT>();
     const uint32_t xb_step = wc * XL.xb_stride, xr_step = wc * XL.rec_stride, ta_step = wc * L.tile_bytes;
     const uint32_t q6_step = wc * Q6_SUB;
@@ -1031,6 +1062,11 @@ gemv_chain_kernel(const GemvArgs *__restrict__ steps, uint32_t n_steps, uint32_t
                 STRIX_TRACE(1)
                 consumer_groups<FMT_Q4_0, ACT, false>(A, C);
                 break;
+            case FMT_Q4_1:
+                chain_prologue<FMT_Q4_1, ACT>(A, C);
+                STRIX_TRACE(1)
+                consumer_groups<FMT_Q4_1, ACT, false>(A, C);
+                break;
             case FMT_Q8_0:
                 chain_prologue<FMT_Q8_0, ACT>(A, C);
                 STRIX_TRACE(1)
@@ -1199,6 +1235,7 @@ cudaError_t launch_gemv(const GemvArgs &a, cudaStream_t stream) {
     if (a.n_tiles == 0) return cudaSuccess;
     switch (a.L.fmt) {
         case FMT_Q4_0: return launch_fmt<FMT_Q4_0>(a, stream);
+        case FMT_Q4_1: return launch_fmt<FMT_Q4_1>(a, stream);
         case FMT_Q8_0: return launch_fmt<FMT_Q8_0>(a, stream);
         default: return launch_fmt<FMT_Q6_K>(a, stream);
     }
@@ -1299,6 +1336,7 @@ static cudaError_t optin_fmt(size_t b) {
 cudaError_t gemv_prepare_device(size_t smem_optin) {
     cudaError_t e;
     if ((e = optin_fmt<FMT_Q4_0>(smem_optin)) != cudaSuccess) return e;
+    if ((e = optin_fmt<FMT_Q4_1>(smem_optin)) != cudaSuccess) return e;
     if ((e = optin_fmt<FMT_Q8_0>(smem_optin)) != cudaSuccess) return e;
     if ((e = optin_fmt<FMT_Q6_K>(smem_optin)) != cudaSuccess) return e;
     if ((e = cudaFuncSetAttribute(gemv_chain_kernel<STRIX_ACT_F32>, cudaFuncAttributeMaxDynamicSharedMemorySize,

@@ -16,6 +16,8 @@
 //       32 lanes x 8 B; lane 4g + t, byte 4h + i = code(row g, k) | code(row g + 8, k) << 4
 //       with k = 16h + 4t + i  (g 0..7, t 0..3, h 0..1, i 0..3)
 //       16 x f16 scales, in pairs (row g, row g + 8)
+//   Q4_1 tile, 320 B: the Q4_0 tile (codes 0..15 with no centring: value = d * code + m) followed by
+//       16 x f16 minimums m, in pairs (row g, row g + 8)
 //   Q6_K tile, 3360 B (16 rows x one 256-weight super-block):
 //       8 sub-tiles of 416 B (32 consecutive weights each):
 //           32 lanes x 8 B low nibbles, 32 lanes x 4 B high bit pairs (see q6k_pack below),
@@ -33,13 +35,13 @@
 
 namespace strix {
 
-enum Fmt : int { FMT_Q4_0 = 0, FMT_Q8_0 = 1, FMT_Q6_K = 2 };
+enum Fmt : int { FMT_Q4_0 = 0, FMT_Q8_0 = 1, FMT_Q6_K = 2, FMT_Q4_1 = 3 };
 
 // ggml type ids (crates/strix-models/src/ggml_quant.rs:568-574)
-constexpr int GGML_Q4_0 = 2, GGML_Q8_0 = 8, GGML_Q6_K = 14;
+constexpr int GGML_Q4_0 = 2, GGML_Q4_1 = 3, GGML_Q8_0 = 8, GGML_Q6_K = 14;
 
 constexpr uint32_t TILE_ROWS = 16;
-constexpr uint32_t Q8_TILE = 544, Q4_TILE = 288, Q6_SUB = 416, Q6_TILE = 8 * Q6_SUB + 32;
+constexpr uint32_t Q8_TILE = 544, Q4_TILE = 288, Q41_TILE = 320, Q6_SUB = 416, Q6_TILE = 8 * Q6_SUB + 32;
 
 struct RowLayout {
     int fmt;
@@ -59,12 +61,14 @@ inline
     L.fmt = fmt;
     L.in_dim = in_dim;
     L.nb = in_dim / (fmt == FMT_Q6_K ? 256u : 32u);
-    L.tile_bytes = fmt == FMT_Q4_0 ? Q4_TILE : fmt == FMT_Q8_0 ? Q8_TILE : Q6_TILE;
+    L.tile_bytes = fmt == FMT_Q4_0 ? Q4_TILE : fmt == FMT_Q4_1 ? Q41_TILE : fmt == FMT_Q8_0 ? Q8_TILE : Q6_TILE;
     L.group_bytes = L.nb * L.tile_bytes;
     return L;
 }
 
-constexpr uint32_t gguf_block_bytes(int fmt) { return fmt == FMT_Q4_0 ? 18u : fmt == FMT_Q8_0 ? 34u : 210u; }
+constexpr uint32_t gguf_block_bytes(int fmt) {
+    return fmt == FMT_Q4_0 ? 18u : fmt == FMT_Q4_1 ? 20u : fmt == FMT_Q8_0 ? 34u : 210u;
+}
 constexpr uint32_t gguf_block_elems(int fmt) { return fmt == FMT_Q6_K ? 256u : 32u; }
 
 inline
@@ -86,9 +90,9 @@ __device__ inline uint32_t resident_code(const uint8_t *res, const RowLayout &L,
         const uint32_t kk = k & 31u;
         return grp[(k >> 5) * Q8_TILE + (rh * 2u + (kk >> 4)) * 128u + g * 16u + (kk & 15u)];
     }
-    if (L.fmt == FMT_Q4_0) {
+    if (L.fmt == FMT_Q4_0 || L.fmt == FMT_Q4_1) {
         const uint32_t kk = k & 31u, h = kk >> 4, t = (kk & 15u) >> 2, i = kk & 3u;
-        const uint32_t b = grp[(k >> 5) * Q4_TILE + 8u * (4u * g + t) + 4u * h + i];
+        const uint32_t b = grp[(k >> 5) * L.tile_bytes + 8u * (4u * g + t) + 4u * h + i];
         return rh ? (b >> 4) : (b & 0x0Fu);
     }
     const uint32_t e = k & 255u, st = e >> 5, kk = e & 31u, h = kk >> 4, t = (kk & 15u) >> 2, i = kk & 3u;
@@ -100,9 +104,15 @@ __device__ inline uint32_t resident_code(const uint8_t *res, const RowLayout &L,
 // f16 bits of the scale of GGUF block `blk` (32 weights; a 256-weight super-block for Q6_K) of a row.
 __device__ inline uint16_t resident_scale_bits(const uint8_t *res, const RowLayout &L, uint32_t row, uint32_t blk) {
     const uint8_t *tile = res + (uint64_t)(row / TILE_ROWS) * L.group_bytes + (uint64_t)blk * L.tile_bytes;
-    const uint32_t off = L.fmt == FMT_Q8_0 ? 512u : L.fmt == FMT_Q4_0 ? 256u : 8u * Q6_SUB;
+    const uint32_t off = L.fmt == FMT_Q8_0 ? 512u : L.fmt == FMT_Q6_K ? 8u * Q6_SUB : 256u;
     const uint32_t r = row % TILE_ROWS;
     return *reinterpret_cast<const uint16_t *>(tile + off + 4u * (r & 7u) + 2u * (r >> 3));
+}
+// Q4_1: f16 bits of the minimum m of GGUF block `blk` of a row.
+__device__ inline uint16_t resident_min_bits(const uint8_t *res, const RowLayout &L, uint32_t row, uint32_t blk) {
+    const uint8_t *tile = res + (uint64_t)(row / TILE_ROWS) * L.group_bytes + (uint64_t)blk * L.tile_bytes;
+    const uint32_t r = row % TILE_ROWS;
+    return *reinterpret_cast<const uint16_t *>(tile + 288u + 4u * (r & 7u) + 2u * (r >> 3));
 }
 // Q6_K: int8 sub-scale of 16-weight group `grp16` (0 .. in_dim/16 - 1) of a row.
 __device__ inline int resident_q6k_subscale(const uint8_t *res, const RowLayout &L, uint32_t row, uint32_t grp16) {

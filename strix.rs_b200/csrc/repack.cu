@@ -52,8 +52,10 @@ __global__ void repack_q4q8_kernel(const uint8_t *__restrict__ raw, uint8_t *__r
         // weight k < 16 in the low nibble of byte k and weight k >= 16 in the high nibble of byte k - 16
 #pragma unroll
         for (uint32_t h = 0; h < 2; h++) {
-            const uint32_t q_lo = v_lo ? rd32(b_lo + 2 + 4u * t) : 0x88888888u;
-            const uint32_t q_hi = v_hi ? rd32(b_hi + 2 + 4u * t) : 0x88888888u;
+            // (rows past the end: Q4_0 code 8 is the value 0; Q4_1 code 0 with d = m = 0 is)
+            constexpr uint32_t QO = FMT == FMT_Q4_1 ? 4u : 2u, PAD = FMT == FMT_Q4_1 ? 0u : 0x88888888u;
+            const uint32_t q_lo = v_lo ? rd32(b_lo + QO + 4u * t) : PAD;
+            const uint32_t q_hi = v_hi ? rd32(b_hi + QO + 4u * t) : PAD;
             const uint32_t n_lo = (h ? (q_lo >> 4) : q_lo) & 0x0F0F0F0Fu, n_hi = (h ? (q_hi >> 4) : q_hi) & 0x0F0F0F0Fu;
             *reinterpret_cast<uint32_t *>(tile + 8u * lane + 4u * h) = n_lo | (n_hi << 4);
         }
@@ -64,6 +66,10 @@ __global__ void repack_q4q8_kernel(const uint8_t *__restrict__ raw, uint8_t *__r
         const uint16_t d = r < n ? (uint16_t)(b[0] | (b[1] << 8)) : (uint16_t)0;
         // scales sit in pairs (row g, row g + 8), so that a lane reads both with one 32-bit load
         *reinterpret_cast<uint16_t *>(tile + (FMT == FMT_Q8_0 ? 512u : 256u) + 4u * (lane & 7u) + 2u * (lane >> 3)) = d;
+        if (FMT == FMT_Q4_1) {
+            const uint16_t m = r < n ? (uint16_t)(b[2] | (b[3] << 8)) : (uint16_t)0;
+            *reinterpret_cast<uint16_t *>(tile + 288u + 4u * (lane & 7u) + 2u * (lane >> 3)) = m;
+        }
     }
 }
 
@@ -134,6 +140,8 @@ cudaError_t launch_repack(int fmt, const uint8_t *d_raw, uint8_t *d_res, uint8_t
         const unsigned gr = (unsigned)((total + T - 1) / T);
         if (fmt == FMT_Q4_0)
             repack_q4q8_kernel<FMT_Q4_0><<<gr, T, 0, stream>>>(d_raw, d_res, nullptr, L, row0, n);
+        else if (fmt == FMT_Q4_1)
+            repack_q4q8_kernel<FMT_Q4_1><<<gr, T, 0, stream>>>(d_raw, d_res, nullptr, L, row0, n);
         else
             repack_q4q8_kernel<FMT_Q8_0><<<gr, T, 0, stream>>>(d_raw, d_res, d_gemm_codes, L, row0, n);
     }
@@ -156,6 +164,11 @@ __global__ void dequant_kernel(const uint8_t *__restrict__ res, float *__restric
         const float d = f16_bits_to_f32(resident_scale_bits(res, L, row, u >> 4));
         const float dsc = __fmul_rn(d, (float)resident_q6k_subscale(res, L, row, u));
         for (uint32_t j = 0; j < 16; j++) o[j] = __fmul_rn(dsc, (float)((int)resident_code(res, L, row, 16u * u + j) - 32));
+    } else if (L.fmt == FMT_Q4_1) {
+        // d * code + m: multiply, then add, two roundings (dequant_q4_1, ggml_quant.rs:264-275)
+        const float d = f16_bits_to_f32(resident_scale_bits(res, L, row, u >> 1));
+        const float m = f16_bits_to_f32(resident_min_bits(res, L, row, u >> 1));
+        for (uint32_t j = 0; j < 16; j++) o[j] = __fadd_rn(__fmul_rn(d, (float)resident_code(res, L, row, 16u * u + j)), m);
     } else {
         const float d = f16_bits_to_f32(resident_scale_bits(res, L, row, u >> 1));
         const int bias = L.fmt == FMT_Q8_0 ? 128 : 8;

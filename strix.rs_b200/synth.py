@@ -11,9 +11,9 @@ import zlib
 
 import numpy as np
 
-Q4_0, Q8_0, Q6_K = 2, 8, 14
-BLOCK_ELEMS = {Q4_0: 32, Q8_0: 32, Q6_K: 256}
-BLOCK_BYTES = {Q4_0: 18, Q8_0: 34, Q6_K: 210}
+Q4_0, Q4_1, Q8_0, Q6_K = 2, 3, 8, 14
+BLOCK_ELEMS = {Q4_0: 32, Q4_1: 32, Q8_0: 32, Q6_K: 256}
+BLOCK_BYTES = {Q4_0: 18, Q4_1: 20, Q8_0: 34, Q6_K: 210}
 
 
 def rng(seed, name):
@@ -32,6 +32,18 @@ def q4_0(seed, name, out_dim, in_dim, d_lo=0.002, d_hi=0.02):
     a = np.empty((out_dim, nb, 18), dtype=np.uint8)
     a[:, :, 0:2] = _f16_bytes(g, (out_dim, nb), d_lo, d_hi)
     a[:, :, 2:] = g.integers(0, 256, size=(out_dim, nb, 16), dtype=np.uint8)
+    return a.reshape(-1)
+
+
+def q4_1(seed, name, out_dim, in_dim, d_lo=0.002, d_hi=0.02):
+    """Q4_1: d = f16(U(d_lo, d_hi)), m = f16(U(-8 d_hi, 0)) (what an asymmetric quantiser of centred
+    weights produces), 16 code bytes with nibbles U{0..15}; value = d * code + m."""
+    nb = in_dim // 32
+    g = rng(seed, name)
+    a = np.empty((out_dim, nb, 20), dtype=np.uint8)
+    a[:, :, 0:2] = _f16_bytes(g, (out_dim, nb), d_lo, d_hi)
+    a[:, :, 2:4] = _f16_bytes(g, (out_dim, nb), -8.0 * d_hi, 0.0)
+    a[:, :, 4:] = g.integers(0, 256, size=(out_dim, nb, 16), dtype=np.uint8)
     return a.reshape(-1)
 
 
@@ -57,7 +69,7 @@ def q6_k(seed, name, out_dim, in_dim, d_lo=1e-4, d_hi=1e-3):
 
 
 def quant(ty, seed, name, out_dim, in_dim):
-    return {Q4_0: q4_0, Q8_0: q8_0, Q6_K: q6_k}[ty](seed, name, out_dim, in_dim)
+    return {Q4_0: q4_0, Q4_1: q4_1, Q8_0: q8_0, Q6_K: q6_k}[ty](seed, name, out_dim, in_dim)
 
 
 def normal(seed, name, *shape):

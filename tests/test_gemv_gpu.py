@@ -17,7 +17,8 @@ def rel_l2(got, want):
 
 
 def uploader(accel, synth, ty):
-    return {synth.Q4_0: accel.upload_q4_0, synth.Q8_0: accel.upload_q8_0, synth.Q6_K: accel.upload_q6_k}[ty]
+    return {synth.Q4_0: accel.upload_q4_0, synth.Q4_1: accel.upload_q4_1, synth.Q8_0: accel.upload_q8_0,
+            synth.Q6_K: accel.upload_q6_k}[ty]
 
 
 # ------------------------------------------------------------------ tier 1
@@ -38,6 +39,7 @@ def test_dequant_golden_bit_exact(accel, name, ty, synth):
     (2, [(1, 32), (7, 64), (9, 2560), (33, 4096), (8, 9728), (5, 16384)]),
     (8, [(1, 32), (7, 96), (9, 2560), (33, 4096), (8, 9728), (3, 16384)]),
     (14, [(1, 256), (7, 512), (9, 2560), (33, 4096), (8, 9728), (3, 16384)]),
+    (3, [(1, 32), (7, 64), (9, 2560), (33, 4096), (8, 9728), (5, 16384)]),
 ])
 def test_dequant_matches_oracle_bit_exact(accel, orc, synth, ty, shapes):
     for out_dim, in_dim in shapes:
@@ -67,7 +69,8 @@ def test_upload_declines_like_the_reference(accel, synth):
     assert accel.upload_q4_0("bad.k", w, 48, 4) is False          # in_dim % 32 != 0  (decode.rs:2492-2494)
     assert accel.upload_q4_0("bad.len", w[:-1], 64, 4) is False   # len mismatch       (decode.rs:2497-2499)
     assert accel.upload_q6_k("bad.k6", w, 128, 4) is False        # in_dim % 256 != 0  (decode.rs:2630-2632)
-    assert accel.upload_q4_1("q41", w, 64, 4) is False            # trait default      (accel.rs:154-156)
+    assert accel.upload_q4_1("q41", w, 64, 4) is False            # 18-byte blocks are not Q4_1's 20 (decode.rs:2594-2596)
+    assert accel.upload_q4_1("q41", synth.q4_1(1, "d", 4, 64), 48, 4) is False   # in_dim % 32 != 0 (decode.rs:2589-2591)
     assert accel.weight_info("bad.k") is None and accel.weight_info("bad.len") is None
 
 
@@ -94,6 +97,8 @@ GEMV_CASES = [
     (2, 1, 32), (2, 7, 64), (2, 9, 96), (2, 257, 2560), (2, 4096, 4096), (2, 2560, 9728), (2, 100, 16384),
     (8, 1, 32), (8, 8, 64), (8, 9, 3840), (8, 9728, 2560), (8, 2560, 9728), (8, 64, 16384),
     (14, 1, 256), (14, 7, 512), (14, 17, 3840), (14, 9728, 2560), (14, 2560, 9728), (14, 40, 16384),
+    # Q4_1 (llama.cpp keeps early-layer ffn_down in it): value = d * code + m
+    (3, 1, 32), (3, 7, 64), (3, 9, 96), (3, 257, 2560), (3, 2560, 9728), (3, 50, 16384), (3, 19, 20480),
     # rows longer than the activation prologue keeps in registers (6 float4 x 768 threads = 18432 values):
     # the rest of the row is re-read; and the widest FFN of the reference's model zoo (27648)
     (2, 33, 20480), (8, 20, 27648), (14, 18, 20480),
@@ -335,7 +340,8 @@ def test_gemv_dev_prologues_and_fused_weights(accel, orc, synth, pkg):
 
 
 # ------------------------------------------------------------------ batched rows (speculative verify)
-@pytest.mark.parametrize("ty,out_dim,in_dim", [(2, 257, 3840), (2, 100, 15360), (8, 64, 2560), (14, 33, 3840), (2, 9, 64)])
+@pytest.mark.parametrize("ty,out_dim,in_dim", [(2, 257, 3840), (2, 100, 15360), (8, 64, 2560), (14, 33, 3840), (2, 9, 64),
+                                               (3, 257, 3840), (3, 40, 15360)])
 @pytest.mark.parametrize("b", [1, 2, 4, 8])
 def test_gemv_rows_matches_oracle(accel, orc, synth, pkg, ty, out_dim, in_dim, b):
     w = synth.quant(ty, 33, "rows", out_dim, in_dim)

@@ -24,16 +24,16 @@ def test_model_file_to_decode_step(pkg, orc, synth, tmp_path):
         for nm, n, k in (("attn_q", qdim, hidden), ("attn_k", kvdim, hidden), ("attn_v", kvdim, hidden),
                          ("attn_output", hidden, qdim), ("ffn_gate", ffn, hidden), ("ffn_up", ffn, hidden)):
             add(b + nm + ".weight", synth.Q4_0, n, k)
-        add(b + "ffn_down.weight", synth.Q8_0, hidden, ffn)  # mixed formats in one file
+        add(b + "ffn_down.weight", synth.Q4_1 if il == 0 else synth.Q8_0, hidden, ffn)  # mixed formats in one file
         for nn in ("attn_norm.weight", "ffn_norm.weight"):
             W[b + nn] = synth.norm_weight(70, b + nn, hidden)
             ts.append((b + nn, [hidden], gguf.GGML_F32, W[b + nn].tobytes()))
     add("output.weight", synth.Q6_K, vocab, hidden)
     W["output_norm.weight"] = synth.norm_weight(70, "output_norm", hidden)
     ts.append(("output_norm.weight", [hidden], gguf.GGML_F32, W["output_norm.weight"].tobytes()))
-    # tensors the accelerator has no kernel for: F16 matrix, Q4_1 matrix (declined by design), 2-D F32
+    # tensors the accelerator has no kernel for: F16 matrix, Q4_K matrix, 2-D F32
     ts.append(("token_embd.weight", [hidden, 8], gguf.GGML_F16, np.zeros(hidden * 8, np.float16).tobytes()))
-    ts.append(("blk.0.q41.weight", [64, 4], gguf.GGML_Q4_1, bytes(2 * 4 * 20)))
+    ts.append(("blk.0.q4k.weight", [256, 4], 12, bytes(4 * 144)))
     ts.append(("rope_freqs", [4, 4], gguf.GGML_F32, bytes(64)))
     path = tmp_path / "model.gguf"
     gguf.write_gguf(path, {"general.architecture": "qwen3", "qwen3.block_count": n_layers,

@@ -250,3 +250,24 @@ def test_argmax_follows_the_reference_kernel(orc):
     for x in cases:
         with np.errstate(invalid="ignore"):
             assert orc.argmax_f32(x) == replay(x), x
+
+
+def test_q4_1_integer_dot_follows_q4_1_gemv_dp(orc, synth):
+    # kernels.rs:289-320: acc += xd * (d * (float)isum + m * (float)xsum), codes 0..15 not centred
+    in_dim, out_dim = 256, 12
+    w = synth.quant(synth.Q4_1, 9, "w41", out_dim, in_dim)
+    x = synth.normal(9, "x41", in_dim)
+    xq, xd, _ = orc.xquant8(x)
+    y, isums = orc.idot_gemm(w, synth.Q4_1, xq, xd, 1, in_dim, out_dim, want_isums=True)
+    blk = w.reshape(out_dim, in_dim // 32, 20)
+    d = blk[:, :, 0:2].copy().view(np.float16)[:, :, 0].astype(np.float64)
+    m = blk[:, :, 2:4].copy().view(np.float16)[:, :, 0].astype(np.float64)
+    codes = np.concatenate([blk[:, :, 4:] & 0x0F, blk[:, :, 4:] >> 4], axis=2).astype(np.int64)   # element order j, j+16
+    xb = xq.reshape(-1, 32).astype(np.int64)
+    want_isum = np.einsum("nbi,bi->nb", codes, xb)
+    np.testing.assert_array_equal(isums[0], want_isum)
+    ref = ((d * want_isum + m * xb.sum(axis=1)[None, :]) * xd.astype(np.float64)[None, :]).sum(axis=1)
+    assert np.linalg.norm(y[0] - ref) / np.linalg.norm(ref) < 1e-5
+    # and close to the f32-activation path (activation quantisation error only)
+    yf = orc.qmatmul(x, w, synth.Q4_1, in_dim, out_dim)
+    assert np.linalg.norm(y[0] - yf) / np.linalg.norm(yf) < 2e-2
