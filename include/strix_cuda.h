@@ -210,19 +210,25 @@ typedef struct strix_gpu_decode_config {
     uint32_t n_swa, max_seq;
     const strix_gpu_layer_cfg *layers; /* n_layers entries; may be NULL (unused by the projection chain) */
     /* Not in the reference struct: */
-    int attn_standin_q; /* must be 1: attention is outside this library's path; Wo is fed with q */
+    int attn_standin_q; /* 1: projection chain only, Wo is fed with q (no KV cache). 0: real attention of the dense
+                         * Qwen3 flavour (QK-norm when qk_norm, NEOX rope, KV cache of max_seq rows, grouped-query
+                         * softmax with 1/sqrt(head_dim)); `layers` must then describe every layer */
     int act;            /* STRIX_ACT_F32 or STRIX_ACT_Q8DOT for every projection */
 } strix_gpu_decode_config;
 
 /* WeightAccel::configure_decode (accel.rs:417; decode.rs:4528-4622). Call after every weight
  * (blk.N.attn_q/attn_k/attn_v/attn_output/ffn_gate/ffn_up/ffn_down.weight, output.weight or
  * token_embd.weight) and norm (blk.N.attn_norm/ffn_norm.weight, output_norm.weight via upload_f32)
- * is uploaded. 0 = declined (a weight missing, post-norm / softcap / real attention requested, or a
- * sharded handle): the model keeps its per-weight gemv path. Any later upload drops the configuration. */
+ * is uploaded; with real attention and qk_norm also blk.N.attn_q_norm / attn_k_norm.weight (head_dim floats).
+ * 0 = declined (a weight missing, post-norm / softcap / V-norm / sliding-window or local layers / shared
+ * K = V / GPT-J rope / per-layer head sizes requested, or a sharded handle): the model keeps its per-weight
+ * gemv path. Any later upload drops the configuration. */
 STRIX_API int strix_cuda_configure_decode(strix_cuda *h, const strix_gpu_decode_config *cfg);
-/* WeightAccel::decode_step (accel.rs:433; decode.rs:5047-5531), projection chain only: logits[vocab]
- * from the embedded hidden state hvec[hidden]; four GEMV launches per layer replayed from a CUDA
- * graph. `pos` is accepted for signature parity (no KV cache on this path). 0 = not configured. */
+/* WeightAccel::decode_step (accel.rs:433; decode.rs:5047-5531): logits[vocab] from the embedded hidden
+ * state hvec[hidden]; four GEMV launches per layer (plus three small attention kernels with real
+ * attention) replayed from a CUDA graph. With real attention row `pos` of the KV cache is written and
+ * rows 0..pos are attended to (pos >= max_seq is an error); with the stand-in `pos` has no effect.
+ * 0 = not configured. */
 STRIX_API int strix_cuda_decode_step(strix_cuda *h, const float *hvec, size_t pos, float *logits, size_t logits_cap);
 /* WeightAccel::decode_step_argmax (accel.rs:437-442; decode.rs:5497-5515, 5533-5538): the same step,
  * then the argmax over the logits on the device; only the winning token id crosses back (4 bytes

@@ -176,3 +176,65 @@ def argmax_f32(x):
         return 0
     masked = np.where(ok, x, -np.inf)
     return int(np.argmax(masked))             # numpy returns the first (lowest) index of the maximum
+
+
+# ---- single-token attention of the dense Qwen3 forward (crates/strix-backend-cpu/src/qwen3.rs) ----
+def rmsnorm_inplace(v, w, eps):
+    """qwen3.rs:117-124: v * (1 / sqrt(mean(v^2) + eps)) * w, over one head."""
+    v = _f32(v)
+    ss = np.float32(0.0)
+    for x in v:                      # the reference's sequential f32 sum
+        ss = np.float32(ss + x * x)
+    scale = np.float32(1.0) / np.sqrt(np.float32(ss / np.float32(v.size) + np.float32(eps)))
+    return (v * scale * _f32(w)).astype(np.float32)
+
+
+def rope_neox(vec, pos, n_dims, freq_base):
+    """qwen3.rs:126-138: pairs (k, k + half); theta starts at pos and is multiplied by
+    freq_base^(-2/n_dims) once per pair, all in f32."""
+    vec = _f32(vec).copy()
+    half = n_dims // 2
+    theta_scale = np.float32(np.power(np.float32(freq_base), np.float32(-2.0) / np.float32(n_dims)))
+    theta = np.float32(pos)
+    for k in range(half):
+        s, c = np.float32(np.sin(theta)), np.float32(np.cos(theta))
+        x0, x1 = vec[k], vec[k + half]
+        vec[k] = x0 * c - x1 * s
+        vec[k + half] = x0 * s + x1 * c
+        theta = np.float32(theta * theta_scale)
+    return vec
+
+
+def attention_token(q, k, v, q_norm, k_norm, pos, kc, vc, n_heads, n_kv, hd, eps, freq_base):
+    """One token of qwen3.rs:823-873: per-head QK-norm then rope, append k / v to the caches (python
+    lists of rows, one per position), softmax(q k^T / sqrt(hd)) v per head with grouped-query sharing.
+    q_norm / k_norm None = no QK-norm. Returns attn[n_heads * hd]."""
+    q, k, v = _f32(q).copy(), _f32(k).copy(), _f32(v)
+    for hh in range(n_heads):
+        qh = q[hh * hd:(hh + 1) * hd]
+        if q_norm is not None:
+            qh = rmsnorm_inplace(qh, q_norm, eps)
+        q[hh * hd:(hh + 1) * hd] = rope_neox(qh, pos, hd, freq_base)
+    for kh in range(n_kv):
+        kk = k[kh * hd:(kh + 1) * hd]
+        if k_norm is not None:
+            kk = rmsnorm_inplace(kk, k_norm, eps)
+        k[kh * hd:(kh + 1) * hd] = rope_neox(kk, pos, hd, freq_base)
+    assert len(kc) == pos and len(vc) == pos
+    kc.append(k)
+    vc.append(v.copy())
+    K = np.stack(kc).reshape(pos + 1, n_kv, hd)
+    V = np.stack(vc).reshape(pos + 1, n_kv, hd)
+    scale = np.float32(1.0) / np.sqrt(np.float32(hd))
+    groups = n_heads // n_kv
+    out = np.zeros(n_heads * hd, dtype=np.float32)
+    for hh in range(n_heads):
+        kvh = hh // groups
+        qh = q[hh * hd:(hh + 1) * hd]
+        scores = np.array([dot_f32(qh, K[t, kvh]) for t in range(pos + 1)], dtype=np.float32) * scale
+        e = np.exp(scores - scores.max()).astype(np.float32)
+        o = np.zeros(hd, dtype=np.float32)
+        for t in range(pos + 1):
+            o += e[t] * V[t, kvh]
+        out[hh * hd:(hh + 1) * hd] = o * (np.float32(1.0) / e.sum(dtype=np.float32))
+    return out

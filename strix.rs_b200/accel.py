@@ -292,11 +292,24 @@ class CudaWeightAccel:
         return out if rc == 1 else None
 
     def configure_decode(self, hidden, n_heads, ffn, vocab, n_layers, eps=1e-6, act_gelu=False, act=ACT_Q8DOT,
-                         attn_standin_q=True, post_norm=False, final_softcap=0.0):
-        """GpuDecodeConfig -> bool (accel.rs:417). Only the projection chain is on this path:
-        attn_standin_q must stay True or the configuration is declined."""
+                         attn_standin_q=True, post_norm=False, final_softcap=0.0, head_dim=0, n_kv=0,
+                         rope_theta=1e6, max_seq=0, qk_norm=True, layer_overrides=None):
+        """GpuDecodeConfig -> bool (accel.rs:417). attn_standin_q=True: the projection chain alone (Wo is
+        fed with q). False: real attention of the dense Qwen3 flavour (QK-norm, NEOX rope, KV cache of
+        max_seq rows, grouped-query softmax); head_dim / n_kv / rope_theta describe every layer
+        (layer_overrides: {layer: {field: value}} for the declined-configuration tests)."""
+        layers = None
+        if not attn_standin_q:
+            layers = (_LayerCfg * n_layers)()
+            for il in range(n_layers):
+                layers[il] = _LayerCfg(head_dim=head_dim, n_kv=n_kv, k_eq_v=0, rope_theta=rope_theta, is_local=0,
+                                       output_scale=1.0, no_rope=0, rope_norm=0)
+                for k, v in (layer_overrides or {}).get(il, {}).items():
+                    setattr(layers[il], k, v)
         c = _DecodeCfg(hidden=hidden, n_heads=n_heads, ffn=ffn, vocab=vocab, n_layers=n_layers, eps=eps,
-                       final_softcap=final_softcap, post_norm=int(post_norm), act_gelu=int(act_gelu),
+                       final_softcap=final_softcap, attn_rsqrt=1, norm_v=0, qk_norm=int(qk_norm),
+                       post_norm=int(post_norm), act_gelu=int(act_gelu), max_seq=max_seq,
+                       layers=layers if layers is not None else None,
                        attn_standin_q=int(attn_standin_q), act=act)
         rc = self._check(self._L.strix_cuda_configure_decode(self._h, C.byref(c)))
         self._vocab = vocab if rc == 1 else None

@@ -13,10 +13,12 @@
 //
 // The reference needs 12 launches per layer for the same work (decode.rs:5239-5477); here the
 // norm, the activation quantiser, the gate activation and the residual add live inside the GEMV.
-// Attention (QK-norm, RoPE, KV cache, SDPA) is outside this library's path: a configuration is
-// accepted only with `attn_standin_q = 1`, which feeds Wo with q itself (n_heads * head_dim
-// values) so that the whole projection chain can be run and measured; anything else is declined
-// and the model keeps its per-weight gemv path.
+// Attention comes in two forms. `attn_standin_q = 1` feeds Wo with q itself (n_heads * head_dim
+// values): the projection chain alone, which is what the benchmark's decode configuration times.
+// `attn_standin_q = 0` runs the dense Qwen3 attention (attention.cu: per-head QK RMSNorm, NEOX RoPE,
+// KV append, grouped-query softmax over the cache) between the q/k/v step and the o step; other
+// attention flavours (sliding window, shared K = V, V-norm, softcap, post-norm) are declined and the
+// model keeps its per-weight gemv path.
 //
 // On one GPU the whole chain runs as ONE cooperative kernel (gemv_chain_kernel): the steps above
 // become a list the kernel walks, with a grid-wide barrier between steps, while its producer warps
@@ -27,6 +29,7 @@
 // The step is captured into a CUDA graph on the first call and replayed afterwards
 // (one H2D of h, one graph launch, one D2H of the logits, one sync per token).
 #include <algorithm>
+#include <cmath>
 #include <cstdio>
 #include <cstring>
 #include <string>
@@ -50,6 +53,8 @@ struct strix_decode_state {
     struct Layer {
         const Resident *q, *k, *v, *o, *gate, *up, *down;
         const float *attn_norm, *ffn_norm;
+        const float *q_norm = nullptr, *k_norm = nullptr;  // real attention with QK-norm only
+        float theta_scale = 1.f;                           // rope base ^ (-2 / head_dim), computed on the host
     };
     std::vector<Layer> layers;
     const Resident *head = nullptr;
@@ -58,6 +63,12 @@ struct strix_decode_state {
     float *h = nullptr, *q = nullptr, *k = nullptr, *v = nullptr, *gate = nullptr, *up = nullptr, *logits = nullptr;
     void *pin_h = nullptr, *pin_logits = nullptr;
     cudaGraphExec_t exec = nullptr;
+    // real attention (attn_standin_q = 0): KV cache [n_layers][max_seq][n_kv * hd] twice, the softmax
+    // partials, the attention output, and the position word the kernels read (a graph replays unchanged)
+    bool real_attn = false;
+    uint32_t hd = 0, n_kv = 0;
+    float *kc = nullptr, *vc = nullptr, *att_part = nullptr, *attn = nullptr;
+    uint32_t *d_pos = nullptr, *pin_pos = nullptr;
     // chain-kernel programs, one per (h, logits) buffer pair
     struct Program {
         const float *h;
@@ -75,8 +86,10 @@ struct strix_decode_state {
 
 static void decode_free(strix_decode_state *d) {
     if (!d) return;
-    for (float *p : {d->h, d->q, d->k, d->v, d->gate, d->up, d->logits})
+    for (float *p : {d->h, d->q, d->k, d->v, d->gate, d->up, d->logits, d->kc, d->vc, d->att_part, d->attn})
         if (p) cudaFree(p);
+    if (d->d_pos) cudaFree(d->d_pos);
+    if (d->pin_pos) cudaFreeHost(d->pin_pos);
     if (d->pin_h) cudaFreeHost(d->pin_h);
     if (d->pin_logits) cudaFreeHost(d->pin_logits);
     if (d->exec) cudaGraphExecDestroy(d->exec);
@@ -110,21 +123,26 @@ static const float *f32_of(strix_cuda *h, const std::string &key, size_t n) {
 }
 
 // The chain as a list of steps, handed one at a time to `emit` (launch it, or collect it).
-template <typename Emit>
-static int walk_chain(strix_decode_state *d, Emit emit) {
+// `mid(layer index)` runs between the q/k/v step and the o step and returns the vector Wo is fed with
+// (q itself for the stand-in; the attention output otherwise), or null on error.
+template <typename Emit, typename Mid>
+static int walk_chain(strix_decode_state *d, Emit emit, Mid mid) {
     const float eps = d->cfg.eps;
     const int gate_pre = d->cfg.act_gelu ? STRIX_PRE_GEGLU : STRIX_PRE_SWIGLU;
-    for (auto &L : d->layers) {
+    for (size_t il = 0; il < d->layers.size(); il++) {
+        auto &L = d->layers[il];
         {
             const Resident *w[3] = {L.q, L.k, L.v};
             float *y[3] = {d->q, d->k, d->v};
             if (emit(3, w, d->h, L.attn_norm, eps, STRIX_PRE_RMSNORM, y, nullptr) < 0) return -1;
         }
-        {   // attention stand-in: Wo is fed with q; h += Wo q
+        {   // h += Wo a, a = the attention output (or q itself: the stand-in)
+            const float *a = mid(il);
+            if (!a) return -1;
             const Resident *w[1] = {L.o};
             float *y[1] = {d->h};
             const float *r[1] = {d->h};
-            if (emit(1, w, d->q, nullptr, 0.f, STRIX_PRE_NONE, y, r) < 0) return -1;
+            if (emit(1, w, a, nullptr, 0.f, STRIX_PRE_NONE, y, r) < 0) return -1;
         }
         {
             const Resident *w[2] = {L.gate, L.up};
@@ -146,7 +164,7 @@ static int walk_chain(strix_decode_state *d, Emit emit) {
 // The chain-kernel program for the current d->h / d->logits, built on first use. Null when the
 // chain kernel cannot be used (plan failed, switched off, or a new buffer pair inside a stream capture).
 static const strix_decode_state::Program *chain_program(strix_cuda *h, strix_decode_state *d, cudaStream_t s) {
-    if (!d->chain_ok) return nullptr;
+    if (!d->chain_ok || d->real_attn) return nullptr;  // (attention is not a GEMV step: launches only)
     for (auto &p : d->programs)
         if (p.h == d->h && p.logits == d->logits) return &p;
     cudaStreamCaptureStatus cs = cudaStreamCaptureStatusNone;
@@ -167,7 +185,7 @@ static const strix_decode_state::Program *chain_program(strix_cuda *h, strix_dec
         if (gemv_fill_args(h, nmat, w, a, b, eps, pre, act, y, r, &g) < 0) return -1;
         steps.push_back(g);
         return 1;
-    });
+    }, [&](size_t) -> const float * { return d->q; });
     uint32_t smem = 0;
     if (rc < 0 || !gemv_chain_plan(steps.data(), (uint32_t)steps.size(), h->num_sms, h->smem_optin, &smem)) {
         d->chain_ok = false;
@@ -211,6 +229,19 @@ static int enqueue_chain(strix_cuda *h, strix_decode_state *d, cudaStream_t s) {
     return walk_chain(d, [&](int nmat, const Resident *const *w, const float *a, const float *b, float eps, int pre,
                              float *const *y, const float *const *r) {
         return gemv_launch(h, nmat, w, a, b, eps, pre, act, y, r, s);
+    }, [&](size_t il) -> const float * {
+        if (!d->real_attn) return d->q;
+        const auto &L = d->layers[il];
+        const size_t per_layer = (size_t)d->cfg.max_seq * d->n_kv * d->hd;
+        const cudaError_t e = launch_attention_step(
+            d->q, d->k, d->v, L.q_norm, L.k_norm, d->kc + il * per_layer, d->vc + il * per_layer, d->att_part, d->attn,
+            d->d_pos, d->cfg.n_heads, d->n_kv, d->hd, d->cfg.eps, L.theta_scale, 1.0f / sqrtf((float)d->hd),
+            d->cfg.max_seq, h->d_status, s);
+        if (e != cudaSuccess) {
+            h->err = std::string("attention: ") + cudaGetErrorString(e);
+            return nullptr;
+        }
+        return d->attn;
     });
 }
 
@@ -221,7 +252,23 @@ int strix_cuda_configure_decode(strix_cuda *h, const strix_gpu_decode_config *cf
     h->err.clear();
     decode_release(h);
     // Only the projection chain is on this library's path; a model that expects attention here is declined.
-    if (!cfg->attn_standin_q || cfg->post_norm || cfg->final_softcap != 0.f) return 0;
+    if (cfg->post_norm || cfg->final_softcap != 0.f) return 0;
+    // Real attention: the dense Qwen3 flavour only (qwen3.rs:683-710): global NEOX-rope layers of one head
+    // size, 1/sqrt(hd) scaling, no V-norm, no sliding window, no shared K = V; anything else is declined.
+    const bool real_attn = !cfg->attn_standin_q;
+    uint32_t hd = 0, n_kv = 0;
+    if (real_attn) {
+        if (!cfg->layers || !cfg->attn_rsqrt || cfg->norm_v || cfg->n_swa || cfg->max_seq == 0 || cfg->n_heads == 0) return 0;
+        hd = cfg->layers[0].head_dim;
+        n_kv = cfg->layers[0].n_kv;
+        if (hd == 0 || hd > 256 || (hd & 1u) || n_kv == 0 || cfg->n_heads % n_kv != 0) return 0;
+        for (uint32_t il = 0; il < cfg->n_layers; il++) {
+            const strix_gpu_layer_cfg &lc = cfg->layers[il];
+            if (lc.head_dim != hd || lc.n_kv != n_kv || lc.k_eq_v || lc.is_local || lc.no_rope || lc.rope_norm ||
+                !(lc.rope_theta > 0.f) || (lc.output_scale != 0.f && lc.output_scale != 1.f))
+                return 0;
+        }
+    }
     if (h->world > 1) return 0;  // a sharded handle holds row shards only; the chain needs whole vectors
     if (cfg->act != STRIX_ACT_F32 && cfg->act != STRIX_ACT_Q8DOT) return 0;
     CU_TRY(h, cudaSetDevice(h->device));
@@ -255,6 +302,16 @@ int strix_cuda_configure_decode(strix_cuda *h, const strix_gpu_decode_config *cf
         L.down = need(b + "ffn_down.weight", ffn, hidden);
         L.attn_norm = f32_of(h, b + "attn_norm.weight", hidden);
         L.ffn_norm = f32_of(h, b + "ffn_norm.weight", hidden);
+        if (real_attn) {
+            if (cfg->qk_norm) {
+                L.q_norm = f32_of(h, b + "attn_q_norm.weight", hd);
+                L.k_norm = f32_of(h, b + "attn_k_norm.weight", hd);
+                ok = ok && L.q_norm && L.k_norm;
+            }
+            // theta_scale = freq_base.powf(-2.0 / n_dims) (qwen3.rs:128), evaluated in f32 on the host
+            L.theta_scale = powf(cfg->layers[il].rope_theta, -2.0f / (float)hd);
+            ok = ok && L.q && L.k && L.q->out_total == (size_t)cfg->n_heads * hd && L.k->out_total == (size_t)n_kv * hd;
+        }
         ok = ok && L.o && L.gate && L.up && L.down && L.attn_norm && L.ffn_norm && L.gate->fmt == L.up->fmt;
         d->layers.push_back(L);
     }
@@ -279,6 +336,20 @@ int strix_cuda_configure_decode(strix_cuda *h, const strix_gpu_decode_config *cf
     alloc(&d->gate, ffn);
     alloc(&d->up, ffn);
     alloc(&d->logits, cfg->vocab);
+    if (real_attn) {
+        d->real_attn = true;
+        d->hd = hd;
+        d->n_kv = n_kv;
+        const size_t cache = (size_t)cfg->n_layers * cfg->max_seq * n_kv * hd;
+        const size_t splits = (cfg->max_seq + ATT_SPLIT_TOKENS - 1) / ATT_SPLIT_TOKENS;
+        alloc(&d->kc, cache);
+        alloc(&d->vc, cache);
+        alloc(&d->att_part, (size_t)cfg->n_heads * splits * (hd + 2));
+        alloc(&d->attn, qdim);
+        if (e == cudaSuccess) e = cudaMalloc(&d->d_pos, 4);
+        if (e == cudaSuccess) e = cudaMemset(d->d_pos, 0, 4);
+        if (e == cudaSuccess) e = cudaMallocHost(&d->pin_pos, 4);
+    }
     if (e == cudaSuccess) e = cudaMallocHost(&d->pin_h, hidden * sizeof(float));
     if (e == cudaSuccess) e = cudaMallocHost(&d->pin_logits, (size_t)cfg->vocab * sizeof(float));
     if (e != cudaSuccess) {
@@ -295,7 +366,7 @@ int strix_cuda_decode_chain_dev(strix_cuda *h, float *d_h, float *d_logits, void
     if (!h || !d_h || !d_logits) return -1;
     h->err.clear();
     strix_decode_state *d = h->decode;
-    if (!d) return 0;
+    if (!d || d->real_attn) return 0;  // (the position travels with decode_step only)
     CU_TRY(h, cudaSetDevice(h->device));
     float *save_h = d->h, *save_l = d->logits;
     d->h = d_h;
@@ -308,8 +379,12 @@ int strix_cuda_decode_chain_dev(strix_cuda *h, float *d_h, float *d_logits, void
 
 // H2D of the hidden state and one replay of the captured chain on the handle's stream (captured on
 // the first call); the logits are then in d->logits.
-static int decode_enqueue_step(strix_cuda *h, strix_decode_state *d, const float *hvec) {
+static int decode_enqueue_step(strix_cuda *h, strix_decode_state *d, const float *hvec, size_t pos) {
     CU_TRY(h, cudaSetDevice(h->device));
+    if (d->real_attn && pos >= d->cfg.max_seq) {
+        h->err = "decode_step: position " + std::to_string(pos) + " beyond max_seq " + std::to_string(d->cfg.max_seq);
+        return -1;
+    }
     if (!d->exec) {
         cudaGraph_t g = nullptr;
         (void)chain_program(h, d, h->stream);  // built (and uploaded) before the capture starts
@@ -331,6 +406,12 @@ static int decode_enqueue_step(strix_cuda *h, strix_decode_state *d, const float
     }
     memcpy(d->pin_h, hvec, d->cfg.hidden * sizeof(float));
     CU_TRY(h, cudaMemcpyAsync(d->h, d->pin_h, d->cfg.hidden * sizeof(float), cudaMemcpyHostToDevice, h->stream));
+    if (d->real_attn) {
+        // the captured kernels read the position from this word: row `pos` of the cache is (re)written, rows
+        // 0..pos are attended to. (The previous step's copy has completed: every step ends with a sync.)
+        *d->pin_pos = (uint32_t)pos;
+        CU_TRY(h, cudaMemcpyAsync(d->d_pos, d->pin_pos, 4, cudaMemcpyHostToDevice, h->stream));
+    }
     CU_TRY(h, cudaGraphLaunch(d->exec, h->stream));
     return 1;
 }
@@ -347,8 +428,7 @@ static int decode_finish(strix_cuda *h, const char *who) {
 }
 
 int strix_cuda_decode_step(strix_cuda *h, const float *hvec, size_t pos, float *logits, size_t logits_cap) {
-    (void)pos;  // no KV cache on this path: the attention stand-in does not depend on the position
-    if (!h || !hvec || !logits) return -1;
+    if (!h || !hvec || !logits) return -1;  // (with the attention stand-in `pos` has no effect)
     h->err.clear();
     strix_decode_state *d = h->decode;
     if (!d) return 0;  // not configured: None, the model falls back to per-weight gemv
@@ -356,7 +436,7 @@ int strix_cuda_decode_step(strix_cuda *h, const float *hvec, size_t pos, float *
         h->err = "decode_step: logits buffer too small";
         return -1;
     }
-    int rc = decode_enqueue_step(h, d, hvec);
+    int rc = decode_enqueue_step(h, d, hvec, pos);
     if (rc < 0) return rc;
     CU_TRY(h, cudaMemcpyAsync(d->pin_logits, d->logits, (size_t)d->cfg.vocab * sizeof(float), cudaMemcpyDeviceToHost, h->stream));
     if ((rc = decode_finish(h, "decode_step")) < 0) return rc;
@@ -369,12 +449,11 @@ int strix_cuda_decode_step(strix_cuda *h, const float *hvec, size_t pos, float *
 // A row-sharded accelerator (world > 1) holds only its own logits and declines (0): the caller folds
 // the shards' winners itself.
 int strix_cuda_decode_step_argmax(strix_cuda *h, const float *hvec, size_t pos, uint32_t *id) {
-    (void)pos;
     if (!h || !hvec || !id) return -1;
     h->err.clear();
     strix_decode_state *d = h->decode;
     if (!d || h->world > 1) return 0;
-    int rc = decode_enqueue_step(h, d, hvec);
+    int rc = decode_enqueue_step(h, d, hvec, pos);
     if (rc < 0) return rc;
     if (argmax_rows_enqueue(h, d->logits, d->cfg.vocab, d->cfg.vocab, 1, h->stream) < 0) return -1;
     CU_TRY(h, cudaMemcpyAsync(h->am_pin, h->am_idx, 4, cudaMemcpyDeviceToHost, h->stream));

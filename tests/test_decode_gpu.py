@@ -102,3 +102,72 @@ def test_decode_step_matches_oracle_chain(pkg, orc, synth, int8, chain_kernel, m
         assert acc.configure_decode(hidden, qdim // 128, ffn, vocab, n_layers + 1) is False
     finally:
         acc.close()
+
+
+def oracle_chain_attn(orc, W, h0, n_layers, eps, kc, vc, pos, n_heads, n_kv, hd, base, int8=False):
+    """qwen3.rs:818-899 for one token at `pos`; kc / vc: per-layer python lists that grow by one row."""
+    def mm(name, x):
+        w, ty, k, n = W[name]
+        if int8:
+            xq, xd, _ = orc.xquant8(x)
+            return orc.idot_gemm(w, ty, xq, xd, 1, k, n)[0]
+        return orc.qmatmul(x, w, ty, k, n)
+
+    h = h0.astype(np.float32).copy()
+    for il in range(n_layers):
+        b = "blk.%d." % il
+        n_ = orc.rmsnorm(h, W[b + "attn_norm.weight"], eps)
+        q, k, v = mm(b + "attn_q.weight", n_), mm(b + "attn_k.weight", n_), mm(b + "attn_v.weight", n_)
+        a = orc.attention_token(q, k, v, W.get(b + "attn_q_norm.weight"), W.get(b + "attn_k_norm.weight"), pos,
+                                kc[il], vc[il], n_heads, n_kv, hd, eps, base)
+        h = (h + mm(b + "attn_output.weight", a)).astype(np.float32)
+        n_ = orc.rmsnorm(h, W[b + "ffn_norm.weight"], eps)
+        g, u = mm(b + "ffn_gate.weight", n_), mm(b + "ffn_up.weight", n_)
+        h = (h + mm(b + "ffn_down.weight", orc.swiglu(g, u))).astype(np.float32)
+    return mm("output.weight", orc.rmsnorm(h, W["output_norm.weight"], eps))
+
+
+@pytest.mark.parametrize("qk_norm", [True, False])
+def test_decode_step_with_real_attention(pkg, orc, synth, qk_norm):
+    """Dense Qwen3 step: QK-norm, NEOX rope, KV cache, grouped-query softmax; several positions, the
+    last ones past one softmax split (256 cached tokens) so that the fold of two splits is exercised."""
+    hidden, hd, n_heads, n_kv, ffn, vocab, n_layers, eps, base = 256, 64, 6, 2, 512, 1000, 2, 1e-6, 1e6
+    qdim, kvdim, max_seq = n_heads * hd, n_kv * hd, 300
+    acc = pkg.CudaWeightAccel(0)
+    try:
+        W = build_model(acc, synth, hidden, qdim, kvdim, ffn, vocab, n_layers, seed=83)
+        if qk_norm:
+            for il in range(n_layers):
+                for nn in ("attn_q_norm.weight", "attn_k_norm.weight"):
+                    W["blk.%d.%s" % (il, nn)] = synth.norm_weight(83, "blk.%d.%s" % (il, nn), hd)
+                    acc.upload_f32("blk.%d.%s" % (il, nn), W["blk.%d.%s" % (il, nn)])
+        kw = dict(eps=eps, act=pkg.ACT_F32, attn_standin_q=False, head_dim=hd, n_kv=n_kv, rope_theta=base,
+                  max_seq=max_seq, qk_norm=qk_norm)
+        # declined: sliding-window layer, shared K = V, GPT-J style rope, a head size that does not match the weights
+        assert acc.configure_decode(hidden, n_heads, ffn, vocab, n_layers, layer_overrides={1: {"is_local": 1}}, **kw) is False
+        assert acc.configure_decode(hidden, n_heads, ffn, vocab, n_layers, layer_overrides={0: {"k_eq_v": 1}}, **kw) is False
+        assert acc.configure_decode(hidden, n_heads, ffn, vocab, n_layers, layer_overrides={0: {"rope_norm": 1}}, **kw) is False
+        assert acc.configure_decode(hidden, n_heads, ffn, vocab, n_layers, **dict(kw, head_dim=32)) is False
+        assert acc.configure_decode(hidden, n_heads, ffn, vocab, n_layers, **kw)
+        kc, vc = [[] for _ in range(n_layers)], [[] for _ in range(n_layers)]
+        worst = 0.0
+        n_tok = 262
+        for pos in range(n_tok):
+            h0 = synth.normal(84, "h.%d" % pos, hidden)
+            got = acc.decode_step(h0, pos)
+            # the oracle's own cache must grow at every position; compare at a few
+            want = oracle_chain_attn(orc, W, h0, n_layers, eps, kc, vc, pos, n_heads, n_kv, hd, base)
+            if pos < 4 or pos in (17, 100, 255, 256, 257, n_tok - 1):
+                r = rel_l2(got, want)
+                worst = max(worst, r)
+                assert r <= REL_L2_TOL, (pos, r)
+        print("real attention qk_norm=%s: worst rel-L2 over checked positions %.2e" % (qk_norm, worst))
+        # a position is re-playable: same input, same position, same cache rows below it -> same bits
+        h0 = synth.normal(84, "h.%d" % (n_tok - 1), hidden)
+        np.testing.assert_array_equal(acc.decode_step(h0, n_tok - 1), got)
+        assert acc.decode_step_argmax(h0, n_tok - 1) == orc.argmax_f32(got)
+        with pytest.raises(pkg.StrixCudaError, match="beyond max_seq"):
+            acc.decode_step(h0, max_seq)
+        assert acc.device_status() == 0
+    finally:
+        acc.close()

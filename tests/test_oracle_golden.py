@@ -271,3 +271,27 @@ def test_q4_1_integer_dot_follows_q4_1_gemv_dp(orc, synth):
     # and close to the f32-activation path (activation quantisation error only)
     yf = orc.qmatmul(x, w, synth.Q4_1, in_dim, out_dim)
     assert np.linalg.norm(y[0] - yf) / np.linalg.norm(yf) < 2e-2
+
+
+def test_attention_pieces_known_answers(orc):
+    # rope_neox (qwen3.rs:126-138) at pos 0 is the identity; at pos p pair k is rotated by p * base^(-2k/n)
+    v = np.arange(1, 9, dtype=np.float32)
+    np.testing.assert_array_equal(orc.rope_neox(v, 0, 8, 10000.0), v)
+    r = orc.rope_neox(v, 3, 8, 10000.0)
+    for k in range(4):
+        th = 3.0 * 10000.0 ** (-2.0 * k / 8)
+        assert abs(r[k] - (v[k] * np.cos(th) - v[k + 4] * np.sin(th))) < 1e-5
+        assert abs(r[k + 4] - (v[k] * np.sin(th) + v[k + 4] * np.cos(th))) < 1e-5
+    # rmsnorm_inplace (qwen3.rs:117-124)
+    x = np.array([3.0, 4.0], dtype=np.float32)
+    np.testing.assert_allclose(orc.rmsnorm_inplace(x, np.array([1.0, 2.0], np.float32), 0.0),
+                               [3.0 / np.sqrt(12.5), 8.0 / np.sqrt(12.5)], rtol=1e-6)
+    # one head, two cached tokens, no norm, hd = 2: softmax over two scores, checked by hand in f64
+    kc, vc = [], []
+    a0 = orc.attention_token([1.0, 0.0], [1.0, 0.0], [5.0, 7.0], None, None, 0, kc, vc, 1, 1, 2, 1e-6, 10000.0)
+    np.testing.assert_allclose(a0, [5.0, 7.0], rtol=1e-6)          # one token: its own value
+    a1 = orc.attention_token([1.0, 0.0], [0.0, 0.0], [1.0, 1.0], None, None, 1, kc, vc, 1, 1, 2, 1e-6, 10000.0)
+    q = np.array([np.cos(1.0), np.sin(1.0)])                        # rope at pos 1, pair (0, 1), theta = 1
+    s = np.array([q @ np.array([1.0, 0.0]), 0.0]) / np.sqrt(2.0)
+    w = np.exp(s - s.max()); w /= w.sum()
+    np.testing.assert_allclose(a1, w[0] * np.array([5.0, 7.0]) + w[1] * np.array([1.0, 1.0]), rtol=1e-5)
