@@ -247,6 +247,23 @@ STRIX_API int strix_cuda_lm_head_argmax_rows(strix_cuda *h, const char *key, con
  * d_ids[rows] / d_vals[rows] (either may be null) are device pointers. No sync. */
 STRIX_API int strix_cuda_argmax_dev(strix_cuda *h, const float *d_x, size_t n, size_t stride, size_t rows,
                                     uint32_t *d_ids, float *d_vals, void *stream);
+/* WeightAccel::prefill (accel.rs:464-473; decode.rs:5555-6394): m tokens hs[m][hidden] at positions
+ * start_pos .. start_pos + m - 1 in ONE pass over the weights per projection (the rows ride through the
+ * batched GEMV as extra tensor-core columns), causal attention row after row, KV cache filled for those
+ * positions; logits[vocab] of the LAST token. 0 = not configured, m == 0 or m > strix_cuda_prefill_max
+ * (the caller chunks, as with the reference's M_CHUNK). */
+STRIX_API int strix_cuda_prefill(strix_cuda *h, const float *hs, size_t start_pos, size_t m, float *logits,
+                                 size_t logits_cap);
+/* WeightAccel::verify (accel.rs:500-506; decode.rs:5548-5553): the same, logits[m][vocab] of ALL tokens
+ * (speculative-decoding verify of gamma + 1 rows). */
+STRIX_API int strix_cuda_verify(strix_cuda *h, const float *hs, size_t start_pos, size_t m, float *logits,
+                                size_t logits_cap);
+/* WeightAccel::prefill_max (accel.rs:475-479): tokens one prefill / verify call accepts (8), 0 = no decode configured. */
+STRIX_API size_t strix_cuda_prefill_max(strix_cuda *h);
+/* WeightAccel::seed_decode_kv (accel.rs:421-427): fill cache rows 0 .. tokens-1 of layer il from a prefill
+ * done elsewhere (k normed and roped, v raw, token-major [tokens][n_kv * head_dim]). 0 = no real-attention
+ * configuration, il or tokens out of range. */
+STRIX_API int strix_cuda_seed_decode_kv(strix_cuda *h, size_t il, const float *k, const float *v, size_t tokens);
 /* The same chain on device pointers (d_h is updated in place), enqueued on `stream`; no copy, no sync. */
 STRIX_API int strix_cuda_decode_chain_dev(strix_cuda *h, float *d_h, float *d_logits, void *stream);
 

@@ -102,6 +102,10 @@ def load_library():
     sig("strix_cuda_decode_step", C.c_int, H, f32p, sz, f32p, sz)
     sig("strix_cuda_decode_chain_dev", C.c_int, H, C.c_void_p, C.c_void_p, C.c_void_p)
     sig("strix_cuda_decode_step_argmax", C.c_int, H, f32p, sz, C.POINTER(C.c_uint32))
+    sig("strix_cuda_prefill", C.c_int, H, f32p, sz, sz, f32p, sz)
+    sig("strix_cuda_verify", C.c_int, H, f32p, sz, sz, f32p, sz)
+    sig("strix_cuda_prefill_max", sz, H)
+    sig("strix_cuda_seed_decode_kv", C.c_int, H, sz, f32p, f32p, sz)
     sig("strix_cuda_lm_head_argmax_rows", C.c_int, H, C.c_char_p, f32p, sz, sz, C.c_int, C.POINTER(C.c_uint32), f32p)
     sig("strix_cuda_argmax_dev", C.c_int, H, C.c_void_p, sz, sz, sz, C.c_void_p, C.c_void_p, C.c_void_p)
     sig("strix_cuda_gemv_rows", C.c_int, H, C.c_char_p, f32p, sz, f32p, sz, C.c_int)
@@ -313,6 +317,7 @@ class CudaWeightAccel:
                        attn_standin_q=int(attn_standin_q), act=act)
         rc = self._check(self._L.strix_cuda_configure_decode(self._h, C.byref(c)))
         self._vocab = vocab if rc == 1 else None
+        self._kvdim = head_dim * n_kv if (rc == 1 and not attn_standin_q) else 0
         return rc == 1
 
     def decode_step(self, h, pos=0):
@@ -323,6 +328,34 @@ class CudaWeightAccel:
         out = np.empty(self._vocab, dtype=np.float32)
         rc = self._check(self._L.strix_cuda_decode_step(self._h, _fp(ha), pos, _fp(out), out.size))
         return out if rc == 1 else None
+
+    def prefill(self, hs, start_pos, m):
+        """Logits of the last of m tokens, KV cache filled for start_pos .. start_pos+m-1, or None (accel.rs:464-473)."""
+        if not getattr(self, "_vocab", None):
+            return None
+        ha = _f32(hs)
+        out = np.empty(self._vocab, dtype=np.float32)
+        rc = self._check(self._L.strix_cuda_prefill(self._h, _fp(ha), start_pos, m, _fp(out), out.size))
+        return out if rc == 1 else None
+
+    def verify(self, hs, start_pos, m):
+        """Logits [m][vocab] of all m tokens, or None (accel.rs:500-506)."""
+        if not getattr(self, "_vocab", None):
+            return None
+        ha = _f32(hs)
+        out = np.empty((max(m, 1), self._vocab), dtype=np.float32)
+        rc = self._check(self._L.strix_cuda_verify(self._h, _fp(ha), start_pos, m, _fp(out), out.size))
+        return out[:m] if rc == 1 else None
+
+    def prefill_max(self):
+        return int(self._L.strix_cuda_prefill_max(self._h))
+
+    def seed_decode_kv(self, il, k, v):
+        ka, va = _f32(k), _f32(v)
+        kvdim = getattr(self, "_kvdim", 0)
+        if not kvdim or ka.size != va.size or ka.size % kvdim:
+            return False
+        return self._check(self._L.strix_cuda_seed_decode_kv(self._h, il, _fp(ka), _fp(va), ka.size // kvdim)) == 1
 
     def decode_step_argmax(self, h, pos=0):
         """Greedy token id of one decode step, argmax on the device, or None (accel.rs:437-442)."""

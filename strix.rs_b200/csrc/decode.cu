@@ -69,6 +69,12 @@ struct strix_decode_state {
     uint32_t hd = 0, n_kv = 0;
     float *kc = nullptr, *vc = nullptr, *att_part = nullptr, *attn = nullptr;
     uint32_t *d_pos = nullptr, *pin_pos = nullptr;
+    // batched rows (prefill / verify, up to ROWS_MAX tokens per call): [m][dim] activations, [m] positions
+    float *r_h = nullptr, *r_q = nullptr, *r_k = nullptr, *r_v = nullptr, *r_attn = nullptr, *r_gate = nullptr,
+          *r_up = nullptr, *r_logits = nullptr;
+    uint32_t *r_pos = nullptr;
+    void *r_pin_in = nullptr, *r_pin_out = nullptr;
+    size_t qdim = 0, kvdim = 0;
     // chain-kernel programs, one per (h, logits) buffer pair
     struct Program {
         const float *h;
@@ -88,6 +94,11 @@ static void decode_free(strix_decode_state *d) {
     if (!d) return;
     for (float *p : {d->h, d->q, d->k, d->v, d->gate, d->up, d->logits, d->kc, d->vc, d->att_part, d->attn})
         if (p) cudaFree(p);
+    for (float *p : {d->r_h, d->r_q, d->r_k, d->r_v, d->r_attn, d->r_gate, d->r_up, d->r_logits})
+        if (p) cudaFree(p);
+    if (d->r_pos) cudaFree(d->r_pos);
+    if (d->r_pin_in) cudaFreeHost(d->r_pin_in);
+    if (d->r_pin_out) cudaFreeHost(d->r_pin_out);
     if (d->d_pos) cudaFree(d->d_pos);
     if (d->pin_pos) cudaFreeHost(d->pin_pos);
     if (d->pin_h) cudaFreeHost(d->pin_h);
@@ -357,7 +368,164 @@ int strix_cuda_configure_decode(strix_cuda *h, const strix_gpu_decode_config *cf
         decode_free(d);
         return -1;
     }
+    d->qdim = qdim;
+    d->kvdim = kvdim;
     h->decode = d;
+    return 1;
+}
+
+}  // extern "C"
+
+// Tokens per prefill / verify call: what one batched-GEMV pass carries (the speculative-verify sizes,
+// gamma + 1 <= 8; generate.rs:604-607, 850-853). Longer prompts are chunked by the caller (prefill_max).
+static constexpr size_t ROWS_MAX = 8;
+
+static int rows_alloc(strix_cuda *h, strix_decode_state *d) {
+    if (d->r_h) return 0;
+    cudaError_t e = cudaSuccess;
+    auto alloc = [&](float **p, size_t n) {
+        if (e == cudaSuccess) e = cudaMalloc(p, ROWS_MAX * std::max<size_t>(n, 4) * sizeof(float));
+    };
+    alloc(&d->r_h, d->cfg.hidden);
+    alloc(&d->r_q, d->qdim);
+    alloc(&d->r_k, d->kvdim);
+    alloc(&d->r_v, d->kvdim);
+    alloc(&d->r_attn, d->qdim);
+    alloc(&d->r_gate, d->cfg.ffn);
+    alloc(&d->r_up, d->cfg.ffn);
+    alloc(&d->r_logits, d->cfg.vocab);
+    if (e == cudaSuccess) e = cudaMalloc(&d->r_pos, ROWS_MAX * 4);
+    if (e == cudaSuccess) e = cudaMallocHost(&d->r_pin_in, ROWS_MAX * (d->cfg.hidden * sizeof(float) + 4));
+    if (e == cudaSuccess) e = cudaMallocHost(&d->r_pin_out, ROWS_MAX * (size_t)d->cfg.vocab * sizeof(float));
+    if (e != cudaSuccess) {
+        h->err = std::string("prefill scratch: ") + cudaGetErrorString(e);
+        return -1;
+    }
+    return 0;
+}
+
+// m tokens (rows) through the chain in one pass over the weights per step: the batched GEMV carries
+// the rows as extra MMA columns; attention runs row after row (row t sees the cache rows the rows
+// before it have just written: causal). all_logits: the head for every row, else for the last one.
+static int rows_run(strix_cuda *h, strix_decode_state *d, const float *hs, size_t start_pos, size_t m, bool all_logits,
+                    float *out, size_t out_cap, const char *who) {
+    if (m == 0 || m > ROWS_MAX) return 0;  // the caller chunks (the reference's `m > M_CHUNK -> None`, decode.rs:5559)
+    const size_t hidden = d->cfg.hidden, vocab = d->cfg.vocab, n_out = all_logits ? m : 1;
+    if (out_cap < n_out * vocab) {
+        h->err = std::string(who) + ": logits buffer too small";
+        return -1;
+    }
+    if (d->real_attn && start_pos + m > d->cfg.max_seq) {
+        h->err = std::string(who) + ": positions up to " + std::to_string(start_pos + m - 1) + " beyond max_seq " +
+                 std::to_string(d->cfg.max_seq);
+        return -1;
+    }
+    CU_TRY(h, cudaSetDevice(h->device));
+    if (rows_alloc(h, d) < 0) return -1;
+    cudaStream_t s = h->stream;
+    float *pin = static_cast<float *>(d->r_pin_in);
+    uint32_t *pin_pos = reinterpret_cast<uint32_t *>(pin + ROWS_MAX * hidden);
+    memcpy(pin, hs, m * hidden * sizeof(float));
+    for (size_t t = 0; t < m; t++) pin_pos[t] = (uint32_t)(start_pos + t);
+    CU_TRY(h, cudaMemcpyAsync(d->r_h, pin, m * hidden * sizeof(float), cudaMemcpyHostToDevice, s));
+    CU_TRY(h, cudaMemcpyAsync(d->r_pos, pin_pos, m * 4, cudaMemcpyHostToDevice, s));
+    const int act = d->cfg.act;
+    const float eps = d->cfg.eps;
+    const int gate_pre = d->cfg.act_gelu ? STRIX_PRE_GEGLU : STRIX_PRE_SWIGLU;
+    const uint32_t b = (uint32_t)m, ffn = d->cfg.ffn;
+    for (size_t il = 0; il < d->layers.size(); il++) {
+        auto &L = d->layers[il];
+        {
+            const Resident *w[3] = {L.q, L.k, L.v};
+            float *y[3] = {d->r_q, d->r_k, d->r_v};
+            if (gemv_launch_rows(h, 3, w, d->r_h, L.attn_norm, eps, STRIX_PRE_RMSNORM, act, y, nullptr, b, (uint32_t)hidden, 0, s) < 0)
+                return -1;
+        }
+        const float *a = d->r_q;  // the stand-in feeds Wo with q
+        if (d->real_attn) {
+            const size_t per_layer = (size_t)d->cfg.max_seq * d->n_kv * d->hd;
+            for (size_t t = 0; t < m; t++) {
+                const cudaError_t e = launch_attention_step(
+                    d->r_q + t * d->qdim, d->r_k + t * d->kvdim, d->r_v + t * d->kvdim, L.q_norm, L.k_norm,
+                    d->kc + il * per_layer, d->vc + il * per_layer, d->att_part, d->r_attn + t * d->qdim, d->r_pos + t,
+                    d->cfg.n_heads, d->n_kv, d->hd, eps, L.theta_scale, 1.0f / sqrtf((float)d->hd), d->cfg.max_seq,
+                    h->d_status, s);
+                if (e != cudaSuccess) {
+                    h->err = std::string("attention: ") + cudaGetErrorString(e);
+                    return -1;
+                }
+            }
+            a = d->r_attn;
+        }
+        {
+            const Resident *w[1] = {L.o};
+            float *y[1] = {d->r_h};
+            const float *r[1] = {d->r_h};
+            if (gemv_launch_rows(h, 1, w, a, nullptr, 0.f, STRIX_PRE_NONE, act, y, r, b, (uint32_t)d->qdim, 0, s) < 0) return -1;
+        }
+        {
+            const Resident *w[2] = {L.gate, L.up};
+            float *y[2] = {d->r_gate, d->r_up};
+            if (gemv_launch_rows(h, 2, w, d->r_h, L.ffn_norm, eps, STRIX_PRE_RMSNORM, act, y, nullptr, b, (uint32_t)hidden, 0, s) < 0)
+                return -1;
+        }
+        {
+            const Resident *w[1] = {L.down};
+            float *y[1] = {d->r_h};
+            const float *r[1] = {d->r_h};
+            if (gemv_launch_rows(h, 1, w, d->r_gate, d->r_up, 0.f, gate_pre, act, y, r, b, ffn, ffn, s) < 0) return -1;
+        }
+    }
+    {
+        const Resident *w[1] = {d->head};
+        float *y[1] = {d->r_logits};
+        const float *x = all_logits ? d->r_h : d->r_h + (m - 1) * hidden;
+        if (gemv_launch_rows(h, 1, w, x, d->out_norm, eps, STRIX_PRE_RMSNORM, act, y, nullptr, (uint32_t)n_out, (uint32_t)hidden, 0, s) < 0)
+            return -1;
+    }
+    CU_TRY(h, cudaMemcpyAsync(d->r_pin_out, d->r_logits, n_out * vocab * sizeof(float), cudaMemcpyDeviceToHost, s));
+    CU_TRY(h, cudaMemcpyAsync(&h->status_host, h->d_status, 4, cudaMemcpyDeviceToHost, s));
+    CU_TRY(h, cudaStreamSynchronize(s));
+    if (h->status_host != 0) {
+        h->err = std::string(who) + ": device status " + std::to_string(h->status_host);
+        cudaMemsetAsync(h->d_status, 0, 4, s);
+        return -2;
+    }
+    memcpy(out, d->r_pin_out, n_out * vocab * sizeof(float));
+    return 1;
+}
+
+extern "C" {
+
+// WeightAccel::prefill (accel.rs:464-473; decode.rs:5555-6394): logits of the LAST of m tokens.
+int strix_cuda_prefill(strix_cuda *h, const float *hs, size_t start_pos, size_t m, float *logits, size_t logits_cap) {
+    if (!h || !hs || !logits) return -1;
+    h->err.clear();
+    if (!h->decode) return 0;
+    return rows_run(h, h->decode, hs, start_pos, m, false, logits, logits_cap, "prefill");
+}
+// WeightAccel::verify (accel.rs:500-506; decode.rs:5548-5553): logits of ALL m tokens, token-major.
+int strix_cuda_verify(strix_cuda *h, const float *hs, size_t start_pos, size_t m, float *logits, size_t logits_cap) {
+    if (!h || !hs || !logits) return -1;
+    h->err.clear();
+    if (!h->decode) return 0;
+    return rows_run(h, h->decode, hs, start_pos, m, true, logits, logits_cap, "verify");
+}
+// WeightAccel::prefill_max (accel.rs:475-479): 0 = prefill unsupported (no decode configured).
+size_t strix_cuda_prefill_max(strix_cuda *h) { return (h && h->decode) ? ROWS_MAX : 0; }
+
+// WeightAccel::seed_decode_kv (accel.rs:421-427): cache rows 0 .. tokens-1 of layer il from a prefill done
+// elsewhere: k already normed and roped, v raw, token-major [tokens][n_kv * head_dim].
+int strix_cuda_seed_decode_kv(strix_cuda *h, size_t il, const float *k, const float *v, size_t tokens) {
+    if (!h || !k || !v) return -1;
+    h->err.clear();
+    strix_decode_state *d = h->decode;
+    if (!d || !d->real_attn || il >= d->layers.size() || tokens > d->cfg.max_seq) return 0;
+    CU_TRY(h, cudaSetDevice(h->device));
+    const size_t per_layer = (size_t)d->cfg.max_seq * d->kvdim, n = tokens * d->kvdim * sizeof(float);
+    CU_TRY(h, cudaMemcpyAsync(d->kc + il * per_layer, k, n, cudaMemcpyHostToDevice, h->stream));
+    CU_TRY(h, cudaMemcpyAsync(d->vc + il * per_layer, v, n, cudaMemcpyHostToDevice, h->stream));
+    CU_TRY(h, cudaStreamSynchronize(h->stream));  // k and v are borrowed for the call
     return 1;
 }
 

@@ -171,3 +171,76 @@ def test_decode_step_with_real_attention(pkg, orc, synth, qk_norm):
         assert acc.device_status() == 0
     finally:
         acc.close()
+
+
+@pytest.mark.parametrize("int8", [False, True])
+def test_prefill_verify_and_seeded_cache(pkg, orc, synth, int8):
+    """prefill / verify push m tokens through the chain in one pass over the weights (batched GEMV rows,
+    causal attention row after row); the cache they leave behind is the one token-at-a-time decoding
+    would have built, and seed_decode_kv can install the same rows from outside."""
+    hidden, hd, n_heads, n_kv, ffn, vocab, n_layers, eps, base = 256, 64, 4, 2, 512, 700, 2, 1e-6, 1e4
+    qdim, kvdim, max_seq = n_heads * hd, n_kv * hd, 64
+    act = pkg.ACT_Q8DOT if int8 else pkg.ACT_F32
+    tol = 5e-2 if int8 else REL_L2_TOL      # int8: re-quantisation noise along the chain (see the chain test above)
+    acc = pkg.CudaWeightAccel(0)
+    try:
+        assert acc.prefill_max() == 0                                   # nothing configured
+        W = build_model(acc, synth, hidden, qdim, kvdim, ffn, vocab, n_layers, seed=85)
+        for il in range(n_layers):
+            for nn in ("attn_q_norm.weight", "attn_k_norm.weight"):
+                W["blk.%d.%s" % (il, nn)] = synth.norm_weight(85, "blk.%d.%s" % (il, nn), hd)
+                acc.upload_f32("blk.%d.%s" % (il, nn), W["blk.%d.%s" % (il, nn)])
+        assert acc.configure_decode(hidden, n_heads, ffn, vocab, n_layers, eps=eps, act=act, attn_standin_q=False,
+                                    head_dim=hd, n_kv=n_kv, rope_theta=base, max_seq=max_seq)
+        assert acc.prefill_max() == 8
+        hs = synth.normal(86, "hs", 13 * hidden).reshape(13, hidden)
+        kc, vc = [[] for _ in range(n_layers)], [[] for _ in range(n_layers)]
+        want = [oracle_chain_attn(orc, W, hs[t], n_layers, eps, kc, vc, t, n_heads, n_kv, hd, base, int8=int8)
+                for t in range(13)]
+        # prompt of 5 tokens: prefill returns the last token's logits
+        got = acc.prefill(hs[:5], 0, 5)
+        assert rel_l2(got, want[4]) <= tol
+        # speculative verify of 4 rows at positions 5..8: all logits
+        gv = acc.verify(hs[5:9], 5, 4)
+        assert gv.shape == (4, vocab)
+        for t in range(4):
+            assert rel_l2(gv[t], want[5 + t]) <= tol, t
+        # rejected draft: positions 7, 8 are decoded again one at a time over the same cache rows
+        for t in (7, 8, 9):
+            assert rel_l2(acc.decode_step(hs[t], t), want[t]) <= tol
+        # a full chunk of 8 rows re-verifies positions 2..9 (rows are rewritten with the same values)
+        g8 = acc.verify(hs[2:10], 2, 8)
+        for t in range(8):
+            assert rel_l2(g8[t], want[2 + t]) <= tol
+        # guards: more than prefill_max rows / zero rows -> None; positions past the cache -> error
+        assert acc.verify(hs[:9], 0, 9) is None and acc.prefill(hs[:1], 0, 0) is None
+        with pytest.raises(pkg.StrixCudaError, match="beyond max_seq"):
+            acc.verify(hs[:4], max_seq - 2, 4)
+        # a cache seeded from outside (the oracle's rows 0..9) continues identically at position 10
+        assert acc.configure_decode(hidden, n_heads, ffn, vocab, n_layers, eps=eps, act=act, attn_standin_q=False,
+                                    head_dim=hd, n_kv=n_kv, rope_theta=base, max_seq=max_seq)
+        for il in range(n_layers):
+            assert acc.seed_decode_kv(il, np.stack(kc[il][:10]), np.stack(vc[il][:10]))
+        assert acc.seed_decode_kv(n_layers, np.zeros(kvdim, np.float32), np.zeros(kvdim, np.float32)) is False
+        for t in (10, 11, 12):
+            assert rel_l2(acc.decode_step(hs[t], t), want[t]) <= tol
+        assert acc.device_status() == 0
+    finally:
+        acc.close()
+
+
+def test_verify_rows_with_the_attention_standin(pkg, orc, synth):
+    """Without real attention (the benchmark's projection chain) verify rows are independent of one another."""
+    hidden, qdim, kvdim, ffn, vocab, n_layers, eps = 512, 768, 256, 1536, 900, 2, 1e-6
+    acc = pkg.CudaWeightAccel(0)
+    try:
+        W = build_model(acc, synth, hidden, qdim, kvdim, ffn, vocab, n_layers, seed=87)
+        assert acc.configure_decode(hidden, qdim // 128, ffn, vocab, n_layers, eps=eps, act=pkg.ACT_F32)
+        hs = synth.normal(88, "hs", 6 * hidden).reshape(6, hidden)
+        gv = acc.verify(hs, 0, 6)
+        for t in range(6):
+            assert rel_l2(gv[t], oracle_chain(orc, W, hs[t], n_layers, eps, False)) <= REL_L2_TOL
+        assert rel_l2(acc.prefill(hs, 0, 6), oracle_chain(orc, W, hs[5], n_layers, eps, False)) <= REL_L2_TOL
+        assert acc.seed_decode_kv(0, np.zeros(kvdim, np.float32), np.zeros(kvdim, np.float32)) is False
+    finally:
+        acc.close()
