@@ -207,6 +207,36 @@ def decode_chain_extra(pkg, synth, torch, device, stream):
                          "ms_per_token_e2e_argmax": round(e2e_argmax_ms, 4),
                          "gbs": round(nbytes / dev_ms / 1e6, 1), "launches_per_token": 4 * n_layers + 1}
         out["bytes_per_token"] = nbytes
+        # the same model as a real token step: QK-norm, NEOX rope, KV cache (32 heads, 8 KV heads of 128),
+        # grouped-query softmax over the cache; the cache is seeded with random rows up to each position
+        hd, n_kv, max_seq = 128, 8, 4096
+        for il in range(n_layers):
+            for nn in ("attn_q_norm", "attn_k_norm"):
+                acc.upload_f32("blk.%d.%s.weight" % (il, nn), synth.norm_weight(3, "dc.%d.%s" % (il, nn), hd))
+        if acc.configure_decode(hidden, 32, ffn, vocab, n_layers, eps=1e-6, act=pkg.ACT_Q8DOT, attn_standin_q=False,
+                                head_dim=hd, n_kv=n_kv, rope_theta=1e6, max_seq=max_seq):
+            real = []
+            rows = synth.normal(3, "dc.kv", max_seq * kvdim).reshape(max_seq, kvdim)
+            for il in range(n_layers):
+                acc.seed_decode_kv(il, rows, rows)
+            for pos in (0, 1024, max_seq - 1):
+                for _ in range(3):
+                    acc.decode_step_argmax(h0, pos)
+                t0 = time.perf_counter()
+                for _ in range(reps):
+                    acc.decode_step_argmax(h0, pos)
+                real.append({"pos": pos, "ms_per_token_e2e": round((time.perf_counter() - t0) / reps * 1e3, 4)})
+            # speculative verify through the same model: 5 rows (gamma + 1) in one pass over the weights
+            hs = synth.normal(3, "dc.hs", 5 * hidden)
+            for _ in range(2):
+                acc.verify(hs, 1024, 5)
+            t0 = time.perf_counter()
+            for _ in range(5):
+                acc.verify(hs, 1024, 5)
+            out["real_attention"] = {"q8dot_decode_step_argmax": real,
+                                     "verify_5_rows_at_1024_ms": round((time.perf_counter() - t0) / 5 * 1e3, 4),
+                                     "note": "whole token step through the host API (H2D of h, graph replay, "
+                                             "argmax on the device, 4 bytes back); KV cache f32, 36 layers x 4096 rows"}
         out["note"] = "projection chain only; attention replaced by feeding Wo with q (no KV cache)"
     finally:
         acc.close()

@@ -6,7 +6,7 @@
 // (crates/strix-backend-cpu/src/qwen3.rs:117-138 rmsnorm_inplace / rope_neox, :823-873 the step).
 //
 // Everything a CUDA graph replays unchanged: the position is read from a device word, and the
-// softmax runs as a fixed grid of (head, split) blocks (flash-decoding: every split of 256 cached
+// softmax runs as a fixed grid of (head, split) blocks (flash-decoding: every split of 64 cached
 // tokens keeps its own maximum, sum and weighted value sum; a second kernel folds them). Splits
 // past the current length write an empty partial and leave.
 #include <cuda_runtime.h>
@@ -17,7 +17,7 @@
 
 namespace strix {
 
-constexpr uint32_t ATT_SPLIT = 256;  // cached tokens per softmax split
+constexpr uint32_t ATT_SPLIT = ATT_SPLIT_TOKENS;  // cached tokens per softmax split
 constexpr uint32_t ATT_THREADS = 256;
 
 // grid = n_heads + 2 n_kv blocks of 128 threads: blocks [0, n_heads) treat a q head in place,
@@ -85,11 +85,13 @@ __global__ void __launch_bounds__(128) qk_post_kernel(float *__restrict__ q, con
 }
 
 // grid = (n_heads, max_splits), 256 threads. part: [n_heads][max_splits][hd + 2] = {max, sum, out[hd]}.
+// A split is short (64 cached tokens) so that a long context spreads over many SMs: the work per
+// token is a few hundred bytes and its latency, not its bandwidth, is what a block waits for.
 __global__ void __launch_bounds__(ATT_THREADS) sdpa_split_kernel(const float *__restrict__ q, const float *__restrict__ kc,
                                                                  const float *__restrict__ vc, float *__restrict__ part,
                                                                  const uint32_t *__restrict__ d_pos, uint32_t n_heads,
                                                                  uint32_t n_kv, uint32_t hd, float scale, uint32_t max_seq) {
-    __shared__ float qs[256], sc[ATT_SPLIT], red[ATT_THREADS / 32];
+    __shared__ float qs[256], sc[ATT_SPLIT], red[ATT_THREADS / 32], vsum[ATT_THREADS];
     const uint32_t hh = blockIdx.x, sp = blockIdx.y, t = threadIdx.x, lane = t & 31u, warp = t >> 5;
     const uint32_t len = min(*d_pos + 1u, max_seq);
     float *my = part + ((size_t)hh * gridDim.y + sp) * (hd + 2u);
@@ -104,13 +106,23 @@ __global__ void __launch_bounds__(ATT_THREADS) sdpa_split_kernel(const float *__
     const uint32_t n = min(ATT_SPLIT, len - t0), kvdim = n_kv * hd, kvh = hh / (n_heads / n_kv);
     for (uint32_t i = t; i < hd; i += ATT_THREADS) qs[i] = q[hh * hd + i];
     __syncthreads();
-    // scores: one warp per cached token
-    for (uint32_t j = warp; j < n; j += ATT_THREADS / 32) {
-        const float *kr = kc + (size_t)(t0 + j) * kvdim + kvh * hd;
-        float a = 0.f;
-        for (uint32_t i = lane; i < hd; i += 32) a = fmaf(qs[i], kr[i], a);
-        a = warp_sum(a);
-        if (lane == 0) sc[j] = a * scale;
+    // scores: a warp takes tokens warp, warp + 8, ...; four tokens per pass so that their loads overlap
+    constexpr uint32_t NW = ATT_THREADS / 32;
+    for (uint32_t j0 = warp; j0 < n; j0 += 4u * NW) {
+        float a[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+        for (uint32_t u = 0; u < 4; u++) {
+            const uint32_t j = j0 + u * NW;
+            if (j < n) {
+                const float *kr = kc + (size_t)(t0 + j) * kvdim + kvh * hd;
+                for (uint32_t i = lane; i < hd; i += 32) a[u] = fmaf(qs[i], kr[i], a[u]);
+            }
+        }
+#pragma unroll
+        for (uint32_t u = 0; u < 4; u++) {
+            const float r = warp_sum(a[u]);
+            if (lane == 0 && j0 + u * NW < n) sc[j0 + u * NW] = r * scale;
+        }
     }
     __syncthreads();
     float m = -3.0e38f;
@@ -120,7 +132,7 @@ __global__ void __launch_bounds__(ATT_THREADS) sdpa_split_kernel(const float *__
     if (lane == 0) red[warp] = m;
     __syncthreads();
     m = red[0];
-    for (uint32_t w2 = 1; w2 < ATT_THREADS / 32; w2++) m = fmaxf(m, red[w2]);
+    for (uint32_t w2 = 1; w2 < NW; w2++) m = fmaxf(m, red[w2]);
     __syncthreads();
     float l = 0.f;
     for (uint32_t j = t; j < n; j += ATT_THREADS) {
@@ -133,15 +145,34 @@ __global__ void __launch_bounds__(ATT_THREADS) sdpa_split_kernel(const float *__
     __syncthreads();
     if (t == 0) {
         float tot = 0.f;
-        for (uint32_t w2 = 0; w2 < ATT_THREADS / 32; w2++) tot += red[w2];
+        for (uint32_t w2 = 0; w2 < NW; w2++) tot += red[w2];
         my[0] = m;
         my[1] = tot;
     }
-    // weighted value sum: thread per output element, tokens in order (coalesced rows of the cache)
-    for (uint32_t i = t; i < hd; i += ATT_THREADS) {
-        float o = 0.f;
-        for (uint32_t j = 0; j < n; j++) o = fmaf(sc[j], vc[(size_t)(t0 + j) * kvdim + kvh * hd + i], o);
-        my[2u + i] = o;
+    // weighted value sum: the 256 threads form `parts` groups of hd; group p takes tokens p, p + parts, ...
+    // (rows of the cache are read coalesced), and the groups' sums meet in shared memory, in group order
+    const uint32_t parts = ATT_THREADS / hd;  // >= 1: hd <= 256
+    const uint32_t p = t / hd, i = t - p * hd;
+    float o = 0.f;
+    if (p < parts) {
+        const float *vr = vc + (size_t)t0 * kvdim + kvh * hd + i;
+        uint32_t j = p;
+        for (; j + 3u * parts < n; j += 4u * parts) {
+            const float v0 = vr[(size_t)j * kvdim], v1 = vr[(size_t)(j + parts) * kvdim];
+            const float v2 = vr[(size_t)(j + 2u * parts) * kvdim], v3 = vr[(size_t)(j + 3u * parts) * kvdim];
+            o = fmaf(sc[j], v0, o);
+            o = fmaf(sc[j + parts], v1, o);
+            o = fmaf(sc[j + 2u * parts], v2, o);
+            o = fmaf(sc[j + 3u * parts], v3, o);
+        }
+        for (; j < n; j += parts) o = fmaf(sc[j], vr[(size_t)j * kvdim], o);
+    }
+    vsum[t] = o;
+    __syncthreads();
+    if (t < hd) {
+        float tot = vsum[t];
+        for (uint32_t k2 = 1; k2 < parts; k2++) tot += vsum[k2 * hd + t];
+        my[2u + t] = tot;
     }
 }
 

@@ -130,7 +130,7 @@ def oracle_chain_attn(orc, W, h0, n_layers, eps, kc, vc, pos, n_heads, n_kv, hd,
 @pytest.mark.parametrize("qk_norm", [True, False])
 def test_decode_step_with_real_attention(pkg, orc, synth, qk_norm):
     """Dense Qwen3 step: QK-norm, NEOX rope, KV cache, grouped-query softmax; several positions, the
-    last ones past one softmax split (256 cached tokens) so that the fold of two splits is exercised."""
+    positions cross several softmax splits (64 cached tokens each) so that the fold of the splits is exercised."""
     hidden, hd, n_heads, n_kv, ffn, vocab, n_layers, eps, base = 256, 64, 6, 2, 512, 1000, 2, 1e-6, 1e6
     qdim, kvdim, max_seq = n_heads * hd, n_kv * hd, 300
     acc = pkg.CudaWeightAccel(0)
