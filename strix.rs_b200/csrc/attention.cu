@@ -30,7 +30,11 @@ __global__ void __launch_bounds__(128) qk_post_kernel(float *__restrict__ q, con
                                                       uint32_t n_heads, uint32_t n_kv, uint32_t hd, float eps,
                                                       float theta_scale, uint32_t max_seq, uint32_t *status) {
     __shared__ float xs[256], th[128], red[4];
-    const uint32_t b = blockIdx.x, t = threadIdx.x, pos = *d_pos, half = hd / 2;
+    // blockIdx.y = activation row (token) of a batched call: its own q / k / v vectors and position
+    q += (size_t)blockIdx.y * n_heads * hd;
+    k += (size_t)blockIdx.y * n_kv * hd;
+    v += (size_t)blockIdx.y * n_kv * hd;
+    const uint32_t b = blockIdx.x, t = threadIdx.x, pos = d_pos[blockIdx.y], half = hd / 2;
     if (pos >= max_seq) {  // the cache is full: report, touch nothing
         if (t == 0 && b == 0 && status) atomicOr(status, STATUS_BAD_ARGS);
         return;
@@ -92,9 +96,10 @@ __global__ void __launch_bounds__(ATT_THREADS) sdpa_split_kernel(const float *__
                                                                  const uint32_t *__restrict__ d_pos, uint32_t n_heads,
                                                                  uint32_t n_kv, uint32_t hd, float scale, uint32_t max_seq) {
     __shared__ float qs[256], sc[ATT_SPLIT], red[ATT_THREADS / 32], vsum[ATT_THREADS];
-    const uint32_t hh = blockIdx.x, sp = blockIdx.y, t = threadIdx.x, lane = t & 31u, warp = t >> 5;
-    const uint32_t len = min(*d_pos + 1u, max_seq);
-    float *my = part + ((size_t)hh * gridDim.y + sp) * (hd + 2u);
+    const uint32_t hh = blockIdx.x, sp = blockIdx.y, row = blockIdx.z, t = threadIdx.x, lane = t & 31u, warp = t >> 5;
+    const uint32_t len = min(d_pos[row] + 1u, max_seq);
+    q += (size_t)row * n_heads * hd;
+    float *my = part + (((size_t)row * n_heads + hh) * gridDim.y + sp) * (hd + 2u);
     const uint32_t t0 = sp * ATT_SPLIT;
     if (t0 >= len) {
         if (t == 0) {
@@ -179,9 +184,10 @@ __global__ void __launch_bounds__(ATT_THREADS) sdpa_split_kernel(const float *__
 // grid = n_heads, hd threads: fold the splits' partials into attn[n_heads * hd].
 __global__ void sdpa_fold_kernel(const float *__restrict__ part, float *__restrict__ attn, const uint32_t *__restrict__ d_pos,
                                  uint32_t hd, uint32_t max_splits, uint32_t max_seq) {
-    const uint32_t hh = blockIdx.x, i = threadIdx.x;
-    const uint32_t len = min(*d_pos + 1u, max_seq), ns = min(max_splits, (len + ATT_SPLIT - 1) / ATT_SPLIT);
-    const float *p = part + (size_t)hh * max_splits * (hd + 2u);
+    const uint32_t hh = blockIdx.x, row = blockIdx.y, i = threadIdx.x;
+    const uint32_t len = min(d_pos[row] + 1u, max_seq), ns = min(max_splits, (len + ATT_SPLIT - 1) / ATT_SPLIT);
+    const float *p = part + ((size_t)row * gridDim.x + hh) * max_splits * (hd + 2u);
+    attn += (size_t)row * gridDim.x * hd;
     float M = -3.0e38f;
     for (uint32_t s = 0; s < ns; s++) M = fmaxf(M, p[(size_t)s * (hd + 2u)]);
     float L = 0.f, o = 0.f;
@@ -197,14 +203,16 @@ __global__ void sdpa_fold_kernel(const float *__restrict__ part, float *__restri
 cudaError_t launch_attention_step(float *d_q, const float *d_k, const float *d_v, const float *d_q_norm,
                                   const float *d_k_norm, float *d_kc, float *d_vc, float *d_part, float *d_attn,
                                   const uint32_t *d_pos, uint32_t n_heads, uint32_t n_kv, uint32_t hd, float eps,
-                                  float theta_scale, float scale, uint32_t max_seq, uint32_t *d_status,
+                                  float theta_scale, float scale, uint32_t max_seq, uint32_t rows, uint32_t *d_status,
                                   cudaStream_t stream) {
     const uint32_t max_splits = (max_seq + ATT_SPLIT - 1) / ATT_SPLIT;
-    qk_post_kernel<<<n_heads + 2u * n_kv, 128, 0, stream>>>(d_q, d_k, d_v, d_q_norm, d_k_norm, d_kc, d_vc, d_pos, n_heads,
+    // all rows' keys and values enter the cache first; then every row attends to rows 0 .. its own position
+    // (causal: a later row's key is in the cache but beyond an earlier row's length)
+    qk_post_kernel<<<dim3(n_heads + 2u * n_kv, rows), 128, 0, stream>>>(d_q, d_k, d_v, d_q_norm, d_k_norm, d_kc, d_vc, d_pos, n_heads,
                                                              n_kv, hd, eps, theta_scale, max_seq, d_status);
-    sdpa_split_kernel<<<dim3(n_heads, max_splits), ATT_THREADS, 0, stream>>>(d_q, d_kc, d_vc, d_part, d_pos, n_heads, n_kv,
+    sdpa_split_kernel<<<dim3(n_heads, max_splits, rows), ATT_THREADS, 0, stream>>>(d_q, d_kc, d_vc, d_part, d_pos, n_heads, n_kv,
                                                                              hd, scale, max_seq);
-    sdpa_fold_kernel<<<n_heads, ((hd + 31u) / 32u) * 32u, 0, stream>>>(d_part, d_attn, d_pos, hd, max_splits, max_seq);
+    sdpa_fold_kernel<<<dim3(n_heads, rows), ((hd + 31u) / 32u) * 32u, 0, stream>>>(d_part, d_attn, d_pos, hd, max_splits, max_seq);
     return cudaGetLastError();
 }
 

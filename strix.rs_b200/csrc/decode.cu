@@ -247,7 +247,7 @@ static int enqueue_chain(strix_cuda *h, strix_decode_state *d, cudaStream_t s) {
         const cudaError_t e = launch_attention_step(
             d->q, d->k, d->v, L.q_norm, L.k_norm, d->kc + il * per_layer, d->vc + il * per_layer, d->att_part, d->attn,
             d->d_pos, d->cfg.n_heads, d->n_kv, d->hd, d->cfg.eps, L.theta_scale, 1.0f / sqrtf((float)d->hd),
-            d->cfg.max_seq, h->d_status, s);
+            d->cfg.max_seq, 1, h->d_status, s);
         if (e != cudaSuccess) {
             h->err = std::string("attention: ") + cudaGetErrorString(e);
             return nullptr;
@@ -355,7 +355,7 @@ int strix_cuda_configure_decode(strix_cuda *h, const strix_gpu_decode_config *cf
         const size_t splits = (cfg->max_seq + ATT_SPLIT_TOKENS - 1) / ATT_SPLIT_TOKENS;
         alloc(&d->kc, cache);
         alloc(&d->vc, cache);
-        alloc(&d->att_part, (size_t)cfg->n_heads * splits * (hd + 2));
+        alloc(&d->att_part, 8 * (size_t)cfg->n_heads * splits * (hd + 2));  // up to 8 rows per call (prefill / verify)
         alloc(&d->attn, qdim);
         if (e == cudaSuccess) e = cudaMalloc(&d->d_pos, 4);
         if (e == cudaSuccess) e = cudaMemset(d->d_pos, 0, 4);
@@ -405,8 +405,8 @@ static int rows_alloc(strix_cuda *h, strix_decode_state *d) {
 }
 
 // m tokens (rows) through the chain in one pass over the weights per step: the batched GEMV carries
-// the rows as extra MMA columns; attention runs row after row (row t sees the cache rows the rows
-// before it have just written: causal). all_logits: the head for every row, else for the last one.
+// the rows as extra MMA columns; attention takes all rows in one launch per kernel (their keys and values
+// enter the cache first, then row t attends to rows 0 .. its own position: causal). all_logits: the head for every row, else for the last one.
 static int rows_run(strix_cuda *h, strix_decode_state *d, const float *hs, size_t start_pos, size_t m, bool all_logits,
                     float *out, size_t out_cap, const char *who) {
     if (m == 0 || m > ROWS_MAX) return 0;  // the caller chunks (the reference's `m > M_CHUNK -> None`, decode.rs:5559)
@@ -444,16 +444,13 @@ static int rows_run(strix_cuda *h, strix_decode_state *d, const float *hs, size_
         const float *a = d->r_q;  // the stand-in feeds Wo with q
         if (d->real_attn) {
             const size_t per_layer = (size_t)d->cfg.max_seq * d->n_kv * d->hd;
-            for (size_t t = 0; t < m; t++) {
-                const cudaError_t e = launch_attention_step(
-                    d->r_q + t * d->qdim, d->r_k + t * d->kvdim, d->r_v + t * d->kvdim, L.q_norm, L.k_norm,
-                    d->kc + il * per_layer, d->vc + il * per_layer, d->att_part, d->r_attn + t * d->qdim, d->r_pos + t,
-                    d->cfg.n_heads, d->n_kv, d->hd, eps, L.theta_scale, 1.0f / sqrtf((float)d->hd), d->cfg.max_seq,
-                    h->d_status, s);
-                if (e != cudaSuccess) {
-                    h->err = std::string("attention: ") + cudaGetErrorString(e);
-                    return -1;
-                }
+            const cudaError_t e = launch_attention_step(
+                d->r_q, d->r_k, d->r_v, L.q_norm, L.k_norm, d->kc + il * per_layer, d->vc + il * per_layer, d->att_part,
+                d->r_attn, d->r_pos, d->cfg.n_heads, d->n_kv, d->hd, eps, L.theta_scale, 1.0f / sqrtf((float)d->hd),
+                d->cfg.max_seq, b, h->d_status, s);
+            if (e != cudaSuccess) {
+                h->err = std::string("attention: ") + cudaGetErrorString(e);
+                return -1;
             }
             a = d->r_attn;
         }

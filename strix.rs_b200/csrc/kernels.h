@@ -115,12 +115,13 @@ cudaError_t launch_xquant8(const float *d_x, int8_t *d_q, float *d_d, uint32_t n
 
 // One token of attention for one layer (attention.cu): QK RMSNorm (null norm pointers = none) + NEOX
 // RoPE in place on d_q, rotated k and v appended to the cache row *d_pos, softmax(q k^T scale) v over
-// rows 0..*d_pos into d_attn[n_heads * hd]. d_part: n_heads * ceil(max_seq / ATT_SPLIT_TOKENS) * (hd + 2) floats.
+// rows 0..*d_pos into d_attn[n_heads * hd]. `rows` tokens at once: d_q / d_k / d_v / d_attn are [rows][dim],
+// d_pos[rows] their positions (ascending, so that attention is causal among them). d_part: rows * n_heads * ceil(max_seq / ATT_SPLIT_TOKENS) * (hd + 2) floats.
 constexpr uint32_t ATT_SPLIT_TOKENS = 64;
 cudaError_t launch_attention_step(float *d_q, const float *d_k, const float *d_v, const float *d_q_norm,
                                   const float *d_k_norm, float *d_kc, float *d_vc, float *d_part, float *d_attn,
                                   const uint32_t *d_pos, uint32_t n_heads, uint32_t n_kv, uint32_t hd, float eps,
-                                  float theta_scale, float scale, uint32_t max_seq, uint32_t *d_status,
+                                  float theta_scale, float scale, uint32_t max_seq, uint32_t rows, uint32_t *d_status,
                                   cudaStream_t stream);
 
 }  // namespace strix
