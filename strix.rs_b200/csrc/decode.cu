@@ -74,6 +74,7 @@ struct strix_decode_state {
           *r_up = nullptr, *r_logits = nullptr;
     uint32_t *r_pos = nullptr;
     void *r_pin_in = nullptr, *r_pin_out = nullptr;
+    cudaGraphExec_t r_exec[2][9] = {};  // [all logits?][rows]: the batched chain captured once per shape
     size_t qdim = 0, kvdim = 0;
     // chain-kernel programs, one per (h, logits) buffer pair
     struct Program {
@@ -96,6 +97,9 @@ static void decode_free(strix_decode_state *d) {
         if (p) cudaFree(p);
     for (float *p : {d->r_h, d->r_q, d->r_k, d->r_v, d->r_attn, d->r_gate, d->r_up, d->r_logits})
         if (p) cudaFree(p);
+    for (auto &row : d->r_exec)
+        for (cudaGraphExec_t g : row)
+            if (g) cudaGraphExecDestroy(g);
     if (d->r_pos) cudaFree(d->r_pos);
     if (d->r_pin_in) cudaFreeHost(d->r_pin_in);
     if (d->r_pin_out) cudaFreeHost(d->r_pin_out);
@@ -404,6 +408,8 @@ static int rows_alloc(strix_cuda *h, strix_decode_state *d) {
     return 0;
 }
 
+static int rows_enqueue(strix_cuda *h, strix_decode_state *d, size_t m, bool all_logits, cudaStream_t s);
+
 // m tokens (rows) through the chain in one pass over the weights per step: the batched GEMV carries
 // the rows as extra MMA columns; attention takes all rows in one launch per kernel (their keys and values
 // enter the cache first, then row t attends to rows 0 .. its own position: causal). all_logits: the head for every row, else for the last one.
@@ -429,6 +435,43 @@ static int rows_run(strix_cuda *h, strix_decode_state *d, const float *hs, size_
     for (size_t t = 0; t < m; t++) pin_pos[t] = (uint32_t)(start_pos + t);
     CU_TRY(h, cudaMemcpyAsync(d->r_h, pin, m * hidden * sizeof(float), cudaMemcpyHostToDevice, s));
     CU_TRY(h, cudaMemcpyAsync(d->r_pos, pin_pos, m * 4, cudaMemcpyHostToDevice, s));
+    // The kernels of one (rows, all-logits) shape are captured into a CUDA graph on first use and replayed
+    // afterwards: a call is ~250 launches, and issuing them one by one costs the host about a millisecond.
+    // (Positions and activations live in fixed device buffers, so the graph does not depend on them.)
+    cudaGraphExec_t &exec = d->r_exec[all_logits ? 1 : 0][m];
+    if (!exec) {
+        cudaGraph_t g = nullptr;
+        CU_TRY(h, cudaStreamBeginCapture(s, cudaStreamCaptureModeThreadLocal));
+        const int rc = rows_enqueue(h, d, m, all_logits, s);
+        const cudaError_t e = cudaStreamEndCapture(s, &g);
+        if (rc < 0 || e != cudaSuccess) {
+            if (g) cudaGraphDestroy(g);
+            if (rc >= 0) h->err = std::string(who) + ": graph capture: " + cudaGetErrorString(e);
+            return -1;
+        }
+        const cudaError_t ei = cudaGraphInstantiate(&exec, g, 0);
+        cudaGraphDestroy(g);
+        if (ei != cudaSuccess) {
+            exec = nullptr;
+            h->err = std::string(who) + ": graph instantiate: " + cudaGetErrorString(ei);
+            return -1;
+        }
+    }
+    CU_TRY(h, cudaGraphLaunch(exec, s));
+    CU_TRY(h, cudaMemcpyAsync(d->r_pin_out, d->r_logits, n_out * vocab * sizeof(float), cudaMemcpyDeviceToHost, s));
+    CU_TRY(h, cudaMemcpyAsync(&h->status_host, h->d_status, 4, cudaMemcpyDeviceToHost, s));
+    CU_TRY(h, cudaStreamSynchronize(s));
+    if (h->status_host != 0) {
+        h->err = std::string(who) + ": device status " + std::to_string(h->status_host);
+        cudaMemsetAsync(h->d_status, 0, 4, s);
+        return -2;
+    }
+    memcpy(out, d->r_pin_out, n_out * vocab * sizeof(float));
+    return 1;
+}
+
+static int rows_enqueue(strix_cuda *h, strix_decode_state *d, size_t m, bool all_logits, cudaStream_t s) {
+    const size_t hidden = d->cfg.hidden, n_out = all_logits ? m : 1;
     const int act = d->cfg.act;
     const float eps = d->cfg.eps;
     const int gate_pre = d->cfg.act_gelu ? STRIX_PRE_GEGLU : STRIX_PRE_SWIGLU;
@@ -480,15 +523,6 @@ static int rows_run(strix_cuda *h, strix_decode_state *d, const float *hs, size_
         if (gemv_launch_rows(h, 1, w, x, d->out_norm, eps, STRIX_PRE_RMSNORM, act, y, nullptr, (uint32_t)n_out, (uint32_t)hidden, 0, s) < 0)
             return -1;
     }
-    CU_TRY(h, cudaMemcpyAsync(d->r_pin_out, d->r_logits, n_out * vocab * sizeof(float), cudaMemcpyDeviceToHost, s));
-    CU_TRY(h, cudaMemcpyAsync(&h->status_host, h->d_status, 4, cudaMemcpyDeviceToHost, s));
-    CU_TRY(h, cudaStreamSynchronize(s));
-    if (h->status_host != 0) {
-        h->err = std::string(who) + ": device status " + std::to_string(h->status_host);
-        cudaMemsetAsync(h->d_status, 0, 4, s);
-        return -2;
-    }
-    memcpy(out, d->r_pin_out, n_out * vocab * sizeof(float));
     return 1;
 }
 
