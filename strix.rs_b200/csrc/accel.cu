@@ -282,6 +282,9 @@ void strix_cuda_destroy(strix_cuda *h) {
     decode_release(h);
     if (h->copy_stream) cudaStreamDestroy(h->copy_stream);
     for (cudaEvent_t e : h->batch_events) cudaEventDestroy(e);
+    if (h->batch_graph.exec) cudaGraphExecDestroy(h->batch_graph.exec);
+    if (h->batch_flags) cudaFreeHost((void *)h->batch_flags);
+    if (h->d_one) cudaFree(h->d_one);
     for (auto &kv : h->weights) {
         cudaFree(kv.second.dev);
         if (kv.second.gemm_codes) cudaFree(kv.second.gemm_codes);
@@ -394,7 +397,6 @@ int strix_cuda_gemv_batch(strix_cuda *h, size_t n, const char *const *keys, cons
     float *pin = static_cast<float *>(h->pin_in.p), *pout = static_cast<float *>(h->pin_out.p);
     for (size_t i = 0; i < n; i++)
         if (ws[i]) memcpy(pin + xoff[i], xs[i], ws[i]->L.in_dim * sizeof(float));
-    CU_TRY(h, cudaMemcpyAsync(h->x.p, pin, xtot * 4, cudaMemcpyHostToDevice, h->stream));
     // Outputs leave on a second stream, each as soon as its kernel is done, so that the copies (and the
     // host's own copy out of the pinned buffer) overlap the kernels still to run.
     if (!h->copy_stream) CU_TRY(h, cudaStreamCreateWithFlags(&h->copy_stream, cudaStreamNonBlocking));
@@ -403,24 +405,125 @@ int strix_cuda_gemv_batch(strix_cuda *h, size_t n, const char *const *keys, cons
         CU_TRY(h, cudaEventCreateWithFlags(&e, cudaEventDisableTiming));
         h->batch_events.push_back(e);
     }
-    for (size_t i = 0; i < n; i++) {
-        if (!ws[i]) continue;
-        const Resident *w1[1] = {ws[i]};
-        float *y1[1] = {h->y.p + yoff[i]};
-        if (gemv_launch(h, 1, w1, h->x.p + xoff[i], nullptr, 0.f, STRIX_PRE_NONE, act, y1, nullptr, h->stream) < 0) return -1;
-        cudaEvent_t done = h->batch_events[2 * i], copied = h->batch_events[2 * i + 1];
-        CU_TRY(h, cudaEventRecord(done, h->stream));
-        CU_TRY(h, cudaStreamWaitEvent(h->copy_stream, done, 0));
-        if (ws[i]->rows)
-            CU_TRY(h, cudaMemcpyAsync(pout + yoff[i], h->y.p + yoff[i], ws[i]->rows * 4, cudaMemcpyDeviceToHost, h->copy_stream));
-        CU_TRY(h, cudaEventRecord(copied, h->copy_stream));
+    // Outputs leave in groups: an event between two launches keeps the second from starting early behind the
+    // first (programmatic dependent launch), so small outputs wait for a later item and only an output that
+    // brings the pending bytes to 256 KB (or the last item) closes a group. group_end[i]: the item whose
+    // event covers item i's output; group_begin[e]: first item of the group that e closes.
+    std::vector<size_t> group_end(n, 0), group_begin(n, 0);
+    {
+        size_t pending = 0, first = n, last_valid = n;
+        for (size_t i = 0; i < n; i++)
+            if (ws[i]) last_valid = i;
+        for (size_t i = 0; i < n; i++) {
+            if (!ws[i]) continue;
+            if (first == n) first = i;
+            pending += ws[i]->rows * 4;
+            if (pending >= (256u << 10) || i == last_valid) {
+                for (size_t j = first; j <= i; j++) group_end[j] = i;
+                group_begin[i] = first;
+                pending = 0;
+                first = n;
+            }
+        }
     }
-    CU_TRY(h, cudaMemcpyAsync(&h->status_host, h->d_status, 4, cudaMemcpyDeviceToHost, h->stream));
-    // hand each output to the caller as its copy lands
-    for (size_t i = 0; i < n; i++) {
-        if (!ws[i]) continue;
-        CU_TRY(h, cudaEventSynchronize(h->batch_events[2 * i + 1]));
-        memcpy(ys[i], pout + yoff[i], ws[i]->rows * sizeof(float));
+    // What the device does for this batch: H2D of the activations, then per item its kernel on the main
+    // stream and, on the copy stream, its output's D2H followed by a one-word copy that raises the item's
+    // pinned flag. `graph`: the same sequence is being captured (the copy stream joins the main one at the
+    // end, the events are capture-internal); otherwise the events are real and the host waits on them.
+    auto enqueue = [&](bool graph) -> int {
+        CU_TRY(h, cudaMemcpyAsync(h->x.p, pin, xtot * 4, cudaMemcpyHostToDevice, h->stream));
+        cudaEvent_t last = nullptr;
+        for (size_t i = 0; i < n; i++) {
+            if (!ws[i]) continue;
+            const Resident *w1[1] = {ws[i]};
+            float *y1[1] = {h->y.p + yoff[i]};
+            if (gemv_launch(h, 1, w1, h->x.p + xoff[i], nullptr, 0.f, STRIX_PRE_NONE, act, y1, nullptr, h->stream) < 0) return -1;
+            if (group_end[i] != i) continue;  // its output leaves with a later item's (see group_end)
+            cudaEvent_t done = h->batch_events[2 * i], copied = h->batch_events[2 * i + 1];
+            CU_TRY(h, cudaEventRecord(done, h->stream));
+            CU_TRY(h, cudaStreamWaitEvent(h->copy_stream, done, 0));
+            // the group's outputs are contiguous in the staging buffers: one copy
+            const size_t g0 = group_begin[i], bytes = (yoff[i] + ws[i]->rows - yoff[g0]) * 4;
+            if (bytes) CU_TRY(h, cudaMemcpyAsync(pout + yoff[g0], h->y.p + yoff[g0], bytes, cudaMemcpyDeviceToHost, h->copy_stream));
+            if (graph)
+                CU_TRY(h, cudaMemcpyAsync((void *)(h->batch_flags + i), h->d_one, 4, cudaMemcpyDeviceToHost, h->copy_stream));
+            CU_TRY(h, cudaEventRecord(copied, h->copy_stream));
+            last = copied;
+        }
+        if (graph && last) CU_TRY(h, cudaStreamWaitEvent(h->stream, last, 0));
+        // (the status word goes to ordinary host memory: that copy stays outside the graph)
+        if (!graph) CU_TRY(h, cudaMemcpyAsync(&h->status_host, h->d_status, 4, cudaMemcpyDeviceToHost, h->stream));
+        return 1;
+    };
+    constexpr size_t BATCH_GRAPH_MAX = 64;
+    bool use_graph = n <= BATCH_GRAPH_MAX;
+    if (const char *e = getenv("STRIX_BATCH_GRAPH")) use_graph = use_graph && atoi(e) != 0;
+    if (use_graph && !h->batch_flags) {
+        CU_TRY(h, cudaMallocHost((void **)&h->batch_flags, BATCH_GRAPH_MAX * 4));
+        CU_TRY(h, cudaMalloc(&h->d_one, 4));
+        const uint32_t one = 1;
+        CU_TRY(h, cudaMemcpy(h->d_one, &one, 4, cudaMemcpyHostToDevice));
+    }
+    if (use_graph) {
+        // the cached graph fits if every pointer and shape its nodes hold is the same as last time
+        auto &bg = h->batch_graph;
+        bool same = bg.exec && bg.act == act && bg.w_dev.size() == n && bg.x == h->x.p && bg.y == h->y.p &&
+                    bg.pin_in == h->pin_in.p && bg.pin_out == h->pin_out.p;
+        for (size_t i = 0; same && i < n; i++)
+            same = bg.w_dev[i] == (ws[i] ? ws[i]->dev : nullptr) && (!ws[i] || (bg.rows[i] == ws[i]->rows && bg.in_dim[i] == ws[i]->L.in_dim));
+        if (!same) {
+            if (bg.exec) cudaGraphExecDestroy(bg.exec);
+            bg.exec = nullptr;
+            cudaGraph_t g = nullptr;
+            CU_TRY(h, cudaStreamBeginCapture(h->stream, cudaStreamCaptureModeThreadLocal));
+            const int rc = enqueue(true);
+            const cudaError_t e = cudaStreamEndCapture(h->stream, &g);
+            if (rc < 0 || e != cudaSuccess) {
+                if (g) cudaGraphDestroy(g);
+                if (rc >= 0) h->err = std::string("gemv_batch: graph capture: ") + cudaGetErrorString(e);
+                return -1;
+            }
+            const cudaError_t ei = cudaGraphInstantiate(&bg.exec, g, 0);
+            cudaGraphDestroy(g);
+            if (ei != cudaSuccess) {
+                bg.exec = nullptr;
+                h->err = std::string("gemv_batch: graph instantiate: ") + cudaGetErrorString(ei);
+                return -1;
+            }
+            bg.act = act;
+            bg.w_dev.assign(n, nullptr);
+            bg.rows.assign(n, 0);
+            bg.in_dim.assign(n, 0);
+            for (size_t i = 0; i < n; i++)
+                if (ws[i]) {
+                    bg.w_dev[i] = ws[i]->dev;
+                    bg.rows[i] = ws[i]->rows;
+                    bg.in_dim[i] = ws[i]->L.in_dim;
+                }
+            bg.x = h->x.p;
+            bg.y = h->y.p;
+            bg.pin_in = h->pin_in.p;
+            bg.pin_out = h->pin_out.p;
+        }
+        for (size_t i = 0; i < n; i++) h->batch_flags[i] = 0u;
+        CU_TRY(h, cudaGraphLaunch(bg.exec, h->stream));
+        CU_TRY(h, cudaMemcpyAsync(&h->status_host, h->d_status, 4, cudaMemcpyDeviceToHost, h->stream));
+        // hand each output to the caller as its flag comes up (bounded: once the stream has drained,
+        // everything has landed whatever the flag says)
+        for (size_t i = 0; i < n; i++) {
+            if (!ws[i]) continue;
+            for (uint64_t spin = 0; h->batch_flags[group_end[i]] == 0u; spin++)
+                if ((spin & 0xfffu) == 0xfffu && cudaStreamQuery(h->stream) != cudaErrorNotReady) break;
+            memcpy(ys[i], pout + yoff[i], ws[i]->rows * sizeof(float));
+        }
+    } else {
+        if (enqueue(false) < 0) return -1;
+        // hand each output to the caller as its copy lands
+        for (size_t i = 0; i < n; i++) {
+            if (!ws[i]) continue;
+            CU_TRY(h, cudaEventSynchronize(h->batch_events[2 * group_end[i] + 1]));
+            memcpy(ys[i], pout + yoff[i], ws[i]->rows * sizeof(float));
+        }
     }
     CU_TRY(h, cudaStreamSynchronize(h->stream));
     const uint32_t st = h->status_host;

@@ -48,6 +48,18 @@ struct strix_cuda {
     cudaStream_t stream = nullptr;
     cudaStream_t copy_stream = nullptr;        // gemv_batch: outputs leave here while later kernels run
     std::vector<cudaEvent_t> batch_events;     // gemv_batch: (kernel done, copy done) per call slot
+    // gemv_batch replays the last batch shape from a CUDA graph (one launch instead of ~5 runtime calls
+    // per item): the graph, what it was captured for, and the pinned words its copies raise as each
+    // output lands (the host copies that output out while later kernels still run)
+    struct BatchGraph {
+        cudaGraphExec_t exec = nullptr;
+        int act = 0;
+        std::vector<const uint8_t *> w_dev;   // resident buffers of the items, in order (null = skipped item)
+        std::vector<size_t> rows, in_dim;
+        const void *x = nullptr, *y = nullptr, *pin_in = nullptr, *pin_out = nullptr;
+    } batch_graph;
+    volatile uint32_t *batch_flags = nullptr;  // pinned, BATCH_GRAPH_MAX words
+    uint32_t *d_one = nullptr;                 // device word holding 1
     uint32_t *d_status = nullptr;
     uint32_t status_host = 0;
     std::unordered_map<std::string, strix::Resident> weights;
