@@ -95,7 +95,8 @@ __global__ void __launch_bounds__(ATT_THREADS) sdpa_split_kernel(const float *__
                                                                  const float *__restrict__ vc, float *__restrict__ part,
                                                                  const uint32_t *__restrict__ d_pos, uint32_t n_heads,
                                                                  uint32_t n_kv, uint32_t hd, float scale, uint32_t max_seq) {
-    __shared__ float qs[256], sc[ATT_SPLIT], red[ATT_THREADS / 32], vsum[ATT_THREADS];
+    __shared__ float sc[ATT_SPLIT], red[ATT_THREADS / 32];
+    __shared__ __align__(16) float vsum[4 * ATT_THREADS];
     const uint32_t hh = blockIdx.x, sp = blockIdx.y, row = blockIdx.z, t = threadIdx.x, lane = t & 31u, warp = t >> 5;
     const uint32_t len = min(d_pos[row] + 1u, max_seq);
     q += (size_t)row * n_heads * hd;
@@ -109,18 +110,28 @@ __global__ void __launch_bounds__(ATT_THREADS) sdpa_split_kernel(const float *__
         return;
     }
     const uint32_t n = min(ATT_SPLIT, len - t0), kvdim = n_kv * hd, kvh = hh / (n_heads / n_kv);
-    for (uint32_t i = t; i < hd; i += ATT_THREADS) qs[i] = q[hh * hd + i];
-    __syncthreads();
-    // scores: a warp takes tokens warp, warp + 8, ...; four tokens per pass so that their loads overlap
+    const uint32_t nq = hd / 4u;  // float4 columns of a head (hd % 4 == 0: rows of the cache are 16-byte aligned)
+    // scores: a warp takes tokens warp, warp + 8, ...; a lane keeps its float4 slice(s) of q in registers
+    // and reads the same slice of each key row with one 16-byte load; four tokens per pass
     constexpr uint32_t NW = ATT_THREADS / 32;
+    const float4 *q4 = reinterpret_cast<const float4 *>(q + hh * hd);
+    const float4 qa = lane < nq ? q4[lane] : make_float4(0.f, 0.f, 0.f, 0.f);
+    const float4 qb = lane + 32u < nq ? q4[lane + 32u] : make_float4(0.f, 0.f, 0.f, 0.f);
     for (uint32_t j0 = warp; j0 < n; j0 += 4u * NW) {
         float a[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
         for (uint32_t u = 0; u < 4; u++) {
             const uint32_t j = j0 + u * NW;
             if (j < n) {
-                const float *kr = kc + (size_t)(t0 + j) * kvdim + kvh * hd;
-                for (uint32_t i = lane; i < hd; i += 32) a[u] = fmaf(qs[i], kr[i], a[u]);
+                const float4 *kr = reinterpret_cast<const float4 *>(kc + (size_t)(t0 + j) * kvdim + kvh * hd);
+                if (lane < nq) {
+                    const float4 kv = kr[lane];
+                    a[u] = fmaf(qa.x, kv.x, fmaf(qa.y, kv.y, fmaf(qa.z, kv.z, qa.w * kv.w)));
+                }
+                if (lane + 32u < nq) {
+                    const float4 kv = kr[lane + 32u];
+                    a[u] = fmaf(qb.x, kv.x, fmaf(qb.y, kv.y, fmaf(qb.z, kv.z, fmaf(qb.w, kv.w, a[u]))));
+                }
             }
         }
 #pragma unroll
@@ -154,25 +165,25 @@ __global__ void __launch_bounds__(ATT_THREADS) sdpa_split_kernel(const float *__
         my[0] = m;
         my[1] = tot;
     }
-    // weighted value sum: the 256 threads form `parts` groups of hd; group p takes tokens p, p + parts, ...
-    // (rows of the cache are read coalesced), and the groups' sums meet in shared memory, in group order
-    const uint32_t parts = ATT_THREADS / hd;  // >= 1: hd <= 256
-    const uint32_t p = t / hd, i = t - p * hd;
-    float o = 0.f;
+    // weighted value sum: the 256 threads form `parts` groups of hd / 4 lanes; a lane owns four output
+    // elements and group p takes tokens p, p + parts, ... (16-byte loads, rows of the cache coalesced); the
+    // groups' sums meet in shared memory, in group order
+    const uint32_t parts = ATT_THREADS / nq;  // >= 4: hd <= 256
+    const uint32_t p = t / nq, c4 = t - p * nq;
+    float4 o = make_float4(0.f, 0.f, 0.f, 0.f);
     if (p < parts) {
-        const float *vr = vc + (size_t)t0 * kvdim + kvh * hd + i;
-        uint32_t j = p;
-        for (; j + 3u * parts < n; j += 4u * parts) {
-            const float v0 = vr[(size_t)j * kvdim], v1 = vr[(size_t)(j + parts) * kvdim];
-            const float v2 = vr[(size_t)(j + 2u * parts) * kvdim], v3 = vr[(size_t)(j + 3u * parts) * kvdim];
-            o = fmaf(sc[j], v0, o);
-            o = fmaf(sc[j + parts], v1, o);
-            o = fmaf(sc[j + 2u * parts], v2, o);
-            o = fmaf(sc[j + 3u * parts], v3, o);
+        const float4 *vr = reinterpret_cast<const float4 *>(vc + (size_t)t0 * kvdim + kvh * hd) + c4;
+        const uint32_t row4 = kvdim / 4u;
+        for (uint32_t j = p; j < n; j += parts) {
+            const float4 v = vr[(size_t)j * row4];
+            const float w = sc[j];
+            o.x = fmaf(w, v.x, o.x);
+            o.y = fmaf(w, v.y, o.y);
+            o.z = fmaf(w, v.z, o.z);
+            o.w = fmaf(w, v.w, o.w);
         }
-        for (; j < n; j += parts) o = fmaf(sc[j], vr[(size_t)j * kvdim], o);
+        reinterpret_cast<float4 *>(vsum)[t] = o;  // as floats: vsum[p * hd + 4 c4 + e]
     }
-    vsum[t] = o;
     __syncthreads();
     if (t < hd) {
         float tot = vsum[t];

@@ -276,7 +276,7 @@ int strix_cuda_configure_decode(strix_cuda *h, const strix_gpu_decode_config *cf
         if (!cfg->layers || !cfg->attn_rsqrt || cfg->norm_v || cfg->n_swa || cfg->max_seq == 0 || cfg->n_heads == 0) return 0;
         hd = cfg->layers[0].head_dim;
         n_kv = cfg->layers[0].n_kv;
-        if (hd == 0 || hd > 256 || (hd & 1u) || n_kv == 0 || cfg->n_heads % n_kv != 0) return 0;
+        if (hd == 0 || hd > 256 || (hd & 3u) || n_kv == 0 || cfg->n_heads % n_kv != 0) return 0;  // 16-byte rows
         for (uint32_t il = 0; il < cfg->n_layers; il++) {
             const strix_gpu_layer_cfg &lc = cfg->layers[il];
             if (lc.head_dim != hd || lc.n_kv != n_kv || lc.k_eq_v || lc.is_local || lc.no_rope || lc.rope_norm ||

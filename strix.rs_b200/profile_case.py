@@ -2,6 +2,10 @@
 
     python strix.rs_b200/profile_case.py gemv <ggml type 2|8|14> <rows> <in_dim> <act 0|1> [launches]
     python strix.rs_b200/profile_case.py gemm <tokens> <in_dim> <rows> [launches]
+    python strix.rs_b200/profile_case.py attn <context> [steps]
+
+`attn`: a two-layer model with the benchmark's attention geometry (32 query heads, 8 KV heads of 128,
+hidden 2560) and a KV cache seeded up to <context>; runs decode_step at that position (``-k regex:sdpa_split``).
 
 Uploads one seeded synthetic weight through the C ABI and launches the device-resident entry
 point a few times on cuda:0. Run it plain first, then under ncu with ``-k regex:gemv_kernel``
@@ -36,6 +40,30 @@ def main():
         y = torch.empty(n, device=dev)
         for _ in range(reps):
             acc.gemv_dev(["w"], x.data_ptr(), [y.data_ptr()], act=act, stream=s)
+    elif kind == "attn":
+        ctx = int(sys.argv[2])
+        reps = int(sys.argv[3]) if len(sys.argv) > 3 else 3
+        hidden, hd, n_heads, n_kv, ffn, vocab, n_layers = 2560, 128, 32, 8, 1024, 2048, 2
+        shapes = {"attn_q": (n_heads * hd, hidden), "attn_k": (n_kv * hd, hidden), "attn_v": (n_kv * hd, hidden),
+                  "attn_output": (hidden, n_heads * hd), "ffn_gate": (ffn, hidden), "ffn_up": (ffn, hidden),
+                  "ffn_down": (hidden, ffn)}
+        for il in range(n_layers):
+            for nm, (n, k) in shapes.items():
+                assert acc.upload_q4_0("blk.%d.%s.weight" % (il, nm), synth.q4_0(1, nm, n, k), k, n)
+            for nn in ("attn_norm", "ffn_norm"):
+                acc.upload_f32("blk.%d.%s.weight" % (il, nn), synth.norm_weight(1, nn, hidden))
+            for nn in ("attn_q_norm", "attn_k_norm"):
+                acc.upload_f32("blk.%d.%s.weight" % (il, nn), synth.norm_weight(1, nn, hd))
+        assert acc.upload_q6_k("output.weight", synth.q6_k(1, "head", vocab, hidden), hidden, vocab)
+        acc.upload_f32("output_norm.weight", synth.norm_weight(1, "on", hidden))
+        assert acc.configure_decode(hidden, n_heads, ffn, vocab, n_layers, eps=1e-6, act=pkg.ACT_Q8DOT,
+                                    attn_standin_q=False, head_dim=hd, n_kv=n_kv, rope_theta=1e6, max_seq=ctx + 1)
+        rows = synth.normal(1, "kv", (ctx + 1) * n_kv * hd).reshape(ctx + 1, n_kv * hd)
+        for il in range(n_layers):
+            assert acc.seed_decode_kv(il, rows, rows)
+        h0 = synth.normal(1, "h0", hidden)
+        for _ in range(reps):
+            y = torch.from_numpy(acc.decode_step(h0, ctx))
     else:
         m, k, n = (int(a) for a in sys.argv[2:5])
         reps = int(sys.argv[5]) if len(sys.argv) > 5 else 3
