@@ -10,7 +10,7 @@ The directory name contains a dot, so it is loaded by path (see
 ``__graft_entry__.load_package``) under the module name ``strix_rs_b200``.
 """
 from .accel import (ACT_F32, ACT_Q8DOT, PRE_GEGLU, PRE_NONE, PRE_RMSNORM, PRE_SWIGLU, CudaWeightAccel,
-                    StrixCudaError, library_path, load_library, shard_begin)
+                    StrixCudaError, fold_argmax_shards, library_path, load_library, shard_begin)
 
-__all__ = ["CudaWeightAccel", "StrixCudaError", "load_library", "library_path", "shard_begin", "ACT_F32",
+__all__ = ["CudaWeightAccel", "StrixCudaError", "load_library", "library_path", "shard_begin", "fold_argmax_shards", "ACT_F32",
            "ACT_Q8DOT", "PRE_NONE", "PRE_RMSNORM", "PRE_SWIGLU", "PRE_GEGLU"]

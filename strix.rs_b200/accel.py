@@ -139,6 +139,23 @@ def _fp(a):
     return a.ctypes.data_as(C.POINTER(C.c_float))
 
 
+def fold_argmax_shards(ids, vals):
+    """Fold the per-shard winners of ``lm_head_argmax_rows`` (one (ids[m], vals[m]) pair per row shard, in
+    rank order) into the winners over the whole weight, with the device kernel's rule: a value replaces
+    the running best (-3.0e38, row 0) only if it is greater, or equal with a lower row index; NaN never wins."""
+    ids = np.asarray(ids, dtype=np.int64)
+    vals = np.asarray(vals, dtype=np.float32)
+    m = ids.shape[1]
+    best_v = np.full(m, np.float32(-3.0e38), dtype=np.float32)
+    best_i = np.zeros(m, dtype=np.int64)
+    for r in range(ids.shape[0]):
+        with np.errstate(invalid="ignore"):
+            take = (vals[r] > best_v) | ((vals[r] == best_v) & (ids[r] < best_i))
+        best_v = np.where(take, vals[r], best_v)
+        best_i = np.where(take, ids[r], best_i)
+    return best_i.astype(np.uint32)
+
+
 class CudaWeightAccel:
     """``impl WeightAccel`` for one CUDA device (the hot-path methods only)."""
 

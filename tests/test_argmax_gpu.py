@@ -103,3 +103,30 @@ def test_decode_step_argmax_equals_argmax_of_decode_step(pkg, orc, synth, int8):
         assert acc.device_status() == 0
     finally:
         acc.close()
+
+
+def test_lm_head_argmax_rows_row_sharded(pkg, orc, synth):
+    """Three row-sharded accelerators (on the one device): each returns the winner among its rows as a row
+    index of the whole weight plus its value; the fold of the shards equals the unsharded answer."""
+    in_dim, out_dim, m, world = 512, 3001, 5, 3
+    w = synth.quant(14, 61, "lhs", out_dim, in_dim)
+    xs = synth.normal(62, "lhs.x", m * in_dim)
+    accs = [pkg.CudaWeightAccel(0, rank=r, world=world) for r in range(world)]
+    whole = pkg.CudaWeightAccel(0)
+    try:
+        assert whole.upload_q6_k("lhs", w, in_dim, out_dim)
+        want = whole.lm_head_argmax_rows("lhs", xs, m)
+        ids, vals = [], []
+        for a in accs:
+            assert a.upload_q6_k("lhs", w, in_dim, out_dim)
+            i, v = a.lm_head_argmax_rows("lhs", xs, m, with_values=True)
+            info = a.weight_info("lhs")
+            assert ((i >= info["row0"]) & (i < info["row0"] + info["rows"])).all()
+            ids.append(i)
+            vals.append(v)
+        np.testing.assert_array_equal(pkg.fold_argmax_shards(ids, vals), want)
+        for a in accs:
+            assert a.decode_step_argmax(np.zeros(8, np.float32)) is None   # nothing configured on a shard
+    finally:
+        for a in accs + [whole]:
+            a.close()

@@ -93,3 +93,48 @@ def test_row_shards_gather_to_the_unsharded_result_gloo():
     for p in ps:
         p.join(60)
     assert res == [(0, True), (1, True)]
+
+
+def _gloo_argmax_worker(rank, world, port, q):
+    sys.path.insert(0, ROOT)
+    import torch.distributed as dist
+
+    import __graft_entry__ as entry
+    pkg = entry.load_package()
+    orc = entry.load_oracle()
+    from strix_rs_b200 import synth
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        # what a row-sharded lm_head_argmax_rows returns on each rank: the winner among ITS rows (global row
+        # index) and its value; the caller gathers the pairs and folds them
+        in_dim, out_dim, m = 256, 41, 3
+        w = synth.q8_0(12, "w", out_dim, in_dim)
+        xs = synth.normal(12, "xs", m * in_dim).reshape(m, in_dim)
+        full = np.stack([orc.qmatmul(xs[t], w, synth.Q8_0, in_dim, out_dim) for t in range(m)])
+        full[1, 7] = full[1, 30] = full[1].max() + 1.0      # a tie across the two shards: the lower row wins
+        full[2, :] = np.nan                                  # nothing wins: row 0
+        r0, r1 = pkg.shard_begin(out_dim, world, rank), pkg.shard_begin(out_dim, world, rank + 1)
+        ids = [orc.argmax_f32(full[t, r0:r1]) + r0 for t in range(m)]
+        vals = [float(full[t, i]) for t, i in enumerate(ids)]
+        got = [None] * world
+        dist.all_gather_object(got, (ids, vals))
+        folded = pkg.fold_argmax_shards([g[0] for g in got], [g[1] for g in got])
+        want = [orc.argmax_f32(full[t]) for t in range(m)]
+        q.put((rank, [int(v) for v in folded] == want and want[1] == 7 and want[2] == 0))
+    finally:
+        dist.destroy_process_group()
+
+
+def test_sharded_argmax_folds_to_the_unsharded_winner_gloo():
+    import torch.multiprocessing as mp
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = 31500 + os.getpid() % 2000
+    ps = [ctx.Process(target=_gloo_argmax_worker, args=(r, 2, port, q)) for r in range(2)]
+    for p in ps:
+        p.start()
+    res = sorted(q.get(timeout=120) for _ in ps)
+    for p in ps:
+        p.join(60)
+    assert res == [(0, True), (1, True)]
