@@ -187,8 +187,11 @@ STRIX_API int strix_cuda_prefill_q8_gemm_dev(strix_cuda *h, const char *key, con
  * strix_cuda_prefill_q8_gemm_dev, but ALL scratch comes from one fixed device array built into the
  * library (strix_cuda_noalloc_scratch_bytes() = 32 MiB per GPU, held until process exit). Calls no
  * cudaMalloc/cudaFree. A shape whose scratch exceeds the array returns <0 with the sizes in the
- * error text. The first call on a device looks the array's address up: make it outside any stream
- * capture. Every call shares the array (it keeps the last call's contents; nothing needs
+ * error text. The driver materialises the array's memory and the kernels' code when they are first
+ * touched, which can allocate: strix_cuda_create does that touching (address look-up with the handle's
+ * device current, kernel attributes), so create the handle before the arena takes the device. (Only for
+ * a device with no handle from strix_cuda_create would the first call do the look-up itself: keep
+ * that call outside any stream capture.) Every call shares the array (it keeps the last call's contents; nothing needs
  * zeroing), so calls whose kernels overlap on the GPU race: serialise them. */
 STRIX_API int strix_cuda_prefill_q8_gemm_noalloc(strix_cuda *h, const char *key, const float *d_xs, size_t m,
                                        float *d_y, void *stream);
@@ -221,12 +224,15 @@ typedef struct strix_gpu_decode_config {
  * token_embd.weight) and norm (blk.N.attn_norm/ffn_norm.weight, output_norm.weight via upload_f32)
  * is uploaded; with real attention and qk_norm also blk.N.attn_q_norm / attn_k_norm.weight (head_dim floats).
  * 0 = declined (a weight missing, post-norm / softcap / V-norm / sliding-window or local layers / shared
- * K = V / GPT-J rope / per-layer head sizes requested, or a sharded handle): the model keeps its per-weight
- * gemv path. Any later upload drops the configuration. */
+ * K = V / GPT-J rope / per-layer head sizes requested, or a sharded handle asking for anything but the
+ * integer-dot projection chain): the model keeps its per-weight gemv path. Any later upload drops the
+ * configuration. */
 STRIX_API int strix_cuda_configure_decode(strix_cuda *h, const strix_gpu_decode_config *cfg);
 /* WeightAccel::decode_step (accel.rs:433; decode.rs:5047-5531): logits[vocab] from the embedded hidden
- * state hvec[hidden]; four GEMV launches per layer (plus three small attention kernels with real
- * attention) replayed from a CUDA graph. With real attention row `pos` of the KV cache is written and
+ * state hvec[hidden]. With the attention stand-in and integer-dot activations the whole chain is ONE
+ * persistent launch (steps hand their outputs on through exchange vectors, no barrier between them);
+ * otherwise four GEMV launches per layer (plus three small attention kernels with real attention),
+ * replayed from a CUDA graph. With real attention row `pos` of the KV cache is written and
  * rows 0..pos are attended to (pos >= max_seq is an error); with the stand-in `pos` has no effect.
  * 0 = not configured. */
 STRIX_API int strix_cuda_decode_step(strix_cuda *h, const float *hvec, size_t pos, float *logits, size_t logits_cap);
@@ -264,7 +270,21 @@ STRIX_API size_t strix_cuda_prefill_max(strix_cuda *h);
  * done elsewhere (k normed and roped, v raw, token-major [tokens][n_kv * head_dim]). 0 = no real-attention
  * configuration, il or tokens out of range. */
 STRIX_API int strix_cuda_seed_decode_kv(strix_cuda *h, size_t il, const float *k, const float *v, size_t tokens);
-/* The same chain on device pointers (d_h is updated in place), enqueued on `stream`; no copy, no sync. */
+/* Row-sharded decode (no counterpart in the reference, which is single-device): on handles created with
+ * world > 1, configure_decode accepts the projection chain (attn_standin_q = 1, STRIX_ACT_Q8DOT). Every
+ * rank runs the persistent chain kernel over its row shards and publishes each step's rows into the
+ * exchange block of EVERY rank with plain peer stores (8-byte {value, epoch} entries; no collective, no
+ * barrier launch, no multicast); a rank's consumers poll their own block. strix_cuda_decode_exchange_info
+ * returns this rank's block (one cudaMalloc allocation, exportable with cudaIpcGetMemHandle);
+ * strix_cuda_decode_set_peers hands over all ranks' blocks as mapped into this process (entry `rank` may
+ * be null). Until the group is wired a rank publishes into its own block only, so its waits for the other
+ * ranks' rows run out: bounded (option "poll_limit"), the status word gets the time-out bit, the call
+ * returns -2 and the handle stays usable. decode_step / decode_chain_dev then return this rank's shard of
+ * the logits (rows shard_row0 .. of the head). All ranks must make the same sequence of decode calls. */
+STRIX_API int strix_cuda_decode_exchange_info(strix_cuda *h, void **base, size_t *bytes);
+STRIX_API int strix_cuda_decode_set_peers(strix_cuda *h, int n, void *const *blocks);
+/* The same chain on device pointers (d_h is updated in place; a row-sharded handle leaves it as it was),
+ * enqueued on `stream`; no copy, no sync. */
 STRIX_API int strix_cuda_decode_chain_dev(strix_cuda *h, float *d_h, float *d_logits, void *stream);
 
 /* Batched GEMV for speculative verify (the reference runs its verify rows through the 128-token
@@ -282,6 +302,22 @@ STRIX_API int strix_cuda_device_status(strix_cuda *h, void *stream, uint32_t *st
 
 /* ---- test / measurement extras (not part of the trait) ---- */
 
+/* Planning and measurement knobs of one handle, by name (the reference reads such knobs from the
+ * environment, e.g. STRIX_NO_SPLITK / STRIX_SK / STRIX_PROF, decode.rs:5652-5671, 25-31; here nothing on
+ * the call path reads the environment). 1 = set, 0 = unknown name. Any configured decode chain and cached
+ * graph is dropped. Names: "q6k_digits" (0 never / 1 in_dim <= 8192 / 2 whenever it fits: Q6_K f32 row as
+ * three int8 digit rows), "gemv_warps_per_group", "gemv_blocks_per_stage", "gemv_stages" (0 = planned),
+ * "gemv_pdl" (programmatic dependent launch between GEMVs), "gemv_debug" (bit 0: stream the weights without
+ * arithmetic, bit 1: empty launches, bit 2: stop after the activation prologue), "batch_graph" (gemv_batch
+ * replays a cached CUDA graph), "decode_chain" (the projection chain as one persistent launch),
+ * "chain_trace" (per-step clocks, see strix_cuda_decode_trace), "poll_limit" (bound, in polls, of a wait on
+ * an exchange vector; 0 = default), "profile" (as strix_cuda_opts.profile). */
+STRIX_API int strix_cuda_set_option(strix_cuda *h, const char *name, long long value);
+/* After set_option("chain_trace", 1): the clock (ns) of CTA 0 of the last decode-chain launch at each
+ * step's start, after its prologue (the wait for its activations included) and after its row groups,
+ * 3 words per step. Returns the number of steps (0 = no trace, or `cap_words` too small). Synchronises. */
+STRIX_API int strix_cuda_decode_trace(strix_cuda *h, unsigned long long *out, size_t cap_words);
+
 /* Dequantise a resident weight back to f32 [shard_rows][in_dim] on the host:
  * must equal dequantize_into (ggml_quant.rs:139-183) bit for bit. */
 STRIX_API int strix_cuda_dequant_to_f32(strix_cuda *h, const char *key, float *out, size_t out_cap);
@@ -290,9 +326,20 @@ STRIX_API int strix_cuda_dequant_to_f32(strix_cuda *h, const char *key, float *o
 STRIX_API int strix_cuda_xquant8(strix_cuda *h, const float *x, size_t n, int8_t *q, float *d);
 
 /* int32 block sums isum[m][rows][in_dim/32] of a resident Q8_0 weight with the int8 codes of
- * xs[m][in_dim] (the bit-exact tier of the GEMM; computed without tensor cores). */
+ * xs[m][in_dim] (the bit-exact tier of the GEMM, q8w_gemm32's per-block accumulator, kernels.rs:1417-1428),
+ * computed by a plain integer loop without tensor cores. */
 STRIX_API int strix_cuda_debug_block_isums(strix_cuda *h, const char *key, const float *xs, size_t m, int32_t *out,
                                  size_t out_cap);
+/* The same sums as the prefill GEMM's own tcgen05 kernel produces them: its producer, MMA and TMEM pipeline
+ * unchanged, with an epilogue that stores each block's integer instead of folding it into f32. `splits`:
+ * split-K slices (0 = what strix_cuda_prefill_q8_gemm would pick). An entry the kernel does not write reads -1. */
+STRIX_API int strix_cuda_debug_gemm_isums(strix_cuda *h, const char *key, const float *xs, size_t m, uint32_t splits,
+                                int32_t *out, size_t out_cap);
+/* Measurement: quantise d_xs[m][in_dim] once, then launch the GEMM kernel `reps` times on `stream` in `mode`:
+ * 0 = the product into d_y[m][rows]; 2 = without the accumulator drain (TMA + tensor pipeline alone);
+ * 3 = without drain and loads (the issue rate of tcgen05.mma kind::i8: the measured int8 peak). No sync. */
+STRIX_API int strix_cuda_debug_gemm_mode_dev(strix_cuda *h, const char *key, const float *d_xs, size_t m, float *d_y,
+                                   int mode, int reps, void *stream);
 
 #ifdef __cplusplus
 }

@@ -114,6 +114,12 @@ def load_library():
     sig("strix_cuda_device_status", C.c_int, H, C.c_void_p, C.POINTER(C.c_uint32))
     sig("strix_cuda_dequant_to_f32", C.c_int, H, C.c_char_p, f32p, sz)
     sig("strix_cuda_xquant8", C.c_int, H, f32p, sz, C.POINTER(C.c_int8), f32p)
+    sig("strix_cuda_debug_gemm_isums", C.c_int, H, C.c_char_p, f32p, sz, C.c_uint32, C.POINTER(C.c_int32), sz)
+    sig("strix_cuda_debug_gemm_mode_dev", C.c_int, H, C.c_char_p, C.c_void_p, sz, C.c_void_p, C.c_int, C.c_int, C.c_void_p)
+    sig("strix_cuda_decode_exchange_info", C.c_int, H, C.POINTER(C.c_void_p), szp)
+    sig("strix_cuda_decode_set_peers", C.c_int, H, C.c_int, C.POINTER(C.c_void_p))
+    sig("strix_cuda_set_option", C.c_int, H, C.c_char_p, C.c_longlong)
+    sig("strix_cuda_decode_trace", C.c_int, H, C.POINTER(C.c_uint64), sz)
     _lib = L
     return L
 
@@ -312,6 +318,26 @@ class CudaWeightAccel:
                                                              out.ctypes.data_as(C.POINTER(C.c_int32)), out.size))
         return out if rc == 1 else None
 
+    def debug_gemm_isums(self, key, xs, m, splits=0):
+        """The same block sums as the tcgen05 GEMM kernel itself produces them (splits: split-K slices, 0 = as
+        prefill_q8_gemm picks)."""
+        info = self.weight_info(key)
+        xa = _f32(xs)
+        if info is None or xa.size != m * info["in_dim"]:
+            return None
+        out = np.empty((m, info["rows"], info["in_dim"] // 32), dtype=np.int32)
+        rc = self._check(self._L.strix_cuda_debug_gemm_isums(self._h, key.encode(), _fp(xa), m, splits,
+                                                            out.ctypes.data_as(C.POINTER(C.c_int32)), out.size))
+        return out if rc == 1 else None
+
+    def debug_gemm_mode_dev(self, key, d_xs, m, d_y, mode, reps, stream=0):
+        """Measurement: quantise once, then `reps` launches of the GEMM kernel in `mode` (0 product, 2 no drain,
+        3 no drain and no loads)."""
+        rc = self._check(self._L.strix_cuda_debug_gemm_mode_dev(self._h, key.encode(), C.c_void_p(int(d_xs)), m,
+                                                               C.c_void_p(int(d_y)), mode, reps,
+                                                               C.c_void_p(int(stream)) if stream else None))
+        return rc == 1
+
     def configure_decode(self, hidden, n_heads, ffn, vocab, n_layers, eps=1e-6, act_gelu=False, act=ACT_Q8DOT,
                          attn_standin_q=True, post_norm=False, final_softcap=0.0, head_dim=0, n_kv=0,
                          rope_theta=1e6, max_seq=0, qk_norm=True, layer_overrides=None):
@@ -338,13 +364,28 @@ class CudaWeightAccel:
         return rc == 1
 
     def decode_step(self, h, pos=0):
-        """logits[vocab] or None (accel.rs:433)."""
+        """logits[vocab] or None (accel.rs:433). A row-sharded accelerator returns its shard of the logits."""
         if not getattr(self, "_vocab", None):
             return None
         ha = _f32(h)
         out = np.empty(self._vocab, dtype=np.float32)
         rc = self._check(self._L.strix_cuda_decode_step(self._h, _fp(ha), pos, _fp(out), out.size))
-        return out if rc == 1 else None
+        if rc != 1:
+            return None
+        if self.world > 1:
+            return out[:shard_begin(self._vocab, self.world, self.rank + 1) - shard_begin(self._vocab, self.world, self.rank)]
+        return out
+
+    def decode_exchange_info(self):
+        """(device address, bytes) of this accelerator's exchange block (row-sharded decode), or None."""
+        base, n = C.c_void_p(), C.c_size_t()
+        rc = self._check(self._L.strix_cuda_decode_exchange_info(self._h, C.byref(base), C.byref(n)))
+        return (base.value, n.value) if rc == 1 else None
+
+    def decode_set_peers(self, blocks):
+        """blocks[r]: rank r's exchange block as mapped into this process (0 / None for this rank's own)."""
+        arr = (C.c_void_p * len(blocks))(*[int(b) if b else None for b in blocks])
+        return self._check(self._L.strix_cuda_decode_set_peers(self._h, len(blocks), arr)) == 1
 
     def prefill(self, hs, start_pos, m):
         """Logits of the last of m tokens, KV cache filled for start_pos .. start_pos+m-1, or None (accel.rs:464-473)."""
@@ -474,6 +515,16 @@ class CudaWeightAccel:
         return s.value
 
     # -- test / measurement extras ---------------------------------------
+    def set_option(self, name, value):
+        """Planning / measurement knob by name (see strix_cuda_set_option); False for an unknown name."""
+        return self._check(self._L.strix_cuda_set_option(self._h, name.encode(), int(value))) == 1
+
+    def decode_trace(self, max_steps=4096):
+        """Per-step clocks [steps][3] (ns) of the last decode-chain launch after set_option("chain_trace", 1), or None."""
+        buf = np.zeros(3 * max_steps, np.uint64)
+        n = self._check(self._L.strix_cuda_decode_trace(self._h, buf.ctypes.data_as(C.POINTER(C.c_uint64)), buf.size))
+        return buf[:3 * n].reshape(n, 3).copy() if n > 0 else None
+
     def dequant_to_f32(self, key):
         info = self.weight_info(key)
         if info is None:

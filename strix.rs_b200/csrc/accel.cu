@@ -94,7 +94,7 @@ static int upload_quant(strix_cuda *h, int fmt, const char *key, const uint8_t *
         probe.L = r.L;
         probe.nmat = 1;
         probe.mat[0].rows = (uint32_t)std::max<size_t>(r.rows, 1);
-        if (!gemv_plan(probe, h->num_sms, h->smem_optin)) return 0;
+        if (!gemv_plan(probe, h->num_sms, h->smem_optin, h->tune)) return 0;
     }
     r.bytes = (size_t)resident_bytes(r.L, r.rows);
     CU_TRY(h, cudaMalloc(&r.dev, std::max<size_t>(r.bytes, 16)));
@@ -133,6 +133,12 @@ static int upload_quant(strix_cuda *h, int fmt, const char *key, const uint8_t *
         return -1;
     }
     decode_release(h);  // a configured chain may hold the pointer this upload replaces
+    if (h->batch_graph.exec) {
+        // so may the cached gemv_batch graph (the allocator can hand the old address back to a weight of
+        // another format or shape)
+        cudaGraphExecDestroy(h->batch_graph.exec);
+        h->batch_graph.exec = nullptr;
+    }
     auto it = h->weights.find(key);
     if (it != h->weights.end()) {
         cudaFree(it->second.dev);
@@ -204,7 +210,7 @@ int gemv_launch_rows(strix_cuda *h, int nmat, const Resident *const *ws, const f
         for (;; chunk = (chunk + 1) / 2) {
             c = a;
             c.nbatch = chunk;
-            if (gemv_plan(c, h->num_sms, h->smem_optin)) break;
+            if (gemv_plan(c, h->num_sms, h->smem_optin, h->tune)) break;
             if (chunk == 1) {
                 h->err = "gemv: in_dim too large for the shared-memory pipeline";
                 return -1;
@@ -263,7 +269,9 @@ int strix_cuda_create(int device, const strix_cuda_opts *opts, strix_cuda **out)
     if (e == cudaSuccess) e = cudaMalloc(&h->d_status, sizeof(uint32_t));
     if (e == cudaSuccess) e = cudaMemset(h->d_status, 0, sizeof(uint32_t));
     if (e == cudaSuccess) e = gemv_prepare_device(h->smem_optin);
+    if (e == cudaSuccess) e = chain_prepare_device(h->smem_optin);
     if (e == cudaSuccess) e = gemm_prepare_device();
+    if (e == cudaSuccess) e = noalloc_prepare_device(device);
     if (e != cudaSuccess) {
         g_create_error = std::string("create: ") + cudaGetErrorString(e);
         if (h->d_status) cudaFree(h->d_status);
@@ -290,7 +298,7 @@ void strix_cuda_destroy(strix_cuda *h) {
         if (kv.second.gemm_codes) cudaFree(kv.second.gemm_codes);
         if (kv.second.scalesT) cudaFree(kv.second.scalesT);
     }
-    for (float *p : {h->gm_x.p, h->gm_y.p, h->gm_part.p, h->gm_xd.p})
+    for (float *p : {h->gm_x.p, h->gm_y.p, h->gm_part.p, h->gm_xd.p, h->gm_xc.p})
         if (p) cudaFree(p);
     if (h->gm_xq) cudaFree(h->gm_xq);
     if (h->am_part) cudaFree(h->am_part);  // one allocation: winners, tickets, ids, values
@@ -304,6 +312,32 @@ void strix_cuda_destroy(strix_cuda *h) {
     cudaFree(h->d_status);
     cudaStreamDestroy(h->stream);
     delete h;
+}
+
+int strix_cuda_set_option(strix_cuda *h, const char *name, long long value) {
+    if (!h || !name) return -1;
+    h->err.clear();
+    const std::string n = name;
+    const uint32_t v = (uint32_t)value;
+    if (n == "q6k_digits") h->tune.digits_rule = v;
+    else if (n == "gemv_warps_per_group") h->tune.force_wc = v;
+    else if (n == "gemv_blocks_per_stage") h->tune.force_ct = v;
+    else if (n == "gemv_stages") h->tune.force_sk = v;
+    else if (n == "gemv_pdl") h->tune.pdl = v;
+    else if (n == "gemv_debug") h->tune.debug = v;
+    else if (n == "batch_graph") h->use_batch_graph = value != 0;
+    else if (n == "decode_chain") h->decode_chain = value != 0;
+    else if (n == "chain_trace") h->chain_trace = value != 0;
+    else if (n == "poll_limit") h->poll_limit = v ? v : CHAIN_POLL_LIMIT;
+    else if (n == "profile") h->profile = value != 0;
+    else return 0;
+    // plans made under the old value must not be replayed
+    decode_release(h);
+    if (h->batch_graph.exec) {
+        cudaGraphExecDestroy(h->batch_graph.exec);
+        h->batch_graph.exec = nullptr;
+    }
+    return 1;
 }
 
 const char *strix_cuda_last_error(strix_cuda *h) { return h ? h->err.c_str() : ""; }
@@ -456,8 +490,7 @@ int strix_cuda_gemv_batch(strix_cuda *h, size_t n, const char *const *keys, cons
         return 1;
     };
     constexpr size_t BATCH_GRAPH_MAX = 64;
-    bool use_graph = n <= BATCH_GRAPH_MAX;
-    if (const char *e = getenv("STRIX_BATCH_GRAPH")) use_graph = use_graph && atoi(e) != 0;
+    const bool use_graph = n <= BATCH_GRAPH_MAX && h->use_batch_graph;
     if (use_graph && !h->batch_flags) {
         CU_TRY(h, cudaMallocHost((void **)&h->batch_flags, BATCH_GRAPH_MAX * 4));
         CU_TRY(h, cudaMalloc(&h->d_one, 4));
@@ -632,7 +665,7 @@ int strix_cuda_gemv_peers_dev(strix_cuda *h, int nmat, const char *const *keys, 
         }
         for (int p = 0; p < h->world; p++) a.sync_peer[p] = sync->peer_flags[p];
     }
-    if (!gemv_plan(a, h->num_sms, h->smem_optin)) {
+    if (!gemv_plan(a, h->num_sms, h->smem_optin, h->tune)) {
         h->err = "gemv_peers_dev: in_dim too large for the shared-memory pipeline";
         return -1;
     }

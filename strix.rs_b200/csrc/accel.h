@@ -42,6 +42,11 @@ struct strix_decode_state;  // decode.cu
 struct strix_cuda {
     int device = 0;
     int rank = 0, world = 1, profile = 0;
+    strix::GemvTune tune;             // planning knobs (strix_cuda_set_option)
+    int use_batch_graph = 1;          // gemv_batch replays a cached CUDA graph
+    int chain_trace = 0;              // measurement: the chain kernel records per-step clocks (strix_cuda_decode_trace)
+    int decode_chain = 1;             // the decode projection chain runs as one persistent launch where it can
+    uint32_t poll_limit = strix::CHAIN_POLL_LIMIT;  // bound of a wait on an exchange vector, in polls
     int num_sms = 0;
     size_t smem_optin = 0;
     std::string name, err;
@@ -70,7 +75,7 @@ struct strix_cuda {
     strix::PinBuf pin_in, pin_out;
     // scratch of the prefill GEMM (grown on demand): f32 activations, their int8 codes, block scales,
     // block code sums, f32 output, split-K partials
-    strix::DevBuf gm_x, gm_y, gm_part, gm_xd;
+    strix::DevBuf gm_x, gm_y, gm_part, gm_xd, gm_xc;
     strix_decode_state *decode = nullptr;  // configured projection chain (decode.cu), or null
     // argmax scratch (argmax.cu), allocated on first use: per-block winners, per-row tickets, results
     void *am_part = nullptr;

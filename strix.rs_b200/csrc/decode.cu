@@ -20,11 +20,13 @@
 // attention flavours (sliding window, shared K = V, V-norm, softcap, post-norm) are declined and the
 // model keeps its per-weight gemv path.
 //
-// On one GPU the whole chain runs as ONE cooperative kernel (gemv_chain_kernel): the steps above
-// become a list the kernel walks, with a grid-wide barrier between steps, while its producer warps
-// keep prefetching the next steps' weights. The list holds device pointers, so it is built (and
-// uploaded) once per (hidden-state, logits) buffer pair, outside any stream capture; a pair first
-// seen inside a capture takes the launch-per-step path.
+// With the attention stand-in and integer-dot activations the whole chain runs as ONE persistent
+// cooperative kernel (chain.cu): the steps above become a list the kernel walks; its producer warps
+// prefetch the next steps' weights without pause and the activations pass from step to step through
+// exchange vectors of {value, epoch} entries (no grid barrier). SwiGLU / GeGLU then sit in the epilogue
+// of the gate|up step. The list holds device pointers, so it is built (and uploaded) once per
+// (hidden-state, logits) buffer pair, outside any stream capture; a pair first seen inside a capture,
+// f32 activations and real attention take the launch-per-step path.
 //
 // The step is captured into a CUDA graph on the first call and replayed afterwards
 // (one H2D of h, one graph launch, one D2H of the logits, one sync per token).
@@ -80,13 +82,21 @@ struct strix_decode_state {
     struct Program {
         const float *h;
         const float *logits;
-        GemvArgs *d_steps;
-        uint32_t n_steps, smem_bytes;
+        ChainStep *d_steps;
+        uint32_t n_steps;
+        ChainGeom geom;
     };
     std::vector<Program> programs;
-    uint32_t *d_gbar = nullptr;
-    unsigned long long *d_trace = nullptr;  // measurement only (STRIX_CHAIN_TRACE): per-step clocks of CTA 0
-    std::string trace_path;
+    // exchange vectors of the chain kernel ({f32 value, epoch} entries): q, the hidden state before and
+    // after the attention block, the gated FFN activation; and the kernel's two control words
+    // (one allocation, so that a group of accelerators can map each other's block through one IPC handle;
+    // peer[r] = rank r's block as mapped into this process, own block included, once the group is wired)
+    unsigned long long *ll_block = nullptr;
+    size_t ll_off[4] = {0, 0, 0, 0}, ll_words = 0;  // q, h_a, h_b, act: offsets in entries
+    unsigned long long *peer[GEMV_MAX_PEERS] = {};
+    int n_peer = 0;
+    uint32_t *d_ctl = nullptr;
+    unsigned long long *d_trace = nullptr;  // measurement only (option "chain_trace"): per-step clocks of CTA 0
     uint32_t trace_n = 0;
     bool chain_ok = true;  // false once a plan has failed: every call takes the launch-per-step path
 };
@@ -109,18 +119,9 @@ static void decode_free(strix_decode_state *d) {
     if (d->pin_logits) cudaFreeHost(d->pin_logits);
     if (d->exec) cudaGraphExecDestroy(d->exec);
     for (auto &p : d->programs) cudaFree(p.d_steps);
-    if (d->d_gbar) cudaFree(d->d_gbar);
-    if (d->d_trace) {
-        std::vector<unsigned long long> t(3 * d->trace_n);
-        if (cudaMemcpy(t.data(), d->d_trace, t.size() * sizeof(unsigned long long), cudaMemcpyDeviceToHost) == cudaSuccess) {
-            if (FILE *f = fopen(d->trace_path.c_str(), "w")) {
-                for (uint32_t i = 0; i < d->trace_n; i++)
-                    fprintf(f, "%u %llu %llu %llu\n", i, t[3 * i], t[3 * i + 1], t[3 * i + 2]);
-                fclose(f);
-            }
-        }
-        cudaFree(d->d_trace);
-    }
+    for (unsigned long long *p : {d->ll_block, d->d_trace})
+        if (p) cudaFree(p);
+    if (d->d_ctl) cudaFree(d->d_ctl);
     delete d;
 }
 
@@ -179,56 +180,126 @@ static int walk_chain(strix_decode_state *d, Emit emit, Mid mid) {
 // The chain-kernel program for the current d->h / d->logits, built on first use. Null when the
 // chain kernel cannot be used (plan failed, switched off, or a new buffer pair inside a stream capture).
 static const strix_decode_state::Program *chain_program(strix_cuda *h, strix_decode_state *d, cudaStream_t s) {
-    if (!d->chain_ok || d->real_attn) return nullptr;  // (attention is not a GEMV step: launches only)
+    // (attention is not a GEMV step, and the exchange-vector prologue is the integer-dot one: launches otherwise)
+    if (!d->chain_ok || d->real_attn || !h->decode_chain || d->cfg.act != STRIX_ACT_Q8DOT) return nullptr;
     for (auto &p : d->programs)
         if (p.h == d->h && p.logits == d->logits) return &p;
     cudaStreamCaptureStatus cs = cudaStreamCaptureStatusNone;
     if (cudaStreamIsCapturing(s, &cs) != cudaSuccess || cs != cudaStreamCaptureStatusNone) return nullptr;
-    {
-        // (measured slower than a launch per step so far: off unless asked for)
-        const char *e = getenv("STRIX_DECODE_CHAIN");
-        if (!e || atoi(e) == 0) {
-            d->chain_ok = false;
-            return nullptr;
-        }
-    }
-    std::vector<GemvArgs> steps;
-    const int act = d->cfg.act;
-    int rc = walk_chain(d, [&](int nmat, const Resident *const *w, const float *a, const float *b, float eps, int pre,
-                               float *const *y, const float *const *r) {
-        GemvArgs g{};
-        if (gemv_fill_args(h, nmat, w, a, b, eps, pre, act, y, r, &g) < 0) return -1;
-        steps.push_back(g);
-        return 1;
-    }, [&](size_t) -> const float * { return d->q; });
-    uint32_t smem = 0;
-    if (rc < 0 || !gemv_chain_plan(steps.data(), (uint32_t)steps.size(), h->num_sms, h->smem_optin, &smem)) {
+    auto fail = [&]() -> const strix_decode_state::Program * {
         d->chain_ok = false;
-        h->err.clear();
         return nullptr;
+    };
+    if (!d->ll_block) return fail();
+    // where a step publishes its rows: into the exchange block of every rank of the group (this rank's own
+    // among them); a lone accelerator, or a group not wired yet, into its own block only
+    auto publish = [&](ChainMat &m, int which) {
+        if (d->n_peer > 1) {
+            m.n_out_ll = (uint32_t)d->n_peer;
+            for (int r = 0; r < d->n_peer; r++) m.out_ll[r] = d->peer[r] + d->ll_off[which];
+        } else {
+            m.n_out_ll = 1;
+            m.out_ll[0] = d->ll_block + d->ll_off[which];
+        }
+    };
+    const unsigned long long *ll_q = d->ll_block + d->ll_off[0], *ll_ha = d->ll_block + d->ll_off[1],
+                             *ll_hb = d->ll_block + d->ll_off[2], *ll_act = d->ll_block + d->ll_off[3];
+    const bool sharded = h->world > 1;
+    std::vector<ChainStep> steps;
+    const int gate_pair = d->cfg.act_gelu ? STRIX_PRE_GEGLU : STRIX_PRE_SWIGLU;
+    const size_t nl = d->layers.size();
+    auto mat = [&](ChainStep &st, int m, const Resident *w) {
+        st.mat[m].w = w->dev;
+        st.mat[m].rows = (uint32_t)w->rows;
+        st.mat[m].row_base = (uint32_t)w->row0;
+    };
+    for (size_t il = 0; il < nl; il++) {
+        const auto &L = d->layers[il];
+        const uint32_t s0 = (uint32_t)(4 * il);
+        ChainStep qkv{};
+        qkv.nmat = 3;
+        qkv.L = L.q->L;
+        qkv.act = STRIX_ACT_Q8DOT;
+        qkv.pre = STRIX_PRE_RMSNORM;
+        qkv.b = L.attn_norm;
+        qkv.eps = d->cfg.eps;
+        if (il == 0) qkv.a = d->h;
+        else { qkv.a_ll = ll_ha; qkv.in_step = s0 - 1; }
+        mat(qkv, 0, L.q); mat(qkv, 1, L.k); mat(qkv, 2, L.v);
+        publish(qkv.mat[0], 0);
+        qkv.mat[0].y = d->q;
+        qkv.mat[1].y = d->k;
+        qkv.mat[2].y = d->v;
+        steps.push_back(qkv);
+        ChainStep o{};  // h += Wo q (the stand-in feeds Wo with q itself)
+        o.nmat = 1;
+        o.L = L.o->L;
+        o.act = STRIX_ACT_Q8DOT;
+        o.pre = STRIX_PRE_NONE;
+        o.a_ll = ll_q;
+        o.in_step = s0;
+        mat(o, 0, L.o);
+        if (il == 0) o.mat[0].res = d->h + L.o->row0;  // (this shard's rows of the hidden state)
+        else { o.mat[0].res_ll = ll_ha; o.res_step = s0 - 1; }
+        publish(o.mat[0], 2);
+        steps.push_back(o);
+        ChainStep gu{};  // act(Wg n) * (Wu n), n = rmsnorm(h)
+        gu.nmat = 2;
+        gu.L = L.gate->L;
+        gu.act = STRIX_ACT_Q8DOT;
+        gu.pre = STRIX_PRE_RMSNORM;
+        gu.pair = gate_pair;
+        gu.b = L.ffn_norm;
+        gu.eps = d->cfg.eps;
+        gu.a_ll = ll_hb;
+        gu.in_step = s0 + 1;
+        mat(gu, 0, L.gate); mat(gu, 1, L.up);
+        publish(gu.mat[0], 3);
+        steps.push_back(gu);
+        ChainStep dn{};  // h += Wd (...)
+        dn.nmat = 1;
+        dn.L = L.down->L;
+        dn.act = STRIX_ACT_Q8DOT;
+        dn.pre = STRIX_PRE_NONE;
+        dn.a_ll = ll_act;
+        dn.in_step = s0 + 2;
+        mat(dn, 0, L.down);
+        dn.mat[0].res_ll = ll_hb;
+        dn.res_step = s0 + 1;
+        publish(dn.mat[0], 1);
+        if (il + 1 == nl && !sharded) dn.mat[0].y = d->h;  // the hidden state after the last layer, for the caller
+        steps.push_back(dn);
+    }
+    {
+        ChainStep hd{};
+        hd.nmat = 1;
+        hd.L = d->head->L;
+        hd.act = STRIX_ACT_Q8DOT;
+        hd.pre = STRIX_PRE_RMSNORM;
+        hd.b = d->out_norm;
+        hd.eps = d->cfg.eps;
+        if (nl == 0) hd.a = d->h;
+        else { hd.a_ll = ll_ha; hd.in_step = (uint32_t)(4 * nl - 1); }
+        mat(hd, 0, d->head);
+        hd.mat[0].y = d->logits;
+        steps.push_back(hd);
     }
     strix_decode_state::Program p{};
+    if (!chain_plan(steps.data(), (uint32_t)steps.size(), h->num_sms, h->smem_optin, &p.geom)) return fail();
     p.h = d->h;
     p.logits = d->logits;
     p.n_steps = (uint32_t)steps.size();
-    p.smem_bytes = smem;
-    if (!d->d_gbar && cudaMalloc(&d->d_gbar, sizeof(uint32_t)) != cudaSuccess) {
-        d->chain_ok = false;
-        return nullptr;
-    }
-    if (const char *e = getenv("STRIX_CHAIN_TRACE")) {
-        // measurement only: the file named by the variable receives the clocks when the state is freed
-        if (!d->d_trace && cudaMalloc(&d->d_trace, 3 * steps.size() * sizeof(unsigned long long)) == cudaSuccess) {
-            cudaMemset(d->d_trace, 0, 3 * steps.size() * sizeof(unsigned long long));
-            d->trace_path = e;
+    if (h->chain_trace && !d->d_trace) {
+        const size_t nb = 3 * steps.size() * sizeof(unsigned long long);
+        if (cudaMalloc(&d->d_trace, nb) == cudaSuccess) {
+            cudaMemset(d->d_trace, 0, nb);
             d->trace_n = (uint32_t)steps.size();
         }
     }
-    if (cudaMalloc(&p.d_steps, steps.size() * sizeof(GemvArgs)) != cudaSuccess ||
-        cudaMemcpy(p.d_steps, steps.data(), steps.size() * sizeof(GemvArgs), cudaMemcpyHostToDevice) != cudaSuccess) {
+    if (cudaMalloc(&p.d_steps, steps.size() * sizeof(ChainStep)) != cudaSuccess ||
+        cudaMemcpy(p.d_steps, steps.data(), steps.size() * sizeof(ChainStep), cudaMemcpyHostToDevice) != cudaSuccess) {
         if (p.d_steps) cudaFree(p.d_steps);
-        d->chain_ok = false;
-        return nullptr;
+        return fail();
     }
     d->programs.push_back(p);
     return &d->programs.back();
@@ -237,8 +308,14 @@ static const strix_decode_state::Program *chain_program(strix_cuda *h, strix_dec
 // Enqueue the whole chain on `s`. Returns 1, or <0 with h->err set.
 static int enqueue_chain(strix_cuda *h, strix_decode_state *d, cudaStream_t s) {
     if (const strix_decode_state::Program *p = chain_program(h, d, s)) {
-        CU_TRY(h, launch_gemv_chain(p->d_steps, p->n_steps, d->cfg.act, d->d_gbar, h->num_sms, p->smem_bytes, d->d_trace, s));
+        CU_TRY(h, launch_chain(p->d_steps, p->n_steps, p->geom, d->d_ctl, h->d_status, h->poll_limit, d->d_trace,
+                               h->num_sms, s));
         return 1;
+    }
+    if (h->world > 1) {
+        // (a row shard cannot run the chain launch by launch: every step needs the other shards' rows)
+        h->err = "decode: the row-sharded chain needs the persistent chain kernel (planning failed, or it is switched off)";
+        return -1;
     }
     const int act = d->cfg.act;
     return walk_chain(d, [&](int nmat, const Resident *const *w, const float *a, const float *b, float eps, int pre,
@@ -284,8 +361,10 @@ int strix_cuda_configure_decode(strix_cuda *h, const strix_gpu_decode_config *cf
                 return 0;
         }
     }
-    if (h->world > 1) return 0;  // a sharded handle holds row shards only; the chain needs whole vectors
     if (cfg->act != STRIX_ACT_F32 && cfg->act != STRIX_ACT_Q8DOT) return 0;
+    // A sharded handle holds row shards only: the chain then runs as the persistent kernel alone (projection
+    // chain with the stand-in, integer-dot form), every rank publishing its rows into all ranks' exchange vectors.
+    if (h->world > 1 && (real_attn || cfg->act != STRIX_ACT_Q8DOT || !h->decode_chain || h->world > GEMV_MAX_PEERS)) return 0;
     CU_TRY(h, cudaSetDevice(h->device));
     auto *d = new strix_decode_state();
     d->cfg = *cfg;
@@ -364,6 +443,21 @@ int strix_cuda_configure_decode(strix_cuda *h, const strix_gpu_decode_config *cf
         if (e == cudaSuccess) e = cudaMalloc(&d->d_pos, 4);
         if (e == cudaSuccess) e = cudaMemset(d->d_pos, 0, 4);
         if (e == cudaSuccess) e = cudaMallocHost(&d->pin_pos, 4);
+    }
+    if (!real_attn && cfg->act == STRIX_ACT_Q8DOT) {
+        // exchange vectors of the chain kernel, one allocation: q | h_a | h_b | act, each 128-byte aligned.
+        // Epoch 0 = never written: the first launch's steps carry epochs 1, 2, ...
+        size_t off = 0;
+        const size_t lens[4] = {qdim, hidden, hidden, ffn};
+        for (int i = 0; i < 4; i++) {
+            d->ll_off[i] = off;
+            off += (lens[i] + 15) & ~(size_t)15;
+        }
+        d->ll_words = std::max<size_t>(off, 16);
+        if (e == cudaSuccess) e = cudaMalloc(&d->ll_block, d->ll_words * 8);
+        if (e == cudaSuccess) e = cudaMemset(d->ll_block, 0, d->ll_words * 8);
+        if (e == cudaSuccess) e = cudaMalloc(&d->d_ctl, 8);
+        if (e == cudaSuccess) e = cudaMemset(d->d_ctl, 0, 8);
     }
     if (e == cudaSuccess) e = cudaMallocHost(&d->pin_h, hidden * sizeof(float));
     if (e == cudaSuccess) e = cudaMallocHost(&d->pin_logits, (size_t)cfg->vocab * sizeof(float));
@@ -576,6 +670,63 @@ int strix_cuda_decode_chain_dev(strix_cuda *h, float *d_h, float *d_logits, void
     return rc;
 }
 
+// Row-sharded groups: this accelerator's exchange block (one device allocation) so that the caller can
+// export it (cudaIpcGetMemHandle) to the other ranks.
+int strix_cuda_decode_exchange_info(strix_cuda *h, void **base, size_t *bytes) {
+    if (!h || !base || !bytes) return -1;
+    h->err.clear();
+    strix_decode_state *d = h->decode;
+    if (!d || !d->ll_block) return 0;
+    *base = d->ll_block;
+    *bytes = d->ll_words * 8;
+    return 1;
+}
+
+// Wires the group: blocks[r] = rank r's exchange block as mapped into this process (blocks[rank] may be null =
+// this accelerator's own). From now on every step publishes its rows into all n blocks.
+int strix_cuda_decode_set_peers(strix_cuda *h, int n, void *const *blocks) {
+    if (!h || !blocks) return -1;
+    h->err.clear();
+    strix_decode_state *d = h->decode;
+    if (!d || !d->ll_block) return 0;
+    if (n != h->world || n > GEMV_MAX_PEERS) {
+        h->err = "decode_set_peers: one block per rank of the group (at most 8)";
+        return -1;
+    }
+    CU_TRY(h, cudaSetDevice(h->device));
+    CU_TRY(h, cudaDeviceSynchronize());
+    for (int r = 0; r < n; r++) {
+        d->peer[r] = (r == h->rank || !blocks[r]) ? d->ll_block : static_cast<unsigned long long *>(blocks[r]);
+        if (r != h->rank && !blocks[r]) {
+            h->err = "decode_set_peers: a null block for another rank";
+            return -1;
+        }
+    }
+    d->n_peer = n;
+    for (auto &p : d->programs) cudaFree(p.d_steps);  // programs built before hold the old destinations
+    d->programs.clear();
+    if (d->exec) {
+        cudaGraphExecDestroy(d->exec);
+        d->exec = nullptr;
+    }
+    d->chain_ok = true;
+    return 1;
+}
+
+// Measurement only: after set_option("chain_trace", 1) the chain kernel's CTA 0 notes the clock
+// (nanoseconds) at each step's start, after its prologue (the wait for the activations included) and after
+// its row groups; this copies out the words of the last launch. Returns the number of steps, 0 without a trace.
+int strix_cuda_decode_trace(strix_cuda *h, unsigned long long *out, size_t cap_words) {
+    if (!h || !out) return -1;
+    h->err.clear();
+    strix_decode_state *d = h->decode;
+    if (!d || !d->d_trace || cap_words < 3u * d->trace_n) return 0;
+    CU_TRY(h, cudaSetDevice(h->device));
+    CU_TRY(h, cudaDeviceSynchronize());
+    CU_TRY(h, cudaMemcpy(out, d->d_trace, 3u * d->trace_n * sizeof(unsigned long long), cudaMemcpyDeviceToHost));
+    return (int)d->trace_n;
+}
+
 // H2D of the hidden state and one replay of the captured chain on the handle's stream (captured on
 // the first call); the logits are then in d->logits.
 static int decode_enqueue_step(strix_cuda *h, strix_decode_state *d, const float *hvec, size_t pos) {
@@ -631,15 +782,16 @@ int strix_cuda_decode_step(strix_cuda *h, const float *hvec, size_t pos, float *
     h->err.clear();
     strix_decode_state *d = h->decode;
     if (!d) return 0;  // not configured: None, the model falls back to per-weight gemv
-    if (logits_cap < d->cfg.vocab) {
+    const size_t n_out = d->head->rows;  // the whole vocabulary, or this accelerator's shard of it
+    if (logits_cap < n_out) {
         h->err = "decode_step: logits buffer too small";
         return -1;
     }
     int rc = decode_enqueue_step(h, d, hvec, pos);
     if (rc < 0) return rc;
-    CU_TRY(h, cudaMemcpyAsync(d->pin_logits, d->logits, (size_t)d->cfg.vocab * sizeof(float), cudaMemcpyDeviceToHost, h->stream));
+    CU_TRY(h, cudaMemcpyAsync(d->pin_logits, d->logits, n_out * sizeof(float), cudaMemcpyDeviceToHost, h->stream));
     if ((rc = decode_finish(h, "decode_step")) < 0) return rc;
-    memcpy(logits, d->pin_logits, (size_t)d->cfg.vocab * sizeof(float));
+    memcpy(logits, d->pin_logits, n_out * sizeof(float));
     return 1;
 }
 

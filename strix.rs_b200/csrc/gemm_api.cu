@@ -43,20 +43,26 @@ static int ensure_scales(strix_cuda *h, Resident *r, cudaStream_t stream) {
     return 1;
 }
 
+// Scratch of the activation quantiser for m token rows of a weight with nb K-blocks.
+static int ensure_quant(strix_cuda *h, size_t m, size_t K, size_t nb) {
+    const size_t n = nb * gemm_x_ld((uint32_t)m);
+    if (ensure_raw(h, h->gm_xq, h->gm_xq_cap, m * K) < 0) return -1;
+    if (ensure_raw(h, h->gm_xs, h->gm_xs_cap, n) < 0) return -1;
+    if (ensure_f32(h, h->gm_xd, n) < 0 || ensure_f32(h, h->gm_xc, n) < 0) return -1;
+    return 1;
+}
+
 // Quantise d_xs[m][in_dim] and run the GEMM into d_y[m][rows]; all scratch from the handle.
 static int gemm_device(strix_cuda *h, Resident *r, const float *d_xs, size_t m, float *d_y, cudaStream_t stream) {
     const size_t K = r->L.in_dim, nb = r->L.nb;
     if (ensure_scales(h, r, stream) < 0) return -1;
-    if (ensure_raw(h, h->gm_xq, h->gm_xq_cap, m * K) < 0) return -1;
-    const size_t ldx = gemm_x_ld((uint32_t)nb);
-    if (ensure_raw(h, h->gm_xs, h->gm_xs_cap, m * ldx) < 0) return -1;
-    if (ensure_f32(h, h->gm_xd, m * ldx) < 0) return -1;
+    if (ensure_quant(h, m, K, nb) < 0) return -1;
     const uint32_t splits = gemm_pick_splits((uint32_t)m, (uint32_t)r->rows, (uint32_t)nb, h->num_sms);
     const size_t wsf = gemm_workspace_floats((uint32_t)m, (uint32_t)r->rows, splits);
     if (wsf && ensure_f32(h, h->gm_part, wsf) < 0) return -1;
-    CU_TRY(h, launch_xquant8_sum(d_xs, h->gm_xq, h->gm_xd.p, h->gm_xs, (uint32_t)m, (uint32_t)nb, stream));
-    CU_TRY(h, launch_gemm_w8a8(r->gemm_codes, r->L, (uint32_t)r->rows, r->scalesT, h->gm_xq, h->gm_xd.p, h->gm_xs, (uint32_t)m,
-                              d_y, h->gm_part.p, splits, h->d_status, stream));
+    CU_TRY(h, launch_xquant8_sum(d_xs, h->gm_xq, h->gm_xd.p, h->gm_xs, h->gm_xc.p, (uint32_t)m, (uint32_t)nb, stream));
+    CU_TRY(h, launch_gemm_w8a8(r->gemm_codes, r->L, (uint32_t)r->rows, r->scalesT, h->gm_xq, h->gm_xd.p, h->gm_xs, h->gm_xc.p,
+                              (uint32_t)m, d_y, h->gm_part.p, splits, 0, nullptr, h->d_status, stream));
     return 1;
 }
 
@@ -100,34 +106,86 @@ int strix_cuda_prefill_q8_gemm_dev(strix_cuda *h, const char *key, const float *
     return gemm_device(h, r, d_xs, m, d_y, static_cast<cudaStream_t>(stream));
 }
 
-int strix_cuda_debug_block_isums(strix_cuda *h, const char *key, const float *xs, size_t m, int32_t *out, size_t out_cap) {
+// mode 0: the GEMM's tensor-core kernel with the epilogue that stores its int32 block sums; mode 1: a plain
+// integer loop (no tensor cores) over the same codes. `splits`: 0 = as the product path picks, else forced.
+static int block_isums(strix_cuda *h, const char *key, const float *xs, size_t m, int32_t *out, size_t out_cap, bool tensor,
+                       uint32_t splits) {
     if (!h || !key || !xs || !out) return -1;
     h->err.clear();
     Resident *r = find_weight_mut(h, key);
     if (!r || r->fmt != FMT_Q8_0) return 0;
     const size_t K = r->L.in_dim, nb = r->L.nb, total = m * r->rows * nb;
     if (out_cap < total) {
-        h->err = "debug_block_isums: output too small";
+        h->err = "debug isums: output too small";
         return -1;
     }
     if (total == 0) return 1;
     CU_TRY(h, cudaSetDevice(h->device));
-    if (ensure_f32(h, h->gm_x, m * K) < 0 || ensure_raw(h, h->gm_xq, h->gm_xq_cap, m * K) < 0 ||
-        ensure_raw(h, h->gm_xs, h->gm_xs_cap, m * gemm_x_ld((uint32_t)nb)) < 0 ||
-        ensure_f32(h, h->gm_xd, m * gemm_x_ld((uint32_t)nb)) < 0)
-        return -1;
+    if (ensure_f32(h, h->gm_x, m * K) < 0 || ensure_quant(h, m, K, nb) < 0) return -1;
+    if (tensor && ensure_scales(h, r, h->stream) < 0) return -1;
+    if (tensor && splits == 0) splits = gemm_pick_splits((uint32_t)m, (uint32_t)r->rows, (uint32_t)nb, h->num_sms);
     int32_t *d_out = nullptr;
     CU_TRY(h, cudaMalloc(&d_out, total * sizeof(int32_t)));
-    cudaError_t e = cudaMemcpyAsync(h->gm_x.p, xs, m * K * sizeof(float), cudaMemcpyHostToDevice, h->stream);
-    if (e == cudaSuccess) e = launch_xquant8_sum(h->gm_x.p, h->gm_xq, h->gm_xd.p, h->gm_xs, (uint32_t)m, (uint32_t)nb, h->stream);
-    if (e == cudaSuccess) e = launch_block_isums(r->gemm_codes, h->gm_xq, d_out, r->L, (uint32_t)m, (uint32_t)r->rows, h->stream);
+    cudaError_t e = cudaMemsetAsync(d_out, 0xff, total * sizeof(int32_t), h->stream);  // an entry nobody writes shows as -1
+    if (e == cudaSuccess) e = cudaMemcpyAsync(h->gm_x.p, xs, m * K * sizeof(float), cudaMemcpyHostToDevice, h->stream);
+    if (e == cudaSuccess)
+        e = launch_xquant8_sum(h->gm_x.p, h->gm_xq, h->gm_xd.p, h->gm_xs, h->gm_xc.p, (uint32_t)m, (uint32_t)nb, h->stream);
+    if (e == cudaSuccess) {
+        if (tensor)
+            e = launch_gemm_w8a8(r->gemm_codes, r->L, (uint32_t)r->rows, r->scalesT, h->gm_xq, h->gm_xd.p, h->gm_xs, h->gm_xc.p,
+                                 (uint32_t)m, nullptr, nullptr, splits, 1, d_out, h->d_status, h->stream);
+        else
+            e = launch_block_isums(r->gemm_codes, h->gm_xq, d_out, r->L, (uint32_t)m, (uint32_t)r->rows, h->stream);
+    }
     if (e == cudaSuccess) e = cudaMemcpyAsync(out, d_out, total * sizeof(int32_t), cudaMemcpyDeviceToHost, h->stream);
+    if (e == cudaSuccess) e = cudaMemcpyAsync(&h->status_host, h->d_status, 4, cudaMemcpyDeviceToHost, h->stream);
     if (e == cudaSuccess) e = cudaStreamSynchronize(h->stream);
     cudaFree(d_out);
     if (e != cudaSuccess) {
-        h->err = std::string("debug_block_isums: ") + cudaGetErrorString(e);
+        h->err = std::string("debug isums: ") + cudaGetErrorString(e);
         return -1;
     }
+    if (h->status_host != 0) {
+        h->err = "debug isums: device status " + std::to_string(h->status_host) + " (a bounded wait ran out)";
+        cudaMemsetAsync(h->d_status, 0, 4, h->stream);
+        return -2;
+    }
+    return 1;
+}
+
+int strix_cuda_debug_block_isums(strix_cuda *h, const char *key, const float *xs, size_t m, int32_t *out, size_t out_cap) {
+    return block_isums(h, key, xs, m, out, out_cap, false, 0);
+}
+
+int strix_cuda_debug_gemm_isums(strix_cuda *h, const char *key, const float *xs, size_t m, uint32_t splits, int32_t *out,
+                                size_t out_cap) {
+    return block_isums(h, key, xs, m, out, out_cap, true, splits);
+}
+
+// Measurement: quantises d_xs[m][in_dim] once, then launches the GEMM kernel `reps` times in `mode`
+// (0 the product into d_y; 2 without the accumulator drain; 3 without drain and loads) on `stream`.
+int strix_cuda_debug_gemm_mode_dev(strix_cuda *h, const char *key, const float *d_xs, size_t m, float *d_y, int mode,
+                                   int reps, void *stream) {
+    if (!h || !key || !d_xs || !d_y) return -1;
+    h->err.clear();
+    if (mode != 0 && mode != 2 && mode != 3) {
+        h->err = "debug_gemm_mode_dev: mode 0, 2 or 3";
+        return -1;
+    }
+    Resident *r = find_weight_mut(h, key);
+    if (!r || r->fmt != FMT_Q8_0) return 0;
+    if (m == 0 || reps <= 0) return 1;
+    CU_TRY(h, cudaSetDevice(h->device));
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    const size_t K = r->L.in_dim, nb = r->L.nb;
+    if (ensure_scales(h, r, st) < 0 || ensure_quant(h, m, K, nb) < 0) return -1;
+    const uint32_t splits = gemm_pick_splits((uint32_t)m, (uint32_t)r->rows, (uint32_t)nb, h->num_sms);
+    const size_t wsf = gemm_workspace_floats((uint32_t)m, (uint32_t)r->rows, splits);
+    if (wsf && ensure_f32(h, h->gm_part, wsf) < 0) return -1;
+    CU_TRY(h, launch_xquant8_sum(d_xs, h->gm_xq, h->gm_xd.p, h->gm_xs, h->gm_xc.p, (uint32_t)m, (uint32_t)nb, st));
+    for (int i = 0; i < reps; i++)
+        CU_TRY(h, launch_gemm_w8a8(r->gemm_codes, r->L, (uint32_t)r->rows, r->scalesT, h->gm_xq, h->gm_xd.p, h->gm_xs,
+                                  h->gm_xc.p, (uint32_t)m, d_y, h->gm_part.p, splits, mode, nullptr, h->d_status, st));
     return 1;
 }
 

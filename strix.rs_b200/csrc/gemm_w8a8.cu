@@ -22,10 +22,18 @@
 //     acc[n] += d_w[n] * (d_x[m] * isum) as packed f32x2 ops, 32 columns per thread;
 //   * int32 -> f32 costs no conversion instruction: a buffer is pre-loaded (tcgen05.st) with
 //     the bit pattern of 1.5 * 2^23 and the MMA ACCUMULATES into it, so what comes back is
-//     the float 12582912 + isum; one packed subtract recovers isum exactly;
-//   * weight codes are resident as q + 128 (unsigned bytes): the MMA runs u8 x s8, and the
-//     128 * sum(x codes) that this adds per (token, K-block) rides on the same subtract
-//     (12582912 + 128 * sum is an exact f32);
+//     the float r = 12582912 + isum + 128 * sum(x codes) (weight codes are resident as q + 128, the
+//     MMA runs u8 x s8). The quantiser leaves c = -d_x * (12582912 + 128 * sum) per (token, K-block),
+//     so d_x * isum = fma(d_x, r, c): TWO packed FMAs per pair of elements (this one and the
+//     accumulation with d_w) instead of subtract, multiply, FMA. c is rounded once, which moves
+//     each block term by at most 0.75 d_x, i.e. ~1e-5 of a typical block sum, against a contract of
+//     1e-3; the bit-exact tier (MODE 1 below) recovers isum with the exact subtract;
+//   * the kernel is a template over MODE: 0 = the product path; 1 = the SAME producer / MMA / TMEM
+//     pipeline with an epilogue that stores every int32 block sum isum[m][n][kb] (the bit-exact
+//     tier of the contract, checked on the tensor-core path itself); 2 = the epilogue only hands
+//     the buffers back (no TMEM read, no arithmetic): what the TMA + tensor pipeline sustains
+//     without the drain; 3 = as 2 and no loads either (operands stay whatever shared memory
+//     holds): the issue rate of tcgen05.mma kind::i8 alone, the measured int8 peak;
 //   * split-K (grid.z) writes f32 partials that a second kernel adds in a fixed
 //     order: reproducible, unlike the reference's atomicAdd;
 //   * every wait is bounded; after a timeout nothing waits again, the status word
@@ -42,7 +50,7 @@ constexpr uint32_t GM_KB_STAGE = 4;               // K-blocks (of 32) per shared
 constexpr uint32_t GM_STAGES = 5;
 constexpr uint32_t GM_TBUF = 4;                   // TMEM accumulator buffers of GM_BN columns
 constexpr uint32_t GM_A_BYTES = GM_BM * 128, GM_B_BYTES = GM_BN * 128, GM_S_BYTES = GM_KB_STAGE * GM_BN * 4;
-constexpr uint32_t GM_XD_BYTES = GM_BM * GM_KB_STAGE * 4;  // per token: 4 activation scales / 4 code sums
+constexpr uint32_t GM_XD_BYTES = GM_BM * GM_KB_STAGE * 4;  // [K-block][token]: activation scales / un-bias terms (MODE 1: code sums)
 constexpr uint32_t GM_OFF_S = GM_A_BYTES + GM_B_BYTES, GM_OFF_XD = GM_OFF_S + GM_S_BYTES, GM_OFF_XS = GM_OFF_XD + GM_XD_BYTES;
 constexpr uint32_t GM_STAGE_BYTES = GM_OFF_XS + GM_XD_BYTES;  // 38912 = 38 KB
 constexpr uint32_t GM_EPI_WARPS = 16, GM_EPI_WARP0 = 2, GM_THREADS = (GM_EPI_WARP0 + GM_EPI_WARPS) * 32;
@@ -123,9 +131,11 @@ struct GemmArgs {
     float *y;           // [splits][M][ldy] (splits > 1: partials) or [M][ldy]
     uint32_t M, N, nb, ldy, ldx;  // ldx: leading dimension of xs / xd (nb rounded up to 4: TMA strides are multiples of 16 B)
     uint32_t kb_per_split;  // K-blocks per grid.z slice, a multiple of GM_KB_STAGE
+    int32_t *dump;          // MODE 1: isum[M][N][nb]
     uint32_t *status;
 };
 
+template <int MODE>
 __global__ void __launch_bounds__(GM_THREADS, 1)
 gemm_w8a8_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_w,
                  const __grid_constant__ CUtensorMap map_s, const __grid_constant__ CUtensorMap map_xd,
@@ -181,12 +191,16 @@ gemm_w8a8_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
                     *ctl = 1;
                 uint8_t *st = stages + s * GM_STAGE_BYTES;
                 const uint32_t kb = kb0 + it * GM_KB_STAGE;
+                if (MODE == 3) {
+                    mbar_arrive(&full[s]);  // nothing is loaded: the phase completes at once
+                    continue;
+                }
                 mbar_arrive_expect_tx(&full[s], GM_STAGE_BYTES);
                 tma_load_2d(st, &map_x, (int)(kb * 32u), (int)m0, &full[s]);
                 tma_load_2d(st + GM_A_BYTES, &map_w, (int)(kb * 32u), (int)n0, &full[s]);
                 tma_load_2d(st + GM_OFF_S, &map_s, (int)n0, (int)kb, &full[s]);
-                tma_load_2d(st + GM_OFF_XD, &map_xd, (int)kb, (int)m0, &full[s]);
-                tma_load_2d(st + GM_OFF_XS, &map_xs, (int)kb, (int)m0, &full[s]);
+                tma_load_2d(st + GM_OFF_XD, &map_xd, (int)m0, (int)kb, &full[s]);
+                tma_load_2d(st + GM_OFF_XS, &map_xs, (int)m0, (int)kb, &full[s]);
             }
         }
     } else if (warp == 1) {
@@ -238,45 +252,64 @@ gemm_w8a8_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
             if (!*ctl && !mbar_wait_bounded(&full[s], (it / GM_STAGES) & 1u, A.status)) *ctl = 1;
             const uint8_t *stg = stages + s * GM_STAGE_BYTES;
             const float *sw = reinterpret_cast<const float *>(stg + GM_OFF_S) + cq * 32u;
-            const float *sxd = reinterpret_cast<const float *>(stg + GM_OFF_XD) + trow * GM_KB_STAGE;
-            const int32_t *sxs = reinterpret_cast<const int32_t *>(stg + GM_OFF_XS) + trow * GM_KB_STAGE;
+            // [K-block][token]: consecutive lanes read consecutive words
+            const float *sxd = reinterpret_cast<const float *>(stg + GM_OFF_XD) + trow;
+            const float *sxc = reinterpret_cast<const float *>(stg + GM_OFF_XS) + trow;
+            const uint32_t nkb = min(GM_KB_STAGE, kb1 - kb);  // uniform across the CTA
 #pragma unroll 1
-            for (uint32_t j = 0; j < GM_KB_STAGE; j++) {
-                if (kb + j < kb1) {  // uniform across the CTA
-                    // this token's scale and code sum for the K-block (rows past M were zero-filled by TMA)
-                    const float dxj = sxd[j];
-                    const float unm = -(12582912.0f + 128.0f * (float)sxs[j]);  // exact: an integer below 2^24
+            for (uint32_t j = 0; j < nkb; j++) {
+                if (MODE >= 2) {
+                    // measurement: the buffer goes straight back (no TMEM read, no arithmetic)
                     if (!*ctl && !mbar_wait_bounded(&tfull[j], it & 1u, A.status)) *ctl = 1;
                     tc_fence_after();
-                    uint32_t r[32];
-                    tc_ld32(taddr0 + j * GM_BN, r);
-                    tc_wait_ld();
-                    tc_rearm32(taddr0 + j * GM_BN, magic);  // completes while the arithmetic below runs
-                    const float2 unmagic = make_float2(unm, unm);
-                    // r holds the floats 12582912 + isum + 128 * xs;  acc[n] += d_w[n] * (d_x * isum)
-                    const float2 c0v = make_float2(dxj, dxj);
+                    tc_fence_before();
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(&tempty[j]);
+                    continue;
+                }
+                // this token's scale and un-bias term for the K-block (rows past M were zero-filled by TMA)
+                const float dxj = sxd[j * GM_BM];
+                const float cj = sxc[j * GM_BM];
+                if (!*ctl && !mbar_wait_bounded(&tfull[j], it & 1u, A.status)) *ctl = 1;
+                tc_fence_after();
+                uint32_t r[32];
+                tc_ld32(taddr0 + j * GM_BN, r);
+                tc_wait_ld();
+                tc_rearm32(taddr0 + j * GM_BN, magic);  // completes while the arithmetic below runs
+                if (MODE == 1) {
+                    // bit-exact tier: r = 12582912 + isum + 128 * sum(x codes), all integers below 2^24, so the
+                    // subtraction is exact; the K-block's code sum arrives where the product path has c
+                    const float unm = -(12582912.0f + 128.0f * (float)__float_as_int(cj));
+                    if (m_ok) {
+#pragma unroll
+                        for (int q = 0; q < 32; q++) {
+                            const uint32_t n = n0 + cq * 32u + (uint32_t)q;
+                            if (n < A.N) A.dump[((uint64_t)m * A.N + n) * A.nb + kb + j] = (int32_t)(__uint_as_float(r[q]) + unm);
+                        }
+                    }
+                } else {
+                    // acc[n] += d_w[n] * (d_x * isum), d_x * isum = fma(d_x, r, c)
+                    const float2 dx2 = make_float2(dxj, dxj), c2 = make_float2(cj, cj);
                     const float4 *swj = reinterpret_cast<const float4 *>(sw + j * GM_BN);
 #pragma unroll
                     for (int q = 0; q < 8; q++) {
                         const float4 w4 = swj[q];
-                        float2 g0 = __fadd2_rn(make_float2(__uint_as_float(r[4 * q]), __uint_as_float(r[4 * q + 1])), unmagic);
-                        float2 g1 = __fadd2_rn(make_float2(__uint_as_float(r[4 * q + 2]), __uint_as_float(r[4 * q + 3])), unmagic);
-                        g0 = __fmul2_rn(c0v, g0);
-                        g1 = __fmul2_rn(c0v, g1);
+                        const float2 g0 = __ffma2_rn(dx2, make_float2(__uint_as_float(r[4 * q]), __uint_as_float(r[4 * q + 1])), c2);
+                        const float2 g1 = __ffma2_rn(dx2, make_float2(__uint_as_float(r[4 * q + 2]), __uint_as_float(r[4 * q + 3])), c2);
                         acc[2 * q] = __ffma2_rn(make_float2(w4.x, w4.y), g0, acc[2 * q]);
                         acc[2 * q + 1] = __ffma2_rn(make_float2(w4.z, w4.w), g1, acc[2 * q + 1]);
                     }
-                    tc_wait_st();
-                    tc_fence_before();
-                    __syncwarp();
-                    if (lane == 0) mbar_arrive(&tempty[j]);  // the MMA warp may accumulate into the buffer again
                 }
+                tc_wait_st();
+                tc_fence_before();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(&tempty[j]);  // the MMA warp may accumulate into the buffer again
             }
             __syncwarp();
             if (lane == 0) mbar_arrive(&empty[s]);  // done with the stage's scale rows
         }
         // write this thread's 32 outputs (one token, 32 consecutive weight rows)
-        if (m_ok) {
+        if (MODE == 0 && m_ok) {
             float *yrow = A.y + ((uint64_t)blockIdx.z * A.M + m) * A.ldy + n0 + cq * 32u;
             const uint32_t nleft = (A.N > n0 + cq * 32u) ? A.N - (n0 + cq * 32u) : 0u;
             if (nleft >= 32u && (A.ldy & 3u) == 0u) {
@@ -313,13 +346,16 @@ __global__ void splitk_reduce_kernel(const float *__restrict__ part, float *__re
     y[(uint64_t)m * N + n] = s;
 }
 
-// Activation quantiser for the GEMM (xquant8_rows, kernels.rs:1000-1013) that also emits the
-// per-block sum of the codes. One warp per 32-element block.
+// Activation quantiser for the GEMM (xquant8_rows, kernels.rs:1000-1013) that also emits, per block, the
+// sum of the codes and the un-bias term the GEMM's epilogue adds: c = -d * (12582912 + 128 * sum).
+// One warp per 32-element block. d / xs / xc are [nb][ldm] (K-block major: a GEMM stage fetches the
+// values of 128 consecutive tokens for 4 K-blocks as one box).
 __global__ void xquant8_sum_kernel(const float *__restrict__ x, int8_t *__restrict__ q, float *__restrict__ d,
-                                   int32_t *__restrict__ xs, uint32_t nblk, uint32_t nb, uint32_t ldx) {
+                                   int32_t *__restrict__ xs, float *__restrict__ xc, uint32_t nblk, uint32_t nb,
+                                   uint32_t ldm) {
     const uint32_t blk = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31u;
     if (blk >= nblk) return;
-    const uint32_t o = (blk / nb) * ldx + blk % nb;  // [row][ldx] with ldx >= nb
+    const uint32_t o = (blk % nb) * ldm + blk / nb;
     const float v = x[(uint64_t)blk * 32u + lane];
     float amax = fabsf(v);
 #pragma unroll
@@ -335,6 +371,7 @@ __global__ void xquant8_sum_kernel(const float *__restrict__ x, int8_t *__restri
     if (lane == 0) {
         d[o] = sc;
         xs[o] = sum;
+        xc[o] = -sc * (12582912.0f + 128.0f * (float)sum);  // the sum in brackets is an integer below 2^24: exact
     }
 }
 
@@ -406,16 +443,17 @@ cudaError_t launch_scales_transpose(const uint8_t *d_res, float *d_out, const Ro
     return cudaGetLastError();
 }
 
-uint32_t gemm_x_ld(uint32_t nb) { return (nb + 3u) & ~3u; }
+uint32_t gemm_x_ld(uint32_t m) { return (m + 3u) & ~3u; }
 
-// x[m][nb*32] -> q[m][nb*32] int8, d[m][ldx] f32, xs[m][ldx] int32 with ldx = gemm_x_ld(nb)
-cudaError_t launch_xquant8_sum(const float *d_x, int8_t *d_q, float *d_d, int32_t *d_xs, uint32_t m, uint32_t nb,
-                               cudaStream_t stream) {
+// x[m][nb*32] -> q[m][nb*32] int8 and, K-block major with ldm = gemm_x_ld(m): d[nb][ldm] f32 block scales,
+// xs[nb][ldm] int32 code sums, xc[nb][ldm] f32 un-bias terms
+cudaError_t launch_xquant8_sum(const float *d_x, int8_t *d_q, float *d_d, int32_t *d_xs, float *d_xc, uint32_t m,
+                               uint32_t nb, cudaStream_t stream) {
     const uint64_t nblk = (uint64_t)m * nb;
     if (nblk == 0) return cudaSuccess;
     const uint32_t T = 256, per = T / 32;
-    xquant8_sum_kernel<<<(unsigned)((nblk + per - 1) / per), T, 0, stream>>>(d_x, d_q, d_d, d_xs, (uint32_t)nblk, nb,
-                                                                               gemm_x_ld(nb));
+    xquant8_sum_kernel<<<(unsigned)((nblk + per - 1) / per), T, 0, stream>>>(d_x, d_q, d_d, d_xs, d_xc, (uint32_t)nblk, nb,
+                                                                               gemm_x_ld(m));
     return cudaGetLastError();
 }
 
@@ -428,7 +466,17 @@ cudaError_t launch_block_isums(const uint8_t *d_res, const int8_t *d_xq, int32_t
 }
 
 cudaError_t gemm_prepare_device() {
-    return cudaFuncSetAttribute(gemm_w8a8_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)GM_SMEM);
+    cudaError_t e = cudaFuncSetAttribute(gemm_w8a8_kernel<0>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)GM_SMEM);
+    if (e == cudaSuccess) e = cudaFuncSetAttribute(gemm_w8a8_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)GM_SMEM);
+    if (e == cudaSuccess) e = cudaFuncSetAttribute(gemm_w8a8_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)GM_SMEM);
+    if (e == cudaSuccess) e = cudaFuncSetAttribute(gemm_w8a8_kernel<3>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)GM_SMEM);
+    // the small kernels of the GEMM path: asking for their attributes makes the driver load their code now
+    // (module loading is lazy), so that a later call that must not allocate finds everything in place
+    cudaFuncAttributes fa;
+    if (e == cudaSuccess) e = cudaFuncGetAttributes(&fa, xquant8_sum_kernel);
+    if (e == cudaSuccess) e = cudaFuncGetAttributes(&fa, scales_transpose_kernel);
+    if (e == cudaSuccess) e = cudaFuncGetAttributes(&fa, splitk_reduce_kernel);
+    return e;
 }
 
 uint32_t gemm_pick_splits(uint32_t M, uint32_t rows, uint32_t nb, int num_sms) {
@@ -450,30 +498,36 @@ size_t gemm_workspace_floats(uint32_t M, uint32_t rows, uint32_t splits) {
 }
 
 // d_y[M][rows] = W8A8 GEMM. d_part: workspace of gemm_workspace_floats() floats when splits > 1.
+// mode: 0 = the product; 1 = int32 block sums into d_dump[M][rows][nb] (d_y untouched); 2, 3 = measurement
+// (no drain / no drain and no loads; nothing is written).
 cudaError_t launch_gemm_w8a8(const uint8_t *d_res, const RowLayout &L, uint32_t rows, const float *d_scalesT,
-                             const int8_t *d_xq, const float *d_xd, const int32_t *d_xs, uint32_t M, float *d_y,
-                             float *d_part, uint32_t splits, uint32_t *d_status, cudaStream_t stream) {
+                             const int8_t *d_xq, const float *d_xd, const int32_t *d_xs, const float *d_xc, uint32_t M,
+                             float *d_y, float *d_part, uint32_t splits, int mode, int32_t *d_dump, uint32_t *d_status,
+                             cudaStream_t stream) {
     if (M == 0 || rows == 0) return cudaSuccess;
     CUtensorMap mx, mw, ms, mxd, mxs;
-    const uint32_t lds = gemm_scales_ld(rows), ldx = gemm_x_ld(L.nb);
-    // activations: [M][K] int8, K innermost; weights: [rows][K] bytes (codes as q + 128), K innermost
-    // are its codes; scales: [nb][lds] f32. Coordinates past a dimension read as zero.
+    const uint32_t lds = gemm_scales_ld(rows), ldm = gemm_x_ld(M);
+    // activations: [M][K] int8, K innermost; weights: [rows][K] bytes (codes as q + 128), K innermost;
+    // weight scales: [nb][lds] f32; token scales and un-bias terms (mode 1: code sums): [nb][ldm].
+    // Coordinates past a dimension read as zero.
+    const void *fifth = mode == 1 ? (const void *)d_xs : (const void *)d_xc;
     if (!make_map_2d(&mx, CU_TENSOR_MAP_DATA_TYPE_UINT8, const_cast<int8_t *>(d_xq), L.in_dim, M, L.in_dim, 128, GM_BM,
                      CU_TENSOR_MAP_SWIZZLE_128B) ||
         !make_map_2d(&mw, CU_TENSOR_MAP_DATA_TYPE_UINT8, const_cast<uint8_t *>(d_res), L.in_dim, rows, L.in_dim, 128,
                      GM_BN, CU_TENSOR_MAP_SWIZZLE_128B) ||
         !make_map_2d(&ms, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, const_cast<float *>(d_scalesT), lds, L.nb, (uint64_t)lds * 4,
                      GM_BN, GM_KB_STAGE, CU_TENSOR_MAP_SWIZZLE_NONE) ||
-        !make_map_2d(&mxd, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, const_cast<float *>(d_xd), L.nb, M, (uint64_t)ldx * 4,
-                     GM_KB_STAGE, GM_BM, CU_TENSOR_MAP_SWIZZLE_NONE) ||
-        !make_map_2d(&mxs, CU_TENSOR_MAP_DATA_TYPE_INT32, const_cast<int32_t *>(d_xs), L.nb, M, (uint64_t)ldx * 4,
-                     GM_KB_STAGE, GM_BM, CU_TENSOR_MAP_SWIZZLE_NONE))
+        !make_map_2d(&mxd, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, const_cast<float *>(d_xd), ldm, L.nb, (uint64_t)ldm * 4,
+                     GM_BM, GM_KB_STAGE, CU_TENSOR_MAP_SWIZZLE_NONE) ||
+        !make_map_2d(&mxs, CU_TENSOR_MAP_DATA_TYPE_INT32, const_cast<void *>(fifth), ldm, L.nb, (uint64_t)ldm * 4,
+                     GM_BM, GM_KB_STAGE, CU_TENSOR_MAP_SWIZZLE_NONE))
         return cudaErrorInvalidValue;
     GemmArgs a{};
     a.M = M;
     a.N = rows;
     a.nb = L.nb;
-    a.ldx = ldx;
+    a.ldx = ldm;
+    a.dump = d_dump;
     a.status = d_status;
     const uint32_t stages = (L.nb + GM_KB_STAGE - 1) / GM_KB_STAGE;
     if (splits < 1) splits = 1;
@@ -488,10 +542,16 @@ cudaError_t launch_gemm_w8a8(const uint8_t *d_res, const RowLayout &L, uint32_t 
         a.ldy = rows;
     }
     dim3 grid((rows + GM_BN - 1) / GM_BN, (M + GM_BM - 1) / GM_BM, splits);
-    gemm_w8a8_kernel<<<grid, GM_THREADS, GM_SMEM, stream>>>(mx, mw, ms, mxd, mxs, a);
+    switch (mode) {
+        case 0: gemm_w8a8_kernel<0><<<grid, GM_THREADS, GM_SMEM, stream>>>(mx, mw, ms, mxd, mxs, a); break;
+        case 1: gemm_w8a8_kernel<1><<<grid, GM_THREADS, GM_SMEM, stream>>>(mx, mw, ms, mxd, mxs, a); break;
+        case 2: gemm_w8a8_kernel<2><<<grid, GM_THREADS, GM_SMEM, stream>>>(mx, mw, ms, mxd, mxs, a); break;
+        case 3: gemm_w8a8_kernel<3><<<grid, GM_THREADS, GM_SMEM, stream>>>(mx, mw, ms, mxd, mxs, a); break;
+        default: return cudaErrorInvalidValue;
+    }
     cudaError_t e = cudaGetLastError();
     if (e != cudaSuccess) return e;
-    if (splits > 1) {
+    if (mode == 0 && splits > 1) {
         const uint64_t total = (uint64_t)M * rows;
         splitk_reduce_kernel<<<(unsigned)((total + 255) / 256), 256, 0, stream>>>(d_part, d_y, M, rows, lds, splits);
         e = cudaGetLastError();

@@ -74,35 +74,100 @@ struct GemvArgs {
     uint32_t *status;
 };
 
+// Planning knobs of one accelerator (strix_cuda_set_option; the defaults are what the planner picks).
+struct GemvTune {
+    uint32_t digits_rule = 1;  // Q6_K with one f32 row as three int8 digit rows: 0 never, 1 for in_dim <= 8192, 2 whenever it fits
+    uint32_t force_wc = 0, force_ct = 0, force_sk = 0;  // warps per row group / blocks per stage / stages per slot (0 = planned)
+    uint32_t pdl = 1;          // programmatic stream serialization between GEMV launches
+    uint32_t debug = 0;        // measurement only: bit 0 stream the tiles without arithmetic, bit 1 empty launch,
+                               // bit 2 stop after the activation prologue
+};
+
 // Fills the launch geometry (rows_per_tile .. smem_bytes, tile0 of each matrix)
 // from L, mat[].rows and the device's SM count. Returns false when in_dim is
 // too large for the shared-memory pipeline.
-bool gemv_plan(GemvArgs &a, int num_sms, size_t smem_optin);
+bool gemv_plan(GemvArgs &a, int num_sms, size_t smem_optin, const GemvTune &tune);
 cudaError_t gemv_prepare_device(size_t smem_optin);  // opt in to large dynamic shared memory, once per device
 cudaError_t launch_gemv(const GemvArgs &a, cudaStream_t stream);
-// A chain of steps (each the outputs of the one before it as activation) in one cooperative launch:
-// plan fills the shared geometry of steps[0..n) on the host; the launch takes the same array on the device.
-bool gemv_chain_plan(GemvArgs *steps, uint32_t n, int num_sms, size_t smem_optin, uint32_t *smem_bytes);
-// d_trace: null, or 3 * n_steps device words that receive CTA 0's clock after each step's barrier,
-// prologue and row groups (measurement only).
-cudaError_t launch_gemv_chain(const GemvArgs *d_steps, uint32_t n_steps, int act, uint32_t *d_gbar, int num_sms,
-                              uint32_t smem_bytes, unsigned long long *d_trace, cudaStream_t stream);
+// ---- step lists in one persistent launch (chain.cu) ------------------------------------------
+// A list of GEMV steps run by ONE cooperative kernel (one CTA per SM): the producer warp of every CTA
+// streams the weights of step after step through one ring of stages without ever waiting for another
+// CTA, while the consumer warps run the steps in order. A step whose activation is the output of an
+// earlier step reads it from an EXCHANGE VECTOR: 8-byte entries {f32 value, epoch}, written by the
+// step that produces them (into the vector of every rank when the rows are sharded over GPUs) and
+// polled by the consumers until every entry carries the epoch of this launch's producing step - the
+// flag travels with the data, so there is no grid barrier, no fence and, across GPUs, no collective.
+constexpr int CHAIN_PART_SLOTS = 12;    // row groups whose per-warp partial sums wait in shared memory for one reduction
+constexpr int CHAIN_ACT_DIGITS = 2;     // ChainStep::act: one f32 row as three int8 digit rows (Q6_K)
+constexpr uint32_t CHAIN_MAX_STAGES = 16;
+constexpr uint32_t CHAIN_POLL_LIMIT = 1u << 21;  // default bound of a wait on an exchange vector (about a second)
+
+struct ChainMat {
+    const uint8_t *w;   // resident rows of this accelerator's shard
+    uint32_t rows;      // rows held here
+    uint32_t item0;     // index of this matrix's first row group in the step's item list
+    uint32_t row_base;  // first global row of the shard: entries row_base + r of res_ll / out_ll belong to local row r
+    float *y;           // plain output [rows], or null
+    const float *res;   // plain residual [rows] added to the output, or null
+    const unsigned long long *res_ll;             // residual taken from an exchange vector, or null
+    unsigned long long *out_ll[GEMV_MAX_PEERS];   // exchange vectors the rows are published into (every rank's, own included)
+    uint32_t n_out_ll;
+};
+
+struct ChainStep {
+    ChainMat mat[GEMV_MAX_MATS];
+    int nmat;
+    RowLayout L;
+    int act;   // STRIX_ACT_F32, STRIX_ACT_Q8DOT or CHAIN_ACT_DIGITS
+    int pre;   // STRIX_PRE_* applied to the activation (an exchange-vector input takes NONE or RMSNORM)
+    int pair;  // 0, or STRIX_PRE_SWIGLU / STRIX_PRE_GEGLU: mat[0] = gate, mat[1] = up (same rows); a work item is row
+               // group g of both, and what mat[0]'s outputs receive is act(gate) * up (the next step's activation)
+    const float *a, *b;           // plain activation (null with a_ll) / norm weight or up vector
+    const unsigned long long *a_ll;  // activation as an exchange vector of in_dim entries, or null
+    uint32_t in_step, res_step;   // steps of this list whose outputs a_ll / res_ll hold
+    float eps;
+    // filled by chain_plan:
+    uint32_t n_items;      // work items: row groups over all matrices (pairs count once)
+    uint32_t chunk_tiles;  // GGUF blocks of K per stage (per matrix of a pair)
+    uint32_t n_chunks;     // stages per work item
+    uint32_t rot;          // CTA that takes the step's first item
+};
+
+struct ChainGeom {
+    uint32_t n_stages, stage_bytes, stage_off, x_off, smem_bytes;
+};
+// Fills the geometry of steps[0..n) and the launch-wide ring; false when a step cannot run this way
+// (activation operands too large for shared memory, an exchange-vector input with an unsupported form).
+bool chain_plan(ChainStep *steps, uint32_t n, int num_sms, size_t smem_optin, ChainGeom *geom);
+cudaError_t chain_prepare_device(size_t smem_optin);
+// d_steps: the planned list in device memory. d_ctl: two words {epoch base, exit ticket}, zero-initialised once
+// and then owned by the launches (each adds n_steps to the base when its last CTA leaves). d_trace: null, or
+// 3 * n_steps device words that receive CTA 0's clock at each step's start, after its prologue and after its
+// row groups (measurement only). poll_limit: bound of every wait on an exchange vector, in polls.
+cudaError_t launch_chain(const ChainStep *d_steps, uint32_t n_steps, const ChainGeom &geom, uint32_t *d_ctl,
+                         uint32_t *d_status, uint32_t poll_limit, unsigned long long *d_trace, int num_sms,
+                         cudaStream_t stream);
 
 // ---- W8A8 prefill GEMM (tcgen05 int8 MMA) ----------------------------------
 cudaError_t gemm_prepare_device();
+cudaError_t noalloc_prepare_device(int device);  // gemm_noalloc.cu: materialises the fixed scratch array on the current device
 uint32_t gemm_scales_ld(uint32_t rows);  // leading dimension (floats) of the transposed f32 scale plane
 cudaError_t launch_scales_transpose(const uint8_t *d_res, float *d_out, const RowLayout &L, uint32_t rows,
                                     cudaStream_t stream);  // d_res: the resident (tile-major) weight
-uint32_t gemm_x_ld(uint32_t nb);  // leading dimension of the per-token scale / code-sum arrays
-cudaError_t launch_xquant8_sum(const float *d_x, int8_t *d_q, float *d_d, int32_t *d_xs, uint32_t m, uint32_t nb,
-                               cudaStream_t stream);
+uint32_t gemm_x_ld(uint32_t m);  // leading dimension (tokens) of the K-block-major per-token arrays
+// x[m][nb*32] -> q int8 [m][nb*32]; block scales d, code sums xs and un-bias terms xc, each [nb][gemm_x_ld(m)]
+cudaError_t launch_xquant8_sum(const float *d_x, int8_t *d_q, float *d_d, int32_t *d_xs, float *d_xc, uint32_t m,
+                               uint32_t nb, cudaStream_t stream);
 cudaError_t launch_block_isums(const uint8_t *d_res, const int8_t *d_xq, int32_t *d_out, const RowLayout &L, uint32_t M,
                                uint32_t rows, cudaStream_t stream);
 uint32_t gemm_pick_splits(uint32_t M, uint32_t rows, uint32_t nb, int num_sms);
 size_t gemm_workspace_floats(uint32_t M, uint32_t rows, uint32_t splits);
+// mode 0: d_y[M][rows]; mode 1: the kernel's int32 block sums into d_dump[M][rows][nb]; modes 2, 3: measurement
+// (no accumulator drain / no drain and no loads), nothing written.
 cudaError_t launch_gemm_w8a8(const uint8_t *d_res, const RowLayout &L, uint32_t rows, const float *d_scalesT,
-                             const int8_t *d_xq, const float *d_xd, const int32_t *d_xs, uint32_t M, float *d_y,
-                             float *d_part, uint32_t splits, uint32_t *d_status, cudaStream_t stream);
+                             const int8_t *d_xq, const float *d_xd, const int32_t *d_xs, const float *d_xc, uint32_t M,
+                             float *d_y, float *d_part, uint32_t splits, int mode, int32_t *d_dump, uint32_t *d_status,
+                             cudaStream_t stream);
 
 // Cross-GPU barrier on flag words in peer-mapped memory (one launch per rank, one rank per GPU):
 // bumps *d_epoch, stores the new value into flag word `rank` of every rank's flag array and waits

@@ -131,14 +131,14 @@ def test_gemv_f32_and_q8dot_match_oracle(accel, orc, synth, pkg, ty, out_dim, in
     assert accel.device_status() == 0
 
 
-@pytest.mark.parametrize("rule", ["0", "2"])
+@pytest.mark.parametrize("rule", [0, 2])
 @pytest.mark.parametrize("out_dim,in_dim", [(300, 256), (1030, 2560), (64, 9728)])
-def test_q6k_f32_forms_agree(accel, orc, synth, monkeypatch, rule, out_dim, in_dim):
+def test_q6k_f32_forms_agree(accel, orc, synth, rule, out_dim, in_dim):
     """Q6_K with one f32 row runs either on f16 tensor-core tiles (activation split hi + lo) or on int8
-    tiles (activation as three base-254 digits). STRIX_GEMV_DIGITS picks: 0 = never the digit form,
+    tiles (activation as three base-254 digits). The option "q6k_digits" picks: 0 = never the digit form,
     2 = whenever it fits. Both must sit at f32 rounding level from the f64 product of the dequantised
     weight, far inside the contract's tolerance."""
-    monkeypatch.setenv("STRIX_GEMV_DIGITS", rule)
+    assert accel.set_option("q6k_digits", rule)
     w = synth.quant(14, 41, "dg", out_dim, in_dim)
     assert accel.upload_q6_k("dg", w, in_dim, out_dim)
     W = accel.dequant_to_f32("dg").reshape(out_dim, in_dim).astype(np.float64)
@@ -150,6 +150,8 @@ def test_q6k_f32_forms_agree(accel, orc, synth, monkeypatch, rule, out_dim, in_d
         assert rel_l2(got, W @ x.astype(np.float64)) <= 2e-6
         assert rel_l2(got, orc.qmatmul(x, w, 14, in_dim, out_dim)) <= REL_L2_TOL
     assert accel.device_status() == 0
+    assert accel.set_option("q6k_digits", 1)
+    assert accel.set_option("no_such_knob", 1) is False
 
 
 def test_lm_head_shapes(accel, orc, synth):
@@ -360,3 +362,66 @@ def test_gemv_rows_matches_oracle(accel, orc, synth, pkg, ty, out_dim, in_dim, b
     for t in range(b):
         assert rel_l2(got_i[t], want_i[t]) <= REL_L2_TOL
     assert accel.device_status() == 0
+
+
+@pytest.mark.parametrize("out_dim,in_dim", [(15360, 3840), (3840, 15360)])
+def test_gemv_rows_at_the_verify_configuration(accel, orc, synth, pkg, out_dim, in_dim):
+    """The speculative-verify configuration's own FFN shapes (3840 -> 15360 and 15360 -> 3840, Q4_0), every
+    batch width, both activation forms, each activation row checked on its own."""
+    w = synth.q4_0(34, "vr", out_dim, in_dim)
+    key = "vr.%d.%d" % (out_dim, in_dim)
+    assert accel.upload_q4_0(key, w, in_dim, out_dim)
+    xs8 = synth.normal(34, "vr.x", 8, in_dim)
+    want8 = orc.qmatmul_batch(xs8, 8, w, synth.Q4_0, in_dim, out_dim)
+    xq, xd, _ = orc.xquant8(xs8)
+    want8_i = orc.idot_gemm(w, synth.Q4_0, xq, xd, 8, in_dim, out_dim)
+    for b in (1, 2, 4, 8):
+        got = accel.gemv_rows(key, xs8[:b], b)
+        got_i = accel.gemv_rows(key, xs8[:b], b, act=pkg.ACT_Q8DOT)
+        for t in range(b):
+            assert rel_l2(got[t], want8[t]) <= REL_L2_TOL, (b, t)
+            assert rel_l2(got_i[t], want8_i[t]) <= REL_L2_TOL, (b, t)
+    assert accel.device_status() == 0
+    accel.upload_q4_0(key, synth.q4_0(1, "tiny", 1, 32), 32, 1)
+
+
+@pytest.mark.parametrize("pre", ["rmsnorm", "swiglu", "geglu"])
+def test_fused_prologue_integer_form_at_the_contract(accel, orc, synth, pkg, pre):
+    """RMSNorm / SwiGLU / GeGLU -> per-32 int8 -> GEMV in ONE launch against the INTEGER oracle on the CPU's
+    own codes (rmsnorm_xquant / silu_xquant / geglu_xquant, kernels.rs:101-226), at the 1e-3 contract.
+    The launch-per-step kernel quantises x * w and applies 1/rms to the outputs (the product is linear in
+    it), so where (x / rms) * w sits within an f32 rounding of a .5 boundary its code can differ from the
+    CPU's by one; the count of such codes is computed here on the host, from the two operand orders, and
+    printed next to the error."""
+    import torch
+    dev = torch.device("cuda:0")
+    hidden, ffn = 2560, 9728
+    s = torch.cuda.current_stream().cuda_stream
+    if pre == "rmsnorm":
+        K, N = hidden, 4096
+        a, b_ = synth.normal(61, "h", K), synth.norm_weight(61, "nw", K)
+        x_cpu = orc.rmsnorm(a, b_, 1e-6)
+        code, eps = pkg.PRE_RMSNORM, 1e-6
+        # the kernel's operand order on the host: codes of x * w (scale-free) against codes of (x / rms) * w
+        xw = (a * b_).astype(np.float32)
+        flips = int((orc.xquant8(xw)[0] != orc.xquant8(x_cpu)[0]).sum())
+    else:
+        K, N = ffn, hidden
+        a, b_ = synth.normal(61, "gate", K), synth.normal(61, "up", K)
+        x_cpu = orc.swiglu(a, b_) if pre == "swiglu" else orc.geglu(a, b_)
+        code, eps, flips = (pkg.PRE_SWIGLU if pre == "swiglu" else pkg.PRE_GEGLU), 0.0, None
+    w = synth.q4_0(61, "fp." + pre, N, K)
+    key = "fp." + pre
+    assert accel.upload_q4_0(key, w, K, N)
+    d_a, d_b = torch.from_numpy(a).to(dev), torch.from_numpy(b_).to(dev)
+    y = torch.full((N,), float("nan"), device=dev)
+    assert accel.gemv_dev([key], d_a.data_ptr(), [y.data_ptr()], d_b=d_b.data_ptr(), eps=eps, pre=code,
+                          act=pkg.ACT_Q8DOT, stream=s)
+    assert accel.device_status(s) == 0
+    xq, xd, _ = orc.xquant8(x_cpu)
+    want = orc.idot_gemm(w, synth.Q4_0, xq, xd, 1, K, N)[0]
+    got = y.cpu().numpy()
+    r = rel_l2(got, want)
+    print("fused %s + int8 + GEMV vs integer oracle: rel-L2 %.2e max-abs %.2e; codes moved by the operand order: %s of %d"
+          % (pre, r, np.abs(got - want).max(), flips, K))
+    assert r <= REL_L2_TOL

@@ -37,6 +37,27 @@ def test_noalloc_gemm_matches_regular_entry_point_twice(accel, synth, pkg):
             assert rel_l2(got, want) <= REL_L2_TOL, (m, n, k, call)
 
 
+def test_noalloc_call_leaves_free_memory_unchanged(accel, synth, pkg):
+    """The handle exists (strix_cuda_create has touched the fixed array and the kernels), so a call - even the
+    first one with a shape this handle has never seen - must not change the device's free memory."""
+    import torch
+    dev = torch.device("cuda:0")
+    s = torch.cuda.current_stream().cuda_stream
+    m, n, k = 77, 300, 1184                                  # never used anywhere else
+    assert accel.upload_q8_0("na.fresh", synth.q8_0(93, "nf", n, k), k, n)
+    x = torch.from_numpy(synth.normal(93, "nf.x", m, k)).to(dev)
+    y = torch.full((m, n), float("nan"), device=dev)
+    y_ref = torch.full((m, n), float("nan"), device=dev)
+    torch.cuda.synchronize()
+    free0, _ = torch.cuda.mem_get_info()
+    assert accel.prefill_q8_gemm_noalloc("na.fresh", x.data_ptr(), m, y.data_ptr(), stream=s)
+    torch.cuda.synchronize()
+    free1, _ = torch.cuda.mem_get_info()
+    assert free1 == free0, "the allocation-free entry point changed free device memory by %d bytes" % (free0 - free1)
+    assert accel.prefill_q8_gemm_dev("na.fresh", x.data_ptr(), m, y_ref.data_ptr(), stream=s)
+    assert rel_l2(y.cpu().numpy(), y_ref.cpu().numpy()) <= REL_L2_TOL
+
+
 def test_noalloc_refuses_what_does_not_fit(accel, synth, pkg):
     import torch
     dev = torch.device("cuda:0")
