@@ -310,12 +310,14 @@ STRIX_API int strix_cuda_device_status(strix_cuda *h, void *stream, uint32_t *st
  * "gemv_pdl" (programmatic dependent launch between GEMVs), "gemv_debug" (bit 0: stream the weights without
  * arithmetic, bit 1: empty launches, bit 2: stop after the activation prologue), "batch_graph" (gemv_batch
  * replays a cached CUDA graph), "decode_chain" (the projection chain as one persistent launch),
- * "chain_trace" (per-step clocks, see strix_cuda_decode_trace), "poll_limit" (bound, in polls, of a wait on
+ * "chain_trace" (per-step clocks, see strix_cuda_decode_trace), "chain_debug" (bit 0: the chain kernel skips
+ * the arithmetic, bit 1: its waits on exchange vectors do not wait; results are then meaningless), "poll_limit" (bound, in polls, of a wait on
  * an exchange vector; 0 = default), "profile" (as strix_cuda_opts.profile). */
 STRIX_API int strix_cuda_set_option(strix_cuda *h, const char *name, long long value);
-/* After set_option("chain_trace", 1): the clock (ns) of CTA 0 of the last decode-chain launch at each
- * step's start, after its prologue (the wait for its activations included) and after its row groups,
- * 3 words per step. Returns the number of steps (0 = no trace, or `cap_words` too small). Synchronises. */
+/* After set_option("chain_trace", 1): per step of the last decode-chain launch, 6 words from its CTA 0: the
+ * clock (ns) at the step's start, when its activations had arrived, after its prologue, after its last row
+ * group, after its reduction and stores; and the SM clocks spent waiting for weight stages. Returns the
+ * number of steps (0 = no trace, or `cap_words` too small). Synchronises. */
 STRIX_API int strix_cuda_decode_trace(strix_cuda *h, unsigned long long *out, size_t cap_words);
 
 /* Dequantise a resident weight back to f32 [shard_rows][in_dim] on the host:

@@ -520,10 +520,11 @@ class CudaWeightAccel:
         return self._check(self._L.strix_cuda_set_option(self._h, name.encode(), int(value))) == 1
 
     def decode_trace(self, max_steps=4096):
-        """Per-step clocks [steps][3] (ns) of the last decode-chain launch after set_option("chain_trace", 1), or None."""
-        buf = np.zeros(3 * max_steps, np.uint64)
+        """Per-step words [steps][6] of the last decode-chain launch after set_option("chain_trace", 1), or None
+        (see strix_cuda_decode_trace)."""
+        buf = np.zeros(6 * max_steps, np.uint64)
         n = self._check(self._L.strix_cuda_decode_trace(self._h, buf.ctypes.data_as(C.POINTER(C.c_uint64)), buf.size))
-        return buf[:3 * n].reshape(n, 3).copy() if n > 0 else None
+        return buf[:6 * n].reshape(n, 6).copy() if n > 0 else None
 
     def dequant_to_f32(self, key):
         info = self.weight_info(key)

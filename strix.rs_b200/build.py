@@ -21,7 +21,7 @@ FLAGS = [
     "-O3", "-std=c++17", "-lineinfo", "--expt-relaxed-constexpr",
     "-Xcompiler", "-fPIC,-fvisibility=hidden",
     "-I", INCLUDE, "-I", CSRC,
-]
+] + os.environ.get("STRIX_NVCC_EXTRA", "").split()
 
 
 def _sources():

@@ -328,6 +328,7 @@ int strix_cuda_set_option(strix_cuda *h, const char *name, long long value) {
     else if (n == "batch_graph") h->use_batch_graph = value != 0;
     else if (n == "decode_chain") h->decode_chain = value != 0;
     else if (n == "chain_trace") h->chain_trace = value != 0;
+    else if (n == "chain_debug") h->chain_debug = v;
     else if (n == "poll_limit") h->poll_limit = v ? v : CHAIN_POLL_LIMIT;
     else if (n == "profile") h->profile = value != 0;
     else return 0;

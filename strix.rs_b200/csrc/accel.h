@@ -44,6 +44,7 @@ struct strix_cuda {
     int rank = 0, world = 1, profile = 0;
     strix::GemvTune tune;             // planning knobs (strix_cuda_set_option)
     int use_batch_graph = 1;          // gemv_batch replays a cached CUDA graph
+    uint32_t chain_debug = 0;         // measurement: see launch_chain
     int chain_trace = 0;              // measurement: the chain kernel records per-step clocks (strix_cuda_decode_trace)
     int decode_chain = 1;             // the decode projection chain runs as one persistent launch where it can
     uint32_t poll_limit = strix::CHAIN_POLL_LIMIT;  // bound of a wait on an exchange vector, in polls

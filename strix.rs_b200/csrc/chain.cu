@@ -34,10 +34,25 @@ namespace strix {
 
 // Shared-memory map (bytes). 0..1919 as in gemv_tiles.cuh (full / empty mbarriers, control words, oscale);
 // the activation prologues use [SMEM_PART_OFF, +2048) as reduction scratch.
-constexpr uint32_t CH_WARPS = GEMV_WARPS;
+// Consumer warps: three per scheduler. Every phase of a 2 us step is run by all consumer warps and its
+// bookkeeping (stage hand-overs, polls, barriers) is per warp, so fewer warps mean fewer instructions
+// competing for issue slots, and 416 threads leave each one 128 registers (24 warps: 72, with spills
+// in the tile loop). Measured on the 36-layer decode chain: 24 warps 1.35 ms, 12 warps 1.37 ms per token
+// with the step skeleton alone (no arithmetic, no waiting) at 1.01 against 0.89 ms.
+#ifndef STRIX_CHAIN_WARPS
+#define STRIX_CHAIN_WARPS 12
+#endif
+constexpr uint32_t CH_WARPS = STRIX_CHAIN_WARPS;
 constexpr uint32_t CH_PART_OFF = SMEM_PART_OFF + 2048u;  // [CHAIN_PART_SLOTS][CH_WARPS][16] f32 partial sums
-constexpr uint32_t CH_X_OFF = (CH_PART_OFF + CHAIN_PART_SLOTS * CH_WARPS * 16u * 4u + 127u) & ~127u;
-constexpr uint32_t CH_NI = 5;  // float4s of an exchange-vector activation a thread keeps: in_dim <= 5 * 4 * 768
+// Step descriptors in shared memory: a step's fields are read many times by every warp, and from global
+// memory each first touch of a line costs an L2 round trip on the critical path of a 2 us step. Warp 0
+// copies step s + 1 in while step s runs (three slots: the threads still storing step s - 1's rows read
+// theirs); the producer warp, which runs steps ahead of the consumers, keeps a slot of its own.
+constexpr uint32_t CH_STEP_BYTES = 512;
+static_assert(sizeof(ChainStep) <= CH_STEP_BYTES && sizeof(ChainStep) % 16 == 0, "one 16-byte word per lane of a warp");
+constexpr uint32_t CH_STEP_OFF = CH_PART_OFF + CHAIN_PART_SLOTS * CH_WARPS * 16u * 4u;  // 3 consumer slots + 1 producer slot
+constexpr uint32_t CH_X_OFF = (CH_STEP_OFF + 4u * CH_STEP_BYTES + 127u) & ~127u;
+constexpr int CH_NORM_NI = 2;  // float4s a thread keeps across the RMSNorm reduction: normed rows up to 2 * 4 * 384 = 3072
 
 struct ChainCta {
     Cta c;
@@ -47,19 +62,27 @@ struct ChainCta {
     uint32_t ubase;        // consumers: tiles of this step seen so far, mod CH_WARPS
     uint32_t poll_limit;
     uint32_t epoch_base;
-    unsigned long long *trace;  // measurement only: this step's three clock words (CTA 0), or null
+    unsigned long long *trace;  // measurement only: this step's clock words (CTA 0), or null
+    uint32_t debug;             // measurement only: bit 0 = no arithmetic, bit 1 = polls do not wait
+    long long wait_clk;         // measurement only: SM clocks this thread spent waiting for weight stages
 };
 static_assert(CHAIN_ACT_DIGITS == ACT_F32_DIGITS, "one code for the digit form");
 
 __device__ __forceinline__ void ch_trace(const ChainCta &C, uint32_t k) {
-    if (C.trace && C.c.tid == 0) {
-        unsigned long long t_;
-        asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t_));
-        C.trace[k] = t_;
-    }
+    if (C.trace && C.c.tid == 0) C.trace[k] = (unsigned long long)clock64();
 }
 
 __device__ __forceinline__ volatile uint32_t *ch_ctl(const ChainCta &C) { return cta_ctl(C.c); }
+// one warp: steps[s] -> shared-memory slot, 16 bytes per lane, as an asynchronous copy (the warp does not
+// wait for the data; ch_fetch_wait before the barrier that hands the slot to the other warps)
+__device__ __forceinline__ void ch_fetch_step(const ChainStep *steps, uint32_t s, uint8_t *slot, uint32_t lane) {
+    if (lane * 16u < sizeof(ChainStep))
+        asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(smem_u32(slot + lane * 16u)),
+                     "l"(reinterpret_cast<const uint8_t *>(steps + s) + lane * 16u)
+                     : "memory");
+    asm volatile("cp.async.commit_group;" ::: "memory");
+}
+__device__ __forceinline__ void ch_fetch_wait() { asm volatile("cp.async.wait_all;" ::: "memory"); }
 // ctl[0]: a wait of the CTA's weight pipeline ran out. ctl[1]: a wait on an exchange vector ran out
 // somewhere: nobody polls again.
 
@@ -102,7 +125,7 @@ __device__ __forceinline__ void chain_produce(const ChainStep &S, ChainCta &C) {
     for (uint32_t n = 0; n < my_n; n++) {
         const ItemRef it = item_ref(S, rank + n * C.c.grid);
         for (uint32_t c = 0; c < NC; c++) {
-            if (!C.lap0 && !mbar_wait_bounded(&empty[C.sl], C.ph ^ 1u, C.c.status)) ctl[0] = 1;
+            if (!C.lap0 && !mbar_wait_suspended(&empty[C.sl], C.ph ^ 1u, C.c.status, 100u)) ctl[0] = 1;
             if (ctl[0]) return;  // after an abort nothing more is issued
             const uint32_t nbk = min(CT, S.L.nb - c * CT), bytes = nbk * tb;
             uint8_t *dst = stages + (uint64_t)C.sl * C.stage_bytes;
@@ -120,7 +143,7 @@ __device__ __forceinline__ void ll_store(unsigned long long *p, float v, uint32_
     asm volatile("st.volatile.global.u64 [%0], %1;" ::"l"(p), "l"(w) : "memory");
 }
 __device__ __forceinline__ void ll_load2(const unsigned long long *p, unsigned long long &a, unsigned long long &b) {
-    asm volatile("ld.volatile.global.v2.u64 {%0,%1}, [%2];" : "=l"(a), "=l"(b) : "l"(p) : "memory");
+    asm volatile("ld.volatile.global.v2.u64 {%0,%1}, [%2];" : "=l"(a), "=l"(b) : "l"(p));
 }
 // One entry, waited for (bounded) by the calling thread alone.
 __device__ __forceinline__ float ll_wait1(const unsigned long long *p, uint32_t want, ChainCta &C) {
@@ -128,7 +151,7 @@ __device__ __forceinline__ float ll_wait1(const unsigned long long *p, uint32_t 
     unsigned long long w = 0;
     for (uint32_t it = 0;; ++it) {
         asm volatile("ld.volatile.global.u64 %0, [%1];" : "=l"(w) : "l"(p) : "memory");
-        if ((uint32_t)(w >> 32) == want || ctl[1]) break;
+        if ((uint32_t)(w >> 32) == want || ctl[1] || (C.debug & 2u)) break;
         if (it >= C.poll_limit) {
             if (C.c.status) atomicOr(C.c.status, STATUS_WAIT_TIMEOUT);
             ctl[1] = 1;
@@ -142,138 +165,207 @@ __device__ __forceinline__ float ll_wait1(const unsigned long long *p, uint32_t 
 
 // ---- prologue of an integer-dot step (one activation row): the activation, plain or from an exchange
 //      vector, through the optional RMSNorm into the per-32 int8 operands of the tiles (see x_layout).
-//      Thread tid owns float4s tid, tid + 768, ... (eight consecutive threads = one 32-element block) and
-//      keeps them in registers across the block-wide sum of squares. ----
-template <int FMT, int PRE>
-__device__ __forceinline__ void chain_prologue_q8(const ChainStep &S, ChainCta &C) {
-    uint8_t *smem = C.c.smem;
-    volatile uint32_t *ctl = ch_ctl(C);
-    float *oscale = reinterpret_cast<float *>(smem + SMEM_OSCALE_OFF);
-    float *scr = reinterpret_cast<float *>(smem + SMEM_PART_OFF);
-    const uint32_t tid = C.c.tid, lane = C.c.lane, warp = C.c.warp;
-    const uint32_t K = S.L.in_dim, K4 = K / 4u, ct = CH_WARPS * 32u, l8 = lane & 7u;
-    const XLayout XL = x_layout(FMT, STRIX_ACT_Q8DOT, K, 1, C.x_off);
-    float4 v[CH_NI], w[PRE == STRIX_PRE_RMSNORM ? CH_NI : 1];
-    if constexpr (PRE == STRIX_PRE_RMSNORM) {
-        // the norm weights depend on nothing: on their way before the wait below
-#pragma unroll
-        for (uint32_t i = 0; i < CH_NI; i++) {
-            const uint32_t e4 = tid + i * ct;
-            w[i] = make_float4(0.f, 0.f, 0.f, 0.f);
-            if (e4 < K4) w[i] = __ldg(reinterpret_cast<const float4 *>(S.b) + e4);
+//      Thread tid owns float4s tid, tid + 768, ... (eight consecutive threads = one 32-element block).
+//      The row is taken in passes of NIP float4s per thread: all of a pass's entries are requested before
+//      the first is looked at (one trip to L2 per pass) and, without a norm, quantised and stored before
+//      the next pass, so a long row (ffn 9728) needs no more registers than a short one. With RMSNorm
+//      the values stay in registers across the block-wide sum of squares (rows up to 4 x NIP x 3072).
+//      Every warp of all 148 CTAs runs this, on the critical path of a 2 us step: what counts is its
+//      instruction count. Warps past the end of the row only meet the barriers. ----
+__device__ __forceinline__ void quant_store(const float4 t4, uint32_t e4, bool live, uint32_t l8, bool q6, int bias, uint32_t *xbw,
+                                            float *rec) {
+    // per-32 quantiser (xquant8, kernels.rs:864-876): d = amax/127, inv = d>0 ? 1/d : 0, q = clamp(rintf(x*inv));
+    // eight lanes per block, four elements each
+    const uint32_t blk = e4 >> 3, t = l8 & 3u, hf = l8 >> 2;
+    float bm = fmaxf(fmaxf(fabsf(t4.x), fabsf(t4.y)), fmaxf(fabsf(t4.z), fabsf(t4.w)));
+    bm = fmaxf(bm, __shfl_xor_sync(0xffffffffu, bm, 1));
+    bm = fmaxf(bm, __shfl_xor_sync(0xffffffffu, bm, 2));
+    bm = fmaxf(bm, __shfl_xor_sync(0xffffffffu, bm, 4));
+    const float d = bm / 127.0f;
+    const float inv = d > 0.f ? 1.0f / d : 0.f;
+    const uint32_t wq = pack4(quant1(t4.x, inv), quant1(t4.y, inv), quant1(t4.z, inv), quant1(t4.w, inv));
+    int cs = sum4(wq);
+    cs += __shfl_xor_sync(0xffffffffu, cs, 1);
+    cs += __shfl_xor_sync(0xffffffffu, cs, 2);
+    const int half_sum = cs;  // over this lane's 16-weight half of the block
+    cs += __shfl_xor_sync(0xffffffffu, cs, 4);
+    if (live) {
+        if (q6) {
+            xbw[(blk * 8u + hf * 4u + t) * 2u + hf] = wq;
+            xbw[(blk * 8u + hf * 4u + t) * 2u + (hf ^ 1u)] = 0u;
+            if (l8 == 0) rec[blk * 16u] = d;
+            if (t == 0) rec[blk * 16u + 1u + hf] = __int_as_float(-bias * half_sum);
+        } else {
+            xbw[(blk * 4u + t) * 2u + hf] = wq;
+            if (l8 == 0) {
+                rec[blk * 2u] = d;
+                rec[blk * 2u + 1u] = -(float)bias * d * (float)cs;
+            }
         }
     }
+}
+
+// One pass: NIP float4s per thread starting at float4 index e0 (this thread's first), ct apart.
+template <int NIP>
+__device__ __forceinline__ void fetch_pass(const ChainStep &S, ChainCta &C, uint32_t e0, uint32_t ct, uint32_t K4, float4 (&v)[NIP]) {
+    volatile uint32_t *ctl = ch_ctl(C);
     if (S.a_ll) {
         const uint32_t want = C.epoch_base + S.in_step + 1u;
         uint32_t pend = 0;
 #pragma unroll
-        for (uint32_t i = 0; i < CH_NI; i++) {
+        for (int i = 0; i < NIP; i++) {
             v[i] = make_float4(0.f, 0.f, 0.f, 0.f);
-            if (tid + i * ct < K4) pend |= 1u << i;
+            if (e0 + i * ct < K4) pend |= 1u << i;
         }
-        for (uint32_t it = 0;; ++it) {
+        for (uint32_t it = 0; pend != 0u; ++it) {
+            unsigned long long e[NIP][4];
 #pragma unroll
-            for (uint32_t i = 0; i < CH_NI; i++) {
+            for (int i = 0; i < NIP; i++) {
                 if (pend & (1u << i)) {
-                    const unsigned long long *p = S.a_ll + (size_t)(tid + i * ct) * 4u;
-                    unsigned long long e0, e1, e2, e3;
-                    ll_load2(p, e0, e1);
-                    ll_load2(p + 2, e2, e3);
-                    if ((uint32_t)(e0 >> 32) == want && (uint32_t)(e1 >> 32) == want && (uint32_t)(e2 >> 32) == want &&
-                        (uint32_t)(e3 >> 32) == want)
-                        pend &= ~(1u << i);
-                    v[i] = make_float4(__uint_as_float((uint32_t)e0), __uint_as_float((uint32_t)e1),
-                                       __uint_as_float((uint32_t)e2), __uint_as_float((uint32_t)e3));
+                    const unsigned long long *p = S.a_ll + (size_t)(e0 + i * ct) * 4u;
+                    ll_load2(p, e[i][0], e[i][1]);
+                    ll_load2(p + 2, e[i][2], e[i][3]);
                 }
             }
-            if (__all_sync(0xffffffffu, pend == 0u)) break;
-            if (ctl[1]) break;  // a wait ran out somewhere: nobody polls again
-            if (it >= C.poll_limit) {
-                if (pend) {
-                    if (C.c.status) atomicOr(C.c.status, STATUS_WAIT_TIMEOUT);
-                    ctl[1] = 1;
+#pragma unroll
+            for (int i = 0; i < NIP; i++) {
+                if (pend & (1u << i)) {
+                    if ((uint32_t)(e[i][0] >> 32) == want && (uint32_t)(e[i][1] >> 32) == want &&
+                        (uint32_t)(e[i][2] >> 32) == want && (uint32_t)(e[i][3] >> 32) == want)
+                        pend &= ~(1u << i);
+                    v[i] = make_float4(__uint_as_float((uint32_t)e[i][0]), __uint_as_float((uint32_t)e[i][1]),
+                                       __uint_as_float((uint32_t)e[i][2]), __uint_as_float((uint32_t)e[i][3]));
                 }
+            }
+            if (pend == 0u || ctl[1] || (C.debug & 2u)) break;  // (a wait ran out somewhere: nobody polls again)
+            if (it >= C.poll_limit) {
+                if (C.c.status) atomicOr(C.c.status, STATUS_WAIT_TIMEOUT);
+                ctl[1] = 1;
                 break;
             }
         }
-        __syncwarp();
     } else {
 #pragma unroll
-        for (uint32_t i = 0; i < CH_NI; i++) {
-            const uint32_t e4 = tid + i * ct;
+        for (int i = 0; i < NIP; i++) {
+            const uint32_t e4 = e0 + i * ct;
             v[i] = make_float4(0.f, 0.f, 0.f, 0.f);
             if (e4 < K4) v[i] = __ldcg(reinterpret_cast<const float4 *>(S.a) + e4);
         }
     }
-    if constexpr (PRE == STRIX_PRE_RMSNORM) {
-        // rmsnorm (crates/strix-backend-cpu/src/qwen3.rs:107-114): (x * (1 / sqrt(mean(x^2) + eps))) * w
-        float ss = 0.f;
-#pragma unroll
-        for (uint32_t i = 0; i < CH_NI; i++) {
-            ss = fmaf(v[i].x, v[i].x, ss); ss = fmaf(v[i].y, v[i].y, ss);
-            ss = fmaf(v[i].z, v[i].z, ss); ss = fmaf(v[i].w, v[i].w, ss);
-        }
-        ss = warp_sum(ss);
-        if (lane == 0) scr[warp] = ss;
-        CH_CONS_BAR();
-        float tot = 0.f;
-#pragma unroll
-        for (uint32_t w2 = 0; w2 < CH_WARPS; w2++) tot += scr[w2];
-        const float sc = 1.0f / sqrtf(tot / (float)K + S.eps);
-#pragma unroll
-        for (uint32_t i = 0; i < CH_NI; i++) {
-            v[i].x = (v[i].x * sc) * w[i].x; v[i].y = (v[i].y * sc) * w[i].y;
-            v[i].z = (v[i].z * sc) * w[i].z; v[i].w = (v[i].w * sc) * w[i].w;
-        }
-    }
-    // per-32 quantiser (xquant8, kernels.rs:864-876): d = amax/127, inv = d>0 ? 1/d : 0, q = clamp(rintf(x*inv));
-    // eight lanes per block, four elements each
+}
+
+template <int PRE>
+__device__ __forceinline__ void chain_prologue_q8(const ChainStep &S, ChainCta &C, bool q6, int bias) {
+    uint8_t *smem = C.c.smem;
+    float *scr = reinterpret_cast<float *>(smem + SMEM_PART_OFF);
+    const uint32_t tid = C.c.tid, lane = C.c.lane, warp = C.c.warp;
+    const uint32_t K = S.L.in_dim, K4 = K / 4u, ct = CH_WARPS * 32u, l8 = lane & 7u;
+    const XLayout XL = x_layout(q6 ? FMT_Q6_K : FMT_Q4_0, STRIX_ACT_Q8DOT, K, 1, C.x_off);
     uint32_t *xbw = reinterpret_cast<uint32_t *>(smem + XL.xb);
     float *rec = reinterpret_cast<float *>(smem + XL.rec);
-    constexpr int BIAS = FMT == FMT_Q8_0 ? 128 : FMT == FMT_Q4_0 ? 8 : FMT == FMT_Q4_1 ? -1 : 32;
+    const uint32_t wbase = tid - lane;  // this warp's first float4
+    if constexpr (PRE == STRIX_PRE_RMSNORM) {
+        // rmsnorm (crates/strix-backend-cpu/src/qwen3.rs:107-114): (x * (1 / sqrt(mean(x^2) + eps))) * w.
+        // Up to CH_NORM_NI float4s per thread stay in registers across the sum of squares.
+        float4 v[CH_NORM_NI], w[CH_NORM_NI];
+        float ss = 0.f;
+        if (wbase < K4) {
+            // the norm weights depend on nothing: on their way before the wait
 #pragma unroll
-    for (uint32_t i = 0; i < CH_NI; i++) {
-        const uint32_t e4 = tid + i * ct;
-        if ((tid - lane) + i * ct >= K4) break;  // the whole warp is past the row's end (the body shuffles)
-        const bool live = e4 < K4;
-        const float4 t4 = v[i];
-        const uint32_t blk = e4 >> 3, t = l8 & 3u, hf = l8 >> 2;
-        float bm = fmaxf(fmaxf(fabsf(t4.x), fabsf(t4.y)), fmaxf(fabsf(t4.z), fabsf(t4.w)));
-        bm = fmaxf(bm, __shfl_xor_sync(0xffffffffu, bm, 1));
-        bm = fmaxf(bm, __shfl_xor_sync(0xffffffffu, bm, 2));
-        bm = fmaxf(bm, __shfl_xor_sync(0xffffffffu, bm, 4));
-        const float d = bm / 127.0f;
-        const float inv = d > 0.f ? 1.0f / d : 0.f;
-        const uint32_t wq = pack4(quant1(t4.x, inv), quant1(t4.y, inv), quant1(t4.z, inv), quant1(t4.w, inv));
-        int cs = sum4(wq);
-        cs += __shfl_xor_sync(0xffffffffu, cs, 1);
-        cs += __shfl_xor_sync(0xffffffffu, cs, 2);
-        const int half_sum = cs;  // over this lane's 16-weight half of the block
-        cs += __shfl_xor_sync(0xffffffffu, cs, 4);
-        if (live) {
-            if (FMT == FMT_Q6_K) {
-                xbw[(blk * 8u + hf * 4u + t) * 2u + hf] = wq;
-                xbw[(blk * 8u + hf * 4u + t) * 2u + (hf ^ 1u)] = 0u;
-                if (l8 == 0) rec[blk * 16u] = d;
-                if (t == 0) rec[blk * 16u + 1u + hf] = __int_as_float(-BIAS * half_sum);
-            } else {
-                xbw[(blk * 4u + t) * 2u + hf] = wq;
-                if (l8 == 0) {
-                    rec[blk * 2u] = d;
-                    rec[blk * 2u + 1u] = -(float)BIAS * d * (float)cs;
-                }
+            for (int i = 0; i < CH_NORM_NI; i++) {
+                const uint32_t e4 = tid + i * ct;
+                w[i] = make_float4(0.f, 0.f, 0.f, 0.f);
+                if (e4 < K4) w[i] = __ldg(reinterpret_cast<const float4 *>(S.b) + e4);
+            }
+            fetch_pass<CH_NORM_NI>(S, C, tid, ct, K4, v);
+#pragma unroll
+            for (int i = 0; i < CH_NORM_NI; i++) {
+                ss = fmaf(v[i].x, v[i].x, ss); ss = fmaf(v[i].y, v[i].y, ss);
+                ss = fmaf(v[i].z, v[i].z, ss); ss = fmaf(v[i].w, v[i].w, ss);
+            }
+            ss = warp_sum(ss);
+        }
+        ch_trace(C, 1);
+        if (lane == 0) scr[warp] = ss;
+        CH_CONS_BAR();
+        if (wbase < K4) {
+            float tot = 0.f;
+#pragma unroll
+            for (uint32_t w2 = 0; w2 < CH_WARPS; w2++) tot += scr[w2];
+            const float sc = 1.0f / sqrtf(tot / (float)K + S.eps);
+#pragma unroll
+            for (int i = 0; i < CH_NORM_NI; i++) {
+                if (wbase + i * ct >= K4) break;  // the whole warp is past the row's end (quant_store shuffles)
+                const float4 x4 = make_float4((v[i].x * sc) * w[i].x, (v[i].y * sc) * w[i].y, (v[i].z * sc) * w[i].z,
+                                              (v[i].w * sc) * w[i].w);
+                quant_store(x4, tid + i * ct, tid + i * ct < K4, l8, q6, bias, xbw, rec);
             }
         }
+    } else {
+        // no norm: each pass (up to 2 float4s per thread, both requested at once) is quantised and stored before
+        // the next one is fetched. Threads past the row's end carry zeros through the shuffles and store nothing.
+        const uint32_t per = (K4 + ct - 1u) / ct;  // float4s per thread
+        if (per <= 1u) {
+            float4 v[1];
+            fetch_pass<1>(S, C, tid, ct, K4, v);
+            quant_store(v[0], tid, tid < K4, l8, q6, bias, xbw, rec);
+        } else if (per <= 2u) {
+            float4 v[2];
+            fetch_pass<2>(S, C, tid, ct, K4, v);
+#pragma unroll
+            for (int i = 0; i < 2; i++) quant_store(v[i], tid + i * ct, tid + i * ct < K4, l8, q6, bias, xbw, rec);
+        } else {
+            for (uint32_t e0 = tid; e0 - lane < K4; e0 += 2u * ct) {
+                float4 v[2];
+                fetch_pass<2>(S, C, e0, ct, K4, v);
+                quant_store(v[0], e0, e0 < K4, l8, q6, bias, xbw, rec);
+                if (e0 - lane + ct < K4) quant_store(v[1], e0 + ct, e0 + ct < K4, l8, q6, bias, xbw, rec);
+            }
+        }
+        ch_trace(C, 1);
     }
-    if (tid == 0) oscale[0] = 1.0f;
+    if (tid == 0) *reinterpret_cast<float *>(smem + SMEM_OSCALE_OFF) = 1.0f;
     CH_CONS_BAR();
 }
 
 // ---- epilogue: add up the partial sums of the row groups waiting in shared memory (warp order) and
 //      publish the rows. Thread r of item `it` owns row r of that row group. ----
+// The residual of the row this thread will publish in the step's FIRST reduction, fetched before the tiles
+// are run so that its trip to L2 is off the critical path. ok = 0: nothing fetched (no residual, a row of a
+// later reduction, or an entry that has not arrived yet): chain_flush then reads it itself.
+struct EarlyRes {
+    float v;
+    uint32_t ok;
+};
+template <bool PAIR>
+__device__ __forceinline__ EarlyRes chain_early_res(const ChainStep &S, ChainCta &C, uint32_t my_n) {
+    EarlyRes E{0.f, 0u};
+    constexpr uint32_t CAP = PAIR ? (uint32_t)CHAIN_PART_SLOTS / 2u : (uint32_t)CHAIN_PART_SLOTS;
+    const uint32_t tid = C.c.tid, n0 = my_n < CAP ? my_n : CAP;
+    if (tid >= n0 * TILE_ROWS) return E;
+    const uint32_t it = tid / TILE_ROWS, r = tid % TILE_ROWS;
+    const ItemRef ref = item_ref(S, ch_rank(C, S) + it * C.c.grid);
+    if (r >= ref.rows) return E;
+    const ChainMat &M = S.mat[ref.mat];
+    const size_t o = ref.row0 + r;
+    if (M.res) {
+        E.v = __ldcg(M.res + o);
+        E.ok = 1u;
+    }
+    if (M.res_ll) {
+        unsigned long long w;
+        asm volatile("ld.volatile.global.u64 %0, [%1];" : "=l"(w) : "l"(M.res_ll + M.row_base + o) : "memory");
+        if ((uint32_t)(w >> 32) == C.epoch_base + S.res_step + 1u) {
+            E.v += __uint_as_float((uint32_t)w);
+            E.ok |= 2u;
+        }
+    }
+    return E;
+}
+
 template <bool PAIR>
 __device__ __forceinline__ void chain_flush(const ChainStep &S, ChainCta &C, uint32_t first_n, uint32_t n_wait, float osc,
-                                            uint32_t epoch) {
+                                            uint32_t epoch, EarlyRes E) {
     const uint32_t tid = C.c.tid;
     if (tid >= n_wait * TILE_ROWS) return;
     const float *part = reinterpret_cast<const float *>(C.c.smem + CH_PART_OFF);
@@ -294,8 +386,9 @@ __device__ __forceinline__ void chain_flush(const ChainStep &S, ChainCta &C, uin
     }
     const ChainMat &M = S.mat[ref.mat];
     const size_t o = ref.row0 + r;
-    if (M.res) val += __ldcg(M.res + o);
-    if (M.res_ll) val += ll_wait1(M.res_ll + M.row_base + o, C.epoch_base + S.res_step + 1u, C);
+    if (first_n == 0u) val += E.v;  // (the early fetch covers the first reduction's rows)
+    if (M.res && !(first_n == 0u && (E.ok & 1u))) val += __ldcg(M.res + o);
+    if (M.res_ll && !(first_n == 0u && (E.ok & 2u))) val += ll_wait1(M.res_ll + M.row_base + o, C.epoch_base + S.res_step + 1u, C);
     if (M.y) M.y[o] = val;
     for (uint32_t p = 0; p < M.n_out_ll; p++) ll_store(M.out_ll[p] + M.row_base + o, val, epoch);
 }
@@ -326,10 +419,17 @@ __device__ __forceinline__ void chain_consume(const ChainStep &S, ChainCta &C, u
     const uint32_t half_off = CT * L.tile_bytes;  // a pair's stage: gate tiles, then up tiles
     constexpr uint32_t PER = PAIR ? 2u : 1u;
     uint32_t waiting = 0, first_n = 0;  // row groups whose partial sums wait in shared memory; the first of them
+    const EarlyRes early = chain_early_res<PAIR>(S, C, my_n);
     for (uint32_t n = 0; n < my_n; n++) {
-        float acc[2] = {0.f, 0.f}, acc2[2] = {0.f, 0.f}, up[2] = {0.f, 0.f}, up2[2] = {0.f, 0.f};
+        float acc[2] = {0.f, 0.f}, up[2] = {0.f, 0.f};
         for (uint32_t c = 0; c < NC; c++) {
-            if (!ctl[0] && !mbar_wait_bounded(&full[C.sl], C.ph, C.c.status)) ctl[0] = 1;
+            if (C.trace) {
+                const long long c0 = clock64();
+                if (!ctl[0] && !mbar_wait_bounded(&full[C.sl], C.ph, C.c.status)) ctl[0] = 1;
+                C.wait_clk += clock64() - c0;
+            } else if (!ctl[0] && !mbar_wait_bounded(&full[C.sl], C.ph, C.c.status)) {
+                ctl[0] = 1;
+            }
             const uint32_t base = st0 + C.sl * C.stage_bytes;
             const uint32_t nbk = min(CT, L.nb - c * CT), U = nbk * SUB;
             uint32_t j = warp >= C.ubase ? warp - C.ubase : warp + CH_WARPS - C.ubase;
@@ -347,20 +447,18 @@ __device__ __forceinline__ void chain_consume(const ChainStep &S, ChainCta &C, u
                 tile_mac<FMT, ACT, false>(ta, da, xb_a, xr_a, TC, lane, a);
                 if (PAIR) tile_mac<FMT, ACT, false>(ta + half_off, da + half_off, xb_a, xr_a, TC, lane, b);
             };
-            // two tiles per pass: two independent chains for the scheduler to interleave
-            for (; j + CH_WARPS < U; j += 2u * CH_WARPS) {
-                mac(j, acc, up);
-                mac(j + CH_WARPS, acc2, up2);
+            // (one call site, not unrolled: a second copy of the tile code costs registers that the compiler then
+            // spills inside this loop, which measured slower than the latency the second chain would hide)
+            if (!(C.debug & 1u)) {
+#pragma unroll 1
+                for (; j < U; j += CH_WARPS) mac(j, acc, up);
             }
-            if (j < U) mac(j, acc, up);
             C.ubase = (C.ubase + U) % CH_WARPS;
             __syncwarp();
             if (lane == 0) mbar_arrive(&empty[C.sl]);  // this warp's reads of the stage are complete
             if (++C.sl == C.n_stages) { C.sl = 0; C.ph ^= 1u; }
         }
         // the row group is complete for this warp: its partial sums wait for the reduction
-        acc[0] += acc2[0]; acc[1] += acc2[1];
-        up[0] += up2[0]; up[1] += up2[1];
         if (ACT == CHAIN_ACT_DIGITS) {
             // lane t of a quad holds digit t's share of rows g and g + 8
 #pragma unroll
@@ -383,8 +481,12 @@ __device__ __forceinline__ void chain_consume(const ChainStep &S, ChainCta &C, u
         waiting += PER;
         const bool last = n + 1u == my_n;
         if (last || waiting + PER > (uint32_t)CHAIN_PART_SLOTS) {
+            if (last) {
+                ch_trace(C, 3);
+                if (warp == 0) ch_fetch_wait();  // the next step's descriptor has landed: this barrier hands it over
+            }
             CH_CONS_BAR();
-            chain_flush<PAIR>(S, C, first_n, waiting / PER, osc, epoch);
+            chain_flush<PAIR>(S, C, first_n, waiting / PER, osc, epoch, early);
             // (after the step's last row group nothing waits here: the next write to this area lies behind
             // the barriers of the next prologue, which the threads still adding up pass last)
             if (!last) CH_CONS_BAR();
@@ -397,32 +499,32 @@ __device__ __forceinline__ void chain_consume(const ChainStep &S, ChainCta &C, u
 template <int FMT>
 __device__ __forceinline__ void chain_step_fmt(const ChainStep &S, ChainCta &C, uint32_t epoch) {
     if (S.act == STRIX_ACT_Q8DOT) {
-        if (S.pre == STRIX_PRE_RMSNORM) chain_prologue_q8<FMT, STRIX_PRE_RMSNORM>(S, C);
-        else chain_prologue_q8<FMT, STRIX_PRE_NONE>(S, C);
-        ch_trace(C, 1);
+        ch_trace(C, 2);
         if (S.pair) chain_consume<FMT, STRIX_ACT_Q8DOT, true>(S, C, epoch);
         else chain_consume<FMT, STRIX_ACT_Q8DOT, false>(S, C, epoch);
         return;
     }
+#ifndef CHAIN_MIN
     // f32 activations (plain input, no pre-op: independent GEMVs of a batch)
     ActIn I;
     I.a = S.a; I.b = nullptr; I.K = S.L.in_dim; I.B = 1; I.a_stride = 0; I.b_stride = 0; I.x_off = C.x_off; I.eps = 0.f;
     if constexpr (FMT == FMT_Q6_K) {
         if (S.act == CHAIN_ACT_DIGITS) {
             consumer_prologue<FMT, ACT_F32_DIGITS, false, STRIX_PRE_NONE>(I, C.c);
-            ch_trace(C, 1);
+            ch_trace(C, 2);
             chain_consume<FMT, ACT_F32_DIGITS, false>(S, C, epoch);
             return;
         }
     }
     consumer_prologue<FMT, STRIX_ACT_F32, false, STRIX_PRE_NONE>(I, C.c);
-    ch_trace(C, 1);
+    ch_trace(C, 2);
     chain_consume<FMT, STRIX_ACT_F32, false>(S, C, epoch);
+#endif
 }
 
 __global__ void __launch_bounds__((CH_WARPS + 1) * 32, 1)
 chain_kernel(const ChainStep *__restrict__ steps, uint32_t n_steps, ChainGeom G, uint32_t *gctl, uint32_t *status,
-             uint32_t poll_limit, unsigned long long *trace) {
+             uint32_t poll_limit, uint32_t debug, unsigned long long *trace) {
     extern __shared__ __align__(128) uint8_t smem[];
     ChainCta C;
     C.c.smem = smem;
@@ -446,6 +548,9 @@ chain_kernel(const ChainStep *__restrict__ steps, uint32_t n_steps, ChainGeom G,
     C.sl = C.ph = C.ubase = 0;
     C.lap0 = 1;
     C.poll_limit = poll_limit;
+    C.debug = debug;
+    C.trace = nullptr;
+    C.wait_clk = 0;
     // the epoch base of this launch: every CTA reads it before it can leave, and the last CTA to leave
     // moves it on (below), so no launch ever sees a value change under it
     C.epoch_base = *reinterpret_cast<volatile uint32_t *>(gctl);
@@ -461,12 +566,20 @@ chain_kernel(const ChainStep *__restrict__ steps, uint32_t n_steps, ChainGeom G,
     __syncthreads();
     if (C.c.warp == CH_WARPS) {
         // ---------------- producer warp ----------------
-        if (C.c.lane == 0) {
-            uint32_t issued = 0;
-            for (uint32_t s = 0; s < n_steps && !ch_ctl(C)[0]; s++) {
-                chain_produce(steps[s], C);
-                issued += ch_items(C, steps[s]) * steps[s].n_chunks;
+        uint8_t *slot = smem + CH_STEP_OFF + 3u * CH_STEP_BYTES;
+        const ChainStep &S = *reinterpret_cast<const ChainStep *>(slot);
+        uint32_t issued = 0;
+        for (uint32_t s = 0; s < n_steps && !ch_ctl(C)[0]; s++) {
+            __syncwarp();
+            ch_fetch_step(steps, s, slot, C.c.lane);
+            ch_fetch_wait();
+            __syncwarp();
+            if (C.c.lane == 0) {
+                chain_produce(S, C);
+                issued += ch_items(C, S) * S.n_chunks;
             }
+        }
+        if (C.c.lane == 0) {
             if (ch_ctl(C)[0]) {
                 // after an abort the consumers stop waiting: let the copies still in flight land (bounded)
                 // before the CTA's shared memory is released
@@ -483,20 +596,44 @@ chain_kernel(const ChainStep *__restrict__ steps, uint32_t n_steps, ChainGeom G,
         return;
     }
     // ---------------- consumer warps ----------------
+    if (C.c.warp == 0) {
+        ch_fetch_step(steps, 0, smem + CH_STEP_OFF, C.c.lane);
+        ch_fetch_wait();
+    }
+    CH_CONS_BAR();
     for (uint32_t s = 0; s < n_steps; s++) {
-        const ChainStep &S = steps[s];
-        C.trace = (trace && C.c.bid == 0) ? trace + 3u * s : nullptr;
+        const ChainStep &S = *reinterpret_cast<const ChainStep *>(smem + CH_STEP_OFF + (s % 3u) * CH_STEP_BYTES);
+        // the next step's descriptor comes in while this step runs; what makes it visible to the other warps
+        // is a barrier of this step (the prologue's, or the one below for a CTA without rows in this step)
+        if (C.c.warp == 0 && s + 1u < n_steps) ch_fetch_step(steps, s + 1u, smem + CH_STEP_OFF + ((s + 1u) % 3u) * CH_STEP_BYTES, C.c.lane);
+        C.trace = (trace && C.c.bid == 0) ? trace + (size_t)CHAIN_TRACE_WORDS * s : nullptr;
+        C.wait_clk = 0;
         ch_trace(C, 0);
+        if (ch_items(C, S) == 0u) {
+            if (C.c.warp == 0) ch_fetch_wait();
+            CH_CONS_BAR();
+        }
         if (ch_items(C, S) != 0u) {
             const uint32_t epoch = C.epoch_base + s + 1u;
+            if (S.act == STRIX_ACT_Q8DOT) {
+                // (one copy of the prologue for all formats: they differ in the operand layout of Q6_K and in the
+                // bias of the stored codes; Q4_1 is not centred: its record keeps +d_x * sum(codes))
+                const int fmt = S.L.fmt;
+                const int bias = fmt == FMT_Q8_0 ? 128 : fmt == FMT_Q4_0 ? 8 : fmt == FMT_Q4_1 ? -1 : 32;
+                if (S.pre == STRIX_PRE_RMSNORM) chain_prologue_q8<STRIX_PRE_RMSNORM>(S, C, fmt == FMT_Q6_K, bias);
+                else chain_prologue_q8<STRIX_PRE_NONE>(S, C, fmt == FMT_Q6_K, bias);
+            }
             switch (S.L.fmt) {
                 case FMT_Q4_0: chain_step_fmt<FMT_Q4_0>(S, C, epoch); break;
+#ifndef CHAIN_MIN
                 case FMT_Q4_1: chain_step_fmt<FMT_Q4_1>(S, C, epoch); break;
                 case FMT_Q8_0: chain_step_fmt<FMT_Q8_0>(S, C, epoch); break;
+#endif
                 default: chain_step_fmt<FMT_Q6_K>(S, C, epoch); break;
             }
         }
-        ch_trace(C, 2);
+        ch_trace(C, 4);
+        if (C.trace && C.c.tid == 0) C.trace[5] = (unsigned long long)C.wait_clk;
     }
     // the last CTA to leave moves the epoch base past this launch's steps
     CH_CONS_BAR();
@@ -522,8 +659,8 @@ bool chain_plan(ChainStep *steps, uint32_t n, int num_sms, size_t smem_optin, Ch
         const uint32_t K = s.L.in_dim;
         if (K == 0 || K % 32u != 0 || s.nmat < 1 || s.nmat > GEMV_MAX_MATS) return false;
         if (s.act == STRIX_ACT_Q8DOT) {
-            // the integer-dot prologue keeps the whole row in registers
-            if (K > CH_NI * 4u * CH_WARPS * 32u) return false;
+            // the RMSNorm prologue keeps the whole row in registers
+            if (s.pre == STRIX_PRE_RMSNORM && K > (uint32_t)CH_NORM_NI * 4u * CH_WARPS * 32u) return false;
             if (s.pre != STRIX_PRE_NONE && s.pre != STRIX_PRE_RMSNORM) return false;
             if (s.pre == STRIX_PRE_RMSNORM && !s.b) return false;
             if (!s.a && !s.a_ll) return false;
@@ -585,12 +722,12 @@ cudaError_t chain_prepare_device(size_t smem_optin) {
 }
 
 cudaError_t launch_chain(const ChainStep *d_steps, uint32_t n_steps, const ChainGeom &geom, uint32_t *d_ctl,
-                         uint32_t *d_status, uint32_t poll_limit, unsigned long long *d_trace, int num_sms,
+                         uint32_t *d_status, uint32_t poll_limit, uint32_t debug, unsigned long long *d_trace, int num_sms,
                          cudaStream_t stream) {
     if (n_steps == 0) return cudaSuccess;
     ChainGeom g = geom;
-    void *args[7] = {(void *)&d_steps, (void *)&n_steps, (void *)&g, (void *)&d_ctl, (void *)&d_status, (void *)&poll_limit,
-                     (void *)&d_trace};
+    void *args[8] = {(void *)&d_steps, (void *)&n_steps, (void *)&g, (void *)&d_ctl, (void *)&d_status, (void *)&poll_limit,
+                     (void *)&debug, (void *)&d_trace};
     const dim3 grid((unsigned)num_sms), block((CH_WARPS + 1) * 32);
     // cooperative: CTAs wait for one another's outputs, so all of them must be resident
     return cudaLaunchCooperativeKernel((const void *)chain_kernel, grid, block, args, geom.smem_bytes, stream);

@@ -58,6 +58,25 @@ __device__ __forceinline__ bool mbar_wait_bounded(uint64_t *bar, uint32_t parity
     return false;
 }
 
+// The same wait for code that shares its SM's issue slots with working warps: each try lets the hardware
+// suspend the thread for up to `hint_ns` before it answers, so a waiting warp issues a handful of
+// instructions per microsecond instead of spinning. Bounded like mbar_wait_bounded.
+__device__ __forceinline__ bool mbar_wait_suspended(uint64_t *bar, uint32_t parity, uint32_t *status, uint32_t hint_ns) {
+    for (uint32_t it = 0; it < (1u << 22); ++it) {
+        uint32_t ok;
+        asm volatile(
+            "{\n\t.reg .pred p;\n\t"
+            "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
+            "selp.b32 %0, 1, 0, p;\n\t}"
+            : "=r"(ok)
+            : "r"(smem_u32(bar)), "r"(parity), "r"(hint_ns)
+            : "memory");
+        if (ok) return true;
+    }
+    if (status) atomicOr(status, STATUS_WAIT_TIMEOUT);
+    return false;
+}
+
 // 1-D bulk async copy global -> shared, completion counted on an mbarrier.
 // dst, src 16-byte aligned; bytes a multiple of 16. No multicast.
 __device__ __forceinline__ void bulk_g2s(void *dst_smem, const void *src_gmem, uint32_t bytes, uint64_t *bar) {

@@ -290,7 +290,7 @@ static const strix_decode_state::Program *chain_program(strix_cuda *h, strix_dec
     p.logits = d->logits;
     p.n_steps = (uint32_t)steps.size();
     if (h->chain_trace && !d->d_trace) {
-        const size_t nb = 3 * steps.size() * sizeof(unsigned long long);
+        const size_t nb = (size_t)CHAIN_TRACE_WORDS * steps.size() * sizeof(unsigned long long);
         if (cudaMalloc(&d->d_trace, nb) == cudaSuccess) {
             cudaMemset(d->d_trace, 0, nb);
             d->trace_n = (uint32_t)steps.size();
@@ -308,7 +308,7 @@ static const strix_decode_state::Program *chain_program(strix_cuda *h, strix_dec
 // Enqueue the whole chain on `s`. Returns 1, or <0 with h->err set.
 static int enqueue_chain(strix_cuda *h, strix_decode_state *d, cudaStream_t s) {
     if (const strix_decode_state::Program *p = chain_program(h, d, s)) {
-        CU_TRY(h, launch_chain(p->d_steps, p->n_steps, p->geom, d->d_ctl, h->d_status, h->poll_limit, d->d_trace,
+        CU_TRY(h, launch_chain(p->d_steps, p->n_steps, p->geom, d->d_ctl, h->d_status, h->poll_limit, h->chain_debug, d->d_trace,
                                h->num_sms, s));
         return 1;
     }
@@ -713,17 +713,18 @@ int strix_cuda_decode_set_peers(strix_cuda *h, int n, void *const *blocks) {
     return 1;
 }
 
-// Measurement only: after set_option("chain_trace", 1) the chain kernel's CTA 0 notes the clock
-// (nanoseconds) at each step's start, after its prologue (the wait for the activations included) and after
-// its row groups; this copies out the words of the last launch. Returns the number of steps, 0 without a trace.
+// Measurement only: after set_option("chain_trace", 1) the chain kernel's CTA 0 notes, per step, the clock (ns)
+// at its start, when its activations have arrived, after its prologue, after its last row group and after its
+// reduction and stores, and the SM clocks spent waiting for weight stages (CHAIN_TRACE_WORDS = 6 words per
+// step); this copies out the words of the last launch. Returns the number of steps, 0 without a trace.
 int strix_cuda_decode_trace(strix_cuda *h, unsigned long long *out, size_t cap_words) {
     if (!h || !out) return -1;
     h->err.clear();
     strix_decode_state *d = h->decode;
-    if (!d || !d->d_trace || cap_words < 3u * d->trace_n) return 0;
+    if (!d || !d->d_trace || cap_words < (size_t)CHAIN_TRACE_WORDS * d->trace_n) return 0;
     CU_TRY(h, cudaSetDevice(h->device));
     CU_TRY(h, cudaDeviceSynchronize());
-    CU_TRY(h, cudaMemcpy(out, d->d_trace, 3u * d->trace_n * sizeof(unsigned long long), cudaMemcpyDeviceToHost));
+    CU_TRY(h, cudaMemcpy(out, d->d_trace, (size_t)CHAIN_TRACE_WORDS * d->trace_n * sizeof(unsigned long long), cudaMemcpyDeviceToHost));
     return (int)d->trace_n;
 }
 

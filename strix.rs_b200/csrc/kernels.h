@@ -131,7 +131,9 @@ struct ChainStep {
     uint32_t chunk_tiles;  // GGUF blocks of K per stage (per matrix of a pair)
     uint32_t n_chunks;     // stages per work item
     uint32_t rot;          // CTA that takes the step's first item
+    uint32_t pad_[2];      // sizeof a multiple of 16: a warp copies a step into shared memory as 16-byte words
 };
+static_assert(sizeof(ChainStep) % 16 == 0 && sizeof(ChainStep) <= 512, "ChainStep: whole 16-byte words, at most 32 of them");
 
 struct ChainGeom {
     uint32_t n_stages, stage_bytes, stage_off, x_off, smem_bytes;
@@ -142,11 +144,15 @@ bool chain_plan(ChainStep *steps, uint32_t n, int num_sms, size_t smem_optin, Ch
 cudaError_t chain_prepare_device(size_t smem_optin);
 // d_steps: the planned list in device memory. d_ctl: two words {epoch base, exit ticket}, zero-initialised once
 // and then owned by the launches (each adds n_steps to the base when its last CTA leaves). d_trace: null, or
-// 3 * n_steps device words that receive CTA 0's clock at each step's start, after its prologue and after its
-// row groups (measurement only). poll_limit: bound of every wait on an exchange vector, in polls.
+// CHAIN_TRACE_WORDS * n_steps device words (measurement only) that receive, from CTA 0 and per step: the clock (ns)
+// at its start, when its activations have arrived, after its prologue, after its last row group, after its
+// reduction and stores; and the SM clocks its first thread spent waiting for weight stages. poll_limit: bound
+// of every wait on an exchange vector, in polls. debug (measurement only): bit 0 = no arithmetic, bit 1 = the
+// waits on exchange vectors do not wait.
+constexpr int CHAIN_TRACE_WORDS = 6;
 cudaError_t launch_chain(const ChainStep *d_steps, uint32_t n_steps, const ChainGeom &geom, uint32_t *d_ctl,
-                         uint32_t *d_status, uint32_t poll_limit, unsigned long long *d_trace, int num_sms,
-                         cudaStream_t stream);
+                         uint32_t *d_status, uint32_t poll_limit, uint32_t debug, unsigned long long *d_trace,
+                         int num_sms, cudaStream_t stream);
 
 // ---- W8A8 prefill GEMM (tcgen05 int8 MMA) ----------------------------------
 cudaError_t gemm_prepare_device();
