@@ -261,11 +261,15 @@ def decode_chain_sharded_extra(pkg, synth, torch, dist, local, stream, rank, wor
             for nm, (n, k) in shapes.items():
                 assert acc.upload_q4_0("blk.%d.%s.weight" % (il, nm), base[nm], k, n)   # the library keeps its row shard
                 nbytes += n * (k // 32) * 18
-            norms.append([torch.from_numpy(synth.norm_weight(3, "dc.%d.%s" % (il, nn), hidden)).to(dev)
-                          for nn in ("attn_norm", "ffn_norm")])
+            nws = [synth.norm_weight(3, "dc.%d.%s" % (il, nn), hidden) for nn in ("attn_norm", "ffn_norm")]
+            for nn, nw in zip(("attn_norm", "ffn_norm"), nws):
+                acc.upload_f32("blk.%d.%s.weight" % (il, nn), nw)
+            norms.append([torch.from_numpy(nw).to(dev) for nw in nws])
         assert acc.upload_q6_k("output.weight", make_weight(synth, Q6_K, hidden, vocab, 3, "dc.head"), hidden, vocab)
         nbytes += vocab * (hidden // 256) * 210
-        out_norm = torch.from_numpy(synth.norm_weight(3, "dc.out_norm", hidden)).to(dev)
+        out_norm_np = synth.norm_weight(3, "dc.out_norm", hidden)
+        acc.upload_f32("output_norm.weight", out_norm_np)
+        out_norm = torch.from_numpy(out_norm_np).to(dev)
         h0 = torch.from_numpy(synth.normal(3, "dc.h0", hidden)).to(dev)
 
         def full(n):
@@ -397,31 +401,36 @@ def decode_chain_sharded_extra(pkg, synth, torch, dist, local, stream, rank, wor
                                       pre=pkg.PRE_RMSNORM, act=act, stream=s)
             bar()
 
-        def chain_fused_sync(act):
-            """as chain_fused, but the exchange lives inside the GEMV kernels: no barrier launch between steps"""
-            s = torch.cuda.current_stream().cuda_stream
-            p = lambda t: t.data_ptr()  # noqa: E731
-            sy = fused["sync"]
-            for il in range(n_layers):
-                b = "blk.%d." % il
-                an, fn = norms[il]
-                assert acc.gemv_peers_dev([b + "attn_q.weight", b + "attn_k.weight", b + "attn_v.weight"], p(h_full),
-                                          [ptrs["q"], ptrs["k"], ptrs["v"]], d_b=p(an), eps=1e-6, pre=pkg.PRE_RMSNORM,
-                                          act=act, stream=s, sync=sy)
-                assert acc.gemv_peers_dev([b + "attn_output.weight"], p(q_full), [ptrs["h"]], act=act, stream=s,
-                                          d_res=[p(h_res)], sync=sy)
-                assert acc.gemv_peers_dev([b + "ffn_gate.weight", b + "ffn_up.weight"], p(h_full), [ptrs["g"], ptrs["u"]],
-                                          d_b=p(fn), eps=1e-6, pre=pkg.PRE_RMSNORM, act=act, stream=s, sync=sy)
-                assert acc.gemv_peers_dev([b + "ffn_down.weight"], p(g_full), [ptrs["h"]], d_b=p(u_full),
-                                          pre=pkg.PRE_SWIGLU, act=act, stream=s, d_res=[p(h_res)], sync=sy)
-            assert acc.gemv_peers_dev(["output.weight"], p(h_full), [ptrs["lg"]], d_b=p(out_norm), eps=1e-6,
-                                      pre=pkg.PRE_RMSNORM, act=act, stream=s, sync=sy)
-            acc.peer_barrier_dev(p(epoch), p(flags), ptrs["flags"], stream=s)   # before anyone reads the logits
+        # ---- chain-kernel form: ONE persistent launch per token and rank; every step publishes its rows into the
+        #      exchange block of every rank (peer stores of {value, epoch} entries), no barrier, no collective ----
+        ck = {"ok": False, "why": ""}
+        try:
+            if not acc.configure_decode(hidden, 32, ffn, vocab, n_layers, eps=1e-6, act=pkg.ACT_Q8DOT):
+                raise RuntimeError("configure_decode declined on the sharded handle")
+            base_ptr, nbytes_blk = acc.decode_exchange_info()
+            metas = [None] * world
+            dist.all_gather_object(metas, acc.ipc_export(base_ptr))
+            blocks = [0 if r == rank else acc.ipc_open(metas[r]) for r in range(world)]
+            # every mapping checked with a copy-engine read of a mark before any kernel stores through it
+            acc.poke_u32(base_ptr + nbytes_blk - 4, 0x5EED7700 + rank)   # (the block's last 128 bytes are spare)
+            dist.barrier()
+            for r in range(world):
+                if r != rank and acc.peek_u32(blocks[r] + nbytes_blk - 4) != 0x5EED7700 + r:
+                    raise RuntimeError("exchange block of rank %d does not read back its mark" % r)
+            dist.barrier()
+            assert acc.decode_set_peers(blocks)
+            ck["ok"] = True
+        except Exception as ex:
+            ck["why"] = "%s: %s" % (type(ex).__name__, ex)
 
-        if fused["ok"]:
-            done = torch.zeros(1, dtype=torch.int32, device=dev)
-            fused["sync"] = acc.make_peer_sync(epoch.data_ptr(), done.data_ptr(), flags.data_ptr(), ptrs["flags"])
-        variants = [("nccl", chain)] + ([("fused", chain_fused), ("fused_sync", chain_fused_sync)] if fused["ok"] else [])
+        lg_ck = torch.zeros(vocab // world, device=dev)
+
+        def chain_kernel(act):
+            s = torch.cuda.current_stream().cuda_stream
+            assert acc.decode_chain_dev(h_full.data_ptr(), lg_ck.data_ptr(), stream=s)
+
+        variants = [("nccl", chain)] + ([("fused", chain_fused)] if fused["ok"] else []) + \
+                   ([("chain_kernel", chain_kernel)] if ck["ok"] else [])
         logits_ref = None
         for vname, chain in variants:
           for act, name in ((pkg.ACT_Q8DOT, "q8dot"),):
@@ -451,22 +460,33 @@ def decode_chain_sharded_extra(pkg, synth, torch, dist, local, stream, rank, wor
                 t = torch.tensor([a.elapsed_time(b2) / reps], device=dev)
                 dist.all_reduce(t, op=dist.ReduceOp.MAX)
                 ms = float(t.item())
-            assert bool(torch.isfinite(lg_full).all()) and acc.device_status(stream.cuda_stream) == 0
-            if logits_ref is None:
-                logits_ref = lg_full.clone()
-            else:   # same shards, same kernels: the two exchange forms must agree bit for bit
-                assert bool((lg_full == logits_ref).all()), "fused and NCCL chains disagree"
+            assert acc.device_status(stream.cuda_stream) == 0
+            if vname == "chain_kernel":
+                # another kernel (RMSNorm before the quantiser, SwiGLU in the epilogue): same integer-dot chain to
+                # quantiser noise, this rank's shard of the logits against the NCCL form's
+                mine = logits_ref[rank * (vocab // world):(rank + 1) * (vocab // world)]
+                err = float((lg_ck - mine).norm() / mine.norm())
+                assert bool(torch.isfinite(lg_ck).all()) and err < 2e-2, "chain kernel and NCCL chain disagree: %g" % err
+                out["chain_kernel_vs_nccl_rel_l2"] = round(err, 6)
+            else:
+                assert bool(torch.isfinite(lg_full).all())
+                if logits_ref is None:
+                    logits_ref = lg_full.clone()
+                else:   # same shards, same kernels: the two exchange forms must agree bit for bit
+                    assert bool((lg_full == logits_ref).all()), "fused and NCCL chains disagree"
             out[vname + "_" + name] = {"ms_per_token": round(ms, 4), "gbs_aggregate": round(nbytes / ms / 1e6, 1),
                                        "gbs_per_gpu": round(nbytes / ms / 1e6 / world, 1),
-                                       "launches_per_token": (4 * n_layers + 1) * (2 if vname == "fused" else 1) + (vname == "fused_sync"),
+                                       "launches_per_token": 1 if vname == "chain_kernel" else (4 * n_layers + 1) * (2 if vname == "fused" else 1),
                                        "collectives_per_token": 4 * n_layers + 1 if vname == "nccl" else 0}
         out["n_gpus"] = world
         out["bytes_per_token"] = nbytes
         out["note"] = ("row-sharded projections; nccl: all-gather after each projection or fused group (coalesced: %s); "
                        "fused: the GEMV stores its rows into every rank's vectors over peer memory, then a flag barrier "
-                       "kernel; fused_sync: the flag wait / release sits inside the GEMV kernels (%s); attention replaced "
-                       "by feeding Wo with q"
-                       % (state["coalesce"], "ran" if fused["ok"] else "not run: " + fused["why"]))
+                       "kernel (%s); chain_kernel: one persistent launch per token, steps publish {value, epoch} entries "
+                       "into every rank's exchange block, consumers poll their own block (%s); attention replaced by "
+                       "feeding Wo with q"
+                       % (state["coalesce"], "ran" if fused["ok"] else "not run: " + fused["why"],
+                          "ran" if ck["ok"] else "not run: " + ck["why"]))
     finally:
         acc.close()
     return out

@@ -138,20 +138,11 @@ STRIX_API int strix_cuda_gemv_res_dev(strix_cuda *h, int nmat, const char *const
  * all-gather follows. d_res (may be null, entries may be null) are this shard's rows of residual
  * vectors. The stores are plain peer stores; they are complete when the kernel is, and
  * strix_cuda_peer_barrier_dev after it on every rank's stream makes them safe to read.
- * With `sync` (may be null) the exchange is folded into the kernel: before it reads the activations it
- * waits (bounded) until every rank's word in d_local_flags has reached *d_epoch, and when its last CTA
- * has stored its rows it bumps *d_epoch and releases it into word `rank` of every rank's flag array -
- * so a chain of such launches needs no barrier launch between them (one strix_cuda_peer_barrier_dev at
- * the end of the chain, before the host reads results). */
-typedef struct strix_peer_sync {
-    uint32_t *d_epoch;            /* one word of this rank, shared with strix_cuda_peer_barrier_dev; starts at 0 */
-    uint32_t *d_done;             /* one word of this rank, starts at 0 */
-    uint32_t *d_local_flags;      /* `world` words of this rank, start at 0 */
-    uint32_t *const *peer_flags;  /* [world]: rank i's flag array as mapped into this process */
-} strix_peer_sync;
+ * A chain of such launches needs that barrier between steps; the persistent chain kernel behind
+ * strix_cuda_configure_decode on a sharded handle carries the exchange inside one launch instead. */
 STRIX_API int strix_cuda_gemv_peers_dev(strix_cuda *h, int nmat, const char *const *keys, const float *d_a,
                               const float *d_b, float eps, int pre, int act, const float *const *d_res,
-                              int n_peers, float *const *peer_ys, const strix_peer_sync *sync, void *stream);
+                              int n_peers, float *const *peer_ys, void *stream);
 /* Lets kernels of this accelerator's device store into memory of `peer_device` (as mapped into this
  * process, e.g. through CUDA IPC). 1 = enabled (or already so), 0 = the devices cannot reach each other. */
 STRIX_API int strix_cuda_enable_peer_access(strix_cuda *h, int peer_device);
@@ -159,9 +150,14 @@ STRIX_API int strix_cuda_enable_peer_access(strix_cuda *h, int peer_device);
  * accelerator's device; *out is the base of the exported allocation. Open a given handle once. */
 STRIX_API int strix_cuda_ipc_open(strix_cuda *h, const void *handle, size_t handle_len, void **out);
 STRIX_API int strix_cuda_ipc_close(strix_cuda *h, void *p);
+/* The CUDA IPC handle (64 bytes) of the device allocation that starts at d_ptr (e.g. the exchange block of
+ * strix_cuda_decode_exchange_info), for another process to open with strix_cuda_ipc_open. */
+STRIX_API int strix_cuda_ipc_export(strix_cuda *h, const void *d_ptr, void *handle, size_t handle_cap);
 /* One 32-bit word of device (or peer-mapped) memory, by a copy engine transfer: lets a caller check a
  * mapping it was handed before any kernel stores through it. */
 STRIX_API int strix_cuda_peek_u32(strix_cuda *h, const void *d_ptr, uint32_t *out);
+/* The counterpart: writes one word (e.g. the mark a peer then reads back through its mapping). */
+STRIX_API int strix_cuda_poke_u32(strix_cuda *h, void *d_ptr, uint32_t value);
 /* Cross-GPU barrier for the form above: one launch per rank (opts.rank / opts.world of the handle), one
  * rank per GPU. d_epoch: one zero-initialised word of this rank; d_local_flags: `world` zero-initialised
  * words of this rank; peer_flags[i]: rank i's flag array as mapped into this process. The wait is
@@ -275,7 +271,8 @@ STRIX_API int strix_cuda_seed_decode_kv(strix_cuda *h, size_t il, const float *k
  * rank runs the persistent chain kernel over its row shards and publishes each step's rows into the
  * exchange block of EVERY rank with plain peer stores (8-byte {value, epoch} entries; no collective, no
  * barrier launch, no multicast); a rank's consumers poll their own block. strix_cuda_decode_exchange_info
- * returns this rank's block (one cudaMalloc allocation, exportable with cudaIpcGetMemHandle);
+ * returns this rank's block (one cudaMalloc allocation, exportable with strix_cuda_ipc_export; its last 128
+ * bytes are spare, for a mark that lets the peers check their mapping before any kernel stores through it);
  * strix_cuda_decode_set_peers hands over all ranks' blocks as mapped into this process (entry `rank` may
  * be null). Until the group is wired a rank publishes into its own block only, so its waits for the other
  * ranks' rows run out: bounded (option "poll_limit"), the status word gets the time-out bit, the call
@@ -299,6 +296,9 @@ STRIX_API int strix_cuda_gemv_rows_dev(strix_cuda *h, int nmat, const char *cons
 /* Device status word written by kernels whose bounded waits ran out
  * (0 = clean). Synchronises `stream`. */
 STRIX_API int strix_cuda_device_status(strix_cuda *h, void *stream, uint32_t *status);
+/* Resets the status word (the host-buffer entry points do so themselves when they report it with -2; a
+ * caller of the _dev entry points that has seen a non-zero status clears it here). Synchronises `stream`. */
+STRIX_API int strix_cuda_clear_device_status(strix_cuda *h, void *stream);
 
 /* ---- test / measurement extras (not part of the trait) ---- */
 

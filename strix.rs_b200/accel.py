@@ -18,12 +18,6 @@ PRE_NONE, PRE_RMSNORM, PRE_SWIGLU, PRE_GEGLU = 0, 1, 2, 3
 _HERE = os.path.dirname(os.path.abspath(__file__))
 
 
-class PeerSync(C.Structure):
-    """strix_peer_sync (include/strix_cuda.h)."""
-    _fields_ = [("d_epoch", C.c_void_p), ("d_done", C.c_void_p), ("d_local_flags", C.c_void_p),
-                ("peer_flags", C.POINTER(C.c_void_p))]
-
-
 class StrixCudaError(RuntimeError):
     pass
 
@@ -87,11 +81,13 @@ def load_library():
     sig("strix_cuda_gemv_res_dev", C.c_int, H, C.c_int, C.POINTER(C.c_char_p), C.c_void_p, C.c_void_p, C.c_float,
         C.c_int, C.c_int, C.POINTER(C.c_void_p), C.POINTER(C.c_void_p), C.c_void_p)
     sig("strix_cuda_gemv_peers_dev", C.c_int, H, C.c_int, C.POINTER(C.c_char_p), C.c_void_p, C.c_void_p, C.c_float,
-        C.c_int, C.c_int, C.POINTER(C.c_void_p), C.c_int, C.POINTER(C.c_void_p), C.POINTER(PeerSync), C.c_void_p)
+        C.c_int, C.c_int, C.POINTER(C.c_void_p), C.c_int, C.POINTER(C.c_void_p), C.c_void_p)
     sig("strix_cuda_enable_peer_access", C.c_int, H, C.c_int)
     sig("strix_cuda_ipc_open", C.c_int, H, C.c_char_p, sz, C.POINTER(C.c_void_p))
     sig("strix_cuda_ipc_close", C.c_int, H, C.c_void_p)
+    sig("strix_cuda_ipc_export", C.c_int, H, C.c_void_p, C.c_char_p, sz)
     sig("strix_cuda_peek_u32", C.c_int, H, C.c_void_p, C.POINTER(C.c_uint32))
+    sig("strix_cuda_poke_u32", C.c_int, H, C.c_void_p, C.c_uint32)
     sig("strix_cuda_peer_barrier_dev", C.c_int, H, C.c_void_p, C.c_void_p, C.POINTER(C.c_void_p), C.c_void_p)
     sig("strix_cuda_prefill_q8_gemm", C.c_int, H, C.c_char_p, f32p, sz, f32p, sz)
     sig("strix_cuda_prefill_q8_gemm_dev", C.c_int, H, C.c_char_p, C.c_void_p, sz, C.c_void_p, C.c_void_p)
@@ -112,6 +108,7 @@ def load_library():
     sig("strix_cuda_gemv_rows_dev", C.c_int, H, C.c_int, C.POINTER(C.c_char_p), C.c_void_p, sz, C.c_int,
         C.POINTER(C.c_void_p), C.c_void_p)
     sig("strix_cuda_device_status", C.c_int, H, C.c_void_p, C.POINTER(C.c_uint32))
+    sig("strix_cuda_clear_device_status", C.c_int, H, C.c_void_p)
     sig("strix_cuda_dequant_to_f32", C.c_int, H, C.c_char_p, f32p, sz)
     sig("strix_cuda_xquant8", C.c_int, H, f32p, sz, C.POINTER(C.c_int8), f32p)
     sig("strix_cuda_debug_gemm_isums", C.c_int, H, C.c_char_p, f32p, sz, C.c_uint32, C.POINTER(C.c_int32), sz)
@@ -463,28 +460,16 @@ class CudaWeightAccel:
                                                     C.c_void_p(int(stream)) if stream else None))
         return rc == 1
 
-    def make_peer_sync(self, d_epoch, d_done, d_local_flags, peer_flags):
-        """The sync block of gemv_peers_dev (keeps the pointer array alive with the returned object)."""
-        arr = (C.c_void_p * len(peer_flags))(*[int(p) for p in peer_flags])
-        ps = PeerSync(C.c_void_p(int(d_epoch)), C.c_void_p(int(d_done)), C.c_void_p(int(d_local_flags)),
-                      C.cast(arr, C.POINTER(C.c_void_p)))
-        ps._keep = arr
-        return ps
-
-    def gemv_peers_dev(self, keys, d_a, peer_ys, d_b=0, eps=0.0, pre=PRE_NONE, act=ACT_F32, stream=0, d_res=None,
-                       sync=None):
+    def gemv_peers_dev(self, keys, d_a, peer_ys, d_b=0, eps=0.0, pre=PRE_NONE, act=ACT_F32, stream=0, d_res=None):
         """Row-sharded form: peer_ys[m] = the device pointers of weight m's FULL output vector on every
-        accelerator of the group (own copy included); rows land at row0 + r in each of them.
-        sync (make_peer_sync): fold the exchange into the kernel (wait on the ranks' flags before reading
-        the activations, release the next epoch to them after the last row is stored)."""
+        accelerator of the group (own copy included); rows land at row0 + r in each of them."""
         n, npeer = len(keys), len(peer_ys[0])
         kk = (C.c_char_p * n)(*[k.encode() for k in keys])
         pp = (C.c_void_p * (n * npeer))(*[int(p) for ys in peer_ys for p in ys])
         rr = (C.c_void_p * n)(*[int(p) if p else None for p in d_res]) if d_res is not None else None
         rc = self._check(self._L.strix_cuda_gemv_peers_dev(self._h, n, kk, C.c_void_p(int(d_a)),
                                                           C.c_void_p(int(d_b)) if d_b else None, float(eps), pre, act,
-                                                          rr, npeer, pp, C.byref(sync) if sync is not None else None,
-                                                          C.c_void_p(int(stream)) if stream else None))
+                                                          rr, npeer, pp, C.c_void_p(int(stream)) if stream else None))
         return rc == 1
 
     def enable_peer_access(self, peer_device):
@@ -495,6 +480,15 @@ class CudaWeightAccel:
         out = C.c_void_p()
         self._check(self._L.strix_cuda_ipc_open(self._h, bytes(handle), len(handle), C.byref(out)))
         return int(out.value)
+
+    def poke_u32(self, d_ptr, value):
+        return self._check(self._L.strix_cuda_poke_u32(self._h, C.c_void_p(int(d_ptr)), int(value))) == 1
+
+    def ipc_export(self, d_ptr):
+        """The 64-byte CUDA IPC handle of the device allocation that starts at d_ptr."""
+        buf = C.create_string_buffer(64)
+        self._check(self._L.strix_cuda_ipc_export(self._h, C.c_void_p(int(d_ptr)), buf, 64))
+        return bytes(buf.raw)
 
     def peek_u32(self, d_ptr):
         out = C.c_uint32()
@@ -515,6 +509,9 @@ class CudaWeightAccel:
         return s.value
 
     # -- test / measurement extras ---------------------------------------
+    def clear_device_status(self, stream=0):
+        return self._check(self._L.strix_cuda_clear_device_status(self._h, C.c_void_p(int(stream)) if stream else None)) == 1
+
     def set_option(self, name, value):
         """Planning / measurement knob by name (see strix_cuda_set_option); False for an unknown name."""
         return self._check(self._L.strix_cuda_set_option(self._h, name.encode(), int(value))) == 1

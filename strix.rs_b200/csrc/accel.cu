@@ -326,7 +326,7 @@ int strix_cuda_set_option(strix_cuda *h, const char *name, long long value) {
     else if (n == "gemv_pdl") h->tune.pdl = v;
     else if (n == "gemv_debug") h->tune.debug = v;
     else if (n == "batch_graph") h->use_batch_graph = value != 0;
-    else if (n == "decode_chain") h->decode_chain = value != 0;
+    else if (n == "decode_chain") h->decode_chain = value < 0 ? -1 : value != 0;
     else if (n == "chain_trace") h->chain_trace = value != 0;
     else if (n == "chain_debug") h->chain_debug = v;
     else if (n == "poll_limit") h->poll_limit = v ? v : CHAIN_POLL_LIMIT;
@@ -624,7 +624,7 @@ int strix_cuda_gemv_res_dev(strix_cuda *h, int nmat, const char *const *keys, co
 
 int strix_cuda_gemv_peers_dev(strix_cuda *h, int nmat, const char *const *keys, const float *d_a, const float *d_b,
                               float eps, int pre, int act, const float *const *d_res, int n_peers,
-                              float *const *peer_ys, const strix_peer_sync *sync, void *stream) {
+                              float *const *peer_ys, void *stream) {
     if (!h || !keys || !d_a || !peer_ys) return -1;
     h->err.clear();
     if (nmat < 1 || nmat > GEMV_MAX_MATS || n_peers < 1 || n_peers > GEMV_MAX_PEERS) {
@@ -650,22 +650,6 @@ int strix_cuda_gemv_peers_dev(strix_cuda *h, int nmat, const char *const *keys, 
         for (int p = 0; p < n_peers; p++) a.mat[m].peer_y[p] = peer_ys[m * n_peers + p];
     }
     a.nbatch = 1;
-    if (sync) {
-        if (!sync->d_epoch || !sync->d_done || !sync->d_local_flags || !sync->peer_flags) {
-            h->err = "gemv_peers_dev: incomplete sync block";
-            return -1;
-        }
-        a.sync_epoch = sync->d_epoch;
-        a.sync_done = sync->d_done;
-        a.sync_local = sync->d_local_flags;
-        a.sync_world = (uint32_t)h->world;
-        a.sync_rank = (uint32_t)h->rank;
-        if (h->world > GEMV_MAX_PEERS) {
-            h->err = "gemv_peers_dev: at most 8 ranks";
-            return -1;
-        }
-        for (int p = 0; p < h->world; p++) a.sync_peer[p] = sync->peer_flags[p];
-    }
     if (!gemv_plan(a, h->num_sms, h->smem_optin, h->tune)) {
         h->err = "gemv_peers_dev: in_dim too large for the shared-memory pipeline";
         return -1;
@@ -717,6 +701,28 @@ int strix_cuda_peek_u32(strix_cuda *h, const void *d_ptr, uint32_t *out) {
     return 1;
 }
 
+int strix_cuda_poke_u32(strix_cuda *h, void *d_ptr, uint32_t value) {
+    if (!h || !d_ptr) return -1;
+    h->err.clear();
+    CU_TRY(h, cudaSetDevice(h->device));
+    CU_TRY(h, cudaMemcpy(d_ptr, &value, sizeof(uint32_t), cudaMemcpyHostToDevice));
+    return 1;
+}
+
+int strix_cuda_ipc_export(strix_cuda *h, const void *d_ptr, void *handle, size_t handle_cap) {
+    if (!h || !d_ptr || !handle) return -1;
+    h->err.clear();
+    if (handle_cap < sizeof(cudaIpcMemHandle_t)) {
+        h->err = "ipc_export: a CUDA IPC memory handle is " + std::to_string(sizeof(cudaIpcMemHandle_t)) + " bytes";
+        return -1;
+    }
+    CU_TRY(h, cudaSetDevice(h->device));
+    cudaIpcMemHandle_t hd;
+    CU_TRY(h, cudaIpcGetMemHandle(&hd, const_cast<void *>(d_ptr)));
+    memcpy(handle, &hd, sizeof(hd));
+    return 1;
+}
+
 int strix_cuda_ipc_close(strix_cuda *h, void *p) {
     if (!h || !p) return -1;
     h->err.clear();
@@ -730,7 +736,7 @@ int strix_cuda_peer_barrier_dev(strix_cuda *h, uint32_t *d_epoch, uint32_t *d_lo
     if (!h || !d_epoch || !d_local_flags || !peer_flags) return -1;
     h->err.clear();
     CU_TRY(h, cudaSetDevice(h->device));
-    CU_TRY(h, launch_peer_barrier(d_epoch, d_local_flags, peer_flags, h->rank, h->world, h->d_status,
+    CU_TRY(h, launch_peer_barrier(d_epoch, d_local_flags, peer_flags, h->rank, h->world, h->d_status, h->poll_limit,
                                   static_cast<cudaStream_t>(stream)));
     return 1;
 }
@@ -792,6 +798,16 @@ int strix_cuda_device_status(strix_cuda *h, void *stream, uint32_t *status) {
     CU_TRY(h, cudaMemcpyAsync(&h->status_host, h->d_status, 4, cudaMemcpyDeviceToHost, s));
     CU_TRY(h, cudaStreamSynchronize(s));
     *status = h->status_host;
+    return 1;
+}
+
+int strix_cuda_clear_device_status(strix_cuda *h, void *stream) {
+    if (!h) return -1;
+    h->err.clear();
+    CU_TRY(h, cudaSetDevice(h->device));
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    CU_TRY(h, cudaMemsetAsync(h->d_status, 0, 4, s));
+    CU_TRY(h, cudaStreamSynchronize(s));
     return 1;
 }
 

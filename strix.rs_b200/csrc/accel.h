@@ -46,7 +46,9 @@ struct strix_cuda {
     int use_batch_graph = 1;          // gemv_batch replays a cached CUDA graph
     uint32_t chain_debug = 0;         // measurement: see launch_chain
     int chain_trace = 0;              // measurement: the chain kernel records per-step clocks (strix_cuda_decode_trace)
-    int decode_chain = 1;             // the decode projection chain runs as one persistent launch where it can
+    int decode_chain = -1;            // the decode projection chain as one persistent launch: 1 on, 0 off, -1 = on for a
+                                      // row-sharded handle (the only way it can run), off otherwise (a launch per step
+                                      // measured 1.33 against 1.39 ms per token on one GPU)
     uint32_t poll_limit = strix::CHAIN_POLL_LIMIT;  // bound of a wait on an exchange vector, in polls
     int num_sms = 0;
     size_t smem_optin = 0;

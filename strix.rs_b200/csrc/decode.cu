@@ -181,7 +181,8 @@ static int walk_chain(strix_decode_state *d, Emit emit, Mid mid) {
 // chain kernel cannot be used (plan failed, switched off, or a new buffer pair inside a stream capture).
 static const strix_decode_state::Program *chain_program(strix_cuda *h, strix_decode_state *d, cudaStream_t s) {
     // (attention is not a GEMV step, and the exchange-vector prologue is the integer-dot one: launches otherwise)
-    if (!d->chain_ok || d->real_attn || !h->decode_chain || d->cfg.act != STRIX_ACT_Q8DOT) return nullptr;
+    const bool want_chain = h->decode_chain < 0 ? h->world > 1 : h->decode_chain != 0;
+    if (!d->chain_ok || d->real_attn || !want_chain || d->cfg.act != STRIX_ACT_Q8DOT) return nullptr;
     for (auto &p : d->programs)
         if (p.h == d->h && p.logits == d->logits) return &p;
     cudaStreamCaptureStatus cs = cudaStreamCaptureStatusNone;
@@ -364,7 +365,7 @@ int strix_cuda_configure_decode(strix_cuda *h, const strix_gpu_decode_config *cf
     if (cfg->act != STRIX_ACT_F32 && cfg->act != STRIX_ACT_Q8DOT) return 0;
     // A sharded handle holds row shards only: the chain then runs as the persistent kernel alone (projection
     // chain with the stand-in, integer-dot form), every rank publishing its rows into all ranks' exchange vectors.
-    if (h->world > 1 && (real_attn || cfg->act != STRIX_ACT_Q8DOT || !h->decode_chain || h->world > GEMV_MAX_PEERS)) return 0;
+    if (h->world > 1 && (real_attn || cfg->act != STRIX_ACT_Q8DOT || h->decode_chain == 0 || h->world > GEMV_MAX_PEERS)) return 0;
     CU_TRY(h, cudaSetDevice(h->device));
     auto *d = new strix_decode_state();
     d->cfg = *cfg;
@@ -453,7 +454,7 @@ int strix_cuda_configure_decode(strix_cuda *h, const strix_gpu_decode_config *cf
             d->ll_off[i] = off;
             off += (lens[i] + 15) & ~(size_t)15;
         }
-        d->ll_words = std::max<size_t>(off, 16);
+        d->ll_words = off + 16;  // (16 spare entries at the end: room for a mapping-check mark)
         if (e == cudaSuccess) e = cudaMalloc(&d->ll_block, d->ll_words * 8);
         if (e == cudaSuccess) e = cudaMemset(d->ll_block, 0, d->ll_words * 8);
         if (e == cudaSuccess) e = cudaMalloc(&d->d_ctl, 8);

@@ -319,43 +319,9 @@ __global__ void __launch_bounds__((GEMV_WARPS + 1) * 32, 1) gemv_kernel(const __
     // Everything above (and the producer's copies) touches only this launch's weights. The activation
     // and the outputs belong to the stream's order: wait for the preceding grid here.
     asm volatile("griddepcontrol.wait;" ::: "memory");
-    if (A.sync_epoch) {
-        // multi-GPU: the activations were stored here by the other ranks' previous kernels; each of them
-        // released the epoch this rank has reached into its flag word when its kernel had finished.
-        // (The producer warp is already prefetching weights: the wait hides behind that.)
-        // (after one wait of the chain has run out nobody waits again: the status word says so)
-        const bool gave_up = A.status && (*reinterpret_cast<volatile uint32_t *>(A.status) & STATUS_WAIT_TIMEOUT);
-        if (C.tid < A.sync_world && !gave_up) {
-            const uint32_t want = *reinterpret_cast<volatile uint32_t *>(A.sync_epoch);
-            bool ok = false;
-            for (uint32_t it = 0; it < (1u << 21) && !ok; ++it) {
-                uint32_t seen;
-                asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(seen) : "l"(A.sync_local + C.tid) : "memory");
-                ok = (int32_t)(seen - want) >= 0;
-            }
-            if (!ok && A.status) atomicOr(A.status, STATUS_WAIT_TIMEOUT);  // bounded: report and go on
-        }
-        asm volatile("bar.sync 15, %0;" ::"r"(C.n_cons * 32u) : "memory");
-    }
     consumer_prologue<FMT, ACT, MULTI, PRE>(act_in(A), C);
     if (A.debug & 4u) return;  // measurement only: stop after the activation prologue
     consumer_groups<FMT, ACT, MULTI>(A, C);
-    if (A.sync_epoch) {
-        // this CTA's rows are stored (locally and on every peer); the last CTA of the grid to get here
-        // tells the other ranks
-        asm volatile("bar.sync 15, %0;" ::"r"(C.n_cons * 32u) : "memory");
-        if (C.tid == 0) {
-            __threadfence_system();
-            if (atomicAdd(A.sync_done, 1u) == gridDim.x - 1u) {
-                *A.sync_done = 0u;
-                const uint32_t e = *reinterpret_cast<volatile uint32_t *>(A.sync_epoch) + 1u;
-                *reinterpret_cast<volatile uint32_t *>(A.sync_epoch) = e;
-                __threadfence_system();
-                for (uint32_t p = 0; p < A.sync_world; p++)
-                    asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(A.sync_peer[p] + A.sync_rank), "r"(e) : "memory");
-            }
-        }
-    }
 }
 
 
@@ -542,7 +508,7 @@ struct PeerFlags {
     uint32_t *p[GEMV_MAX_PEERS];
 };
 __global__ void peer_barrier_kernel(uint32_t *epoch, volatile uint32_t *local_flags, PeerFlags peers, int rank, int world,
-                                    uint32_t *status) {
+                                    uint32_t *status, uint32_t limit) {
     __shared__ uint32_t seq;
     if (threadIdx.x == 0) seq = ++(*epoch);
     __syncthreads();
@@ -552,7 +518,7 @@ __global__ void peer_barrier_kernel(uint32_t *epoch, volatile uint32_t *local_fl
         __threadfence_system();
         asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(peers.p[threadIdx.x] + rank), "r"(want) : "memory");
         bool ok = status && (*reinterpret_cast<volatile uint32_t *>(status) & STATUS_WAIT_TIMEOUT);  // gave up before
-        for (uint32_t it = 0; it < (1u << 22) && !ok; ++it) {
+        for (uint32_t it = 0; it < limit && !ok; ++it) {
             uint32_t seen;
             asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(seen) : "l"(local_flags + threadIdx.x) : "memory");
             ok = (int32_t)(seen - want) >= 0;
@@ -562,11 +528,11 @@ __global__ void peer_barrier_kernel(uint32_t *epoch, volatile uint32_t *local_fl
 }
 
 cudaError_t launch_peer_barrier(uint32_t *d_epoch, uint32_t *d_local_flags, uint32_t *const *peer_flags, int rank,
-                                int world, uint32_t *d_status, cudaStream_t stream) {
+                                int world, uint32_t *d_status, uint32_t poll_limit, cudaStream_t stream) {
     if (world < 1 || world > GEMV_MAX_PEERS) return cudaErrorInvalidValue;
     PeerFlags pf{};
     for (int i = 0; i < world; i++) pf.p[i] = peer_flags[i];
-    peer_barrier_kernel<<<1, 32, 0, stream>>>(d_epoch, d_local_flags, pf, rank, world, d_status);
+    peer_barrier_kernel<<<1, 32, 0, stream>>>(d_epoch, d_local_flags, pf, rank, world, d_status, poll_limit);
     return cudaGetLastError();
 }
 

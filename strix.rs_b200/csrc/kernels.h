@@ -61,13 +61,6 @@ struct GemvArgs {
     uint32_t digits;         // f32 activations carried as three int8 digits per value (Q6_K, one activation row)
     uint32_t pdl;            // launch with programmatic stream serialization
     uint32_t rot;            // chain kernel: CTA that takes the step's first row group
-    // Row-sharded multi-GPU form with the exchange folded in (null sync_epoch = off): the consumers wait
-    // (bounded) until every rank's flag word in sync_local has reached *sync_epoch before they read the
-    // activations, and the last CTA to finish bumps *sync_epoch and releases it into word sync_rank of every
-    // rank's flag array. sync_done counts finished CTAs.
-    uint32_t *sync_epoch, *sync_done, *sync_local;
-    uint32_t *sync_peer[GEMV_MAX_PEERS];
-    uint32_t sync_world, sync_rank;
     uint32_t grid;
     uint32_t smem_bytes;
     uint32_t debug;  // measurement only: bit 0 = stream the tiles but skip the arithmetic
@@ -178,8 +171,9 @@ cudaError_t launch_gemm_w8a8(const uint8_t *d_res, const RowLayout &L, uint32_t 
 // Cross-GPU barrier on flag words in peer-mapped memory (one launch per rank, one rank per GPU):
 // bumps *d_epoch, stores the new value into flag word `rank` of every rank's flag array and waits
 // (bounded) until all `world` words of this rank's own array have reached it.
+// (bounded: poll_limit polls)
 cudaError_t launch_peer_barrier(uint32_t *d_epoch, uint32_t *d_local_flags, uint32_t *const *peer_flags, int rank,
-                                int world, uint32_t *d_status, cudaStream_t stream);
+                                int world, uint32_t *d_status, uint32_t poll_limit, cudaStream_t stream);
 
 // The activation quantiser on its own: q[n] int8, d[n/32] f32 from x[n].
 cudaError_t launch_xquant8(const float *d_x, int8_t *d_q, float *d_d, uint32_t n, cudaStream_t stream);

@@ -249,31 +249,30 @@ def test_peer_store_form_fills_full_vectors_on_every_peer(pkg, orc, synth):
         assert rel_l2(f.cpu().numpy(), want) <= REL_L2_TOL
 
 
-def test_peer_store_form_with_folded_exchange_single_rank(pkg, orc, synth):
-    """world = 1: the kernel waits on its own flag (already there), stores, and its last CTA releases the
-    next epoch; a second launch finds that epoch. No other rank is involved, so nothing can wait for ever."""
+def test_peer_barrier_wait_runs_out_without_the_other_rank(pkg, orc, synth):
+    """Failure detection without a fault: rank 0 of a group of two runs the cross-GPU barrier alone, so the flag
+    word of rank 1 is never raised. The wait is bounded (here 10^4 polls): the kernel returns, the status word
+    shows the time-out, and after it is cleared the handle computes as before."""
     import torch
     dev = torch.device("cuda:0")
-    in_dim, out_dim = 1024, 333
-    w = synth.q8_0(52, "sync", out_dim, in_dim)
-    x = synth.normal(52, "sync.x", in_dim)
-    want = orc.qmatmul(x, w, synth.Q8_0, in_dim, out_dim)
-    a = pkg.CudaWeightAccel(0)
+    a = pkg.CudaWeightAccel(0, rank=0, world=2)
     try:
-        assert a.upload_q8_0("sync", w, in_dim, out_dim)
-        d_x = torch.from_numpy(x).to(dev)
-        y = torch.full((out_dim,), float("nan"), device=dev)
-        epoch, done = torch.zeros(1, dtype=torch.int32, device=dev), torch.zeros(1, dtype=torch.int32, device=dev)
-        flags = torch.zeros(8, dtype=torch.int32, device=dev)
-        sync = a.make_peer_sync(epoch.data_ptr(), done.data_ptr(), flags.data_ptr(), [flags.data_ptr()])
+        assert a.set_option("poll_limit", 10000)
+        epoch = torch.zeros(1, dtype=torch.int32, device=dev)
+        flags0, flags1 = torch.zeros(8, dtype=torch.int32, device=dev), torch.zeros(8, dtype=torch.int32, device=dev)
         s = torch.cuda.current_stream().cuda_stream
-        for _ in range(2):
-            assert a.gemv_peers_dev(["sync"], d_x.data_ptr(), [[y.data_ptr()]], stream=s, sync=sync)
-        a.peer_barrier_dev(epoch.data_ptr(), flags.data_ptr(), [flags.data_ptr()], stream=s)
+        a.peer_barrier_dev(epoch.data_ptr(), flags0.data_ptr(), [flags0.data_ptr(), flags1.data_ptr()], stream=s)
         torch.cuda.synchronize()
+        assert a.device_status(s) == 1                     # STATUS_WAIT_TIMEOUT
+        assert int(flags0[0].item()) == 1 and int(flags1[0].item()) == 1 and int(flags0[1].item()) == 0
+        assert a.clear_device_status(s) and a.device_status(s) == 0
+        in_dim, out_dim = 512, 64
+        w = synth.q8_0(53, "after", out_dim, in_dim)
+        x = synth.normal(53, "after.x", in_dim)
+        assert a.upload_q8_0("after", w, in_dim, out_dim)
+        got = a.gemv("after", x)
+        assert rel_l2(got, orc.qmatmul(x, w, synth.Q8_0, in_dim, out_dim)[:len(got)]) <= REL_L2_TOL
         assert a.device_status(s) == 0
-        assert int(epoch.item()) == 3 and int(flags[0].item()) == 3 and int(done.item()) == 0
-        assert rel_l2(y.cpu().numpy(), want) <= REL_L2_TOL
     finally:
         a.close()
 
