@@ -307,7 +307,9 @@ STRIX_API int strix_cuda_clear_device_status(strix_cuda *h, void *stream);
  * the call path reads the environment). 1 = set, 0 = unknown name. Any configured decode chain and cached
  * graph is dropped. Names: "q6k_digits" (0 never / 1 in_dim <= 8192 / 2 whenever it fits: Q6_K f32 row as
  * three int8 digit rows), "gemv_warps_per_group", "gemv_blocks_per_stage", "gemv_stages" (0 = planned),
- * "gemv_pdl" (programmatic dependent launch between GEMVs), "gemv_debug" (bit 0: stream the weights without
+ * "gemv_pdl" (programmatic dependent launch between GEMVs), "rows_operand_image" (batched integer-dot GEMV:
+ * the activation operands are prepared once by a kernel of their own and fetched by every CTA; 0 = every CTA
+ * quantises all rows itself), "gemv_debug" (bit 0: stream the weights without
  * arithmetic, bit 1: empty launches, bit 2: stop after the activation prologue), "batch_graph" (gemv_batch
  * replays a cached CUDA graph), "decode_chain" (the projection chain as one persistent launch),
  * "chain_trace" (per-step clocks, see strix_cuda_decode_trace), "chain_debug" (bit 0: the chain kernel skips

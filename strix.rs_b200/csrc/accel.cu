@@ -59,6 +59,18 @@ int ensure_pinned(strix_cuda *h, PinBuf &b, size_t bytes) {
     return 1;
 }
 
+// The operand image of a batched integer-dot GEMV (grown on demand; a caller that captures launches into a
+// graph sizes it beforehand, since nothing may be allocated during a capture).
+int ensure_xop(strix_cuda *h, size_t bytes) {
+    if (h->xop_cap >= bytes) return 1;
+    if (h->xop) cudaFree(h->xop);
+    h->xop = nullptr;
+    h->xop_cap = 0;
+    CU_TRY(h, cudaMalloc(&h->xop, bytes));
+    h->xop_cap = bytes;
+    return 1;
+}
+
 const Resident *find_weight(strix_cuda *h, const char *key) {
     auto it = h->weights.find(key);
     return it == h->weights.end() ? nullptr : &it->second;
@@ -218,6 +230,17 @@ int gemv_launch_rows(strix_cuda *h, int nmat, const Resident *const *ws, const f
         }
         c.a = d_a + (size_t)done * a_stride;
         c.b = d_b ? d_b + (size_t)done * b_stride : nullptr;
+        // Several activation rows in the integer-dot form: their operands are prepared ONCE by a kernel of its own
+        // and fetched by every CTA, instead of being quantised by each of the 148 CTAs (8 rows of 15360 cost a CTA
+        // ~15 us of prologue, on the critical path of a launch whose weights stream in 5 us). One row stays with
+        // the in-kernel prologue: a second launch costs more than it saves there.
+        if (act == STRIX_ACT_Q8DOT && chunk >= 2 && a.L.in_dim <= 16384u && h->tune.xop != 0) {
+            if (ensure_xop(h, xop_image_bytes(a.L.fmt, a.L.in_dim, chunk)) < 0) return -1;
+            CU_TRY(h, launch_xop_prepare(a.L.fmt, a.L.in_dim, chunk, c.a, pre == STRIX_PRE_RMSNORM ? d_b : c.b, a_stride,
+                                         b_stride, eps, pre, h->xop, h->tune.pdl != 0, stream));
+            c.xop = h->xop;
+            c.pre = STRIX_PRE_NONE;
+        }
         for (int m = 0; m < nmat; m++) {
             c.mat[m].y = d_ys[m] + (size_t)done * c.mat[m].ystride;
             c.mat[m].res = (d_res && d_res[m]) ? d_res[m] + (size_t)done * c.mat[m].ystride : nullptr;
@@ -305,6 +328,7 @@ void strix_cuda_destroy(strix_cuda *h) {
     if (h->am_pin) cudaFreeHost(h->am_pin);
     if (h->gm_xs) cudaFree(h->gm_xs);
     for (auto &kv : h->f32s) cudaFree(kv.second.p);
+    if (h->xop) cudaFree(h->xop);
     if (h->x.p) cudaFree(h->x.p);
     if (h->y.p) cudaFree(h->y.p);
     if (h->pin_in.p) cudaFreeHost(h->pin_in.p);
@@ -325,6 +349,7 @@ int strix_cuda_set_option(strix_cuda *h, const char *name, long long value) {
     else if (n == "gemv_stages") h->tune.force_sk = v;
     else if (n == "gemv_pdl") h->tune.pdl = v;
     else if (n == "gemv_debug") h->tune.debug = v;
+    else if (n == "rows_operand_image") h->tune.xop = v;
     else if (n == "batch_graph") h->use_batch_graph = value != 0;
     else if (n == "decode_chain") h->decode_chain = value < 0 ? -1 : value != 0;
     else if (n == "chain_trace") h->chain_trace = value != 0;

@@ -74,6 +74,8 @@ struct strix_cuda {
     std::unordered_map<std::string, strix::DevBuf> f32s;
     // staging for the host-pointer entry points (grown on demand, never shrunk; like the
     // reference's persistent gemv_x / gemv_y, decode.rs:3827-3832)
+    uint8_t *xop = nullptr;  // operand image of a batched integer-dot GEMV (launch_xop_prepare), grown on demand
+    size_t xop_cap = 0;
     strix::DevBuf x, y;
     strix::PinBuf pin_in, pin_out;
     // scratch of the prefill GEMM (grown on demand): f32 activations, their int8 codes, block scales,
@@ -95,6 +97,7 @@ namespace strix {
 size_t shard_begin(size_t rows, int world, int r);
 int ensure_f32(strix_cuda *h, DevBuf &b, size_t n);
 int ensure_pinned(strix_cuda *h, PinBuf &b, size_t bytes);
+int ensure_xop(strix_cuda *h, size_t bytes);
 const Resident *find_weight(strix_cuda *h, const char *key);
 // argmax per row of d_x[rows][stride] (n entries each, rows <= 16) into h->am_idx (and h->am_val) on `stream`
 int argmax_rows_enqueue(strix_cuda *h, const float *d_x, size_t n, size_t stride, size_t rows, cudaStream_t stream);

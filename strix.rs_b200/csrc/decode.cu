@@ -481,6 +481,17 @@ static constexpr size_t ROWS_MAX = 8;
 
 static int rows_alloc(strix_cuda *h, strix_decode_state *d) {
     if (d->r_h) return 0;
+    {
+        // the batched GEMV's operand image, sized for the largest step before anything is captured into a graph
+        size_t need = 0;
+        auto see = [&](const Resident *w) {
+            need = std::max(need, xop_image_bytes(w->fmt, w->L.in_dim, w->fmt == FMT_Q6_K ? 4u : (uint32_t)ROWS_MAX));
+        };
+        for (auto &L : d->layers)
+            for (const Resident *w : {L.q, L.o, L.gate, L.down}) see(w);
+        see(d->head);
+        if (ensure_xop(h, need) < 0) return -1;
+    }
     cudaError_t e = cudaSuccess;
     auto alloc = [&](float **p, size_t n) {
         if (e == cudaSuccess) e = cudaMalloc(p, ROWS_MAX * std::max<size_t>(n, 4) * sizeof(float));

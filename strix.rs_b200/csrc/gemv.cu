@@ -319,11 +319,168 @@ __global__ void __launch_bounds__((GEMV_WARPS + 1) * 32, 1) gemv_kernel(const __
     // Everything above (and the producer's copies) touches only this launch's weights. The activation
     // and the outputs belong to the stream's order: wait for the preceding grid here.
     asm volatile("griddepcontrol.wait;" ::: "memory");
-    consumer_prologue<FMT, ACT, MULTI, PRE>(act_in(A), C);
+    if (A.xop) {
+        const XLayout XL = x_layout(FMT, ACT, A.L.in_dim, A.nbatch, A.x_off);
+        image_prologue(A.xop, XL.xb, (XL.end - XL.xb + 15u) & ~15u, A.nbatch, C);
+    } else {
+        consumer_prologue<FMT, ACT, MULTI, PRE>(act_in(A), C);
+    }
     if (A.debug & 4u) return;  // measurement only: stop after the activation prologue
     consumer_groups<FMT, ACT, MULTI>(A, C);
 }
 
+
+// ---- the activation operands of an integer-dot launch, prepared once for all CTAs ----
+// One CTA per activation row (rows past nbatch only clear their record slots, which must read zero).
+// Pre-ops as the reference's fused quantisers: RMSNorm in its operand order ((x * 1/rms) * w, kernels.rs:101-147),
+// SwiGLU / GeGLU (kernels.rs:151-226), then xquant8 (kernels.rs:864-876). The image is the shared-memory
+// operand region of gemv_kernel in x_layout order, so a CTA fetches it with plain bulk copies.
+constexpr uint32_t XOP_THREADS = 1024, XOP_NI = 4;  // rows up to 4 * 4 * 1024 = 16384 elements
+template <int PRE>
+__global__ void __launch_bounds__(XOP_THREADS, 1)
+xop_prepare_kernel(const float *__restrict__ a, const float *__restrict__ b, uint32_t a_stride, uint32_t b_stride, float eps,
+                   uint32_t K, uint32_t B, int q6, int bias, uint8_t *__restrict__ image) {
+    __shared__ float scr[32];
+    asm volatile("griddepcontrol.launch_dependents;");
+    const uint32_t tid = threadIdx.x, lane = tid & 31u, warp = tid >> 5, l8 = lane & 7u, bi = blockIdx.x;
+    const uint32_t K4 = K / 4u, nb32 = K / 32u;
+    const XLayout XL = x_layout(q6 ? FMT_Q6_K : FMT_Q4_0, STRIX_ACT_Q8DOT, K, B, 0u);
+    uint32_t *xbw = reinterpret_cast<uint32_t *>(image + XL.xb);
+    float *rec = reinterpret_cast<float *>(image + XL.rec);
+    // the image (and the activations) belong to the stream's order: the launch before this one may still read them
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    if (bi >= B) {
+        // a record slot without an activation row reads zero (what its MMA column produces is never stored)
+        if (q6) {
+            for (uint32_t blk = tid; blk < nb32; blk += XOP_THREADS)
+                reinterpret_cast<float4 *>(rec)[blk * 4u + bi] = make_float4(0.f, 0.f, 0.f, 0.f);
+        } else {
+            for (uint32_t blk = tid; blk < nb32; blk += XOP_THREADS) {
+                rec[blk * 16u + (bi >> 1) * 4u + (bi & 1u)] = 0.f;
+                rec[blk * 16u + (bi >> 1) * 4u + 2u + (bi & 1u)] = 0.f;
+            }
+        }
+        return;
+    }
+    const float *Aa = a + (size_t)bi * a_stride;
+    const float *Ab = b ? b + (size_t)bi * b_stride : nullptr;
+    float4 v[XOP_NI];
+    float ss = 0.f;
+#pragma unroll
+    for (uint32_t i = 0; i < XOP_NI; i++) {
+        const uint32_t e4 = tid + i * XOP_THREADS;
+        v[i] = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (e4 < K4) {
+            float4 a4 = __ldcg(reinterpret_cast<const float4 *>(Aa) + e4);
+            if (PRE == STRIX_PRE_RMSNORM) {
+                ss = fmaf(a4.x, a4.x, ss); ss = fmaf(a4.y, a4.y, ss); ss = fmaf(a4.z, a4.z, ss); ss = fmaf(a4.w, a4.w, ss);
+            } else if (PRE != STRIX_PRE_NONE) {
+                const float4 b4 = __ldcg(reinterpret_cast<const float4 *>(Ab) + e4);
+                if (PRE == STRIX_PRE_SWIGLU) {
+                    a4.x = silu_f(a4.x) * b4.x; a4.y = silu_f(a4.y) * b4.y; a4.z = silu_f(a4.z) * b4.z; a4.w = silu_f(a4.w) * b4.w;
+                } else {
+                    a4.x = gelu_tanh_f(a4.x) * b4.x; a4.y = gelu_tanh_f(a4.y) * b4.y;
+                    a4.z = gelu_tanh_f(a4.z) * b4.z; a4.w = gelu_tanh_f(a4.w) * b4.w;
+                }
+            }
+            v[i] = a4;
+        }
+    }
+    if (PRE == STRIX_PRE_RMSNORM) {
+        ss = warp_sum(ss);
+        if (lane == 0) scr[warp] = ss;
+        __syncthreads();
+        float tot = 0.f;
+#pragma unroll
+        for (uint32_t w2 = 0; w2 < XOP_THREADS / 32u; w2++) tot += scr[w2];
+        const float sc = 1.0f / sqrtf(tot / (float)K + eps);
+#pragma unroll
+        for (uint32_t i = 0; i < XOP_NI; i++) {
+            const uint32_t e4 = tid + i * XOP_THREADS;
+            if (e4 < K4) {
+                const float4 w4 = __ldg(reinterpret_cast<const float4 *>(b) + e4);  // the norm weight is shared by the rows
+                v[i].x = (v[i].x * sc) * w4.x; v[i].y = (v[i].y * sc) * w4.y;
+                v[i].z = (v[i].z * sc) * w4.z; v[i].w = (v[i].w * sc) * w4.w;
+            }
+        }
+    }
+#pragma unroll
+    for (uint32_t i = 0; i < XOP_NI; i++) {
+        const uint32_t e4 = tid + i * XOP_THREADS;
+        if ((tid - lane) + i * XOP_THREADS >= K4) break;  // the whole warp is past the row's end (the body shuffles)
+        const bool live = e4 < K4;
+        const float4 t4 = v[i];
+        const uint32_t blk = e4 >> 3, t = l8 & 3u, hf = l8 >> 2;
+        float bm = fmaxf(fmaxf(fabsf(t4.x), fabsf(t4.y)), fmaxf(fabsf(t4.z), fabsf(t4.w)));
+        bm = fmaxf(bm, __shfl_xor_sync(0xffffffffu, bm, 1));
+        bm = fmaxf(bm, __shfl_xor_sync(0xffffffffu, bm, 2));
+        bm = fmaxf(bm, __shfl_xor_sync(0xffffffffu, bm, 4));
+        const float d = bm / 127.0f;
+        const float inv = d > 0.f ? 1.0f / d : 0.f;
+        const uint32_t wq = pack4(quant1(t4.x, inv), quant1(t4.y, inv), quant1(t4.z, inv), quant1(t4.w, inv));
+        int cs = sum4(wq);
+        cs += __shfl_xor_sync(0xffffffffu, cs, 1);
+        cs += __shfl_xor_sync(0xffffffffu, cs, 2);
+        const int half_sum = cs;
+        cs += __shfl_xor_sync(0xffffffffu, cs, 4);
+        if (live) {
+            if (q6) {
+                xbw[(blk * 8u * B + (2u * bi + hf) * 4u + t) * 2u + hf] = wq;
+                xbw[(blk * 8u * B + (2u * bi + hf) * 4u + t) * 2u + (hf ^ 1u)] = 0u;
+                if (l8 == 0) rec[blk * 16u + bi * 4u] = d;
+                if (t == 0) rec[blk * 16u + bi * 4u + 1u + hf] = __int_as_float(-bias * half_sum);
+                if (l8 == 0) rec[blk * 16u + bi * 4u + 3u] = 0.f;
+            } else {
+                xbw[(blk * 4u * B + bi * 4u + t) * 2u + hf] = wq;
+                if (l8 == 0) {
+                    const float kf = -(float)bias * d * (float)cs;
+                    if (B > 1) {
+                        rec[blk * 16u + (bi >> 1) * 4u + (bi & 1u)] = d;
+                        rec[blk * 16u + (bi >> 1) * 4u + 2u + (bi & 1u)] = kf;
+                    } else {
+                        rec[blk * 2u] = d;
+                        rec[blk * 2u + 1u] = kf;
+                    }
+                }
+            }
+        }
+    }
+}
+
+size_t xop_image_bytes(int fmt, uint32_t in_dim, uint32_t nbatch) {
+    const XLayout XL = x_layout(fmt, STRIX_ACT_Q8DOT, in_dim, nbatch, 0u);
+    return ((size_t)(XL.end - XL.xb) + 15u) & ~(size_t)15u;
+}
+
+cudaError_t launch_xop_prepare(int fmt, uint32_t in_dim, uint32_t nbatch, const float *d_a, const float *d_b,
+                               uint32_t a_stride, uint32_t b_stride, float eps, int pre, uint8_t *d_image, bool pdl,
+                               cudaStream_t stream) {
+    if (in_dim > XOP_NI * 4u * XOP_THREADS || in_dim % 32u != 0) return cudaErrorInvalidValue;
+    const bool q6 = fmt == FMT_Q6_K;
+    const int bias = fmt == FMT_Q8_0 ? 128 : fmt == FMT_Q4_0 ? 8 : fmt == FMT_Q4_1 ? -1 : 32;
+    cudaLaunchConfig_t cfg = {};
+    // one CTA per record slot of the layout: rows without an activation clear theirs
+    cfg.gridDim = dim3(nbatch > 1 || q6 ? (q6 ? 4u : 8u) : 1u);
+    cfg.blockDim = dim3(XOP_THREADS);
+    cfg.stream = stream;
+    cudaLaunchAttribute at[1];
+    at[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    at[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = at;
+    cfg.numAttrs = pdl ? 1u : 0u;
+    const int q6i = q6 ? 1 : 0;
+    switch (pre) {
+        case STRIX_PRE_NONE:
+            return cudaLaunchKernelEx(&cfg, xop_prepare_kernel<STRIX_PRE_NONE>, d_a, d_b, a_stride, b_stride, eps, in_dim, nbatch, q6i, bias, d_image);
+        case STRIX_PRE_RMSNORM:
+            return cudaLaunchKernelEx(&cfg, xop_prepare_kernel<STRIX_PRE_RMSNORM>, d_a, d_b, a_stride, b_stride, eps, in_dim, nbatch, q6i, bias, d_image);
+        case STRIX_PRE_SWIGLU:
+            return cudaLaunchKernelEx(&cfg, xop_prepare_kernel<STRIX_PRE_SWIGLU>, d_a, d_b, a_stride, b_stride, eps, in_dim, nbatch, q6i, bias, d_image);
+        case STRIX_PRE_GEGLU:
+            return cudaLaunchKernelEx(&cfg, xop_prepare_kernel<STRIX_PRE_GEGLU>, d_a, d_b, a_stride, b_stride, eps, in_dim, nbatch, q6i, bias, d_image);
+        default: return cudaErrorInvalidValue;
+    }
+}
 
 // ------------------------------------------------------------------ host side
 static inline uint32_t align128u(uint32_t v) { return (v + 127u) & ~127u; }

@@ -445,6 +445,26 @@ __device__ __forceinline__ ActIn act_in(const GemvArgs &A) {
     return I;
 }
 
+// ---- consumers: operands prepared elsewhere ----
+// The operand region arrives as an image in global memory (launch_xop_prepare wrote it once for all CTAs):
+// thread 0 fetches it with bulk copies of at most 32 KB on an mbarrier of its own, everybody waits (bounded).
+constexpr uint32_t SMEM_XBAR_OFF = SMEM_CTL_OFF + 32u;
+__device__ __forceinline__ void image_prologue(const uint8_t *image, uint32_t x_off, uint32_t bytes, uint32_t nrows, const Cta &C) {
+    uint64_t *bar = reinterpret_cast<uint64_t *>(C.smem + SMEM_XBAR_OFF);
+    const uint32_t ct = C.n_cons * 32u;
+    if (C.tid == 0) {
+        mbar_init(bar, 1);
+        mbar_fence_init();
+        mbar_arrive_expect_tx(bar, bytes);
+        for (uint32_t o = 0; o < bytes; o += 32768u)
+            bulk_g2s(C.smem + x_off + o, image + o, min(32768u, bytes - o), bar);
+    }
+    if (C.tid < 8u) reinterpret_cast<float *>(C.smem + SMEM_OSCALE_OFF)[C.tid] = 1.0f;  // (the image is fully scaled)
+    asm volatile("bar.sync 15, %0;" ::"r"(ct) : "memory");  // the barrier is initialised for everyone
+    if (!mbar_wait_bounded(bar, 0u, C.status)) cta_ctl(C)[0] = 1;
+    (void)nrows;
+}
+
 // ---- consumers: activation prologue ----
 // The activation (after the optional RMSNorm / SwiGLU / GeGLU) is turned ONCE per CTA,
 // cooperatively, into the B operands of the tensor-core instructions, in shared memory (see

@@ -61,6 +61,10 @@ struct GemvArgs {
     uint32_t digits;         // f32 activations carried as three int8 digits per value (Q6_K, one activation row)
     uint32_t pdl;            // launch with programmatic stream serialization
     uint32_t rot;            // chain kernel: CTA that takes the step's first row group
+    // Integer-dot form with the activation operands prepared ONCE by a kernel of their own (launch_xop_prepare)
+    // instead of by every CTA: the image of the shared-memory operand region (x_layout order) in global
+    // memory, which each CTA fetches with bulk copies. Null = the CTA builds its operands itself.
+    const uint8_t *xop;
     uint32_t grid;
     uint32_t smem_bytes;
     uint32_t debug;  // measurement only: bit 0 = stream the tiles but skip the arithmetic
@@ -72,6 +76,7 @@ struct GemvTune {
     uint32_t digits_rule = 1;  // Q6_K with one f32 row as three int8 digit rows: 0 never, 1 for in_dim <= 8192, 2 whenever it fits
     uint32_t force_wc = 0, force_ct = 0, force_sk = 0;  // warps per row group / blocks per stage / stages per slot (0 = planned)
     uint32_t pdl = 1;          // programmatic stream serialization between GEMV launches
+    uint32_t xop = 1;          // batched integer-dot GEMV: operands prepared once by a kernel of their own (0 = by every CTA)
     uint32_t debug = 0;        // measurement only: bit 0 stream the tiles without arithmetic, bit 1 empty launch,
                                // bit 2 stop after the activation prologue
 };
@@ -82,6 +87,13 @@ struct GemvTune {
 bool gemv_plan(GemvArgs &a, int num_sms, size_t smem_optin, const GemvTune &tune);
 cudaError_t gemv_prepare_device(size_t smem_optin);  // opt in to large dynamic shared memory, once per device
 cudaError_t launch_gemv(const GemvArgs &a, cudaStream_t stream);
+// Bytes of the operand image of nbatch activation rows (what GemvArgs::xop points at), and the kernel that
+// writes it: the pre-op (RMSNorm in the reference's operand order, SwiGLU, GeGLU) and the per-32 int8
+// quantiser, one CTA per activation row. a / b / strides / eps / pre as in GemvArgs.
+size_t xop_image_bytes(int fmt, uint32_t in_dim, uint32_t nbatch);
+cudaError_t launch_xop_prepare(int fmt, uint32_t in_dim, uint32_t nbatch, const float *d_a, const float *d_b,
+                               uint32_t a_stride, uint32_t b_stride, float eps, int pre, uint8_t *d_image, bool pdl,
+                               cudaStream_t stream);
 // ---- step lists in one persistent launch (chain.cu) ------------------------------------------
 // A list of GEMV steps run by ONE cooperative kernel (one CTA per SM): the producer warp of every CTA
 // streams the weights of step after step through one ring of stages without ever waiting for another
