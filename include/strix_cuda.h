@@ -341,7 +341,9 @@ STRIX_API int strix_cuda_debug_gemm_isums(strix_cuda *h, const char *key, const 
                                 int32_t *out, size_t out_cap);
 /* Measurement: quantise d_xs[m][in_dim] once, then launch the GEMM kernel `reps` times on `stream` in `mode`:
  * 0 = the product into d_y[m][rows]; 2 = without the accumulator drain (TMA + tensor pipeline alone);
- * 3 = without drain and loads (the issue rate of tcgen05.mma kind::i8: the measured int8 peak). No sync. */
+ * 3 = without drain and loads (the issue loop with its buffer hand-overs only); 4 = the MMAs alone, issued
+ * back to back with one commit at the end (the issue rate of tcgen05.mma kind::i8: the measured int8 peak).
+ * No sync. */
 STRIX_API int strix_cuda_debug_gemm_mode_dev(strix_cuda *h, const char *key, const float *d_xs, size_t m, float *d_y,
                                    int mode, int reps, void *stream);
 

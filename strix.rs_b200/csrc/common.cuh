@@ -58,6 +58,29 @@ __device__ __forceinline__ bool mbar_wait_bounded(uint64_t *bar, uint32_t parity
     return false;
 }
 
+// A wait that polls without ever suspending (mbarrier.test_wait): for the few threads of a kernel whose
+// reaction time IS its throughput (the hand-over of a TMEM accumulator between the MMA issuer and the
+// warps that drain it). try_wait may park the thread for a system-dependent time when the phase is
+// not complete yet, and being woken from that takes longer than the work between two hand-overs.
+__device__ __forceinline__ bool mbar_test_wait(uint64_t *bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.b32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(smem_u32(bar)), "r"(parity)
+        : "memory");
+    return ok != 0;
+}
+__device__ __forceinline__ bool mbar_spin_bounded(uint64_t *bar, uint32_t parity, uint32_t *status) {
+    for (uint32_t it = 0; it < (1u << 24); ++it) {
+        if (mbar_test_wait(bar, parity)) return true;
+    }
+    if (status) atomicOr(status, STATUS_WAIT_TIMEOUT);
+    return false;
+}
+
 // The same wait for code that shares its SM's issue slots with working warps: each try lets the hardware
 // suspend the thread for up to `hint_ns` before it answers, so a waiting warp issues a handful of
 // instructions per microsecond instead of spinning. Bounded like mbar_wait_bounded.

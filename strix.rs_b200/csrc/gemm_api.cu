@@ -168,8 +168,8 @@ int strix_cuda_debug_gemm_mode_dev(strix_cuda *h, const char *key, const float *
                                    int reps, void *stream) {
     if (!h || !key || !d_xs || !d_y) return -1;
     h->err.clear();
-    if (mode != 0 && mode != 2 && mode != 3) {
-        h->err = "debug_gemm_mode_dev: mode 0, 2 or 3";
+    if (mode != 0 && (mode < 2 || mode > 5)) {
+        h->err = "debug_gemm_mode_dev: mode 0, 2, 3, 4 or 5";
         return -1;
     }
     Resident *r = find_weight_mut(h, key);

@@ -20,12 +20,16 @@
 //   * sixteen epilogue warps (TMEM lane group = warp % 4, column quarter = index / 4)
 //     read a finished buffer with tcgen05.ld, re-arm it, hand it back, and run
 //     acc[n] += d_w[n] * (d_x[m] * isum) as packed f32x2 ops, 32 columns per thread;
-//   * int32 -> f32 costs no conversion instruction: a buffer is pre-loaded (tcgen05.st) with
-//     the bit pattern of 1.5 * 2^23 and the MMA ACCUMULATES into it, so what comes back is
-//     the float r = 12582912 + isum + 128 * sum(x codes) (weight codes are resident as q + 128, the
-//     MMA runs u8 x s8). The quantiser leaves c = -d_x * (12582912 + 128 * sum) per (token, K-block),
-//     so d_x * isum = fma(d_x, r, c): TWO packed FMAs per pair of elements (this one and the
-//     accumulation with d_w) instead of subtract, multiply, FMA. c is rounded once, which moves
+//   * int32 -> f32 costs no conversion instruction: the integer r = isum + 128 * sum(x codes) that
+//     comes back from TMEM (weight codes are resident as q + 128, the MMA runs u8 x s8) is ADDED to
+//     the bit pattern of 1.5 * 2^23 (an integer add, off the FMA pipe), which is the float
+//     12582912 + r. The quantiser leaves c = -d_x * (12582912 + 128 * sum) per (token, K-block),
+//     so d_x * isum = fma(d_x, 12582912 + r, c): TWO packed FMAs per pair of elements (this one and
+//     the accumulation with d_w). The MMA overwrites its buffer (no accumulator input), so a
+//     drained buffer needs nothing written into it and goes back to the MMA warp as soon as its
+//     contents are in registers: the hand-over, not the arithmetic, is what bounds this kernel
+//     (four buffers of 128 columns are all of TMEM, and an MMA takes ~500 clocks from issue to
+//     completion). c is rounded once, which moves
 //     each block term by at most 0.75 d_x, i.e. ~1e-5 of a typical block sum, against a contract of
 //     1e-3; the bit-exact tier (MODE 1 below) recovers isum with the exact subtract;
 //   * the kernel is a template over MODE: 0 = the product path; 1 = the SAME producer / MMA / TMEM
@@ -33,7 +37,8 @@
 //     tier of the contract, checked on the tensor-core path itself); 2 = the epilogue only hands
 //     the buffers back (no TMEM read, no arithmetic): what the TMA + tensor pipeline sustains
 //     without the drain; 3 = as 2 and no loads either (operands stay whatever shared memory
-//     holds): the issue rate of tcgen05.mma kind::i8 alone, the measured int8 peak;
+//     holds): the MMA issue loop with its buffer hand-overs but no data movement; 4 = the MMAs alone,
+//     issued back to back by one thread with a single commit at the end: the measured int8 peak;
 //   * split-K (grid.z) writes f32 partials that a second kernel adds in a fixed
 //     order: reproducible, unlike the reference's atomicAdd;
 //   * every wait is bounded; after a timeout nothing waits again, the status word
@@ -71,13 +76,14 @@ __device__ __forceinline__ void tc_commit(uint64_t *bar) {
     asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar))
                  : "memory");
 }
-// D[tmem] += A[smem desc] * B[smem desc], int8 inputs, int32 accumulation.
+// D[tmem] = A[smem desc] * B[smem desc], int8 inputs, int32 result (the accumulator input is disabled: every
+// K-block gets a fresh sum, and nothing has to be written into the buffer before it is used again).
 __device__ __forceinline__ void tc_mma_i8(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc) {
     asm volatile(
         "{\n\t.reg .pred p;\n\t"
         "setp.ne.b32 p, %4, 0;\n\t"
         "tcgen05.mma.cta_group::1.kind::i8 [%0], %1, %2, %3, {%5, %5, %5, %5}, p;\n\t}"
-        ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(1u), "r"(0u)
+        ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(0u), "r"(0u)
         : "memory");
 }
 __device__ __forceinline__ void tc_ld32(uint32_t taddr, uint32_t (&r)[32]) {
@@ -93,21 +99,6 @@ __device__ __forceinline__ void tc_ld32(uint32_t taddr, uint32_t (&r)[32]) {
         : "memory");
 }
 __device__ __forceinline__ void tc_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
-// 8 columns of this thread's TMEM lane <- c[0..7] (kept in registers for the whole kernel)
-__device__ __forceinline__ void tc_st8(uint32_t taddr, const uint32_t (&c)[8]) {
-    asm volatile("tcgen05.st.sync.aligned.32x32b.x8.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};" ::"r"(taddr),
-                 "r"(c[0]), "r"(c[1]), "r"(c[2]), "r"(c[3]), "r"(c[4]), "r"(c[5]), "r"(c[6]), "r"(c[7])
-                 : "memory");
-}
-// 32 columns of this thread's TMEM lane <- the magic constant
-__device__ __forceinline__ void tc_rearm32(uint32_t taddr, const uint32_t (&c)[8]) {
-    tc_st8(taddr, c);
-    tc_st8(taddr + 8u, c);
-    tc_st8(taddr + 16u, c);
-    tc_st8(taddr + 24u, c);
-}
-__device__ __forceinline__ void tc_wait_st() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
-
 // Shared-memory matrix descriptor of a K-major tile stored as rows of 128 bytes with the
 // 128-byte swizzle (what TMA writes with CU_TENSOR_MAP_SWIZZLE_128B): start address >> 4,
 // leading byte offset 1 (ignored for swizzled K-major), stride byte offset = 8 rows x 128 B = 1024
@@ -182,7 +173,26 @@ gemm_w8a8_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
 
-    if (warp == 0) {
+    if (MODE == 4) {
+        // measurement: the bare issue rate of tcgen05.mma kind::i8 - one thread issues this CTA's MMAs back to back
+        // on whatever shared memory holds, into the four buffers in turn, with one commit at the end
+        if (warp == 1 && lane == 0) {
+            const uint32_t sa = smem_u32(stages);
+            const uint64_t adesc = smem_desc_sw128(sa), bdesc = smem_desc_sw128(sa + GM_A_BYTES);
+            if (A.dump) {
+                // (A.dump non-null: every MMA is committed and waited for before the next one: its issue-to-completion latency)
+                for (uint32_t g = 0; g < kb1 - kb0; g++) {
+                    tc_mma_i8(tmem_base + (g % GM_TBUF) * GM_BN, adesc + 2u * (g & 3u), bdesc + 2u * (g & 3u), GM_IDESC);
+                    tc_commit(&tfull[0]);
+                    mbar_wait_bounded(&tfull[0], g & 1u, A.status);
+                }
+            } else {
+                for (uint32_t g = 0; g < kb1 - kb0; g++) tc_mma_i8(tmem_base + (g % GM_TBUF) * GM_BN, adesc + 2u * (g & 3u), bdesc + 2u * (g & 3u), GM_IDESC);
+                tc_commit(&tfull[0]);
+                mbar_wait_bounded(&tfull[0], 0u, A.status);
+            }
+        }
+    } else if (warp == 0) {
         // ---------------- TMA producer ----------------
         if (lane == 0) {
             for (uint32_t it = 0; it < n_stage_iters; it++) {
@@ -207,9 +217,11 @@ gemm_w8a8_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
         // ---------------- MMA issuer ----------------
         if (lane == 0) {
             uint32_t g = 0;  // K-block counter of this CTA
+            uint32_t aborted = 0;  // (once a wait has run out nobody waits again; other warps learn it through *ctl)
             for (uint32_t it = 0; it < n_stage_iters; it++) {
+                if ((it & 7u) == 7u) aborted |= *ctl;
                 const uint32_t s = it % GM_STAGES;
-                if (!*ctl && !mbar_wait_bounded(&full[s], (it / GM_STAGES) & 1u, A.status)) *ctl = 1;
+                if (!aborted && !mbar_wait_bounded(&full[s], (it / GM_STAGES) & 1u, A.status)) *ctl = aborted = 1;
                 tc_fence_after();
                 const uint32_t sa = smem_u32(stages + s * GM_STAGE_BYTES);
                 const uint64_t adesc = smem_desc_sw128(sa), bdesc = smem_desc_sw128(sa + GM_A_BYTES);
@@ -217,7 +229,7 @@ gemm_w8a8_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
                 for (uint32_t j = 0; j < nkb; j++, g++) {
                     const uint32_t buf = g % GM_TBUF, use = g / GM_TBUF;
                     // the epilogue warps pre-load every buffer (first use included) before it may be accumulated into
-                    if (!*ctl && !mbar_wait_bounded(&tempty[buf], use & 1u, A.status)) *ctl = 1;
+                    if (!aborted && !mbar_wait_bounded(&tempty[buf], use & 1u, A.status)) *ctl = aborted = 1;
                     tc_fence_after();
                     tc_mma_i8(tmem_base + buf * GM_BN, adesc + 2u * j, bdesc + 2u * j, GM_IDESC);
                     tc_commit(&tfull[buf]);  // arrives when this MMA (and all before it) has completed
@@ -232,24 +244,18 @@ gemm_w8a8_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
         const bool m_ok = m < A.M;
         const uint32_t taddr0 = tmem_base + ((lg * 32u) << 16) + cq * 32u;
         const uint32_t trow = lg * 32u + lane;  // this thread's row in the tile
-        uint32_t magic[8];
-#pragma unroll
-        for (int i = 0; i < 8; i++) magic[i] = GM_MAGIC;
-        // arm the four buffers
-#pragma unroll
-        for (uint32_t j = 0; j < GM_TBUF; j++) tc_rearm32(taddr0 + j * GM_BN, magic);
-        tc_wait_st();
-        tc_fence_before();
-        __syncwarp();
+        // the four buffers start out free
         if (lane == 0)
             for (uint32_t j = 0; j < GM_TBUF; j++) mbar_arrive(&tempty[j]);
         float2 acc[16];
 #pragma unroll
         for (int i = 0; i < 16; i++) acc[i] = make_float2(0.f, 0.f);
+        uint32_t aborted = 0;
         for (uint32_t it = 0; it < n_stage_iters; it++) {
             const uint32_t s = it % GM_STAGES;
             const uint32_t kb = kb0 + it * GM_KB_STAGE;
-            if (!*ctl && !mbar_wait_bounded(&full[s], (it / GM_STAGES) & 1u, A.status)) *ctl = 1;
+            aborted |= *ctl;
+            if (!aborted && !mbar_wait_bounded(&full[s], (it / GM_STAGES) & 1u, A.status)) *ctl = aborted = 1;
             const uint8_t *stg = stages + s * GM_STAGE_BYTES;
             const float *sw = reinterpret_cast<const float *>(stg + GM_OFF_S) + cq * 32u;
             // [K-block][token]: consecutive lanes read consecutive words
@@ -260,7 +266,7 @@ gemm_w8a8_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
             for (uint32_t j = 0; j < nkb; j++) {
                 if (MODE >= 2) {
                     // measurement: the buffer goes straight back (no TMEM read, no arithmetic)
-                    if (!*ctl && !mbar_wait_bounded(&tfull[j], it & 1u, A.status)) *ctl = 1;
+                    if (!aborted && !mbar_wait_bounded(&tfull[j], it & 1u, A.status)) *ctl = aborted = 1;
                     tc_fence_after();
                     tc_fence_before();
                     __syncwarp();
@@ -270,40 +276,40 @@ gemm_w8a8_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
                 // this token's scale and un-bias term for the K-block (rows past M were zero-filled by TMA)
                 const float dxj = sxd[j * GM_BM];
                 const float cj = sxc[j * GM_BM];
-                if (!*ctl && !mbar_wait_bounded(&tfull[j], it & 1u, A.status)) *ctl = 1;
+                if (!aborted && !mbar_wait_bounded(&tfull[j], it & 1u, A.status)) *ctl = aborted = 1;
                 tc_fence_after();
                 uint32_t r[32];
                 tc_ld32(taddr0 + j * GM_BN, r);
                 tc_wait_ld();
-                tc_rearm32(taddr0 + j * GM_BN, magic);  // completes while the arithmetic below runs
+                // the sums are in registers: the buffer goes back to the MMA warp before the arithmetic, not after it
+                tc_fence_before();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(&tempty[j]);
                 if (MODE == 1) {
-                    // bit-exact tier: r = 12582912 + isum + 128 * sum(x codes), all integers below 2^24, so the
-                    // subtraction is exact; the K-block's code sum arrives where the product path has c
-                    const float unm = -(12582912.0f + 128.0f * (float)__float_as_int(cj));
+                    // bit-exact tier: r = isum + 128 * sum(x codes) as an integer (weight codes are resident as q + 128);
+                    // the K-block's code sum arrives where the product path has c
+                    const int32_t off = 128 * __float_as_int(cj);
                     if (m_ok) {
 #pragma unroll
                         for (int q = 0; q < 32; q++) {
                             const uint32_t n = n0 + cq * 32u + (uint32_t)q;
-                            if (n < A.N) A.dump[((uint64_t)m * A.N + n) * A.nb + kb + j] = (int32_t)(__uint_as_float(r[q]) + unm);
+                            if (n < A.N) A.dump[((uint64_t)m * A.N + n) * A.nb + kb + j] = (int32_t)r[q] - off;
                         }
                     }
                 } else {
-                    // acc[n] += d_w[n] * (d_x * isum), d_x * isum = fma(d_x, r, c)
+                    // int -> float without the conversion unit: adding the integer to the bit pattern of 1.5 * 2^23 gives
+                    // the float 12582912 + r (|r| < 2^22); acc[n] += d_w[n] * (d_x * isum), d_x * isum = fma(d_x, 12582912 + r, c)
                     const float2 dx2 = make_float2(dxj, dxj), c2 = make_float2(cj, cj);
                     const float4 *swj = reinterpret_cast<const float4 *>(sw + j * GM_BN);
 #pragma unroll
                     for (int q = 0; q < 8; q++) {
                         const float4 w4 = swj[q];
-                        const float2 g0 = __ffma2_rn(dx2, make_float2(__uint_as_float(r[4 * q]), __uint_as_float(r[4 * q + 1])), c2);
-                        const float2 g1 = __ffma2_rn(dx2, make_float2(__uint_as_float(r[4 * q + 2]), __uint_as_float(r[4 * q + 3])), c2);
+                        const float2 g0 = __ffma2_rn(dx2, make_float2(__uint_as_float(r[4 * q] + GM_MAGIC), __uint_as_float(r[4 * q + 1] + GM_MAGIC)), c2);
+                        const float2 g1 = __ffma2_rn(dx2, make_float2(__uint_as_float(r[4 * q + 2] + GM_MAGIC), __uint_as_float(r[4 * q + 3] + GM_MAGIC)), c2);
                         acc[2 * q] = __ffma2_rn(make_float2(w4.x, w4.y), g0, acc[2 * q]);
                         acc[2 * q + 1] = __ffma2_rn(make_float2(w4.z, w4.w), g1, acc[2 * q + 1]);
                     }
                 }
-                tc_wait_st();
-                tc_fence_before();
-                __syncwarp();
-                if (lane == 0) mbar_arrive(&tempty[j]);  // the MMA warp may accumulate into the buffer again
             }
             __syncwarp();
             if (lane == 0) mbar_arrive(&empty[s]);  // done with the stage's scale rows
@@ -470,6 +476,7 @@ cudaError_t gemm_prepare_device() {
     if (e == cudaSuccess) e = cudaFuncSetAttribute(gemm_w8a8_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)GM_SMEM);
     if (e == cudaSuccess) e = cudaFuncSetAttribute(gemm_w8a8_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)GM_SMEM);
     if (e == cudaSuccess) e = cudaFuncSetAttribute(gemm_w8a8_kernel<3>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)GM_SMEM);
+    if (e == cudaSuccess) e = cudaFuncSetAttribute(gemm_w8a8_kernel<4>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)GM_SMEM);
     // the small kernels of the GEMM path: asking for their attributes makes the driver load their code now
     // (module loading is lazy), so that a later call that must not allocate finds everything in place
     cudaFuncAttributes fa;
@@ -547,6 +554,11 @@ cudaError_t launch_gemm_w8a8(const uint8_t *d_res, const RowLayout &L, uint32_t 
         case 1: gemm_w8a8_kernel<1><<<grid, GM_THREADS, GM_SMEM, stream>>>(mx, mw, ms, mxd, mxs, a); break;
         case 2: gemm_w8a8_kernel<2><<<grid, GM_THREADS, GM_SMEM, stream>>>(mx, mw, ms, mxd, mxs, a); break;
         case 3: gemm_w8a8_kernel<3><<<grid, GM_THREADS, GM_SMEM, stream>>>(mx, mw, ms, mxd, mxs, a); break;
+        case 4: gemm_w8a8_kernel<4><<<grid, GM_THREADS, GM_SMEM, stream>>>(mx, mw, ms, mxd, mxs, a); break;
+        case 5:  // measurement: mode 4 with every MMA waited for before the next is issued
+            a.dump = reinterpret_cast<int32_t *>(d_y);
+            gemm_w8a8_kernel<4><<<grid, GM_THREADS, GM_SMEM, stream>>>(mx, mw, ms, mxd, mxs, a);
+            break;
         default: return cudaErrorInvalidValue;
     }
     cudaError_t e = cudaGetLastError();
