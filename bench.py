@@ -46,6 +46,18 @@ TYNAME = {Q8_0: "q8_0", Q6_K: "q6_k", Q4_0: "q4_0"}
 GEN_ROWS = 8192   # synthetic rows generated per weight, tiled up to out_dim (keeps host set-up short)
 
 
+WORKLOAD_NAME = "configs[1]: Q8_0+Q6_K dequant-GEMV, batch 1, 2560->9728, 9728->2560, 2560->151936"
+REPLAYS = 64   # the GPU arm replays the step's CUDA graph this many times per timed step and divides (a step is 0.17 ms)
+
+
+def bench_config():
+    """The `config` object of both arms (the driver compares them)."""
+    return {"workload": WORKLOAD_NAME,
+            "l2": "inputs larger than L2 (827.5 MB of weights streamed per step)",
+            "timing": "GPU arm: each timed step replays the step's CUDA graph %d times and divides, so that the timed "
+                      "region lasts ~0.5 s; CPU arm: each step runs once on a bounded row sample" % REPLAYS}
+
+
 def algo_bytes(ty, k, n):
     """Algorithmic bytes of one GEMV: GGUF blocks + f32 x + f32 y."""
     be, bb = BLOCK[ty]
@@ -165,7 +177,10 @@ def decode_chain_extra(pkg, synth, torch, device, stream):
         acc.upload_f32("output_norm.weight", synth.norm_weight(3, "dc.out_norm", hidden))
         h0 = synth.normal(3, "dc.h0", hidden)
         dev = torch.device("cuda", device)
-        for act, name in ((pkg.ACT_Q8DOT, "q8dot"), (pkg.ACT_F32, "f32")):
+        for act, name, chain in ((pkg.ACT_Q8DOT, "q8dot", 0), (pkg.ACT_Q8DOT, "q8dot_chain_kernel", 1), (pkg.ACT_F32, "f32", 0)):
+            # chain = 1: the whole chain as ONE persistent launch (steps exchange {value, epoch} entries); 0: a launch per step
+            acc.set_option("decode_chain", chain)
+            acc.set_option("chain_trace", chain)
             assert acc.configure_decode(hidden, 32, ffn, vocab, n_layers, eps=1e-6, act=act)
             for _ in range(3):
                 logits = acc.decode_step(h0, 0)
@@ -205,7 +220,21 @@ def decode_chain_extra(pkg, synth, torch, device, stream):
                 dev_ms = a.elapsed_time(b) / reps
             out[name] = {"ms_per_token": round(dev_ms, 4), "ms_per_token_e2e": round(e2e_ms, 4),
                          "ms_per_token_e2e_argmax": round(e2e_argmax_ms, 4),
-                         "gbs": round(nbytes / dev_ms / 1e6, 1), "launches_per_token": 4 * n_layers + 1}
+                         "gbs": round(nbytes / dev_ms / 1e6, 1), "launches_per_token": 1 if chain else 4 * n_layers + 1}
+            tr = acc.decode_trace() if chain else None
+            if tr is not None:
+                # CTA 0's clocks per step: start, activations arrived, prologue done, last row group done, rows published
+                tt = tr.astype(np.int64)
+                phases = {}
+                for kk, nm in enumerate(("qkv", "o", "gate_up", "down")):
+                    idx = np.arange(kk + 4, len(tt) - 1, 4)
+                    f = lambda a_, b_: round(float((tt[idx, b_] - tt[idx, a_]).mean()) / 1965.0, 2)  # noqa: E731
+                    phases[nm] = {"wait_us": f(0, 1), "prologue_us": f(1, 2), "tiles_us": f(2, 3), "reduce_store_us": f(3, 4),
+                                  "stalled_on_weights_us": round(float(tt[idx, 5].mean()) / 1965.0, 2)}
+                out[name]["phases_cta0"] = phases
+                out[name]["phases_note"] = "SM clocks of CTA 0 at 1965 MHz, mean over layers 1..35"
+        acc.set_option("decode_chain", -1)
+        acc.set_option("chain_trace", 0)
         out["bytes_per_token"] = nbytes
         # the same model as a real token step: QK-norm, NEOX rope, KV cache (32 heads, 8 KV heads of 128),
         # grouped-query softmax over the cache; the cache is seeded with random rows up to each position
@@ -492,11 +521,13 @@ def decode_chain_sharded_extra(pkg, synth, torch, dist, local, stream, rank, wor
     return out
 
 
-def verify_rows_extra(pkg, synth, torch, device, stream):
+def verify_rows_extra(pkg, synth, torch, device, stream, rank=0, world=1, bs=(1, 2, 4, 8)):
     """configs[4]: speculative-verify batched GEMV at Gemma-3-12B-class shapes (48 layers, hidden 3840,
-    q 4096, kv 2048, ffn 15360, Q4_0), b in {1,2,4,8} activation rows; 6.05 GB of weights per step."""
+    q 4096, kv 2048, ffn 15360, Q4_0), b activation rows; 6.05 GB of weights per step, row-sharded over
+    `world` GPUs (every rank streams its shard of every weight; the rows are independent dot products, so this
+    step has no exchange). Per-step latency is the slowest rank's; GB/s per GPU and aggregate."""
     hidden, qdim, kvdim, ffn, n_layers = 3840, 4096, 2048, 15360, 48
-    acc = pkg.CudaWeightAccel(device)
+    acc = pkg.CudaWeightAccel(device, rank=rank, world=world)
     out = {"per_b": []}
     try:
         shapes = {"q": (qdim, hidden), "k": (kvdim, hidden), "v": (kvdim, hidden), "o": (hidden, qdim),
@@ -505,26 +536,25 @@ def verify_rows_extra(pkg, synth, torch, device, stream):
         nbytes = 0
         for il in range(n_layers):
             for nm, (n, k) in shapes.items():
-                assert acc.upload_q4_0("L%d.%s" % (il, nm), base[nm], k, n)
+                assert acc.upload_q4_0("L%d.%s" % (il, nm), base[nm], k, n)     # the library keeps its row shard
                 nbytes += n * (k // 32) * 18
         dev = torch.device("cuda", device)
-        for b in (1, 2, 4, 8):
+        rows = {nm: acc.weight_info("L0." + nm)["rows"] for nm in shapes}
+        for b in bs:
             xh = torch.randn(b, hidden, device=dev)
             xq_ = torch.randn(b, qdim, device=dev)
             xf = torch.randn(b, ffn, device=dev)
-            yq, yk, yv = (torch.empty(b, n, device=dev) for n in (qdim, kvdim, kvdim))
-            yo, yd = torch.empty(b, hidden, device=dev), torch.empty(b, hidden, device=dev)
-            yg, yu = torch.empty(b, ffn, device=dev), torch.empty(b, ffn, device=dev)
+            y = {nm: torch.empty(b, max(rows[nm], 1), device=dev) for nm in shapes}
 
             def step(s):
                 for il in range(n_layers):
                     p = "L%d." % il
                     acc.gemv_rows_dev([p + "q", p + "k", p + "v"], xh.data_ptr(), b,
-                                      [yq.data_ptr(), yk.data_ptr(), yv.data_ptr()], act=pkg.ACT_Q8DOT, stream=s)
-                    acc.gemv_rows_dev([p + "o"], xq_.data_ptr(), b, [yo.data_ptr()], act=pkg.ACT_Q8DOT, stream=s)
-                    acc.gemv_rows_dev([p + "gate", p + "up"], xh.data_ptr(), b, [yg.data_ptr(), yu.data_ptr()],
+                                      [y["q"].data_ptr(), y["k"].data_ptr(), y["v"].data_ptr()], act=pkg.ACT_Q8DOT, stream=s)
+                    acc.gemv_rows_dev([p + "o"], xq_.data_ptr(), b, [y["o"].data_ptr()], act=pkg.ACT_Q8DOT, stream=s)
+                    acc.gemv_rows_dev([p + "gate", p + "up"], xh.data_ptr(), b, [y["gate"].data_ptr(), y["up"].data_ptr()],
                                       act=pkg.ACT_Q8DOT, stream=s)
-                    acc.gemv_rows_dev([p + "down"], xf.data_ptr(), b, [yd.data_ptr()], act=pkg.ACT_Q8DOT, stream=s)
+                    acc.gemv_rows_dev([p + "down"], xf.data_ptr(), b, [y["down"].data_ptr()], act=pkg.ACT_Q8DOT, stream=s)
 
             with torch.cuda.stream(stream):
                 s = stream.cuda_stream
@@ -535,6 +565,9 @@ def verify_rows_extra(pkg, synth, torch, device, stream):
                     step(s)
                 g.replay()
                 torch.cuda.synchronize()
+                if world > 1:
+                    torch.distributed.barrier()
+                    torch.cuda.synchronize()
                 a, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
                 reps = 5
                 a.record()
@@ -543,9 +576,81 @@ def verify_rows_extra(pkg, synth, torch, device, stream):
                 e.record()
                 torch.cuda.synchronize()
                 ms = a.elapsed_time(e) / reps
-            out["per_b"].append({"b": b, "ms_per_step": round(ms, 4), "gbs": round(nbytes / ms / 1e6, 1)})
+                if world > 1:
+                    tt = torch.tensor([ms], device=dev)
+                    torch.distributed.all_reduce(tt, op=torch.distributed.ReduceOp.MAX)
+                    ms = float(tt.item())
+            out["per_b"].append({"b": b, "ms_per_step": round(ms, 4), "gbs_aggregate": round(nbytes / ms / 1e6, 1),
+                                 "gbs_per_gpu": round(nbytes / ms / 1e6 / world, 1)})
         out["bytes_per_step"] = nbytes
-        out["note"] = "int8-dot activations; projections only (4 launches per layer), weights streamed once per step"
+        out["n_gpus"] = world
+        assert acc.device_status() == 0
+        out["note"] = ("int8-dot activations; projections only (4 launches per layer, plus one operand-preparation launch "
+                       "each for b > 1), weights streamed once per step; row shards, no exchange")
+    finally:
+        acc.close()
+    return out
+
+
+def config0_extra(pkg, synth, torch, device, stream):
+    """configs[0]: one Q4_0 dequant-GEMV, 4096 x 4096, batch 1 (9,469,952 algorithmic bytes). HBM figure: 40
+    distinct resident copies of the weight (377 MB, three times L2) in rotation; L2 figure: one copy, repeated."""
+    k = n = 4096
+    copies = 40
+    acc = pkg.CudaWeightAccel(device)
+    out = {}
+    try:
+        w = make_weight(synth, Q4_0, k, n, 9, "c0")
+        for i in range(copies):
+            assert acc.upload_q4_0("c0.%d" % i, w, k, n)
+        dev = torch.device("cuda", device)
+        x = torch.from_numpy(synth.normal(9, "c0.x", k)).to(dev)
+        y = torch.empty(n, device=dev)
+        by = algo_bytes(Q4_0, k, n)
+        for act, an in ((pkg.ACT_F32, "f32"), (pkg.ACT_Q8DOT, "q8dot")):
+            for label, keys in (("hbm_40_copies", ["c0.%d" % i for i in range(copies)]), ("l2_resident", ["c0.0"] * copies)):
+                with torch.cuda.stream(stream):
+                    s = stream.cuda_stream
+                    g = torch.cuda.CUDAGraph()
+                    acc.gemv_dev([keys[0]], x.data_ptr(), [y.data_ptr()], act=act, stream=s)
+                    torch.cuda.synchronize()
+                    with torch.cuda.graph(g, stream=stream):
+                        for kk in keys:
+                            acc.gemv_dev([kk], x.data_ptr(), [y.data_ptr()], act=act, stream=s)
+                    for _ in range(3):
+                        g.replay()
+                    torch.cuda.synchronize()
+                    a, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                    a.record()
+                    for _ in range(10):
+                        g.replay()
+                    e.record()
+                    torch.cuda.synchronize()
+                    us = a.elapsed_time(e) * 1e3 / 10 / copies
+                out["%s_%s" % (an, label)] = {"us_per_gemv": round(us, 3), "gbs": round(by / us / 1e3, 1)}
+        out["algorithmic_bytes"] = by
+        out["note"] = "back-to-back launches with programmatic dependent launch; one GEMV moves 9.4 MB (1.4 us of HBM time)"
+    finally:
+        acc.close()
+    return out
+
+
+def upload_extra(pkg, synth, device):
+    """upload_q4_0 / upload_q8_0 / upload_q6_k of one 2560 -> 9728 weight: GGUF bytes per second of wall time
+    (H2D of the borrowed host bytes + the repack kernel + the sync that ends the borrow)."""
+    acc = pkg.CudaWeightAccel(device)
+    out = {}
+    try:
+        for ty, up in ((Q4_0, acc.upload_q4_0), (Q8_0, acc.upload_q8_0), (Q6_K, acc.upload_q6_k)):
+            w = make_weight(synth, ty, 2560, 9728, 8, "up.%d" % ty)
+            up("up.%d" % ty, w, 2560, 9728)
+            t0 = time.perf_counter()
+            reps = 5
+            for _ in range(reps):
+                assert up("up.%d" % ty, w, 2560, 9728)
+            dt = (time.perf_counter() - t0) / reps
+            out[TYNAME[ty]] = {"mb": round(w.size / 1e6, 2), "ms": round(dt * 1e3, 3), "gbs": round(w.size / dt / 1e9, 2)}
+        out["note"] = "host bytes are pageable numpy memory (as a caller's mmap slice would be)"
     finally:
         acc.close()
     return out
@@ -586,8 +691,7 @@ def run_reference(args):
         "impl": "reference", "metric": "dequant_gemv_hbm_gbs", "value": val, "unit": "GB/s", "n_gpus": args.gpus,
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": dt * 1e3, "higher_is_better": True,
         "scaling": "strong" if args.gpus > 1 else "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-        "config": {"workload": "configs[1]: Q8_0+Q6_K dequant-GEMV, batch 1, 2560->9728, 9728->2560, 2560->151936",
-                   "sample": sample},
+        "config": bench_config(), "sample": sample,
         "cpu_baseline": {"value": val, "unit": "GB/s", "cores": threads, "kind": "port", "sample": sample},
         "e2e": {"value": val, "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
@@ -693,11 +797,11 @@ def main():
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         barrier()
         e0.record()
-        for _ in range(args.steps):
+        for _ in range(args.steps * REPLAYS):
             graph.replay()
         e1.record()
         barrier()
-        ms_total = e0.elapsed_time(e1)
+        ms_total = e0.elapsed_time(e1) / REPLAYS
     if acc.device_status() != 0:
         raise SystemExit("device status word is non-zero: a bounded wait ran out")
     t = torch.tensor([ms_total], device=dev)
@@ -784,10 +888,17 @@ def main():
                     "share_of_step": round(share[kname] / sum(share.values()), 3),
                     "traffic": int(traffic65536[it["ty"]] * it["n"] / 65536) if world == 1 and it["k"] == 2560 else None}
         dom, sec = roof_of(order[0]), roof_of(order[1])
+        def frac_all(kname):
+            """the instantiation over ALL its launches of the step: their algorithmic bytes / their summed durations"""
+            cand = [(d, it) for d, it in zip(detail, items) if kernel_of(it) == kname]
+            by = sum(it["bytes"] * it["y"].numel() / it["n"] for _, it in cand)
+            return round(by / sum(d["us"] for d, _ in cand) / 1e3 / peak, 4)
         roof = {"bound": "hbm", "achieved": dom["achieved"], "peak": peak, "unit": "GB/s", "frac": dom["frac"],
                 "traffic": dom["traffic"], "kernel": dom["kernel"] + " (of %s peak)" % peak_src,
                 "share_of_step": dom["share_of_step"], "frac_of_8tbs": round(dom["achieved"] / 8000.0, 4),
-                "second_kernel": sec}
+                "frac_over_all_launches_of_the_instantiation": frac_all(order[0]),
+                "frac_of_the_whole_step": round(value / world / peak, 4),
+                "second_kernel": dict(sec, frac_over_all_launches_of_the_instantiation=frac_all(order[1]))}
 
     # ---- extras on rank 0 at N=1: the integer-dot GEMV variant and the W8A8 GEMM (configs[2]) ----
     extras = None
@@ -832,19 +943,48 @@ def main():
                     b.record()
                     torch.cuda.synchronize()
                     us = a.elapsed_time(b) * 1e3 / 10
-                    extras["w8a8_gemm"].append({"M": m, "K": k, "N": n, "us": round(us, 1),
-                                                "tops": round(2.0 * m * n * k / us / 1e6, 1)})
+                    rec = {"M": m, "K": k, "N": n, "us": round(us, 1), "tops": round(2.0 * m * n * k / us / 1e6, 1)}
+                    # the same kernel without the accumulator drain and loads (its hand-over loop alone), and the bare
+                    # issue rate of tcgen05.mma kind::i8 (128 x 128 x 32 per instruction): the measured int8 peak
+                    for mode, nm in ((3, "tops_handover_loop_only"), (4, "tops_mma_issue_only")):
+                        acc.debug_gemm_mode_dev(key, xg.data_ptr(), m, yg.data_ptr(), mode, 2, stream=s)
+                        torch.cuda.synchronize()
+                        a.record()
+                        acc.debug_gemm_mode_dev(key, xg.data_ptr(), m, yg.data_ptr(), mode, 10, stream=s)
+                        b.record()
+                        torch.cuda.synchronize()
+                        rec[nm] = round(2.0 * m * n * k / (a.elapsed_time(b) * 1e3 / 10) / 1e6, 1)
+                    extras["w8a8_gemm"].append(rec)
                     del xg, yg
+        extras["w8a8_gemm_peaks"] = {
+            "nominal_int8_dense_tops": 4500,
+            "measured_mma_issue_only_tops": max(r["tops_mma_issue_only"] for r in extras["w8a8_gemm"]),
+            "note": "tcgen05.mma kind::i8, 128 x 128 x 32 per instruction, operands in shared memory, issued back to back by "
+                    "one thread per CTA: the rate the tensor pipe sustains at this instruction shape. The product needs a "
+                    "fresh accumulator per 32 of K (per-block scales on both operands), and all of TMEM holds four of them"}
+        extras["config0"] = config0_extra(pkg, synth, torch, local, stream)
+        extras["upload"] = upload_extra(pkg, synth, local)
         extras["decode_chain"] = decode_chain_extra(pkg, synth, torch, local, stream)
         extras["verify_rows"] = verify_rows_extra(pkg, synth, torch, local, stream)
         if acc.device_status() != 0:
             raise SystemExit("device status word is non-zero after the extras")
+        # the keys the N > 1 lines carry too, so that a curve over N can be read for them
+        dc = extras["decode_chain"]
+        extras["scaling_curve"] = {
+            "decode_ms_per_token": min(dc["q8dot"]["ms_per_token"], dc["q8dot_chain_kernel"]["ms_per_token"]),
+            "decode_form": "launch per step" if dc["q8dot"]["ms_per_token"] <= dc["q8dot_chain_kernel"]["ms_per_token"] else "chain kernel",
+            "verify_rows": {"b%d" % r["b"]: r for r in extras["verify_rows"]["per_b"] if r["b"] in (1, 8)}}
 
     if world > 1:
         # configs[3] on all ranks: the row-sharded decode chain with an all-gather per projection
         sharded = decode_chain_sharded_extra(pkg, synth, torch, dist, local, stream, rank, world)
+        vr = verify_rows_extra(pkg, synth, torch, local, stream, rank, world, bs=(1, 8))
         if rank == 0:
-            extras = {"decode_chain_sharded": sharded}
+            forms = {k_: v_["ms_per_token"] for k_, v_ in sharded.items() if isinstance(v_, dict) and "ms_per_token" in v_}
+            best = min(forms, key=forms.get)
+            extras = {"decode_chain_sharded": sharded, "verify_rows_sharded": vr,
+                      "scaling_curve": {"decode_ms_per_token": forms[best], "decode_form": best,
+                                        "verify_rows": {"b%d" % r["b"]: r for r in vr["per_b"]}}}
 
     cpu = None
     if rank == 0 and world == 1 and not args.no_cpu_baseline:
@@ -857,12 +997,11 @@ def main():
             "metric": "dequant_gemv_hbm_gbs", "value": round(value, 2), "unit": "GB/s", "n_gpus": world,
             "steps": args.steps, "warmup": args.warmup, "ms_per_step": round(ms_step, 5), "higher_is_better": True,
             "scaling": "strong" if world > 1 else "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-            "config": {"workload": "configs[1]: Q8_0+Q6_K dequant-GEMV, batch 1, 2560->9728, 9728->2560, 2560->151936",
-                       "bytes_per_step": step_bytes, "l2": "inputs larger than L2 (827.5 MB streamed per step)",
-                       "parallelism": "rows sharded over %d GPU(s)%s" % (
-                           world, ", one NCCL all-gather of the six output shards per step" if world > 1 else "")},
+            "config": bench_config(), "bytes_per_step": step_bytes, "replays_per_step": REPLAYS,
+            "parallelism": "rows sharded over %d GPU(s)%s" % (
+                world, ", one NCCL all-gather of the six output shards per step" if world > 1 else ""),
             "e2e": {"value": round(e2e_val, 2), "unit": "GB/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
-            "gpu_launches": args.steps * len(items),
+            "gpu_launches": args.steps * REPLAYS * len(items),
             "clocks": clocks, "roofline": roof, "cpu_baseline": cpu, "per_weight": detail, "extras": extras,
             "frac_of_8tbs": round(value / 8000.0, 4),
         }
