@@ -176,6 +176,15 @@ STRIX_API int strix_cuda_prefill_q8_gemm(strix_cuda *h, const char *key, const f
 /* The same on device pointers: d_y[m][rows] from d_xs[m][in_dim] on `stream`; no copy, no sync. */
 STRIX_API int strix_cuda_prefill_q8_gemm_dev(strix_cuda *h, const char *key, const float *d_xs, size_t m, float *d_y,
                                    void *stream);
+/* The prefill GEMM with a resident Q4_0 weight: the reference's q4_gemm_w / q4_gemm_w_sk (kernels.rs:443-601;
+ * dispatch decode.rs:5655-5720), Q4_0 weights x per-32 int8 activations, int32 block sums (sum of (nibble - 8) * xq,
+ * exact), f32 combine with both block scales, split-K with a fixed-order reduction. Runs on the same tcgen05 kernel:
+ * on first use the weight gets a byte-per-code copy ((nibble - 8) + 128, row-major) next to its tile-major form.
+ * 0 when `key` is not a resident Q4_0 weight. */
+STRIX_API int strix_cuda_prefill_q4_gemm(strix_cuda *h, const char *key, const float *xs, size_t m, float *y,
+                               size_t y_cap);
+STRIX_API int strix_cuda_prefill_q4_gemm_dev(strix_cuda *h, const char *key, const float *d_xs, size_t m, float *d_y,
+                                   void *stream);
 
 /* No counterpart in the reference. The W8A8 GEMM for callers that must not allocate device memory
  * (a server whose arena owns the whole device; a latency-critical path that cannot risk the
@@ -245,8 +254,15 @@ STRIX_API int strix_cuda_decode_step_argmax(strix_cuda *h, const float *hvec, si
  * vals (may be null) receives the winning values so that the caller can fold the shards. */
 STRIX_API int strix_cuda_lm_head_argmax_rows(strix_cuda *h, const char *key, const float *xs, size_t xs_len, size_t m,
                                              int act, uint32_t *ids, float *vals);
+/* Folds the per-shard winners of a row-sharded lm_head_argmax_rows (ids / vals: [n_shards][m], shards in rank order)
+ * into the winners over the whole weight with the kernel's rule: a value replaces the running best (-3.0e38, row 0)
+ * only if it is greater, or equal with a lower row index; NaN never wins (argmax_f32, kernels.rs:2088-2110).
+ * Host-side; needs no handle. */
+STRIX_API void strix_cuda_fold_argmax_shards(size_t n_shards, size_t m, const uint32_t *ids, const float *vals,
+                                             uint32_t *out_ids, float *out_vals);
 /* argmax per row of a device matrix d_x[rows][stride] (n entries per row, rows <= 16) on `stream`;
- * d_ids[rows] / d_vals[rows] (either may be null) are device pointers. No sync. */
+ * d_ids[rows] / d_vals[rows] (either may be null) are device pointers. No sync. The per-block winners, tickets and
+ * results are one scratch set per handle: argmax calls on one handle must be serialised (one stream at a time). */
 STRIX_API int strix_cuda_argmax_dev(strix_cuda *h, const float *d_x, size_t n, size_t stride, size_t rows,
                                     uint32_t *d_ids, float *d_vals, void *stream);
 /* WeightAccel::prefill (accel.rs:464-473; decode.rs:5555-6394): m tokens hs[m][hidden] at positions
@@ -260,6 +276,9 @@ STRIX_API int strix_cuda_prefill(strix_cuda *h, const float *hs, size_t start_po
  * (speculative-decoding verify of gamma + 1 rows). */
 STRIX_API int strix_cuda_verify(strix_cuda *h, const float *hs, size_t start_pos, size_t m, float *logits,
                                 size_t logits_cap);
+/* verify, greedy form: ids[m] = argmax of each of the m rows' logits, taken on the device (4 m bytes come back instead
+ * of m * vocab floats): what the speculative loops compare the proposals with (generate.rs:644-651, 873-878). */
+STRIX_API int strix_cuda_verify_argmax(strix_cuda *h, const float *hs, size_t start_pos, size_t m, uint32_t *ids);
 /* WeightAccel::prefill_max (accel.rs:475-479): tokens one prefill / verify call accepts (8), 0 = no decode configured. */
 STRIX_API size_t strix_cuda_prefill_max(strix_cuda *h);
 /* WeightAccel::seed_decode_kv (accel.rs:421-427): fill cache rows 0 .. tokens-1 of layer il from a prefill
@@ -329,7 +348,7 @@ STRIX_API int strix_cuda_dequant_to_f32(strix_cuda *h, const char *key, float *o
  * q[n] int8 and d[n/32] f32 from x[n], n a multiple of 32. */
 STRIX_API int strix_cuda_xquant8(strix_cuda *h, const float *x, size_t n, int8_t *q, float *d);
 
-/* int32 block sums isum[m][rows][in_dim/32] of a resident Q8_0 weight with the int8 codes of
+/* int32 block sums isum[m][rows][in_dim/32] of a resident Q8_0 or Q4_0 weight with the int8 codes of
  * xs[m][in_dim] (the bit-exact tier of the GEMM, q8w_gemm32's per-block accumulator, kernels.rs:1417-1428),
  * computed by a plain integer loop without tensor cores. */
 STRIX_API int strix_cuda_debug_block_isums(strix_cuda *h, const char *key, const float *xs, size_t m, int32_t *out,

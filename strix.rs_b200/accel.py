@@ -111,6 +111,9 @@ def load_library():
     sig("strix_cuda_clear_device_status", C.c_int, H, C.c_void_p)
     sig("strix_cuda_dequant_to_f32", C.c_int, H, C.c_char_p, f32p, sz)
     sig("strix_cuda_xquant8", C.c_int, H, f32p, sz, C.POINTER(C.c_int8), f32p)
+    sig("strix_cuda_fold_argmax_shards", None, sz, sz, C.POINTER(C.c_uint32), f32p, C.POINTER(C.c_uint32), f32p)
+    sig("strix_cuda_prefill_q4_gemm", C.c_int, H, C.c_char_p, f32p, sz, f32p, sz)
+    sig("strix_cuda_prefill_q4_gemm_dev", C.c_int, H, C.c_char_p, C.c_void_p, sz, C.c_void_p, C.c_void_p)
     sig("strix_cuda_debug_gemm_isums", C.c_int, H, C.c_char_p, f32p, sz, C.c_uint32, C.POINTER(C.c_int32), sz)
     sig("strix_cuda_debug_gemm_mode_dev", C.c_int, H, C.c_char_p, C.c_void_p, sz, C.c_void_p, C.c_int, C.c_int, C.c_void_p)
     sig("strix_cuda_decode_exchange_info", C.c_int, H, C.POINTER(C.c_void_p), szp)
@@ -144,19 +147,15 @@ def _fp(a):
 
 def fold_argmax_shards(ids, vals):
     """Fold the per-shard winners of ``lm_head_argmax_rows`` (one (ids[m], vals[m]) pair per row shard, in
-    rank order) into the winners over the whole weight, with the device kernel's rule: a value replaces
-    the running best (-3.0e38, row 0) only if it is greater, or equal with a lower row index; NaN never wins."""
-    ids = np.asarray(ids, dtype=np.int64)
-    vals = np.asarray(vals, dtype=np.float32)
-    m = ids.shape[1]
-    best_v = np.full(m, np.float32(-3.0e38), dtype=np.float32)
-    best_i = np.zeros(m, dtype=np.int64)
-    for r in range(ids.shape[0]):
-        with np.errstate(invalid="ignore"):
-            take = (vals[r] > best_v) | ((vals[r] == best_v) & (ids[r] < best_i))
-        best_v = np.where(take, vals[r], best_v)
-        best_i = np.where(take, ids[r], best_i)
-    return best_i.astype(np.uint32)
+    rank order) into the winners over the whole weight (strix_cuda_fold_argmax_shards: the device kernel's rule)."""
+    L = load_library()
+    ids = np.ascontiguousarray(np.asarray(ids, dtype=np.uint32))
+    vals = np.ascontiguousarray(np.asarray(vals, dtype=np.float32))
+    n, m = ids.shape
+    out = np.zeros(m, dtype=np.uint32)
+    L.strix_cuda_fold_argmax_shards(n, m, ids.ctypes.data_as(C.POINTER(C.c_uint32)), _fp(vals),
+                                    out.ctypes.data_as(C.POINTER(C.c_uint32)), None)
+    return out
 
 
 class CudaWeightAccel:
@@ -285,6 +284,16 @@ class CudaWeightAccel:
             return None
         y = np.empty((m, info["rows"]), dtype=np.float32)
         rc = self._check(self._L.strix_cuda_prefill_q8_gemm(self._h, key.encode(), _fp(xa), m, _fp(y), y.size))
+        return y if rc == 1 else None
+
+    def prefill_q4_gemm(self, key, xs, m):
+        """The prefill GEMM with a resident Q4_0 weight (q4_gemm_w, kernels.rs:443-601): [m][rows] f32 or None."""
+        info = self.weight_info(key)
+        xa = _f32(xs)
+        if info is None or xa.size != m * info["in_dim"]:
+            return None
+        y = np.empty((m, info["rows"]), dtype=np.float32)
+        rc = self._check(self._L.strix_cuda_prefill_q4_gemm(self._h, key.encode(), _fp(xa), m, _fp(y), y.size))
         return y if rc == 1 else None
 
     def prefill_q8_gemm_dev(self, key, d_xs, m, d_y, stream=0):

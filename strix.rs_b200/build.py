@@ -25,7 +25,12 @@ FLAGS = [
 
 
 def _sources():
-    return sorted(f for f in os.listdir(CSRC) if f.endswith(".cu"))
+    """CUDA sources and host-only C++ sources (both through nvcc, which hands the latter to the host compiler)."""
+    return sorted(f for f in os.listdir(CSRC) if f.endswith((".cu", ".cpp")))
+
+
+def _obj(src):
+    return os.path.join(OBJ, os.path.splitext(src)[0] + ".o")
 
 
 def _newest_header():
@@ -38,7 +43,7 @@ def _newest_header():
 
 
 def _compile(src, verbose):
-    obj = os.path.join(OBJ, src[:-3] + ".o")
+    obj = _obj(src)
     cmd = [NVCC] + FLAGS + (["-Xptxas", "-v"] if verbose else []) + ["-c", os.path.join(CSRC, src), "-o", obj]
     r = subprocess.run(cmd, capture_output=True, text=True)
     if r.returncode != 0:
@@ -53,7 +58,7 @@ def build(force=False, verbose=False):
     hdr_t = _newest_header()
     todo = []
     for s in srcs:
-        obj = os.path.join(OBJ, s[:-3] + ".o")
+        obj = _obj(s)
         st = max(os.path.getmtime(os.path.join(CSRC, s)), hdr_t)
         if force or verbose or not os.path.exists(obj) or os.path.getmtime(obj) < st:
             todo.append(s)
@@ -62,7 +67,7 @@ def build(force=False, verbose=False):
         with ThreadPoolExecutor(max_workers=min(8, len(todo))) as ex:
             for obj, log in ex.map(lambda s: _compile(s, verbose), todo):
                 logs.append(log)
-    objs = [os.path.join(OBJ, s[:-3] + ".o") for s in srcs]
+    objs = [_obj(s) for s in srcs]
     if todo or not os.path.exists(LIB):
         cmd = [NVCC, "-shared", "-o", LIB] + objs + ["-gencode", "arch=compute_100a,code=sm_100a", "-lcudart", "-ldl"]
         r = subprocess.run(cmd, capture_output=True, text=True)

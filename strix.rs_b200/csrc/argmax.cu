@@ -121,6 +121,8 @@ static int ensure_argmax(strix_cuda *h) {
     void *p = nullptr;
     cudaError_t e = cudaMalloc(&p, total);
     if (e == cudaSuccess) e = cudaMemset(p, 0, total);
+    // (the memset runs on the legacy default stream, the kernels on non-blocking streams: nothing else orders them)
+    if (e == cudaSuccess) e = cudaDeviceSynchronize();
     if (e == cudaSuccess) e = cudaMallocHost(reinterpret_cast<void **>(&h->am_pin), (ARGMAX_MAX_ROWS + 1) * 4);
     if (e != cudaSuccess) {
         if (p) cudaFree(p);
@@ -220,3 +222,22 @@ int strix_cuda_lm_head_argmax_rows(strix_cuda *h, const char *key, const float *
 }
 
 }  // extern "C"
+
+extern "C" void strix_cuda_fold_argmax_shards(size_t n_shards, size_t m, const uint32_t *ids, const float *vals,
+                                              uint32_t *out_ids, float *out_vals) {
+    if (!ids || !vals || !out_ids) return;
+    for (size_t t = 0; t < m; t++) {
+        float best_v = -3.0e38f;
+        uint32_t best_i = 0;
+        for (size_t r = 0; r < n_shards; r++) {
+            const float v = vals[r * m + t];
+            const uint32_t i = ids[r * m + t];
+            if (v > best_v || (v == best_v && i < best_i)) {  // (a NaN compares false both ways: it never wins)
+                best_v = v;
+                best_i = i;
+            }
+        }
+        out_ids[t] = best_i;
+        if (out_vals) out_vals[t] = best_v;
+    }
+}

@@ -519,11 +519,12 @@ static int rows_enqueue(strix_cuda *h, strix_decode_state *d, size_t m, bool all
 // m tokens (rows) through the chain in one pass over the weights per step: the batched GEMV carries
 // the rows as extra MMA columns; attention takes all rows in one launch per kernel (their keys and values
 // enter the cache first, then row t attends to rows 0 .. its own position: causal). all_logits: the head for every row, else for the last one.
+// ids (may be null): the rows' greedy tokens instead of their logits (argmax on the device).
 static int rows_run(strix_cuda *h, strix_decode_state *d, const float *hs, size_t start_pos, size_t m, bool all_logits,
-                    float *out, size_t out_cap, const char *who) {
+                    float *out, size_t out_cap, const char *who, uint32_t *ids = nullptr) {
     if (m == 0 || m > ROWS_MAX) return 0;  // the caller chunks (the reference's `m > M_CHUNK -> None`, decode.rs:5559)
     const size_t hidden = d->cfg.hidden, vocab = d->cfg.vocab, n_out = all_logits ? m : 1;
-    if (out_cap < n_out * vocab) {
+    if (!ids && out_cap < n_out * vocab) {
         h->err = std::string(who) + ": logits buffer too small";
         return -1;
     }
@@ -564,7 +565,12 @@ static int rows_run(strix_cuda *h, strix_decode_state *d, const float *hs, size_
         }
     }
     CU_TRY(h, cudaGraphLaunch(exec, s));
-    CU_TRY(h, cudaMemcpyAsync(d->r_pin_out, d->r_logits, n_out * vocab * sizeof(float), cudaMemcpyDeviceToHost, s));
+    if (ids) {
+        if (argmax_rows_enqueue(h, d->r_logits, vocab, vocab, n_out, s) < 0) return -1;
+        CU_TRY(h, cudaMemcpyAsync(h->am_pin, h->am_idx, n_out * 4, cudaMemcpyDeviceToHost, s));
+    } else {
+        CU_TRY(h, cudaMemcpyAsync(d->r_pin_out, d->r_logits, n_out * vocab * sizeof(float), cudaMemcpyDeviceToHost, s));
+    }
     CU_TRY(h, cudaMemcpyAsync(&h->status_host, h->d_status, 4, cudaMemcpyDeviceToHost, s));
     CU_TRY(h, cudaStreamSynchronize(s));
     if (h->status_host != 0) {
@@ -572,7 +578,10 @@ static int rows_run(strix_cuda *h, strix_decode_state *d, const float *hs, size_
         cudaMemsetAsync(h->d_status, 0, 4, s);
         return -2;
     }
-    memcpy(out, d->r_pin_out, n_out * vocab * sizeof(float));
+    if (ids)
+        for (size_t t = 0; t < n_out; t++) ids[t] = h->am_pin[t];
+    else
+        memcpy(out, d->r_pin_out, n_out * vocab * sizeof(float));
     return 1;
 }
 
@@ -647,6 +656,12 @@ int strix_cuda_verify(strix_cuda *h, const float *hs, size_t start_pos, size_t m
     h->err.clear();
     if (!h->decode) return 0;
     return rows_run(h, h->decode, hs, start_pos, m, true, logits, logits_cap, "verify");
+}
+int strix_cuda_verify_argmax(strix_cuda *h, const float *hs, size_t start_pos, size_t m, uint32_t *ids) {
+    if (!h || !hs || !ids) return -1;
+    h->err.clear();
+    if (!h->decode || h->world > 1) return 0;
+    return rows_run(h, h->decode, hs, start_pos, m, true, nullptr, 0, "verify_argmax", ids);
 }
 // WeightAccel::prefill_max (accel.rs:475-479): 0 = prefill unsupported (no decode configured).
 size_t strix_cuda_prefill_max(strix_cuda *h) { return (h && h->decode) ? ROWS_MAX : 0; }

@@ -43,6 +43,25 @@ static int ensure_scales(strix_cuda *h, Resident *r, cudaStream_t stream) {
     return 1;
 }
 
+// A Q4_0 weight gets its byte-per-code copy for the GEMM on first use (Q8_0 weights have theirs from the upload).
+static int ensure_codes(strix_cuda *h, Resident *r, cudaStream_t stream) {
+    if (r->gemm_codes) return 1;
+    if (r->fmt != FMT_Q4_0) {
+        h->err = "prefill GEMM: this weight has no byte-per-code copy";
+        return -1;
+    }
+    uint8_t *p = nullptr;
+    CU_TRY(h, cudaMalloc(&p, std::max<size_t>(r->rows * (size_t)r->L.in_dim, 16)));
+    const cudaError_t e = launch_expand_q4_codes(r->dev, p, r->L, (uint32_t)r->rows, stream);
+    if (e != cudaSuccess) {
+        cudaFree(p);
+        h->err = std::string("expand q4 codes: ") + cudaGetErrorString(e);
+        return -1;
+    }
+    r->gemm_codes = p;
+    return 1;
+}
+
 // Scratch of the activation quantiser for m token rows of a weight with nb K-blocks.
 static int ensure_quant(strix_cuda *h, size_t m, size_t K, size_t nb) {
     const size_t n = nb * gemm_x_ld((uint32_t)m);
@@ -55,7 +74,7 @@ static int ensure_quant(strix_cuda *h, size_t m, size_t K, size_t nb) {
 // Quantise d_xs[m][in_dim] and run the GEMM into d_y[m][rows]; all scratch from the handle.
 static int gemm_device(strix_cuda *h, Resident *r, const float *d_xs, size_t m, float *d_y, cudaStream_t stream) {
     const size_t K = r->L.in_dim, nb = r->L.nb;
-    if (ensure_scales(h, r, stream) < 0) return -1;
+    if (ensure_codes(h, r, stream) < 0 || ensure_scales(h, r, stream) < 0) return -1;
     if (ensure_quant(h, m, K, nb) < 0) return -1;
     const uint32_t splits = gemm_pick_splits((uint32_t)m, (uint32_t)r->rows, (uint32_t)nb, h->num_sms);
     const size_t wsf = gemm_workspace_floats((uint32_t)m, (uint32_t)r->rows, splits);
@@ -68,12 +87,12 @@ static int gemm_device(strix_cuda *h, Resident *r, const float *d_xs, size_t m, 
 
 extern "C" {
 
-int strix_cuda_prefill_q8_gemm(strix_cuda *h, const char *key, const float *xs, size_t m, float *y, size_t y_cap) {
+static int prefill_gemm_host(strix_cuda *h, int fmt, const char *key, const float *xs, size_t m, float *y, size_t y_cap) {
     if (!h || !key || !xs || !y) return -1;
     h->err.clear();
     Resident *r = find_weight_mut(h, key);
-    // None for an unknown key or a weight that is not Q8_0 (decode.rs:3258 looks only in the q8 map)
-    if (!r || r->fmt != FMT_Q8_0) return 0;
+    // None for an unknown key or a weight of another format (decode.rs:3258 looks only in the q8 map)
+    if (!r || r->fmt != fmt) return 0;
     if (m == 0) return 1;
     if (m > 0x7fffffffu / std::max<size_t>(r->L.in_dim, 1)) return 0;
     if (y_cap < m * r->rows) {
@@ -96,6 +115,24 @@ int strix_cuda_prefill_q8_gemm(strix_cuda *h, const char *key, const float *xs, 
     return 1;
 }
 
+int strix_cuda_prefill_q8_gemm(strix_cuda *h, const char *key, const float *xs, size_t m, float *y, size_t y_cap) {
+    return prefill_gemm_host(h, FMT_Q8_0, key, xs, m, y, y_cap);
+}
+
+int strix_cuda_prefill_q4_gemm(strix_cuda *h, const char *key, const float *xs, size_t m, float *y, size_t y_cap) {
+    return prefill_gemm_host(h, FMT_Q4_0, key, xs, m, y, y_cap);
+}
+
+int strix_cuda_prefill_q4_gemm_dev(strix_cuda *h, const char *key, const float *d_xs, size_t m, float *d_y, void *stream) {
+    if (!h || !key || !d_xs || !d_y) return -1;
+    h->err.clear();
+    Resident *r = find_weight_mut(h, key);
+    if (!r || r->fmt != FMT_Q4_0) return 0;
+    if (m == 0) return 1;
+    CU_TRY(h, cudaSetDevice(h->device));
+    return gemm_device(h, r, d_xs, m, d_y, static_cast<cudaStream_t>(stream));
+}
+
 int strix_cuda_prefill_q8_gemm_dev(strix_cuda *h, const char *key, const float *d_xs, size_t m, float *d_y, void *stream) {
     if (!h || !key || !d_xs || !d_y) return -1;
     h->err.clear();
@@ -113,7 +150,7 @@ static int block_isums(strix_cuda *h, const char *key, const float *xs, size_t m
     if (!h || !key || !xs || !out) return -1;
     h->err.clear();
     Resident *r = find_weight_mut(h, key);
-    if (!r || r->fmt != FMT_Q8_0) return 0;
+    if (!r || (r->fmt != FMT_Q8_0 && r->fmt != FMT_Q4_0)) return 0;
     const size_t K = r->L.in_dim, nb = r->L.nb, total = m * r->rows * nb;
     if (out_cap < total) {
         h->err = "debug isums: output too small";
@@ -121,7 +158,7 @@ static int block_isums(strix_cuda *h, const char *key, const float *xs, size_t m
     }
     if (total == 0) return 1;
     CU_TRY(h, cudaSetDevice(h->device));
-    if (ensure_f32(h, h->gm_x, m * K) < 0 || ensure_quant(h, m, K, nb) < 0) return -1;
+    if (ensure_f32(h, h->gm_x, m * K) < 0 || ensure_quant(h, m, K, nb) < 0 || ensure_codes(h, r, h->stream) < 0) return -1;
     if (tensor && ensure_scales(h, r, h->stream) < 0) return -1;
     if (tensor && splits == 0) splits = gemm_pick_splits((uint32_t)m, (uint32_t)r->rows, (uint32_t)nb, h->num_sms);
     int32_t *d_out = nullptr;

@@ -393,6 +393,28 @@ __global__ void scales_transpose_kernel(const uint8_t *__restrict__ res, float *
     out[i] = v;
 }
 
+// Q4_0 weights for the same GEMM (the reference's q4_gemm_w bakes the nibbles into signed bytes while it
+// stages them, kernels.rs:443-537): the codes once more, row-major [rows][in_dim], one byte each as
+// (nibble - 8) + 128 - the Q8_0 convention, so that the kernel, its un-bias term and the block scales are
+// the same. Built on the first GEMM with the weight, from the resident tile-major form.
+__global__ void expand_q4_codes_kernel(const uint8_t *__restrict__ res, uint8_t *__restrict__ out, RowLayout L, uint32_t rows) {
+    const uint64_t i = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x;  // one thread per 4 codes
+    const uint64_t total = (uint64_t)rows * L.in_dim / 4u;
+    if (i >= total) return;
+    const uint32_t row = (uint32_t)(i / (L.in_dim / 4u)), k = (uint32_t)(i % (L.in_dim / 4u)) * 4u;
+    uint32_t w = 0;
+#pragma unroll
+    for (uint32_t j = 0; j < 4; j++) w |= (resident_code(res, L, row, k + j) + 120u) << (8u * j);
+    reinterpret_cast<uint32_t *>(out)[i] = w;
+}
+
+cudaError_t launch_expand_q4_codes(const uint8_t *d_res, uint8_t *d_out, const RowLayout &L, uint32_t rows, cudaStream_t stream) {
+    const uint64_t total = (uint64_t)rows * L.in_dim / 4u;
+    if (total == 0) return cudaSuccess;
+    expand_q4_codes_kernel<<<(unsigned)((total + 255) / 256), 256, 0, stream>>>(d_res, d_out, L, rows);
+    return cudaGetLastError();
+}
+
 // int32 block sums isum[m][n][kb] of a Q8_0 weight with int8 activations, one thread each:
 // the bit-exact tier of the GEMM contract, computed the plain way (no tensor cores).
 // `codes`: the weight's codes row-major [rows][in_dim], stored as q + 128.

@@ -211,12 +211,18 @@ int parse(strix_gguf *g) {
         t.n_dims = c.rd<uint32_t>();
         if (!c.ok) break;
         if (t.n_dims > 4) {
+            // (the reference accepts any count, gguf.rs:145-149; no GGUF writer emits more than four, and four is what
+            // strix_gguf_tensor carries: a deliberate difference)
             g_err = "GGUF tensor `" + t.name + "`: " + std::to_string(t.n_dims) + " dimensions";
             return -1;
         }
         for (uint32_t d = 0; d < t.n_dims; d++) {
             t.dims[d] = c.rd<uint64_t>();
-            t.numel *= t.dims[d];
+            // sizes in a file are untrusted: a product that wraps would let dims and byte count disagree
+            if (__builtin_mul_overflow(t.numel, t.dims[d], &t.numel)) {
+                g_err = "GGUF tensor `" + t.name + "`: element count overflows 64 bits";
+                return -1;
+            }
         }
         t.type = c.rd<uint32_t>();
         t.offset = c.rd<uint64_t>();
@@ -239,7 +245,15 @@ int parse(strix_gguf *g) {
         const bool is_int = m.type <= 5 || m.type == 10 || m.type == 11;
         if (is_int && m.i >= 0) g->alignment = (size_t)m.u;
     }
-    g->data_offset = g->alignment ? (c.pos + g->alignment - 1) / g->alignment * g->alignment : c.pos;
+    size_t padded = c.pos;
+    if (g->alignment) {
+        if (__builtin_add_overflow(c.pos, g->alignment - 1, &padded)) {
+            g_err = "GGUF: general.alignment " + std::to_string(g->alignment) + " overflows the data offset";
+            return -1;
+        }
+        padded = padded / g->alignment * g->alignment;
+    }
+    g->data_offset = padded;
     if (g->data_offset > g->len) {
         g_err = "GGUF tensor data offset past EOF";
         return -1;
@@ -249,8 +263,18 @@ int parse(strix_gguf *g) {
 
 int fill(const strix_gguf *g, size_t i, strix_gguf_tensor *out) {
     const Tensor &t = g->tensors[i];
-    const size_t nbytes = (size_t)(t.numel / block_elems(t.type)) * block_bytes(t.type);
-    const uint64_t start = (uint64_t)g->data_offset + t.offset;
+    if (t.numel % block_elems(t.type) != 0) {
+        g_err = "tensor `" + t.name + "`: " + std::to_string(t.numel) + " elements are not whole blocks of " +
+                std::to_string(block_elems(t.type));
+        return -1;
+    }
+    uint64_t nbytes64 = 0, start = 0;
+    if (__builtin_mul_overflow((uint64_t)(t.numel / block_elems(t.type)), (uint64_t)block_bytes(t.type), &nbytes64) ||
+        __builtin_add_overflow((uint64_t)g->data_offset, t.offset, &start)) {
+        g_err = "tensor `" + t.name + "`: size or offset overflows 64 bits";
+        return -1;
+    }
+    const size_t nbytes = (size_t)nbytes64;
     if (start > g->len || nbytes > g->len - start) {
         g_err = "tensor `" + t.name + "` data [" + std::to_string(start) + ".." + std::to_string(start + nbytes) +
                 "] past EOF " + std::to_string(g->len);
@@ -435,7 +459,9 @@ int strix_cuda_upload_gguf_tensor(strix_cuda *h, const strix_gguf *g, const char
             default: rc = 0; break;  // no kernel for this format: the weight stays with the CPU path
         }
     } else if (t.n_dims == 1 && t.ggml_type == STRIX_GGML_F32) {
-        rc = strix_cuda_upload_f32(h, name, reinterpret_cast<const float *>(t.data), (size_t)t.dims[0]);
+        // (a file with general.alignment below 4 can leave the vector on an odd address: it is declined, not cast)
+        if (reinterpret_cast<uintptr_t>(t.data) % alignof(float) == 0)
+            rc = strix_cuda_upload_f32(h, name, reinterpret_cast<const float *>(t.data), (size_t)t.dims[0]);
     }
     if (rc == 1 && drop_pages) strix_gguf_advise_dontneed(g, name);
     return rc;

@@ -165,6 +165,9 @@ cudaError_t noalloc_prepare_device(int device);  // gemm_noalloc.cu: materialise
 uint32_t gemm_scales_ld(uint32_t rows);  // leading dimension (floats) of the transposed f32 scale plane
 cudaError_t launch_scales_transpose(const uint8_t *d_res, float *d_out, const RowLayout &L, uint32_t rows,
                                     cudaStream_t stream);  // d_res: the resident (tile-major) weight
+// Q4_0: the weight's codes as bytes (nibble - 8) + 128, row-major [rows][in_dim], for the GEMM's TMA boxes
+cudaError_t launch_expand_q4_codes(const uint8_t *d_res, uint8_t *d_out, const RowLayout &L, uint32_t rows,
+                                   cudaStream_t stream);
 uint32_t gemm_x_ld(uint32_t m);  // leading dimension (tokens) of the K-block-major per-token arrays
 // x[m][nb*32] -> q int8 [m][nb*32]; block scales d, code sums xs and un-bias terms xc, each [nb][gemm_x_ld(m)]
 cudaError_t launch_xquant8_sum(const float *d_x, int8_t *d_q, float *d_d, int32_t *d_xs, float *d_xc, uint32_t m,

@@ -3,7 +3,7 @@
 ``GgufFile`` mirrors the reference's ``GgufFile`` (crates/strix-models/src/gguf.rs:104-269) over the
 C-ABI of ``include/strix_gguf.h``: open / parse, metadata getters with the reference's widening
 rules, the tensor index, borrowed raw tensor bytes, and the hand-over of tensors to a
-``CudaWeightAccel``. The parser itself is the C++ code in ``csrc/gguf.cu``; nothing is parsed here.
+``CudaWeightAccel``. The parser itself is the C++ code in ``csrc/gguf.cpp``; nothing is parsed here.
 
 ``write_gguf`` writes a GGUF v3 file from Python values (synthetic models for tests and benchmarks:
 there are no model files in this environment). It follows the published container layout the

@@ -11,7 +11,7 @@ def declared_symbols():
     for fn in sorted(os.listdir(os.path.join(ROOT, "include"))):
         if fn.endswith(".h"):
             txt = open(os.path.join(ROOT, "include", fn)).read()
-            names += re.findall(r"STRIX_API[^;(]*?\b(strix_(?:cuda|gguf|ggml)_\w+)\s*\(", txt)
+            names += re.findall(r"STRIX_API[^;(]*?\b(strix_(?:cuda|gguf|ggml|spec)_\w+)\s*\(", txt)
     return names
 
 

@@ -107,3 +107,29 @@ def test_gemm_declines_like_the_reference(accel, synth):
     assert accel.prefill_q8_gemm("gd.none", np.zeros((2, 64), np.float32), 2) is None
     assert accel.upload_q8_0("gd.q8", synth.q8_0(1, "gd8", 8, 64), 64, 8)
     assert accel.prefill_q8_gemm("gd.q8", np.zeros(100, np.float32), 2) is None           # xs.len() != m * in_dim
+
+
+@pytest.mark.parametrize("m,n,k", [(1, 8, 32), (17, 100, 160), (130, 257, 2560), (200, 3840, 15360), (256, 4096, 3840)])
+def test_q4_gemm_matches_integer_oracle(accel, orc, synth, m, n, k):
+    """The prefill GEMM with Q4_0 weights (q4_gemm_w / q4_gemm_w_sk, kernels.rs:443-601): int32 block sums
+    sum((nibble - 8) * xq) bit-exact from the tensor-core kernel, scaled output at the 1e-3 contract. The last two
+    shapes are the verify configuration's ffn_down (K = 15360: split-K, the reference splits from K >= 12288) and
+    q projection at the reference's chunk size of 256 tokens."""
+    w = synth.q4_0(74, "g4", n, k)
+    xs = synth.normal(74, "g4.x", m, k)
+    key = "g4.%d.%d" % (n, k)
+    assert accel.upload_q4_0(key, w, k, n)
+    xq, xd, _ = orc.xquant8(xs)
+    if m * n * (k // 32) <= 20_000_000:
+        want, want_i = orc.idot_gemm(w, synth.Q4_0, xq, xd, m, k, n, want_isums=True)
+        np.testing.assert_array_equal(accel.debug_gemm_isums(key, xs, m), want_i)
+    else:
+        want = orc.idot_gemm(w, synth.Q4_0, xq, xd, m, k, n)
+    got = accel.prefill_q4_gemm(key, xs, m)
+    assert got is not None and got.shape == (m, n)
+    r = rel_l2(got, want)
+    print("q4 gemm m=%d n=%d k=%d rel-L2 %.2e max-abs %.2e" % (m, n, k, r, np.abs(got - want).max()))
+    assert r <= REL_L2_TOL and np.abs(got - want).max() <= 1e-3 * np.abs(want).max()
+    assert accel.prefill_q8_gemm(key, xs, m) is None          # the q8 entry point looks only at Q8_0 weights
+    assert accel.device_status() == 0
+    accel.upload_q4_0(key, synth.q4_0(1, "tiny", 1, 32), 32, 1)

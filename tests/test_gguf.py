@@ -127,6 +127,30 @@ def test_refused_inputs(gguf):
         gguf.GgufFile(data=gguf.gguf_bytes({"general.alignment": T(4, 1 << 20)}, [])[:100])
 
 
+def test_sizes_that_wrap_are_parse_errors(gguf):
+    """Sizes in a file are untrusted: an element count whose product wraps, an offset near 2^64, a tensor that is
+    not whole blocks and an alignment that overflows the data offset are errors, never a view whose dims and bytes
+    disagree."""
+    hdr = lambda n_t, n_kv: struct.pack("<IIQQ", 0x46554747, 3, n_t, n_kv)  # noqa: E731
+    name = struct.pack("<Q", 1) + b"t"
+    # dims 2^33 x 2^33: the product wraps to 0
+    b = hdr(1, 0) + name + struct.pack("<I", 2) + struct.pack("<QQ", 1 << 33, 1 << 33) + struct.pack("<IQ", 0, 0) + bytes(64)
+    with pytest.raises(gguf.GgufError, match="overflows"):
+        gguf.GgufFile(data=b)
+    # offset close to 2^64: data_offset + offset wraps
+    b = hdr(1, 0) + name + struct.pack("<I", 1) + struct.pack("<Q", 32) + struct.pack("<IQ", 0, (1 << 64) - 8) + bytes(256)
+    with pytest.raises(gguf.GgufError, match="overflows|past EOF"):
+        gguf.GgufFile(data=b).tensor_bytes("t")
+    # 40 elements of a 32-element block type
+    b = hdr(1, 0) + name + struct.pack("<I", 1) + struct.pack("<Q", 40) + struct.pack("<IQ", 2, 0) + bytes(256)
+    with pytest.raises(gguf.GgufError, match="whole blocks"):
+        gguf.GgufFile(data=b).tensor_bytes("t")
+    # general.alignment = 2^63 - 1 (the largest the reference's widening admits): the data offset lands past the file
+    T = gguf.Typed
+    with pytest.raises(gguf.GgufError, match="overflows|past EOF"):
+        gguf.GgufFile(data=gguf.gguf_bytes({"general.alignment": T(10, (1 << 63) - 1)}, []))
+
+
 def test_block_geometry_table(gguf, orc):
     # ggml_quant.rs:88-124
     want = {0: (1, 4), 1: (1, 2), 2: (32, 18), 3: (32, 20), 6: (32, 22), 7: (32, 24), 8: (32, 34), 9: (32, 36),

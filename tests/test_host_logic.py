@@ -138,3 +138,24 @@ def test_sharded_argmax_folds_to_the_unsharded_winner_gloo():
     for p in ps:
         p.join(60)
     assert res == [(0, True), (1, True)]
+
+
+def test_fold_argmax_shards_rule(pkg):
+    """strix_cuda_fold_argmax_shards against the kernel's rule restated in numpy: greater wins, ties go to the
+    lower row index, NaN never wins, nothing above the floor leaves (row 0, -3.0e38)."""
+    import numpy as np
+    rng = np.random.default_rng(11)
+    for n_sh, m in ((1, 1), (3, 5), (8, 16)):
+        ids = rng.integers(0, 1000, size=(n_sh, m)).astype(np.uint32)
+        vals = rng.normal(size=(n_sh, m)).astype(np.float32)
+        vals[0, 0] = np.nan
+        if n_sh > 1:
+            vals[1, m - 1] = vals[0, m - 1]                 # a tie: the lower index must win
+        best_v = np.full(m, np.float32(-3.0e38)); best_i = np.zeros(m, np.int64)
+        for r in range(n_sh):
+            with np.errstate(invalid="ignore"):
+                take = (vals[r] > best_v) | ((vals[r] == best_v) & (ids[r] < best_i))
+            best_v = np.where(take, vals[r], best_v); best_i = np.where(take, ids[r], best_i)
+        np.testing.assert_array_equal(pkg.fold_argmax_shards(ids, vals), best_i.astype(np.uint32))
+    allnan = np.full((2, 3), np.nan, np.float32)
+    np.testing.assert_array_equal(pkg.fold_argmax_shards(np.ones((2, 3), np.uint32), allnan), np.zeros(3, np.uint32))
