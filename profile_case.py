@@ -1,8 +1,12 @@
 """Small driver for profiling one kernel on one shape (what the ncu summaries under profiles/ ran).
 
-    python strix.rs_b200/profile_case.py gemv <ggml type 2|8|14> <rows> <in_dim> <act 0|1> [launches]
-    python strix.rs_b200/profile_case.py gemm <tokens> <in_dim> <rows> [launches]
-    python strix.rs_b200/profile_case.py attn <context> [steps]
+    python profile_case.py gemv <ggml type 2|8|14> <rows> <in_dim> <act 0|1> [launches]
+    python profile_case.py gemm <tokens> <in_dim> <rows> [launches]
+    python profile_case.py attn <context> [steps]
+    python profile_case.py chain <layers> [tokens]
+
+`chain`: the decode configuration's layer shapes (hidden 2560, q 4096, k/v 1024, ffn 9728, Q4_0; Q6_K head over
+151936 rows) with <layers> layers, integer-dot form, run as the persistent chain kernel (``-k regex:chain_kernel``).
 
 `attn`: a two-layer model with the benchmark's attention geometry (32 query heads, 8 KV heads of 128,
 hidden 2560) and a KV cache seeded up to <context>; runs decode_step at that position (``-k regex:sdpa_split``).
@@ -16,7 +20,7 @@ import sys
 
 import numpy as np
 
-ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+ROOT = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, ROOT)
 import __graft_entry__ as entry  # noqa: E402
 
@@ -40,6 +44,27 @@ def main():
         y = torch.empty(n, device=dev)
         for _ in range(reps):
             acc.gemv_dev(["w"], x.data_ptr(), [y.data_ptr()], act=act, stream=s)
+    elif kind == "chain":
+        n_layers = int(sys.argv[2])
+        reps = int(sys.argv[3]) if len(sys.argv) > 3 else 3
+        hidden, qdim, kvdim, ffn, vocab = 2560, 4096, 1024, 9728, 151936
+        shapes = {"attn_q": (qdim, hidden), "attn_k": (kvdim, hidden), "attn_v": (kvdim, hidden), "attn_output": (hidden, qdim),
+                  "ffn_gate": (ffn, hidden), "ffn_up": (ffn, hidden), "ffn_down": (hidden, ffn)}
+        base = {nm: synth.q4_0(1, nm, n_, k_) for nm, (n_, k_) in shapes.items()}
+        for il in range(n_layers):
+            for nm, (n_, k_) in shapes.items():
+                assert acc.upload_q4_0("blk.%d.%s.weight" % (il, nm), base[nm], k_, n_)
+            for nn in ("attn_norm", "ffn_norm"):
+                acc.upload_f32("blk.%d.%s.weight" % (il, nn), synth.norm_weight(1, nn, hidden))
+        gen = 8192
+        hb = synth.q6_k(1, "head", gen, hidden).reshape(gen, -1)
+        assert acc.upload_q6_k("output.weight", np.ascontiguousarray(hb[np.arange(vocab) % gen]).reshape(-1), hidden, vocab)
+        acc.upload_f32("output_norm.weight", synth.norm_weight(1, "on", hidden))
+        acc.set_option("decode_chain", 1)
+        assert acc.configure_decode(hidden, 32, ffn, vocab, n_layers, eps=1e-6, act=pkg.ACT_Q8DOT)
+        h0 = synth.normal(1, "h0", hidden)
+        for i in range(reps):
+            y = torch.from_numpy(acc.decode_step(h0, i))
     elif kind == "attn":
         ctx = int(sys.argv[2])
         reps = int(sys.argv[3]) if len(sys.argv) > 3 else 3

@@ -39,3 +39,15 @@ def test_create_fails_loudly_without_a_device(pkg):
         assert str(e)  # a real message, not a silent fallback
     else:
         raise AssertionError("create succeeded without a CUDA device")
+
+
+def test_rust_ffi_is_generated_from_the_headers():
+    """strix-backend-cuda/src/ffi.rs (the Rust side of the boundary, uncompiled here) declares exactly what
+    include/*.h declares: it is generated, and this checks that it is current."""
+    import subprocess
+    import sys
+    gen = os.path.join(ROOT, "strix.rs_b200", "rust", "gen_ffi.py")
+    assert subprocess.run([sys.executable, gen, "--check"]).returncode == 0, "run strix.rs_b200/rust/gen_ffi.py"
+    txt = open(os.path.join(ROOT, "strix.rs_b200", "rust", "strix-backend-cuda", "src", "ffi.rs")).read()
+    for name in declared_symbols():
+        assert "pub fn %s(" % name in txt, name
