@@ -218,20 +218,35 @@ typedef struct strix_gpu_decode_config {
     uint32_t n_swa, max_seq;
     const strix_gpu_layer_cfg *layers; /* n_layers entries; may be NULL (unused by the projection chain) */
     /* Not in the reference struct: */
-    int attn_standin_q; /* 1: projection chain only, Wo is fed with q (no KV cache). 0: real attention of the dense
-                         * Qwen3 flavour (QK-norm when qk_norm, NEOX rope, KV cache of max_seq rows, grouped-query
-                         * softmax with 1/sqrt(head_dim)); `layers` must then describe every layer */
+    int attn_standin_q; /* 1: projection chain only, Wo is fed with q (no KV cache). 0: real attention over a KV cache
+                         * of max_seq rows in the flavours of the reference's forwards; `layers` must then describe
+                         * every layer (see strix_cuda_configure_decode) */
     int act;            /* STRIX_ACT_F32 or STRIX_ACT_Q8DOT for every projection */
 } strix_gpu_decode_config;
 
 /* WeightAccel::configure_decode (accel.rs:417; decode.rs:4528-4622). Call after every weight
  * (blk.N.attn_q/attn_k/attn_v/attn_output/ffn_gate/ffn_up/ffn_down.weight, output.weight or
  * token_embd.weight) and norm (blk.N.attn_norm/ffn_norm.weight, output_norm.weight via upload_f32)
- * is uploaded; with real attention and qk_norm also blk.N.attn_q_norm / attn_k_norm.weight (head_dim floats).
- * 0 = declined (a weight missing, post-norm / softcap / V-norm / sliding-window or local layers / shared
- * K = V / GPT-J rope / per-layer head sizes requested, or a sharded handle asking for anything but the
- * integer-dot projection chain): the model keeps its per-weight gemv path. Any later upload drops the
- * configuration. */
+ * is uploaded; with qk_norm also blk.N.attn_q_norm / attn_k_norm.weight (head_dim floats); with post_norm
+ * blk.N.post_attention_norm / post_ffw_norm.weight (hidden floats); optionally rope_freqs.weight.
+ * Real attention (attn_standin_q = 0) follows the reference's forwards field by field:
+ *   head_dim, n_kv   per layer (<= 512, a multiple of 4; n_heads a multiple of n_kv)
+ *   k_eq_v           no V projection on that layer: V is the raw K projection, taken before the K-norm
+ *   norm_v           V RMS-normalised per head without a weight
+ *   qk_norm          per-head RMSNorm of q and k before the rope
+ *   no_rope, rope_norm (pairs (2k, 2k+1) instead of (k, k + head_dim/2)), rope_theta per layer. The angle of
+ *                    pair j is pos * theta^(-2j/hd) / rope_freqs[j] (factors on non-local layers, when uploaded)
+ *                    for a post_norm model (the Gemma forward, ops.rs:159-176), else the running product
+ *                    pos * (theta^(-2/hd))^j of the Qwen3 / SmolLM3 forwards (qwen3.rs:126-138)
+ *   is_local + n_swa a local layer attends only to the last n_swa cached rows (decode.rs:5312-5325)
+ *   attn_rsqrt       scores scaled by 1/sqrt(head_dim), else by 1
+ *   post_norm        h += rmsnorm(Wo a) * post_attention_norm; h = (h + rmsnorm(Wd act) * post_ffw_norm) * output_scale
+ *   final_softcap    > 0: logits = cap * tanh(logits / cap) on every logits-returning call (the argmax calls skip it)
+ * set_option("kv_f16", 1) before this call keeps the cache in f16 (the reference's STRIX_F16_KV), rows rounded
+ * to nearest with ties away from zero as the reference's stores do (kernels.rs:18-32).
+ * 0 = declined (a weight or norm missing, a head size out of range, or a sharded handle asking for anything
+ * but the integer-dot projection chain without post_norm): the model keeps its per-weight gemv path. Any later
+ * upload drops the configuration. */
 STRIX_API int strix_cuda_configure_decode(strix_cuda *h, const strix_gpu_decode_config *cfg);
 /* WeightAccel::decode_step (accel.rs:433; decode.rs:5047-5531): logits[vocab] from the embedded hidden
  * state hvec[hidden]. With the attention stand-in and integer-dot activations the whole chain is ONE
@@ -331,6 +346,7 @@ STRIX_API int strix_cuda_clear_device_status(strix_cuda *h, void *stream);
  * quantises all rows itself), "gemv_debug" (bit 0: stream the weights without
  * arithmetic, bit 1: empty launches, bit 2: stop after the activation prologue), "batch_graph" (gemv_batch
  * replays a cached CUDA graph), "decode_chain" (the projection chain as one persistent launch),
+ * "kv_f16" (real attention keeps its KV cache in f16),
  * "chain_trace" (per-step clocks, see strix_cuda_decode_trace), "chain_debug" (bit 0: the chain kernel skips
  * the arithmetic, bit 1: its waits on exchange vectors do not wait; results are then meaningless), "poll_limit" (bound, in polls, of a wait on
  * an exchange vector; 0 = default), "profile" (as strix_cuda_opts.profile). */

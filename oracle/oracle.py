@@ -238,3 +238,131 @@ def attention_token(q, k, v, q_norm, k_norm, pos, kc, vc, n_heads, n_kv, hd, eps
             o += e[t] * V[t, kvh]
         out[hh * hd:(hh + 1) * hd] = o * (np.float32(1.0) / e.sum(dtype=np.float32))
     return out
+
+
+# ---- the other attention flavours: SmolLM3 (smollm3.rs), Gemma (gemma.rs, ops.rs), f16 KV cache (kernels.rs) ----
+def rope_adjacent(vec, pos, n_dims, freq_base):
+    """smollm3.rs:126-138: pairs (2k, 2k + 1); the angle chain of rope_neox."""
+    vec = _f32(vec).copy()
+    half = n_dims // 2
+    theta_scale = np.float32(np.power(np.float32(freq_base), np.float32(-2.0) / np.float32(n_dims)))
+    theta = np.float32(pos)
+    for k in range(half):
+        s, c = np.float32(np.sin(theta)), np.float32(np.cos(theta))
+        x0, x1 = vec[2 * k], vec[2 * k + 1]
+        vec[2 * k] = x0 * c - x1 * s
+        vec[2 * k + 1] = x0 * s + x1 * c
+        theta = np.float32(theta * theta_scale)
+    return vec
+
+
+def rope_pow(vec, pos, theta, freq_factors=None):
+    """ops.rs:159-176 rope_in_place_ff: pairs (j, j + half), inv_freq = theta^(-(2 j) / head_dim), divided by
+    freq_factors[j] where given, angle = pos * inv_freq, all in f32."""
+    vec = _f32(vec).copy()
+    hd = vec.size
+    half = hd // 2
+    for j in range(half):
+        ex = np.float32(-(np.float32(2.0) * np.float32(j))) / np.float32(hd)
+        inv = np.float32(np.power(np.float32(theta), ex))
+        if freq_factors is not None:
+            inv = np.float32(inv / np.float32(freq_factors[j]))
+        ang = np.float32(np.float32(pos) * inv)
+        s, c = np.float32(np.sin(ang)), np.float32(np.cos(ang))
+        x1, x2 = vec[j], vec[j + half]
+        vec[j] = x1 * c - x2 * s
+        vec[j + half] = x2 * c + x1 * s
+    return vec
+
+
+def softcap(x, cap):
+    """ops.rs:127-135 softcap_inplace: cap * tanh(x * (1 / cap)); cap <= 0 leaves x alone."""
+    x = _f32(x)
+    if cap <= 0:
+        return x.copy()
+    inv = np.float32(1.0) / np.float32(cap)
+    return (np.float32(cap) * np.tanh(x * inv)).astype(np.float32)
+
+
+def addnorm(h, x, w, eps, out_scale=1.0):
+    """gemma.rs:268-275 norm, then the sandwich residual gemma.rs:876-879 / 896-906:
+    (h + x * (1 / sqrt(mean(x^2) + eps)) * w) * out_scale."""
+    on = rmsnorm_inplace(x, w, eps)
+    return ((_f32(h) + on).astype(np.float32) * np.float32(out_scale)).astype(np.float32)
+
+
+def f32_to_f16_cache(x):
+    """f2h of the reference's f16 KV cache (kernels.rs:18-32): to nearest, a tie AWAY from zero (numpy's own
+    conversion rounds ties to even), overflow and NaN to infinity. Returns uint16 words."""
+    b = _f32(x).view(np.uint32).astype(np.uint64)
+    sign = (b >> 16) & 0x8000
+    a = b & 0x7FFFFFFF
+    normal = ((a + 0x1000) >> 13) - (112 << 10)
+    mant = (a & 0x7FFFFF) | 0x800000
+    shift = np.clip(125 - (a >> 23).astype(np.int64), 0, 63).astype(np.uint64)
+    sub = ((mant >> shift) + 1) >> 1
+    h = np.where(a >= 0x47800000, 0x7C00, np.where(a >= 0x38800000, normal, np.where(a < 0x33000000, 0, sub)))
+    return (sign | h).astype(np.uint16)
+
+
+def f16_cache_to_f32(hw):
+    """h2f (kernels.rs:8-16): exact."""
+    return np.asarray(hw, dtype=np.uint16).view(np.float16).astype(np.float32)
+
+
+def attention_token_flavour(q, k, v, q_norm, k_norm, pos, kc, vc, n_heads, n_kv, hd, eps, rope, adjacent=False,
+                            norm_v=False, window=0, scale=None, kv_f16=False):
+    """One token of attention in the flavours of smollm3.rs:590-648 and gemma.rs:779-872.
+    v None: the layer shares K and V, V is the RAW k (gemma.rs:796-803). q_norm / k_norm None: no QK-norm.
+    rope: None | ("chain", base) (qwen3.rs / smollm3.rs) | ("pow", theta, freq_factors or None) (ops.rs:159-176).
+    norm_v: V RMS-normed per head without a weight (gemma.rs:804-813). window > 0: only the last `window` cached
+    rows are attended to (gemma.rs:840-851). kv_f16: rows pass through the f16 cache (kernels.rs:1984-1995, KVLD).
+    kc / vc: python lists of cached rows (already rounded when kv_f16), one per position. Returns attn[n_heads * hd]."""
+    q, k = _f32(q).copy(), _f32(k).copy()
+    vv = k.copy() if v is None else _f32(v).copy()
+    if norm_v:
+        ones = np.ones(hd, dtype=np.float32)
+        for kh in range(n_kv):
+            vv[kh * hd:(kh + 1) * hd] = rmsnorm_inplace(vv[kh * hd:(kh + 1) * hd], ones, eps)
+
+    def rot(x):
+        if rope is None:
+            return x
+        if rope[0] == "chain":
+            return rope_adjacent(x, pos, hd, rope[1]) if adjacent else rope_neox(x, pos, hd, rope[1])
+        assert not adjacent
+        return rope_pow(x, pos, rope[1], rope[2])
+
+    for hh in range(n_heads):
+        qh = q[hh * hd:(hh + 1) * hd]
+        if q_norm is not None:
+            qh = rmsnorm_inplace(qh, q_norm, eps)
+        q[hh * hd:(hh + 1) * hd] = rot(qh)
+    for kh in range(n_kv):
+        kk = k[kh * hd:(kh + 1) * hd]
+        if k_norm is not None:
+            kk = rmsnorm_inplace(kk, k_norm, eps)
+        k[kh * hd:(kh + 1) * hd] = rot(kk)
+    if kv_f16:
+        k, vv = f16_cache_to_f32(f32_to_f16_cache(k)), f16_cache_to_f32(f32_to_f16_cache(vv))
+    assert len(kc) == pos and len(vc) == pos
+    kc.append(k)
+    vc.append(vv)
+    length = pos + 1
+    first = length - min(length, window) if window > 0 else 0
+    K = np.stack(kc[first:]).reshape(length - first, n_kv, hd)
+    V = np.stack(vc[first:]).reshape(length - first, n_kv, hd)
+    sc = np.float32(1.0) / np.sqrt(np.float32(hd)) if scale is None else np.float32(scale)
+    groups = n_heads // n_kv
+    out = np.zeros(n_heads * hd, dtype=np.float32)
+    for hh in range(n_heads):
+        kvh = hh // groups
+        qh = q[hh * hd:(hh + 1) * hd]
+        scores = np.array([dot_f32(qh, K[t, kvh]) for t in range(length - first)], dtype=np.float32) * sc
+        e = np.exp(scores - scores.max()).astype(np.float32)          # ops.rs:50-72 softmax_inplace
+        e = (e * (np.float32(1.0) / e.sum(dtype=np.float32))).astype(np.float32)
+        o = np.zeros(hd, dtype=np.float32)
+        for t in range(length - first):
+            o += e[t] * V[t, kvh]
+        out[hh * hd:(hh + 1) * hd] = o
+    return out

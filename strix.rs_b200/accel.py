@@ -346,27 +346,32 @@ class CudaWeightAccel:
 
     def configure_decode(self, hidden, n_heads, ffn, vocab, n_layers, eps=1e-6, act_gelu=False, act=ACT_Q8DOT,
                          attn_standin_q=True, post_norm=False, final_softcap=0.0, head_dim=0, n_kv=0,
-                         rope_theta=1e6, max_seq=0, qk_norm=True, layer_overrides=None):
+                         rope_theta=1e6, max_seq=0, qk_norm=True, layer_overrides=None, attn_rsqrt=True,
+                         norm_v=False, n_swa=0, layers=None):
         """GpuDecodeConfig -> bool (accel.rs:417). attn_standin_q=True: the projection chain alone (Wo is
-        fed with q). False: real attention of the dense Qwen3 flavour (QK-norm, NEOX rope, KV cache of
-        max_seq rows, grouped-query softmax); head_dim / n_kv / rope_theta describe every layer
-        (layer_overrides: {layer: {field: value}} for the declined-configuration tests)."""
-        layers = None
-        if not attn_standin_q:
-            layers = (_LayerCfg * n_layers)()
+        fed with q). False: real attention (QK-norm, rope, KV cache of max_seq rows, grouped-query softmax);
+        head_dim / n_kv / rope_theta describe every layer unless `layers` (a list of dicts with the GpuLayerCfg
+        fields, accel.rs:19-39) gives them per layer; layer_overrides: {layer: {field: value}} on top of either.
+        A post_norm model with the stand-in takes its output scales from `layers` too (default 1)."""
+        lay = None
+        if not attn_standin_q or layers is not None:
+            lay = (_LayerCfg * n_layers)()
             for il in range(n_layers):
-                layers[il] = _LayerCfg(head_dim=head_dim, n_kv=n_kv, k_eq_v=0, rope_theta=rope_theta, is_local=0,
-                                       output_scale=1.0, no_rope=0, rope_norm=0)
-                for k, v in (layer_overrides or {}).get(il, {}).items():
-                    setattr(layers[il], k, v)
+                f = dict(head_dim=head_dim, n_kv=n_kv, k_eq_v=0, rope_theta=rope_theta, is_local=0,
+                         output_scale=1.0, no_rope=0, rope_norm=0)
+                if layers is not None:
+                    f.update(layers[il])
+                f.update((layer_overrides or {}).get(il, {}))
+                lay[il] = _LayerCfg(**f)
         c = _DecodeCfg(hidden=hidden, n_heads=n_heads, ffn=ffn, vocab=vocab, n_layers=n_layers, eps=eps,
-                       final_softcap=final_softcap, attn_rsqrt=1, norm_v=0, qk_norm=int(qk_norm),
-                       post_norm=int(post_norm), act_gelu=int(act_gelu), max_seq=max_seq,
-                       layers=layers if layers is not None else None,
+                       final_softcap=final_softcap, attn_rsqrt=int(attn_rsqrt), norm_v=int(norm_v), qk_norm=int(qk_norm),
+                       post_norm=int(post_norm), act_gelu=int(act_gelu), n_swa=n_swa, max_seq=max_seq,
+                       layers=lay if lay is not None else None,
                        attn_standin_q=int(attn_standin_q), act=act)
         rc = self._check(self._L.strix_cuda_configure_decode(self._h, C.byref(c)))
         self._vocab = vocab if rc == 1 else None
-        self._kvdim = head_dim * n_kv if (rc == 1 and not attn_standin_q) else 0
+        self._kvdims = [int(l.head_dim) * int(l.n_kv) for l in lay] if (rc == 1 and not attn_standin_q) else []
+        self._kvdim = self._kvdims[0] if self._kvdims else 0
         return rc == 1
 
     def decode_step(self, h, pos=0):
@@ -416,7 +421,8 @@ class CudaWeightAccel:
 
     def seed_decode_kv(self, il, k, v):
         ka, va = _f32(k), _f32(v)
-        kvdim = getattr(self, "_kvdim", 0)
+        kvdims = getattr(self, "_kvdims", [])
+        kvdim = kvdims[il] if il < len(kvdims) else 0
         if not kvdim or ka.size != va.size or ka.size % kvdim:
             return False
         return self._check(self._L.strix_cuda_seed_decode_kv(self._h, il, _fp(ka), _fp(va), ka.size // kvdim)) == 1

@@ -351,6 +351,7 @@ int strix_cuda_set_option(strix_cuda *h, const char *name, long long value) {
     else if (n == "gemv_debug") h->tune.debug = v;
     else if (n == "rows_operand_image") h->tune.xop = v;
     else if (n == "batch_graph") h->use_batch_graph = value != 0;
+    else if (n == "kv_f16") h->kv_f16 = value != 0;
     else if (n == "decode_chain") h->decode_chain = value < 0 ? -1 : value != 0;
     else if (n == "chain_trace") h->chain_trace = value != 0;
     else if (n == "chain_debug") h->chain_debug = v;

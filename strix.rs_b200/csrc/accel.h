@@ -46,6 +46,7 @@ struct strix_cuda {
     int use_batch_graph = 1;          // gemv_batch replays a cached CUDA graph
     uint32_t chain_debug = 0;         // measurement: see launch_chain
     int chain_trace = 0;              // measurement: the chain kernel records per-step clocks (strix_cuda_decode_trace)
+    int kv_f16 = 0;                   // real attention keeps its KV cache in f16 (the reference's STRIX_F16_KV, decode.rs:513-516)
     int decode_chain = -1;            // the decode projection chain as one persistent launch: 1 on, 0 off, -1 = on for a
                                       // row-sharded handle (the only way it can run), off otherwise (a launch per step
                                       // measured 1.33 against 1.39 ms per token on one GPU)

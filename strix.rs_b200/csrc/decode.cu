@@ -15,10 +15,11 @@
 // norm, the activation quantiser, the gate activation and the residual add live inside the GEMV.
 // Attention comes in two forms. `attn_standin_q = 1` feeds Wo with q itself (n_heads * head_dim
 // values): the projection chain alone, which is what the benchmark's decode configuration times.
-// `attn_standin_q = 0` runs the dense Qwen3 attention (attention.cu: per-head QK RMSNorm, NEOX RoPE,
-// KV append, grouped-query softmax over the cache) between the q/k/v step and the o step; other
-// attention flavours (sliding window, shared K = V, V-norm, softcap, post-norm) are declined and the
-// model keeps its per-weight gemv path.
+// `attn_standin_q = 0` runs real attention (attention.cu) between the q/k/v step and the o step, in the
+// flavours of the reference's three forwards: dense Qwen3 (QK-norm, half-split rope), SmolLM3 (no QK-norm,
+// adjacent-pair rope, layers without rope) and Gemma (per-layer head sizes, V = raw K on layers without a V
+// projection, weightless V-norm, frequency factors, sliding window on local layers, scale 1 or 1/sqrt(hd),
+// sandwich post-norm residuals with a per-layer output scale, final logit soft-cap), with an f32 or f16 KV cache.
 //
 // With the attention stand-in and integer-dot activations the whole chain runs as ONE persistent
 // cooperative kernel (chain.cu): the steps above become a list the kernel walks; its producer warps
@@ -53,10 +54,20 @@ using namespace strix;
 struct strix_decode_state {
     strix_gpu_decode_config cfg{};
     struct Layer {
-        const Resident *q, *k, *v, *o, *gate, *up, *down;
+        const Resident *q, *k, *v, *o, *gate, *up, *down;  // v = null: the layer shares K and V (gemma.rs:796-803)
         const float *attn_norm, *ffn_norm;
         const float *q_norm = nullptr, *k_norm = nullptr;  // real attention with QK-norm only
-        float theta_scale = 1.f;                           // rope base ^ (-2 / head_dim), computed on the host
+        const float *post_attn = nullptr, *post_ffw = nullptr;  // sandwich post-norm weights (post_norm models)
+        float out_scale = 1.f;                                  // per-layer output scale of a post_norm model
+        size_t qdim = 0, kvdim = 0;                             // rows of Wq, of Wk
+        // real attention
+        uint32_t hd = 0, n_kv = 0, window = 0;
+        int rope = ATT_ROPE_CHAIN, rope_adjacent = 0;
+        float theta_scale = 1.f;  // rope base ^ (-2 / head_dim), computed on the host (ATT_ROPE_CHAIN)
+        float theta = 0.f;        // rope base (ATT_ROPE_POW)
+        const float *freq = nullptr;
+        float scale = 1.f;
+        void *kc = nullptr, *vc = nullptr;  // this layer's cache rows inside kv_block
     };
     std::vector<Layer> layers;
     const Resident *head = nullptr;
@@ -65,19 +76,21 @@ struct strix_decode_state {
     float *h = nullptr, *q = nullptr, *k = nullptr, *v = nullptr, *gate = nullptr, *up = nullptr, *logits = nullptr;
     void *pin_h = nullptr, *pin_logits = nullptr;
     cudaGraphExec_t exec = nullptr;
-    // real attention (attn_standin_q = 0): KV cache [n_layers][max_seq][n_kv * hd] twice, the softmax
-    // partials, the attention output, and the position word the kernels read (a graph replays unchanged)
-    bool real_attn = false;
-    uint32_t hd = 0, n_kv = 0;
-    float *kc = nullptr, *vc = nullptr, *att_part = nullptr, *attn = nullptr;
+    // real attention (attn_standin_q = 0): KV cache (per layer [max_seq][n_kv * hd] for k and for v, f32 or f16,
+    // one allocation), the softmax partials, the attention output, and the position word the kernels read (a graph
+    // replays unchanged)
+    bool real_attn = false, kv_f16 = false;
+    void *kv_block = nullptr;
+    float *att_part = nullptr, *attn = nullptr;
+    float *t = nullptr;  // a projection's output before its sandwich post-norm (post_norm models)
     uint32_t *d_pos = nullptr, *pin_pos = nullptr;
     // batched rows (prefill / verify, up to ROWS_MAX tokens per call): [m][dim] activations, [m] positions
     float *r_h = nullptr, *r_q = nullptr, *r_k = nullptr, *r_v = nullptr, *r_attn = nullptr, *r_gate = nullptr,
-          *r_up = nullptr, *r_logits = nullptr;
+          *r_up = nullptr, *r_logits = nullptr, *r_t = nullptr;
     uint32_t *r_pos = nullptr;
     void *r_pin_in = nullptr, *r_pin_out = nullptr;
     cudaGraphExec_t r_exec[2][9] = {};  // [all logits?][rows]: the batched chain captured once per shape
-    size_t qdim = 0, kvdim = 0;
+    size_t qdim = 0, kvdim = 0;  // the largest layer's
     // chain-kernel programs, one per (h, logits) buffer pair
     struct Program {
         const float *h;
@@ -103,9 +116,10 @@ struct strix_decode_state {
 
 static void decode_free(strix_decode_state *d) {
     if (!d) return;
-    for (float *p : {d->h, d->q, d->k, d->v, d->gate, d->up, d->logits, d->kc, d->vc, d->att_part, d->attn})
+    for (float *p : {d->h, d->q, d->k, d->v, d->gate, d->up, d->logits, d->att_part, d->attn, d->t})
         if (p) cudaFree(p);
-    for (float *p : {d->r_h, d->r_q, d->r_k, d->r_v, d->r_attn, d->r_gate, d->r_up, d->r_logits})
+    if (d->kv_block) cudaFree(d->kv_block);
+    for (float *p : {d->r_h, d->r_q, d->r_k, d->r_v, d->r_attn, d->r_gate, d->r_up, d->r_logits, d->r_t})
         if (p) cudaFree(p);
     for (auto &row : d->r_exec)
         for (cudaGraphExec_t g : row)
@@ -140,25 +154,28 @@ static const float *f32_of(strix_cuda *h, const std::string &key, size_t n) {
 
 // The chain as a list of steps, handed one at a time to `emit` (launch it, or collect it).
 // `mid(layer index)` runs between the q/k/v step and the o step and returns the vector Wo is fed with
-// (q itself for the stand-in; the attention output otherwise), or null on error.
-template <typename Emit, typename Mid>
-static int walk_chain(strix_decode_state *d, Emit emit, Mid mid) {
+// (q itself for the stand-in; the attention output otherwise), or null on error. In a post_norm model the o and
+// down steps write into d->t and `post(layer index, 0 | 1)` folds that into h (sandwich norm, residual, output scale).
+template <typename Emit, typename Mid, typename Post>
+static int walk_chain(strix_decode_state *d, Emit emit, Mid mid, Post post) {
     const float eps = d->cfg.eps;
     const int gate_pre = d->cfg.act_gelu ? STRIX_PRE_GEGLU : STRIX_PRE_SWIGLU;
+    const bool sandwich = d->cfg.post_norm != 0;
     for (size_t il = 0; il < d->layers.size(); il++) {
         auto &L = d->layers[il];
         {
             const Resident *w[3] = {L.q, L.k, L.v};
             float *y[3] = {d->q, d->k, d->v};
-            if (emit(3, w, d->h, L.attn_norm, eps, STRIX_PRE_RMSNORM, y, nullptr) < 0) return -1;
+            if (emit(L.v ? 3 : 2, w, d->h, L.attn_norm, eps, STRIX_PRE_RMSNORM, y, nullptr) < 0) return -1;
         }
         {   // h += Wo a, a = the attention output (or q itself: the stand-in)
             const float *a = mid(il);
             if (!a) return -1;
             const Resident *w[1] = {L.o};
-            float *y[1] = {d->h};
+            float *y[1] = {sandwich ? d->t : d->h};
             const float *r[1] = {d->h};
-            if (emit(1, w, a, nullptr, 0.f, STRIX_PRE_NONE, y, r) < 0) return -1;
+            if (emit(1, w, a, nullptr, 0.f, STRIX_PRE_NONE, y, sandwich ? nullptr : r) < 0) return -1;
+            if (sandwich && post(il, 0) < 0) return -1;
         }
         {
             const Resident *w[2] = {L.gate, L.up};
@@ -167,9 +184,10 @@ static int walk_chain(strix_decode_state *d, Emit emit, Mid mid) {
         }
         {
             const Resident *w[1] = {L.down};
-            float *y[1] = {d->h};
+            float *y[1] = {sandwich ? d->t : d->h};
             const float *r[1] = {d->h};
-            if (emit(1, w, d->gate, d->up, 0.f, gate_pre, y, r) < 0) return -1;
+            if (emit(1, w, d->gate, d->up, 0.f, gate_pre, y, sandwich ? nullptr : r) < 0) return -1;
+            if (sandwich && post(il, 1) < 0) return -1;
         }
     }
     const Resident *w[1] = {d->head};
@@ -177,12 +195,62 @@ static int walk_chain(strix_decode_state *d, Emit emit, Mid mid) {
     return emit(1, w, d->h, d->out_norm, eps, STRIX_PRE_RMSNORM, y, nullptr);
 }
 
+// One layer's attention over `rows` tokens whose q / k / v sit in the given buffers.
+static int attention_enqueue(strix_cuda *h, strix_decode_state *d, const strix_decode_state::Layer &L, float *q, const float *k,
+                             const float *v, float *attn, const uint32_t *pos, uint32_t rows, cudaStream_t s) {
+    AttnArgs A{};
+    A.q = q;
+    A.k = k;
+    A.v = L.v ? v : k;
+    A.q_norm = L.q_norm;
+    A.k_norm = L.k_norm;
+    A.freq = L.freq;
+    A.kc = L.kc;
+    A.vc = L.vc;
+    A.part = d->att_part;
+    A.attn = attn;
+    A.pos = pos;
+    A.n_heads = d->cfg.n_heads;
+    A.n_kv = L.n_kv;
+    A.hd = L.hd;
+    A.max_seq = d->cfg.max_seq;
+    A.rows = rows;
+    A.window = L.window;
+    A.kv_f16 = d->kv_f16 ? 1u : 0u;
+    A.norm_v = d->cfg.norm_v ? 1u : 0u;
+    A.rope = (uint32_t)L.rope;
+    A.rope_adjacent = (uint32_t)L.rope_adjacent;
+    A.eps = d->cfg.eps;
+    A.theta_scale = L.theta_scale;
+    A.theta = L.theta;
+    A.scale = L.scale;
+    A.status = h->d_status;
+    const cudaError_t e = launch_attention_step(A, s);
+    if (e != cudaSuccess) {
+        h->err = std::string("attention: ") + cudaGetErrorString(e);
+        return -1;
+    }
+    return 0;
+}
+
+// The sandwich residual after the o (which = 0) or down (which = 1) projection of a post_norm model.
+static int post_enqueue(strix_cuda *h, strix_decode_state *d, const strix_decode_state::Layer &L, int which, float *hid,
+                        const float *t, uint32_t rows, cudaStream_t s) {
+    const cudaError_t e = launch_addnorm(hid, t, which ? L.post_ffw : L.post_attn, d->cfg.hidden, d->cfg.eps,
+                                         which ? L.out_scale : 1.0f, rows, s);
+    if (e != cudaSuccess) {
+        h->err = std::string("post-norm: ") + cudaGetErrorString(e);
+        return -1;
+    }
+    return 0;
+}
+
 // The chain-kernel program for the current d->h / d->logits, built on first use. Null when the
 // chain kernel cannot be used (plan failed, switched off, or a new buffer pair inside a stream capture).
 static const strix_decode_state::Program *chain_program(strix_cuda *h, strix_decode_state *d, cudaStream_t s) {
     // (attention is not a GEMV step, and the exchange-vector prologue is the integer-dot one: launches otherwise)
     const bool want_chain = h->decode_chain < 0 ? h->world > 1 : h->decode_chain != 0;
-    if (!d->chain_ok || d->real_attn || !want_chain || d->cfg.act != STRIX_ACT_Q8DOT) return nullptr;
+    if (!d->chain_ok || d->real_attn || d->cfg.post_norm || !want_chain || d->cfg.act != STRIX_ACT_Q8DOT) return nullptr;
     for (auto &p : d->programs)
         if (p.h == d->h && p.logits == d->logits) return &p;
     cudaStreamCaptureStatus cs = cudaStreamCaptureStatusNone;
@@ -324,18 +392,9 @@ static int enqueue_chain(strix_cuda *h, strix_decode_state *d, cudaStream_t s) {
         return gemv_launch(h, nmat, w, a, b, eps, pre, act, y, r, s);
     }, [&](size_t il) -> const float * {
         if (!d->real_attn) return d->q;
-        const auto &L = d->layers[il];
-        const size_t per_layer = (size_t)d->cfg.max_seq * d->n_kv * d->hd;
-        const cudaError_t e = launch_attention_step(
-            d->q, d->k, d->v, L.q_norm, L.k_norm, d->kc + il * per_layer, d->vc + il * per_layer, d->att_part, d->attn,
-            d->d_pos, d->cfg.n_heads, d->n_kv, d->hd, d->cfg.eps, L.theta_scale, 1.0f / sqrtf((float)d->hd),
-            d->cfg.max_seq, 1, h->d_status, s);
-        if (e != cudaSuccess) {
-            h->err = std::string("attention: ") + cudaGetErrorString(e);
-            return nullptr;
-        }
+        if (attention_enqueue(h, d, d->layers[il], d->q, d->k, d->v, d->attn, d->d_pos, 1, s) < 0) return nullptr;
         return d->attn;
-    });
+    }, [&](size_t il, int which) { return post_enqueue(h, d, d->layers[il], which, d->h, d->t, 1, s); });
 }
 
 extern "C" {
@@ -344,68 +403,92 @@ int strix_cuda_configure_decode(strix_cuda *h, const strix_gpu_decode_config *cf
     if (!h || !cfg) return -1;
     h->err.clear();
     decode_release(h);
-    // Only the projection chain is on this library's path; a model that expects attention here is declined.
-    if (cfg->post_norm || cfg->final_softcap != 0.f) return 0;
-    // Real attention: the dense Qwen3 flavour only (qwen3.rs:683-710): global NEOX-rope layers of one head
-    // size, 1/sqrt(hd) scaling, no V-norm, no sliding window, no shared K = V; anything else is declined.
     const bool real_attn = !cfg->attn_standin_q;
-    uint32_t hd = 0, n_kv = 0;
     if (real_attn) {
-        if (!cfg->layers || !cfg->attn_rsqrt || cfg->norm_v || cfg->n_swa || cfg->max_seq == 0 || cfg->n_heads == 0) return 0;
-        hd = cfg->layers[0].head_dim;
-        n_kv = cfg->layers[0].n_kv;
-        if (hd == 0 || hd > 256 || (hd & 3u) || n_kv == 0 || cfg->n_heads % n_kv != 0) return 0;  // 16-byte rows
+        // per-layer head sizes within what attention.cu handles (16-byte cache rows, <= ATT_MAX_HD), grouped-query heads
+        if (!cfg->layers || cfg->max_seq == 0 || cfg->n_heads == 0) return 0;
         for (uint32_t il = 0; il < cfg->n_layers; il++) {
             const strix_gpu_layer_cfg &lc = cfg->layers[il];
-            if (lc.head_dim != hd || lc.n_kv != n_kv || lc.k_eq_v || lc.is_local || lc.no_rope || lc.rope_norm ||
-                !(lc.rope_theta > 0.f) || (lc.output_scale != 0.f && lc.output_scale != 1.f))
+            if (lc.head_dim == 0 || lc.head_dim > ATT_MAX_HD || (lc.head_dim & 3u) || lc.n_kv == 0 || cfg->n_heads % lc.n_kv != 0 ||
+                (!lc.no_rope && !(lc.rope_theta > 0.f)))
                 return 0;
         }
     }
     if (cfg->act != STRIX_ACT_F32 && cfg->act != STRIX_ACT_Q8DOT) return 0;
     // A sharded handle holds row shards only: the chain then runs as the persistent kernel alone (projection
     // chain with the stand-in, integer-dot form), every rank publishing its rows into all ranks' exchange vectors.
-    if (h->world > 1 && (real_attn || cfg->act != STRIX_ACT_Q8DOT || h->decode_chain == 0 || h->world > GEMV_MAX_PEERS)) return 0;
+    if (h->world > 1 && (real_attn || cfg->post_norm || cfg->act != STRIX_ACT_Q8DOT || h->decode_chain == 0 || h->world > GEMV_MAX_PEERS))
+        return 0;
     CU_TRY(h, cudaSetDevice(h->device));
     auto *d = new strix_decode_state();
     d->cfg = *cfg;
     d->cfg.layers = nullptr;
+    d->kv_f16 = real_attn && h->kv_f16 != 0;
     const size_t hidden = cfg->hidden, ffn = cfg->ffn;
-    size_t qdim = 0, kvdim = 0;
+    size_t qdim = 0, kvdim = 0, hd_max = 0, cache_bytes = 0;
     auto need = [&](const std::string &key, size_t in_dim, size_t out_dim) -> const Resident * {
         const Resident *r = find_weight(h, key.c_str());
         if (!r || r->L.in_dim != in_dim || (out_dim && r->out_total != out_dim)) return nullptr;
         return r;
     };
+    const size_t kv_elem = d->kv_f16 ? 2 : 4;
     bool ok = true;
     for (uint32_t il = 0; il < cfg->n_layers && ok; il++) {
         const std::string b = "blk." + std::to_string(il) + ".";
         strix_decode_state::Layer L{};
+        const bool shared_kv = real_attn && cfg->layers[il].k_eq_v;
         L.q = need(b + "attn_q.weight", hidden, 0);
         L.k = need(b + "attn_k.weight", hidden, 0);
-        L.v = need(b + "attn_v.weight", hidden, 0);
-        ok = L.q && L.k && L.v && L.k->out_total == L.v->out_total && L.q->fmt == L.k->fmt && L.q->fmt == L.v->fmt;
+        L.v = shared_kv ? nullptr : need(b + "attn_v.weight", hidden, 0);
+        ok = L.q && L.k && L.q->fmt == L.k->fmt && (shared_kv || (L.v && L.k->out_total == L.v->out_total && L.q->fmt == L.v->fmt));
         if (!ok) break;
-        if (il == 0) {
-            qdim = L.q->out_total;
-            kvdim = L.k->out_total;
-        }
-        ok = L.q->out_total == qdim && L.k->out_total == kvdim;
-        L.o = need(b + "attn_output.weight", qdim, hidden);
+        L.qdim = L.q->out_total;
+        L.kvdim = L.k->out_total;
+        // the stand-in keeps one q size for all layers (its exchange vectors are sized once)
+        ok = real_attn || il == 0 || (L.qdim == qdim && L.kvdim == kvdim);
+        qdim = std::max(qdim, L.qdim);
+        kvdim = std::max(kvdim, L.kvdim);
+        L.o = need(b + "attn_output.weight", L.qdim, hidden);
         L.gate = need(b + "ffn_gate.weight", hidden, ffn);
         L.up = need(b + "ffn_up.weight", hidden, ffn);
         L.down = need(b + "ffn_down.weight", ffn, hidden);
         L.attn_norm = f32_of(h, b + "attn_norm.weight", hidden);
         L.ffn_norm = f32_of(h, b + "ffn_norm.weight", hidden);
+        if (cfg->post_norm) {
+            // gemma.rs:876-879, 896-906: h += norm(Wo a) * post_attention_norm; h = (h + norm(Wd act) * post_ffw_norm) * scale
+            L.post_attn = f32_of(h, b + "post_attention_norm.weight", hidden);
+            L.post_ffw = f32_of(h, b + "post_ffw_norm.weight", hidden);
+            L.out_scale = cfg->layers ? cfg->layers[il].output_scale : 1.0f;
+            ok = ok && L.post_attn && L.post_ffw;
+        }
         if (real_attn) {
+            const strix_gpu_layer_cfg &lc = cfg->layers[il];
+            L.hd = lc.head_dim;
+            L.n_kv = lc.n_kv;
+            hd_max = std::max<size_t>(hd_max, L.hd);
             if (cfg->qk_norm) {
-                L.q_norm = f32_of(h, b + "attn_q_norm.weight", hd);
-                L.k_norm = f32_of(h, b + "attn_k_norm.weight", hd);
+                L.q_norm = f32_of(h, b + "attn_q_norm.weight", L.hd);
+                L.k_norm = f32_of(h, b + "attn_k_norm.weight", L.hd);
                 ok = ok && L.q_norm && L.k_norm;
             }
-            // theta_scale = freq_base.powf(-2.0 / n_dims) (qwen3.rs:128), evaluated in f32 on the host
-            L.theta_scale = powf(cfg->layers[il].rope_theta, -2.0f / (float)hd);
-            ok = ok && L.q && L.k && L.q->out_total == (size_t)cfg->n_heads * hd && L.k->out_total == (size_t)n_kv * hd;
+            // Which angle formula: the Gemma forward (the post_norm family) evaluates base^(-2j/hd) per pair and divides
+            // by the frequency factors on its global layers (ops.rs:159-176, gemma.rs:819-829); the Qwen3 and SmolLM3
+            // forwards multiply the angle by base^(-2/hd) pair after pair (qwen3.rs:126-138, smollm3.rs:126-138).
+            if (lc.no_rope) L.rope = ATT_ROPE_NONE;
+            else if (cfg->post_norm) {
+                L.rope = ATT_ROPE_POW;
+                L.theta = lc.rope_theta;
+                if (!lc.is_local) L.freq = f32_of(h, "rope_freqs.weight", L.hd / 2);  // absent: no factors
+            } else {
+                L.rope = ATT_ROPE_CHAIN;
+                // theta_scale = freq_base.powf(-2.0 / n_dims) (qwen3.rs:128), evaluated in f32 on the host
+                L.theta_scale = powf(lc.rope_theta, -2.0f / (float)L.hd);
+            }
+            L.rope_adjacent = lc.rope_norm ? 1 : 0;
+            L.window = (lc.is_local && cfg->n_swa > 0) ? cfg->n_swa : 0;  // decode.rs:5312-5320
+            L.scale = cfg->attn_rsqrt ? 1.0f / sqrtf((float)L.hd) : 1.0f;
+            ok = ok && L.qdim == (size_t)cfg->n_heads * L.hd && L.kvdim == (size_t)L.n_kv * L.hd;
+            cache_bytes += 2 * (((size_t)cfg->max_seq * L.kvdim * kv_elem + 255) & ~(size_t)255);
         }
         ok = ok && L.o && L.gate && L.up && L.down && L.attn_norm && L.ffn_norm && L.gate->fmt == L.up->fmt;
         d->layers.push_back(L);
@@ -431,15 +514,19 @@ int strix_cuda_configure_decode(strix_cuda *h, const strix_gpu_decode_config *cf
     alloc(&d->gate, ffn);
     alloc(&d->up, ffn);
     alloc(&d->logits, cfg->vocab);
+    if (cfg->post_norm) alloc(&d->t, hidden);
     if (real_attn) {
         d->real_attn = true;
-        d->hd = hd;
-        d->n_kv = n_kv;
-        const size_t cache = (size_t)cfg->n_layers * cfg->max_seq * n_kv * hd;
         const size_t splits = (cfg->max_seq + ATT_SPLIT_TOKENS - 1) / ATT_SPLIT_TOKENS;
-        alloc(&d->kc, cache);
-        alloc(&d->vc, cache);
-        alloc(&d->att_part, 8 * (size_t)cfg->n_heads * splits * (hd + 2));  // up to 8 rows per call (prefill / verify)
+        if (e == cudaSuccess) e = cudaMalloc(&d->kv_block, std::max<size_t>(cache_bytes, 256));
+        size_t off = 0;
+        for (auto &L : d->layers) {
+            const size_t bytes = ((size_t)cfg->max_seq * L.kvdim * kv_elem + 255) & ~(size_t)255;
+            L.kc = static_cast<char *>(d->kv_block) + off;
+            L.vc = static_cast<char *>(d->kv_block) + off + bytes;
+            off += 2 * bytes;
+        }
+        alloc(&d->att_part, 8 * (size_t)cfg->n_heads * splits * (hd_max + 2));  // up to 8 rows per call (prefill / verify)
         alloc(&d->attn, qdim);
         if (e == cudaSuccess) e = cudaMalloc(&d->d_pos, 4);
         if (e == cudaSuccess) e = cudaMemset(d->d_pos, 0, 4);
@@ -504,6 +591,7 @@ static int rows_alloc(strix_cuda *h, strix_decode_state *d) {
     alloc(&d->r_gate, d->cfg.ffn);
     alloc(&d->r_up, d->cfg.ffn);
     alloc(&d->r_logits, d->cfg.vocab);
+    if (d->cfg.post_norm) alloc(&d->r_t, d->cfg.hidden);
     if (e == cudaSuccess) e = cudaMalloc(&d->r_pos, ROWS_MAX * 4);
     if (e == cudaSuccess) e = cudaMallocHost(&d->r_pin_in, ROWS_MAX * (d->cfg.hidden * sizeof(float) + 4));
     if (e == cudaSuccess) e = cudaMallocHost(&d->r_pin_out, ROWS_MAX * (size_t)d->cfg.vocab * sizeof(float));
@@ -569,6 +657,7 @@ static int rows_run(strix_cuda *h, strix_decode_state *d, const float *hs, size_
         if (argmax_rows_enqueue(h, d->r_logits, vocab, vocab, n_out, s) < 0) return -1;
         CU_TRY(h, cudaMemcpyAsync(h->am_pin, h->am_idx, n_out * 4, cudaMemcpyDeviceToHost, s));
     } else {
+        if (d->cfg.final_softcap > 0.f) CU_TRY(h, launch_softcap(d->r_logits, n_out * vocab, d->cfg.final_softcap, s));  // decode.rs:6382-6393
         CU_TRY(h, cudaMemcpyAsync(d->r_pin_out, d->r_logits, n_out * vocab * sizeof(float), cudaMemcpyDeviceToHost, s));
     }
     CU_TRY(h, cudaMemcpyAsync(&h->status_host, h->d_status, 4, cudaMemcpyDeviceToHost, s));
@@ -591,32 +680,27 @@ static int rows_enqueue(strix_cuda *h, strix_decode_state *d, size_t m, bool all
     const float eps = d->cfg.eps;
     const int gate_pre = d->cfg.act_gelu ? STRIX_PRE_GEGLU : STRIX_PRE_SWIGLU;
     const uint32_t b = (uint32_t)m, ffn = d->cfg.ffn;
+    const bool sandwich = d->cfg.post_norm != 0;
     for (size_t il = 0; il < d->layers.size(); il++) {
         auto &L = d->layers[il];
         {
             const Resident *w[3] = {L.q, L.k, L.v};
             float *y[3] = {d->r_q, d->r_k, d->r_v};
-            if (gemv_launch_rows(h, 3, w, d->r_h, L.attn_norm, eps, STRIX_PRE_RMSNORM, act, y, nullptr, b, (uint32_t)hidden, 0, s) < 0)
+            if (gemv_launch_rows(h, L.v ? 3 : 2, w, d->r_h, L.attn_norm, eps, STRIX_PRE_RMSNORM, act, y, nullptr, b, (uint32_t)hidden, 0, s) < 0)
                 return -1;
         }
         const float *a = d->r_q;  // the stand-in feeds Wo with q
         if (d->real_attn) {
-            const size_t per_layer = (size_t)d->cfg.max_seq * d->n_kv * d->hd;
-            const cudaError_t e = launch_attention_step(
-                d->r_q, d->r_k, d->r_v, L.q_norm, L.k_norm, d->kc + il * per_layer, d->vc + il * per_layer, d->att_part,
-                d->r_attn, d->r_pos, d->cfg.n_heads, d->n_kv, d->hd, eps, L.theta_scale, 1.0f / sqrtf((float)d->hd),
-                d->cfg.max_seq, b, h->d_status, s);
-            if (e != cudaSuccess) {
-                h->err = std::string("attention: ") + cudaGetErrorString(e);
-                return -1;
-            }
+            if (attention_enqueue(h, d, L, d->r_q, d->r_k, d->r_v, d->r_attn, d->r_pos, b, s) < 0) return -1;
             a = d->r_attn;
         }
         {
             const Resident *w[1] = {L.o};
-            float *y[1] = {d->r_h};
+            float *y[1] = {sandwich ? d->r_t : d->r_h};
             const float *r[1] = {d->r_h};
-            if (gemv_launch_rows(h, 1, w, a, nullptr, 0.f, STRIX_PRE_NONE, act, y, r, b, (uint32_t)d->qdim, 0, s) < 0) return -1;
+            if (gemv_launch_rows(h, 1, w, a, nullptr, 0.f, STRIX_PRE_NONE, act, y, sandwich ? nullptr : r, b, (uint32_t)L.qdim, 0, s) < 0)
+                return -1;
+            if (sandwich && post_enqueue(h, d, L, 0, d->r_h, d->r_t, b, s) < 0) return -1;
         }
         {
             const Resident *w[2] = {L.gate, L.up};
@@ -626,9 +710,10 @@ static int rows_enqueue(strix_cuda *h, strix_decode_state *d, size_t m, bool all
         }
         {
             const Resident *w[1] = {L.down};
-            float *y[1] = {d->r_h};
+            float *y[1] = {sandwich ? d->r_t : d->r_h};
             const float *r[1] = {d->r_h};
-            if (gemv_launch_rows(h, 1, w, d->r_gate, d->r_up, 0.f, gate_pre, act, y, r, b, ffn, ffn, s) < 0) return -1;
+            if (gemv_launch_rows(h, 1, w, d->r_gate, d->r_up, 0.f, gate_pre, act, y, sandwich ? nullptr : r, b, ffn, ffn, s) < 0) return -1;
+            if (sandwich && post_enqueue(h, d, L, 1, d->r_h, d->r_t, b, s) < 0) return -1;
         }
     }
     {
@@ -674,9 +759,19 @@ int strix_cuda_seed_decode_kv(strix_cuda *h, size_t il, const float *k, const fl
     strix_decode_state *d = h->decode;
     if (!d || !d->real_attn || il >= d->layers.size() || tokens > d->cfg.max_seq) return 0;
     CU_TRY(h, cudaSetDevice(h->device));
-    const size_t per_layer = (size_t)d->cfg.max_seq * d->kvdim, n = tokens * d->kvdim * sizeof(float);
-    CU_TRY(h, cudaMemcpyAsync(d->kc + il * per_layer, k, n, cudaMemcpyHostToDevice, h->stream));
-    CU_TRY(h, cudaMemcpyAsync(d->vc + il * per_layer, v, n, cudaMemcpyHostToDevice, h->stream));
+    const auto &L = d->layers[il];
+    const size_t n = tokens * L.kvdim;
+    if (d->kv_f16) {  // the cache holds f16: round on the host the way the cache's own stores do
+        std::vector<unsigned short> kh(n), vh(n);
+        f32_to_f16_ref(k, kh.data(), n);
+        f32_to_f16_ref(v, vh.data(), n);
+        CU_TRY(h, cudaMemcpyAsync(L.kc, kh.data(), n * 2, cudaMemcpyHostToDevice, h->stream));
+        CU_TRY(h, cudaMemcpyAsync(L.vc, vh.data(), n * 2, cudaMemcpyHostToDevice, h->stream));
+        CU_TRY(h, cudaStreamSynchronize(h->stream));
+        return 1;
+    }
+    CU_TRY(h, cudaMemcpyAsync(L.kc, k, n * sizeof(float), cudaMemcpyHostToDevice, h->stream));
+    CU_TRY(h, cudaMemcpyAsync(L.vc, v, n * sizeof(float), cudaMemcpyHostToDevice, h->stream));
     CU_TRY(h, cudaStreamSynchronize(h->stream));  // k and v are borrowed for the call
     return 1;
 }
@@ -817,6 +912,8 @@ int strix_cuda_decode_step(strix_cuda *h, const float *hvec, size_t pos, float *
     }
     int rc = decode_enqueue_step(h, d, hvec, pos);
     if (rc < 0) return rc;
+    // the final logit soft-cap (decode.rs:5516-5527); the greedy entry point skips it: cap * tanh(x / cap) is monotone
+    if (d->cfg.final_softcap > 0.f) CU_TRY(h, launch_softcap(d->logits, n_out, d->cfg.final_softcap, h->stream));
     CU_TRY(h, cudaMemcpyAsync(d->pin_logits, d->logits, n_out * sizeof(float), cudaMemcpyDeviceToHost, h->stream));
     if ((rc = decode_finish(h, "decode_step")) < 0) return rc;
     memcpy(logits, d->pin_logits, n_out * sizeof(float));

@@ -193,15 +193,33 @@ cudaError_t launch_peer_barrier(uint32_t *d_epoch, uint32_t *d_local_flags, uint
 // The activation quantiser on its own: q[n] int8, d[n/32] f32 from x[n].
 cudaError_t launch_xquant8(const float *d_x, int8_t *d_q, float *d_d, uint32_t n, cudaStream_t stream);
 
-// One token of attention for one layer (attention.cu): QK RMSNorm (null norm pointers = none) + NEOX
-// RoPE in place on d_q, rotated k and v appended to the cache row *d_pos, softmax(q k^T scale) v over
-// rows 0..*d_pos into d_attn[n_heads * hd]. `rows` tokens at once: d_q / d_k / d_v / d_attn are [rows][dim],
-// d_pos[rows] their positions (ascending, so that attention is causal among them). d_part: rows * n_heads * ceil(max_seq / ATT_SPLIT_TOKENS) * (hd + 2) floats.
+// One layer's attention for `rows` tokens at once (attention.cu): per-head norm and rope of q (in place) and k, k / v
+// appended to the cache at the tokens' positions, then softmax(q k^T * scale) v over the cached rows into attn.
+// q / k / v / attn are [rows][dim]; pos[rows] ascending (so that attention is causal among the rows).
+// part: rows * n_heads * ceil(max_seq / ATT_SPLIT_TOKENS) * (hd + 2) floats.
 constexpr uint32_t ATT_SPLIT_TOKENS = 64;
-cudaError_t launch_attention_step(float *d_q, const float *d_k, const float *d_v, const float *d_q_norm,
-                                  const float *d_k_norm, float *d_kc, float *d_vc, float *d_part, float *d_attn,
-                                  const uint32_t *d_pos, uint32_t n_heads, uint32_t n_kv, uint32_t hd, float eps,
-                                  float theta_scale, float scale, uint32_t max_seq, uint32_t rows, uint32_t *d_status,
-                                  cudaStream_t stream);
+constexpr uint32_t ATT_MAX_HD = 512;
+enum { ATT_ROPE_NONE = 0, ATT_ROPE_CHAIN = 1, ATT_ROPE_POW = 2 };
+struct AttnArgs {
+    float *q;
+    const float *k, *v;            // v = the raw k vector on a layer that shares K and V
+    const float *q_norm, *k_norm;  // [hd] each, null = no QK-norm
+    const float *freq;             // [hd / 2] frequency factors of ATT_ROPE_POW, or null
+    void *kc, *vc;                 // [max_seq][n_kv * hd] of float, or of f16 when kv_f16
+    float *part, *attn;
+    const uint32_t *pos;
+    uint32_t n_heads, n_kv, hd, max_seq, rows;
+    uint32_t window;        // 0 = attend to every cached row; else to the last `window` rows
+    uint32_t kv_f16, norm_v, rope, rope_adjacent;
+    float eps, theta_scale /* ATT_ROPE_CHAIN */, theta /* ATT_ROPE_POW */, scale;
+    uint32_t *status;
+};
+cudaError_t launch_attention_step(const AttnArgs &A, cudaStream_t stream);
+// h[r] = (h[r] + rmsnorm(x[r]) * w) * out_scale for `rows` vectors of `dim`
+cudaError_t launch_addnorm(float *d_h, const float *d_x, const float *d_w, uint32_t dim, float eps, float out_scale,
+                           uint32_t rows, cudaStream_t stream);
+// x = cap * tanh(x / cap)
+cudaError_t launch_softcap(float *d_x, size_t n, float cap, cudaStream_t stream);
+void f32_to_f16_ref(const float *src, unsigned short *dst, size_t n);
 
 }  // namespace strix

@@ -143,11 +143,11 @@ def test_decode_step_with_real_attention(pkg, orc, synth, qk_norm):
                     acc.upload_f32("blk.%d.%s" % (il, nn), W["blk.%d.%s" % (il, nn)])
         kw = dict(eps=eps, act=pkg.ACT_F32, attn_standin_q=False, head_dim=hd, n_kv=n_kv, rope_theta=base,
                   max_seq=max_seq, qk_norm=qk_norm)
-        # declined: sliding-window layer, shared K = V, GPT-J style rope, a head size that does not match the weights
-        assert acc.configure_decode(hidden, n_heads, ffn, vocab, n_layers, layer_overrides={1: {"is_local": 1}}, **kw) is False
-        assert acc.configure_decode(hidden, n_heads, ffn, vocab, n_layers, layer_overrides={0: {"k_eq_v": 1}}, **kw) is False
-        assert acc.configure_decode(hidden, n_heads, ffn, vocab, n_layers, layer_overrides={0: {"rope_norm": 1}}, **kw) is False
+        # declined: a head size that does not match the weights, one beyond the kernels' limit, heads that do not group
         assert acc.configure_decode(hidden, n_heads, ffn, vocab, n_layers, **dict(kw, head_dim=32)) is False
+        assert acc.configure_decode(hidden, n_heads, ffn, vocab, n_layers, layer_overrides={1: {"head_dim": 516}}, **kw) is False
+        assert acc.configure_decode(hidden, n_heads, ffn, vocab, n_layers, layer_overrides={0: {"n_kv": 4}}, **kw) is False
+        assert acc.configure_decode(hidden, n_heads, ffn, vocab, n_layers, layer_overrides={0: {"rope_theta": 0.0}}, **kw) is False
         assert acc.configure_decode(hidden, n_heads, ffn, vocab, n_layers, **kw)
         kc, vc = [[] for _ in range(n_layers)], [[] for _ in range(n_layers)]
         worst = 0.0
@@ -436,5 +436,241 @@ def test_decode_chain_config3_full_size(pkg, orc, synth, int8):
             r1 = rel_l2(g1, w1)
             print("   %s on the CPU's input: rel-L2 %.2e max-abs %.2e" % (name, r1, np.abs(g1 - w1).max()))
             assert r1 <= REL_L2_TOL
+    finally:
+        acc.close()
+
+
+def build_model_flavour(acc, synth, hidden, n_heads, layers, ffn, vocab, seed, post_norm=False, qk_norm=False, freq_hd=0):
+    """A random-init Q4_0 model with per-layer head sizes; layers: dicts with head_dim, n_kv, k_eq_v (no V weight then)."""
+    W = {}
+
+    def up(name, ty, n, k):
+        w = synth.quant(ty, seed, name, n, k)
+        ok = {synth.Q4_0: acc.upload_q4_0, synth.Q6_K: acc.upload_q6_k}[ty](name, w, k, n)
+        assert ok, name
+        W[name] = (w, ty, k, n)
+
+    def f32(name, n, lo=None):
+        W[name] = synth.norm_weight(seed, name, n) if lo is None else lo
+        acc.upload_f32(name, W[name])
+
+    for il, lc in enumerate(layers):
+        b, hd = "blk.%d." % il, lc["head_dim"]
+        up(b + "attn_q.weight", synth.Q4_0, n_heads * hd, hidden)
+        up(b + "attn_k.weight", synth.Q4_0, lc["n_kv"] * hd, hidden)
+        if not lc.get("k_eq_v"):
+            up(b + "attn_v.weight", synth.Q4_0, lc["n_kv"] * hd, hidden)
+        up(b + "attn_output.weight", synth.Q4_0, hidden, n_heads * hd)
+        up(b + "ffn_gate.weight", synth.Q4_0, ffn, hidden)
+        up(b + "ffn_up.weight", synth.Q4_0, ffn, hidden)
+        up(b + "ffn_down.weight", synth.Q4_0, hidden, ffn)
+        for nn in ("attn_norm.weight", "ffn_norm.weight"):
+            f32(b + nn, hidden)
+        if post_norm:
+            for nn in ("post_attention_norm.weight", "post_ffw_norm.weight"):
+                f32(b + nn, hidden)
+        if qk_norm:
+            for nn in ("attn_q_norm.weight", "attn_k_norm.weight"):
+                f32(b + nn, hd)
+    up("output.weight", synth.Q6_K, vocab, hidden)
+    f32("output_norm.weight", hidden)
+    if freq_hd:
+        # proportional-rope frequency factors of the global layers (gemma.rs:367, 819-829): > 0, around 1 .. 8
+        f32("rope_freqs.weight", freq_hd // 2, (1.0 + 7.0 * np.linspace(0.0, 1.0, freq_hd // 2) ** 2).astype(np.float32))
+    return W
+
+
+def oracle_chain_flavour(orc, W, h0, layers, eps, kc, vc, pos, n_heads, cfg, int8=False):
+    """One token of smollm3.rs:557-680 / gemma.rs:772-925 over the oracle's pieces. cfg: post_norm, act_gelu, norm_v,
+    attn_rsqrt, n_swa, final_softcap, kv_f16, qk_norm; layers: the GpuLayerCfg fields per layer. Returns RAW logits
+    (the caller applies the soft-cap where it wants it)."""
+    def mm(name, x):
+        w, ty, k, n = W[name]
+        if int8:
+            xq, xd, _ = orc.xquant8(x)
+            return orc.idot_gemm(w, ty, xq, xd, 1, k, n)[0]
+        return orc.qmatmul(x, w, ty, k, n)
+
+    h = h0.astype(np.float32).copy()
+    for il, lc in enumerate(layers):
+        b, hd = "blk.%d." % il, lc["head_dim"]
+        n_ = orc.rmsnorm(h, W[b + "attn_norm.weight"], eps)
+        q, k = mm(b + "attn_q.weight", n_), mm(b + "attn_k.weight", n_)
+        v = None if lc.get("k_eq_v") else mm(b + "attn_v.weight", n_)
+        if lc.get("no_rope"):
+            rope = None
+        elif cfg.get("post_norm"):
+            rope = ("pow", lc["rope_theta"], None if lc.get("is_local") else W.get("rope_freqs.weight"))
+        else:
+            rope = ("chain", lc["rope_theta"])
+        a = orc.attention_token_flavour(
+            q, k, v, W.get(b + "attn_q_norm.weight") if cfg.get("qk_norm") else None,
+            W.get(b + "attn_k_norm.weight") if cfg.get("qk_norm") else None, pos, kc[il], vc[il], n_heads, lc["n_kv"], hd, eps,
+            rope, adjacent=bool(lc.get("rope_norm")), norm_v=bool(cfg.get("norm_v")),
+            window=cfg.get("n_swa", 0) if lc.get("is_local") else 0,
+            scale=None if cfg.get("attn_rsqrt", True) else 1.0, kv_f16=bool(cfg.get("kv_f16")))
+        o = mm(b + "attn_output.weight", a)
+        if cfg.get("post_norm"):
+            h = orc.addnorm(h, o, W[b + "post_attention_norm.weight"], eps)
+        else:
+            h = (h + o).astype(np.float32)
+        n_ = orc.rmsnorm(h, W[b + "ffn_norm.weight"], eps)
+        g, u = mm(b + "ffn_gate.weight", n_), mm(b + "ffn_up.weight", n_)
+        dn = mm(b + "ffn_down.weight", orc.geglu(g, u) if cfg.get("act_gelu") else orc.swiglu(g, u))
+        if cfg.get("post_norm"):
+            h = orc.addnorm(h, dn, W[b + "post_ffw_norm.weight"], eps, lc.get("output_scale", 1.0))
+        else:
+            h = (h + dn).astype(np.float32)
+    return mm("output.weight", orc.rmsnorm(h, W["output_norm.weight"], eps))
+
+
+def test_decode_step_smollm3_flavour(pkg, orc, synth):
+    """smollm3.rs:557-680: no QK-norm, adjacent-pair rope (the Llama-permuted layout), every second layer without rope."""
+    hidden, hd, n_heads, n_kv, ffn, vocab, eps, base, max_seq = 256, 64, 4, 2, 512, 800, 1e-6, 5e6, 160
+    layers = [dict(head_dim=hd, n_kv=n_kv, rope_theta=base, rope_norm=1, no_rope=int(il % 2 == 1)) for il in range(2)]
+    acc = pkg.CudaWeightAccel(0)
+    try:
+        W = build_model_flavour(acc, synth, hidden, n_heads, layers, ffn, vocab, seed=301)
+        assert acc.configure_decode(hidden, n_heads, ffn, vocab, 2, eps=eps, act=pkg.ACT_F32, attn_standin_q=False,
+                                    max_seq=max_seq, qk_norm=False, layers=layers)
+        kc, vc = [[], []], [[], []]
+        worst = 0.0
+        for pos in range(131):
+            h0 = synth.normal(302, "h.%d" % pos, hidden)
+            got = acc.decode_step(h0, pos)
+            want = oracle_chain_flavour(orc, W, h0, layers, eps, kc, vc, pos, n_heads, dict(qk_norm=False))
+            if pos < 3 or pos in (63, 64, 65, 130):
+                r = rel_l2(got, want)
+                worst = max(worst, r)
+                assert r <= REL_L2_TOL, (pos, r)
+        print("smollm3 flavour: worst rel-L2 %.2e" % worst)
+        assert acc.device_status() == 0
+    finally:
+        acc.close()
+
+
+GEMMA_LAYERS = [
+    # local layer: its own head size, sliding window, rope base 1e4, no frequency factors
+    dict(head_dim=64, n_kv=2, k_eq_v=0, rope_theta=1e4, is_local=1, output_scale=0.75),
+    # global layer: wider heads, one KV head shared by all, V = raw K, rope base 1e6 with frequency factors
+    dict(head_dim=128, n_kv=1, k_eq_v=1, rope_theta=1e6, is_local=0, output_scale=1.25),
+    dict(head_dim=64, n_kv=2, k_eq_v=0, rope_theta=1e4, is_local=1, output_scale=0.9),
+]
+GEMMA_CFG = dict(post_norm=True, act_gelu=True, norm_v=True, attn_rsqrt=False, n_swa=40, final_softcap=30.0, qk_norm=True)
+
+
+def gemma_configure(pkg, acc, hidden, n_heads, ffn, vocab, eps, max_seq, act, cfg=GEMMA_CFG):
+    return acc.configure_decode(hidden, n_heads, ffn, vocab, len(GEMMA_LAYERS), eps=eps, act=act, attn_standin_q=False,
+                                max_seq=max_seq, qk_norm=True, layers=GEMMA_LAYERS, post_norm=True, act_gelu=True,
+                                norm_v=cfg["norm_v"], attn_rsqrt=cfg["attn_rsqrt"], n_swa=cfg["n_swa"],
+                                final_softcap=cfg["final_softcap"])
+
+
+@pytest.mark.parametrize("kv_f16", [False, True])
+def test_decode_step_gemma_flavour(pkg, orc, synth, kv_f16):
+    """gemma.rs:772-925: per-layer head sizes, shared K = V on the global layer, weightless V-norm, QK-norm, rope with
+    frequency factors on the global layer, a sliding window of 40 rows on the local layers (positions run past it and
+    past a softmax split), scale 1.0, GeGLU, sandwich post-norms with per-layer output scales, final soft-cap.
+    kv_f16: the cache keeps f16 rows rounded as the reference's cache stores round (kernels.rs:18-35)."""
+    hidden, n_heads, ffn, vocab, eps, max_seq = 256, 4, 512, 900, 1e-6, 128
+    cfg = dict(GEMMA_CFG, kv_f16=kv_f16)
+    acc = pkg.CudaWeightAccel(0)
+    try:
+        assert acc.set_option("kv_f16", int(kv_f16))
+        W = build_model_flavour(acc, synth, hidden, n_heads, GEMMA_LAYERS, ffn, vocab, seed=311, post_norm=True, qk_norm=True,
+                                freq_hd=128)
+        assert gemma_configure(pkg, acc, hidden, n_heads, ffn, vocab, eps, max_seq, pkg.ACT_F32)
+        kc, vc = [[] for _ in GEMMA_LAYERS], [[] for _ in GEMMA_LAYERS]
+        worst = 0.0
+        for pos in range(100):
+            h0 = synth.normal(312, "h.%d" % pos, hidden)
+            got = acc.decode_step(h0, pos)
+            raw = oracle_chain_flavour(orc, W, h0, GEMMA_LAYERS, eps, kc, vc, pos, n_heads, cfg)
+            if pos < 3 or pos in (39, 40, 41, 63, 64, 65, 99):
+                want = orc.softcap(raw, cfg["final_softcap"])
+                r = rel_l2(got, want)
+                worst = max(worst, r)
+                # f16 rows: a GPU value one f32 ulp from the oracle's can round to the neighbouring f16 code
+                assert r <= (3e-3 if kv_f16 else REL_L2_TOL), (pos, r)
+                assert np.abs(got).max() <= cfg["final_softcap"]
+        print("gemma flavour kv_f16=%s: worst rel-L2 %.2e" % (kv_f16, worst))
+        # the greedy entry point skips the soft-cap (monotone): same winner
+        h0 = synth.normal(312, "h.99", hidden)
+        assert acc.decode_step_argmax(h0, 99) == orc.argmax_f32(got)
+        assert acc.device_status() == 0
+    finally:
+        acc.close()
+
+
+@pytest.mark.parametrize("kv_f16", [False, True])
+def test_prefill_verify_gemma_flavour_and_seeded_f16_cache(pkg, orc, synth, kv_f16):
+    """The batched rows (prefill / verify) of the Gemma flavour against token-at-a-time oracle steps, with the
+    integer-dot projections; then a cache seeded from outside (f32 rows in, rounded to f16 by the library when the
+    cache is f16) continues like the one decoding built."""
+    hidden, n_heads, ffn, vocab, eps, max_seq = 256, 4, 512, 900, 1e-6, 64
+    cfg = dict(GEMMA_CFG, n_swa=6, kv_f16=kv_f16)
+    acc = pkg.CudaWeightAccel(0)
+    try:
+        assert acc.set_option("kv_f16", int(kv_f16))
+        W = build_model_flavour(acc, synth, hidden, n_heads, GEMMA_LAYERS, ffn, vocab, seed=321, post_norm=True, qk_norm=True,
+                                freq_hd=128)
+        assert gemma_configure(pkg, acc, hidden, n_heads, ffn, vocab, eps, max_seq, pkg.ACT_Q8DOT, cfg)
+        hs = synth.normal(322, "hs", 14 * hidden).reshape(14, hidden)
+        kc, vc = [[] for _ in GEMMA_LAYERS], [[] for _ in GEMMA_LAYERS]
+        want = [orc.softcap(oracle_chain_flavour(orc, W, hs[t], GEMMA_LAYERS, eps, kc, vc, t, n_heads, cfg, int8=True), 30.0)
+                for t in range(14)]
+        # re-quantisation noise along an integer-dot chain of 13 quantisers (a code that flips moves a value by 1/127
+        # of its block's amax; with f16 rows a flip of a cache code adds to it); the flavours themselves are held to
+        # 1e-3 with f32 activations in test_decode_step_gemma_flavour
+        tol = 8e-2
+        assert rel_l2(acc.prefill(hs[:5], 0, 5), want[4]) <= tol
+        gv = acc.verify(hs[5:12], 5, 7)                    # rows 5..11 run past the window of 6
+        for t in range(7):
+            assert rel_l2(gv[t], want[5 + t]) <= tol, t
+        assert rel_l2(acc.decode_step(hs[12], 12), want[12]) <= tol
+        from strix_rs_b200 import spec
+        ids = spec.verify_argmax(acc, hs[5:12], 5, 7)
+        assert list(ids) == [orc.argmax_f32(gv[t]) for t in range(7)]
+        # a cache seeded from outside continues identically
+        assert gemma_configure(pkg, acc, hidden, n_heads, ffn, vocab, eps, max_seq, pkg.ACT_Q8DOT, cfg)
+        for il in range(len(GEMMA_LAYERS)):
+            assert acc.seed_decode_kv(il, np.stack(kc[il][:13]), np.stack(vc[il][:13]))
+        assert rel_l2(acc.decode_step(hs[13], 13), want[13]) <= tol
+        assert acc.device_status() == 0
+    finally:
+        acc.close()
+
+
+def test_post_norm_chain_with_the_attention_standin(pkg, orc, synth):
+    """The sandwich post-norm residuals on the projection chain alone (stand-in attention): launch path, f32."""
+    hidden, qdim, kvdim, ffn, vocab, n_layers, eps = 512, 768, 256, 1536, 1100, 2, 1e-6
+    acc = pkg.CudaWeightAccel(0)
+    try:
+        W = build_model(acc, synth, hidden, qdim, kvdim, ffn, vocab, n_layers, seed=331)
+        for il in range(n_layers):
+            for nn in ("post_attention_norm.weight", "post_ffw_norm.weight"):
+                W["blk.%d.%s" % (il, nn)] = synth.norm_weight(331, "blk.%d.%s" % (il, nn), hidden)
+                acc.upload_f32("blk.%d.%s" % (il, nn), W["blk.%d.%s" % (il, nn)])
+        scales = [0.5, 1.5]
+        assert acc.configure_decode(hidden, qdim // 128, ffn, vocab, n_layers, eps=eps, act=pkg.ACT_F32, post_norm=True,
+                                    final_softcap=20.0, layers=[dict(output_scale=s) for s in scales])
+        h0 = synth.normal(332, "h0", hidden)
+
+        def mm(name, x):
+            w, ty, k, n = W[name]
+            return orc.qmatmul(x, w, ty, k, n)
+        h = h0.copy()
+        for il in range(n_layers):
+            b = "blk.%d." % il
+            n_ = orc.rmsnorm(h, W[b + "attn_norm.weight"], eps)
+            q = mm(b + "attn_q.weight", n_)
+            h = orc.addnorm(h, mm(b + "attn_output.weight", q), W[b + "post_attention_norm.weight"], eps)
+            n_ = orc.rmsnorm(h, W[b + "ffn_norm.weight"], eps)
+            a = orc.swiglu(mm(b + "ffn_gate.weight", n_), mm(b + "ffn_up.weight", n_))
+            h = orc.addnorm(h, mm(b + "ffn_down.weight", a), W[b + "post_ffw_norm.weight"], eps, scales[il])
+        want = orc.softcap(mm("output.weight", orc.rmsnorm(h, W["output_norm.weight"], eps)), 20.0)
+        assert rel_l2(acc.decode_step(h0, 0), want) <= REL_L2_TOL
+        gv = acc.verify(np.stack([h0, h0]), 0, 2)
+        assert rel_l2(gv[1], want) <= REL_L2_TOL
     finally:
         acc.close()

@@ -295,3 +295,72 @@ def test_attention_pieces_known_answers(orc):
     s = np.array([q @ np.array([1.0, 0.0]), 0.0]) / np.sqrt(2.0)
     w = np.exp(s - s.max()); w /= w.sum()
     np.testing.assert_allclose(a1, w[0] * np.array([5.0, 7.0]) + w[1] * np.array([1.0, 1.0]), rtol=1e-5)
+
+
+def test_attention_flavour_known_answers(orc):
+    """The known answers of the reference's own unit tests for these pieces (crates/strix-backend-cpu/src/ops.rs
+    tests: rope at position 0, first-pair rotation, norm preservation, softcap bounds; attention.rs tests: a single
+    position returns its value, equal scores average, a dominant key dominates, convexity), against the oracle."""
+    # ops.rs rope_at_position_zero_is_identity / rope_rotates_first_pair_as_expected / rope_preserves_norm
+    v = np.array([0.5, -1.0, 2.0, 0.25], dtype=np.float32)
+    np.testing.assert_allclose(orc.rope_pow(v, 0, 10000.0), v, atol=1e-6)
+    r = orc.rope_pow(np.array([1.0, 0.0], np.float32), 1, 10000.0)
+    np.testing.assert_allclose(r, [np.cos(np.float32(1.0)), np.sin(np.float32(1.0))], atol=1e-6)
+    v6 = np.array([0.3, 0.7, -1.2, 2.5, 0.1, -0.6], dtype=np.float32)
+    for rot in (orc.rope_pow(v6, 7, 10000.0), orc.rope_adjacent(v6, 7, 6, 10000.0), orc.rope_neox(v6, 7, 6, 10000.0)):
+        assert abs(float((rot * rot).sum()) - float((v6 * v6).sum())) < 1e-4
+    # frequency factors divide the inverse frequency (ops.rs:166-168): a factor of 2 on pair 0 halves its angle
+    r2 = orc.rope_pow(np.array([1.0, 0.0], np.float32), 1, 10000.0, np.array([2.0], np.float32))
+    np.testing.assert_allclose(r2, [np.cos(0.5), np.sin(0.5)], atol=1e-6)
+    # adjacent pairs (smollm3.rs:126-138): hd = 4 at pos 1: pair 0 = (x0, x1) by angle 1, pair 1 = (x2, x3) by base^(-1/2)
+    ra = orc.rope_adjacent(np.array([1.0, 0.0, 1.0, 0.0], np.float32), 1, 4, 10000.0)
+    np.testing.assert_allclose(ra, [np.cos(1.0), np.sin(1.0), np.cos(0.01), np.sin(0.01)], atol=1e-6)
+    # ops.rs softcap_bounds_and_is_near_identity_for_small
+    x = orc.softcap(np.array([1000.0, -1000.0, 0.5], np.float32), 30.0)
+    assert 29.0 < x[0] <= 30.0 and -30.0 <= x[1] < -29.0
+    assert abs(x[2] - 30.0 * np.tanh(np.float32(0.5) / np.float32(30.0))) < 1e-6
+    np.testing.assert_array_equal(orc.softcap(np.array([3.0], np.float32), 0.0), [3.0])
+    # attention.rs single_position_returns_that_value / equal_scores_average_values / dominant_key / convexity,
+    # through the flavour entry point (no norm, no rope, one head)
+    def attend(q, keys, values, hd, scale):
+        kc, vc, out = [], [], None
+        n = len(keys) // hd
+        for t in range(n):
+            out = orc.attention_token_flavour(q, keys[t * hd:(t + 1) * hd], values[t * hd:(t + 1) * hd], None, None, t,
+                                              kc, vc, 1, 1, hd, 0.0, None, scale=scale)
+        return out
+    np.testing.assert_allclose(attend([0.3, -0.7], [1.0, 2.0], [5.0, -9.0], 2, 1 / np.sqrt(2.0)), [5.0, -9.0], atol=1e-6)
+    np.testing.assert_allclose(attend([1.0, 1.0], [0.5] * 4, [2.0, 4.0, 6.0, 8.0], 2, 1 / np.sqrt(2.0)), [4.0, 6.0], atol=1e-6)
+    np.testing.assert_allclose(attend([10.0, 0.0], [10.0, 0.0, -10.0, 0.0], [1.0, 1.0, 99.0, 99.0], 2, 1 / np.sqrt(2.0)),
+                               [1.0, 1.0], atol=1e-3)
+    o = attend([0.4], [0.1, 0.9, -0.3], [3.0, 7.0, 5.0], 1, 1.0)
+    assert 3.0 - 1e-6 <= o[0] <= 7.0 + 1e-6
+    # the sliding window (gemma.rs:840-851): with window 2 the third token no longer sees the first
+    kc, vc = [], []
+    for t, (k, val) in enumerate([([9.0], [100.0]), ([0.0], [1.0]), ([0.0], [3.0])]):
+        o = orc.attention_token_flavour([1.0], k, val, None, None, t, kc, vc, 1, 1, 1, 0.0, None, window=2, scale=1.0)
+    np.testing.assert_allclose(o, [2.0], atol=1e-6)
+    # shared K = V takes the RAW k as value, before the K-norm (gemma.rs:796-803); V-norm has no weight (gemma.rs:804-813)
+    o = orc.attention_token_flavour([1.0, 0.0], [3.0, 4.0], None, None, np.array([2.0, 2.0], np.float32), 0, [], [], 1, 1, 2,
+                                    0.0, None, scale=1.0)
+    np.testing.assert_allclose(o, [3.0, 4.0], atol=1e-6)
+    o = orc.attention_token_flavour([1.0, 0.0], [3.0, 4.0], None, None, None, 0, [], [], 1, 1, 2, 0.0, None, norm_v=True, scale=1.0)
+    np.testing.assert_allclose(o, np.array([3.0, 4.0]) / np.sqrt(12.5), rtol=1e-6)
+    # sandwich residual (gemma.rs:268-275, 876-879, 896-906)
+    np.testing.assert_allclose(orc.addnorm([1.0, 1.0], [3.0, 4.0], [1.0, 2.0], 0.0, 0.5),
+                               0.5 * (1.0 + np.array([3.0, 8.0]) / np.sqrt(12.5)), rtol=1e-6)
+
+
+def test_f16_cache_rounding_follows_the_reference_kernel(orc):
+    """kernels.rs:18-32 f2h: to nearest, a tie away from zero (numpy rounds a tie to even); overflow -> infinity;
+    below half the smallest subnormal -> zero; kernels.rs:8-16 h2f is exact."""
+    x = np.array([1.0, 1.0 + 2.0 ** -11, 1.0 + 3 * 2.0 ** -11, -1.0 - 2.0 ** -11, 65519.0, 65520.0, 1e9, 2.0 ** -24,
+                  2.0 ** -25, 2.0 ** -26, 2.0 ** -15 + 2.0 ** -25, 0.0, -0.0], dtype=np.float32)
+    want = [0x3C00, 0x3C01, 0x3C02, 0xBC01, 0x7BFF, 0x7C00, 0x7C00, 0x0001, 0x0001, 0x0000, 0x0201, 0x0000, 0x8000]
+    np.testing.assert_array_equal(orc.f32_to_f16_cache(x), np.array(want, dtype=np.uint16))
+    # away from ties it is the IEEE conversion
+    r = np.random.default_rng(5).standard_normal(50000).astype(np.float32)
+    h = orc.f32_to_f16_cache(r)
+    ties = (r.view(np.uint32) & 0x1FFF) == 0x1000
+    np.testing.assert_array_equal(h[~ties], r.astype(np.float16).view(np.uint16)[~ties])
+    np.testing.assert_array_equal(orc.f16_cache_to_f32(h), h.view(np.float16).astype(np.float32))
