@@ -202,6 +202,44 @@ STRIX_API int strix_cuda_prefill_q8_gemm_noalloc(strix_cuda *h, const char *key,
                                        float *d_y, void *stream);
 STRIX_API size_t strix_cuda_noalloc_scratch_bytes(void);
 
+/* WeightAccel::upload_moe_q8 / upload_moe_q6 (accel.rs:167-196; decode.rs:2717-2831): adopt a whole
+ * mixture-of-experts layer: gate and up hold ne experts of [eff][hidden] raw GGUF blocks back to back, down ne
+ * experts of [hidden][eff] (Q8_0 34-byte blocks / Q6_K 210-byte super-blocks). 1 = adopted, 0 = declined as the
+ * reference declines (hidden or eff not whole blocks or above 4096, a length that does not match) or on a
+ * row-sharded handle, <0 = error. The experts of a projection become one resident stack that the GEMV kernel
+ * indexes by expert id. */
+STRIX_API int strix_cuda_upload_moe_q8(strix_cuda *h, size_t layer, const uint8_t *gate, size_t gate_len, const uint8_t *up,
+                             size_t up_len, const uint8_t *down, size_t down_len, size_t hidden, size_t eff, size_t ne);
+STRIX_API int strix_cuda_upload_moe_q6(strix_cuda *h, size_t layer, const uint8_t *gate, size_t gate_len, const uint8_t *up,
+                             size_t up_len, const uint8_t *down, size_t down_len, size_t hidden, size_t eff, size_t ne);
+/* WeightAccel::moe_ffn (accel.rs:198-211; decode.rs:2833-2870): y[hidden] = sum_i wexp[i] *
+ * down_{ids[i]}(silu(gate_{ids[i]} x) * up_{ids[i]} x) over the k <= 16 routed experts of one token, in the order
+ * given, plus sgate * the shared expert (blk.<layer>.ffn_{gate,up,down}_shexp.weight, resident through the usual
+ * uploads) when sgate != 0. act: STRIX_ACT_F32 (the reference's default kernels) or STRIX_ACT_Q8DOT (its
+ * integer-dot kernels, q8i_moe_*). 1 = done, 0 = None in the reference (layer not adopted, a length mismatch,
+ * k = 0 or > 16, an id outside [0, ne), a shared expert asked for but not resident), <0 = error. */
+STRIX_API int strix_cuda_moe_ffn(strix_cuda *h, size_t layer, const int *ids, const float *wexp, size_t k, const float *x,
+                       size_t x_len, float sgate, int act, float *y, size_t y_cap);
+/* The same with ids, weights, x and y on the device, enqueued on `stream`, no synchronisation (the router's top-k
+ * can stay on the device: strix_cuda_topk_router_dev). An id outside [0, ne) is clamped into the range. */
+STRIX_API int strix_cuda_moe_ffn_dev(strix_cuda *h, size_t layer, const int *d_ids, const float *d_wexp, size_t k,
+                           const float *d_x, float sgate, int act, float *d_y, void *stream);
+/* WeightAccel::moe_expert_ffn (accel.rs:220-223; decode.rs:3299-3356): m grouped tokens xs[m][hidden] through
+ * expert e: y[m][hidden] = down_e(silu(gate_e xs) * up_e xs), the weights read once per 8 tokens. */
+STRIX_API int strix_cuda_moe_expert_ffn(strix_cuda *h, size_t layer, size_t e, const float *xs, size_t m, int act, float *y,
+                              size_t y_cap);
+/* WeightAccel::moe_layer_ffn (accel.rs:236-246; decode.rs:3552-3630): plan[n_plan] pairs (expert id, row count);
+ * xs[rows][hidden] gathered expert-major in plan order; y[rows][hidden] the experts' outputs in the same order.
+ * 0 = None (unknown layer, an id out of range, counts that do not add up to rows). */
+STRIX_API int strix_cuda_moe_layer_ffn(strix_cuda *h, size_t layer, const int *plan, size_t n_plan, const float *xs, size_t rows,
+                             int act, float *y, size_t y_cap);
+/* The router's top-k (mellum.rs:1590-1609; the reference's topk_router kernel, kernels.rs:1846-1873): softmax over
+ * logits[ne <= 128], the k <= 16 most probable experts (a tie goes to the lower index), weights = their
+ * probabilities divided by the sum of the chosen ones. 0 = sizes out of range. */
+STRIX_API int strix_cuda_topk_router(strix_cuda *h, const float *logits, size_t ne, size_t k, int *ids, float *w);
+STRIX_API int strix_cuda_topk_router_dev(strix_cuda *h, const float *d_logits, size_t ne, size_t k, int *d_ids, float *d_w,
+                               void *stream);
+
 /* Plain-data mirror of GpuLayerCfg / GpuDecodeConfig (crates/strix-core/src/accel.rs:19-72). */
 typedef struct strix_gpu_layer_cfg {
     uint32_t head_dim, n_kv;

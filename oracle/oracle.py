@@ -366,3 +366,54 @@ def attention_token_flavour(q, k, v, q_norm, k_norm, pos, kc, vc, n_heads, n_kv,
             o += e[t] * V[t, kvh]
         out[hh * hd:(hh + 1) * hd] = o
     return out
+
+
+# ---- mixture-of-experts FFN (crates/strix-backend-cpu/src/mellum.rs:1582-1663) ----
+def topk_router(logits, k):
+    """mellum.rs:1590-1609: p = exp(l - max) then p /= sum (sequential f32 sum), the k largest by a STABLE
+    descending sort (a tie keeps the lower index first), weights p[e] / (sum of the chosen p, in that order).
+    Returns (ids int32[k], weights f32[k])."""
+    l = _f32(logits)
+    mx = l.max()
+    p = np.exp((l - mx).astype(np.float32)).astype(np.float32)
+    s = np.float32(0.0)
+    for v in p:
+        s = np.float32(s + v)
+    p = (p / s).astype(np.float32)
+    idx = sorted(range(p.size), key=lambda e: -float(p[e]))[:k]      # python's sort is stable
+    ws = np.float32(0.0)
+    for e in idx:
+        ws = np.float32(ws + p[e])
+    return np.array(idx, dtype=np.int32), np.array([p[e] / ws for e in idx], dtype=np.float32)
+
+
+def moe_expert_bytes(ty, hidden, eff):
+    """Bytes of one expert's gate (= up) matrix and of its down matrix (mellum.rs:1620-1622)."""
+    be, bb = BLOCK_ELEMS[ty], BLOCK_BYTES[ty]
+    return (hidden // be) * bb * eff, (eff // be) * bb * hidden
+
+
+def moe_expert_ffn(x, gate, up, down, ty, hidden, eff, e, int8=False):
+    """mellum.rs:1629-1654 for expert e and one token: down_e(silu(gate_e x) * up_e x); the expert's blocks are the
+    e-th slice of the layer's tensors. int8: activations through the per-32 int8 quantiser before each matmul
+    (the reference's q8i_moe_* kernels)."""
+    gb, db = moe_expert_bytes(ty, hidden, eff)
+
+    def mm(data, xv, k, n):
+        if int8:
+            xq, xd, _ = xquant8(xv)
+            return idot_gemm(data, ty, xq, xd, 1, k, n)[0]
+        return qmatmul(xv, data, ty, k, n)
+
+    g = mm(_u8(gate)[e * gb:(e + 1) * gb], x, hidden, eff)
+    u = mm(_u8(up)[e * gb:(e + 1) * gb], x, hidden, eff)
+    return mm(_u8(down)[e * db:(e + 1) * db], swiglu(g, u), eff, hidden)
+
+
+def moe_ffn(x, gate, up, down, ty, hidden, eff, ids, wexp, int8=False):
+    """mellum.rs:1624-1660: out += wexp[i] * expert_{ids[i]}(x), in the order given, multiply then add in f32."""
+    out = np.zeros(hidden, dtype=np.float32)
+    for e, w in zip(ids, _f32(wexp)):
+        dy = moe_expert_ffn(x, gate, up, down, ty, hidden, eff, int(e), int8)
+        out = (out + (np.float32(w) * dy).astype(np.float32)).astype(np.float32)
+    return out

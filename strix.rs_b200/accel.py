@@ -114,6 +114,15 @@ def load_library():
     sig("strix_cuda_fold_argmax_shards", None, sz, sz, C.POINTER(C.c_uint32), f32p, C.POINTER(C.c_uint32), f32p)
     sig("strix_cuda_prefill_q4_gemm", C.c_int, H, C.c_char_p, f32p, sz, f32p, sz)
     sig("strix_cuda_prefill_q4_gemm_dev", C.c_int, H, C.c_char_p, C.c_void_p, sz, C.c_void_p, C.c_void_p)
+    i32p = C.POINTER(C.c_int32)
+    for nm in ("strix_cuda_upload_moe_q8", "strix_cuda_upload_moe_q6"):
+        sig(nm, C.c_int, H, sz, u8p, sz, u8p, sz, u8p, sz, sz, sz, sz)
+    sig("strix_cuda_moe_ffn", C.c_int, H, sz, i32p, f32p, sz, f32p, sz, C.c_float, C.c_int, f32p, sz)
+    sig("strix_cuda_moe_ffn_dev", C.c_int, H, sz, C.c_void_p, C.c_void_p, sz, C.c_void_p, C.c_float, C.c_int, C.c_void_p, C.c_void_p)
+    sig("strix_cuda_moe_expert_ffn", C.c_int, H, sz, sz, f32p, sz, C.c_int, f32p, sz)
+    sig("strix_cuda_moe_layer_ffn", C.c_int, H, sz, i32p, sz, f32p, sz, C.c_int, f32p, sz)
+    sig("strix_cuda_topk_router", C.c_int, H, f32p, sz, sz, i32p, f32p)
+    sig("strix_cuda_topk_router_dev", C.c_int, H, C.c_void_p, sz, sz, C.c_void_p, C.c_void_p, C.c_void_p)
     sig("strix_cuda_debug_gemm_isums", C.c_int, H, C.c_char_p, f32p, sz, C.c_uint32, C.POINTER(C.c_int32), sz)
     sig("strix_cuda_debug_gemm_mode_dev", C.c_int, H, C.c_char_p, C.c_void_p, sz, C.c_void_p, C.c_int, C.c_int, C.c_void_p)
     sig("strix_cuda_decode_exchange_info", C.c_int, H, C.POINTER(C.c_void_p), szp)
@@ -295,6 +304,68 @@ class CudaWeightAccel:
         y = np.empty((m, info["rows"]), dtype=np.float32)
         rc = self._check(self._L.strix_cuda_prefill_q4_gemm(self._h, key.encode(), _fp(xa), m, _fp(y), y.size))
         return y if rc == 1 else None
+
+    # ---- mixture-of-experts layers (accel.rs:167-246) ----
+    def _upload_moe(self, fn, layer, gate, up, down, hidden, eff, ne):
+        g, u, d = (np.ascontiguousarray(np.frombuffer(b, dtype=np.uint8) if not isinstance(b, np.ndarray) else b.view(np.uint8))
+                   for b in (gate, up, down))
+        u8 = lambda a: a.ctypes.data_as(C.POINTER(C.c_uint8))
+        rc = self._check(fn(self._h, layer, u8(g), g.size, u8(u), u.size, u8(d), d.size, hidden, eff, ne))
+        if rc == 1:
+            self._moe = getattr(self, "_moe", {})
+            self._moe[layer] = (hidden, eff, ne)
+        return rc == 1
+
+    def upload_moe_q8(self, layer, gate, up, down, hidden, eff, ne):
+        """Adopt a layer's experts in native Q8_0 blocks (accel.rs:167-181)."""
+        return self._upload_moe(self._L.strix_cuda_upload_moe_q8, layer, gate, up, down, hidden, eff, ne)
+
+    def upload_moe_q6(self, layer, gate, up, down, hidden, eff, ne):
+        """Adopt a layer's experts in native Q6_K super-blocks (accel.rs:183-196)."""
+        return self._upload_moe(self._L.strix_cuda_upload_moe_q6, layer, gate, up, down, hidden, eff, ne)
+
+    def moe_ffn(self, layer, ids, wexp, x, sgate=0.0, act=ACT_F32):
+        """y[hidden] of one token over its routed experts, or None (accel.rs:198-211)."""
+        dims = getattr(self, "_moe", {}).get(layer)
+        if dims is None:
+            return None
+        ia = np.ascontiguousarray(ids, dtype=np.int32)
+        wa, xa = _f32(wexp), _f32(x)
+        if ia.size != wa.size:
+            return None
+        y = np.empty(dims[0], dtype=np.float32)
+        rc = self._check(self._L.strix_cuda_moe_ffn(self._h, layer, ia.ctypes.data_as(C.POINTER(C.c_int32)), _fp(wa), ia.size,
+                                                     _fp(xa), xa.size, float(sgate), act, _fp(y), y.size))
+        return y if rc == 1 else None
+
+    def moe_expert_ffn(self, layer, e, xs, m, act=ACT_F32):
+        """y[m][hidden]: m grouped tokens through expert e, or None (accel.rs:220-223)."""
+        dims = getattr(self, "_moe", {}).get(layer)
+        xa = _f32(xs)
+        if dims is None or xa.size != m * dims[0] or m == 0:
+            return None
+        y = np.empty((m, dims[0]), dtype=np.float32)
+        rc = self._check(self._L.strix_cuda_moe_expert_ffn(self._h, layer, e, _fp(xa), m, act, _fp(y), y.size))
+        return y if rc == 1 else None
+
+    def moe_layer_ffn(self, layer, plan, xs, rows, act=ACT_F32):
+        """plan: [(expert, row count)]; xs[rows][hidden] gathered expert-major -> y[rows][hidden], or None (accel.rs:236-246)."""
+        dims = getattr(self, "_moe", {}).get(layer)
+        xa = _f32(xs)
+        if dims is None or xa.size != rows * dims[0] or rows == 0:
+            return None
+        pa = np.ascontiguousarray(np.asarray(plan, dtype=np.int32).reshape(-1))
+        y = np.empty((rows, dims[0]), dtype=np.float32)
+        rc = self._check(self._L.strix_cuda_moe_layer_ffn(self._h, layer, pa.ctypes.data_as(C.POINTER(C.c_int32)), pa.size // 2,
+                                                           _fp(xa), rows, act, _fp(y), y.size))
+        return y if rc == 1 else None
+
+    def topk_router(self, logits, k):
+        """(ids[k], weights[k]) of the router's softmax top-k, or None."""
+        la = _f32(logits)
+        ids, w = np.zeros(k, dtype=np.int32), np.zeros(k, dtype=np.float32)
+        rc = self._check(self._L.strix_cuda_topk_router(self._h, _fp(la), la.size, k, ids.ctypes.data_as(C.POINTER(C.c_int32)), _fp(w)))
+        return (ids, w) if rc == 1 else None
 
     def prefill_q8_gemm_dev(self, key, d_xs, m, d_y, stream=0):
         rc = self._check(self._L.strix_cuda_prefill_q8_gemm_dev(self._h, key.encode(), C.c_void_p(int(d_xs)), m,

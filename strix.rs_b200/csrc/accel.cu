@@ -82,8 +82,9 @@ Resident *find_weight_mut(strix_cuda *h, const char *key) {
 
 }  // namespace strix
 
-static int upload_quant(strix_cuda *h, int fmt, const char *key, const uint8_t *bytes, size_t len, size_t in_dim,
-                        size_t out_dim) {
+namespace strix {
+int upload_quant(strix_cuda *h, int fmt, const char *key, const uint8_t *bytes, size_t len, size_t in_dim, size_t out_dim,
+                 bool gemm_copy) {
     if (!h || !key || !bytes) return -1;
     h->err.clear();
     const size_t be = gguf_block_elems(fmt), bb = gguf_block_bytes(fmt);
@@ -110,7 +111,7 @@ static int upload_quant(strix_cuda *h, int fmt, const char *key, const uint8_t *
     }
     r.bytes = (size_t)resident_bytes(r.L, r.rows);
     CU_TRY(h, cudaMalloc(&r.dev, std::max<size_t>(r.bytes, 16)));
-    if (fmt == FMT_Q8_0) {
+    if (fmt == FMT_Q8_0 && gemm_copy) {
         const cudaError_t eg = cudaMalloc(&r.gemm_codes, std::max<size_t>(r.rows * in_dim, 16));
         if (eg != cudaSuccess) {
             cudaFree(r.dev);
@@ -162,6 +163,7 @@ static int upload_quant(strix_cuda *h, int fmt, const char *key, const uint8_t *
     }
     return 1;
 }
+}  // namespace strix
 
 // One GEMV launch over up to 3 resident weights that share the activation.
 namespace strix {
@@ -324,6 +326,9 @@ void strix_cuda_destroy(strix_cuda *h) {
     for (float *p : {h->gm_x.p, h->gm_y.p, h->gm_part.p, h->gm_xd.p, h->gm_xc.p})
         if (p) cudaFree(p);
     if (h->gm_xq) cudaFree(h->gm_xq);
+    for (float *p : {h->moe_g.p, h->moe_u.p, h->moe_dy.p, h->moe_out.p, h->moe_w.p, h->moe_sh.p})
+        if (p) cudaFree(p);
+    if (h->moe_ids) cudaFree(h->moe_ids);
     if (h->am_part) cudaFree(h->am_part);  // one allocation: winners, tickets, ids, values
     if (h->am_pin) cudaFreeHost(h->am_pin);
     if (h->gm_xs) cudaFree(h->gm_xs);
@@ -374,18 +379,18 @@ size_t strix_cuda_resident_count(strix_cuda *h) { return h ? h->weights.size() :
 
 int strix_cuda_upload_q4_0(strix_cuda *h, const char *key, const uint8_t *bytes, size_t len, size_t in_dim,
                            size_t out_dim) {
-    return upload_quant(h, FMT_Q4_0, key, bytes, len, in_dim, out_dim);
+    return upload_quant(h, FMT_Q4_0, key, bytes, len, in_dim, out_dim, true);
 }
 int strix_cuda_upload_q8_0(strix_cuda *h, const char *key, const uint8_t *bytes, size_t len, size_t in_dim,
                            size_t out_dim) {
-    return upload_quant(h, FMT_Q8_0, key, bytes, len, in_dim, out_dim);
+    return upload_quant(h, FMT_Q8_0, key, bytes, len, in_dim, out_dim, true);
 }
 int strix_cuda_upload_q6_k(strix_cuda *h, const char *key, const uint8_t *bytes, size_t len, size_t in_dim,
                            size_t out_dim) {
-    return upload_quant(h, FMT_Q6_K, key, bytes, len, in_dim, out_dim);
+    return upload_quant(h, FMT_Q6_K, key, bytes, len, in_dim, out_dim, true);
 }
 int strix_cuda_upload_q4_1(strix_cuda *h, const char *key, const uint8_t *bytes, size_t len, size_t in_dim, size_t out_dim) {
-    return upload_quant(h, FMT_Q4_1, key, bytes, len, in_dim, out_dim);
+    return upload_quant(h, FMT_Q4_1, key, bytes, len, in_dim, out_dim, true);
 }
 
 int strix_cuda_upload_f32(strix_cuda *h, const char *key, const float *data, size_t n) {

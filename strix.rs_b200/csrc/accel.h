@@ -83,6 +83,15 @@ struct strix_cuda {
     // block code sums, f32 output, split-K partials
     strix::DevBuf gm_x, gm_y, gm_part, gm_xd, gm_xc;
     strix_decode_state *decode = nullptr;  // configured projection chain (decode.cu), or null
+    // mixture-of-experts layers adopted by upload_moe_q8 / upload_moe_q6 (moe.cu): the experts of a projection are one
+    // resident stack "moe.<layer>.gate|up|down" of n_expert * rows-per-expert rows
+    struct MoeLayer {
+        int fmt = 0;
+        uint32_t hidden = 0, eff = 0, n_expert = 0;
+    };
+    std::unordered_map<size_t, MoeLayer> moe;
+    strix::DevBuf moe_g, moe_u, moe_dy, moe_out, moe_w, moe_sh;  // scratch: gate / up rows, down rows, result, weights, shared expert
+    int *moe_ids = nullptr;
     // argmax scratch (argmax.cu), allocated on first use: per-block winners, per-row tickets, results
     void *am_part = nullptr;
     uint32_t *am_ticket = nullptr, *am_idx = nullptr;
@@ -100,6 +109,10 @@ int ensure_f32(strix_cuda *h, DevBuf &b, size_t n);
 int ensure_pinned(strix_cuda *h, PinBuf &b, size_t bytes);
 int ensure_xop(strix_cuda *h, size_t bytes);
 const Resident *find_weight(strix_cuda *h, const char *key);
+// Repack + upload of raw GGUF blocks [out_dim][in_dim] under `key` (1 adopted, 0 declined, <0 error). gemm_copy: Q8_0
+// weights also keep the row-major code copy the prefill GEMM reads.
+int upload_quant(strix_cuda *h, int fmt, const char *key, const uint8_t *bytes, size_t len, size_t in_dim, size_t out_dim,
+                 bool gemm_copy);
 // argmax per row of d_x[rows][stride] (n entries each, rows <= 16) into h->am_idx (and h->am_val) on `stream`
 int argmax_rows_enqueue(strix_cuda *h, const float *d_x, size_t n, size_t stride, size_t rows, cudaStream_t stream);
 Resident *find_weight_mut(strix_cuda *h, const char *key);

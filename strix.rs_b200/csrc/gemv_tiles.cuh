@@ -81,7 +81,12 @@ __device__ __forceinline__ GroupRef group_ref(const GemvArgs &A, uint32_t t) {
     const uint32_t gl = t - A.mat[m].tile0;
     r.row0 = gl * TILE_ROWS;
     r.rows = min(TILE_ROWS, A.mat[m].rows - r.row0);
-    r.src = A.mat[m].w + (uint64_t)gl * A.L.group_bytes;
+    uint32_t gs = gl;  // the row group inside the resident stack
+    if (A.sel_ids) {
+        const uint32_t sel = gl / A.sel_groups;
+        gs = min((uint32_t)A.sel_ids[sel], A.sel_experts - 1u) * A.sel_groups + (gl - sel * A.sel_groups);
+    }
+    r.src = A.mat[m].w + (uint64_t)gs * A.L.group_bytes;
     return r;
 }
 

@@ -65,6 +65,12 @@ struct GemvArgs {
     // instead of by every CTA: the image of the shared-memory operand region (x_layout order) in global
     // memory, which each CTA fetches with bulk copies. Null = the CTA builds its operands itself.
     const uint8_t *xop;
+    // Expert indirection (mixture-of-experts layers): every matrix of the launch is a stack of experts of
+    // sel_groups row groups each; the launch's virtual matrix is the stack of the experts sel_ids[0], sel_ids[1], ...
+    // (device words, read by the kernel), so mat[].rows = selections * rows per expert. Null = none.
+    const int *sel_ids;
+    uint32_t sel_groups;
+    uint32_t sel_experts;  // experts in the stack; an id outside [0, sel_experts) is clamped into it (never read out of bounds)
     uint32_t grid;
     uint32_t smem_bytes;
     uint32_t debug;  // measurement only: bit 0 = stream the tiles but skip the arithmetic

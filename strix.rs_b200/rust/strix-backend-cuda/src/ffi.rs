@@ -90,6 +90,14 @@ extern "C" {
     pub fn strix_cuda_prefill_q4_gemm_dev(h: *mut StrixCuda, key: *const c_char, d_xs: *const f32, m: usize, d_y: *mut f32, stream: *mut c_void) -> c_int;
     pub fn strix_cuda_prefill_q8_gemm_noalloc(h: *mut StrixCuda, key: *const c_char, d_xs: *const f32, m: usize, d_y: *mut f32, stream: *mut c_void) -> c_int;
     pub fn strix_cuda_noalloc_scratch_bytes() -> usize;
+    pub fn strix_cuda_upload_moe_q8(h: *mut StrixCuda, layer: usize, gate: *const u8, gate_len: usize, up: *const u8, up_len: usize, down: *const u8, down_len: usize, hidden: usize, eff: usize, ne: usize) -> c_int;
+    pub fn strix_cuda_upload_moe_q6(h: *mut StrixCuda, layer: usize, gate: *const u8, gate_len: usize, up: *const u8, up_len: usize, down: *const u8, down_len: usize, hidden: usize, eff: usize, ne: usize) -> c_int;
+    pub fn strix_cuda_moe_ffn(h: *mut StrixCuda, layer: usize, ids: *const c_int, wexp: *const f32, k: usize, x: *const f32, x_len: usize, sgate: f32, act: c_int, y: *mut f32, y_cap: usize) -> c_int;
+    pub fn strix_cuda_moe_ffn_dev(h: *mut StrixCuda, layer: usize, d_ids: *const c_int, d_wexp: *const f32, k: usize, d_x: *const f32, sgate: f32, act: c_int, d_y: *mut f32, stream: *mut c_void) -> c_int;
+    pub fn strix_cuda_moe_expert_ffn(h: *mut StrixCuda, layer: usize, e: usize, xs: *const f32, m: usize, act: c_int, y: *mut f32, y_cap: usize) -> c_int;
+    pub fn strix_cuda_moe_layer_ffn(h: *mut StrixCuda, layer: usize, plan: *const c_int, n_plan: usize, xs: *const f32, rows: usize, act: c_int, y: *mut f32, y_cap: usize) -> c_int;
+    pub fn strix_cuda_topk_router(h: *mut StrixCuda, logits: *const f32, ne: usize, k: usize, ids: *mut c_int, w: *mut f32) -> c_int;
+    pub fn strix_cuda_topk_router_dev(h: *mut StrixCuda, d_logits: *const f32, ne: usize, k: usize, d_ids: *mut c_int, d_w: *mut f32, stream: *mut c_void) -> c_int;
     pub fn strix_cuda_configure_decode(h: *mut StrixCuda, cfg: *const StrixGpuDecodeConfig) -> c_int;
     pub fn strix_cuda_decode_step(h: *mut StrixCuda, hvec: *const f32, pos: usize, logits: *mut f32, logits_cap: usize) -> c_int;
     pub fn strix_cuda_decode_step_argmax(h: *mut StrixCuda, hvec: *const f32, pos: usize, id: *mut u32) -> c_int;

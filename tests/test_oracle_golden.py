@@ -364,3 +364,32 @@ def test_f16_cache_rounding_follows_the_reference_kernel(orc):
     ties = (r.view(np.uint32) & 0x1FFF) == 0x1000
     np.testing.assert_array_equal(h[~ties], r.astype(np.float16).view(np.uint16)[~ties])
     np.testing.assert_array_equal(orc.f16_cache_to_f32(h), h.view(np.float16).astype(np.float32))
+
+
+def test_moe_router_and_ffn_rules(orc, synth):
+    """mellum.rs:1590-1609 router: softmax, the k most probable by a stable sort (a tie keeps the lower index),
+    weights renormalised over the chosen; mellum.rs:1624-1660: the weighted sum of the experts' FFNs."""
+    ids, w = orc.topk_router(np.array([0.0, 2.0, 2.0, -1.0, 1.0], np.float32), 3)
+    assert list(ids) == [1, 2, 4]
+    p = np.exp(np.array([2.0, 2.0, 1.0]) - 2.0)
+    np.testing.assert_allclose(w, p / p.sum(), rtol=1e-6)
+    assert abs(float(w.sum()) - 1.0) < 1e-6
+    ids, w = orc.topk_router(np.zeros(8, np.float32), 8)            # all tied: index order, uniform weights
+    assert list(ids) == list(range(8))
+    np.testing.assert_allclose(w, np.full(8, 0.125), rtol=1e-6)
+    # two experts, weights (1, 0) -> exactly the first expert's FFN; (0.5, 0.5) -> the mean
+    hidden, eff, ne = 64, 32, 3
+    gate = synth.quant(synth.Q8_0, 7, "moe.gate", ne * eff, hidden)
+    up = synth.quant(synth.Q8_0, 7, "moe.up", ne * eff, hidden)
+    down = synth.quant(synth.Q8_0, 7, "moe.down", ne * hidden, eff)
+    x = synth.normal(8, "x", hidden)
+    e0 = orc.moe_expert_ffn(x, gate, up, down, synth.Q8_0, hidden, eff, 2)
+    e1 = orc.moe_expert_ffn(x, gate, up, down, synth.Q8_0, hidden, eff, 0)
+    np.testing.assert_array_equal(orc.moe_ffn(x, gate, up, down, synth.Q8_0, hidden, eff, [2, 0], [1.0, 0.0]), e0)
+    np.testing.assert_allclose(orc.moe_ffn(x, gate, up, down, synth.Q8_0, hidden, eff, [2, 0], [0.5, 0.5]), 0.5 * (e0 + e1), rtol=1e-6, atol=1e-7)
+    # the expert slices are what a per-expert matmul on the slice gives (mellum.rs:1620-1622)
+    gb, db = orc.moe_expert_bytes(synth.Q8_0, hidden, eff)
+    assert gb == (hidden // 32) * 34 * eff and db == (eff // 32) * 34 * hidden
+    g = orc.qmatmul(x, np.frombuffer(gate, np.uint8)[2 * gb:3 * gb], synth.Q8_0, hidden, eff)
+    u = orc.qmatmul(x, np.frombuffer(up, np.uint8)[2 * gb:3 * gb], synth.Q8_0, hidden, eff)
+    np.testing.assert_array_equal(e0, orc.qmatmul(orc.swiglu(g, u), np.frombuffer(down, np.uint8)[2 * db:3 * db], synth.Q8_0, eff, hidden))
