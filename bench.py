@@ -767,11 +767,24 @@ def main():
 
     stream = torch.cuda.Stream(device=dev)
 
-    def step_device():
+    # The six GEMVs do not depend on one another: the step is ONE gemv_batch_dev call (the trait's gemv_batch on
+    # device vectors). The library runs a shard above 64 MiB as a launch of its own and the smaller ones side by
+    # side in one launch (up to six problems; its CTAs dealt out among them). The same rule here, for the launch
+    # count and the per-launch events: units = lists of items that share a launch.
+    SMALL = 64 << 20
+    def shard_bytes(it):
+        be, bb = BLOCK[it["ty"]]
+        return it["rows"] * (it["k"] // be) * bb
+    small = [it for it in items if shard_bytes(it) <= SMALL]
+    if len(small) < 2:
+        small = []
+    units = [[it] for it in items if not any(it is s_ for s_ in small)] + [small[i:i + 6] for i in range(0, len(small), 6)]
+
+    def step_device(act=None):
         s = torch.cuda.current_stream().cuda_stream
-        for it in items:
-            ok = acc.gemv_dev([it["key"]], it["x"].data_ptr(), [it["y"].data_ptr()], act=pkg.ACT_F32, stream=s)
-            assert ok
+        ok = acc.gemv_batch_dev([it["key"] for it in items], [it["x"].data_ptr() for it in items],
+                                [it["y"].data_ptr() for it in items], act=pkg.ACT_F32 if act is None else act, stream=s)
+        assert ok
         if world > 1:
             dist.all_gather_into_tensor(y_all, y_mine)
 
@@ -841,64 +854,78 @@ def main():
             pass
         peak = float(peaks.get("hbm_gbs", 6650.0))
         peak_src = "measured" if "hbm_gbs" in peaks else "fallback"
+        def unit_launch(u, s):
+            ok = acc.gemv_batch_dev([it["key"] for it in u], [it["x"].data_ptr() for it in u], [it["y"].data_ptr() for it in u],
+                                    act=pkg.ACT_F32, stream=s)
+            assert ok
         with torch.cuda.stream(stream):
             s = stream.cuda_stream
             rounds = 20
-            evs = [[(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in items]
+            evs = [[(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in units]
                    for _ in range(rounds)]
             for _ in range(3):
-                for it in items:
-                    acc.gemv_dev([it["key"]], it["x"].data_ptr(), [it["y"].data_ptr()], act=pkg.ACT_F32, stream=s)
+                for u in units:
+                    unit_launch(u, s)
             torch.cuda.synchronize()
             # (a few ms of device-side spinning first, so that the host has queued every launch before the
             # first one runs and no event pair includes a wait for the host)
             torch.cuda._sleep(20_000_000)
             for r in range(rounds):
-                for i, it in enumerate(items):
+                for i, u in enumerate(units):
                     evs[r][i][0].record()
-                    acc.gemv_dev([it["key"]], it["x"].data_ptr(), [it["y"].data_ptr()], act=pkg.ACT_F32, stream=s)
+                    unit_launch(u, s)
                     evs[r][i][1].record()
             torch.cuda.synchronize()
-            for i, it in enumerate(items):
-                shard_frac = it["y"].numel() / it["n"]
+            for i, u in enumerate(units):
+                by = sum(it["bytes"] * it["y"].numel() / it["n"] for it in u)
                 us = statistics.median(evs[r][i][0].elapsed_time(evs[r][i][1]) for r in range(rounds)) * 1e3
-                detail.append({"weight": it["key"], "us": round(us, 2),
-                               "gbs": round(it["bytes"] * shard_frac / us / 1e3, 1)})
-        # Three kernel instantiations run in the timed step: Q8_0 f32 (three launches), Q6_K with the
-        # f32 row as int8 digits (the two K = 2560 launches) and Q6_K on f16 tiles (K = 9728). The
-        # roofline is reported for the one with the largest share of the step (these per-launch events;
-        # the ncu launch list under profiles/ gives the same order), on its largest launch; the runner-up
-        # follows as second_kernel. DRAM traffic per launch from the ncu captures of 65536-row cases,
-        # scaled by rows (traffic grows with rows).
-        def kernel_of(it):
+                detail.append({"weight": " + ".join(it["key"] for it in u), "us": round(us, 2), "gbs": round(by / us / 1e3, 1)})
+        # The kernels of the timed step: one instantiation of gemv_kernel per large weight (Q8_0 with the f32 row on
+        # f16 tiles; Q6_K with the f32 row as int8 digits for K <= 8192, on f16 tiles beyond) and gemv_multi_kernel
+        # for the weights that run side by side. The roofline is reported for the one with the largest share of the
+        # step (these per-launch events; the ncu launch list under profiles/ gives the same order), on its largest
+        # launch; the runner-up follows as second_kernel. DRAM traffic per launch from the ncu captures of
+        # 65536-row cases, scaled by rows (traffic grows with rows).
+        def kernel_of(u):
+            if len(u) > 1:
+                return "gemv_multi_kernel<%d weights side by side>" % len(u)
+            it = u[0]
             if it["ty"] == Q8_0:
                 return "gemv_kernel<Q8_0, f32 row on f16 tiles>"
             return "gemv_kernel<Q6_K, f32 row as int8 digits>" if it["k"] <= 8192 else "gemv_kernel<Q6_K, f32 row on f16 tiles>"
         share = {}
-        for d, it in zip(detail, items):
-            share[kernel_of(it)] = share.get(kernel_of(it), 0.0) + d["us"]
+        for d, u in zip(detail, units):
+            share[kernel_of(u)] = share.get(kernel_of(u), 0.0) + d["us"]
         order = sorted(share, key=lambda k_: -share[k_])
         traffic65536 = {Q8_0: 181.86e6, Q6_K: 141.15e6}   # dram__bytes_read.sum + dram__bytes_write.sum, 65536 x 2560
 
+        def unit_bytes(u):
+            return sum(it["bytes"] * it["y"].numel() / it["n"] for it in u)
+
         def roof_of(kname):
-            cand = [(d, it) for d, it in zip(detail, items) if kernel_of(it) == kname]
-            d, it = max(cand, key=lambda c: c[1]["bytes"])
-            return {"kernel": "%s on %s, %s algorithmic bytes per launch" % (kname, it["key"], format(it["bytes"], ",")),
+            cand = [(d, u) for d, u in zip(detail, units) if kernel_of(u) == kname]
+            d, u = max(cand, key=lambda c: unit_bytes(c[1]))
+            it = u[0]
+            one = len(u) == 1 and world == 1 and it["k"] == 2560
+            return {"kernel": "%s on %s, %s algorithmic bytes per launch" % (kname, d["weight"], format(int(unit_bytes(u)), ",")),
                     "achieved": d["gbs"], "frac": round(d["gbs"] / peak, 4),
                     "share_of_step": round(share[kname] / sum(share.values()), 3),
-                    "traffic": int(traffic65536[it["ty"]] * it["n"] / 65536) if world == 1 and it["k"] == 2560 else None}
-        dom, sec = roof_of(order[0]), roof_of(order[1])
+                    "traffic": int(traffic65536[it["ty"]] * it["n"] / 65536) if one else None}
+        dom = roof_of(order[0])
+        sec = roof_of(order[1]) if len(order) > 1 else None
         def frac_all(kname):
             """the instantiation over ALL its launches of the step: their algorithmic bytes / their summed durations"""
-            cand = [(d, it) for d, it in zip(detail, items) if kernel_of(it) == kname]
-            by = sum(it["bytes"] * it["y"].numel() / it["n"] for _, it in cand)
+            cand = [(d, u) for d, u in zip(detail, units) if kernel_of(u) == kname]
+            by = sum(unit_bytes(u) for _, u in cand)
             return round(by / sum(d["us"] for d, _ in cand) / 1e3 / peak, 4)
         roof = {"bound": "hbm", "achieved": dom["achieved"], "peak": peak, "unit": "GB/s", "frac": dom["frac"],
                 "traffic": dom["traffic"], "kernel": dom["kernel"] + " (of %s peak)" % peak_src,
                 "share_of_step": dom["share_of_step"], "frac_of_8tbs": round(dom["achieved"] / 8000.0, 4),
                 "frac_over_all_launches_of_the_instantiation": frac_all(order[0]),
                 "frac_of_the_whole_step": round(value / world / peak, 4),
-                "second_kernel": dict(sec, frac_over_all_launches_of_the_instantiation=frac_all(order[1]))}
+                "second_kernel": dict(sec, frac_over_all_launches_of_the_instantiation=frac_all(order[1])) if sec else None,
+                "launches_of_the_step": [{"kernel": kernel_of(u), "weights": d["weight"], "us": d["us"], "gbs": d["gbs"],
+                                          "frac": round(d["gbs"] / peak, 4)} for d, u in zip(detail, units)]}
 
     # ---- extras on rank 0 at N=1: the integer-dot GEMV variant and the W8A8 GEMM (configs[2]) ----
     extras = None
@@ -908,8 +935,8 @@ def main():
             s = stream.cuda_stream
             g = torch.cuda.CUDAGraph()
             with torch.cuda.graph(g, stream=stream):
-                for it in items:
-                    acc.gemv_dev([it["key"]], it["x"].data_ptr(), [it["y"].data_ptr()], act=pkg.ACT_Q8DOT, stream=s)
+                assert acc.gemv_batch_dev([it["key"] for it in items], [it["x"].data_ptr() for it in items],
+                                          [it["y"].data_ptr() for it in items], act=pkg.ACT_Q8DOT, stream=s)
             for _ in range(3):
                 g.replay()
             torch.cuda.synchronize()
@@ -1001,7 +1028,7 @@ def main():
             "parallelism": "rows sharded over %d GPU(s)%s" % (
                 world, ", one NCCL all-gather of the six output shards per step" if world > 1 else ""),
             "e2e": {"value": round(e2e_val, 2), "unit": "GB/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
-            "gpu_launches": args.steps * REPLAYS * len(items),
+            "gpu_launches": args.steps * REPLAYS * len(units), "launches_per_step": len(units),
             "clocks": clocks, "roofline": roof, "cpu_baseline": cpu, "per_weight": detail, "extras": extras,
             "frac_of_8tbs": round(value / 8000.0, 4),
         }

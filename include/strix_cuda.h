@@ -165,6 +165,17 @@ STRIX_API int strix_cuda_poke_u32(strix_cuda *h, void *d_ptr, uint32_t value);
 STRIX_API int strix_cuda_peer_barrier_dev(strix_cuda *h, uint32_t *d_epoch, uint32_t *d_local_flags,
                                 uint32_t *const *peer_flags, void *stream);
 
+/* WeightAccel::gemv_batch (accel.rs:397-399; decode.rs:3227-3255) for device-resident vectors: n INDEPENDENT GEMVs,
+ * d_ys[i] = W(keys[i]) d_xs[i], enqueued from `stream` (no copies, no synchronisation). Independent means: no item
+ * reads or writes what another writes; the items then need not run in the order given. Items whose weights are at
+ * most "batch_small_bytes" (set_option; 64 MiB) run SIDE BY SIDE in one launch, up to 6 per launch: its CTAs are
+ * dealt out among the items by their bytes, so the launch fills and drains once for all of them (a launch of its
+ * own costs such an item more in fill and drain than its weights take to stream). The others get a launch each,
+ * before it. The host-pointer form strix_cuda_gemv_batch splits a batch the same way.
+ * set_option("batch_side_by_side", 0) gives every item its own launch, 2 runs all items side by side.
+ * 0 = an unknown key or a null vector. */
+STRIX_API int strix_cuda_gemv_batch_dev(strix_cuda *h, size_t n, const char *const *keys, const float *const *d_xs,
+                              float *const *d_ys, int act, void *stream);
 /* WeightAccel::prefill_q8_gemm (accel.rs:213; decode.rs:3257-3297): y[m][rows] = W8A8 GEMM of m
  * token rows xs[m][in_dim] with a resident Q8_0 weight: per-32 int8 activations (xquant8_rows,
  * kernels.rs:1000-1013), int32 block sums on tcgen05, f32 combine with both block scales
@@ -383,7 +394,8 @@ STRIX_API int strix_cuda_clear_device_status(strix_cuda *h, void *stream);
  * the activation operands are prepared once by a kernel of their own and fetched by every CTA; 0 = every CTA
  * quantises all rows itself), "gemv_debug" (bit 0: stream the weights without
  * arithmetic, bit 1: empty launches, bit 2: stop after the activation prologue), "batch_graph" (gemv_batch
- * replays a cached CUDA graph), "decode_chain" (the projection chain as one persistent launch),
+ * replays a cached CUDA graph), "batch_side_by_side" / "batch_small_bytes" (which items of a gemv_batch share a launch,
+ * see strix_cuda_gemv_batch_dev), "decode_chain" (the projection chain as one persistent launch),
  * "kv_f16" (real attention keeps its KV cache in f16),
  * "chain_trace" (per-step clocks, see strix_cuda_decode_trace), "chain_debug" (bit 0: the chain kernel skips
  * the arithmetic, bit 1: its waits on exchange vectors do not wait; results are then meaningless), "poll_limit" (bound, in polls, of a wait on

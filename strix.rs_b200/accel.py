@@ -74,8 +74,10 @@ def load_library():
     sig("strix_cuda_upload_f32", C.c_int, H, C.c_char_p, f32p, sz)
     sig("strix_cuda_weight_info", C.c_int, H, C.c_char_p, szp, szp, szp, szp, C.POINTER(C.c_int))
     sig("strix_cuda_gemv", C.c_int, H, C.c_char_p, f32p, sz, f32p, sz, C.c_int)
-    sig("strix_cuda_gemv_batch", C.c_int, H, sz, C.POINTER(C.c_char_p), C.POINTER(f32p), szp, C.POINTER(f32p), szp,
+    sig("strix_cuda_gemv_batch", C.c_int, H, sz, C.POINTER(C.c_char_p), C.POINTER(C.c_void_p), szp, C.POINTER(C.c_void_p), szp,
         C.c_int, C.POINTER(C.c_int))
+    sig("strix_cuda_gemv_batch_dev", C.c_int, H, sz, C.POINTER(C.c_char_p), C.POINTER(C.c_void_p), C.POINTER(C.c_void_p), C.c_int,
+        C.c_void_p)
     sig("strix_cuda_gemv_dev", C.c_int, H, C.c_int, C.POINTER(C.c_char_p), C.c_void_p, C.c_void_p, C.c_float,
         C.c_int, C.c_int, C.POINTER(C.c_void_p), C.c_void_p)
     sig("strix_cuda_gemv_res_dev", C.c_int, H, C.c_int, C.POINTER(C.c_char_p), C.c_void_p, C.c_void_p, C.c_float,
@@ -211,6 +213,7 @@ class CudaWeightAccel:
         return int(self._L.strix_cuda_resident_count(self._h))
 
     def _upload(self, fn, key, data, in_dim, out_dim):
+        self._rows = {}
         b = _u8(data)
         rc = fn(self._h, key.encode(), b.ctypes.data_as(C.POINTER(C.c_uint8)), b.size, in_dim, out_dim)
         return self._check(rc) == 1
@@ -255,17 +258,30 @@ class CudaWeightAccel:
         n = len(calls)
         if n == 0:
             return []
-        infos = [self.weight_info(k) for k, _ in calls]
+        # rows of each weight held here (what the output buffers need), remembered until the next upload
+        rows = getattr(self, "_rows", None)
+        if rows is None:
+            rows = self._rows = {}
+        nrows = []
+        for k, _ in calls:
+            r = rows.get(k, -1)
+            if r < 0:
+                info = self.weight_info(k)
+                r = rows[k] = info["rows"] if info else 0
+                if info is None:
+                    del rows[k]          # (an unknown key may be uploaded later through another path)
+                    r = None
+            nrows.append(r)
         xs = [_f32(x) for _, x in calls]
-        ys = [np.empty(i["rows"] if i else 0, dtype=np.float32) for i in infos]
+        ys = [np.empty(r or 0, dtype=np.float32) for r in nrows]
         keys = (C.c_char_p * n)(*[k.encode() for k, _ in calls])
-        xp = (C.POINTER(C.c_float) * n)(*[_fp(x) for x in xs])
-        yp = (C.POINTER(C.c_float) * n)(*[_fp(y) for y in ys])
+        xp = (C.c_void_p * n)(*[x.ctypes.data for x in xs])
+        yp = (C.c_void_p * n)(*[y.ctypes.data for y in ys])
         ks = (C.c_size_t * n)(*[x.size for x in xs])
         yc = (C.c_size_t * n)(*[y.size for y in ys])
         st = (C.c_int * n)()
         self._check(self._L.strix_cuda_gemv_batch(self._h, n, keys, xp, ks, yp, yc, act, st))
-        return [ys[i] if (infos[i] is not None and st[i] == 1) else None for i in range(n)]
+        return [ys[i] if (nrows[i] is not None and st[i] == 1) else None for i in range(n)]
 
     def gemv_rows(self, key, xs, b, act=ACT_F32):
         """ys[b][rows] = W xs[b][in_dim]: b activation rows, one pass over the weights. None if not resident."""
@@ -544,6 +560,15 @@ class CudaWeightAccel:
         rc = self._check(self._L.strix_cuda_gemv_dev(self._h, n, kk, C.c_void_p(int(d_a)),
                                                     C.c_void_p(int(d_b)) if d_b else None, float(eps), pre, act, yy,
                                                     C.c_void_p(int(stream)) if stream else None))
+        return rc == 1
+
+    def gemv_batch_dev(self, keys, d_xs, d_ys, act=ACT_F32, stream=0):
+        """n independent GEMVs on device vectors (ys[i] = W(keys[i]) xs[i]); the small ones run side by side in one launch."""
+        n = len(keys)
+        kk = (C.c_char_p * n)(*[k.encode() for k in keys])
+        xx = (C.c_void_p * n)(*[int(p) for p in d_xs])
+        yy = (C.c_void_p * n)(*[int(p) for p in d_ys])
+        rc = self._check(self._L.strix_cuda_gemv_batch_dev(self._h, n, kk, xx, yy, act, C.c_void_p(int(stream)) if stream else None))
         return rc == 1
 
     def gemv_peers_dev(self, keys, d_a, peer_ys, d_b=0, eps=0.0, pre=PRE_NONE, act=ACT_F32, stream=0, d_res=None):

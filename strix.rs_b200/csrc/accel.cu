@@ -146,12 +146,8 @@ int upload_quant(strix_cuda *h, int fmt, const char *key, const uint8_t *bytes, 
         return -1;
     }
     decode_release(h);  // a configured chain may hold the pointer this upload replaces
-    if (h->batch_graph.exec) {
-        // so may the cached gemv_batch graph (the allocator can hand the old address back to a weight of
-        // another format or shape)
-        cudaGraphExecDestroy(h->batch_graph.exec);
-        h->batch_graph.exec = nullptr;
-    }
+    batch_release(h);   // so may the cached gemv_batch graph and programs (the allocator can hand the old address
+                        // back to a weight of another format or shape)
     auto it = h->weights.find(key);
     if (it != h->weights.end()) {
         cudaFree(it->second.dev);
@@ -162,6 +158,57 @@ int upload_quant(strix_cuda *h, int fmt, const char *key, const uint8_t *bytes, 
         h->weights.emplace(key, r);
     }
     return 1;
+}
+}  // namespace strix
+
+namespace strix {
+void batch_release(strix_cuda *h) {
+    if (h->batch_graph.exec) {
+        cudaGraphExecDestroy(h->batch_graph.exec);
+        h->batch_graph.exec = nullptr;
+    }
+}
+
+// Items idx of a batch (independent GEMVs ws[i], d_xs[i] -> d_ys[i]) side by side: up to GEMV_MULTI_MAX problems
+// per launch (gemv_multi_kernel), the CTAs dealt out among them by their bytes. What cannot be planned that way
+// gets a launch of its own.
+static int batch_enqueue_side_by_side(strix_cuda *h, const std::vector<size_t> &idx, const Resident *const *ws,
+                                      const float *const *d_xs, float *const *d_ys, int act, cudaStream_t s) {
+    for (size_t at = 0; at < idx.size(); at += GEMV_MULTI_MAX) {
+        const size_t cnt = std::min<size_t>(GEMV_MULTI_MAX, idx.size() - at);
+        GemvMultiArgs m{};
+        m.n = (uint32_t)cnt;
+        bool ok = cnt >= 2;
+        for (size_t k = 0; ok && k < cnt; k++) {
+            const size_t i = idx[at + k];
+            const Resident *w1[1] = {ws[i]};
+            float *y1[1] = {d_ys[i]};
+            if (gemv_fill_args(h, 1, w1, d_xs[i], nullptr, 0.f, STRIX_PRE_NONE, act, y1, nullptr, &m.p[k]) < 0) return -1;
+        }
+        if (ok) ok = gemv_multi_plan(m, h->num_sms, h->smem_optin, h->tune);
+        if (ok) {
+            CU_TRY(h, launch_gemv_multi(m, s));
+            continue;
+        }
+        for (size_t k = 0; k < cnt; k++) {
+            const size_t i = idx[at + k];
+            const Resident *w1[1] = {ws[i]};
+            float *y1[1] = {d_ys[i]};
+            if (gemv_launch(h, 1, w1, d_xs[i], nullptr, 0.f, STRIX_PRE_NONE, act, y1, nullptr, s) < 0) return -1;
+        }
+    }
+    return 1;
+}
+
+// Which items of a batch run side by side in one launch: those whose weights are at most batch_small_bytes (a large
+// weight saturates the memory system from a launch of its own), if there are at least two of them.
+static std::vector<size_t> batch_small_items(const strix_cuda *h, size_t n, const Resident *const *ws) {
+    std::vector<size_t> small;
+    if (h->batch_side_by_side == 0) return small;
+    for (size_t i = 0; i < n; i++)
+        if (ws[i] && (h->batch_side_by_side == 2 || ws[i]->bytes <= h->batch_small_bytes)) small.push_back(i);
+    if (small.size() < 2) small.clear();
+    return small;
 }
 }  // namespace strix
 
@@ -315,7 +362,7 @@ void strix_cuda_destroy(strix_cuda *h) {
     decode_release(h);
     if (h->copy_stream) cudaStreamDestroy(h->copy_stream);
     for (cudaEvent_t e : h->batch_events) cudaEventDestroy(e);
-    if (h->batch_graph.exec) cudaGraphExecDestroy(h->batch_graph.exec);
+    batch_release(h);
     if (h->batch_flags) cudaFreeHost((void *)h->batch_flags);
     if (h->d_one) cudaFree(h->d_one);
     for (auto &kv : h->weights) {
@@ -356,6 +403,8 @@ int strix_cuda_set_option(strix_cuda *h, const char *name, long long value) {
     else if (n == "gemv_debug") h->tune.debug = v;
     else if (n == "rows_operand_image") h->tune.xop = v;
     else if (n == "batch_graph") h->use_batch_graph = value != 0;
+    else if (n == "batch_side_by_side") h->batch_side_by_side = (int)v;
+    else if (n == "batch_small_bytes") h->batch_small_bytes = (size_t)value;
     else if (n == "kv_f16") h->kv_f16 = value != 0;
     else if (n == "decode_chain") h->decode_chain = value < 0 ? -1 : value != 0;
     else if (n == "chain_trace") h->chain_trace = value != 0;
@@ -436,10 +485,7 @@ int strix_cuda_gemv_batch(strix_cuda *h, size_t n, const char *const *keys, cons
     if (!h || (n && (!keys || !xs || !ks || !ys || !y_caps))) return -1;
     h->err.clear();
     CU_TRY(h, cudaSetDevice(h->device));
-    // lay the n activations and n outputs out back to back in the staging buffers
     std::vector<const Resident *> ws(n, nullptr);
-    std::vector<size_t> xoff(n, 0), yoff(n, 0);
-    size_t xtot = 0, ytot = 0;
     int any = 0;
     for (size_t i = 0; i < n; i++) {
         const Resident *r = find_weight(h, keys[i]);
@@ -449,14 +495,35 @@ int strix_cuda_gemv_batch(strix_cuda *h, size_t n, const char *const *keys, cons
             continue;
         }
         ws[i] = r;
-        xoff[i] = xtot;
-        yoff[i] = ytot;
-        xtot += (r->L.in_dim + 3) & ~(size_t)3;  // keep every x 16-byte aligned
-        ytot += r->rows;
         if (status) status[i] = 1;
         any = 1;
     }
     if (!any) return n ? 0 : 1;
+    // The items are independent, so the device may take them in any order. Units of work, in the order they run:
+    // every large item as a launch of its own, first (their outputs, the big ones, leave while later kernels run),
+    // then the small items side by side in one launch (gemv_multi_kernel), whose outputs are all that is left to
+    // copy when the last kernel ends. Activations and outputs lie back to back in the staging buffers in
+    // that order.
+    const std::vector<size_t> small = batch_small_items(h, n, ws.data());
+    std::vector<char> is_small(n, 0);
+    for (size_t i : small) is_small[i] = 1;
+    std::vector<std::vector<size_t>> units;
+    for (size_t i = 0; i < n; i++)
+        if (ws[i] && !is_small[i]) units.push_back({i});
+    if (!small.empty()) units.push_back(small);
+    const size_t nu = units.size();
+    std::vector<size_t> xoff(n, 0), yoff(n, 0), unit_y0(nu, 0), unit_y1(nu, 0);
+    size_t xtot = 0, ytot = 0;
+    for (size_t u = 0; u < nu; u++) {
+        unit_y0[u] = ytot;
+        for (size_t i : units[u]) {
+            xoff[i] = xtot;
+            yoff[i] = ytot;
+            xtot += (ws[i]->L.in_dim + 3) & ~(size_t)3;  // keep every x 16-byte aligned
+            ytot += (ws[i]->rows + 3) & ~(size_t)3;      // and every y
+        }
+        unit_y1[u] = ytot;
+    }
     if (ensure_f32(h, h->x, xtot) < 0 || ensure_f32(h, h->y, std::max<size_t>(ytot, 1)) < 0) return -1;
     if (ensure_pinned(h, h->pin_in, xtot * 4) < 0 || ensure_pinned(h, h->pin_out, std::max<size_t>(ytot, 1) * 4) < 0)
         return -1;
@@ -466,53 +533,62 @@ int strix_cuda_gemv_batch(strix_cuda *h, size_t n, const char *const *keys, cons
     // Outputs leave on a second stream, each as soon as its kernel is done, so that the copies (and the
     // host's own copy out of the pinned buffer) overlap the kernels still to run.
     if (!h->copy_stream) CU_TRY(h, cudaStreamCreateWithFlags(&h->copy_stream, cudaStreamNonBlocking));
-    while (h->batch_events.size() < 2 * n) {
+    while (h->batch_events.size() < 2 * nu) {
         cudaEvent_t e = nullptr;
         CU_TRY(h, cudaEventCreateWithFlags(&e, cudaEventDisableTiming));
         h->batch_events.push_back(e);
     }
     // Outputs leave in groups: an event between two launches keeps the second from starting early behind the
-    // first (programmatic dependent launch), so small outputs wait for a later item and only an output that
-    // brings the pending bytes to 256 KB (or the last item) closes a group. group_end[i]: the item whose
-    // event covers item i's output; group_begin[e]: first item of the group that e closes.
-    std::vector<size_t> group_end(n, 0), group_begin(n, 0);
+    // first (programmatic dependent launch), so small outputs wait for a later unit and only an output that
+    // brings the pending bytes to 256 KB (or the last unit) closes a group. group_end[u]: the unit whose
+    // event covers unit u's outputs; group_begin[e]: first unit of the group that e closes.
+    std::vector<size_t> group_end(nu, 0), group_begin(nu, 0);
     {
-        size_t pending = 0, first = n, last_valid = n;
-        for (size_t i = 0; i < n; i++)
-            if (ws[i]) last_valid = i;
-        for (size_t i = 0; i < n; i++) {
-            if (!ws[i]) continue;
-            if (first == n) first = i;
-            pending += ws[i]->rows * 4;
-            if (pending >= (256u << 10) || i == last_valid) {
-                for (size_t j = first; j <= i; j++) group_end[j] = i;
-                group_begin[i] = first;
+        size_t pending = 0, first = nu;
+        for (size_t u = 0; u < nu; u++) {
+            if (first == nu) first = u;
+            pending += (unit_y1[u] - unit_y0[u]) * 4;
+            if (pending >= (256u << 10) || u + 1 == nu) {
+                for (size_t j = first; j <= u; j++) group_end[j] = u;
+                group_begin[u] = first;
                 pending = 0;
-                first = n;
+                first = nu;
             }
         }
     }
-    // What the device does for this batch: H2D of the activations, then per item its kernel on the main
-    // stream and, on the copy stream, its output's D2H followed by a one-word copy that raises the item's
+    std::vector<const float *> dxs(n, nullptr);
+    std::vector<float *> dys(n, nullptr);
+    for (size_t i = 0; i < n; i++)
+        if (ws[i]) {
+            dxs[i] = h->x.p + xoff[i];
+            dys[i] = h->y.p + yoff[i];
+        }
+    // What the device does for this batch: H2D of the activations, then per unit its kernel(s) on the main
+    // stream and, on the copy stream, its outputs' D2H followed by a one-word copy that raises the unit's
     // pinned flag. `graph`: the same sequence is being captured (the copy stream joins the main one at the
     // end, the events are capture-internal); otherwise the events are real and the host waits on them.
     auto enqueue = [&](bool graph) -> int {
         CU_TRY(h, cudaMemcpyAsync(h->x.p, pin, xtot * 4, cudaMemcpyHostToDevice, h->stream));
         cudaEvent_t last = nullptr;
-        for (size_t i = 0; i < n; i++) {
-            if (!ws[i]) continue;
-            const Resident *w1[1] = {ws[i]};
-            float *y1[1] = {h->y.p + yoff[i]};
-            if (gemv_launch(h, 1, w1, h->x.p + xoff[i], nullptr, 0.f, STRIX_PRE_NONE, act, y1, nullptr, h->stream) < 0) return -1;
-            if (group_end[i] != i) continue;  // its output leaves with a later item's (see group_end)
-            cudaEvent_t done = h->batch_events[2 * i], copied = h->batch_events[2 * i + 1];
+        for (size_t u = 0; u < nu; u++) {
+            if (units[u].size() > 1) {
+                if (batch_enqueue_side_by_side(h, units[u], ws.data(), dxs.data(), dys.data(), act, h->stream) < 0) return -1;
+            } else {
+                for (size_t i : units[u]) {
+                    const Resident *w1[1] = {ws[i]};
+                    float *y1[1] = {dys[i]};
+                    if (gemv_launch(h, 1, w1, dxs[i], nullptr, 0.f, STRIX_PRE_NONE, act, y1, nullptr, h->stream) < 0) return -1;
+                }
+            }
+            if (group_end[u] != u) continue;  // its outputs leave with a later unit's (see group_end)
+            cudaEvent_t done = h->batch_events[2 * u], copied = h->batch_events[2 * u + 1];
             CU_TRY(h, cudaEventRecord(done, h->stream));
             CU_TRY(h, cudaStreamWaitEvent(h->copy_stream, done, 0));
             // the group's outputs are contiguous in the staging buffers: one copy
-            const size_t g0 = group_begin[i], bytes = (yoff[i] + ws[i]->rows - yoff[g0]) * 4;
-            if (bytes) CU_TRY(h, cudaMemcpyAsync(pout + yoff[g0], h->y.p + yoff[g0], bytes, cudaMemcpyDeviceToHost, h->copy_stream));
+            const size_t y0 = unit_y0[group_begin[u]], bytes = (unit_y1[u] - y0) * 4;
+            if (bytes) CU_TRY(h, cudaMemcpyAsync(pout + y0, h->y.p + y0, bytes, cudaMemcpyDeviceToHost, h->copy_stream));
             if (graph)
-                CU_TRY(h, cudaMemcpyAsync((void *)(h->batch_flags + i), h->d_one, 4, cudaMemcpyDeviceToHost, h->copy_stream));
+                CU_TRY(h, cudaMemcpyAsync((void *)(h->batch_flags + u), h->d_one, 4, cudaMemcpyDeviceToHost, h->copy_stream));
             CU_TRY(h, cudaEventRecord(copied, h->copy_stream));
             last = copied;
         }
@@ -533,9 +609,11 @@ int strix_cuda_gemv_batch(strix_cuda *h, size_t n, const char *const *keys, cons
         // the cached graph fits if every pointer and shape its nodes hold is the same as last time
         auto &bg = h->batch_graph;
         bool same = bg.exec && bg.act == act && bg.w_dev.size() == n && bg.x == h->x.p && bg.y == h->y.p &&
-                    bg.pin_in == h->pin_in.p && bg.pin_out == h->pin_out.p;
+                    bg.pin_in == h->pin_in.p && bg.pin_out == h->pin_out.p && bg.side_by_side == h->batch_side_by_side &&
+                    bg.small_bytes == h->batch_small_bytes;
         for (size_t i = 0; same && i < n; i++)
-            same = bg.w_dev[i] == (ws[i] ? ws[i]->dev : nullptr) && (!ws[i] || (bg.rows[i] == ws[i]->rows && bg.in_dim[i] == ws[i]->L.in_dim));
+            same = bg.w_dev[i] == (ws[i] ? ws[i]->dev : nullptr) &&
+                   (!ws[i] || (bg.rows[i] == ws[i]->rows && bg.in_dim[i] == ws[i]->L.in_dim && bg.fmt[i] == ws[i]->fmt));
         if (!same) {
             if (bg.exec) cudaGraphExecDestroy(bg.exec);
             bg.exec = nullptr;
@@ -559,35 +637,37 @@ int strix_cuda_gemv_batch(strix_cuda *h, size_t n, const char *const *keys, cons
             bg.w_dev.assign(n, nullptr);
             bg.rows.assign(n, 0);
             bg.in_dim.assign(n, 0);
+            bg.fmt.assign(n, 0);
             for (size_t i = 0; i < n; i++)
                 if (ws[i]) {
                     bg.w_dev[i] = ws[i]->dev;
                     bg.rows[i] = ws[i]->rows;
                     bg.in_dim[i] = ws[i]->L.in_dim;
+                    bg.fmt[i] = ws[i]->fmt;
                 }
             bg.x = h->x.p;
             bg.y = h->y.p;
             bg.pin_in = h->pin_in.p;
             bg.pin_out = h->pin_out.p;
+            bg.side_by_side = h->batch_side_by_side;
+            bg.small_bytes = h->batch_small_bytes;
         }
-        for (size_t i = 0; i < n; i++) h->batch_flags[i] = 0u;
+        for (size_t u = 0; u < nu; u++) h->batch_flags[u] = 0u;
         CU_TRY(h, cudaGraphLaunch(bg.exec, h->stream));
         CU_TRY(h, cudaMemcpyAsync(&h->status_host, h->d_status, 4, cudaMemcpyDeviceToHost, h->stream));
         // hand each output to the caller as its flag comes up (bounded: once the stream has drained,
         // everything has landed whatever the flag says)
-        for (size_t i = 0; i < n; i++) {
-            if (!ws[i]) continue;
-            for (uint64_t spin = 0; h->batch_flags[group_end[i]] == 0u; spin++)
+        for (size_t u = 0; u < nu; u++) {
+            for (uint64_t spin = 0; h->batch_flags[group_end[u]] == 0u; spin++)
                 if ((spin & 0xfffu) == 0xfffu && cudaStreamQuery(h->stream) != cudaErrorNotReady) break;
-            memcpy(ys[i], pout + yoff[i], ws[i]->rows * sizeof(float));
+            for (size_t i : units[u]) memcpy(ys[i], pout + yoff[i], ws[i]->rows * sizeof(float));
         }
     } else {
         if (enqueue(false) < 0) return -1;
         // hand each output to the caller as its copy lands
-        for (size_t i = 0; i < n; i++) {
-            if (!ws[i]) continue;
-            CU_TRY(h, cudaEventSynchronize(h->batch_events[2 * group_end[i] + 1]));
-            memcpy(ys[i], pout + yoff[i], ws[i]->rows * sizeof(float));
+        for (size_t u = 0; u < nu; u++) {
+            CU_TRY(h, cudaEventSynchronize(h->batch_events[2 * group_end[u] + 1]));
+            for (size_t i : units[u]) memcpy(ys[i], pout + yoff[i], ws[i]->rows * sizeof(float));
         }
     }
     CU_TRY(h, cudaStreamSynchronize(h->stream));
@@ -597,6 +677,36 @@ int strix_cuda_gemv_batch(strix_cuda *h, size_t n, const char *const *keys, cons
         cudaMemsetAsync(h->d_status, 0, 4, h->stream);
         return -2;
     }
+    return 1;
+}
+
+// WeightAccel::gemv_batch for device-resident vectors: n independent GEMVs enqueued from `stream`, no copies and
+// no synchronisation. Large items first, a launch each; then the small ones side by side in one launch.
+int strix_cuda_gemv_batch_dev(strix_cuda *h, size_t n, const char *const *keys, const float *const *d_xs, float *const *d_ys,
+                              int act, void *stream) {
+    if (!h || (n && (!keys || !d_xs || !d_ys))) return -1;
+    h->err.clear();
+    if (act != STRIX_ACT_F32 && act != STRIX_ACT_Q8DOT) {
+        h->err = "gemv_batch_dev: unknown activation mode";
+        return -1;
+    }
+    CU_TRY(h, cudaSetDevice(h->device));
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    std::vector<const Resident *> ws(n, nullptr);
+    for (size_t i = 0; i < n; i++) {
+        ws[i] = find_weight(h, keys[i]);
+        if (!ws[i] || !d_xs[i] || !d_ys[i]) return 0;
+    }
+    const std::vector<size_t> small = batch_small_items(h, n, ws.data());
+    std::vector<char> is_small(n, 0);
+    for (size_t i : small) is_small[i] = 1;
+    for (size_t i = 0; i < n; i++) {
+        if (is_small[i]) continue;
+        const Resident *w1[1] = {ws[i]};
+        float *y1[1] = {d_ys[i]};
+        if (gemv_launch(h, 1, w1, d_xs[i], nullptr, 0.f, STRIX_PRE_NONE, act, y1, nullptr, s) < 0) return -1;
+    }
+    if (!small.empty() && batch_enqueue_side_by_side(h, small, ws.data(), d_xs, d_ys, act, s) < 0) return -1;
     return 1;
 }
 

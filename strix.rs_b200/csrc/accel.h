@@ -65,8 +65,15 @@ struct strix_cuda {
         int act = 0;
         std::vector<const uint8_t *> w_dev;   // resident buffers of the items, in order (null = skipped item)
         std::vector<size_t> rows, in_dim;
+        std::vector<int> fmt;
+        int side_by_side = 0;                 // the options the graph was captured under
+        size_t small_bytes = 0;
         const void *x = nullptr, *y = nullptr, *pin_in = nullptr, *pin_out = nullptr;
     } batch_graph;
+    // gemv_batch / gemv_batch_dev: the small items of a batch (independent GEMVs that would each pay a launch's fill
+    // and drain, ~9 us against 3-4 us of HBM time) run side by side in one launch (gemv_multi_kernel)
+    int batch_side_by_side = 1;       // 0 = a launch per item, 1 = items up to batch_small_bytes share launches, 2 = all items do
+    size_t batch_small_bytes = (size_t)64 << 20;
     volatile uint32_t *batch_flags = nullptr;  // pinned, BATCH_GRAPH_MAX words
     uint32_t *d_one = nullptr;                 // device word holding 1
     uint32_t *d_status = nullptr;
@@ -123,6 +130,7 @@ int gemv_launch_rows(strix_cuda *h, int nmat, const Resident *const *ws, const f
                      uint32_t b_stride, cudaStream_t stream);
 int gemv_fill_args(strix_cuda *h, int nmat, const Resident *const *ws, const float *d_a, const float *d_b, float eps,
                    int pre, int act, float *const *d_ys, const float *const *d_res, GemvArgs *out);
+void batch_release(strix_cuda *h);   // drops the cached gemv_batch graph (it holds weight pointers)
 void decode_release(strix_cuda *h);  // drops a configured decode chain (its graph holds weight pointers)
 int gemv_launch(strix_cuda *h, int nmat, const Resident *const *ws, const float *d_a, const float *d_b, float eps,
                 int pre, int act, float *const *d_ys, const float *const *d_res, cudaStream_t stream);

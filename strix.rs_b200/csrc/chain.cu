@@ -52,6 +52,7 @@ constexpr uint32_t CH_STEP_BYTES = 512;
 static_assert(sizeof(ChainStep) <= CH_STEP_BYTES && sizeof(ChainStep) % 16 == 0, "one 16-byte word per lane of a warp");
 constexpr uint32_t CH_STEP_OFF = CH_PART_OFF + CHAIN_PART_SLOTS * CH_WARPS * 16u * 4u;  // 3 consumer slots + 1 producer slot
 constexpr uint32_t CH_X_OFF = (CH_STEP_OFF + 4u * CH_STEP_BYTES + 127u) & ~127u;
+constexpr int CH_PASS_NI = 4;  // float4s a thread requests per pass over a row that needs no norm
 constexpr int CH_NORM_NI = 2;  // float4s a thread keeps across the RMSNorm reduction: normed rows up to 2 * 4 * 384 = 3072
 
 struct ChainCta {
@@ -302,8 +303,8 @@ __device__ __forceinline__ void chain_prologue_q8(const ChainStep &S, ChainCta &
             }
         }
     } else {
-        // no norm: each pass (up to 2 float4s per thread, both requested at once) is quantised and stored before
-        // the next one is fetched. Threads past the row's end carry zeros through the shuffles and store nothing.
+        // no norm: each pass (up to CH_PASS_NI float4s per thread, all requested at once) is quantised and stored
+        // before the next one is fetched. Threads past the row's end carry zeros through the shuffles and store nothing.
         const uint32_t per = (K4 + ct - 1u) / ct;  // float4s per thread
         if (per <= 1u) {
             float4 v[1];
@@ -315,11 +316,14 @@ __device__ __forceinline__ void chain_prologue_q8(const ChainStep &S, ChainCta &
 #pragma unroll
             for (int i = 0; i < 2; i++) quant_store(v[i], tid + i * ct, tid + i * ct < K4, l8, q6, bias, xbw, rec);
         } else {
-            for (uint32_t e0 = tid; e0 - lane < K4; e0 += 2u * ct) {
-                float4 v[2];
-                fetch_pass<2>(S, C, e0, ct, K4, v);
-                quant_store(v[0], e0, e0 < K4, l8, q6, bias, xbw, rec);
-                if (e0 - lane + ct < K4) quant_store(v[1], e0 + ct, e0 + ct < K4, l8, q6, bias, xbw, rec);
+            // (four float4s per thread and pass: a pass costs one trip to L2 whatever it carries, and the longest
+            // row of the decode chain, ffn 9728, then takes two trips instead of four)
+            for (uint32_t e0 = tid; e0 - lane < K4; e0 += (uint32_t)CH_PASS_NI * ct) {
+                float4 v[CH_PASS_NI];
+                fetch_pass<CH_PASS_NI>(S, C, e0, ct, K4, v);
+#pragma unroll
+                for (int i = 0; i < CH_PASS_NI; i++)
+                    if (e0 - lane + i * ct < K4) quant_store(v[i], e0 + i * ct, e0 + i * ct < K4, l8, q6, bias, xbw, rec);
             }
         }
         ch_trace(C, 1);

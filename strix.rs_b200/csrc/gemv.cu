@@ -329,6 +329,46 @@ __global__ void __launch_bounds__((GEMV_WARPS + 1) * 32, 1) gemv_kernel(const __
     consumer_groups<FMT, ACT, MULTI>(A, C);
 }
 
+// Several INDEPENDENT GEMVs side by side in one launch (the items of a gemv_batch: gemv_batch, decode.rs:3227-3255).
+// A small GEMV (20-30 MB of weights, 3-4 us of HBM time) costs a launch of its own ~9 us in fill and drain, and
+// nothing of another launch overlaps it because one CTA fills an SM. Here the CTAs of ONE launch are dealt out
+// among the problems in proportion to their bytes (gemv_multi_plan), every CTA runs the ordinary pipeline on its
+// own problem (its own format, activation form, in_dim, geometry), and the launch fills and drains once.
+// One kernel carries every (format, activation form) body, pre-op none, one activation row; a CTA runs one of them.
+template <int FMT, int ACT>
+__device__ __forceinline__ void multi_body(const GemvArgs &A, Cta &C) {
+    consumer_prologue<FMT, ACT, false, STRIX_PRE_NONE>(act_in(A), C);
+    consumer_groups<FMT, ACT, false>(A, C);
+}
+template <int FMT>
+__device__ __forceinline__ void multi_fmt(const GemvArgs &A, Cta &C) {
+    if constexpr (FMT == FMT_Q6_K) {
+        if (A.digits) return multi_body<FMT, ACT_F32_DIGITS>(A, C);
+    }
+    if (A.act == STRIX_ACT_F32) return multi_body<FMT, STRIX_ACT_F32>(A, C);
+    return multi_body<FMT, STRIX_ACT_Q8DOT>(A, C);
+}
+__global__ void __launch_bounds__((GEMV_WARPS + 1) * 32, 1) gemv_multi_kernel(const __grid_constant__ GemvMultiArgs M) {
+    extern __shared__ __align__(128) uint8_t smem[];
+    asm volatile("griddepcontrol.launch_dependents;");
+    uint32_t i = 0;
+    while (i + 1u < M.n && blockIdx.x >= M.cta0[i + 1u]) i++;
+    const GemvArgs &A = M.p[i];
+    Cta C = cta_init(smem, A.wc, A.slots, A.n_stages, A.stage_bytes, A.stage_off, A.status);
+    C.bid = blockIdx.x - M.cta0[i];  // the problem's CTAs are numbered from 0 among themselves
+    C.grid = M.cta0[i + 1u] - M.cta0[i];
+    if (C.warp == C.n_cons) {
+        producer_step(A, C);
+        return;
+    }
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    switch (A.L.fmt) {
+        case FMT_Q4_0: multi_fmt<FMT_Q4_0>(A, C); break;
+        case FMT_Q4_1: multi_fmt<FMT_Q4_1>(A, C); break;
+        case FMT_Q8_0: multi_fmt<FMT_Q8_0>(A, C); break;
+        default: multi_fmt<FMT_Q6_K>(A, C); break;
+    }
+}
 
 // ---- the activation operands of an integer-dot launch, prepared once for all CTAs ----
 // One CTA per activation row (rows past nbatch only clear their record slots, which must read zero).
@@ -633,6 +673,59 @@ cudaError_t launch_gemv(const GemvArgs &a, cudaStream_t stream) {
     }
 }
 
+// Deals num_sms CTAs out among n planned-to-be problems (nmat = 1, one activation row, pre-op none) and plans each
+// on its share: every problem gets one CTA, then the problem whose busiest CTA carries the most bytes gets the next
+// one, until none is left or nobody can use another. False when a problem cannot run this way.
+bool gemv_multi_plan(GemvMultiArgs &m, int num_sms, size_t smem_optin, const GemvTune &tune) {
+    const uint32_t n = m.n;
+    if (n < 1 || n > (uint32_t)GEMV_MULTI_MAX || n > (uint32_t)num_sms) return false;
+    uint32_t nc[GEMV_MULTI_MAX], groups[GEMV_MULTI_MAX];
+    for (uint32_t i = 0; i < n; i++) {
+        const GemvArgs &a = m.p[i];
+        if (a.nmat != 1 || a.pre != STRIX_PRE_NONE || a.nbatch > 1 || a.xop || a.sel_ids) return false;
+        groups[i] = (a.mat[0].rows + TILE_ROWS - 1) / TILE_ROWS;
+        nc[i] = 1;
+    }
+    auto load = [&](uint32_t i) { return (uint64_t)((groups[i] + nc[i] - 1u) / nc[i]) * m.p[i].L.group_bytes; };
+    for (uint32_t left = (uint32_t)num_sms - n; left > 0; left--) {
+        uint32_t worst = n;
+        for (uint32_t i = 0; i < n; i++)
+            if (nc[i] < groups[i] && (worst == n || load(i) > load(worst))) worst = i;
+        if (worst == n) break;  // (more CTAs than row groups help nobody)
+        nc[worst]++;
+    }
+    uint32_t c0 = 0, smem = 0;
+    for (uint32_t i = 0; i < n; i++) {
+        GemvArgs &a = m.p[i];
+        a.nbatch = 1;
+        if (!gemv_plan(a, (int)nc[i], smem_optin, tune)) return false;
+        a.rot = 0;
+        m.cta0[i] = c0;
+        c0 += a.grid ? a.grid : 1u;  // (a problem without rows keeps one idle CTA: the CTA ranges stay well-formed)
+        if (a.smem_bytes > smem) smem = a.smem_bytes;
+    }
+    m.cta0[n] = c0;
+    m.grid = c0;
+    m.smem_bytes = smem;
+    m.pdl = tune.pdl;
+    return true;
+}
+
+cudaError_t launch_gemv_multi(const GemvMultiArgs &m, cudaStream_t stream) {
+    if (m.n == 0 || m.grid == 0) return cudaSuccess;
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(m.grid);
+    cfg.blockDim = dim3((GEMV_WARPS + 1) * 32);
+    cfg.dynamicSmemBytes = m.smem_bytes;
+    cfg.stream = stream;
+    cudaLaunchAttribute at[1];
+    at[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    at[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = at;
+    cfg.numAttrs = m.pdl ? 1u : 0u;
+    return cudaLaunchKernelEx(&cfg, gemv_multi_kernel, m);
+}
+
 template <int FMT>
 static cudaError_t optin_fmt(size_t b) {
     cudaError_t e = cudaSuccess;
@@ -657,7 +750,7 @@ cudaError_t gemv_prepare_device(size_t smem_optin) {
     if ((e = optin_fmt<FMT_Q4_1>(smem_optin)) != cudaSuccess) return e;
     if ((e = optin_fmt<FMT_Q8_0>(smem_optin)) != cudaSuccess) return e;
     if ((e = optin_fmt<FMT_Q6_K>(smem_optin)) != cudaSuccess) return e;
-    return cudaSuccess;
+    return cudaFuncSetAttribute(gemv_multi_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_optin);
 }
 
 // ---- cross-GPU barrier (one rank per GPU; never run two ranks of it on one GPU) ----

@@ -93,6 +93,19 @@ struct GemvTune {
 bool gemv_plan(GemvArgs &a, int num_sms, size_t smem_optin, const GemvTune &tune);
 cudaError_t gemv_prepare_device(size_t smem_optin);  // opt in to large dynamic shared memory, once per device
 cudaError_t launch_gemv(const GemvArgs &a, cudaStream_t stream);
+// Several independent GEMVs side by side in one launch (see gemv_multi_kernel): p[i] as for launch_gemv (one weight,
+// one activation row, no pre-op), planned by gemv_multi_plan, which also deals the CTAs out: problem i runs on CTAs
+// [cta0[i], cta0[i + 1]).
+constexpr int GEMV_MULTI_MAX = 6;
+struct GemvMultiArgs {
+    GemvArgs p[GEMV_MULTI_MAX];
+    uint32_t n;
+    uint32_t cta0[GEMV_MULTI_MAX + 1];
+    uint32_t grid, smem_bytes, pdl;
+};
+static_assert(sizeof(GemvMultiArgs) <= 4000, "passed by value: kernel parameters are limited to 4 KB");
+bool gemv_multi_plan(GemvMultiArgs &m, int num_sms, size_t smem_optin, const GemvTune &tune);
+cudaError_t launch_gemv_multi(const GemvMultiArgs &m, cudaStream_t stream);
 // Bytes of the operand image of nbatch activation rows (what GemvArgs::xop points at), and the kernel that
 // writes it: the pre-op (RMSNorm in the reference's operand order, SwiGLU, GeGLU) and the per-32 int8
 // quantiser, one CTA per activation row. a / b / strides / eps / pre as in GemvArgs.

@@ -195,6 +195,7 @@ class GgufFile:
     # -- hand-over to the accelerator ------------------------------------------------
     def upload_tensor(self, accel, name, drop_pages=False):
         """True = adopted, False = declined (no kernel for the type / rank)."""
+        accel._rows = {}  # (the mirror's per-key row counts: a key may be replaced)
         rc = self._L.strix_cuda_upload_gguf_tensor(accel._h, self._g, name.encode(), int(drop_pages))
         if rc < 0:
             msg = accel._L.strix_cuda_last_error(accel._h).decode() or self._L.strix_gguf_last_error().decode()
@@ -204,6 +205,7 @@ class GgufFile:
     def upload_all(self, accel, drop_pages=False):
         """Returns (adopted, declined) tensor counts."""
         a, d = C.c_size_t(), C.c_size_t()
+        accel._rows = {}
         rc = self._L.strix_cuda_upload_gguf(accel._h, self._g, int(drop_pages), C.byref(a), C.byref(d))
         if rc < 0:
             msg = accel._L.strix_cuda_last_error(accel._h).decode() or self._L.strix_gguf_last_error().decode()

@@ -424,3 +424,96 @@ def test_fused_prologue_integer_form_at_the_contract(accel, orc, synth, pkg, pre
     print("fused %s + int8 + GEMV vs integer oracle: rel-L2 %.2e max-abs %.2e; codes moved by the operand order: %s of %d"
           % (pre, r, np.abs(got - want).max(), flips, K))
     assert r <= REL_L2_TOL
+
+
+@pytest.mark.parametrize("act_name", ["f32", "q8dot"])
+def test_gemv_batch_small_items_side_by_side(pkg, orc, synth, act_name):
+    """gemv_batch_dev / gemv_batch: independent items; the small ones run side by side in one launch (its CTAs dealt
+    out among them), the large ones as a launch each. Every result against the oracle at the contract and against
+    the item's own launch; with the option off; under stream capture; with an unknown key; after a weight of the
+    batch was replaced by one of another format (the cached graph must go)."""
+    import torch
+    act = pkg.ACT_F32 if act_name == "f32" else pkg.ACT_Q8DOT
+    shapes = [(synth.Q8_0, 2560, 1200), (synth.Q6_K, 2560, 1000), (synth.Q4_0, 4096, 777), (synth.Q8_0, 9728, 640),
+              (synth.Q6_K, 9728, 48), (synth.Q4_1, 1024, 331)]
+    up_of = lambda acc: {synth.Q8_0: acc.upload_q8_0, synth.Q6_K: acc.upload_q6_k, synth.Q4_0: acc.upload_q4_0,
+                         synth.Q4_1: acc.upload_q4_1}
+    acc = pkg.CudaWeightAccel(0)
+    try:
+        dev = torch.device("cuda", 0)
+        assert acc.set_option("batch_small_bytes", 8 << 20)       # items 0..2, 4, 5 are small, item 3 is not
+        keys, hx, xs, ys, want, ws = [], [], [], [], [], []
+
+        def oracle_of(i):
+            ty, k, n = shapes[i]
+            if act == pkg.ACT_F32:
+                return orc.qmatmul(hx[i], ws[i], ty, k, n)
+            xq, xd, _ = orc.xquant8(hx[i])
+            return orc.idot_gemm(ws[i], ty, xq, xd, 1, k, n)[0]
+
+        for i, (ty, k, n) in enumerate(shapes):
+            key = "bd.%d" % i
+            w = synth.quant(ty, 601, key, n, k)
+            assert up_of(acc)[ty](key, w, k, n)
+            x = synth.normal(602, key, k)
+            keys.append(key); hx.append(x); ws.append(w)
+            xs.append(torch.from_numpy(x).to(dev))
+            ys.append(torch.zeros(n, device=dev))
+            one = torch.zeros(n, device=dev)
+            assert acc.gemv_dev([key], xs[-1].data_ptr(), [one.data_ptr()], act=act)
+            torch.cuda.synchronize()
+            want.append(one.cpu().numpy())
+            assert rel_l2(want[-1], oracle_of(i)) <= REL_L2_TOL
+
+        def check(got_list, tag):
+            for i, g in enumerate(got_list):
+                r1, r2 = rel_l2(g, oracle_of(i)), rel_l2(g, want[i])
+                assert r1 <= REL_L2_TOL and r2 <= 1e-5, (tag, i, r1, r2)
+
+        for mode in (1, 2, 0):
+            assert acc.set_option("batch_side_by_side", mode)
+            for y in ys:
+                y.zero_()
+            assert acc.gemv_batch_dev(keys, [x.data_ptr() for x in xs], [y.data_ptr() for y in ys], act=act)
+            torch.cuda.synchronize()
+            check([y.cpu().numpy() for y in ys], "dev mode %d" % mode)
+            got = acc.gemv_batch(list(zip(keys, hx)), act=act)
+            check(got, "host mode %d" % mode)
+            got = acc.gemv_batch(list(zip(keys, hx)), act=act)   # the cached graph
+            check(got, "host mode %d again" % mode)
+        assert acc.set_option("batch_side_by_side", 1)
+        st = torch.cuda.Stream(device=dev)
+        with torch.cuda.stream(st):
+            assert acc.gemv_batch_dev(keys, [x.data_ptr() for x in xs], [y.data_ptr() for y in ys], act=act, stream=st.cuda_stream)
+            torch.cuda.synchronize()
+            g = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g, stream=st):
+                assert acc.gemv_batch_dev(keys, [x.data_ptr() for x in xs], [y.data_ptr() for y in ys], act=act,
+                                          stream=torch.cuda.current_stream().cuda_stream)
+            for y in ys:
+                y.zero_()
+            for _ in range(3):
+                g.replay()
+            torch.cuda.synchronize()
+        check([y.cpu().numpy() for y in ys], "captured")
+        assert acc.gemv_batch_dev(keys + ["nope"], [x.data_ptr() for x in xs] + [xs[0].data_ptr()],
+                                  [y.data_ptr() for y in ys] + [ys[0].data_ptr()], act=act) is False
+        got = acc.gemv_batch(list(zip(keys, hx)) + [("nope", hx[0])], act=act)
+        assert got[-1] is None
+        check(got[:-1], "host with an unknown key")
+        # replace item 0 (Q8_0 2560 -> 1200) by a Q4_0 weight of the same shape: same key, possibly the same address
+        ty, k, n = synth.Q4_0, 2560, 1200
+        shapes[0] = (ty, k, n)
+        ws[0] = synth.quant(ty, 603, keys[0], n, k)
+        assert acc.upload_q4_0(keys[0], ws[0], k, n)
+        one = torch.zeros(n, device=dev)
+        assert acc.gemv_dev([keys[0]], xs[0].data_ptr(), [one.data_ptr()], act=act)
+        torch.cuda.synchronize()
+        want[0] = one.cpu().numpy()
+        check(acc.gemv_batch(list(zip(keys, hx)), act=act), "host after the re-upload")
+        assert acc.gemv_batch_dev(keys, [x.data_ptr() for x in xs], [y.data_ptr() for y in ys], act=act)
+        torch.cuda.synchronize()
+        check([y.cpu().numpy() for y in ys], "dev after the re-upload")
+        assert acc.device_status() == 0
+    finally:
+        acc.close()
