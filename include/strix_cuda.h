@@ -63,10 +63,18 @@ typedef struct strix_cuda_opts {
     int rank;
     int world;
     /* 1 = time every launch with CUDA events and keep per-kernel totals
-     * (the reference's STRIX_PROF, decode.rs:25-69). */
+     * (the reference's STRIX_PROF, decode.rs:25-69); read them with
+     * strix_cuda_profile_dump. Launches no longer overlap while it is on (an
+     * event sits between them), and launches made inside a stream capture are
+     * not timed. */
     int profile;
     int reserved[5];
 } strix_cuda_opts;
+
+/* prof_dump (decode.rs:36-69): the per-kernel totals gathered since the last call (opts.profile or
+ * set_option("profile", 1)), most expensive first, as text; the totals are then reset. Waits for the device.
+ * Returns the length of the whole text; at most cap - 1 characters and a 0 are written to buf (which may be NULL). */
+STRIX_API size_t strix_cuda_profile_dump(strix_cuda *h, char *buf, size_t cap);
 
 /* RocmWeightAccel::new (decode.rs:565-829). `opts` may be NULL. */
 STRIX_API int strix_cuda_create(int device, const strix_cuda_opts *opts, strix_cuda **out);

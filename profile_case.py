@@ -4,6 +4,10 @@
     python profile_case.py gemm <tokens> <in_dim> <rows> [launches]
     python profile_case.py attn <context> [steps]
     python profile_case.py chain <layers> [tokens]
+    python profile_case.py multi <act 0|1> [launches]
+
+`multi`: the four small weights of the benchmark step (Q8_0 and Q6_K, 2560 -> 9728 and 9728 -> 2560) as one
+gemv_batch_dev call, i.e. side by side in one launch (``-k regex:gemv_multi_kernel``).
 
 `chain`: the decode configuration's layer shapes (hidden 2560, q 4096, k/v 1024, ffn 9728, Q4_0; Q6_K head over
 151936 rows) with <layers> layers, integer-dot form, run as the persistent chain kernel (``-k regex:chain_kernel``).
@@ -44,6 +48,21 @@ def main():
         y = torch.empty(n, device=dev)
         for _ in range(reps):
             acc.gemv_dev(["w"], x.data_ptr(), [y.data_ptr()], act=act, stream=s)
+    elif kind == "multi":
+        act = int(sys.argv[2])
+        reps = int(sys.argv[3]) if len(sys.argv) > 3 else 3
+        keys, xs, ys = [], [], []
+        for ty, k, n in ((8, 2560, 9728), (8, 9728, 2560), (14, 2560, 9728), (14, 9728, 2560)):
+            key = "w.%d.%d.%d" % (ty, k, n)
+            assert {8: acc.upload_q8_0, 14: acc.upload_q6_k}[ty](key, synth.quant(ty, 1, key, n, k), k, n)
+            keys.append(key)
+            xs.append(torch.randn(k, device=dev))
+            ys.append(torch.empty(n, device=dev))
+        flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
+        for _ in range(reps):
+            flush.zero_()   # (the 94 MB of weights would otherwise sit in L2 from the launch before)
+            assert acc.gemv_batch_dev(keys, [x.data_ptr() for x in xs], [y_.data_ptr() for y_ in ys], act=act, stream=s)
+        y = ys[0]
     elif kind == "chain":
         n_layers = int(sys.argv[2])
         reps = int(sys.argv[3]) if len(sys.argv) > 3 else 3

@@ -78,6 +78,7 @@ def load_library():
         C.c_int, C.POINTER(C.c_int))
     sig("strix_cuda_gemv_batch_dev", C.c_int, H, sz, C.POINTER(C.c_char_p), C.POINTER(C.c_void_p), C.POINTER(C.c_void_p), C.c_int,
         C.c_void_p)
+    sig("strix_cuda_profile_dump", C.c_size_t, H, C.c_char_p, C.c_size_t)
     sig("strix_cuda_gemv_dev", C.c_int, H, C.c_int, C.POINTER(C.c_char_p), C.c_void_p, C.c_void_p, C.c_float,
         C.c_int, C.c_int, C.POINTER(C.c_void_p), C.c_void_p)
     sig("strix_cuda_gemv_res_dev", C.c_int, H, C.c_int, C.POINTER(C.c_char_p), C.c_void_p, C.c_void_p, C.c_float,
@@ -561,6 +562,13 @@ class CudaWeightAccel:
                                                     C.c_void_p(int(d_b)) if d_b else None, float(eps), pre, act, yy,
                                                     C.c_void_p(int(stream)) if stream else None))
         return rc == 1
+
+    def profile_dump(self):
+        """Per-kernel totals since the last call (set_option("profile", 1) first), as text; resets them."""
+        n = self._L.strix_cuda_profile_dump(self._h, None, 0)
+        buf = C.create_string_buffer(n + 1)
+        self._L.strix_cuda_profile_dump(self._h, buf, n + 1)
+        return buf.value.decode()
 
     def gemv_batch_dev(self, keys, d_xs, d_ys, act=ACT_F32, stream=0):
         """n independent GEMVs on device vectors (ys[i] = W(keys[i]) xs[i]); the small ones run side by side in one launch."""

@@ -162,6 +162,43 @@ int upload_quant(strix_cuda *h, int fmt, const char *key, const uint8_t *bytes, 
 }  // namespace strix
 
 namespace strix {
+ProfScope::ProfScope(strix_cuda *h_, cudaStream_t s_, const char *name_) : h(h_), s(s_), name(name_) {
+    if (!h->profile) return;
+    cudaStreamCaptureStatus cap = cudaStreamCaptureStatusNone;
+    if (cudaStreamIsCapturing(s, &cap) != cudaSuccess || cap != cudaStreamCaptureStatusNone) {
+        cudaGetLastError();
+        return;
+    }
+    if (h->prof_pending.size() >= 8192) prof_fold(h);  // (bounded: fold what has run so far)
+    if (cudaEventCreate(&a) != cudaSuccess || cudaEventCreate(&b) != cudaSuccess) {
+        cudaGetLastError();
+        if (a) cudaEventDestroy(a);
+        a = b = nullptr;
+        return;
+    }
+    cudaEventRecord(a, s);
+}
+ProfScope::~ProfScope() {
+    if (!a) return;
+    cudaEventRecord(b, s);
+    h->prof_pending.push_back({name, a, b});
+}
+void prof_fold(strix_cuda *h) {
+    for (auto &p : h->prof_pending) {
+        float ms = 0.f;
+        if (cudaEventSynchronize(p.b) == cudaSuccess && cudaEventElapsedTime(&ms, p.a, p.b) == cudaSuccess) {
+            auto &t = h->prof_total[p.name];
+            t.first += ms;
+            t.second += 1;
+        } else {
+            cudaGetLastError();
+        }
+        cudaEventDestroy(p.a);
+        cudaEventDestroy(p.b);
+    }
+    h->prof_pending.clear();
+}
+
 void batch_release(strix_cuda *h) {
     if (h->batch_graph.exec) {
         cudaGraphExecDestroy(h->batch_graph.exec);
@@ -187,6 +224,7 @@ static int batch_enqueue_side_by_side(strix_cuda *h, const std::vector<size_t> &
         }
         if (ok) ok = gemv_multi_plan(m, h->num_sms, h->smem_optin, h->tune);
         if (ok) {
+            ProfScope prof(h, s, "gemv_multi");
             CU_TRY(h, launch_gemv_multi(m, s));
             continue;
         }
@@ -211,6 +249,46 @@ static std::vector<size_t> batch_small_items(const strix_cuda *h, size_t n, cons
     return small;
 }
 }  // namespace strix
+
+namespace strix {
+// "gemv.<format>.<activation form>" of a planned launch (string literals: ProfScope keeps the pointer)
+const char *gemv_prof_name(const GemvArgs &a) {
+    static const char *const names[4][3] = {{"gemv.q4_0.f32", "gemv.q4_0.q8dot", "gemv.q4_0.q8dot"},
+                                            {"gemv.q8_0.f32", "gemv.q8_0.q8dot", "gemv.q8_0.q8dot"},
+                                            {"gemv.q6_k.f32", "gemv.q6_k.q8dot", "gemv.q6_k.f32_digits"},
+                                            {"gemv.q4_1.f32", "gemv.q4_1.q8dot", "gemv.q4_1.q8dot"}};
+    const int f = a.L.fmt == FMT_Q4_0 ? 0 : a.L.fmt == FMT_Q8_0 ? 1 : a.L.fmt == FMT_Q6_K ? 2 : 3;
+    return names[f][a.digits ? 2 : a.act == STRIX_ACT_Q8DOT ? 1 : 0];
+}
+}  // namespace strix
+
+// Per-kernel totals since the last call, as text (most expensive first; the reference's prof_dump, decode.rs:36-69),
+// then reset. Returns the length of the whole text; at most cap - 1 characters of it are copied to buf.
+size_t strix_cuda_profile_dump(strix_cuda *h, char *buf, size_t cap) {
+    if (!h) return 0;
+    cudaSetDevice(h->device);
+    prof_fold(h);
+    std::vector<std::pair<std::string, std::pair<double, uint32_t>>> v(h->prof_total.begin(), h->prof_total.end());
+    std::sort(v.begin(), v.end(), [](const auto &x, const auto &y) { return x.second.first > y.second.first; });
+    double total = 0;
+    for (auto &e : v) total += e.second.first;
+    std::string out;
+    char line[256];
+    snprintf(line, sizeof line, "== strix profile: total kernel time %.3f ms ==\n", total);
+    out += line;
+    for (auto &e : v) {
+        snprintf(line, sizeof line, "  %24s  %9.3f ms  %6u calls  %5.1f%%  (%.4f ms/call)\n", e.first.c_str(), e.second.first,
+                 e.second.second, total > 0 ? e.second.first / total * 100.0 : 0.0, e.second.first / e.second.second);
+        out += line;
+    }
+    h->prof_total.clear();
+    if (buf && cap) {
+        const size_t n = std::min(out.size(), cap - 1);
+        memcpy(buf, out.data(), n);
+        buf[n] = 0;
+    }
+    return out.size();
+}
 
 // One GEMV launch over up to 3 resident weights that share the activation.
 namespace strix {
@@ -285,6 +363,7 @@ int gemv_launch_rows(strix_cuda *h, int nmat, const Resident *const *ws, const f
         // the in-kernel prologue: a second launch costs more than it saves there.
         if (act == STRIX_ACT_Q8DOT && chunk >= 2 && a.L.in_dim <= 16384u && h->tune.xop != 0) {
             if (ensure_xop(h, xop_image_bytes(a.L.fmt, a.L.in_dim, chunk)) < 0) return -1;
+            ProfScope prof(h, stream, "xop_prepare");
             CU_TRY(h, launch_xop_prepare(a.L.fmt, a.L.in_dim, chunk, c.a, pre == STRIX_PRE_RMSNORM ? d_b : c.b, a_stride,
                                          b_stride, eps, pre, h->xop, h->tune.pdl != 0, stream));
             c.xop = h->xop;
@@ -294,7 +373,10 @@ int gemv_launch_rows(strix_cuda *h, int nmat, const Resident *const *ws, const f
             c.mat[m].y = d_ys[m] + (size_t)done * c.mat[m].ystride;
             c.mat[m].res = (d_res && d_res[m]) ? d_res[m] + (size_t)done * c.mat[m].ystride : nullptr;
         }
-        CU_TRY(h, launch_gemv(c, stream));
+        {
+            ProfScope prof(h, stream, gemv_prof_name(c));
+            CU_TRY(h, launch_gemv(c, stream));
+        }
         done += chunk;
     }
     return 1;
@@ -360,6 +442,7 @@ void strix_cuda_destroy(strix_cuda *h) {
     cudaSetDevice(h->device);
     cudaStreamSynchronize(h->stream);
     decode_release(h);
+    prof_fold(h);
     if (h->copy_stream) cudaStreamDestroy(h->copy_stream);
     for (cudaEvent_t e : h->batch_events) cudaEventDestroy(e);
     batch_release(h);
@@ -598,7 +681,8 @@ int strix_cuda_gemv_batch(strix_cuda *h, size_t n, const char *const *keys, cons
         return 1;
     };
     constexpr size_t BATCH_GRAPH_MAX = 64;
-    const bool use_graph = n <= BATCH_GRAPH_MAX && h->use_batch_graph;
+    // (with per-kernel timing on, the launches are made directly: events inside a captured graph cannot be timed)
+    const bool use_graph = n <= BATCH_GRAPH_MAX && h->use_batch_graph && !h->profile;
     if (use_graph && !h->batch_flags) {
         CU_TRY(h, cudaMallocHost((void **)&h->batch_flags, BATCH_GRAPH_MAX * 4));
         CU_TRY(h, cudaMalloc(&h->d_one, 4));
@@ -795,7 +879,10 @@ int strix_cuda_gemv_peers_dev(strix_cuda *h, int nmat, const char *const *keys, 
         h->err = "gemv_peers_dev: in_dim too large for the shared-memory pipeline";
         return -1;
     }
-    CU_TRY(h, launch_gemv(a, static_cast<cudaStream_t>(stream)));
+    {
+        ProfScope prof(h, static_cast<cudaStream_t>(stream), gemv_prof_name(a));
+        CU_TRY(h, launch_gemv(a, static_cast<cudaStream_t>(stream)));
+    }
     return 1;
 }
 

@@ -1,6 +1,7 @@
 // Internal definition of the accelerator handle (shared by the .cu files that
 // implement groups of C-ABI entry points).
 #pragma once
+#include <map>
 #include <cuda_runtime.h>
 
 #include <string>
@@ -89,6 +90,14 @@ struct strix_cuda {
     // scratch of the prefill GEMM (grown on demand): f32 activations, their int8 codes, block scales,
     // block code sums, f32 output, split-K partials
     strix::DevBuf gm_x, gm_y, gm_part, gm_xd, gm_xc;
+    // Per-kernel timing (opts.profile / option "profile"; the reference's STRIX_PROF, decode.rs:25-69): every launch
+    // site brackets its kernel with two CUDA events; strix_cuda_profile_dump folds them into per-kernel totals.
+    struct ProfPending {
+        const char *name;
+        cudaEvent_t a, b;
+    };
+    std::vector<ProfPending> prof_pending;
+    std::map<std::string, std::pair<double, uint32_t>> prof_total;  // name -> (milliseconds, launches)
     strix_decode_state *decode = nullptr;  // configured projection chain (decode.cu), or null
     // mixture-of-experts layers adopted by upload_moe_q8 / upload_moe_q6 (moe.cu): the experts of a projection are one
     // resident stack "moe.<layer>.gate|up|down" of n_expert * rows-per-expert rows
@@ -111,6 +120,18 @@ struct strix_cuda {
 };
 
 namespace strix {
+// Brackets the launches made while it lives with two events on `s`, when profiling is on and `s` is not being
+// captured (events inside a capture cannot be timed). `name` must be a string literal.
+struct ProfScope {
+    strix_cuda *h;
+    cudaStream_t s;
+    const char *name;
+    cudaEvent_t a = nullptr, b = nullptr;
+    ProfScope(strix_cuda *h_, cudaStream_t s_, const char *name_);
+    ~ProfScope();
+};
+void prof_fold(strix_cuda *h);  // waits for the pending event pairs and adds them to the totals
+const char *gemv_prof_name(const GemvArgs &a);
 size_t shard_begin(size_t rows, int world, int r);
 int ensure_f32(strix_cuda *h, DevBuf &b, size_t n);
 int ensure_pinned(strix_cuda *h, PinBuf &b, size_t bytes);

@@ -147,6 +147,7 @@ int argmax_rows_enqueue(strix_cuda *h, const float *d_x, size_t n, size_t stride
     // one block per SM up to the scratch's width; at least 1024 entries per block
     uint32_t nb = (uint32_t)std::min<size_t>((size_t)std::min(h->num_sms, ARGMAX_MAX_BLOCKS), (n + 1023) / 1024);
     if (nb == 0) nb = 1;
+    ProfScope prof(h, stream, "argmax");
     argmax_rows_kernel<<<dim3(nb, (unsigned)rows), ARGMAX_THREADS, 0, stream>>>(
         d_x, (uint32_t)n, stride, static_cast<Best *>(h->am_part), h->am_ticket, h->am_idx, h->am_val);
     cudaError_t e = cudaGetLastError();

@@ -52,7 +52,7 @@ constexpr uint32_t CH_STEP_BYTES = 512;
 static_assert(sizeof(ChainStep) <= CH_STEP_BYTES && sizeof(ChainStep) % 16 == 0, "one 16-byte word per lane of a warp");
 constexpr uint32_t CH_STEP_OFF = CH_PART_OFF + CHAIN_PART_SLOTS * CH_WARPS * 16u * 4u;  // 3 consumer slots + 1 producer slot
 constexpr uint32_t CH_X_OFF = (CH_STEP_OFF + 4u * CH_STEP_BYTES + 127u) & ~127u;
-constexpr int CH_PASS_NI = 4;  // float4s a thread requests per pass over a row that needs no norm
+constexpr int CH_PASS_NI = 2;  // float4s a thread requests per pass over a row that needs no norm (see chain_prologue_q8)
 constexpr int CH_NORM_NI = 2;  // float4s a thread keeps across the RMSNorm reduction: normed rows up to 2 * 4 * 384 = 3072
 
 struct ChainCta {
@@ -316,8 +316,9 @@ __device__ __forceinline__ void chain_prologue_q8(const ChainStep &S, ChainCta &
 #pragma unroll
             for (int i = 0; i < 2; i++) quant_store(v[i], tid + i * ct, tid + i * ct < K4, l8, q6, bias, xbw, rec);
         } else {
-            // (four float4s per thread and pass: a pass costs one trip to L2 whatever it carries, and the longest
-            // row of the decode chain, ffn 9728, then takes two trips instead of four)
+            // (two float4s per thread and pass; four measured slower, 1.61 against 1.55 ms per token: the registers
+            // they take are spilled in the tile loop, and the time a row takes to arrive is set by the L2-to-SM
+            // paths it shares with the weight stream, not by the number of passes)
             for (uint32_t e0 = tid; e0 - lane < K4; e0 += (uint32_t)CH_PASS_NI * ct) {
                 float4 v[CH_PASS_NI];
                 fetch_pass<CH_PASS_NI>(S, C, e0, ct, K4, v);

@@ -225,6 +225,7 @@ static int attention_enqueue(strix_cuda *h, strix_decode_state *d, const strix_d
     A.theta = L.theta;
     A.scale = L.scale;
     A.status = h->d_status;
+    ProfScope prof(h, s, "attention");
     const cudaError_t e = launch_attention_step(A, s);
     if (e != cudaSuccess) {
         h->err = std::string("attention: ") + cudaGetErrorString(e);
@@ -236,6 +237,7 @@ static int attention_enqueue(strix_cuda *h, strix_decode_state *d, const strix_d
 // The sandwich residual after the o (which = 0) or down (which = 1) projection of a post_norm model.
 static int post_enqueue(strix_cuda *h, strix_decode_state *d, const strix_decode_state::Layer &L, int which, float *hid,
                         const float *t, uint32_t rows, cudaStream_t s) {
+    ProfScope prof(h, s, "addnorm");
     const cudaError_t e = launch_addnorm(hid, t, which ? L.post_ffw : L.post_attn, d->cfg.hidden, d->cfg.eps,
                                          which ? L.out_scale : 1.0f, rows, s);
     if (e != cudaSuccess) {
@@ -377,6 +379,7 @@ static const strix_decode_state::Program *chain_program(strix_cuda *h, strix_dec
 // Enqueue the whole chain on `s`. Returns 1, or <0 with h->err set.
 static int enqueue_chain(strix_cuda *h, strix_decode_state *d, cudaStream_t s) {
     if (const strix_decode_state::Program *p = chain_program(h, d, s)) {
+        ProfScope prof(h, s, "chain");
         CU_TRY(h, launch_chain(p->d_steps, p->n_steps, p->geom, d->d_ctl, h->d_status, h->poll_limit, h->chain_debug, d->d_trace,
                                h->num_sms, s));
         return 1;

@@ -79,6 +79,7 @@ static int gemm_device(strix_cuda *h, Resident *r, const float *d_xs, size_t m, 
     const uint32_t splits = gemm_pick_splits((uint32_t)m, (uint32_t)r->rows, (uint32_t)nb, h->num_sms);
     const size_t wsf = gemm_workspace_floats((uint32_t)m, (uint32_t)r->rows, splits);
     if (wsf && ensure_f32(h, h->gm_part, wsf) < 0) return -1;
+    ProfScope prof(h, stream, "gemm_w8a8");  // (quantiser, GEMM and split-K reduction together)
     CU_TRY(h, launch_xquant8_sum(d_xs, h->gm_xq, h->gm_xd.p, h->gm_xs, h->gm_xc.p, (uint32_t)m, (uint32_t)nb, stream));
     CU_TRY(h, launch_gemm_w8a8(r->gemm_codes, r->L, (uint32_t)r->rows, r->scalesT, h->gm_xq, h->gm_xd.p, h->gm_xs, h->gm_xc.p,
                               (uint32_t)m, d_y, h->gm_part.p, splits, 0, nullptr, h->d_status, stream));
@@ -219,6 +220,7 @@ int strix_cuda_debug_gemm_mode_dev(strix_cuda *h, const char *key, const float *
     const uint32_t splits = gemm_pick_splits((uint32_t)m, (uint32_t)r->rows, (uint32_t)nb, h->num_sms);
     const size_t wsf = gemm_workspace_floats((uint32_t)m, (uint32_t)r->rows, splits);
     if (wsf && ensure_f32(h, h->gm_part, wsf) < 0) return -1;
+    ProfScope prof(h, st, "gemm_w8a8");
     CU_TRY(h, launch_xquant8_sum(d_xs, h->gm_xq, h->gm_xd.p, h->gm_xs, h->gm_xc.p, (uint32_t)m, (uint32_t)nb, st));
     for (int i = 0; i < reps; i++)
         CU_TRY(h, launch_gemm_w8a8(r->gemm_codes, r->L, (uint32_t)r->rows, r->scalesT, h->gm_xq, h->gm_xd.p, h->gm_xs,

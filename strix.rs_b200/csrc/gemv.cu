@@ -686,7 +686,18 @@ bool gemv_multi_plan(GemvMultiArgs &m, int num_sms, size_t smem_optin, const Gem
         groups[i] = (a.mat[0].rows + TILE_ROWS - 1) / TILE_ROWS;
         nc[i] = 1;
     }
-    auto load = [&](uint32_t i) { return (uint64_t)((groups[i] + nc[i] - 1u) / nc[i]) * m.p[i].L.group_bytes; };
+    // what a row group costs a CTA, in bytes streamed at the rate a CTA sustains for this format and activation form
+    // (Q8_0 runs at the memory pipeline's pace; the others are bound by instruction issue: measured fractions of
+    // the copy peak on large launches are 0.93 Q8_0, 0.74 Q6_K as digits or int8, 0.60 Q6_K and Q4_0 on f16 tiles,
+    // 0.74 Q4_0 int8)
+    auto slow = [&](uint32_t i) -> uint64_t {
+        const GemvArgs &a = m.p[i];
+        const bool f16_tiles = a.act == STRIX_ACT_F32 && !(a.L.fmt == FMT_Q6_K && tune.digits_rule != 0 &&
+                                                            (a.L.in_dim <= 8192u || tune.digits_rule == 2));
+        if (a.L.fmt == FMT_Q8_0) return 100;
+        return f16_tiles ? 155 : 125;
+    };
+    auto load = [&](uint32_t i) { return (uint64_t)((groups[i] + nc[i] - 1u) / nc[i]) * m.p[i].L.group_bytes * slow(i); };
     for (uint32_t left = (uint32_t)num_sms - n; left > 0; left--) {
         uint32_t worst = n;
         for (uint32_t i = 0; i < n; i++)

@@ -186,6 +186,7 @@ int moe_launch(strix_cuda *h, GemvArgs &c, uint32_t rows_nbatch, int pre, const 
             return -1;
         }
     }
+    ProfScope prof(h, s, "gemv.moe");
     CU_TRY(h, launch_gemv(c, s));
     return 0;
 }

@@ -60,6 +60,7 @@ pub const PRE_GEGLU: c_int = 3;
 #[link(name = "strix_cuda")]
 extern "C" {
     // ---- include/strix_cuda.h
+    pub fn strix_cuda_profile_dump(h: *mut StrixCuda, buf: *mut c_char, cap: usize) -> usize;
     pub fn strix_cuda_create(device: c_int, opts: *const StrixCudaOpts, out: *mut *mut StrixCuda) -> c_int;
     pub fn strix_cuda_destroy(h: *mut StrixCuda);
     pub fn strix_cuda_last_error(h: *mut StrixCuda) -> *const c_char;

@@ -517,3 +517,35 @@ def test_gemv_batch_small_items_side_by_side(pkg, orc, synth, act_name):
         assert acc.device_status() == 0
     finally:
         acc.close()
+
+
+def test_profile_option_times_every_launch(pkg, synth):
+    """opts.profile / set_option("profile", 1): the reference's STRIX_PROF (decode.rs:25-69). Every launch made
+    outside a capture is bracketed by events; profile_dump names the kernels with their launch counts and
+    resets; with the option off nothing is recorded."""
+    acc = pkg.CudaWeightAccel(0)
+    try:
+        k, n = 1024, 640
+        assert acc.upload_q8_0("p.a", synth.quant(synth.Q8_0, 611, "p.a", n, k), k, n)
+        assert acc.upload_q6_k("p.b", synth.quant(synth.Q6_K, 611, "p.b", n, k), k, n)
+        x = synth.normal(612, "p.x", k)
+        assert "total kernel time 0.000" in acc.profile_dump()
+        acc.gemv("p.a", x)                                   # option off: not recorded
+        assert "gemv" not in acc.profile_dump()
+        assert acc.set_option("profile", 1)
+        for _ in range(3):
+            acc.gemv("p.a", x)
+        acc.gemv("p.b", x, act=pkg.ACT_Q8DOT)
+        acc.gemv_batch([("p.a", x), ("p.b", x)])             # two small items: one side-by-side launch
+        txt = acc.profile_dump()
+        print(txt)
+        lines = {ln.split()[0]: ln for ln in txt.splitlines()[1:]}
+        assert "gemv.q8_0.f32" in lines and " 3 calls" in lines["gemv.q8_0.f32"]
+        assert "gemv.q6_k.q8dot" in lines and " 1 calls" in lines["gemv.q6_k.q8dot"]
+        assert "gemv_multi" in lines and " 1 calls" in lines["gemv_multi"]
+        assert "total kernel time 0.000" in acc.profile_dump()   # reset by the dump
+        assert acc.set_option("profile", 0)
+        acc.gemv("p.a", x)
+        assert "gemv" not in acc.profile_dump()
+    finally:
+        acc.close()
