@@ -72,8 +72,9 @@ typedef struct strix_cuda_opts {
 } strix_cuda_opts;
 
 /* prof_dump (decode.rs:36-69): the per-kernel totals gathered since the last call (opts.profile or
- * set_option("profile", 1)), most expensive first, as text; the totals are then reset. Waits for the device.
- * Returns the length of the whole text; at most cap - 1 characters and a 0 are written to buf (which may be NULL). */
+ * set_option("profile", 1)), most expensive first, as text. Waits for the device. Returns the length of the whole
+ * text; with buf != NULL at most cap - 1 characters and a 0 are written to it and the totals are reset; with
+ * buf == NULL (a sizing call) nothing is reset. */
 STRIX_API size_t strix_cuda_profile_dump(strix_cuda *h, char *buf, size_t cap);
 
 /* RocmWeightAccel::new (decode.rs:565-829). `opts` may be NULL. */

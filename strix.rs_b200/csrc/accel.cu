@@ -262,8 +262,9 @@ const char *gemv_prof_name(const GemvArgs &a) {
 }
 }  // namespace strix
 
-// Per-kernel totals since the last call, as text (most expensive first; the reference's prof_dump, decode.rs:36-69),
-// then reset. Returns the length of the whole text; at most cap - 1 characters of it are copied to buf.
+// Per-kernel totals since the last reset, as text (most expensive first; the reference's prof_dump, decode.rs:36-69).
+// Returns the length of the whole text; with a buffer, at most cap - 1 characters of it are copied and the totals are
+// reset; without one (a sizing call) they are kept.
 size_t strix_cuda_profile_dump(strix_cuda *h, char *buf, size_t cap) {
     if (!h) return 0;
     cudaSetDevice(h->device);
@@ -281,11 +282,11 @@ size_t strix_cuda_profile_dump(strix_cuda *h, char *buf, size_t cap) {
                  e.second.second, total > 0 ? e.second.first / total * 100.0 : 0.0, e.second.first / e.second.second);
         out += line;
     }
-    h->prof_total.clear();
     if (buf && cap) {
         const size_t n = std::min(out.size(), cap - 1);
         memcpy(buf, out.data(), n);
         buf[n] = 0;
+        h->prof_total.clear();  // (a call without a buffer only asks for the length)
     }
     return out.size();
 }
@@ -646,6 +647,7 @@ int strix_cuda_gemv_batch(strix_cuda *h, size_t n, const char *const *keys, cons
             dxs[i] = h->x.p + xoff[i];
             dys[i] = h->y.p + yoff[i];
         }
+    constexpr size_t BATCH_GRAPH_MAX = 64;
     // What the device does for this batch: H2D of the activations, then per unit its kernel(s) on the main
     // stream and, on the copy stream, its outputs' D2H followed by a one-word copy that raises the unit's
     // pinned flag. `graph`: the same sequence is being captured (the copy stream joins the main one at the
@@ -677,14 +679,16 @@ int strix_cuda_gemv_batch(strix_cuda *h, size_t n, const char *const *keys, cons
         }
         if (graph && last) CU_TRY(h, cudaStreamWaitEvent(h->stream, last, 0));
         // (the status word goes to ordinary host memory: that copy stays outside the graph)
-        if (!graph) CU_TRY(h, cudaMemcpyAsync(&h->status_host, h->d_status, 4, cudaMemcpyDeviceToHost, h->stream));
+        if (!graph) CU_TRY(h, cudaMemcpyAsync((void *)(h->batch_flags + BATCH_GRAPH_MAX), h->d_status, 4, cudaMemcpyDeviceToHost, h->stream));
         return 1;
     };
-    constexpr size_t BATCH_GRAPH_MAX = 64;
     // (with per-kernel timing on, the launches are made directly: events inside a captured graph cannot be timed)
     const bool use_graph = n <= BATCH_GRAPH_MAX && h->use_batch_graph && !h->profile;
-    if (use_graph && !h->batch_flags) {
-        CU_TRY(h, cudaMallocHost((void **)&h->batch_flags, BATCH_GRAPH_MAX * 4));
+    if (!h->batch_flags) {
+        // pinned: one word per unit of a captured batch, and after them the copy of the device status word (into
+        // pageable memory that copy would hold the host until the whole batch has run, and no output could be
+        // handed over while later kernels still run)
+        CU_TRY(h, cudaMallocHost((void **)&h->batch_flags, (BATCH_GRAPH_MAX + 1) * 4));
         CU_TRY(h, cudaMalloc(&h->d_one, 4));
         const uint32_t one = 1;
         CU_TRY(h, cudaMemcpy(h->d_one, &one, 4, cudaMemcpyHostToDevice));
@@ -738,7 +742,7 @@ int strix_cuda_gemv_batch(strix_cuda *h, size_t n, const char *const *keys, cons
         }
         for (size_t u = 0; u < nu; u++) h->batch_flags[u] = 0u;
         CU_TRY(h, cudaGraphLaunch(bg.exec, h->stream));
-        CU_TRY(h, cudaMemcpyAsync(&h->status_host, h->d_status, 4, cudaMemcpyDeviceToHost, h->stream));
+        CU_TRY(h, cudaMemcpyAsync((void *)(h->batch_flags + BATCH_GRAPH_MAX), h->d_status, 4, cudaMemcpyDeviceToHost, h->stream));
         // hand each output to the caller as its flag comes up (bounded: once the stream has drained,
         // everything has landed whatever the flag says)
         for (size_t u = 0; u < nu; u++) {
@@ -755,7 +759,7 @@ int strix_cuda_gemv_batch(strix_cuda *h, size_t n, const char *const *keys, cons
         }
     }
     CU_TRY(h, cudaStreamSynchronize(h->stream));
-    const uint32_t st = h->status_host;
+    const uint32_t st = h->batch_flags[BATCH_GRAPH_MAX];
     if (st != 0) {
         h->err = "gemv: device status " + std::to_string(st) + " (a bounded wait ran out)";
         cudaMemsetAsync(h->d_status, 0, 4, h->stream);
