@@ -768,10 +768,10 @@ def main():
     stream = torch.cuda.Stream(device=dev)
 
     # The six GEMVs do not depend on one another: the step is ONE gemv_batch_dev call (the trait's gemv_batch on
-    # device vectors). The library runs a shard above 64 MiB as a launch of its own and the smaller ones side by
+    # device vectors). The library runs a shard above 256 MiB as a launch of its own and the smaller ones side by
     # side in one launch (up to six problems; its CTAs dealt out among them). The same rule here, for the launch
     # count and the per-launch events: units = lists of items that share a launch.
-    SMALL = 64 << 20
+    SMALL = 256 << 20
     def shard_bytes(it):
         be, bb = BLOCK[it["ty"]]
         return it["rows"] * (it["k"] // be) * bb

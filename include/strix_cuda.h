@@ -177,7 +177,7 @@ STRIX_API int strix_cuda_peer_barrier_dev(strix_cuda *h, uint32_t *d_epoch, uint
 /* WeightAccel::gemv_batch (accel.rs:397-399; decode.rs:3227-3255) for device-resident vectors: n INDEPENDENT GEMVs,
  * d_ys[i] = W(keys[i]) d_xs[i], enqueued from `stream` (no copies, no synchronisation). Independent means: no item
  * reads or writes what another writes; the items then need not run in the order given. Items whose weights are at
- * most "batch_small_bytes" (set_option; 64 MiB) run SIDE BY SIDE in one launch, up to 6 per launch: its CTAs are
+ * most "batch_small_bytes" (set_option; 256 MiB) run SIDE BY SIDE in one launch, up to 6 per launch: its CTAs are
  * dealt out among the items by their bytes, so the launch fills and drains once for all of them (a launch of its
  * own costs such an item more in fill and drain than its weights take to stream). The others get a launch each,
  * before it. The host-pointer form strix_cuda_gemv_batch splits a batch the same way.
