@@ -259,28 +259,24 @@ class CudaWeightAccel:
         n = len(calls)
         if n == 0:
             return []
-        # rows of each weight held here (what the output buffers need), remembered until the next upload
-        rows = getattr(self, "_rows", None)
-        if rows is None:
-            rows = self._rows = {}
-        nrows = []
-        for k, _ in calls:
-            r = rows.get(k, -1)
-            if r < 0:
-                info = self.weight_info(k)
-                r = rows[k] = info["rows"] if info else 0
-                if info is None:
-                    del rows[k]          # (an unknown key may be uploaded later through another path)
-                    r = None
-            nrows.append(r)
+        # What depends on the keys only (their C strings, the rows each weight holds here, the capacity array) is
+        # kept until the next upload: a token step repeats the same batch.
+        plans = getattr(self, "_rows", None)
+        if plans is None:
+            plans = self._rows = {}
+        names = tuple(k for k, _ in calls)
+        plan = plans.get(names)
+        if plan is None:
+            infos = [self.weight_info(k) for k in names]
+            nrows = [i["rows"] if i else None for i in infos]
+            plan = plans[names] = (nrows, (C.c_char_p * n)(*[k.encode() for k in names]),
+                                   (C.c_size_t * n)(*[r or 0 for r in nrows]), (C.c_int * n)())
+        nrows, keys, yc, st = plan
         xs = [_f32(x) for _, x in calls]
         ys = [np.empty(r or 0, dtype=np.float32) for r in nrows]
-        keys = (C.c_char_p * n)(*[k.encode() for k, _ in calls])
         xp = (C.c_void_p * n)(*[x.ctypes.data for x in xs])
         yp = (C.c_void_p * n)(*[y.ctypes.data for y in ys])
         ks = (C.c_size_t * n)(*[x.size for x in xs])
-        yc = (C.c_size_t * n)(*[y.size for y in ys])
-        st = (C.c_int * n)()
         self._check(self._L.strix_cuda_gemv_batch(self._h, n, keys, xp, ks, yp, yc, act, st))
         return [ys[i] if (nrows[i] is not None and st[i] == 1) else None for i in range(n)]
 
@@ -324,6 +320,7 @@ class CudaWeightAccel:
 
     # ---- mixture-of-experts layers (accel.rs:167-246) ----
     def _upload_moe(self, fn, layer, gate, up, down, hidden, eff, ne):
+        self._rows = {}
         g, u, d = (np.ascontiguousarray(np.frombuffer(b, dtype=np.uint8) if not isinstance(b, np.ndarray) else b.view(np.uint8))
                    for b in (gate, up, down))
         u8 = lambda a: a.ctypes.data_as(C.POINTER(C.c_uint8))
