@@ -272,6 +272,51 @@ def decode_chain_extra(pkg, synth, torch, device, stream):
     return out
 
 
+def share_tensor(acc, dist, t, rank, world, opened):
+    """Device pointers of every rank's copy of tensor t: the owner exports the CUDA IPC handle of the allocation
+    (through torch, which knows its base) and the offset of t in it; the library opens each handle once, with this
+    rank's device current. `opened`: (rank, handle) -> mapped base, shared between calls."""
+    meta = t.untyped_storage()._share_cuda_()
+    handle = bytes(meta[1])
+    if len(handle) == 66 and handle[1:2] == b"c":
+        handle = handle[2:]      # torch prefixes a version byte and a type byte ('c' = cudaMalloc)
+    if len(handle) != 64:
+        raise RuntimeError("torch exported a %d-byte handle: not a plain cudaMalloc allocation" % len(handle))
+    mine = (handle, int(meta[3]) + t.storage_offset() * t.element_size())
+    metas = [None] * world
+    dist.all_gather_object(metas, mine)
+    ptrs = []
+    for r, (handle, offset) in enumerate(metas):
+        if r == rank:
+            ptrs.append(t.data_ptr())
+            continue
+        if (r, handle) not in opened:
+            opened[(r, handle)] = acc.ipc_open(handle)
+        ptrs.append(opened[(r, handle)] + offset)
+    return ptrs
+
+
+def check_peer_mappings(acc, dist, torch, named, ptrs, rank, world):
+    """Every mapping is checked with a copy-engine read before any kernel stores through it: each rank leaves a mark
+    in the last word of each of its buffers and reads its peers' marks. named: [(name, int32-viewable tensor)]."""
+    marks = {}
+    for i, (nm, t) in enumerate(named):
+        marks[nm] = (t, 0x5EED0000 + 256 * i)
+        t.view(torch.int32)[-1] = marks[nm][1] + rank
+    torch.cuda.synchronize()
+    dist.barrier()
+    for nm, (t, mark) in marks.items():
+        for r in range(world):
+            got = acc.peek_u32(ptrs[nm][r] + 4 * (t.numel() - 1))
+            if got != mark + r:
+                raise RuntimeError("peer mapping of %s on rank %d reads %#x, expected %#x" % (nm, r, got, mark + r))
+    dist.barrier()
+    for nm, (t, mark) in marks.items():
+        t.view(torch.int32)[-1] = 0
+    torch.cuda.synchronize()
+    dist.barrier()
+
+
 def decode_chain_sharded_extra(pkg, synth, torch, dist, local, stream, rank, world):
     """configs[3] on `world` GPUs: every projection row-sharded, an NCCL all-gather after each sharded
     projection or group (q|k|v and gate|up gathered in one coalesced call each). Every rank runs this."""
@@ -794,33 +839,95 @@ def main():
         torch.cuda.synchronize()
 
     # ---- resident-input throughput: one step captured in a CUDA graph, replayed ----------
-    with torch.cuda.stream(stream):
-        for _ in range(2):
-            step_device()
-        torch.cuda.synchronize()
-        graph = torch.cuda.CUDAGraph()
-        with torch.cuda.graph(graph, stream=stream):
-            step_device()
-        for _ in range(args.warmup):
-            graph.replay()
-        barrier()
-        sampler = ClockSampler(local)
-        if rank == 0:
-            sampler.start()
-        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        barrier()
-        e0.record()
-        for _ in range(args.steps * REPLAYS):
-            graph.replay()
-        e1.record()
-        barrier()
-        ms_total = e0.elapsed_time(e1) / REPLAYS
-    if acc.device_status() != 0:
-        raise SystemExit("device status word is non-zero: a bounded wait ran out")
-    t = torch.tensor([ms_total], device=dev)
+    sampler = ClockSampler(local)
+
+    def time_step(step_fn, sample_clocks):
+        """ms per step of step_fn: W warm-up replays of its CUDA graph, then K x REPLAYS timed ones between barriers,
+        CUDA events on the launching stream, the slowest rank's time."""
+        with torch.cuda.stream(stream):
+            for _ in range(2):
+                step_fn()
+            torch.cuda.synchronize()
+            g_ = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g_, stream=stream):
+                step_fn()
+            for _ in range(args.warmup):
+                g_.replay()
+            barrier()
+            if rank == 0 and sample_clocks:
+                sampler.start()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            barrier()
+            e0.record()
+            for _ in range(args.steps * REPLAYS):
+                g_.replay()
+            e1.record()
+            barrier()
+            ms_total = e0.elapsed_time(e1) / REPLAYS
+        st_ = torch.tensor([acc.device_status()], device=dev)
+        if world > 1:
+            dist.all_reduce(st_, op=dist.ReduceOp.MAX)   # (every rank takes the same way out)
+        if st_.item() != 0:
+            if sample_clocks:
+                raise SystemExit("device status word is non-zero: a bounded wait ran out")
+            acc.clear_device_status()
+            torch.cuda.synchronize()
+            raise RuntimeError("a bounded wait ran out (device status %d)" % int(st_.item()))
+        t = torch.tensor([ms_total], device=dev)
+        if world > 1:
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item()) / args.steps, g_
+
+    ms_step, graph = time_step(step_device, True)
+    exchange = None
     if world > 1:
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-    ms_step = float(t.item()) / args.steps
+        # The same step with the output exchange fused into the kernels: every rank's kernels store their rows
+        # straight into the full output vectors of ALL ranks (plain stores into CUDA-IPC-mapped peer memory over
+        # NVLink), and a one-warp flag barrier replaces the all-gather. Checked against the gathered result, bit
+        # for bit; the faster form that checks out is the one reported as `value`.
+        exchange = {"nccl_all_gather_ms_per_step": round(ms_step, 5), "peer_stores_ms_per_step": None, "form": "nccl all-gather"}
+        try:
+            foff, tot = [], 0
+            for it in items:
+                foff.append(tot)
+                tot += (it["n"] + 31) & ~31
+            y_full = torch.zeros(tot + 32, device=dev)
+            flags = torch.zeros(8, dtype=torch.int32, device=dev)
+            epoch = torch.zeros(1, dtype=torch.int32, device=dev)
+            opened = {}
+            ptrs = {"y": share_tensor(acc, dist, y_full, rank, world, opened),
+                    "flags": share_tensor(acc, dist, flags, rank, world, opened)}
+            check_peer_mappings(acc, dist, torch, [("y", y_full), ("flags", flags)], ptrs, rank, world)
+            peer_ys = [[ptrs["y"][r] + 4 * foff[i] for r in range(world)] for i in range(len(items))]
+
+            def step_peers():
+                s = torch.cuda.current_stream().cuda_stream
+                assert acc.gemv_batch_peers_dev([it["key"] for it in items], [it["x"].data_ptr() for it in items], peer_ys,
+                                                act=pkg.ACT_F32, stream=s)
+                acc.peer_barrier_dev(epoch.data_ptr(), flags.data_ptr(), ptrs["flags"], stream=s)
+
+            ms_peers, graph_peers = time_step(step_peers, False)
+            # the gathered result of the NCCL form, item by item, against what the peer stores left on this rank
+            graph.replay()
+            torch.cuda.synchronize()
+            same = True
+            for i, it in enumerate(items):
+                per = -(-it["n"] // world)
+                got = y_full[foff[i]:foff[i] + it["n"]]
+                parts = [y_all[r * off + it["off"]:r * off + it["off"] + (pkg.shard_begin(it["n"], world, r + 1) - pkg.shard_begin(it["n"], world, r))]
+                         for r in range(world)]
+                same = same and bool(torch.equal(got, torch.cat(parts)))
+                del per
+            ok = torch.tensor([1 if same else 0], device=dev)
+            dist.all_reduce(ok, op=dist.ReduceOp.MIN)
+            exchange["peer_stores_ms_per_step"] = round(ms_peers, 5)
+            exchange["peer_stores_equal_to_gathered"] = bool(ok.item())
+            if ok.item() and ms_peers < ms_step:
+                ms_step = ms_peers
+                exchange["form"] = "peer stores + flag barrier"
+            del graph_peers
+        except Exception as ex:   # the NCCL form stands on its own
+            exchange["why_not_peer_stores"] = "%s: %s" % (type(ex).__name__, ex)
     value = step_bytes / (ms_step * 1e-3) / 1e9
 
     # ---- end to end through the host API: host x in, host y out, one sync per step --------
@@ -1026,7 +1133,8 @@ def main():
             "scaling": "strong" if world > 1 else "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
             "config": bench_config(), "bytes_per_step": step_bytes, "replays_per_step": REPLAYS,
             "parallelism": "rows sharded over %d GPU(s)%s" % (
-                world, ", one NCCL all-gather of the six output shards per step" if world > 1 else ""),
+                world, ", outputs exchanged once per step (%s)" % exchange["form"] if world > 1 else ""),
+            "exchange": exchange,
             "e2e": {"value": round(e2e_val, 2), "unit": "GB/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
             "gpu_launches": args.steps * REPLAYS * len(units), "launches_per_step": len(units),
             "clocks": clocks, "roofline": roof, "cpu_baseline": cpu, "per_weight": detail, "extras": extras,

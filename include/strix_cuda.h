@@ -185,6 +185,14 @@ STRIX_API int strix_cuda_peer_barrier_dev(strix_cuda *h, uint32_t *d_epoch, uint
  * 0 = an unknown key or a null vector. */
 STRIX_API int strix_cuda_gemv_batch_dev(strix_cuda *h, size_t n, const char *const *keys, const float *const *d_xs,
                               float *const *d_ys, int act, void *stream);
+/* The row-sharded form of strix_cuda_gemv_batch_dev (no counterpart in the reference, which is single-device,
+ * hip.rs:149; BASELINE's "output all-gather" fused into the kernels): item i's rows are stored by the kernels
+ * themselves into the FULL output vector of weight i on every accelerator of the group,
+ * peer_ys[i * n_peers + p][row0 + r] for p < n_peers (peer-mapped device memory, see strix_cuda_ipc_open; this GPU's
+ * own copy is one of them), with plain stores over NVLink. No collective follows; strix_cuda_peer_barrier_dev on the
+ * same stream makes the vectors safe to read on every rank. */
+STRIX_API int strix_cuda_gemv_batch_peers_dev(strix_cuda *h, size_t n, const char *const *keys, const float *const *d_xs,
+                                    int n_peers, float *const *peer_ys, int act, void *stream);
 /* WeightAccel::prefill_q8_gemm (accel.rs:213; decode.rs:3257-3297): y[m][rows] = W8A8 GEMM of m
  * token rows xs[m][in_dim] with a resident Q8_0 weight: per-32 int8 activations (xquant8_rows,
  * kernels.rs:1000-1013), int32 block sums on tcgen05, f32 combine with both block scales

@@ -79,6 +79,8 @@ def load_library():
     sig("strix_cuda_gemv_batch_dev", C.c_int, H, sz, C.POINTER(C.c_char_p), C.POINTER(C.c_void_p), C.POINTER(C.c_void_p), C.c_int,
         C.c_void_p)
     sig("strix_cuda_profile_dump", C.c_size_t, H, C.c_char_p, C.c_size_t)
+    sig("strix_cuda_gemv_batch_peers_dev", C.c_int, H, sz, C.POINTER(C.c_char_p), C.POINTER(C.c_void_p), C.c_int,
+        C.POINTER(C.c_void_p), C.c_int, C.c_void_p)
     sig("strix_cuda_gemv_dev", C.c_int, H, C.c_int, C.POINTER(C.c_char_p), C.c_void_p, C.c_void_p, C.c_float,
         C.c_int, C.c_int, C.POINTER(C.c_void_p), C.c_void_p)
     sig("strix_cuda_gemv_res_dev", C.c_int, H, C.c_int, C.POINTER(C.c_char_p), C.c_void_p, C.c_void_p, C.c_float,
@@ -574,6 +576,17 @@ class CudaWeightAccel:
         xx = (C.c_void_p * n)(*[int(p) for p in d_xs])
         yy = (C.c_void_p * n)(*[int(p) for p in d_ys])
         rc = self._check(self._L.strix_cuda_gemv_batch_dev(self._h, n, kk, xx, yy, act, C.c_void_p(int(stream)) if stream else None))
+        return rc == 1
+
+    def gemv_batch_peers_dev(self, keys, d_xs, peer_ys, act=ACT_F32, stream=0):
+        """Row-sharded gemv_batch_dev: peer_ys[i] = the device pointers of item i's FULL output vector on every
+        accelerator of the group (own copy included); the kernels store this shard's rows into all of them."""
+        n, npeer = len(keys), len(peer_ys[0])
+        kk = (C.c_char_p * n)(*[k.encode() for k in keys])
+        xx = (C.c_void_p * n)(*[int(p) for p in d_xs])
+        pp = (C.c_void_p * (n * npeer))(*[int(p) for ys in peer_ys for p in ys])
+        rc = self._check(self._L.strix_cuda_gemv_batch_peers_dev(self._h, n, kk, xx, npeer, pp, act,
+                                                                C.c_void_p(int(stream)) if stream else None))
         return rc == 1
 
     def gemv_peers_dev(self, keys, d_a, peer_ys, d_b=0, eps=0.0, pre=PRE_NONE, act=ACT_F32, stream=0, d_res=None):

@@ -209,8 +209,37 @@ void batch_release(strix_cuda *h) {
 // Items idx of a batch (independent GEMVs ws[i], d_xs[i] -> d_ys[i]) side by side: up to GEMV_MULTI_MAX problems
 // per launch (gemv_multi_kernel), the CTAs dealt out among them by their bytes. What cannot be planned that way
 // gets a launch of its own.
+// peer_ys (may be null): the row-sharded multi-GPU form - item i's rows go straight into the FULL output vector of
+// every accelerator of the group, peer_ys[i * n_peers + p] (peer-mapped device memory, this GPU's own copy among
+// them), at row_base + row, instead of into d_ys[i].
+static void batch_set_peers(GemvArgs &a, const Resident *w, float *const *peer_ys, size_t i, int n_peers) {
+    if (!peer_ys) return;
+    a.mat[0].y = nullptr;
+    a.mat[0].n_peer = (uint32_t)n_peers;
+    a.mat[0].row_base = (uint32_t)w->row0;
+    for (int p = 0; p < n_peers; p++) a.mat[0].peer_y[p] = peer_ys[i * (size_t)n_peers + (size_t)p];
+}
+// one item as a launch of its own
+static int batch_enqueue_one(strix_cuda *h, size_t i, const Resident *const *ws, const float *const *d_xs, float *const *d_ys,
+                             float *const *peer_ys, int n_peers, int act, cudaStream_t s) {
+    const Resident *w1[1] = {ws[i]};
+    float *y1[1] = {d_ys ? d_ys[i] : nullptr};
+    if (!peer_ys) return gemv_launch(h, 1, w1, d_xs[i], nullptr, 0.f, STRIX_PRE_NONE, act, y1, nullptr, s);
+    GemvArgs a{};
+    if (gemv_fill_args(h, 1, w1, d_xs[i], nullptr, 0.f, STRIX_PRE_NONE, act, y1, nullptr, &a) < 0) return -1;
+    batch_set_peers(a, ws[i], peer_ys, i, n_peers);
+    a.nbatch = 1;
+    if (!gemv_plan(a, h->num_sms, h->smem_optin, h->tune)) {
+        h->err = "gemv_batch: in_dim too large for the shared-memory pipeline";
+        return -1;
+    }
+    ProfScope prof(h, s, gemv_prof_name(a));
+    CU_TRY(h, launch_gemv(a, s));
+    return 1;
+}
 static int batch_enqueue_side_by_side(strix_cuda *h, const std::vector<size_t> &idx, const Resident *const *ws,
-                                      const float *const *d_xs, float *const *d_ys, int act, cudaStream_t s) {
+                                      const float *const *d_xs, float *const *d_ys, int act, cudaStream_t s,
+                                      float *const *peer_ys = nullptr, int n_peers = 0) {
     for (size_t at = 0; at < idx.size(); at += GEMV_MULTI_MAX) {
         const size_t cnt = std::min<size_t>(GEMV_MULTI_MAX, idx.size() - at);
         GemvMultiArgs m{};
@@ -219,8 +248,9 @@ static int batch_enqueue_side_by_side(strix_cuda *h, const std::vector<size_t> &
         for (size_t k = 0; ok && k < cnt; k++) {
             const size_t i = idx[at + k];
             const Resident *w1[1] = {ws[i]};
-            float *y1[1] = {d_ys[i]};
+            float *y1[1] = {d_ys ? d_ys[i] : nullptr};
             if (gemv_fill_args(h, 1, w1, d_xs[i], nullptr, 0.f, STRIX_PRE_NONE, act, y1, nullptr, &m.p[k]) < 0) return -1;
+            batch_set_peers(m.p[k], ws[i], peer_ys, i, n_peers);
         }
         if (ok) ok = gemv_multi_plan(m, h->num_sms, h->smem_optin, h->tune);
         if (ok) {
@@ -228,12 +258,8 @@ static int batch_enqueue_side_by_side(strix_cuda *h, const std::vector<size_t> &
             CU_TRY(h, launch_gemv_multi(m, s));
             continue;
         }
-        for (size_t k = 0; k < cnt; k++) {
-            const size_t i = idx[at + k];
-            const Resident *w1[1] = {ws[i]};
-            float *y1[1] = {d_ys[i]};
-            if (gemv_launch(h, 1, w1, d_xs[i], nullptr, 0.f, STRIX_PRE_NONE, act, y1, nullptr, s) < 0) return -1;
-        }
+        for (size_t k = 0; k < cnt; k++)
+            if (batch_enqueue_one(h, idx[at + k], ws, d_xs, d_ys, peer_ys, n_peers, act, s) < 0) return -1;
     }
     return 1;
 }
@@ -770,32 +796,48 @@ int strix_cuda_gemv_batch(strix_cuda *h, size_t n, const char *const *keys, cons
 
 // WeightAccel::gemv_batch for device-resident vectors: n independent GEMVs enqueued from `stream`, no copies and
 // no synchronisation. Large items first, a launch each; then the small ones side by side in one launch.
-int strix_cuda_gemv_batch_dev(strix_cuda *h, size_t n, const char *const *keys, const float *const *d_xs, float *const *d_ys,
-                              int act, void *stream) {
-    if (!h || (n && (!keys || !d_xs || !d_ys))) return -1;
+static int gemv_batch_device(strix_cuda *h, size_t n, const char *const *keys, const float *const *d_xs, float *const *d_ys,
+                             float *const *peer_ys, int n_peers, int act, cudaStream_t s, const char *who) {
     h->err.clear();
     if (act != STRIX_ACT_F32 && act != STRIX_ACT_Q8DOT) {
-        h->err = "gemv_batch_dev: unknown activation mode";
+        h->err = std::string(who) + ": unknown activation mode";
         return -1;
     }
     CU_TRY(h, cudaSetDevice(h->device));
-    cudaStream_t s = static_cast<cudaStream_t>(stream);
     std::vector<const Resident *> ws(n, nullptr);
     for (size_t i = 0; i < n; i++) {
         ws[i] = find_weight(h, keys[i]);
-        if (!ws[i] || !d_xs[i] || !d_ys[i]) return 0;
+        if (!ws[i] || !d_xs[i] || (d_ys && !d_ys[i])) return 0;
+        for (int p = 0; peer_ys && p < n_peers; p++)
+            if (!peer_ys[i * (size_t)n_peers + (size_t)p]) return 0;
     }
     const std::vector<size_t> small = batch_small_items(h, n, ws.data());
     std::vector<char> is_small(n, 0);
     for (size_t i : small) is_small[i] = 1;
-    for (size_t i = 0; i < n; i++) {
-        if (is_small[i]) continue;
-        const Resident *w1[1] = {ws[i]};
-        float *y1[1] = {d_ys[i]};
-        if (gemv_launch(h, 1, w1, d_xs[i], nullptr, 0.f, STRIX_PRE_NONE, act, y1, nullptr, s) < 0) return -1;
-    }
-    if (!small.empty() && batch_enqueue_side_by_side(h, small, ws.data(), d_xs, d_ys, act, s) < 0) return -1;
+    for (size_t i = 0; i < n; i++)
+        if (!is_small[i] && batch_enqueue_one(h, i, ws.data(), d_xs, d_ys, peer_ys, n_peers, act, s) < 0) return -1;
+    if (!small.empty() && batch_enqueue_side_by_side(h, small, ws.data(), d_xs, d_ys, act, s, peer_ys, n_peers) < 0) return -1;
     return 1;
+}
+
+int strix_cuda_gemv_batch_dev(strix_cuda *h, size_t n, const char *const *keys, const float *const *d_xs, float *const *d_ys,
+                              int act, void *stream) {
+    if (!h || (n && (!keys || !d_xs || !d_ys))) return -1;
+    return gemv_batch_device(h, n, keys, d_xs, d_ys, nullptr, 0, act, static_cast<cudaStream_t>(stream), "gemv_batch_dev");
+}
+
+// The row-sharded form of gemv_batch_dev: every item's rows are stored into the full output vector of every
+// accelerator of the group (peer_ys[i * n_peers + p], this GPU's own copy included) by the kernels themselves, over
+// peer memory, so no collective follows: strix_cuda_peer_barrier_dev on the same stream makes them safe to read.
+int strix_cuda_gemv_batch_peers_dev(strix_cuda *h, size_t n, const char *const *keys, const float *const *d_xs, int n_peers,
+                                    float *const *peer_ys, int act, void *stream) {
+    if (!h || (n && (!keys || !d_xs || !peer_ys))) return -1;
+    if (n_peers < 1 || n_peers > GEMV_MAX_PEERS) {
+        h->err = "gemv_batch_peers_dev: between 1 and 8 peers";
+        return -1;
+    }
+    return gemv_batch_device(h, n, keys, d_xs, nullptr, peer_ys, n_peers, act, static_cast<cudaStream_t>(stream),
+                             "gemv_batch_peers_dev");
 }
 
 int strix_cuda_gemv(strix_cuda *h, const char *key, const float *x, size_t k, float *y, size_t y_cap, int act) {

@@ -86,6 +86,7 @@ extern "C" {
     pub fn strix_cuda_poke_u32(h: *mut StrixCuda, d_ptr: *mut c_void, value: u32) -> c_int;
     pub fn strix_cuda_peer_barrier_dev(h: *mut StrixCuda, d_epoch: *mut u32, d_local_flags: *mut u32, peer_flags: *const *mut u32, stream: *mut c_void) -> c_int;
     pub fn strix_cuda_gemv_batch_dev(h: *mut StrixCuda, n: usize, keys: *const *const c_char, d_xs: *const *const f32, d_ys: *const *mut f32, act: c_int, stream: *mut c_void) -> c_int;
+    pub fn strix_cuda_gemv_batch_peers_dev(h: *mut StrixCuda, n: usize, keys: *const *const c_char, d_xs: *const *const f32, n_peers: c_int, peer_ys: *const *mut f32, act: c_int, stream: *mut c_void) -> c_int;
     pub fn strix_cuda_prefill_q8_gemm(h: *mut StrixCuda, key: *const c_char, xs: *const f32, m: usize, y: *mut f32, y_cap: usize) -> c_int;
     pub fn strix_cuda_prefill_q8_gemm_dev(h: *mut StrixCuda, key: *const c_char, d_xs: *const f32, m: usize, d_y: *mut f32, stream: *mut c_void) -> c_int;
     pub fn strix_cuda_prefill_q4_gemm(h: *mut StrixCuda, key: *const c_char, xs: *const f32, m: usize, y: *mut f32, y_cap: usize) -> c_int;

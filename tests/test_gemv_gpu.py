@@ -549,3 +549,42 @@ def test_profile_option_times_every_launch(pkg, synth):
         assert "gemv" not in acc.profile_dump()
     finally:
         acc.close()
+
+
+def test_gemv_batch_peers_dev_fills_every_ranks_full_vectors(pkg, orc, synth):
+    """The row-sharded form of gemv_batch_dev: each of three row shards (three handles on one GPU, run one after
+    the other: no kernel waits for another) stores its rows of every item into the full output vectors of both
+    'accelerators' (two local buffers per item). One item runs as a launch of its own, the others side by side.
+    Every element of every vector against the oracle."""
+    import torch
+    dev = torch.device("cuda:0")
+    world = 3
+    shapes = [(synth.Q8_0, 2560, 1203), (synth.Q6_K, 2560, 997), (synth.Q4_0, 4096, 777), (synth.Q8_0, 1024, 50)]
+    ws = [synth.quant(ty, 621, "bp.%d" % i, n, k) for i, (ty, k, n) in enumerate(shapes)]
+    xs = [synth.normal(622, "bp.x.%d" % i, k) for i, (ty, k, n) in enumerate(shapes)]
+    want = [orc.qmatmul(xs[i], ws[i], ty, k, n) for i, (ty, k, n) in enumerate(shapes)]
+    d_xs = [torch.from_numpy(x).to(dev) for x in xs]
+    full = [[torch.full((n,), float("nan"), device=dev) for _ in range(2)] for (_, _, n) in shapes]
+    s = torch.cuda.current_stream().cuda_stream
+    keys = ["bp.%d" % i for i in range(len(shapes))]
+    for r in range(world):
+        a = pkg.CudaWeightAccel(0, rank=r, world=world)
+        try:
+            assert a.set_option("batch_small_bytes", 600 << 10)   # item 0's shard is above it: a launch of its own
+            for i, (ty, k, n) in enumerate(shapes):
+                up = {synth.Q8_0: a.upload_q8_0, synth.Q6_K: a.upload_q6_k, synth.Q4_0: a.upload_q4_0}[ty]
+                assert up(keys[i], ws[i], k, n)
+            assert a.gemv_batch_peers_dev(keys, [x.data_ptr() for x in d_xs], [[f.data_ptr() for f in fs] for fs in full],
+                                          stream=s)
+            torch.cuda.synchronize()
+            assert a.device_status(s) == 0
+            assert a.gemv_batch_peers_dev(keys + ["nope"], [x.data_ptr() for x in d_xs] + [d_xs[0].data_ptr()],
+                                          [[f.data_ptr() for f in fs] for fs in full] + [[full[0][0].data_ptr()] * 2],
+                                          stream=s) is False
+        finally:
+            a.close()
+    for i, fs in enumerate(full):
+        for f in fs:
+            got = f.cpu().numpy()
+            assert np.isfinite(got).all()
+            assert rel_l2(got, want[i]) <= REL_L2_TOL, i
