@@ -548,10 +548,40 @@ def decode_chain_sharded_extra(pkg, synth, torch, dist, local, stream, rank, wor
                     logits_ref = lg_full.clone()
                 else:   # same shards, same kernels: the two exchange forms must agree bit for bit
                     assert bool((lg_full == logits_ref).all()), "fused and NCCL chains disagree"
+            phases = None
+            if vname == "chain_kernel":
+                # where a step's time goes on this many GPUs: rank 0's CTA 0 notes its clocks per step (a separate,
+                # untimed pass: tracing costs ~10 %); all ranks run it, the chain needs everybody
+                acc.set_option("chain_trace", 1)
+                with torch.cuda.stream(stream):
+                    for _ in range(3):
+                        h_full.copy_(h0)
+                        chain(act)
+                    torch.cuda.synchronize()
+                dist.barrier()
+                tr = acc.decode_trace()
+                acc.set_option("chain_trace", 0)
+                if tr is not None and rank == 0:
+                    tt = tr.astype(np.int64)
+                    phases = {}
+                    for kk, nm in enumerate(("qkv", "o", "gate_up", "down")):
+                        idx = np.arange(kk + 4, len(tt) - 1, 4)
+                        idx = idx[(tt[idx, 1] != 0) & (tt[idx, 2] != 0) & (tt[idx, 3] != 0)]   # steps in which CTA 0 had rows
+                        if idx.size == 0:
+                            phases[nm] = {"note": "CTA 0 of rank 0 holds no row group of this step on %d GPUs" % world}
+                            continue
+                        f = lambda a_, b_: round(float((tt[idx, b_] - tt[idx, a_]).mean()) / 1965.0, 2)  # noqa: E731
+                        phases[nm] = {"wait_us": f(0, 1), "prologue_us": f(1, 2), "tiles_us": f(2, 3), "reduce_publish_us": f(3, 4),
+                                      "step_us": f(0, 4)}
             out[vname + "_" + name] = {"ms_per_token": round(ms, 4), "gbs_aggregate": round(nbytes / ms / 1e6, 1),
                                        "gbs_per_gpu": round(nbytes / ms / 1e6 / world, 1),
                                        "launches_per_token": 1 if vname == "chain_kernel" else (4 * n_layers + 1) * (2 if vname == "fused" else 1),
                                        "collectives_per_token": 4 * n_layers + 1 if vname == "nccl" else 0}
+            if phases:
+                out[vname + "_" + name]["phases_cta0_rank0"] = phases
+                out[vname + "_" + name]["phases_note"] = ("SM clocks of rank 0's CTA 0 at 1965 MHz, mean over layers 1..%d: waiting "
+                                                          "for the step's activation row (all ranks' rows), quantising it, "
+                                                          "this shard's tiles, reduction and stores to every rank" % (n_layers - 1))
         out["n_gpus"] = world
         out["bytes_per_token"] = nbytes
         out["note"] = ("row-sharded projections; nccl: all-gather after each projection or fused group (coalesced: %s); "

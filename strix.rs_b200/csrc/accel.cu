@@ -513,14 +513,19 @@ int strix_cuda_set_option(strix_cuda *h, const char *name, long long value) {
     else if (n == "gemv_debug") h->tune.debug = v;
     else if (n == "rows_operand_image") h->tune.xop = v;
     else if (n == "batch_graph") h->use_batch_graph = value != 0;
-    else if (n == "batch_side_by_side") h->batch_side_by_side = (int)v;
-    else if (n == "batch_small_bytes") h->batch_small_bytes = (size_t)value;
     else if (n == "kv_f16") h->kv_f16 = value != 0;
     else if (n == "decode_chain") h->decode_chain = value < 0 ? -1 : value != 0;
-    else if (n == "chain_trace") h->chain_trace = value != 0;
     else if (n == "chain_debug") h->chain_debug = v;
     else if (n == "poll_limit") h->poll_limit = v ? v : CHAIN_POLL_LIMIT;
-    else if (n == "profile") h->profile = value != 0;
+    // (what follows leaves a configured decode chain as it is)
+    else if (n == "batch_side_by_side") { h->batch_side_by_side = (int)v; return 1; }
+    else if (n == "batch_small_bytes") { h->batch_small_bytes = (size_t)value; return 1; }
+    else if (n == "profile") { h->profile = value != 0; return 1; }
+    else if (n == "chain_trace") {
+        h->chain_trace = value != 0;
+        if (h->chain_trace) decode_trace_enable(h);
+        return 1;
+    }
     else return 0;
     // plans made under the old value must not be replayed
     decode_release(h);

@@ -152,6 +152,7 @@ int gemv_launch_rows(strix_cuda *h, int nmat, const Resident *const *ws, const f
 int gemv_fill_args(strix_cuda *h, int nmat, const Resident *const *ws, const float *d_a, const float *d_b, float eps,
                    int pre, int act, float *const *d_ys, const float *const *d_res, GemvArgs *out);
 void batch_release(strix_cuda *h);   // drops the cached gemv_batch graph (it holds weight pointers)
+void decode_trace_enable(strix_cuda *h);  // see decode.cu
 void decode_release(strix_cuda *h);  // drops a configured decode chain (its graph holds weight pointers)
 int gemv_launch(strix_cuda *h, int nmat, const Resident *const *ws, const float *d_a, const float *d_b, float eps,
                 int pre, int act, float *const *d_ys, const float *const *d_res, cudaStream_t stream);

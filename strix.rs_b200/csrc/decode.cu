@@ -144,6 +144,26 @@ void decode_release(strix_cuda *h) {
     decode_free(h->decode);
     h->decode = nullptr;
 }
+// Option "chain_trace" switched on for a chain that is already configured (and, row-sharded, already wired to its
+// peers): the trace words are allocated now, and the captured token step, which holds the old null pointer, goes.
+void decode_trace_enable(strix_cuda *h) {
+    strix_decode_state *d = h->decode;
+    if (!d || d->d_trace) return;
+    const size_t n = 4 * d->layers.size() + 1;
+    const size_t nb = (size_t)CHAIN_TRACE_WORDS * n * sizeof(unsigned long long);
+    if (cudaMalloc(&d->d_trace, nb) != cudaSuccess) {
+        cudaGetLastError();
+        d->d_trace = nullptr;
+        return;
+    }
+    cudaMemset(d->d_trace, 0, nb);
+    cudaDeviceSynchronize();
+    d->trace_n = (uint32_t)n;
+    if (d->exec) {
+        cudaGraphExecDestroy(d->exec);
+        d->exec = nullptr;
+    }
+}
 }  // namespace strix
 
 static const float *f32_of(strix_cuda *h, const std::string &key, size_t n) {
@@ -380,8 +400,8 @@ static const strix_decode_state::Program *chain_program(strix_cuda *h, strix_dec
 static int enqueue_chain(strix_cuda *h, strix_decode_state *d, cudaStream_t s) {
     if (const strix_decode_state::Program *p = chain_program(h, d, s)) {
         ProfScope prof(h, s, "chain");
-        CU_TRY(h, launch_chain(p->d_steps, p->n_steps, p->geom, d->d_ctl, h->d_status, h->poll_limit, h->chain_debug, d->d_trace,
-                               h->num_sms, s));
+        CU_TRY(h, launch_chain(p->d_steps, p->n_steps, p->geom, d->d_ctl, h->d_status, h->poll_limit, h->chain_debug,
+                               h->chain_trace ? d->d_trace : nullptr, h->num_sms, s));
         return 1;
     }
     if (h->world > 1) {
