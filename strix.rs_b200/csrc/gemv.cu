@@ -2,9 +2,9 @@
 // and int8-activation (integer-dot) forms, for 1 to 8 activation rows per pass over the weights.
 //
 // Replaces the reference's batch-1 decode kernels (crates/strix-backend-rocm/src/kernels.rs:
-// q4_gemv :141-176, q4_gemv_dp :259-287, q6k_gemv :178-237, q8_gemv :239-257, q8i_gemv :894-912,
-// and the batched-verify GEMVs) and the CPU loops they mirror (crates/strix-backend-cpu/src/
-// qwen3.rs:62-105 qmatmul / dot_f32).
+// q4_gemv :41-69, q4_gemv_dp :259-287 with its fused forms dp2 / dp3 :324-361, q4_1_gemv_dp :292-320,
+// q6_gemv :607-640, q8_0_gemv :646-668, q8i_gemv :894-912, and the batched-verify GEMVs) and the CPU
+// loops they mirror (crates/strix-backend-cpu/src/qwen3.rs:90-105, 173-182 dot_f32 / qmatmul).
 //
 // Shape of the kernel (one persistent CTA per SM, 24 consumer warps + 1 producer warp):
 //   * The weights stream through shared memory: the producer warp issues 1-D bulk async copies
@@ -25,6 +25,8 @@
 //     memory pipeline as the limit and makes activation rows 2..8 almost free.
 //   * Every wait is bounded: on expiry the kernel flags STATUS_WAIT_TIMEOUT, stops issuing copies,
 //     stops waiting, and runs out.
+//   * gemv_multi_kernel runs several independent GEMVs (the items of a gemv_batch) side by side in one
+//     launch: the CTAs are dealt out among the problems and each runs this same pipeline on its own.
 #include "gemv_tiles.cuh"
 
 namespace strix {
