@@ -52,7 +52,6 @@ constexpr uint32_t CH_STEP_BYTES = 512;
 static_assert(sizeof(ChainStep) <= CH_STEP_BYTES && sizeof(ChainStep) % 16 == 0, "one 16-byte word per lane of a warp");
 constexpr uint32_t CH_STEP_OFF = CH_PART_OFF + CHAIN_PART_SLOTS * CH_WARPS * 16u * 4u;  // 3 consumer slots + 1 producer slot
 constexpr uint32_t CH_X_OFF = (CH_STEP_OFF + 4u * CH_STEP_BYTES + 127u) & ~127u;
-constexpr int CH_PASS_NI = 2;  // float4s a thread requests per pass over a row that needs no norm (see chain_prologue_q8)
 constexpr int CH_NORM_NI = 2;  // float4s a thread keeps across the RMSNorm reduction: normed rows up to 2 * 4 * 384 = 3072
 
 struct ChainCta {
@@ -303,8 +302,8 @@ __device__ __forceinline__ void chain_prologue_q8(const ChainStep &S, ChainCta &
             }
         }
     } else {
-        // no norm: each pass (up to CH_PASS_NI float4s per thread, all requested at once) is quantised and stored
-        // before the next one is fetched. Threads past the row's end carry zeros through the shuffles and store nothing.
+        // no norm: each pass (up to 2 float4s per thread, both requested at once) is quantised and stored before
+        // the next one is fetched. Threads past the row's end carry zeros through the shuffles and store nothing.
         const uint32_t per = (K4 + ct - 1u) / ct;  // float4s per thread
         if (per <= 1u) {
             float4 v[1];
@@ -316,15 +315,14 @@ __device__ __forceinline__ void chain_prologue_q8(const ChainStep &S, ChainCta &
 #pragma unroll
             for (int i = 0; i < 2; i++) quant_store(v[i], tid + i * ct, tid + i * ct < K4, l8, q6, bias, xbw, rec);
         } else {
-            // (two float4s per thread and pass; four measured slower, 1.61 against 1.55 ms per token: the registers
-            // they take are spilled in the tile loop, and the time a row takes to arrive is set by the L2-to-SM
-            // paths it shares with the weight stream, not by the number of passes)
-            for (uint32_t e0 = tid; e0 - lane < K4; e0 += (uint32_t)CH_PASS_NI * ct) {
-                float4 v[CH_PASS_NI];
-                fetch_pass<CH_PASS_NI>(S, C, e0, ct, K4, v);
-#pragma unroll
-                for (int i = 0; i < CH_PASS_NI; i++)
-                    if (e0 - lane + i * ct < K4) quant_store(v[i], e0 + i * ct, e0 + i * ct < K4, l8, q6, bias, xbw, rec);
+            // (Two float4s per thread and pass. Four measured slower - the registers they take are spilled in the
+            // tile loop - and even writing this loop over a pass size with its first store under the same test as the
+            // second cost 11 %, 1.54 against 1.39 ms per token: the kernel's register allocation is that tight.)
+            for (uint32_t e0 = tid; e0 - lane < K4; e0 += 2u * ct) {
+                float4 v[2];
+                fetch_pass<2>(S, C, e0, ct, K4, v);
+                quant_store(v[0], e0, e0 < K4, l8, q6, bias, xbw, rec);
+                if (e0 - lane + ct < K4) quant_store(v[1], e0 + ct, e0 + ct < K4, l8, q6, bias, xbw, rec);
             }
         }
         ch_trace(C, 1);
