@@ -1166,7 +1166,9 @@ def main():
                 world, ", outputs exchanged once per step (%s)" % exchange["form"] if world > 1 else ""),
             "exchange": exchange,
             "e2e": {"value": round(e2e_val, 2), "unit": "GB/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
-            "gpu_launches": args.steps * REPLAYS * len(units), "launches_per_step": len(units),
+            # (with the fused exchange the flag-barrier kernel is one more launch of ours per step)
+            "gpu_launches": args.steps * REPLAYS * (len(units) + (1 if exchange and exchange["form"].startswith("peer") else 0)),
+            "launches_per_step": len(units) + (1 if exchange and exchange["form"].startswith("peer") else 0),
             "clocks": clocks, "roofline": roof, "cpu_baseline": cpu, "per_weight": detail, "extras": extras,
             "frac_of_8tbs": round(value / 8000.0, 4),
         }
