@@ -1,5 +1,6 @@
 //! `impl WeightAccel for CudaWeightAccel` (crates/strix-core/src/accel.rs:147-507): every hot-path method of the
 //! trait forwarded to the C ABI; everything else keeps the trait's declining defaults. Uncompiled here.
+use std::collections::HashMap;
 use std::ffi::{CStr, CString};
 use std::os::raw::c_char;
 
@@ -12,6 +13,7 @@ pub struct CudaWeightAccel {
     name: String,
     int8_act: bool,
     vocab: usize,
+    moe_hidden: HashMap<usize, usize>,  // adopted mixture-of-experts layers -> hidden size (the length of their outputs)
 }
 // Same soundness argument as RocmWeightAccel (decode.rs:559-562): one caller at a time.
 unsafe impl Send for CudaWeightAccel {}
@@ -31,7 +33,7 @@ impl CudaWeightAccel {
         }
         let name = cstr(unsafe { ffi::strix_cuda_name(h) });
         // STRIX_NO_INT8 keeps the f32-activation kernels, as in decode.rs:771
-        Ok(Self { h, name, int8_act: std::env::var("STRIX_NO_INT8").is_err(), vocab: 0 })
+        Ok(Self { h, name, int8_act: std::env::var("STRIX_NO_INT8").is_err(), vocab: 0, moe_hidden: HashMap::new() })
     }
     fn act(&self) -> i32 { if self.int8_act { ffi::ACT_Q8DOT } else { ffi::ACT_F32 } }
     fn rows(&self, key: &CString) -> Option<usize> {
@@ -91,6 +93,48 @@ impl WeightAccel for CudaWeightAccel {
         let k = CString::new(key).ok()?;
         let mut y = vec![0f32; m * self.rows(&k)?];
         let rc = unsafe { ffi::strix_cuda_prefill_q8_gemm(self.h, k.as_ptr(), xs.as_ptr(), m, y.as_mut_ptr(), y.len()) };
+        (rc == 1).then_some(y)
+    }
+
+    // mixture-of-experts layers (accel.rs:167-246): whole-layer uploads, one token's routed FFN, grouped tokens
+    fn upload_moe_q8(&mut self, layer: usize, gate: &[u8], up: &[u8], down: &[u8], hidden: usize, eff: usize, ne: usize) -> bool {
+        let rc = unsafe {
+            ffi::strix_cuda_upload_moe_q8(self.h, layer, gate.as_ptr(), gate.len(), up.as_ptr(), up.len(), down.as_ptr(),
+                                          down.len(), hidden, eff, ne)
+        };
+        if rc == 1 { self.moe_hidden.insert(layer, hidden); }
+        rc == 1
+    }
+    fn upload_moe_q6(&mut self, layer: usize, gate: &[u8], up: &[u8], down: &[u8], hidden: usize, eff: usize, ne: usize) -> bool {
+        let rc = unsafe {
+            ffi::strix_cuda_upload_moe_q6(self.h, layer, gate.as_ptr(), gate.len(), up.as_ptr(), up.len(), down.as_ptr(),
+                                          down.len(), hidden, eff, ne)
+        };
+        if rc == 1 { self.moe_hidden.insert(layer, hidden); }
+        rc == 1
+    }
+    fn moe_ffn(&self, layer: usize, ids: &[i32], wexp: &[f32], x: &[f32], sgate: f32) -> Option<Vec<f32>> {
+        if ids.len() != wexp.len() { return None; }
+        let mut y = vec![0f32; *self.moe_hidden.get(&layer)?];
+        let rc = unsafe {
+            ffi::strix_cuda_moe_ffn(self.h, layer, ids.as_ptr(), wexp.as_ptr(), ids.len(), x.as_ptr(), x.len(), sgate, self.act(),
+                                    y.as_mut_ptr(), y.len())
+        };
+        (rc == 1).then_some(y)
+    }
+    fn moe_expert_ffn(&self, layer: usize, e: usize, xs: &[f32], m: usize) -> Option<Vec<f32>> {
+        let mut y = vec![0f32; m * *self.moe_hidden.get(&layer)?];
+        let rc = unsafe { ffi::strix_cuda_moe_expert_ffn(self.h, layer, e, xs.as_ptr(), m, self.act(), y.as_mut_ptr(), y.len()) };
+        (rc == 1).then_some(y)
+    }
+    fn moe_layer_ffn(&self, layer: usize, plan: &[(i32, i32)], xs: &[f32], rows: usize) -> Option<Vec<f32>> {
+        // (expert id, row count) pairs are two consecutive ints, which is what the C side reads
+        let flat: Vec<i32> = plan.iter().flat_map(|(e, n)| [*e, *n]).collect();
+        let mut y = vec![0f32; rows * *self.moe_hidden.get(&layer)?];
+        let rc = unsafe {
+            ffi::strix_cuda_moe_layer_ffn(self.h, layer, flat.as_ptr(), plan.len(), xs.as_ptr(), rows, self.act(), y.as_mut_ptr(),
+                                          y.len())
+        };
         (rc == 1).then_some(y)
     }
 
