@@ -385,7 +385,10 @@ xop_prepare_kernel(const float *__restrict__ a, const float *__restrict__ b, uin
     __shared__ float scr[32];
     asm volatile("griddepcontrol.launch_dependents;");
     const uint32_t tid = threadIdx.x, lane = tid & 31u, warp = tid >> 5, l8 = lane & 7u, bi = blockIdx.x;
-    const uint32_t K4 = K / 4u, nb32 = K / 32u;
+    const uint32_t nb32 = K / 32u;
+    // Without a norm nothing ties a row's blocks together: gridDim.y CTAs share a row, each takes a run of whole
+    // 32-blocks (float4 indices [lo4, lo4 + K4)). With RMSNorm the launch has one CTA per row.
+    const uint32_t lo4 = blockIdx.y * (K / 4u / gridDim.y), K4 = K / 4u / gridDim.y;
     const XLayout XL = x_layout(q6 ? FMT_Q6_K : FMT_Q4_0, STRIX_ACT_Q8DOT, K, B, 0u);
     uint32_t *xbw = reinterpret_cast<uint32_t *>(image + XL.xb);
     float *rec = reinterpret_cast<float *>(image + XL.rec);
@@ -393,6 +396,7 @@ xop_prepare_kernel(const float *__restrict__ a, const float *__restrict__ b, uin
     asm volatile("griddepcontrol.wait;" ::: "memory");
     if (bi >= B) {
         // a record slot without an activation row reads zero (what its MMA column produces is never stored)
+        if (blockIdx.y != 0u) return;
         if (q6) {
             for (uint32_t blk = tid; blk < nb32; blk += XOP_THREADS)
                 reinterpret_cast<float4 *>(rec)[blk * 4u + bi] = make_float4(0.f, 0.f, 0.f, 0.f);
@@ -413,11 +417,11 @@ xop_prepare_kernel(const float *__restrict__ a, const float *__restrict__ b, uin
         const uint32_t e4 = tid + i * XOP_THREADS;
         v[i] = make_float4(0.f, 0.f, 0.f, 0.f);
         if (e4 < K4) {
-            float4 a4 = __ldcg(reinterpret_cast<const float4 *>(Aa) + e4);
+            float4 a4 = __ldcg(reinterpret_cast<const float4 *>(Aa) + lo4 + e4);
             if (PRE == STRIX_PRE_RMSNORM) {
                 ss = fmaf(a4.x, a4.x, ss); ss = fmaf(a4.y, a4.y, ss); ss = fmaf(a4.z, a4.z, ss); ss = fmaf(a4.w, a4.w, ss);
             } else if (PRE != STRIX_PRE_NONE) {
-                const float4 b4 = __ldcg(reinterpret_cast<const float4 *>(Ab) + e4);
+                const float4 b4 = __ldcg(reinterpret_cast<const float4 *>(Ab) + lo4 + e4);
                 if (PRE == STRIX_PRE_SWIGLU) {
                     a4.x = silu_f(a4.x) * b4.x; a4.y = silu_f(a4.y) * b4.y; a4.z = silu_f(a4.z) * b4.z; a4.w = silu_f(a4.w) * b4.w;
                 } else {
@@ -435,7 +439,7 @@ xop_prepare_kernel(const float *__restrict__ a, const float *__restrict__ b, uin
         float tot = 0.f;
 #pragma unroll
         for (uint32_t w2 = 0; w2 < XOP_THREADS / 32u; w2++) tot += scr[w2];
-        const float sc = 1.0f / sqrtf(tot / (float)K + eps);
+        const float sc = 1.0f / sqrtf(tot / (float)K + eps);   // (one CTA per row here: K4 is the whole row)
 #pragma unroll
         for (uint32_t i = 0; i < XOP_NI; i++) {
             const uint32_t e4 = tid + i * XOP_THREADS;
@@ -452,7 +456,7 @@ xop_prepare_kernel(const float *__restrict__ a, const float *__restrict__ b, uin
         if ((tid - lane) + i * XOP_THREADS >= K4) break;  // the whole warp is past the row's end (the body shuffles)
         const bool live = e4 < K4;
         const float4 t4 = v[i];
-        const uint32_t blk = e4 >> 3, t = l8 & 3u, hf = l8 >> 2;
+        const uint32_t blk = (lo4 + e4) >> 3, t = l8 & 3u, hf = l8 >> 2;
         float bm = fmaxf(fmaxf(fabsf(t4.x), fabsf(t4.y)), fmaxf(fabsf(t4.z), fabsf(t4.w)));
         bm = fmaxf(bm, __shfl_xor_sync(0xffffffffu, bm, 1));
         bm = fmaxf(bm, __shfl_xor_sync(0xffffffffu, bm, 2));
@@ -502,7 +506,10 @@ cudaError_t launch_xop_prepare(int fmt, uint32_t in_dim, uint32_t nbatch, const 
     const int bias = fmt == FMT_Q8_0 ? 128 : fmt == FMT_Q4_0 ? 8 : fmt == FMT_Q4_1 ? -1 : 32;
     cudaLaunchConfig_t cfg = {};
     // one CTA per record slot of the layout: rows without an activation clear theirs
-    cfg.gridDim = dim3(nbatch > 1 || q6 ? (q6 ? 4u : 8u) : 1u);
+    // (pre-ops other than RMSNorm work element by element: four CTAs per row, or two, when the row's blocks divide)
+    const uint32_t nb32 = in_dim / 32u;
+    const uint32_t parts = pre == STRIX_PRE_RMSNORM ? 1u : nb32 % 4u == 0u ? 4u : nb32 % 2u == 0u ? 2u : 1u;
+    cfg.gridDim = dim3(nbatch > 1 || q6 ? (q6 ? 4u : 8u) : 1u, parts);
     cfg.blockDim = dim3(XOP_THREADS);
     cfg.stream = stream;
     cudaLaunchAttribute at[1];
