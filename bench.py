@@ -220,7 +220,9 @@ def decode_chain_extra(pkg, synth, torch, device, stream):
                 dev_ms = a.elapsed_time(b) / reps
             out[name] = {"ms_per_token": round(dev_ms, 4), "ms_per_token_e2e": round(e2e_ms, 4),
                          "ms_per_token_e2e_argmax": round(e2e_argmax_ms, 4),
-                         "gbs": round(nbytes / dev_ms / 1e6, 1), "launches_per_token": 1 if chain else 4 * n_layers + 1}
+                         "gbs": round(nbytes / dev_ms / 1e6, 1),
+                         # (integer-dot form: the ffn-long row of every down projection is prepared by a launch of its own)
+                         "launches_per_token": 1 if chain else 4 * n_layers + 1 + (n_layers if act == pkg.ACT_Q8DOT and ffn >= 8192 else 0)}
             tr = acc.decode_trace() if chain else None
             if tr is not None:
                 # CTA 0's clocks per step: start, activations arrived, prologue done, last row group done, rows published

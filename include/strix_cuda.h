@@ -409,7 +409,8 @@ STRIX_API int strix_cuda_clear_device_status(strix_cuda *h, void *stream);
  * three int8 digit rows), "gemv_warps_per_group", "gemv_blocks_per_stage", "gemv_stages" (0 = planned),
  * "gemv_pdl" (programmatic dependent launch between GEMVs), "rows_operand_image" (batched integer-dot GEMV:
  * the activation operands are prepared once by a kernel of their own and fetched by every CTA; 0 = every CTA
- * quantises all rows itself), "gemv_debug" (bit 0: stream the weights without
+ * quantises all rows itself), "operand_image_min_k" (a single row is prepared that way too from this in_dim on;
+ * 8192), "gemv_debug" (bit 0: stream the weights without
  * arithmetic, bit 1: empty launches, bit 2: stop after the activation prologue), "batch_graph" (gemv_batch
  * replays a cached CUDA graph), "batch_side_by_side" / "batch_small_bytes" (which items of a gemv_batch share a launch,
  * see strix_cuda_gemv_batch_dev), "decode_chain" (the projection chain as one persistent launch),

@@ -387,8 +387,9 @@ int gemv_launch_rows(strix_cuda *h, int nmat, const Resident *const *ws, const f
         // Several activation rows in the integer-dot form: their operands are prepared ONCE by a kernel of its own
         // and fetched by every CTA, instead of being quantised by each of the 148 CTAs (8 rows of 15360 cost a CTA
         // ~15 us of prologue, on the critical path of a launch whose weights stream in 5 us). One row stays with
-        // the in-kernel prologue: a second launch costs more than it saves there.
-        if (act == STRIX_ACT_Q8DOT && chunk >= 2 && a.L.in_dim <= 16384u && h->tune.xop != 0) {
+        // the in-kernel prologue while it is short: there a second launch costs more than it saves; from
+        // xop_single_min_k elements on (the ffn-long rows of the down projections) it is prepared the same way.
+        if (act == STRIX_ACT_Q8DOT && (chunk >= 2 || a.L.in_dim >= h->tune.xop_single_min_k) && a.L.in_dim <= 16384u && h->tune.xop != 0) {
             if (ensure_xop(h, xop_image_bytes(a.L.fmt, a.L.in_dim, chunk)) < 0) return -1;
             ProfScope prof(h, stream, "xop_prepare");
             CU_TRY(h, launch_xop_prepare(a.L.fmt, a.L.in_dim, chunk, c.a, pre == STRIX_PRE_RMSNORM ? d_b : c.b, a_stride,
@@ -453,8 +454,16 @@ int strix_cuda_create(int device, const strix_cuda_opts *opts, strix_cuda **out)
     if (e == cudaSuccess) e = chain_prepare_device(h->smem_optin);
     if (e == cudaSuccess) e = gemm_prepare_device();
     if (e == cudaSuccess) e = noalloc_prepare_device(device);
+    // the operand image of a GEMV whose activations are prepared by a kernel of their own: at most 8 rows of 16384
+    // elements (320 bytes per 32-block), allocated here because its first use may lie inside a stream capture
+    if (e == cudaSuccess) {
+        const size_t image_max = (size_t)512 * 320 + 4096;
+        e = cudaMalloc(&h->xop, image_max);
+        if (e == cudaSuccess) h->xop_cap = image_max;
+    }
     if (e != cudaSuccess) {
         g_create_error = std::string("create: ") + cudaGetErrorString(e);
+        if (h->xop) cudaFree(h->xop);
         if (h->d_status) cudaFree(h->d_status);
         if (h->stream) cudaStreamDestroy(h->stream);
         delete h;
@@ -512,6 +521,7 @@ int strix_cuda_set_option(strix_cuda *h, const char *name, long long value) {
     else if (n == "gemv_pdl") h->tune.pdl = v;
     else if (n == "gemv_debug") h->tune.debug = v;
     else if (n == "rows_operand_image") h->tune.xop = v;
+    else if (n == "operand_image_min_k") h->tune.xop_single_min_k = v;
     else if (n == "batch_graph") h->use_batch_graph = value != 0;
     else if (n == "kv_f16") h->kv_f16 = value != 0;
     else if (n == "decode_chain") h->decode_chain = value < 0 ? -1 : value != 0;

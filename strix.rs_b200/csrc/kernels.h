@@ -83,6 +83,8 @@ struct GemvTune {
     uint32_t force_wc = 0, force_ct = 0, force_sk = 0;  // warps per row group / blocks per stage / stages per slot (0 = planned)
     uint32_t pdl = 1;          // programmatic stream serialization between GEMV launches
     uint32_t xop = 1;          // batched integer-dot GEMV: operands prepared once by a kernel of their own (0 = by every CTA)
+    uint32_t xop_single_min_k = 8192;  // ... and a single activation row too, from this in_dim on (measured: decode chain 1.365 -> 1.300 ms per token
+                               // with its 9728-long rows prepared this way, 1.32 from 4096 on, 1.37 from 2560 on; verify step 2.08 -> 1.98 ms)
     uint32_t debug = 0;        // measurement only: bit 0 stream the tiles without arithmetic, bit 1 empty launch,
                                // bit 2 stop after the activation prologue
 };
