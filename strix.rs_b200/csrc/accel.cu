@@ -504,6 +504,7 @@ void strix_cuda_destroy(strix_cuda *h) {
     if (h->y.p) cudaFree(h->y.p);
     if (h->pin_in.p) cudaFreeHost(h->pin_in.p);
     if (h->pin_out.p) cudaFreeHost(h->pin_out.p);
+    if (h->xop) cudaFree(h->xop);
     cudaFree(h->d_status);
     cudaStreamDestroy(h->stream);
     delete h;
