@@ -34,13 +34,14 @@ namespace strix {
 
 // Shared-memory map (bytes). 0..1919 as in gemv_tiles.cuh (full / empty mbarriers, control words, oscale);
 // the activation prologues use [SMEM_PART_OFF, +2048) as reduction scratch.
-// Consumer warps: three per scheduler. Every phase of a 2 us step is run by all consumer warps and its
-// bookkeeping (stage hand-overs, polls, barriers) is per warp, so fewer warps mean fewer instructions
-// competing for issue slots, and 416 threads leave each one 128 registers (24 warps: 72, with spills
-// in the tile loop). Measured on the 36-layer decode chain: 24 warps 1.35 ms, 12 warps 1.37 ms per token
-// with the step skeleton alone (no arithmetic, no waiting) at 1.01 against 0.89 ms.
+// Consumer warps: fifteen, i.e. sixteen warps with the producer. Every phase of a 2 us step is run by all consumer
+// warps and its bookkeeping (stage hand-overs, polls, barriers) is per warp, so fewer warps mean fewer instructions
+// competing for issue slots; the compiler gives a thread 128 registers for any CTA of 13 to 16 warps (24 warps: 72,
+// with spills in the tile loop), so sixteen is the most that costs no registers. Measured on the 36-layer decode
+// chain, ms per token on one box: 11 warps 1.384, 12 1.386, 14 1.394, 15 1.345-1.353; 24 warps 1.35 against 1.37
+// for 12 in an earlier revision. Row-sharded over two GPUs: 1.151 with 15 against 1.160-1.168 with 12.
 #ifndef STRIX_CHAIN_WARPS
-#define STRIX_CHAIN_WARPS 12
+#define STRIX_CHAIN_WARPS 15
 #endif
 constexpr uint32_t CH_WARPS = STRIX_CHAIN_WARPS;
 constexpr uint32_t CH_PART_OFF = SMEM_PART_OFF + 2048u;  // [CHAIN_PART_SLOTS][CH_WARPS][16] f32 partial sums
