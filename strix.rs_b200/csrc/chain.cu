@@ -7,8 +7,8 @@
 //   * the producer warp of every CTA streams the weights of step after step through ONE ring of
 //     stages (1-D bulk async copies, mbarrier complete_tx) and never waits for another CTA - weights
 //     depend on nothing - so HBM keeps streaming while activations are exchanged;
-//   * all 24 consumer warps of a CTA work on every stage: the CTA's tiles of a step form one flat
-//     list and tile u belongs to warp u mod 24, whatever row group it is in, so small steps (160 row
+//   * all consumer warps of a CTA work on every stage: the CTA's tiles of a step form one flat
+//     list and tile u belongs to warp u mod CH_WARPS, whatever row group it is in, so small steps (160 row
 //     groups on 148 SMs) still use every warp. A warp keeps the partial sums of the row group it is
 //     in; they wait in shared memory, per (row group, warp), and are added in warp order (deterministic)
 //     once per step (or per 12 row groups);
