@@ -397,7 +397,7 @@ __device__ __forceinline__ void chain_flush(const ChainStep &S, ChainCta &C, uin
     for (uint32_t p = 0; p < M.n_out_ll; p++) ll_store(M.out_ll[p] + M.row_base + o, val, epoch);
 }
 
-// ---- consumers: all warps on every stage; tile u of the CTA's flat list of this step belongs to warp u mod 24 ----
+// ---- consumers: all warps on every stage; tile u of the CTA's flat list of this step belongs to warp u mod CH_WARPS ----
 template <int FMT, int ACT, bool PAIR>
 __device__ __forceinline__ void chain_consume(const ChainStep &S, ChainCta &C, uint32_t epoch) {
     uint8_t *smem = C.c.smem;
