@@ -182,6 +182,11 @@ STRIX_API int strix_cuda_peer_barrier_dev(strix_cuda *h, uint32_t *d_epoch, uint
  * own costs such an item more in fill and drain than its weights take to stream). The others get a launch each,
  * before it. The host-pointer form strix_cuda_gemv_batch splits a batch the same way.
  * set_option("batch_side_by_side", 0) gives every item its own launch, 2 runs all items side by side.
+ * Because the items are independent, only the batch's FIRST launch waits for the work that precedes the call on
+ * `stream`; every later launch starts its row groups as soon as its CTAs get an SM, beside the tail of the launch
+ * before it, and waits for that launch only at its own end, so that the batch still completes in stream order
+ * (set_option("batch_overlap", 0): every launch waits before it reads its activation, as an ordinary GEMV does).
+ * All activations must therefore be complete before the call; none may be written by an item of the batch.
  * 0 = an unknown key or a null vector. */
 STRIX_API int strix_cuda_gemv_batch_dev(strix_cuda *h, size_t n, const char *const *keys, const float *const *d_xs,
                               float *const *d_ys, int act, void *stream);
@@ -413,7 +418,8 @@ STRIX_API int strix_cuda_clear_device_status(strix_cuda *h, void *stream);
  * 8192), "gemv_debug" (bit 0: stream the weights without
  * arithmetic, bit 1: empty launches, bit 2: stop after the activation prologue), "batch_graph" (gemv_batch
  * replays a cached CUDA graph), "batch_side_by_side" / "batch_small_bytes" (which items of a gemv_batch share a launch,
- * see strix_cuda_gemv_batch_dev), "decode_chain" (the projection chain as one persistent launch),
+ * see strix_cuda_gemv_batch_dev), "batch_overlap" (later launches of a batch do not wait for earlier ones; 1),
+ * "decode_chain" (the projection chain as one persistent launch),
  * "kv_f16" (real attention keeps its KV cache in f16),
  * "chain_trace" (per-step clocks, see strix_cuda_decode_trace), "chain_debug" (bit 0: the chain kernel skips
  * the arithmetic, bit 1: its waits on exchange vectors do not wait; results are then meaningless), "poll_limit" (bound, in polls, of a wait on

@@ -220,11 +220,29 @@ static void batch_set_peers(GemvArgs &a, const Resident *w, float *const *peer_y
     for (int p = 0; p < n_peers; p++) a.mat[0].peer_y[p] = peer_ys[i * (size_t)n_peers + (size_t)p];
 }
 // one item as a launch of its own
+// The place of each launch among the launches of one batch (GemvArgs::order): the items are independent, so only the
+// first launch waits for what the batch follows and the later ones overlap their predecessors' tails. Off when an
+// item's operands come from a preparation launch of their own (that launch writes what the next one reads).
+struct BatchOrder {
+    bool overlap = false;
+    uint32_t launched = 0;
+    uint32_t next() { return overlap ? (launched++ ? 2u : 1u) : 0u; }
+};
+static bool batch_item_prepares_operands(const strix_cuda *h, const Resident *w, int act) {
+    return act == STRIX_ACT_Q8DOT && h->tune.xop != 0 && w->L.in_dim >= h->tune.xop_single_min_k && w->L.in_dim <= 16384u;
+}
+static BatchOrder batch_order(const strix_cuda *h, size_t n, const Resident *const *ws, int act) {
+    BatchOrder o;
+    o.overlap = h->batch_overlap != 0 && h->tune.pdl != 0;
+    for (size_t i = 0; o.overlap && i < n; i++)
+        if (ws[i] && batch_item_prepares_operands(h, ws[i], act)) o.overlap = false;
+    return o;
+}
 static int batch_enqueue_one(strix_cuda *h, size_t i, const Resident *const *ws, const float *const *d_xs, float *const *d_ys,
-                             float *const *peer_ys, int n_peers, int act, cudaStream_t s) {
+                             float *const *peer_ys, int n_peers, int act, cudaStream_t s, BatchOrder &order) {
     const Resident *w1[1] = {ws[i]};
     float *y1[1] = {d_ys ? d_ys[i] : nullptr};
-    if (!peer_ys) return gemv_launch(h, 1, w1, d_xs[i], nullptr, 0.f, STRIX_PRE_NONE, act, y1, nullptr, s);
+    if (!peer_ys && !order.overlap) return gemv_launch(h, 1, w1, d_xs[i], nullptr, 0.f, STRIX_PRE_NONE, act, y1, nullptr, s);
     GemvArgs a{};
     if (gemv_fill_args(h, 1, w1, d_xs[i], nullptr, 0.f, STRIX_PRE_NONE, act, y1, nullptr, &a) < 0) return -1;
     batch_set_peers(a, ws[i], peer_ys, i, n_peers);
@@ -233,13 +251,14 @@ static int batch_enqueue_one(strix_cuda *h, size_t i, const Resident *const *ws,
         h->err = "gemv_batch: in_dim too large for the shared-memory pipeline";
         return -1;
     }
+    a.order = order.next();
     ProfScope prof(h, s, gemv_prof_name(a));
     CU_TRY(h, launch_gemv(a, s));
     return 1;
 }
 static int batch_enqueue_side_by_side(strix_cuda *h, const std::vector<size_t> &idx, const Resident *const *ws,
                                       const float *const *d_xs, float *const *d_ys, int act, cudaStream_t s,
-                                      float *const *peer_ys = nullptr, int n_peers = 0) {
+                                      BatchOrder &order, float *const *peer_ys = nullptr, int n_peers = 0) {
     for (size_t at = 0; at < idx.size(); at += GEMV_MULTI_MAX) {
         const size_t cnt = std::min<size_t>(GEMV_MULTI_MAX, idx.size() - at);
         GemvMultiArgs m{};
@@ -254,12 +273,13 @@ static int batch_enqueue_side_by_side(strix_cuda *h, const std::vector<size_t> &
         }
         if (ok) ok = gemv_multi_plan(m, h->num_sms, h->smem_optin, h->tune);
         if (ok) {
+            m.order = order.next();
             ProfScope prof(h, s, "gemv_multi");
             CU_TRY(h, launch_gemv_multi(m, s));
             continue;
         }
         for (size_t k = 0; k < cnt; k++)
-            if (batch_enqueue_one(h, idx[at + k], ws, d_xs, d_ys, peer_ys, n_peers, act, s) < 0) return -1;
+            if (batch_enqueue_one(h, idx[at + k], ws, d_xs, d_ys, peer_ys, n_peers, act, s, order) < 0) return -1;
     }
     return 1;
 }
@@ -504,7 +524,6 @@ void strix_cuda_destroy(strix_cuda *h) {
     if (h->y.p) cudaFree(h->y.p);
     if (h->pin_in.p) cudaFreeHost(h->pin_in.p);
     if (h->pin_out.p) cudaFreeHost(h->pin_out.p);
-    if (h->xop) cudaFree(h->xop);
     cudaFree(h->d_status);
     cudaStreamDestroy(h->stream);
     delete h;
@@ -531,6 +550,7 @@ int strix_cuda_set_option(strix_cuda *h, const char *name, long long value) {
     // (what follows leaves a configured decode chain as it is)
     else if (n == "batch_side_by_side") { h->batch_side_by_side = (int)v; return 1; }
     else if (n == "batch_small_bytes") { h->batch_small_bytes = (size_t)value; return 1; }
+    else if (n == "batch_overlap") { h->batch_overlap = (int)v; batch_release(h); return 1; }
     else if (n == "profile") { h->profile = value != 0; return 1; }
     else if (n == "chain_trace") {
         h->chain_trace = value != 0;
@@ -697,15 +717,13 @@ int strix_cuda_gemv_batch(strix_cuda *h, size_t n, const char *const *keys, cons
     auto enqueue = [&](bool graph) -> int {
         CU_TRY(h, cudaMemcpyAsync(h->x.p, pin, xtot * 4, cudaMemcpyHostToDevice, h->stream));
         cudaEvent_t last = nullptr;
+        BatchOrder order = batch_order(h, n, ws.data(), act);
         for (size_t u = 0; u < nu; u++) {
             if (units[u].size() > 1) {
-                if (batch_enqueue_side_by_side(h, units[u], ws.data(), dxs.data(), dys.data(), act, h->stream) < 0) return -1;
+                if (batch_enqueue_side_by_side(h, units[u], ws.data(), dxs.data(), dys.data(), act, h->stream, order) < 0) return -1;
             } else {
-                for (size_t i : units[u]) {
-                    const Resident *w1[1] = {ws[i]};
-                    float *y1[1] = {dys[i]};
-                    if (gemv_launch(h, 1, w1, dxs[i], nullptr, 0.f, STRIX_PRE_NONE, act, y1, nullptr, h->stream) < 0) return -1;
-                }
+                for (size_t i : units[u])
+                    if (batch_enqueue_one(h, i, ws.data(), dxs.data(), dys.data(), nullptr, 0, act, h->stream, order) < 0) return -1;
             }
             if (group_end[u] != u) continue;  // its outputs leave with a later unit's (see group_end)
             cudaEvent_t done = h->batch_events[2 * u], copied = h->batch_events[2 * u + 1];
@@ -830,9 +848,10 @@ static int gemv_batch_device(strix_cuda *h, size_t n, const char *const *keys, c
     const std::vector<size_t> small = batch_small_items(h, n, ws.data());
     std::vector<char> is_small(n, 0);
     for (size_t i : small) is_small[i] = 1;
+    BatchOrder order = batch_order(h, n, ws.data(), act);
     for (size_t i = 0; i < n; i++)
-        if (!is_small[i] && batch_enqueue_one(h, i, ws.data(), d_xs, d_ys, peer_ys, n_peers, act, s) < 0) return -1;
-    if (!small.empty() && batch_enqueue_side_by_side(h, small, ws.data(), d_xs, d_ys, act, s, peer_ys, n_peers) < 0) return -1;
+        if (!is_small[i] && batch_enqueue_one(h, i, ws.data(), d_xs, d_ys, peer_ys, n_peers, act, s, order) < 0) return -1;
+    if (!small.empty() && batch_enqueue_side_by_side(h, small, ws.data(), d_xs, d_ys, act, s, order, peer_ys, n_peers) < 0) return -1;
     return 1;
 }
 

@@ -74,6 +74,7 @@ struct strix_cuda {
     // gemv_batch / gemv_batch_dev: the small items of a batch (independent GEMVs that would each pay a launch's fill
     // and drain, ~9 us against 3-4 us of HBM time) run side by side in one launch (gemv_multi_kernel)
     int batch_side_by_side = 1;       // 0 = a launch per item, 1 = items up to batch_small_bytes share launches, 2 = all items do
+    int batch_overlap = 1;            // later launches of a batch do not wait for the earlier ones (GemvArgs::order)
     size_t batch_small_bytes = (size_t)256 << 20;  // (measured on 1/2 and 1/4 row shards of the benchmark step: 87 against 95 us, 50 against 61 us with 64 MiB)
     volatile uint32_t *batch_flags = nullptr;  // pinned, BATCH_GRAPH_MAX words
     uint32_t *d_one = nullptr;                 // device word holding 1

@@ -61,6 +61,14 @@ struct GemvArgs {
     uint32_t digits;         // f32 activations carried as three int8 digits per value (Q6_K, one activation row)
     uint32_t pdl;            // launch with programmatic stream serialization
     uint32_t rot;            // chain kernel: CTA that takes the step's first row group
+    // Place among the launches of a batch of INDEPENDENT items (activations all there before the batch starts, outputs
+    // disjoint), which have no reason to wait for one another. 0 = an ordinary launch: dependents may be scheduled
+    // from its start, and it waits for the grid before it ahead of its activation prologue. 1 = the batch's first
+    // launch: waits the same way, but lets dependents be scheduled only AFTER that wait, so that nothing of the batch
+    // starts before the work the batch follows is complete. 2 = a later launch of the batch: runs its prologue and its
+    // row groups as soon as its CTAs get an SM, and waits for the grid before it only at its end (completion stays in
+    // stream order). Between two such launches no SM idles while the slowest CTA of the first one finishes.
+    uint32_t order;
     // Integer-dot form with the activation operands prepared ONCE by a kernel of their own (launch_xop_prepare)
     // instead of by every CTA: the image of the shared-memory operand region (x_layout order) in global
     // memory, which each CTA fetches with bulk copies. Null = the CTA builds its operands itself.
@@ -104,6 +112,7 @@ struct GemvMultiArgs {
     uint32_t n;
     uint32_t cta0[GEMV_MULTI_MAX + 1];
     uint32_t grid, smem_bytes, pdl;
+    uint32_t order;  // as GemvArgs::order
 };
 static_assert(sizeof(GemvMultiArgs) <= 4000, "passed by value: kernel parameters are limited to 4 KB");
 bool gemv_multi_plan(GemvMultiArgs &m, int num_sms, size_t smem_optin, const GemvTune &tune);

@@ -470,18 +470,20 @@ def test_gemv_batch_small_items_side_by_side(pkg, orc, synth, act_name):
                 r1, r2 = rel_l2(g, oracle_of(i)), rel_l2(g, want[i])
                 assert r1 <= REL_L2_TOL and r2 <= 1e-5, (tag, i, r1, r2)
 
-        for mode in (1, 2, 0):
+        for mode, overlap in ((1, 1), (1, 0), (2, 1), (0, 1), (0, 0)):
             assert acc.set_option("batch_side_by_side", mode)
+            assert acc.set_option("batch_overlap", overlap)   # later launches of the batch wait for nothing / as usual
             for y in ys:
                 y.zero_()
             assert acc.gemv_batch_dev(keys, [x.data_ptr() for x in xs], [y.data_ptr() for y in ys], act=act)
             torch.cuda.synchronize()
-            check([y.cpu().numpy() for y in ys], "dev mode %d" % mode)
+            check([y.cpu().numpy() for y in ys], "dev mode %d overlap %d" % (mode, overlap))
             got = acc.gemv_batch(list(zip(keys, hx)), act=act)
             check(got, "host mode %d" % mode)
             got = acc.gemv_batch(list(zip(keys, hx)), act=act)   # the cached graph
             check(got, "host mode %d again" % mode)
         assert acc.set_option("batch_side_by_side", 1)
+        assert acc.set_option("batch_overlap", 1)
         st = torch.cuda.Stream(device=dev)
         with torch.cuda.stream(st):
             assert acc.gemv_batch_dev(keys, [x.data_ptr() for x in xs], [y.data_ptr() for y in ys], act=act, stream=st.cuda_stream)
@@ -549,6 +551,75 @@ def test_profile_option_times_every_launch(pkg, synth):
         assert "gemv" not in acc.profile_dump()
     finally:
         acc.close()
+
+
+def test_gemv_batch_overlap_keeps_stream_order(pkg, synth):
+    """The launches of a batch do not wait for one another, but the batch as a whole keeps its place in the stream:
+    activations written by kernels enqueued just before the call (behind a long-running one) are the ones every item
+    reads, and a reader enqueued just after the call sees every item's output. Two sets of activations alternate;
+    the results must equal, bit for bit, those of the same batch run with every launch waiting."""
+    import torch
+    dev = torch.device("cuda", 0)
+    shapes = [(synth.Q8_0, 2560, 9000), (synth.Q6_K, 2560, 7000), (synth.Q8_0, 1024, 640), (synth.Q4_0, 4096, 777),
+              (synth.Q6_K, 2560, 331)]
+    acc = pkg.CudaWeightAccel(0)
+    try:
+        assert acc.set_option("batch_small_bytes", 4 << 20)   # items 0 and 1: a launch each; 2..4 side by side
+        keys = []
+        for i, (ty, k, n) in enumerate(shapes):
+            keys.append("so.%d" % i)
+            up = {synth.Q8_0: acc.upload_q8_0, synth.Q6_K: acc.upload_q6_k, synth.Q4_0: acc.upload_q4_0}[ty]
+            assert up(keys[-1], synth.quant(ty, 631, keys[-1], n, k), k, n)
+        sets = [[torch.from_numpy(synth.normal(632 + v, keys[i], k)).to(dev) for i, (_, k, _) in enumerate(shapes)]
+                for v in range(2)]
+        xs = [torch.zeros(k, device=dev) for (_, k, _) in shapes]
+        ys = [torch.zeros(n, device=dev) for (_, _, n) in shapes]
+        s = torch.cuda.current_stream().cuda_stream
+        ballast = torch.ones(32 << 20, device=dev)
+
+        def run(v):
+            ballast.mul_(1.0000001)                       # ~0.1 ms of work the copies queue behind
+            for x, src in zip(xs, sets[v]):
+                x.copy_(src)
+            assert acc.gemv_batch_dev(keys, [x.data_ptr() for x in xs], [y.data_ptr() for y in ys], stream=s)
+            return [y.clone() for y in ys]                # readers enqueued right behind the batch
+
+        assert acc.set_option("batch_overlap", 0)
+        want = [run(v) for v in range(2)]
+        torch.cuda.synchronize()
+        assert not any(torch.equal(a, b) for a, b in zip(want[0], want[1]))
+        assert acc.set_option("batch_overlap", 1)
+        for it in range(6):
+            got = run(it & 1)
+            torch.cuda.synchronize()
+            for i, (g, w) in enumerate(zip(got, want[it & 1])):
+                assert torch.equal(g, w), (it, i)
+        assert acc.device_status() == 0
+    finally:
+        acc.close()
+
+
+def test_close_leaves_no_cuda_error_behind(pkg, synth):
+    """A handle that is created, used and closed leaves no pending CUDA error for the next user of the runtime in
+    the process (a runtime call that fails, a second free of one pointer for one, stays 'the last error' until someone
+    asks for it, and the next library that checks after its own launch reports it as its own)."""
+    import ctypes
+    import torch
+    rt = ctypes.CDLL("libcudart.so.12")
+    rt.cudaPeekAtLastError.restype = ctypes.c_int
+    torch.zeros(4, device="cuda:0")
+    torch.cuda.synchronize()
+    assert rt.cudaPeekAtLastError() == 0
+    acc = pkg.CudaWeightAccel(0)
+    k, n = 1024, 64
+    assert acc.upload_q8_0("c.a", synth.quant(synth.Q8_0, 641, "c.a", n, k), k, n)
+    x = synth.normal(642, "c.x", k)
+    assert acc.gemv("c.a", x) is not None
+    assert acc.gemv("c.a", x, act=pkg.ACT_Q8DOT) is not None
+    acc.close()
+    assert rt.cudaPeekAtLastError() == 0
+    torch.full((4,), 1.0, device="cuda:0")
+    torch.cuda.synchronize()
 
 
 def test_gemv_batch_peers_dev_fills_every_ranks_full_vectors(pkg, orc, synth):
