@@ -711,17 +711,10 @@ bool gemv_multi_plan(GemvMultiArgs &m, int num_sms, size_t smem_optin, const Gem
     // (Q8_0 runs at the memory pipeline's pace; the others are bound by instruction issue: measured fractions of
     // the copy peak on large launches are 0.93 Q8_0, 0.74 Q6_K as digits or int8, 0.60 Q6_K and Q4_0 on f16 tiles,
     // 0.74 Q4_0 int8)
-    // Side by side, a Q6_K problem with an f32 row takes the digit form whenever its operands fit beside two stages, not
-    // only up to 8192 elements: here it has its share of the SMs to itself and is bound by instruction issue (68
-    // against 90 instructions per tile), where a launch of its own with a long row is bound by what is left for the
-    // rings (measured inside the benchmark step, 9728-long rows: 165.5 against 167.2 us in a half-second run, 147.1
-    // against 150.0 us in a burst).
-    GemvTune tune_here = tune;
-    if (tune_here.digits_rule == 1) tune_here.digits_rule = 2;
     auto slow = [&](uint32_t i) -> uint64_t {
         const GemvArgs &a = m.p[i];
-        const bool f16_tiles = a.act == STRIX_ACT_F32 && !(a.L.fmt == FMT_Q6_K && tune_here.digits_rule != 0 &&
-                                                            (a.L.in_dim <= 8192u || tune_here.digits_rule == 2));
+        const bool f16_tiles = a.act == STRIX_ACT_F32 && !(a.L.fmt == FMT_Q6_K && tune.digits_rule != 0 &&
+                                                            (a.L.in_dim <= 8192u || tune.digits_rule == 2));
         if (a.L.fmt == FMT_Q8_0) return 100;
         return f16_tiles ? 155 : 125;
     };
@@ -737,7 +730,7 @@ bool gemv_multi_plan(GemvMultiArgs &m, int num_sms, size_t smem_optin, const Gem
     for (uint32_t i = 0; i < n; i++) {
         GemvArgs &a = m.p[i];
         a.nbatch = 1;
-        if (!gemv_plan(a, (int)nc[i], smem_optin, tune_here)) return false;
+        if (!gemv_plan(a, (int)nc[i], smem_optin, tune)) return false;
         a.rot = 0;
         m.cta0[i] = c0;
         c0 += a.grid ? a.grid : 1u;  // (a problem without rows keeps one idle CTA: the CTA ranges stay well-formed)
