@@ -186,7 +186,8 @@ STRIX_API int strix_cuda_peer_barrier_dev(strix_cuda *h, uint32_t *d_epoch, uint
  * `stream`; every later launch starts its row groups as soon as its CTAs get an SM, beside the tail of the launch
  * before it, and waits for that launch only at its own end, so that the batch still completes in stream order
  * (set_option("batch_overlap", 0): every launch waits before it reads its activation, as an ordinary GEMV does).
- * All activations must therefore be complete before the call; none may be written by an item of the batch.
+ * All activations must therefore come from work that precedes the call on `stream` (or be complete already); none may
+ * be written by an item of the batch.
  * 0 = an unknown key or a null vector. */
 STRIX_API int strix_cuda_gemv_batch_dev(strix_cuda *h, size_t n, const char *const *keys, const float *const *d_xs,
                               float *const *d_ys, int act, void *stream);
