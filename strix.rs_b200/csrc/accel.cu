@@ -222,7 +222,8 @@ static void batch_set_peers(GemvArgs &a, const Resident *w, float *const *peer_y
 // one item as a launch of its own
 // The place of each launch among the launches of one batch (GemvArgs::order): the items are independent, so only the
 // first launch waits for what the batch follows and the later ones overlap their predecessors' tails. Off when an
-// item's operands come from a preparation launch of their own (that launch writes what the next one reads).
+// item that runs as a launch of its own gets its operands from a preparation launch (that launch writes what the
+// next one reads); items that run side by side always build their operands themselves.
 struct BatchOrder {
     bool overlap = false;
     uint32_t launched = 0;
@@ -231,11 +232,11 @@ struct BatchOrder {
 static bool batch_item_prepares_operands(const strix_cuda *h, const Resident *w, int act) {
     return act == STRIX_ACT_Q8DOT && h->tune.xop != 0 && w->L.in_dim >= h->tune.xop_single_min_k && w->L.in_dim <= 16384u;
 }
-static BatchOrder batch_order(const strix_cuda *h, size_t n, const Resident *const *ws, int act) {
+static BatchOrder batch_order(const strix_cuda *h, size_t n, const Resident *const *ws, int act, const std::vector<char> &is_small) {
     BatchOrder o;
     o.overlap = h->batch_overlap != 0 && h->tune.pdl != 0;
     for (size_t i = 0; o.overlap && i < n; i++)
-        if (ws[i] && batch_item_prepares_operands(h, ws[i], act)) o.overlap = false;
+        if (ws[i] && !is_small[i] && batch_item_prepares_operands(h, ws[i], act)) o.overlap = false;
     return o;
 }
 static int batch_enqueue_one(strix_cuda *h, size_t i, const Resident *const *ws, const float *const *d_xs, float *const *d_ys,
@@ -717,7 +718,7 @@ int strix_cuda_gemv_batch(strix_cuda *h, size_t n, const char *const *keys, cons
     auto enqueue = [&](bool graph) -> int {
         CU_TRY(h, cudaMemcpyAsync(h->x.p, pin, xtot * 4, cudaMemcpyHostToDevice, h->stream));
         cudaEvent_t last = nullptr;
-        BatchOrder order = batch_order(h, n, ws.data(), act);
+        BatchOrder order = batch_order(h, n, ws.data(), act, is_small);
         for (size_t u = 0; u < nu; u++) {
             if (units[u].size() > 1) {
                 if (batch_enqueue_side_by_side(h, units[u], ws.data(), dxs.data(), dys.data(), act, h->stream, order) < 0) return -1;
@@ -848,7 +849,7 @@ static int gemv_batch_device(strix_cuda *h, size_t n, const char *const *keys, c
     const std::vector<size_t> small = batch_small_items(h, n, ws.data());
     std::vector<char> is_small(n, 0);
     for (size_t i : small) is_small[i] = 1;
-    BatchOrder order = batch_order(h, n, ws.data(), act);
+    BatchOrder order = batch_order(h, n, ws.data(), act, is_small);
     for (size_t i = 0; i < n; i++)
         if (!is_small[i] && batch_enqueue_one(h, i, ws.data(), d_xs, d_ys, peer_ys, n_peers, act, s, order) < 0) return -1;
     if (!small.empty() && batch_enqueue_side_by_side(h, small, ws.data(), d_xs, d_ys, act, s, order, peer_ys, n_peers) < 0) return -1;
