@@ -219,7 +219,6 @@ static void batch_set_peers(GemvArgs &a, const Resident *w, float *const *peer_y
     a.mat[0].row_base = (uint32_t)w->row0;
     for (int p = 0; p < n_peers; p++) a.mat[0].peer_y[p] = peer_ys[i * (size_t)n_peers + (size_t)p];
 }
-// one item as a launch of its own
 // The place of each launch among the launches of one batch (GemvArgs::order): the items are independent, so only the
 // first launch waits for what the batch follows and the later ones overlap their predecessors' tails. Off when an
 // item that runs as a launch of its own gets its operands from a preparation launch (that launch writes what the
@@ -239,6 +238,7 @@ static BatchOrder batch_order(const strix_cuda *h, size_t n, const Resident *con
         if (ws[i] && !is_small[i] && batch_item_prepares_operands(h, ws[i], act)) o.overlap = false;
     return o;
 }
+// one item as a launch of its own
 static int batch_enqueue_one(strix_cuda *h, size_t i, const Resident *const *ws, const float *const *d_xs, float *const *d_ys,
                              float *const *peer_ys, int n_peers, int act, cudaStream_t s, BatchOrder &order) {
     const Resident *w1[1] = {ws[i]};
