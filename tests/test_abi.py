@@ -51,3 +51,16 @@ def test_rust_ffi_is_generated_from_the_headers():
     txt = open(os.path.join(ROOT, "strix.rs_b200", "rust", "strix-backend-cuda", "src", "ffi.rs")).read()
     for name in declared_symbols():
         assert "pub fn %s(" % name in txt, name
+
+
+def test_every_option_name_is_documented_in_the_header():
+    """strix_cuda_set_option answers 0 for a name it does not know; every name it does know must be described in
+    include/strix_cuda.h, which is all a binder has to go by."""
+    src = open(os.path.join(ROOT, "strix.rs_b200", "csrc", "accel.cu")).read()
+    body = src[src.index("int strix_cuda_set_option("):]
+    body = body[:body.index("\n}\n")]
+    import re
+    names = re.findall(r'n == "([a-z0-9_]+)"', body)
+    assert len(names) >= 10
+    hdr = open(os.path.join(ROOT, "include", "strix_cuda.h")).read()
+    assert [n for n in names if '"%s"' % n not in hdr] == []
