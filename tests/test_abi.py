@@ -59,7 +59,6 @@ def test_every_option_name_is_documented_in_the_header():
     src = open(os.path.join(ROOT, "strix.rs_b200", "csrc", "accel.cu")).read()
     body = src[src.index("int strix_cuda_set_option("):]
     body = body[:body.index("\n}\n")]
-    import re
     names = re.findall(r'n == "([a-z0-9_]+)"', body)
     assert len(names) >= 10
     hdr = open(os.path.join(ROOT, "include", "strix_cuda.h")).read()
