@@ -1022,8 +1022,8 @@ def main():
                 by = sum(it["bytes"] * it["y"].numel() / it["n"] for it in u)
                 us = statistics.median(evs[r][i][0].elapsed_time(evs[r][i][1]) for r in range(rounds)) * 1e3
                 detail.append({"weight": " + ".join(it["key"] for it in u), "us": round(us, 2), "gbs": round(by / us / 1e3, 1)})
-        # The kernels of the timed step: one instantiation of gemv_kernel per large weight (Q8_0 with the f32 row on
-        # f16 tiles; Q6_K with the f32 row as int8 digits for K <= 8192, on f16 tiles beyond) and gemv_multi_kernel
+        # The kernels of the timed step: one instantiation of gemv_kernel per large weight (Q8_0 and Q6_K with the f32
+        # row as int8 digits for K <= 8192, on f16 tiles beyond) and gemv_multi_kernel
         # for the weights that run side by side. The roofline is reported for the one with the largest share of the
         # step (these per-launch events; the ncu launch list under profiles/ gives the same order), on its largest
         # launch; the runner-up follows as second_kernel. DRAM traffic per launch from the ncu captures of
@@ -1033,13 +1033,13 @@ def main():
                 return "gemv_multi_kernel<%d weights side by side>" % len(u)
             it = u[0]
             if it["ty"] == Q8_0:
-                return "gemv_kernel<Q8_0, f32 row on f16 tiles>"
+                return "gemv_kernel<Q8_0, f32 row as int8 digits>" if it["k"] <= 8192 else "gemv_kernel<Q8_0, f32 row on f16 tiles>"
             return "gemv_kernel<Q6_K, f32 row as int8 digits>" if it["k"] <= 8192 else "gemv_kernel<Q6_K, f32 row on f16 tiles>"
         share = {}
         for d, u in zip(detail, units):
             share[kernel_of(u)] = share.get(kernel_of(u), 0.0) + d["us"]
         order = sorted(share, key=lambda k_: -share[k_])
-        traffic65536 = {Q8_0: 181.86e6, Q6_K: 141.15e6}   # dram__bytes_read.sum + dram__bytes_write.sum, 65536 x 2560
+        traffic65536 = {Q8_0: 181.93e6, Q6_K: 141.15e6}   # dram__bytes_read.sum + dram__bytes_write.sum, 65536 x 2560
 
         def unit_bytes(u):
             return sum(it["bytes"] * it["y"].numel() / it["n"] for it in u)

@@ -156,7 +156,9 @@ __device__ __forceinline__ void consumer_groups(const GemvArgs &A, Cta &C) {
     const uint32_t n_op = XL.cols * 4u;
     const uint32_t lane_eff = (n_op > 16u && lane >= 16u) ? 16u + (lane - 16u) % (n_op - 16u) : lane % n_op;
     const uint32_t xb_l = xs0 + XL.xb + lane_eff * (ACT == STRIX_ACT_F32 ? 16u : 8u);
-    const uint32_t xr_l = xs0 + XL.rec + ((FMT == FMT_Q6_K || MULTI) ? 16u * t : (FMT == FMT_Q4_1 && ACT == STRIX_ACT_F32) ? 4u * t : 0u);
+    const uint32_t xr_l = xs0 + XL.rec + ((FMT == FMT_Q6_K || MULTI || ACT == ACT_F32_DIGITS) ? 16u * t
+                                          : (FMT == FMT_Q4_1 && ACT == STRIX_ACT_F32)             ? 4u * t
+                                                                                                   : 0u);
     const TileConsts TC = tile_consts<FMT, ACT>();
     const uint32_t xb_step = wc * XL.xb_stride, xr_step = wc * XL.rec_stride, ta_step = wc * L.tile_bytes;
     const uint32_t q6_step = wc * Q6_SUB;
@@ -356,7 +358,7 @@ __device__ __forceinline__ void multi_body(const GemvArgs &A, Cta &C) {
 }
 template <int FMT>
 __device__ __forceinline__ void multi_fmt(const GemvArgs &A, Cta &C) {
-    if constexpr (FMT == FMT_Q6_K) {
+    if constexpr (FMT == FMT_Q6_K || FMT == FMT_Q8_0) {
         if (A.digits) return multi_body<FMT, ACT_F32_DIGITS>(A, C);
     }
     if (A.act == STRIX_ACT_F32) return multi_body<FMT, STRIX_ACT_F32>(A, C);
@@ -564,8 +566,9 @@ bool gemv_plan(GemvArgs &a, int num_sms, size_t smem_optin, const GemvTune &tune
     a.x_off = align128u(SMEM_PART_OFF + pool * 32u * nv * 4u);
     // Q6_K with one f32 row: the digit form (its operands take 8 bytes of shared memory per weight
     // column, so long rows, which would starve the rings, keep the f16 form)
-    const uint32_t digit_rule = tune.digits_rule;  // 0 = never, 1 = K <= 8192, 2 = whenever it fits
-    a.digits = (a.L.fmt == FMT_Q6_K && a.act == STRIX_ACT_F32 && nbt == 1 && digit_rule != 0 &&
+    // (Q8_0 takes the same form by a rule of its own: its f16 form is the faster one in a burst on small launches)
+    const uint32_t digit_rule = a.L.fmt == FMT_Q8_0 ? tune.q8_digits_rule : tune.digits_rule;  // 0 = never, 1 = K <= 8192, 2 = whenever it fits
+    a.digits = ((a.L.fmt == FMT_Q6_K || a.L.fmt == FMT_Q8_0) && a.act == STRIX_ACT_F32 && nbt == 1 && digit_rule != 0 &&
                 (K <= 8192u || digit_rule == 2))
                    ? 1u
                    : 0u;
@@ -676,7 +679,7 @@ static cudaError_t launch_t(const GemvArgs &a, cudaStream_t stream) {
 
 template <int FMT>
 static cudaError_t launch_fmt(const GemvArgs &a, cudaStream_t stream) {
-    if constexpr (FMT == FMT_Q6_K) {
+    if constexpr (FMT == FMT_Q6_K || FMT == FMT_Q8_0) {
         if (a.digits) return launch_t<FMT, ACT_F32_DIGITS, false>(a, stream);
     }
     if (a.act == STRIX_ACT_F32) return launch_t<FMT, STRIX_ACT_F32, false>(a, stream);
@@ -782,7 +785,7 @@ static cudaError_t optin_fmt(size_t b) {
     STRIX_ATTR1(ACT_, MULTI_, STRIX_PRE_SWIGLU) STRIX_ATTR1(ACT_, MULTI_, STRIX_PRE_GEGLU)
     STRIX_ATTR(STRIX_ACT_F32, false) STRIX_ATTR(STRIX_ACT_Q8DOT, false)
     if constexpr (FMT != FMT_Q6_K) { STRIX_ATTR(STRIX_ACT_Q8DOT, true) }
-    if constexpr (FMT == FMT_Q6_K) { STRIX_ATTR(ACT_F32_DIGITS, false) }
+    if constexpr (FMT == FMT_Q6_K || FMT == FMT_Q8_0) { STRIX_ATTR(ACT_F32_DIGITS, false) }
 #undef STRIX_ATTR
 #undef STRIX_ATTR1
     return e;

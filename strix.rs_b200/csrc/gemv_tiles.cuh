@@ -107,12 +107,15 @@ constexpr uint32_t SMEM_PART_OFF = 1920;
 // (integer form with more than one activation row: C columns 2t and 2t + 1 are rows 2t, 2t + 1).
 __host__ __device__ constexpr int lane_values(int act, bool multi) { return (act == STRIX_ACT_Q8DOT && multi) ? 4 : 2; }
 
-// Kernel-internal third activation form (Q6_K, one f32 activation row): the row is carried as THREE
+// Kernel-internal third activation form (Q6_K and Q8_0, one f32 activation row): the row is carried as THREE
 // int8 digit rows, x = d * (q1 + q2 / 254 + q3 / 254^2) per 32-weight block (d = amax / 127, what is
 // left over is below 2^-24 of the block's largest value), and runs through the integer form as if
 // they were three activation rows; the epilogue adds the three partial results. The weight codes
 // then feed the u8 x s8 MMA as they are stored: no conversion to f16, which was a third of the f32
-// form's instructions for this format.
+// form's instructions for this format. For Q8_0 the f16 form is close to the memory pipeline's pace in a burst, but
+// it is the one kernel of the family that slows down under sustained load (74.9 against 65.3 us on 151936 x 2560
+// after half a second; the integer forms hold their burst time): its byte -> f16 conversions and two f16 MMAs per
+// tile are the most work per byte of all forms.
 constexpr int ACT_F32_DIGITS = 2;
 constexpr uint32_t N_DIGITS = 3;
 
@@ -131,7 +134,8 @@ constexpr uint32_t N_DIGITS = 3;
 //                      Q4_0 / Q8_0, 2..8 rows: [K/32][4] { d_x(2t), d_x(2t+1), kf(2t), kf(2t+1) }
 //                      Q6_K:                   [K/32][4] { d_x(t), -32 * sum(codes of row t, first 16) as an int,
 //                                                          the same for the last 16, 0 }
-//   digit form:    the integer form's Q6_K layout with three rows (the digits of the one f32 row)
+//   digit form:    the integer form's Q6_K layout with three rows (the digits of the one f32 row), for Q8_0 weights
+//                  too (their MMA then adds the two halves' columns)
 struct XLayout {
     uint32_t xb, rec, end;
     uint32_t xb_stride, rec_stride;  // bytes per 32-weight block
@@ -147,7 +151,7 @@ __host__ __device__ inline XLayout x_layout(int fmt, int act, uint32_t K, uint32
         X.xb_stride = X.cols * 4u * 16u;
         X.rec_stride = fmt == FMT_Q4_1 ? 16u : 0u;  // Q4_1: the block's sum of (scaled) activations, per row
     } else {
-        X.cols = fmt == FMT_Q6_K ? 2u * b : b;
+        X.cols = (fmt == FMT_Q6_K || act == ACT_F32_DIGITS) ? 2u * b : b;
         X.xb_stride = X.cols * 4u * 8u;
         X.rec_stride = (fmt == FMT_Q6_K || b > 1) ? 64u : 8u;
     }
@@ -351,6 +355,18 @@ __device__ __forceinline__ void tile_mac(uint32_t ta, uint32_t da, uint32_t xb_a
             const float dx = __uint_as_float(r.x);
             acc[0] = fmaf(Q6D ? dx * d.x : dx, (float)(s0 * c[0] + s1 * c[1]), acc[0]);
             acc[1] = fmaf(Q6D ? dx * d.y : dx, (float)(s2 * c[2] + s3 * c[3]), acc[1]);
+            return;
+        }
+        if (ACT == ACT_F32_DIGITS) {
+            // Q8_0 against the digit operands (the Q6_K layout: columns 2j, 2j + 1 = digit j against the first / last
+            // 16 weights; the record holds d_x(j) and -32 * sum(codes) of each half, the stored weight codes carry
+            // +128): y += (d_w * d_x) * (isum_first + isum_last - 128 * sum(codes))
+            const uint4 r = lds128(xr_a);
+            const int cin[4] = {4 * (int)r.y, 4 * (int)r.z, 4 * (int)r.y, 4 * (int)r.z};
+            mma_u8s8_c(c, W0, W1, W2, W3, xq.x, xq.y, cin);
+            const float dx = __uint_as_float(r.x);
+            acc[0] = fmaf(dx * d.x, (float)(c[0] + c[1]), acc[0]);
+            acc[1] = fmaf(dx * d.y, (float)(c[2] + c[3]), acc[1]);
             return;
         }
         mma_u8s8_c(c, W0, W1, W2, W3, xq.x, xq.y, C.magic);

@@ -542,7 +542,7 @@ def test_profile_option_times_every_launch(pkg, synth):
         txt = acc.profile_dump()
         print(txt)
         lines = {ln.split()[0]: ln for ln in txt.splitlines()[1:]}
-        assert "gemv.q8_0.f32" in lines and " 3 calls" in lines["gemv.q8_0.f32"]
+        assert "gemv.q8_0.f32_digits" in lines and " 3 calls" in lines["gemv.q8_0.f32_digits"]
         assert "gemv.q6_k.q8dot" in lines and " 1 calls" in lines["gemv.q6_k.q8dot"]
         assert "gemv_multi" in lines and " 1 calls" in lines["gemv_multi"]
         assert "total kernel time 0.000" in acc.profile_dump()   # reset by the dump
