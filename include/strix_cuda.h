@@ -412,7 +412,7 @@ STRIX_API int strix_cuda_clear_device_status(strix_cuda *h, void *stream);
  * environment, e.g. STRIX_NO_SPLITK / STRIX_SK / STRIX_PROF, decode.rs:5652-5671, 25-31; here nothing on
  * the call path reads the environment). 1 = set, 0 = unknown name. Any configured decode chain and cached
  * graph is dropped. Names: "q6k_digits" (0 never / 1 in_dim <= 8192 / 2 whenever it fits: Q6_K f32 row as
- * three int8 digit rows), "q8_0_digits" (the same for Q8_0), "gemv_warps_per_group", "gemv_blocks_per_stage", "gemv_stages" (0 = planned),
+ * three int8 digit rows), "q8_0_digits" / "q4_0_digits" (the same for Q8_0 / Q4_0), "gemv_warps_per_group", "gemv_blocks_per_stage", "gemv_stages" (0 = planned),
  * "gemv_pdl" (programmatic dependent launch between GEMVs), "rows_operand_image" (batched integer-dot GEMV:
  * the activation operands are prepared once by a kernel of their own and fetched by every CTA; 0 = every CTA
  * quantises all rows itself), "operand_image_min_k" (a single row is prepared that way too from this in_dim on;

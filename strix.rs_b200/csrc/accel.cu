@@ -300,7 +300,7 @@ static std::vector<size_t> batch_small_items(const strix_cuda *h, size_t n, cons
 namespace strix {
 // "gemv.<format>.<activation form>" of a planned launch (string literals: ProfScope keeps the pointer)
 const char *gemv_prof_name(const GemvArgs &a) {
-    static const char *const names[4][3] = {{"gemv.q4_0.f32", "gemv.q4_0.q8dot", "gemv.q4_0.q8dot"},
+    static const char *const names[4][3] = {{"gemv.q4_0.f32", "gemv.q4_0.q8dot", "gemv.q4_0.f32_digits"},
                                             {"gemv.q8_0.f32", "gemv.q8_0.q8dot", "gemv.q8_0.f32_digits"},
                                             {"gemv.q6_k.f32", "gemv.q6_k.q8dot", "gemv.q6_k.f32_digits"},
                                             {"gemv.q4_1.f32", "gemv.q4_1.q8dot", "gemv.q4_1.q8dot"}};
@@ -537,6 +537,7 @@ int strix_cuda_set_option(strix_cuda *h, const char *name, long long value) {
     const uint32_t v = (uint32_t)value;
     if (n == "q6k_digits") h->tune.digits_rule = v;
     else if (n == "q8_0_digits") h->tune.q8_digits_rule = v;
+    else if (n == "q4_0_digits") h->tune.q4_digits_rule = v;
     else if (n == "gemv_warps_per_group") h->tune.force_wc = v;
     else if (n == "gemv_blocks_per_stage") h->tune.force_ct = v;
     else if (n == "gemv_stages") h->tune.force_sk = v;

@@ -358,7 +358,7 @@ __device__ __forceinline__ void multi_body(const GemvArgs &A, Cta &C) {
 }
 template <int FMT>
 __device__ __forceinline__ void multi_fmt(const GemvArgs &A, Cta &C) {
-    if constexpr (FMT == FMT_Q6_K || FMT == FMT_Q8_0) {
+    if constexpr (FMT == FMT_Q6_K || FMT == FMT_Q8_0 || FMT == FMT_Q4_0) {
         if (A.digits) return multi_body<FMT, ACT_F32_DIGITS>(A, C);
     }
     if (A.act == STRIX_ACT_F32) return multi_body<FMT, STRIX_ACT_F32>(A, C);
@@ -567,8 +567,10 @@ bool gemv_plan(GemvArgs &a, int num_sms, size_t smem_optin, const GemvTune &tune
     // Q6_K with one f32 row: the digit form (its operands take 8 bytes of shared memory per weight
     // column, so long rows, which would starve the rings, keep the f16 form)
     // (Q8_0 takes the same form by a rule of its own: its f16 form is the faster one in a burst on small launches)
-    const uint32_t digit_rule = a.L.fmt == FMT_Q8_0 ? tune.q8_digits_rule : tune.digits_rule;  // 0 = never, 1 = K <= 8192, 2 = whenever it fits
-    a.digits = ((a.L.fmt == FMT_Q6_K || a.L.fmt == FMT_Q8_0) && a.act == STRIX_ACT_F32 && nbt == 1 && digit_rule != 0 &&
+    const uint32_t digit_rule = a.L.fmt == FMT_Q8_0   ? tune.q8_digits_rule
+                                : a.L.fmt == FMT_Q4_0 ? tune.q4_digits_rule
+                                                      : tune.digits_rule;  // 0 = never, 1 = K <= 8192, 2 = whenever it fits
+    a.digits = ((a.L.fmt == FMT_Q6_K || a.L.fmt == FMT_Q8_0 || a.L.fmt == FMT_Q4_0) && a.act == STRIX_ACT_F32 && nbt == 1 && digit_rule != 0 &&
                 (K <= 8192u || digit_rule == 2))
                    ? 1u
                    : 0u;
@@ -679,7 +681,7 @@ static cudaError_t launch_t(const GemvArgs &a, cudaStream_t stream) {
 
 template <int FMT>
 static cudaError_t launch_fmt(const GemvArgs &a, cudaStream_t stream) {
-    if constexpr (FMT == FMT_Q6_K || FMT == FMT_Q8_0) {
+    if constexpr (FMT == FMT_Q6_K || FMT == FMT_Q8_0 || FMT == FMT_Q4_0) {
         if (a.digits) return launch_t<FMT, ACT_F32_DIGITS, false>(a, stream);
     }
     if (a.act == STRIX_ACT_F32) return launch_t<FMT, STRIX_ACT_F32, false>(a, stream);
@@ -718,8 +720,8 @@ bool gemv_multi_plan(GemvMultiArgs &m, int num_sms, size_t smem_optin, const Gem
     // 0.74 Q4_0 int8)
     auto slow = [&](uint32_t i) -> uint64_t {
         const GemvArgs &a = m.p[i];
-        const bool f16_tiles = a.act == STRIX_ACT_F32 && !(a.L.fmt == FMT_Q6_K && tune.digits_rule != 0 &&
-                                                            (a.L.in_dim <= 8192u || tune.digits_rule == 2));
+        const uint32_t rule = a.L.fmt == FMT_Q6_K ? tune.digits_rule : a.L.fmt == FMT_Q4_0 ? tune.q4_digits_rule : 0u;
+        const bool f16_tiles = a.act == STRIX_ACT_F32 && !(rule != 0 && (a.L.in_dim <= 8192u || rule == 2));
         if (a.L.fmt == FMT_Q8_0) return 100;
         return f16_tiles ? 155 : 125;
     };
@@ -785,7 +787,7 @@ static cudaError_t optin_fmt(size_t b) {
     STRIX_ATTR1(ACT_, MULTI_, STRIX_PRE_SWIGLU) STRIX_ATTR1(ACT_, MULTI_, STRIX_PRE_GEGLU)
     STRIX_ATTR(STRIX_ACT_F32, false) STRIX_ATTR(STRIX_ACT_Q8DOT, false)
     if constexpr (FMT != FMT_Q6_K) { STRIX_ATTR(STRIX_ACT_Q8DOT, true) }
-    if constexpr (FMT == FMT_Q6_K || FMT == FMT_Q8_0) { STRIX_ATTR(ACT_F32_DIGITS, false) }
+    if constexpr (FMT == FMT_Q6_K || FMT == FMT_Q8_0 || FMT == FMT_Q4_0) { STRIX_ATTR(ACT_F32_DIGITS, false) }
 #undef STRIX_ATTR
 #undef STRIX_ATTR1
     return e;

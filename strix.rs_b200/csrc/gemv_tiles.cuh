@@ -107,7 +107,7 @@ constexpr uint32_t SMEM_PART_OFF = 1920;
 // (integer form with more than one activation row: C columns 2t and 2t + 1 are rows 2t, 2t + 1).
 __host__ __device__ constexpr int lane_values(int act, bool multi) { return (act == STRIX_ACT_Q8DOT && multi) ? 4 : 2; }
 
-// Kernel-internal third activation form (Q6_K and Q8_0, one f32 activation row): the row is carried as THREE
+// Kernel-internal third activation form (Q6_K, Q8_0 and Q4_0, one f32 activation row): the row is carried as THREE
 // int8 digit rows, x = d * (q1 + q2 / 254 + q3 / 254^2) per 32-weight block (d = amax / 127, what is
 // left over is below 2^-24 of the block's largest value), and runs through the integer form as if
 // they were three activation rows; the epilogue adds the three partial results. The weight codes
@@ -358,11 +358,13 @@ __device__ __forceinline__ void tile_mac(uint32_t ta, uint32_t da, uint32_t xb_a
             return;
         }
         if (ACT == ACT_F32_DIGITS) {
-            // Q8_0 against the digit operands (the Q6_K layout: columns 2j, 2j + 1 = digit j against the first / last
-            // 16 weights; the record holds d_x(j) and -32 * sum(codes) of each half, the stored weight codes carry
-            // +128): y += (d_w * d_x) * (isum_first + isum_last - 128 * sum(codes))
+            // Q8_0 / Q4_0 against the digit operands (the Q6_K layout: columns 2j, 2j + 1 = digit j against the first /
+            // last 16 weights; the record holds d_x(j) and -32 * sum(codes) of each half, the stored weight codes carry
+            // +128 / +8): y += (d_w * d_x) * (isum_first + isum_last - bias * sum(codes))
             const uint4 r = lds128(xr_a);
-            const int cin[4] = {4 * (int)r.y, 4 * (int)r.z, 4 * (int)r.y, 4 * (int)r.z};
+            // (-32 * sum is a multiple of 32: the shift is exact)
+            const int k0 = FMT == FMT_Q8_0 ? 4 * (int)r.y : ((int)r.y >> 2), k1 = FMT == FMT_Q8_0 ? 4 * (int)r.z : ((int)r.z >> 2);
+            const int cin[4] = {k0, k1, k0, k1};
             mma_u8s8_c(c, W0, W1, W2, W3, xq.x, xq.y, cin);
             const float dx = __uint_as_float(r.x);
             acc[0] = fmaf(dx * d.x, (float)(c[0] + c[1]), acc[0]);

@@ -89,6 +89,7 @@ struct GemvArgs {
 struct GemvTune {
     uint32_t digits_rule = 1;  // Q6_K with one f32 row as three int8 digit rows: 0 never, 1 for in_dim <= 8192, 2 whenever it fits
     uint32_t q8_digits_rule = 1;  // the same for Q8_0
+    uint32_t q4_digits_rule = 1;  // ... and for Q4_0
     uint32_t force_wc = 0, force_ct = 0, force_sk = 0;  // warps per row group / blocks per stage / stages per slot (0 = planned)
     uint32_t pdl = 1;          // programmatic stream serialization between GEMV launches
     uint32_t xop = 1;          // batched integer-dot GEMV: operands prepared once by a kernel of their own (0 = by every CTA)
