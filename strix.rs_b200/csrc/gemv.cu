@@ -20,6 +20,10 @@
 //     two f16 numbers (x = hi + lo to 2^-22), so that the f32 result keeps f32 accuracy. The code
 //     biases (+128, +8, +32, +1024) are removed with the per-block sums of x, and the block scale is
 //     applied to the block's sum, as the reference does.
+//   * One f32 activation row of up to 8192 elements (Q4_0, Q8_0, Q6_K) does not take the f16 tiles: it is carried
+//     as three int8 digits per value and runs through the integer tile as three activation rows (gemv_tiles.cuh,
+//     ACT_F32_DIGITS): no byte -> f16 conversion, one MMA per tile, f32 accuracy; the form that holds its burst
+//     time under sustained load.
 //   * Without the tensor cores the kernel was bound by instruction issue (about 85 instructions per
 //     16 weights x 32 lanes for Q8_0, more for Q6_K); a tile now costs about 25, which leaves the
 //     memory pipeline as the limit and makes activation rows 2..8 almost free.
