@@ -154,6 +154,33 @@ def test_q6k_f32_forms_agree(accel, orc, synth, rule, out_dim, in_dim):
     assert accel.set_option("no_such_knob", 1) is False
 
 
+@pytest.mark.parametrize("rule", [0, 2])
+@pytest.mark.parametrize("fmt", ["q8_0", "q4_0"])
+@pytest.mark.parametrize("out_dim,in_dim", [(300, 256), (1030, 2560), (64, 9728)])
+def test_q8_0_and_q4_0_f32_forms_agree(accel, orc, synth, fmt, rule, out_dim, in_dim):
+    """Q8_0 and Q4_0 with one f32 row, like Q6_K: f16 tensor-core tiles (rule 0) or the three-digit int8 form
+    (rule 2 = whenever it fits; the default takes it up to 8192 elements). Both at f32 rounding level from the f64
+    product of the dequantised weight, and inside the contract against the oracle."""
+    ty = synth.Q8_0 if fmt == "q8_0" else synth.Q4_0
+    opt = fmt + "_digits"
+    assert accel.set_option(opt, rule)
+    try:
+        key = "dg." + fmt
+        w = synth.quant(ty, 43, key, out_dim, in_dim)
+        assert uploader(accel, synth, ty)(key, w, in_dim, out_dim)
+        W = accel.dequant_to_f32(key).reshape(out_dim, in_dim).astype(np.float64)
+        for seed, scale in ((1, 1.0), (2, 1e-4), (3, 3e3)):
+            x = (synth.normal(seed, key + ".x", in_dim) * scale).astype(np.float32)
+            x[::7] = 0.0                      # zeros inside blocks
+            x[32:64] = 0.0                    # an all-zero block
+            got = accel.gemv(key, x)
+            assert rel_l2(got, W @ x.astype(np.float64)) <= 2e-6
+            assert rel_l2(got, orc.qmatmul(x, w, ty, in_dim, out_dim)) <= REL_L2_TOL
+        assert accel.device_status() == 0
+    finally:
+        assert accel.set_option(opt, 1)
+
+
 def test_lm_head_shapes(accel, orc, synth):
     # the 2560 -> 151936 lm_head of the benchmark, Q8_0 and Q6_K; every row must be written
     # (the reference once left half the rows unwritten through a grid-size slip, README.md:125-128)
